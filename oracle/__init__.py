@@ -1,0 +1,323 @@
+"""ctypes front end of the CPU oracle (``smelt_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by the smoke check and by the CPU-baseline
+and reference legs of ``bench.py``; never by the ``smelt_b200`` package.  Every function takes
+and returns numpy arrays; fp16 data travels as ``np.float16`` (viewed as uint16 at the ABI).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libsmelt_oracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile ``smelt_oracle.c`` into ``libsmelt_oracle.so`` (gcc, OpenMP, no FMA contraction)."""
+    src = os.path.join(_HERE, "smelt_oracle.c")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.so_model_create.restype = C.c_void_p
+        _lib.so_argmax_f16.restype = C.c_int32
+    return _lib
+
+
+class OracleError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"oracle {what} failed with code {code}")
+        self.code = code
+
+
+GEOMETRY, INVALID_CODE = -1, -2
+BINARY1, TERNARY2 = 1, 2
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _h(a) -> np.ndarray:
+    a = np.ascontiguousarray(a)
+    assert a.dtype == np.float16, a.dtype
+    return a
+
+
+def _u8(a) -> np.ndarray:
+    a = np.ascontiguousarray(a)
+    assert a.dtype == np.uint8, a.dtype
+    return a
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise OracleError(rc, what)
+
+
+def num_threads() -> int:
+    return lib().so_num_threads()
+
+
+def set_num_threads(n: int) -> None:
+    lib().so_set_num_threads(int(n))
+
+
+# ── affine u4 ────────────────────────────────────────────────────────────────
+def affine_quantize(values: np.ndarray, group: int):
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    rows, cols = values.shape
+    groups = (cols + group - 1) // group
+    packed = np.zeros((rows, (cols + 1) // 2), np.uint8)
+    scales = np.zeros((rows, groups), np.float16)
+    biases = np.zeros((rows, groups), np.float16)
+    for r in range(rows):
+        _check(lib().so_affine_u4_quantize_row(_p(values[r]), cols, group, _p(packed[r]), _p(scales[r]), _p(biases[r])),
+               "affine_u4_quantize_row")
+    return packed, scales, biases
+
+
+def affine_dequantize(packed, scales, biases, cols: int, group: int) -> np.ndarray:
+    packed, scales, biases = _u8(packed), _h(scales), _h(biases)
+    rows = packed.shape[0]
+    out = np.zeros((rows, cols), np.float32)
+    for r in range(rows):
+        _check(lib().so_affine_u4_dequantize_row(_p(packed[r]), _p(scales[r]), _p(biases[r]), cols, group, _p(out[r])),
+               "affine_u4_dequantize_row")
+    return out
+
+
+def affine_dequantize_f16(packed, scales, biases, rows: int, cols: int, group: int) -> np.ndarray:
+    out = np.zeros((rows, cols), np.float16)
+    _check(lib().so_affine_u4_dequantize_rows_f16(_p(_u8(packed)), _p(_h(scales)), _p(_h(biases)), rows, cols, group, _p(out)),
+           "affine_u4_dequantize_rows_f16")
+    return out
+
+
+def _xb(x, cols):
+    x = _h(x)
+    x2 = x.reshape(-1, cols)
+    return x2, x2.shape[0]
+
+
+def affine_matvec(w, s, b, x, rows: int, cols: int, group: int, f32: bool = False) -> np.ndarray:
+    x2, batch = _xb(x, cols)
+    y = np.zeros((batch, rows), np.float32 if f32 else np.float16)
+    fn = lib().so_affine_matvec_f32 if f32 else lib().so_affine_matvec
+    _check(fn(_p(_u8(w)), _p(_h(s)), _p(_h(b)), _p(x2), rows, cols, group, batch, _p(y)), "affine_matvec")
+    return y
+
+
+def affine_matvec_add(w, s, b, x, residual, rows, cols, group) -> np.ndarray:
+    x2, batch = _xb(x, cols)
+    y = np.zeros((batch, rows), np.float16)
+    _check(lib().so_affine_matvec_add(_p(_u8(w)), _p(_h(s)), _p(_h(b)), _p(x2), _p(_h(residual)), rows, cols, group, batch, _p(y)),
+           "affine_matvec_add")
+    return y
+
+
+def affine_gate_up_swiglu(gw, gs, gb, uw, us, ub, x, rows, cols, group, round_gate_up: bool = False) -> np.ndarray:
+    x2, batch = _xb(x, cols)
+    y = np.zeros((batch, rows), np.float16)
+    _check(lib().so_affine_gate_up_swiglu(_p(_u8(gw)), _p(_h(gs)), _p(_h(gb)), _p(_u8(uw)), _p(_h(us)), _p(_h(ub)), _p(x2),
+                                          rows, cols, group, batch, int(round_gate_up), _p(y)), "affine_gate_up_swiglu")
+    return y
+
+
+def fp16_matvec(w, x, rows, cols) -> np.ndarray:
+    x2, batch = _xb(x, cols)
+    y = np.zeros((batch, rows), np.float16)
+    _check(lib().so_fp16_matvec(_p(_h(w)), _p(x2), rows, cols, batch, _p(y)), "fp16_matvec")
+    return y
+
+
+# ── binary / ternary ─────────────────────────────────────────────────────────
+def signed_packed_byte_count(n: int, fmt: int) -> int:
+    out = C.c_int64()
+    _check(lib().so_signed_packed_byte_count(C.c_int64(n), fmt, C.byref(out)), "signed_packed_byte_count")
+    return out.value
+
+
+def signed_groups_per_row(padded_cols: int, group: int) -> int:
+    out = C.c_int()
+    _check(lib().so_signed_groups_per_row(padded_cols, group, C.byref(out)), "signed_groups_per_row")
+    return out.value
+
+
+def signed_validate_codes(codes, logical_count: int, fmt: int):
+    codes = _u8(codes)
+    bad = C.c_int64(-1)
+    rc = lib().so_signed_validate_codes(_p(codes), C.c_int64(codes.size), C.c_int64(logical_count), fmt, C.byref(bad))
+    return rc, bad.value
+
+
+def signed_dequantize_row(fmt, codes, scales, cols, padded_cols, group) -> np.ndarray:
+    codes, scales = _u8(codes), _h(scales)
+    out = np.zeros(cols, np.float32)
+    _check(lib().so_signed_dequantize_row(fmt, _p(codes), C.c_int64(codes.size), _p(scales), C.c_int64(scales.size * 2),
+                                          cols, padded_cols, group, _p(out)), "signed_dequantize_row")
+    return out
+
+
+def signed_matvec(fmt, codes, scales, x, rows, cols, group=128, f32: bool = False) -> np.ndarray:
+    x2, batch = _xb(x, cols)
+    y = np.zeros((batch, rows), np.float32 if f32 else np.float16)
+    fn = lib().so_signed_matvec_f32 if f32 else lib().so_signed_matvec
+    _check(fn(fmt, _p(_u8(codes)), _p(_h(scales)), _p(x2), rows, cols, group, batch, _p(y)), "signed_matvec")
+    return y
+
+
+def signed_matvec_add(fmt, codes, scales, x, residual, rows, cols, group=128) -> np.ndarray:
+    x2, batch = _xb(x, cols)
+    y = np.zeros((batch, rows), np.float16)
+    _check(lib().so_signed_matvec_add(fmt, _p(_u8(codes)), _p(_h(scales)), _p(x2), _p(_h(residual)), rows, cols, group, batch, _p(y)),
+           "signed_matvec_add")
+    return y
+
+
+def signed_gate_up_swiglu(fmt, gc, gs, uc, us, x, rows, cols, group=128, staged: bool = True) -> np.ndarray:
+    x2, batch = _xb(x, cols)
+    y = np.zeros((batch, rows), np.float16)
+    _check(lib().so_signed_gate_up_swiglu(fmt, _p(_u8(gc)), _p(_h(gs)), _p(_u8(uc)), _p(_h(us)), _p(x2), rows, cols, group,
+                                          batch, int(staged), _p(y)), "signed_gate_up_swiglu")
+    return y
+
+
+def swiglu_staged(gate, up) -> np.ndarray:
+    gate, up = _h(gate), _h(up)
+    y = np.zeros(gate.shape, np.float16)
+    lib().so_swiglu_staged(_p(gate), _p(up), C.c_int64(gate.size), _p(y))
+    return y
+
+
+# ── glue ─────────────────────────────────────────────────────────────────────
+def rms_norm_1pw(x, w, eps: float, two_stage: bool = True) -> np.ndarray:
+    x, w = _h(x), _h(w)
+    y = np.zeros(x.shape, np.float16)
+    _check(lib().so_rms_norm_1pw(_p(x), _p(w), x.size, C.c_float(eps), int(two_stage), _p(y)), "rms_norm_1pw")
+    return y
+
+
+def per_head_rms_norm(x, w, heads, head_dim, eps) -> np.ndarray:
+    x, w = _h(x), _h(w)
+    y = np.zeros(x.shape, np.float16)
+    _check(lib().so_per_head_rms_norm(_p(x), _p(w), heads, head_dim, C.c_float(eps), _p(y)), "per_head_rms_norm")
+    return y
+
+
+def elementwise_add(a, b) -> np.ndarray:
+    a, b = _h(a), _h(b)
+    y = np.zeros(a.shape, np.float16)
+    lib().so_elementwise_add(_p(a), _p(b), C.c_int64(a.size), _p(y))
+    return y
+
+
+def argmax_f16(logits) -> int:
+    logits = _h(logits)
+    return int(lib().so_argmax_f16(_p(logits), C.c_int64(logits.size)))
+
+
+def apply_rope(qk, head_dim, rope_dim, heads, layout, position, base_log2=0.0, math_mode=1, cos=None, sin=None) -> np.ndarray:
+    out = _h(qk).copy()
+    cp = _p(_h(cos)) if cos is not None else None
+    sp = _p(_h(sin)) if sin is not None else None
+    _check(lib().so_apply_rope(_p(out), cp, sp, head_dim, rope_dim, heads, layout, C.c_uint32(position), C.c_float(base_log2),
+                               math_mode), "apply_rope")
+    return out
+
+
+def kv_cache_update(cache, new_kv, capacity, head_dim, pos, heads) -> np.ndarray:
+    out = _h(cache).copy()
+    _check(lib().so_kv_cache_update(_p(out), _p(_h(new_kv)), capacity, head_dim, pos, heads), "kv_cache_update")
+    return out
+
+
+def rope_kv_cache_update(cache, new_kv, capacity, head_dim, pos, heads, rope_dim, layout, base_log2=0.0, math_mode=1,
+                         cos=None, sin=None) -> np.ndarray:
+    out = _h(cache).copy()
+    cp = _p(_h(cos)) if cos is not None else None
+    sp = _p(_h(sin)) if sin is not None else None
+    _check(lib().so_rope_kv_cache_update(_p(out), _p(_h(new_kv)), cp, sp, capacity, head_dim, pos, heads, rope_dim, layout,
+                                         C.c_float(base_log2), math_mode), "rope_kv_cache_update")
+    return out
+
+
+def attention_decode(q, k_cache, v_cache, n_q, n_kv, head_dim, capacity, seq_len, scale=None, sliding_window=0) -> np.ndarray:
+    q, k_cache, v_cache = _h(q), _h(k_cache), _h(v_cache)
+    if scale is None:
+        scale = 1.0 / np.sqrt(np.float32(head_dim))
+    out = np.zeros((n_q, head_dim), np.float16)
+    _check(lib().so_attention_decode(_p(q), _p(k_cache), _p(v_cache), n_q, n_kv, head_dim, capacity, seq_len,
+                                     C.c_float(scale), sliding_window, _p(out)), "attention_decode")
+    return out
+
+
+# ── whole decoder ────────────────────────────────────────────────────────────
+class Model:
+    """Greedy decoder over packed weights held in numpy arrays (kept alive by this object)."""
+
+    WHICH = {"q": 0, "k": 1, "v": 2, "o": 3, "gate": 4, "up": 5, "down": 6}
+
+    def __init__(self, cfg: dict, capacity: int):
+        self.cfg = dict(cfg)
+        self.capacity = capacity
+        self._keep = []
+        self._m = C.c_void_p(lib().so_model_create(
+            cfg["layers"], cfg["hidden"], cfg["inter"], cfg["n_q"], cfg["n_kv"], cfg["head_dim"], cfg["vocab"],
+            cfg.get("group", 64), capacity, C.c_float(cfg.get("eps", 1e-6)), C.c_float(cfg.get("rope_theta", 1e6))))
+        if not self._m:
+            raise MemoryError("so_model_create")
+
+    def close(self):
+        if self._m:
+            lib().so_model_destroy(self._m)
+            self._m = None
+
+    def __del__(self):
+        self.close()
+
+    def set_globals(self, embedding, lm_head, final_norm):
+        arrs = [_h(embedding), _h(lm_head), _h(final_norm)]
+        self._keep += arrs
+        lib().so_model_set_globals(self._m, *[_p(a) for a in arrs])
+
+    def set_layer(self, layer: int, tensors: dict, input_norm, post_norm):
+        for name, idx in self.WHICH.items():
+            w, s, b = tensors[name]
+            arrs = [_u8(w), _h(s), _h(b)]
+            self._keep += arrs
+            _check(lib().so_model_set_affine(self._m, layer, idx, *[_p(a) for a in arrs]), "model_set_affine")
+        arrs = [_h(input_norm), _h(post_norm)]
+        self._keep += arrs
+        _check(lib().so_model_set_norms(self._m, layer, *[_p(a) for a in arrs]), "model_set_norms")
+
+    def reset(self):
+        lib().so_model_reset_cache(self._m)
+
+    def decode_step(self, token: int, position: int, want_logits: bool = False):
+        logits = np.zeros(self.cfg["vocab"], np.float16) if want_logits else None
+        out = C.c_int32(-1)
+        _check(lib().so_model_decode_step(self._m, C.c_int32(token), position, _p(logits) if want_logits else None,
+                                          C.byref(out)), "model_decode_step")
+        return (out.value, logits) if want_logits else out.value
+
+    def generate(self, prompt, n_decode: int):
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        toks = np.zeros(n_decode, np.int32)
+        margins = np.zeros(n_decode, np.float32)
+        _check(lib().so_model_generate(self._m, _p(prompt), prompt.size, n_decode, _p(toks), _p(margins)), "model_generate")
+        return toks, margins

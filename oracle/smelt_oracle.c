@@ -1,0 +1,819 @@
+/*
+ * smelt_oracle.c — CPU restatement of the reference's scalar oracles for the decode hot path.
+ *
+ * TEST INFRASTRUCTURE ONLY. Nothing in the product library links, imports or executes this
+ * file; only the test-suite, the smoke check and the CPU-baseline leg of the benchmark do.
+ * The reference (Swift + Metal) cannot be compiled on Linux, so every function restates the
+ * scalar Swift (or, where no Swift oracle exists, the Metal kernel's arithmetic) it cites, in
+ * the same evaluation order, in fp32 with no fused multiply-add (build with
+ * -ffp-contract=off).  The restatement is pinned against the reference's own known-answer
+ * vectors in tests/test_oracle_golden.py.
+ *
+ * Conventions: fp16 values cross the ABI as uint16_t bit patterns; "f32" arrays are float.
+ * All functions return 0 on success or a negative SO_ERR_* code.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define SO_OK 0
+#define SO_ERR_GEOMETRY (-1)
+#define SO_ERR_INVALID_CODE (-2)
+#define SO_ERR_ALLOC (-3)
+
+#define SO_API __attribute__((visibility("default")))
+
+/* ───────────────────────── fp16 helpers ───────────────────────── */
+
+static inline float h2f(uint16_t h) {
+    _Float16 v;
+    memcpy(&v, &h, 2);
+    return (float)v;
+}
+static inline uint16_t f2h(float f) {
+    _Float16 v = (_Float16)f; /* round-to-nearest-even, as Swift's Float16(Float) */
+    uint16_t h;
+    memcpy(&h, &v, 2);
+    return h;
+}
+static inline float round_h(float f) { return h2f(f2h(f)); }
+
+SO_API int so_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+SO_API void so_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+SO_API void so_f16_to_f32(const uint16_t *in, float *out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = h2f(in[i]);
+}
+SO_API void so_f32_to_f16(const float *in, uint16_t *out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = f2h(in[i]);
+}
+
+/* ───────────────────────── affine u4 codec ─────────────────────────
+ * Sources/SmeltCompiler/SmeltAffineU4.swift:94-161.  Two nibbles per byte, LOW nibble =
+ * even column; scale = (max-min)/15 (1 when the range is below 1e-12), bias = min; the
+ * dequantised value is float(nibble) * float(fp16 scale) + float(fp16 bias), a separate
+ * multiply and add.
+ */
+SO_API int so_affine_u4_quantize_row(const float *values, int cols, int group, uint8_t *packed,
+                                     uint16_t *scales, uint16_t *biases) {
+    if (cols <= 0 || group <= 0) return SO_ERR_GEOMETRY;
+    int groups = (cols + group - 1) / group;
+    for (int g = 0; g < groups; ++g) {
+        int c0 = g * group, c1 = c0 + group < cols ? c0 + group : cols;
+        float lo = INFINITY, hi = -INFINITY;
+        for (int c = c0; c < c1; ++c) {
+            float v = values[c];
+            if (v < lo) lo = v;
+            if (v > hi) hi = v;
+        }
+        float range = hi - lo;
+        float scale = range < 1e-12f ? 1.0f : range / 15.0f;
+        scales[g] = f2h(scale);
+        biases[g] = f2h(lo);
+        float inv = 1.0f / scale;
+        for (int c = c0; c < c1; ++c) {
+            float n = (values[c] - lo) * inv;
+            n = n < 0.0f ? 0.0f : (n > 15.0f ? 15.0f : n);
+            uint8_t nib = (uint8_t)roundf(n); /* Swift .rounded(): half away from zero */
+            if ((c & 1) == 0) packed[c >> 1] = nib;
+            else packed[c >> 1] |= (uint8_t)(nib << 4);
+        }
+    }
+    return SO_OK;
+}
+
+SO_API int so_affine_u4_dequantize_row(const uint8_t *packed, const uint16_t *scales,
+                                       const uint16_t *biases, int cols, int group, float *out) {
+    if (cols <= 0 || group <= 0) return SO_ERR_GEOMETRY;
+    int groups = (cols + group - 1) / group;
+    for (int g = 0; g < groups; ++g) {
+        int c0 = g * group, c1 = c0 + group < cols ? c0 + group : cols;
+        float scale = h2f(scales[g]), bias = h2f(biases[g]);
+        for (int c = c0; c < c1; ++c) {
+            uint8_t byte = packed[c >> 1];
+            uint8_t nib = (c & 1) == 0 ? (byte & 0x0F) : (byte >> 4);
+            out[c] = (float)nib * scale + bias;
+        }
+    }
+    return SO_OK;
+}
+
+/* The on-device form of the same dequant, rounded to fp16 when stored
+ * (Resources/Shaders/lut_matvec.metal:994-1025, affine_embedding_gather). */
+SO_API int so_affine_u4_dequantize_rows_f16(const uint8_t *packed, const uint16_t *scales,
+                                            const uint16_t *biases, int rows, int cols, int group,
+                                            uint16_t *out) {
+    if (cols <= 0 || group <= 0 || cols % 2) return SO_ERR_GEOMETRY;
+    int groups = cols / group;
+    if (groups * group != cols) return SO_ERR_GEOMETRY;
+    for (int r = 0; r < rows; ++r) {
+        const uint8_t *p = packed + (size_t)r * (cols / 2);
+        for (int c = 0; c < cols; ++c) {
+            uint8_t byte = p[c >> 1];
+            uint8_t nib = (c & 1) == 0 ? (byte & 0x0F) : (byte >> 4);
+            float s = h2f(scales[(size_t)r * groups + c / group]);
+            float b = h2f(biases[(size_t)r * groups + c / group]);
+            out[(size_t)r * cols + c] = f2h((float)nib * s + b);
+        }
+    }
+    return SO_OK;
+}
+
+/* ───────────────────────── affine matvec ─────────────────────────
+ * Tests/SmeltCompilerTests/Helpers/MetalKernelTestSupport.swift:396-428
+ * (referenceAffineMatvecRow): per group, dot += float(nibble)*x and xsum += x in column
+ * order; acc += scale*dot + bias*xsum; optional fp16 rounding of the row result.
+ */
+static inline float affine_row_acc(const uint8_t *w, const uint16_t *s, const uint16_t *b,
+                                   const float *x, int cols, int group) {
+    int groups = cols / group;
+    float acc = 0.0f;
+    for (int g = 0; g < groups; ++g) {
+        float scale = h2f(s[g]), bias = h2f(b[g]);
+        int base = g * group;
+        float dot = 0.0f, xsum = 0.0f;
+        for (int i = 0; i < group; ++i) {
+            int col = base + i;
+            uint8_t byte = w[col >> 1];
+            uint8_t nib = (col & 1) == 0 ? (byte & 0x0F) : (byte >> 4);
+            float xv = x[col];
+            dot += (float)nib * xv;
+            xsum += xv;
+        }
+        acc += scale * dot + bias * xsum;
+    }
+    return acc;
+}
+
+/* Four rows at once: the same per-row arithmetic in the same order as affine_row_acc, with
+ * the four independent dependency chains interleaved so the CPU's add latency is hidden. */
+static inline void affine_row_acc4(const uint8_t *w, size_t wstride, const uint16_t *s, const uint16_t *b,
+                                   size_t sstride, const float *x, int cols, int group, float out[4]) {
+    int groups = cols / group;
+    float acc[4] = {0, 0, 0, 0};
+    for (int g = 0; g < groups; ++g) {
+        int base = g * group;
+        float dot[4] = {0, 0, 0, 0}, xsum[4] = {0, 0, 0, 0};
+        for (int i = 0; i < group; i += 2) {
+            int col = base + i;
+            float x0 = x[col], x1 = x[col + 1];
+            for (int r = 0; r < 4; ++r) {
+                uint8_t byte = w[r * wstride + (col >> 1)];
+                dot[r] += (float)(byte & 0x0F) * x0;
+                xsum[r] += x0;
+                dot[r] += (float)(byte >> 4) * x1;
+                xsum[r] += x1;
+            }
+        }
+        for (int r = 0; r < 4; ++r)
+            acc[r] += h2f(s[r * sstride + g]) * dot[r] + h2f(b[r * sstride + g]) * xsum[r];
+    }
+    for (int r = 0; r < 4; ++r) out[r] = acc[r];
+}
+
+static int affine_geometry_ok(int rows, int cols, int group, int batch) {
+    return rows > 0 && cols > 0 && group > 0 && batch > 0 && cols % group == 0 && cols % 2 == 0;
+}
+
+/* y_f32[b*rows + r] = acc (not rounded).  x is fp16 [batch, cols]. */
+static int affine_matvec_acc(const uint8_t *w, const uint16_t *s, const uint16_t *bz,
+                             const uint16_t *x_f16, int rows, int cols, int group, int batch,
+                             float *y) {
+    if (!affine_geometry_ok(rows, cols, group, batch)) return SO_ERR_GEOMETRY;
+    float *x = (float *)malloc(sizeof(float) * (size_t)batch * cols);
+    if (!x) return SO_ERR_ALLOC;
+    so_f16_to_f32(x_f16, x, (int64_t)batch * cols);
+    int groups = cols / group;
+    int blocks = (rows + 3) / 4;
+#pragma omp parallel for schedule(static)
+    for (int blk = 0; blk < blocks; ++blk) {
+        int r0 = blk * 4;
+        const uint8_t *wr = w + (size_t)r0 * (cols / 2);
+        const uint16_t *sr = s + (size_t)r0 * groups, *br = bz + (size_t)r0 * groups;
+        if (r0 + 4 <= rows && group % 2 == 0) {
+            for (int b = 0; b < batch; ++b) {
+                float out[4];
+                affine_row_acc4(wr, (size_t)cols / 2, sr, br, (size_t)groups, x + (size_t)b * cols, cols, group, out);
+                for (int r = 0; r < 4; ++r) y[(size_t)b * rows + r0 + r] = out[r];
+            }
+        } else {
+            for (int r = r0; r < rows && r < r0 + 4; ++r)
+                for (int b = 0; b < batch; ++b)
+                    y[(size_t)b * rows + r] = affine_row_acc(w + (size_t)r * (cols / 2), s + (size_t)r * groups,
+                                                             bz + (size_t)r * groups, x + (size_t)b * cols, cols, group);
+        }
+    }
+    free(x);
+    return SO_OK;
+}
+
+/* affine_matvec: y = half(acc).  Kernel contract: lut_matvec.metal:1157-1287. */
+SO_API int so_affine_matvec(const uint8_t *w, const uint16_t *s, const uint16_t *b,
+                            const uint16_t *x, int rows, int cols, int group, int batch,
+                            uint16_t *y) {
+    float *acc = (float *)malloc(sizeof(float) * (size_t)batch * rows);
+    if (!acc) return SO_ERR_ALLOC;
+    int rc = affine_matvec_acc(w, s, b, x, rows, cols, group, batch, acc);
+    if (rc == SO_OK) so_f32_to_f16(acc, y, (int64_t)batch * rows);
+    free(acc);
+    return rc;
+}
+
+/* Unrounded fp32 accumulators, for error analysis in the tests. */
+SO_API int so_affine_matvec_f32(const uint8_t *w, const uint16_t *s, const uint16_t *b,
+                                const uint16_t *x, int rows, int cols, int group, int batch,
+                                float *y) {
+    return affine_matvec_acc(w, s, b, x, rows, cols, group, batch, y);
+}
+
+/* fused_affine_matvec_add (lut_matvec.metal:1718-1817): the matvec result is rounded to
+ * fp16 first, then added to the fp16 residual with an fp16 add (:1802-1803). */
+SO_API int so_affine_matvec_add(const uint8_t *w, const uint16_t *s, const uint16_t *b,
+                                const uint16_t *x, const uint16_t *residual, int rows, int cols,
+                                int group, int batch, uint16_t *y) {
+    float *acc = (float *)malloc(sizeof(float) * (size_t)batch * rows);
+    if (!acc) return SO_ERR_ALLOC;
+    int rc = affine_matvec_acc(w, s, b, x, rows, cols, group, batch, acc);
+    if (rc == SO_OK)
+        for (int64_t i = 0; i < (int64_t)batch * rows; ++i)
+            y[i] = f2h(round_h(acc[i]) + h2f(residual[i]));
+    free(acc);
+    return rc;
+}
+
+/* fused_affine_gate_up_swiglu.  round_gate_up = 0: gate and up stay fp32 into SiLU, one
+ * rounding at the end (kernel lut_matvec.metal:2228; oracle
+ * Tests/SmeltCompilerTests/RegionExactnessTests.swift:346-360).  round_gate_up = 1: gate and
+ * up are each rounded to fp16 first (Tests/SmeltCompilerTests/PrefillKernelTests.swift:390-430). */
+SO_API int so_affine_gate_up_swiglu(const uint8_t *gw, const uint16_t *gs, const uint16_t *gb,
+                                    const uint8_t *uw, const uint16_t *us, const uint16_t *ub,
+                                    const uint16_t *x, int rows, int cols, int group, int batch,
+                                    int round_gate_up, uint16_t *y) {
+    size_t n = (size_t)batch * rows;
+    float *g = (float *)malloc(sizeof(float) * n), *u = (float *)malloc(sizeof(float) * n);
+    if (!g || !u) { free(g); free(u); return SO_ERR_ALLOC; }
+    int rc = affine_matvec_acc(gw, gs, gb, x, rows, cols, group, batch, g);
+    if (rc == SO_OK) rc = affine_matvec_acc(uw, us, ub, x, rows, cols, group, batch, u);
+    if (rc == SO_OK)
+        for (size_t i = 0; i < n; ++i) {
+            float gv = g[i], uv = u[i];
+            if (round_gate_up) { gv = round_h(gv); uv = round_h(uv); }
+            y[i] = f2h(gv / (1.0f + expf(-gv)) * uv);
+        }
+    free(g); free(u);
+    return rc;
+}
+
+/* ───────────────────────── dense fp16 matvec ─────────────────────────
+ * Resources/Shaders/lut_matvec.metal:799-834 (fp16_matvec): fp32 accumulation, clamp to
+ * ±65504, fp16 out.  No Swift scalar twin exists; summation is in column order.
+ */
+SO_API int so_fp16_matvec(const uint16_t *w, const uint16_t *x_f16, int rows, int cols, int batch,
+                          uint16_t *y) {
+    if (rows <= 0 || cols <= 0 || batch <= 0) return SO_ERR_GEOMETRY;
+    float *x = (float *)malloc(sizeof(float) * (size_t)batch * cols);
+    if (!x) return SO_ERR_ALLOC;
+    so_f16_to_f32(x_f16, x, (int64_t)batch * cols);
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t *wr = w + (size_t)r * cols;
+        for (int b = 0; b < batch; ++b) {
+            const float *xb = x + (size_t)b * cols;
+            float acc = 0.0f;
+            for (int c = 0; c < cols; ++c) acc += h2f(wr[c]) * xb[c];
+            acc = acc < -65504.0f ? -65504.0f : (acc > 65504.0f ? 65504.0f : acc);
+            y[(size_t)b * rows + r] = f2h(acc);
+        }
+    }
+    free(x);
+    return SO_OK;
+}
+
+/* ───────────────────────── binary1 / ternary2 codec ─────────────────────────
+ * Sources/SmeltRuntime/SmeltSignedQuantCodec.swift:22-35 (semanticCode), :102-124 (code,
+ * LSB-first), :219-257 (dequantizeRow).  format: 1 = binary1 (0 -> -1, 1 -> +1),
+ * 2 = ternary2 (0 -> -1, 1 -> 0, 2 -> +1, 3 invalid).
+ */
+static inline int signed_bits(int format) { return format == 1 ? 1 : (format == 2 ? 2 : 0); }
+
+SO_API int so_signed_packed_byte_count(int64_t logical_count, int format, int64_t *out) {
+    int bits = signed_bits(format);
+    if (!bits || logical_count < 0) return SO_ERR_GEOMETRY;
+    *out = (logical_count * bits + 7) / 8;
+    return SO_OK;
+}
+
+SO_API int so_signed_groups_per_row(int padded_cols, int group, int *out) {
+    if (padded_cols <= 0 || group <= 0 || padded_cols % group != 0) return SO_ERR_GEOMETRY;
+    *out = padded_cols / group;
+    return SO_OK;
+}
+
+static inline uint8_t signed_code_at(const uint8_t *bytes, int64_t idx, int bits) {
+    int64_t bit = idx * bits;
+    return (uint8_t)((bytes[bit >> 3] >> (bit & 7)) & ((1u << bits) - 1u));
+}
+
+/* Returns SO_ERR_INVALID_CODE and the first offending logical index when a ternary code 3
+ * is present (validateCodes, :127-147). */
+SO_API int so_signed_validate_codes(const uint8_t *codes, int64_t byte_count, int64_t logical_count,
+                                    int format, int64_t *bad_index) {
+    int bits = signed_bits(format);
+    if (!bits || logical_count < 0) return SO_ERR_GEOMETRY;
+    if (byte_count < (logical_count * bits + 7) / 8) return SO_ERR_GEOMETRY;
+    if (format != 2) return SO_OK;
+    for (int64_t i = 0; i < logical_count; ++i)
+        if (signed_code_at(codes, i, 2) == 3) {
+            if (bad_index) *bad_index = i;
+            return SO_ERR_INVALID_CODE;
+        }
+    return SO_OK;
+}
+
+SO_API int so_signed_dequantize_row(int format, const uint8_t *codes, int64_t code_bytes,
+                                    const uint16_t *scales, int64_t scale_bytes, int cols,
+                                    int padded_cols, int group, float *out) {
+    int bits = signed_bits(format);
+    if (!bits || cols <= 0 || cols > padded_cols) return SO_ERR_GEOMETRY;
+    int groups;
+    if (so_signed_groups_per_row(padded_cols, group, &groups)) return SO_ERR_GEOMETRY;
+    if (code_bytes < ((int64_t)padded_cols * bits + 7) / 8) return SO_ERR_GEOMETRY;
+    if (scale_bytes < (int64_t)groups * 2) return SO_ERR_GEOMETRY;
+    int rc = so_signed_validate_codes(codes, code_bytes, padded_cols, format, NULL);
+    if (rc) return rc;
+    for (int c = 0; c < cols; ++c) {
+        uint8_t code = signed_code_at(codes, c, bits);
+        int sem = format == 1 ? (code == 0 ? -1 : 1) : (int)code - 1;
+        out[c] = (float)sem * h2f(scales[c / group]);
+    }
+    return SO_OK;
+}
+
+/* ───────────────────────── binary / ternary matvec ─────────────────────────
+ * Tests/SmeltCompilerTests/SignedQuantKernelTests.swift:1030-1045: one fp32 accumulator per
+ * (batch,row), expected += x * semantic * scale in column order.  row_stride_bytes is the
+ * packed row stride (padded_cols*bits/8).
+ */
+static int signed_matvec_acc(int format, const uint8_t *codes, const uint16_t *scales,
+                             const uint16_t *x_f16, int rows, int cols, int group, int batch,
+                             float *y) {
+    int bits = signed_bits(format);
+    if (!bits || rows <= 0 || cols <= 0 || group <= 0 || batch <= 0 || cols % group) return SO_ERR_GEOMETRY;
+    int groups = cols / group;
+    size_t row_bytes = (size_t)cols * bits / 8;
+    float *x = (float *)malloc(sizeof(float) * (size_t)batch * cols);
+    if (!x) return SO_ERR_ALLOC;
+    so_f16_to_f32(x_f16, x, (int64_t)batch * cols);
+    int bad = 0;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const uint8_t *cr = codes + (size_t)r * row_bytes;
+        const uint16_t *sr = scales + (size_t)r * groups;
+        for (int b = 0; b < batch; ++b) {
+            const float *xb = x + (size_t)b * cols;
+            float acc = 0.0f;
+            for (int c = 0; c < cols; ++c) {
+                uint8_t code = signed_code_at(cr, c, bits);
+                float sem;
+                if (format == 1) sem = code == 0 ? -1.0f : 1.0f;
+                else {
+                    if (code == 3) { bad = 1; sem = 0.0f; }
+                    else sem = (float)((int)code - 1);
+                }
+                acc += xb[c] * sem * h2f(sr[c / group]);
+            }
+            y[(size_t)b * rows + r] = acc;
+        }
+    }
+    free(x);
+    return bad ? SO_ERR_INVALID_CODE : SO_OK;
+}
+
+SO_API int so_signed_matvec(int format, const uint8_t *codes, const uint16_t *scales,
+                            const uint16_t *x, int rows, int cols, int group, int batch,
+                            uint16_t *y) {
+    float *acc = (float *)malloc(sizeof(float) * (size_t)batch * rows);
+    if (!acc) return SO_ERR_ALLOC;
+    int rc = signed_matvec_acc(format, codes, scales, x, rows, cols, group, batch, acc);
+    if (rc == SO_OK) so_f32_to_f16(acc, y, (int64_t)batch * rows);
+    free(acc);
+    return rc;
+}
+
+SO_API int so_signed_matvec_f32(int format, const uint8_t *codes, const uint16_t *scales,
+                                const uint16_t *x, int rows, int cols, int group, int batch,
+                                float *y) {
+    return signed_matvec_acc(format, codes, scales, x, rows, cols, group, batch, y);
+}
+
+/* signed_*_matvec_add (Resources/Shaders/signed_quant.metal:271-278): half(float(half(acc))
+ * + float(residual)). */
+SO_API int so_signed_matvec_add(int format, const uint8_t *codes, const uint16_t *scales,
+                                const uint16_t *x, const uint16_t *residual, int rows, int cols,
+                                int group, int batch, uint16_t *y) {
+    float *acc = (float *)malloc(sizeof(float) * (size_t)batch * rows);
+    if (!acc) return SO_ERR_ALLOC;
+    int rc = signed_matvec_acc(format, codes, scales, x, rows, cols, group, batch, acc);
+    if (rc == SO_OK)
+        for (int64_t i = 0; i < (int64_t)batch * rows; ++i)
+            y[i] = f2h(round_h(acc[i]) + h2f(residual[i]));
+    free(acc);
+    return rc;
+}
+
+/* Staged-fp16 SwiGLU shared by the signed kernels and swiglu_fused
+ * (Resources/Shaders/signed_quant.metal:15-20, activations_precise.metal:9-22): every
+ * intermediate is an fp16 value: tail = 1/(1+exp(|g|)), sigmoid = g<0 ? tail : 1-tail,
+ * activated = g*sigmoid, out = activated*up. */
+static inline uint16_t swiglu_staged_half(uint16_t gate, uint16_t up) {
+    float g = h2f(gate);
+    float e = round_h(expf(fabsf(g)));
+    float denom = round_h(1.0f + e);
+    float tail = round_h(1.0f / denom);
+    float sig = g < 0.0f ? tail : round_h(1.0f - tail);
+    float act = round_h(g * sig);
+    return f2h(act * h2f(up));
+}
+
+SO_API void so_swiglu_staged(const uint16_t *gate, const uint16_t *up, int64_t n, uint16_t *y) {
+    for (int64_t i = 0; i < n; ++i) y[i] = swiglu_staged_half(gate[i], up[i]);
+}
+
+/* signed_*_gate_up_swiglu.  staged = 1: the kernel's staged-fp16 chain (signed_quant.metal
+ * :15-20).  staged = 0: the test oracle's form, gate and up rounded to fp16 then
+ * half(clamp(g/(1+exp(-g))*u, ±65504)) (SignedQuantKernelTests.swift:1210-1226). */
+SO_API int so_signed_gate_up_swiglu(int format, const uint8_t *gc, const uint16_t *gs,
+                                    const uint8_t *uc, const uint16_t *us, const uint16_t *x,
+                                    int rows, int cols, int group, int batch, int staged,
+                                    uint16_t *y) {
+    size_t n = (size_t)batch * rows;
+    float *g = (float *)malloc(sizeof(float) * n), *u = (float *)malloc(sizeof(float) * n);
+    if (!g || !u) { free(g); free(u); return SO_ERR_ALLOC; }
+    int rc = signed_matvec_acc(format, gc, gs, x, rows, cols, group, batch, g);
+    if (rc == SO_OK) rc = signed_matvec_acc(format, uc, us, x, rows, cols, group, batch, u);
+    if (rc == SO_OK)
+        for (size_t i = 0; i < n; ++i) {
+            uint16_t gh = f2h(g[i]), uh = f2h(u[i]);
+            if (staged) y[i] = swiglu_staged_half(gh, uh);
+            else {
+                float gv = h2f(gh), uv = h2f(uh);
+                float v = gv / (1.0f + expf(-gv)) * uv;
+                v = v < -65504.0f ? -65504.0f : (v > 65504.0f ? 65504.0f : v);
+                y[i] = f2h(v);
+            }
+        }
+    free(g); free(u);
+    return rc;
+}
+
+/* ───────────────────────── glue ───────────────────────── */
+
+/* rms_norm_1pw.  two_stage = 0: Tests/.../MetalKernelTestSupport.swift:227-243 (cpuRmsNorm1pw),
+ * one rounding of x*invRms*(1+w).  two_stage = 1: the kernel's rounding points
+ * (Resources/Shaders/norms.metal:58-63): half(x*rs) times half(1+w) as an fp16 product. */
+SO_API int so_rms_norm_1pw(const uint16_t *x, const uint16_t *w, int dim, float eps, int two_stage,
+                           uint16_t *y) {
+    if (dim <= 0) return SO_ERR_GEOMETRY;
+    float ss = 0.0f;
+    for (int i = 0; i < dim; ++i) { float v = h2f(x[i]); ss += v * v; }
+    float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int i = 0; i < dim; ++i) {
+        if (two_stage) {
+            float n = round_h(h2f(x[i]) * inv);
+            float dw = round_h(1.0f + h2f(w[i]));
+            y[i] = f2h(dw * n);
+        } else {
+            y[i] = f2h(h2f(x[i]) * inv * (1.0f + h2f(w[i])));
+        }
+    }
+    return SO_OK;
+}
+
+/* per_head_rms_norm with a direct weight (Resources/Shaders/attention_fused.metal:93-145):
+ * weight * half(x*rs) as an fp16 product. */
+SO_API int so_per_head_rms_norm(const uint16_t *x, const uint16_t *w, int heads, int head_dim,
+                                float eps, uint16_t *y) {
+    if (heads <= 0 || head_dim <= 0) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < heads; ++h) {
+        const uint16_t *xh = x + (size_t)h * head_dim;
+        float ss = 0.0f;
+        for (int i = 0; i < head_dim; ++i) { float v = h2f(xh[i]); ss += v * v; }
+        float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+        for (int i = 0; i < head_dim; ++i) {
+            float n = round_h(h2f(xh[i]) * inv);
+            y[(size_t)h * head_dim + i] = f2h(h2f(w[i]) * n);
+        }
+    }
+    return SO_OK;
+}
+
+/* elementwise_add (Resources/Shaders/activations.metal:56-66): fp16 a + b. */
+SO_API void so_elementwise_add(const uint16_t *a, const uint16_t *b, int64_t n, uint16_t *y) {
+    for (int64_t i = 0; i < n; ++i) y[i] = f2h(h2f(a[i]) + h2f(b[i]));
+}
+
+/* embedding_gather (lut_matvec.metal:951-962): row copy. */
+SO_API void so_embedding_gather(const uint16_t *table, int64_t token, int hidden, uint16_t *y) {
+    memcpy(y, table + (size_t)token * hidden, (size_t)hidden * 2);
+}
+
+/* Argmax over fp16 logits: strictly-greater scan, so ties keep the lowest index and -0
+ * equals +0 (Sources/SmeltRuntime/SmeltSelection.swift:165-204; key order
+ * Resources/Shaders/lut_matvec.metal:4045-4074). */
+SO_API int32_t so_argmax_f16(const uint16_t *logits, int64_t n) {
+    float best = -INFINITY;
+    int32_t idx = -1;
+    for (int64_t i = 0; i < n; ++i) {
+        float v = h2f(logits[i]);
+        if (v > best) { best = v; idx = (int32_t)i; }
+    }
+    return idx;
+}
+
+/* ───────────────────────── RoPE + KV cache ─────────────────────────
+ * Resources/Shaders/attention.metal:11-115.  layout: 0 adjacent pairs, 1 split-half,
+ * 2 proportional split-half.  math_mode 1 (analytic): invFreq = exp2(-(pair/halfRope)*log2θ),
+ * angle = float(position)*invFreq, fp32 cos/sin; math_mode 0: fp16 cos/sin table rows.
+ * Results x0*c0 - x1*s0 and x0*s1 + x1*c1, rounded to fp16, in place.
+ */
+static inline void rope_pair_indices(int layout, int dim, int half_rope, int head_dim, int *d0, int *d1,
+                                     int *c0, int *c1) {
+    if (layout == 1) { *d0 = dim; *d1 = dim + half_rope; *c0 = *d0; *c1 = *d1; }
+    else if (layout == 2) { *d0 = dim; *d1 = dim + head_dim / 2; *c0 = dim; *c1 = dim + half_rope; }
+    else { *d0 = dim * 2; *d1 = *d0 + 1; *c0 = *d0; *c1 = *d1; }
+}
+
+static inline void rope_trig(int pair, int half_rope, uint32_t position, float base_log2, int math_mode,
+                             const uint16_t *cos_t, const uint16_t *sin_t, int c0i, int c1i,
+                             float *c0, float *s0, float *c1, float *s1) {
+    if (math_mode == 1) {
+        float d = (float)pair / (float)half_rope;
+        float inv_freq = exp2f(-d * base_log2);
+        float angle = (float)position * inv_freq;
+        float c = cosf(angle), s = sinf(angle);
+        *c0 = c; *s0 = s; *c1 = c; *s1 = s;
+    } else {
+        *c0 = h2f(cos_t[c0i]); *s0 = h2f(sin_t[c0i]);
+        *c1 = h2f(cos_t[c1i]); *s1 = h2f(sin_t[c1i]);
+    }
+}
+
+SO_API int so_apply_rope(uint16_t *qk, const uint16_t *cos_t, const uint16_t *sin_t, int head_dim,
+                         int rope_dim, int heads, int layout, uint32_t position, float base_log2,
+                         int math_mode) {
+    if (head_dim <= 0 || rope_dim <= 0 || rope_dim > head_dim || heads <= 0) return SO_ERR_GEOMETRY;
+    int half_rope = rope_dim / 2;
+    for (int h = 0; h < heads; ++h) {
+        uint16_t *v = qk + (size_t)h * head_dim;
+        for (int dim = 0; dim < half_rope; ++dim) {
+            int d0, d1, c0i, c1i;
+            rope_pair_indices(layout, dim, half_rope, head_dim, &d0, &d1, &c0i, &c1i);
+            float x0 = h2f(v[d0]), x1 = h2f(v[d1]);
+            float c0, s0, c1, s1;
+            rope_trig(dim, half_rope, position, base_log2, math_mode, cos_t, sin_t, c0i, c1i, &c0, &s0, &c1, &s1);
+            v[d0] = f2h(x0 * c0 - x1 * s0);
+            v[d1] = f2h(x0 * s1 + x1 * c1);
+        }
+    }
+    return SO_OK;
+}
+
+/* kv_cache_update (attention.metal:122-139; Tests/.../RegionExactnessTests.swift:909-925):
+ * cache[h, pos, :] = new[h, :], cache laid out [heads, capacity, head_dim]. */
+SO_API int so_kv_cache_update(uint16_t *cache, const uint16_t *new_kv, int capacity, int head_dim,
+                              int pos, int heads) {
+    if (pos < 0 || pos >= capacity || head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < heads; ++h)
+        memcpy(cache + ((size_t)h * capacity + pos) * head_dim, new_kv + (size_t)h * head_dim,
+               (size_t)head_dim * 2);
+    return SO_OK;
+}
+
+/* rope_kv_cache_update (attention.metal:141-209): rotate the new K row and write it at pos. */
+SO_API int so_rope_kv_cache_update(uint16_t *cache, const uint16_t *new_kv, const uint16_t *cos_t,
+                                   const uint16_t *sin_t, int capacity, int head_dim, int pos,
+                                   int heads, int rope_dim, int layout, float base_log2,
+                                   int math_mode) {
+    if (pos < 0 || pos >= capacity || head_dim <= 0 || heads <= 0 || rope_dim > head_dim) return SO_ERR_GEOMETRY;
+    uint16_t *tmp = (uint16_t *)malloc((size_t)heads * head_dim * 2);
+    if (!tmp) return SO_ERR_ALLOC;
+    memcpy(tmp, new_kv, (size_t)heads * head_dim * 2);
+    int rc = so_apply_rope(tmp, cos_t, sin_t, head_dim, rope_dim, heads, layout, (uint32_t)pos, base_log2, math_mode);
+    if (rc == SO_OK) rc = so_kv_cache_update(cache, tmp, capacity, head_dim, pos, heads);
+    free(tmp);
+    return rc;
+}
+
+/* ───────────────────────── attention decode ─────────────────────────
+ * Tests/SmeltCompilerTests/RegionExactnessTests.swift:1414-1475
+ * (referenceAttentionDecodeCPU): per q head, scores = (q·k)*scale over [seqStart, seqLen),
+ * max, exp(score-max), invSum = 1/sum, out[d] = half(Σ_s (p_s*invSum) * v[s,d]).
+ * K/V are [kv_heads, capacity, head_dim] fp16; GQA kvHead = qHead / (nQ/nKV).
+ */
+SO_API int so_attention_decode(const uint16_t *q, const uint16_t *k_cache, const uint16_t *v_cache,
+                               int n_q, int n_kv, int head_dim, int capacity, int seq_len,
+                               float scale, int sliding_window, uint16_t *out) {
+    if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || head_dim <= 0 || seq_len <= 0 || seq_len > capacity)
+        return SO_ERR_GEOMETRY;
+    int ratio = n_q / n_kv;
+    size_t kv_stride = (size_t)capacity * head_dim;
+    int seq_start = 0;
+    if (sliding_window > 0 && sliding_window < seq_len) seq_start = seq_len - sliding_window;
+    int n = seq_len - seq_start;
+    int fail = 0;
+#pragma omp parallel for schedule(static)
+    for (int qh = 0; qh < n_q; ++qh) {
+        int kvh = qh / ratio;
+        float *qf = (float *)malloc(sizeof(float) * head_dim);
+        float *scores = (float *)malloc(sizeof(float) * n);
+        if (!qf || !scores) { fail = 1; free(qf); free(scores); continue; }
+        for (int d = 0; d < head_dim; ++d) qf[d] = h2f(q[(size_t)qh * head_dim + d]);
+        float mx = -INFINITY;
+        for (int s = seq_start; s < seq_len; ++s) {
+            const uint16_t *kr = k_cache + kvh * kv_stride + (size_t)s * head_dim;
+            float dot = 0.0f;
+            for (int d = 0; d < head_dim; ++d) dot += qf[d] * h2f(kr[d]);
+            float sc = dot * scale;
+            scores[s - seq_start] = sc;
+            if (sc > mx) mx = sc;
+        }
+        float sum = 0.0f;
+        for (int i = 0; i < n; ++i) { scores[i] = expf(scores[i] - mx); sum += scores[i]; }
+        float inv = 1.0f / sum;
+        for (int d = 0; d < head_dim; ++d) {
+            float acc = 0.0f;
+            for (int s = seq_start; s < seq_len; ++s) {
+                float w = scores[s - seq_start] * inv;
+                acc += w * h2f(v_cache[kvh * kv_stride + (size_t)s * head_dim + d]);
+            }
+            out[(size_t)qh * head_dim + d] = f2h(acc);
+        }
+        free(qf); free(scores);
+    }
+    return fail ? SO_ERR_ALLOC : SO_OK;
+}
+
+/* ───────────────────────── whole decoder ─────────────────────────
+ * Structure: Sources/SmeltRuntime/Qwen3TTSTalker.swift:229-292 (forwardStep: norm → q/k/v →
+ * RoPE → cache append → GQA attention → o → residual → norm → gate/up SwiGLU → down →
+ * residual → final norm), with the per-dispatch fp16 rounding points of the Metal text path:
+ * every inter-kernel buffer is fp16 (embedding row, two-stage rms_norm_1pw with a stored
+ * weight delta, half(acc) after each projection, analytic-mode split-half RoPE, fp16 KV,
+ * half attention output, fp16 residual add, one rounding after the fp32 SwiGLU, clamped fp16
+ * logits, lowest-index argmax).
+ */
+typedef struct {
+    const uint8_t *w;
+    const uint16_t *s, *b;
+} so_affine_t;
+
+typedef struct {
+    const uint16_t *input_norm, *post_norm; /* stored as weight-1 */
+    so_affine_t q, k, v, o, gate, up, down;
+} so_layer_t;
+
+typedef struct {
+    int layers, hidden, inter, n_q, n_kv, head_dim, vocab, group, capacity;
+    float eps, rope_theta;
+    const uint16_t *embedding;  /* [vocab, hidden] fp16 */
+    const uint16_t *lm_head;    /* [vocab, hidden] fp16 */
+    const uint16_t *final_norm; /* weight-1 */
+    so_layer_t *layer;
+    uint16_t **k_cache, **v_cache; /* per layer [n_kv, capacity, head_dim] */
+} so_model_t;
+
+SO_API so_model_t *so_model_create(int layers, int hidden, int inter, int n_q, int n_kv, int head_dim,
+                                   int vocab, int group, int capacity, float eps, float rope_theta) {
+    so_model_t *m = (so_model_t *)calloc(1, sizeof(so_model_t));
+    if (!m) return NULL;
+    m->layers = layers; m->hidden = hidden; m->inter = inter; m->n_q = n_q; m->n_kv = n_kv;
+    m->head_dim = head_dim; m->vocab = vocab; m->group = group; m->capacity = capacity;
+    m->eps = eps; m->rope_theta = rope_theta;
+    m->layer = (so_layer_t *)calloc((size_t)layers, sizeof(so_layer_t));
+    m->k_cache = (uint16_t **)calloc((size_t)layers, sizeof(uint16_t *));
+    m->v_cache = (uint16_t **)calloc((size_t)layers, sizeof(uint16_t *));
+    size_t kv = (size_t)n_kv * capacity * head_dim;
+    for (int l = 0; l < layers; ++l) {
+        m->k_cache[l] = (uint16_t *)calloc(kv, 2);
+        m->v_cache[l] = (uint16_t *)calloc(kv, 2);
+    }
+    return m;
+}
+
+SO_API void so_model_destroy(so_model_t *m) {
+    if (!m) return;
+    for (int l = 0; l < m->layers; ++l) { free(m->k_cache[l]); free(m->v_cache[l]); }
+    free(m->k_cache); free(m->v_cache); free(m->layer); free(m);
+}
+
+SO_API void so_model_set_globals(so_model_t *m, const uint16_t *embedding, const uint16_t *lm_head,
+                                 const uint16_t *final_norm) {
+    m->embedding = embedding; m->lm_head = lm_head; m->final_norm = final_norm;
+}
+
+/* which: 0 q, 1 k, 2 v, 3 o, 4 gate, 5 up, 6 down */
+SO_API int so_model_set_affine(so_model_t *m, int layer, int which, const uint8_t *w, const uint16_t *s,
+                               const uint16_t *b) {
+    if (layer < 0 || layer >= m->layers || which < 0 || which > 6) return SO_ERR_GEOMETRY;
+    so_affine_t *t = &m->layer[layer].q + which;
+    t->w = w; t->s = s; t->b = b;
+    return SO_OK;
+}
+
+SO_API int so_model_set_norms(so_model_t *m, int layer, const uint16_t *input_norm, const uint16_t *post_norm) {
+    if (layer < 0 || layer >= m->layers) return SO_ERR_GEOMETRY;
+    m->layer[layer].input_norm = input_norm; m->layer[layer].post_norm = post_norm;
+    return SO_OK;
+}
+
+SO_API void so_model_reset_cache(so_model_t *m) {
+    size_t kv = (size_t)m->n_kv * m->capacity * m->head_dim;
+    for (int l = 0; l < m->layers; ++l) { memset(m->k_cache[l], 0, kv * 2); memset(m->v_cache[l], 0, kv * 2); }
+}
+
+/* One decode step for one sequence.  Writes fp16 logits [vocab] when logits != NULL and
+ * returns the greedy token through *out_token. */
+SO_API int so_model_decode_step(so_model_t *m, int32_t token, int position, uint16_t *logits_out,
+                                int32_t *out_token) {
+    if (token < 0 || token >= m->vocab || position < 0 || position >= m->capacity) return SO_ERR_GEOMETRY;
+    int H = m->hidden, I = m->inter, D = m->head_dim, qd = m->n_q * D, kvd = m->n_kv * D, G = m->group;
+    size_t scratch = (size_t)H * 3 + qd * 2 + kvd * 2 + I;
+    uint16_t *buf = (uint16_t *)malloc(scratch * 2);
+    uint16_t *logits = logits_out ? logits_out : (uint16_t *)malloc((size_t)m->vocab * 2);
+    if (!buf || !logits) { free(buf); if (!logits_out) free(logits); return SO_ERR_ALLOC; }
+    uint16_t *h = buf, *normed = h + H, *tmp = normed + H, *q = tmp + H, *attn = q + qd, *k = attn + qd,
+             *v = k + kvd, *act = v + kvd;
+    int rc = SO_OK;
+    float base_log2 = log2f(m->rope_theta);
+    float scale = 1.0f / sqrtf((float)D);
+    so_embedding_gather(m->embedding, token, H, h);
+    for (int l = 0; l < m->layers && rc == SO_OK; ++l) {
+        so_layer_t *L = &m->layer[l];
+        rc = so_rms_norm_1pw(h, L->input_norm, H, m->eps, 1, normed);
+        if (!rc) rc = so_affine_matvec(L->q.w, L->q.s, L->q.b, normed, qd, H, G, 1, q);
+        if (!rc) rc = so_affine_matvec(L->k.w, L->k.s, L->k.b, normed, kvd, H, G, 1, k);
+        if (!rc) rc = so_affine_matvec(L->v.w, L->v.s, L->v.b, normed, kvd, H, G, 1, v);
+        if (!rc) rc = so_apply_rope(q, NULL, NULL, D, D, m->n_q, 1, (uint32_t)position, base_log2, 1);
+        if (!rc) rc = so_rope_kv_cache_update(m->k_cache[l], k, NULL, NULL, m->capacity, D, position, m->n_kv, D, 1, base_log2, 1);
+        if (!rc) rc = so_kv_cache_update(m->v_cache[l], v, m->capacity, D, position, m->n_kv);
+        if (!rc) rc = so_attention_decode(q, m->k_cache[l], m->v_cache[l], m->n_q, m->n_kv, D, m->capacity,
+                                          position + 1, scale, 0, attn);
+        if (!rc) rc = so_affine_matvec(L->o.w, L->o.s, L->o.b, attn, H, qd, G, 1, tmp);
+        if (!rc) so_elementwise_add(h, tmp, H, h);
+        if (!rc) rc = so_rms_norm_1pw(h, L->post_norm, H, m->eps, 1, normed);
+        if (!rc) rc = so_affine_gate_up_swiglu(L->gate.w, L->gate.s, L->gate.b, L->up.w, L->up.s, L->up.b,
+                                               normed, I, H, G, 1, 0, act);
+        if (!rc) rc = so_affine_matvec(L->down.w, L->down.s, L->down.b, act, H, I, G, 1, tmp);
+        if (!rc) so_elementwise_add(h, tmp, H, h);
+    }
+    if (!rc) rc = so_rms_norm_1pw(h, m->final_norm, H, m->eps, 1, normed);
+    if (!rc) rc = so_fp16_matvec(m->lm_head, normed, m->vocab, H, 1, logits);
+    if (!rc && out_token) *out_token = so_argmax_f16(logits, m->vocab);
+    free(buf);
+    if (!logits_out) free(logits);
+    return rc;
+}
+
+/* Greedy generation: feed the prompt token by token (the reference does the same when a
+ * package has no prefill table, Sources/SmeltRuntime/SmeltModel.swift:619-631), then
+ * n_decode greedy steps.  out_tokens receives n_decode ids; margins (optional, n_decode
+ * floats) receives top1-top2 logit gaps. */
+SO_API int so_model_generate(so_model_t *m, const int32_t *prompt, int n_prompt, int n_decode,
+                             int32_t *out_tokens, float *margins) {
+    if (n_prompt <= 0 || n_prompt + n_decode > m->capacity) return SO_ERR_GEOMETRY;
+    uint16_t *logits = (uint16_t *)malloc((size_t)m->vocab * 2);
+    if (!logits) return SO_ERR_ALLOC;
+    so_model_reset_cache(m);
+    int32_t cur = -1;
+    int rc = SO_OK, pos = 0;
+    for (int i = 0; i < n_prompt && !rc; ++i, ++pos) rc = so_model_decode_step(m, prompt[i], pos, logits, &cur);
+    for (int i = 0; i < n_decode && !rc; ++i, ++pos) {
+        out_tokens[i] = cur;
+        if (margins) {
+            float best = -INFINITY, second = -INFINITY;
+            for (int t = 0; t < m->vocab; ++t) {
+                float v = h2f(logits[t]);
+                if (v > best) { second = best; best = v; } else if (v > second) second = v;
+            }
+            margins[i] = best - second;
+        }
+        if (i + 1 < n_decode) rc = so_model_decode_step(m, cur, pos, logits, &cur);
+    }
+    free(logits);
+    return rc;
+}

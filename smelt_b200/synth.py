@@ -1,0 +1,120 @@
+"""Seeded synthetic tensors with the shapes and value distributions of the benchmark configs,
+plus the reference test-suite's closed-form fixtures.
+
+Every tensor is drawn from its own counter-based Philox stream keyed by ``(seed, tensor_id)``,
+so any rank can regenerate any tensor (or the same tensor twice) without generating the rest.
+Packed layouts follow the reference package format: affine u4 is two nibbles per byte with the
+low nibble holding the even column (Sources/SmeltCompiler/SmeltAffineU4.swift:128-133);
+binary1 / ternary2 codes are LSB-first (Sources/SmeltRuntime/SmeltSignedQuantCodec.swift:102-124).
+"""
+from __future__ import annotations
+
+import zlib
+
+import numpy as np
+
+
+def rng_for(seed: int, tensor_id) -> np.random.Generator:
+    if not isinstance(tensor_id, int):
+        tensor_id = zlib.crc32(str(tensor_id).encode())
+    return np.random.Generator(np.random.Philox(key=[int(seed) & 0xFFFFFFFFFFFFFFFF, int(tensor_id) & 0xFFFFFFFFFFFFFFFF]))
+
+
+# ── benchmark-config distributions ──────────────────────────────────────────
+def affine_u4(seed: int, tensor_id, rows: int, cols: int, group: int = 64):
+    """Nibbles uniform 0..15; scale ~U(0.002,0.02) as fp16; bias = -8*scale_fp16 + U(-0.001,0.001) as fp16."""
+    g = rng_for(seed, tensor_id)
+    packed = g.integers(0, 256, size=(rows, cols // 2), dtype=np.uint8)
+    scales = g.uniform(0.002, 0.02, size=(rows, cols // group)).astype(np.float32).astype(np.float16)
+    biases = (-8.0 * scales.astype(np.float32) + g.uniform(-0.001, 0.001, size=scales.shape).astype(np.float32)).astype(np.float16)
+    return packed, scales, biases
+
+
+def activations(seed: int, tensor_id, *shape) -> np.ndarray:
+    """fp16 ~N(0,1)."""
+    return rng_for(seed, tensor_id).standard_normal(size=shape, dtype=np.float32).astype(np.float16)
+
+
+def normal_f16(seed: int, tensor_id, shape, std: float) -> np.ndarray:
+    g = rng_for(seed, tensor_id)
+    out = np.empty(shape, np.float16)
+    flat = out.reshape(-1)
+    step = 1 << 24
+    for i in range(0, flat.size, step):
+        n = min(step, flat.size - i)
+        flat[i:i + n] = (g.standard_normal(size=n, dtype=np.float32) * np.float32(std)).astype(np.float16)
+    return out
+
+
+def binary1(seed: int, tensor_id, rows: int, cols: int, group: int = 128):
+    """Sign bits iid Bernoulli(1/2), 32 per uint32 LSB-first; scale per group ~U(0.005,0.03) as fp16."""
+    g = rng_for(seed, tensor_id)
+    codes = g.integers(0, 256, size=(rows, cols // 8), dtype=np.uint8)
+    scales = g.uniform(0.005, 0.03, size=(rows, cols // group)).astype(np.float32).astype(np.float16)
+    return codes, scales
+
+
+def ternary2(seed: int, tensor_id, rows: int, cols: int, group: int = 128, p_zero: float = 0.33):
+    """Codes {0,1,2} = {-1,0,+1} with P(0 weight)=p_zero and the rest split evenly; 4 codes per byte LSB-first."""
+    g = rng_for(seed, tensor_id)
+    u = g.random(size=(rows, cols), dtype=np.float32)
+    half = (1.0 - p_zero) / 2.0
+    code = np.where(u < half, 0, np.where(u < half + p_zero, 1, 2)).astype(np.uint8)
+    codes = pack_codes(code, 2)
+    scales = g.uniform(0.005, 0.03, size=(rows, cols // group)).astype(np.float32).astype(np.float16)
+    return codes, scales
+
+
+def pack_codes(code: np.ndarray, bits: int) -> np.ndarray:
+    """Pack a [rows, cols] array of small integer codes LSB-first, ``8/bits`` per byte."""
+    rows, cols = code.shape
+    per = 8 // bits
+    c = code.reshape(rows, cols // per, per).astype(np.uint16)
+    out = np.zeros((rows, cols // per), np.uint16)
+    for i in range(per):
+        out |= c[:, :, i] << (bits * i)
+    return out.astype(np.uint8)
+
+
+def kv_cache(seed: int, tensor_id, batch: int, n_kv: int, capacity: int, head_dim: int) -> np.ndarray:
+    """K or V ~N(0,1)/sqrt(head_dim), fp16, laid out [batch][n_kv, capacity, head_dim]."""
+    g = rng_for(seed, tensor_id)
+    x = g.standard_normal(size=(batch, n_kv, capacity, head_dim), dtype=np.float32)
+    return (x / np.float32(np.sqrt(head_dim))).astype(np.float16)
+
+
+# ── the reference test-suite's closed-form fixtures ─────────────────────────
+REGION_SEED_PRIMARY, REGION_SEED_SECONDARY, REGION_SEED_TERTIARY = 6151, 7919, 4817
+
+
+def ref_float16_vector(count: int, seed_offset: float, multiplier: float, bias: float = 0.0, phase: float = 0.0137) -> np.ndarray:
+    """Tests/SmeltCompilerTests/Helpers/MetalKernelTestSupport.swift:320-332 (makeFloat16Vector)."""
+    i = np.arange(count, dtype=np.float32)
+    arg = (i + np.float32(seed_offset)) * np.float32(phase)
+    return (np.float32(bias) + np.float32(multiplier) * np.sin(arg, dtype=np.float32)).astype(np.float16)
+
+
+def ref_affine_fixture(rows: int, cols: int, group: int, seed: int):
+    """Tests/SmeltCompilerTests/Helpers/MetalKernelTestSupport.swift:361-388 (makeQuantizedAffineFixture)."""
+    nbytes = rows * cols // 2
+    nsb = rows * (cols // group)
+    i = np.arange(nbytes, dtype=np.int64)
+    weights = ((i * 17 + 23 + seed * 131) & 0xFF).astype(np.uint8).reshape(rows, cols // 2)
+    j = np.arange(nsb, dtype=np.float32)
+    scale_seed = np.float32(seed * REGION_SEED_SECONDARY)
+    bias_seed = np.float32(seed * 6869)
+    scales = (np.float32(0.01) + np.float32(0.04) * (np.float32(0.5) + np.float32(0.5) * np.sin((j + scale_seed) * np.float32(0.0071), dtype=np.float32)))
+    biases = np.cos((j + bias_seed) * np.float32(0.0113), dtype=np.float32) * np.float32(0.03)
+    return weights, scales.astype(np.float16).reshape(rows, -1), biases.astype(np.float16).reshape(rows, -1)
+
+
+def ref_attention_inputs(n_q: int, n_kv: int, head_dim: int, capacity: int, seed: int):
+    """Tests/SmeltCompilerTests/RegionExactnessTests.swift:1367-1412 (makeAttentionDecodeInputs)."""
+    q = ref_float16_vector(n_q * head_dim, float(seed * REGION_SEED_PRIMARY), 0.3, 0.05)
+    per = capacity * head_dim
+    k = np.zeros((n_kv, per), np.float16)
+    v = np.zeros((n_kv, per), np.float16)
+    for h in range(n_kv):
+        k[h] = ref_float16_vector(per, float(seed * REGION_SEED_SECONDARY) + float(h * 1009), 0.2 + 0.3 * h, 0.05)
+        v[h] = ref_float16_vector(per, float(seed * REGION_SEED_TERTIARY) + float(h * 1013), 0.2 + 0.4 * h, 0.05)
+    return q.reshape(n_q, head_dim), k.reshape(n_kv, capacity, head_dim), v.reshape(n_kv, capacity, head_dim)
