@@ -1,0 +1,326 @@
+/*
+ * smelt_cuda.h — C ABI of libsmelt_cuda: the sm_100a (B200) replacement for the Metal kernels
+ * behind SmeltRuntime's decode dispatch surface.
+ *
+ * What it replaces.  In the reference, Sources/SmeltRuntime/SmeltRuntime.swift interprets a
+ * table of fixed-width SmeltDispatchRecord values (Sources/SmeltSchema/SmeltDispatchTable.swift
+ * :21-165) into Metal compute commands: it resolves a pipeline by name, binds slot-indexed
+ * buffers at byte offsets, resolves up to eight constants and dispatches
+ * (SmeltRuntime.swift:3187-3247, emitDecodeDispatchRecord).  This library keeps that surface —
+ * the same 360-byte records, the same kernel names, buffer binding indices and constant
+ * binding indices, the same packed-weight layout — and launches hand-written CUDA kernels.
+ * A Metal grid / threadgroup size in a record is advisory; launch geometry is derived from the
+ * kernel name, constants and shapes.
+ *
+ * Conventions.  Every function returns a smelt_status (0 = ok) and never aborts; the text of
+ * the last failure is available from smelt_cuda_last_error().  A context is bound to one CUDA
+ * device and one stream and is not thread-safe (the reference runtime is single-threaded per
+ * instance, SmeltRuntime.swift:1950).  Pointers named *_dev are device pointers, everything
+ * else is host memory.  fp16 data is IEEE binary16 stored as uint16_t.  There is no CPU
+ * fallback anywhere: when no CUDA device is usable, smelt_cuda_create fails.
+ */
+#ifndef SMELT_CUDA_H
+#define SMELT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMELT_CUDA_API __attribute__((visibility("default")))
+
+typedef int32_t smelt_status;
+enum {
+    SMELT_OK = 0,
+    SMELT_ERR_BAD_ARGUMENT = 1,     /* shape / alignment / null-pointer violation */
+    SMELT_ERR_UNKNOWN_PIPELINE = 2, /* kernel name not implemented (no silent default) */
+    SMELT_ERR_OUT_OF_RANGE = 3,     /* token, position, slot or weight offset out of range */
+    SMELT_ERR_CUDA = 4,             /* a CUDA runtime call failed */
+    SMELT_ERR_ALLOC = 5,            /* device or host allocation failed */
+    SMELT_ERR_UNSUPPORTED = 6,      /* valid request outside the implemented hot path */
+    SMELT_ERR_COMM = 7,             /* tensor-parallel communicator failure */
+    SMELT_ERR_DEVICE_TIMEOUT = 8    /* a bounded device-side wait gave up */
+};
+
+typedef struct smelt_cuda_ctx smelt_cuda_ctx;
+
+/* ── SmeltDispatchRecord, byte for byte (Sources/SmeltSchema/SmeltDispatchTable.swift:21-165;
+ *    sizes 16 / 8 / 360 pinned by Tests/SmeltCompilerTests/DispatchTableTests.swift:12-30) ── */
+typedef struct {
+    int16_t slot;         /* >= 0 literal slot, -1 = cur, -2 = alt */
+    uint8_t binding_index;
+    uint8_t offset_kind;  /* 0 literal byte offset, 1 position * offset */
+    uint32_t _pad;
+    uint64_t offset;
+} smelt_buffer_record;
+
+typedef struct {
+    uint8_t kind;           /* SMELT_CONST_* */
+    uint8_t binding_index;  /* 255 = guard only, not bound */
+    uint16_t pad;
+    uint32_t value;
+} smelt_constant_record;
+
+typedef struct {
+    uint8_t op_kind; /* 0 dispatch, 1 swap cur/alt */
+    uint8_t _pad0;
+    uint16_t pipeline;
+    uint8_t style;
+    uint8_t buffer_count;
+    uint8_t constant_count;
+    uint8_t _pad1;
+    uint16_t min_seq_len;
+    uint16_t _pad2;
+    uint32_t grid[3];
+    uint32_t threadgroup[3];
+    uint32_t _pad3;
+    smelt_buffer_record buf[16];
+    smelt_constant_record con[8];
+} smelt_dispatch_record;
+
+enum {
+    SMELT_CONST_LITERAL_U32 = 0,
+    SMELT_CONST_LITERAL_F32 = 1,
+    SMELT_CONST_POSITION = 2,
+    SMELT_CONST_POSITION_PLUS1 = 3,
+    SMELT_CONST_SKIP_UNLESS_POS1_LT = 10,
+    SMELT_CONST_SKIP_UNLESS_POS1_GE = 11,
+    SMELT_CONST_CACHE_SEQ_CAPACITY = 12
+};
+enum { SMELT_OP_DISPATCH = 0, SMELT_OP_SWAP = 1 };
+enum { SMELT_SLOT_CUR = -1, SMELT_SLOT_ALT = -2 };
+
+/* ── context ─────────────────────────────────────────────────────────────────
+ * Replaces the MTLDevice / MTLCommandQueue set-up of SmeltRuntime.init
+ * (SmeltRuntime.swift:695-712). */
+SMELT_CUDA_API smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx);
+SMELT_CUDA_API void smelt_cuda_destroy(smelt_cuda_ctx* ctx);
+SMELT_CUDA_API const char* smelt_cuda_last_error(const smelt_cuda_ctx* ctx);
+SMELT_CUDA_API smelt_status smelt_cuda_synchronize(smelt_cuda_ctx* ctx);
+/* The context's cudaStream_t, for callers that enqueue their own work around the library's. */
+SMELT_CUDA_API void* smelt_cuda_stream(smelt_cuda_ctx* ctx);
+/* Reads and clears the device error word that kernels set when a bounded wait gives up.
+ * Synchronises the stream.  *out_flags == 0 means no kernel reported a problem. */
+SMELT_CUDA_API smelt_status smelt_cuda_device_error(smelt_cuda_ctx* ctx, uint32_t* out_flags);
+SMELT_CUDA_API int smelt_cuda_sm_count(const smelt_cuda_ctx* ctx);
+
+/* Raw device memory for callers that drive the typed launchers directly (tests, benchmarks). */
+SMELT_CUDA_API smelt_status smelt_cuda_malloc(smelt_cuda_ctx* ctx, size_t bytes, void** out_dev);
+SMELT_CUDA_API smelt_status smelt_cuda_free(smelt_cuda_ctx* ctx, void* dev);
+SMELT_CUDA_API smelt_status smelt_cuda_memcpy_h2d(smelt_cuda_ctx* ctx, void* dst_dev, const void* src, size_t bytes);
+SMELT_CUDA_API smelt_status smelt_cuda_memcpy_d2h(smelt_cuda_ctx* ctx, void* dst, const void* src_dev, size_t bytes);
+SMELT_CUDA_API smelt_status smelt_cuda_memset(smelt_cuda_ctx* ctx, void* dst_dev, int value, size_t bytes);
+
+/* ── buffer slots ────────────────────────────────────────────────────────────
+ * The slot-indexed buffer array of SmeltRuntime (allocation and zero fill
+ * SmeltRuntime.swift:922-979; request-scoped growth :6803-6913; KV sizing
+ * heads * capacity * head_dim * 2 bytes :6891-6913).  Slots are zero-filled at creation. */
+SMELT_CUDA_API smelt_status smelt_cuda_alloc_slot(smelt_cuda_ctx* ctx, int slot, size_t bytes);
+/* Grow (or shrink) a slot, keeping the first preserve_bytes bytes and zero-filling the rest.
+ * Any device pointer obtained earlier for the slot is stale afterwards
+ * (SmeltRuntime.swift:5101-5103). */
+SMELT_CUDA_API smelt_status smelt_cuda_resize_slot(smelt_cuda_ctx* ctx, int slot, size_t bytes, size_t preserve_bytes);
+/* Grow a KV-cache slot laid out [heads, capacity, head_dim] fp16 from old_capacity to
+ * new_capacity positions, keeping the first live_len positions of every head in place
+ * (contents are preserved across growth, SmeltRuntime.swift:6957-6959). */
+SMELT_CUDA_API smelt_status smelt_cuda_resize_kv_slot(smelt_cuda_ctx* ctx, int slot, int heads, int head_dim,
+                                                      uint32_t old_capacity, uint32_t new_capacity, uint32_t live_len);
+SMELT_CUDA_API smelt_status smelt_cuda_slot_ptr(smelt_cuda_ctx* ctx, int slot, void** out_dev, size_t* out_bytes);
+SMELT_CUDA_API smelt_status smelt_cuda_write_slot(smelt_cuda_ctx* ctx, int slot, size_t offset, const void* src, size_t bytes);
+SMELT_CUDA_API smelt_status smelt_cuda_read_slot(smelt_cuda_ctx* ctx, int slot, size_t offset, void* dst, size_t bytes);
+SMELT_CUDA_API smelt_status smelt_cuda_zero_slot(smelt_cuda_ctx* ctx, int slot);
+/* The whole weights.bin image into one device allocation bound to `slot`; record offsets into
+ * that slot index the image exactly as bindBuffer does (SmeltRuntime.swift:3153-3169). */
+SMELT_CUDA_API smelt_status smelt_cuda_upload_weights(smelt_cuda_ctx* ctx, int slot, const void* image, size_t bytes);
+
+/* Runtime configuration a package's manifest provides (slot layout and limits,
+ * Sources/SmeltSchema/SmeltManifest.swift:806-817; bounds checks SmeltRuntime.swift:3176-3183). */
+typedef struct {
+    int32_t token_id_slot;      /* int32 token id(s), one per sequence */
+    int32_t position_slot;      /* int32 position */
+    int32_t weights_slot;
+    int32_t argmax_slot;        /* int32 result(s) read back by smelt_cuda_decode_step */
+    int32_t cur_slot, alt_slot; /* initial double-buffer pair (0 and 1 in the reference) */
+    uint32_t cache_seq_capacity;
+    uint32_t context_limit;
+    uint32_t vocab_size;
+    uint32_t batch;             /* independent sequences decoded together (1 in the reference) */
+} smelt_cuda_runtime_config;
+SMELT_CUDA_API smelt_status smelt_cuda_configure(smelt_cuda_ctx* ctx, const smelt_cuda_runtime_config* cfg);
+
+/* ── pipelines and dispatch ──────────────────────────────────────────────────
+ * manifest.pipelines[index] = "name" or "name:cols:groupSize" (function constants 0/1,
+ * SmeltRuntime.swift:6229-6263).  Unknown names are an error, mirroring the reference's
+ * total kernel table (Sources/SmeltCompiler/MatvecKernelTable.swift:258-270). */
+SMELT_CUDA_API smelt_status smelt_cuda_register_pipeline(smelt_cuda_ctx* ctx, int index, const char* name);
+/* 1 when `name` (with or without the :cols:group suffix) is an implemented kernel. */
+SMELT_CUDA_API int smelt_cuda_pipeline_supported(const char* name);
+
+/* One decoded token, synchronously: writes token / position into their slots, interprets the
+ * table, waits, reads the argmax slot (SmeltRuntime.decodeStep, SmeltRuntime.swift:1573-1641).
+ * tokens / out_tokens hold config.batch entries. */
+SMELT_CUDA_API smelt_status smelt_cuda_decode_step(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records,
+                                                   const int32_t* tokens, int32_t position, int32_t* out_tokens);
+/* Enqueue-only form (encodeTrunkDecode, SmeltRuntime.swift:5029-5091): no wait, no readback.
+ * Capacity must have been ensured before the call. */
+SMELT_CUDA_API smelt_status smelt_cuda_enqueue_decode(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records,
+                                                      const int32_t* tokens, int32_t position);
+/* Capture the table once into a CUDA graph whose kernels read token and position from device
+ * memory; each replay decodes one token and feeds the argmax result back as the next token
+ * on the device, so a run of greedy steps needs no host round trip.  Rebuild after any slot
+ * resize. */
+SMELT_CUDA_API smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records);
+/* Set the device-resident token(s) and position the next replay starts from. */
+SMELT_CUDA_API smelt_status smelt_cuda_graph_seed(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position);
+/* Replay n_steps tokens.  When out_tokens != NULL, waits and returns the n_steps * batch
+ * generated ids (step-major). */
+SMELT_CUDA_API smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* out_tokens);
+/* Number of kernel launches one interpretation of the last built / enqueued table issues. */
+SMELT_CUDA_API int smelt_cuda_last_launch_count(const smelt_cuda_ctx* ctx);
+
+/* ── decoder table builder ───────────────────────────────────────────────────
+ * Emits, for a plain decoder-only model, the per-token record sequence the reference
+ * compiler emits (Sources/SmeltCompiler/TopLevelEmitter.swift:89-930, AttentionPlugin.swift
+ * :105-560): embedding gather, per layer rms_norm_1pw -> Q/K/V projections -> RoPE ->
+ * KV append -> attention decode -> O projection -> residual add -> rms_norm_1pw ->
+ * fused gate/up SwiGLU -> down projection -> residual add, final norm, LM head, argmax.
+ * Weight offsets address the weights slot; the slot numbers follow SmeltFixedSlot
+ * (Sources/SmeltCompiler/SmeltBufferPlan.swift:129-198). */
+typedef struct {
+    uint64_t packed, scales, biases; /* byte offsets into the weights image */
+} smelt_affine_ref;
+typedef struct {
+    uint64_t input_norm, post_norm;  /* fp16 [hidden], stored as weight - 1 */
+    smelt_affine_ref q, k, v, o, gate, up, down;
+} smelt_layer_ref;
+typedef struct {
+    int32_t layers, hidden, inter, n_q, n_kv, head_dim, vocab, group;
+    float eps, rope_theta;
+    uint64_t embedding, lm_head, final_norm;
+    int32_t tp_world;   /* 1 = single GPU; >1 inserts an all-reduce after the O and down projections */
+    int32_t tp_rank;
+    int32_t fuse_residual; /* 1 = emit fused_affine_matvec_add instead of matvec + elementwise_add (tp_world == 1 only) */
+} smelt_decoder_desc;
+/* Allocates the activation / KV / scratch slots for `desc` at `capacity` positions and
+ * `batch` sequences, registers the pipelines, configures the context and writes the table.
+ * records may be NULL to query the count through *n_records. */
+SMELT_CUDA_API smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc,
+                                                     const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
+                                                     smelt_dispatch_record* records, size_t* n_records);
+
+/* ── tensor parallelism (no counterpart in the reference, which is single-device) ──
+ * One process per GPU.  Rank 0 creates an id, the caller ships it to the other ranks, every
+ * rank calls init.  The record interpreter then accepts the pipeline name
+ * "smelt_tp_all_reduce" (buffer 0 in/out fp16, constant 1 = element count). */
+#define SMELT_TP_ID_BYTES 128
+SMELT_CUDA_API smelt_status smelt_cuda_tp_unique_id(uint8_t id[SMELT_TP_ID_BYTES]);
+SMELT_CUDA_API smelt_status smelt_cuda_tp_init(smelt_cuda_ctx* ctx, int rank, int world, const uint8_t id[SMELT_TP_ID_BYTES]);
+SMELT_CUDA_API smelt_status smelt_cuda_tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data_dev, size_t count);
+
+/* ── typed launchers (asynchronous on the context's stream) ──────────────────
+ * Packed-weight layouts are the package's: affine u4 = two nibbles per byte, low nibble =
+ * even column, scales / biases fp16 [rows, cols/group]
+ * (Sources/SmeltCompiler/SmeltAffineU4.swift:5-10); binary1 / ternary2 = LSB-first codes,
+ * scales fp16 [rows, cols/128] (Sources/SmeltRuntime/SmeltSignedQuantCodec.swift:102-124).
+ * Activations x are fp16 [batch, cols]; outputs y fp16 [batch, rows]. */
+
+/* affine_matvec (Resources/Shaders/lut_matvec.metal:1157-1287) and its batched forms (:3238-3461). */
+SMELT_CUDA_API smelt_status smelt_cuda_affine_matvec(smelt_cuda_ctx* ctx, const void* w_dev, const void* scales_dev,
+                                                     const void* biases_dev, const void* x_dev, void* y_dev, int rows,
+                                                     int cols, int group, int batch);
+/* fused_affine_matvec_add (lut_matvec.metal:1718-1817): y = half(acc) + residual; y may alias residual. */
+SMELT_CUDA_API smelt_status smelt_cuda_affine_matvec_add(smelt_cuda_ctx* ctx, const void* w_dev, const void* scales_dev,
+                                                         const void* biases_dev, const void* x_dev,
+                                                         const void* residual_dev, void* y_dev, int rows, int cols,
+                                                         int group, int batch);
+/* fused_affine_gate_up_swiglu (lut_matvec.metal:2152-2233): y = half(silu(gate) * up), fp32 gate / up. */
+SMELT_CUDA_API smelt_status smelt_cuda_affine_gate_up_swiglu(smelt_cuda_ctx* ctx, const void* gw_dev, const void* gs_dev,
+                                                             const void* gb_dev, const void* uw_dev, const void* us_dev,
+                                                             const void* ub_dev, const void* x_dev, void* y_dev,
+                                                             int rows, int cols, int group, int batch);
+/* fused_dual_affine_matvec (lut_matvec.metal:1824-1908): two same-shape matvecs sharing x. */
+SMELT_CUDA_API smelt_status smelt_cuda_affine_dual_matvec(smelt_cuda_ctx* ctx, const void* w0_dev, const void* s0_dev,
+                                                          const void* b0_dev, const void* w1_dev, const void* s1_dev,
+                                                          const void* b1_dev, const void* x_dev, void* y0_dev,
+                                                          void* y1_dev, int rows, int cols, int group, int batch);
+/* Whole-tensor dequant probe: out_f32[rows*cols] and/or out_f16 (either may be NULL) —
+ * SmeltAffineU4.dequantizeRow (SmeltAffineU4.swift:141-161), bit-exact. */
+SMELT_CUDA_API smelt_status smelt_cuda_affine_dequantize(smelt_cuda_ctx* ctx, const void* w_dev, const void* scales_dev,
+                                                         const void* biases_dev, void* out_f32_dev, void* out_f16_dev,
+                                                         int rows, int cols, int group);
+/* fp16_matvec (lut_matvec.metal:799-834): dense fp16 [rows, cols], clamp to +-65504. */
+SMELT_CUDA_API smelt_status smelt_cuda_fp16_matvec(smelt_cuda_ctx* ctx, const void* w_dev, const void* x_dev, void* y_dev,
+                                                   int rows, int cols, int batch);
+
+/* signed_binary_matvec_g128_rows8 / signed_ternary_matvec_g128_rows8
+ * (Resources/Shaders/signed_quant.metal:81-138, :288-332); format 1 = binary1, 2 = ternary2. */
+SMELT_CUDA_API smelt_status smelt_cuda_signed_matvec(smelt_cuda_ctx* ctx, int format, const void* codes_dev,
+                                                     const void* scales_dev, const void* x_dev, void* y_dev, int rows,
+                                                     int cols, int batch);
+/* signed_*_matvec_add (signed_quant.metal:223-286). */
+SMELT_CUDA_API smelt_status smelt_cuda_signed_matvec_add(smelt_cuda_ctx* ctx, int format, const void* codes_dev,
+                                                         const void* scales_dev, const void* x_dev,
+                                                         const void* residual_dev, void* y_dev, int rows, int cols,
+                                                         int batch);
+/* signed_*_gate_up_swiglu (signed_quant.metal:140-221): gate and up rounded to fp16, staged-fp16 SwiGLU. */
+SMELT_CUDA_API smelt_status smelt_cuda_signed_gate_up_swiglu(smelt_cuda_ctx* ctx, int format, const void* gc_dev,
+                                                             const void* gs_dev, const void* uc_dev, const void* us_dev,
+                                                             const void* x_dev, void* y_dev, int rows, int cols,
+                                                             int batch);
+/* SmeltSignedQuantCodec.dequantizeRow (SmeltSignedQuantCodec.swift:219-257) for whole tensors;
+ * *out_invalid = 1 when a ternary code 3 is present (the codec's invalidCode error). */
+SMELT_CUDA_API smelt_status smelt_cuda_signed_dequantize(smelt_cuda_ctx* ctx, int format, const void* codes_dev,
+                                                         const void* scales_dev, void* out_f32_dev, int rows, int cols,
+                                                         int* out_invalid);
+
+/* attention_decode (Resources/Shaders/attention.metal:217-314) and its specialisations:
+ * q, out fp16 [batch, n_q, head_dim] (may alias); caches fp16 [n_kv, capacity, head_dim] per
+ * sequence, kv_seq_stride elements apart; keys [seqStart, seq_len) with seqStart from the
+ * sliding window (0 = full causal). */
+SMELT_CUDA_API smelt_status smelt_cuda_attention_decode(smelt_cuda_ctx* ctx, const void* q_dev, const void* k_cache_dev,
+                                                        const void* v_cache_dev, void* out_dev, int n_q, int n_kv,
+                                                        int head_dim, uint32_t capacity, uint32_t seq_len, float scale,
+                                                        uint32_t sliding_window, int batch, size_t kv_seq_stride);
+/* kv_cache_update / rope_kv_cache_update (attention.metal:122-209). cos/sin may be NULL in analytic mode. */
+SMELT_CUDA_API smelt_status smelt_cuda_kv_cache_update(smelt_cuda_ctx* ctx, void* cache_dev, const void* new_kv_dev,
+                                                       uint32_t capacity, int head_dim, uint32_t position, int heads,
+                                                       int batch, size_t kv_seq_stride);
+SMELT_CUDA_API smelt_status smelt_cuda_rope_kv_cache_update(smelt_cuda_ctx* ctx, void* cache_dev, const void* new_kv_dev,
+                                                            const void* cos_dev, const void* sin_dev, uint32_t capacity,
+                                                            int head_dim, uint32_t position, int heads, int rope_dim,
+                                                            int layout, float base_log2, int math_mode, int batch,
+                                                            size_t kv_seq_stride);
+/* apply_rope (attention.metal:48-115), in place on [batch, heads, head_dim]. */
+SMELT_CUDA_API smelt_status smelt_cuda_apply_rope(smelt_cuda_ctx* ctx, void* qk_dev, const void* cos_dev, const void* sin_dev,
+                                                  int head_dim, int rope_dim, int heads, int layout, uint32_t position,
+                                                  float base_log2, int math_mode, int batch);
+
+/* rms_norm_1pw (Resources/Shaders/norms.metal:9-67); weight stored as a delta from one. */
+SMELT_CUDA_API smelt_status smelt_cuda_rms_norm_1pw(smelt_cuda_ctx* ctx, const void* x_dev, const void* w_dev, void* y_dev,
+                                                    int dim, float eps, int batch);
+/* per_head_rms_norm (Resources/Shaders/attention_fused.metal:93-145); direct weight. */
+SMELT_CUDA_API smelt_status smelt_cuda_per_head_rms_norm(smelt_cuda_ctx* ctx, const void* x_dev, const void* w_dev,
+                                                         void* y_dev, int heads, int head_dim, float eps);
+/* elementwise_add (Resources/Shaders/activations.metal:56-66). */
+SMELT_CUDA_API smelt_status smelt_cuda_elementwise_add(smelt_cuda_ctx* ctx, const void* a_dev, const void* b_dev,
+                                                       void* y_dev, size_t count);
+/* swiglu_fused (Resources/Shaders/activations_precise.metal:9-22). */
+SMELT_CUDA_API smelt_status smelt_cuda_swiglu_fused(smelt_cuda_ctx* ctx, const void* gate_dev, const void* up_dev,
+                                                    void* y_dev, size_t count);
+/* embedding_gather / affine_embedding_gather (lut_matvec.metal:951-962, :994-1025); token ids int32 on device. */
+SMELT_CUDA_API smelt_status smelt_cuda_embedding_gather(smelt_cuda_ctx* ctx, const void* table_dev, const void* token_dev,
+                                                        void* y_dev, int hidden, int batch);
+SMELT_CUDA_API smelt_status smelt_cuda_affine_embedding_gather(smelt_cuda_ctx* ctx, const void* w_dev, const void* scales_dev,
+                                                               const void* biases_dev, const void* token_dev,
+                                                               void* y_dev, int cols, int group);
+/* argmax_fp16_partials + argmax_key_reduce (lut_matvec.metal:8901-8966): lowest index on ties,
+ * -0 == +0.  out_dev receives `batch` int32 ids. */
+SMELT_CUDA_API smelt_status smelt_cuda_argmax_f16(smelt_cuda_ctx* ctx, const void* logits_dev, void* out_dev, int vocab,
+                                                  int batch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMELT_CUDA_H */

@@ -1,0 +1,433 @@
+// Group-wise affine u4 matvec / small-batch matmul for sm_100a.
+//
+// Replaces the reference's affine_matvec family (Resources/Shaders/lut_matvec.metal:1157-1287
+// affine_matvec, :1718-1817 fused_affine_matvec_add, :2152-2233 fused_affine_gate_up_swiglu,
+// :1824-1908 fused_dual_affine_matvec, :3238-3461 the batched / ext forms) with ONE kernel
+// template that serves batch 1..16:
+//
+//   y[b, r] = sum_g ( s[r,g] * sum_{k in g} q[r,k] * x[b,k]  +  b[r,g] * sum_{k in g} x[b,k] )
+//
+// Data path.  A CTA owns 16 output rows and one K-slice (<= 4096 columns).  Its whole packed
+// weight tile is fetched with untiled bulk async copies (one per row and K-quarter) that
+// complete on four mbarriers, so the copies are issued before the programmatic-dependent-
+// launch wait and overlap the tail of the kernel that produces x.  Eight warps split the
+// slice's groups; a warp dequantises a 16-row x GROUP-column block in registers (two LOP3 and
+// two HFMA2 per eight nibbles give exact fp16 integers 0..15) and multiplies it with up to 8
+// (or 16) activation rows by mma.sync.m16n8k16 with fp32 accumulators: the tensor pipe is used
+// as a wide FMA unit so the CUDA cores only pay for the unpack.  The k order inside an MMA is
+// permuted (nibbles i and i+4 of a word share a half2) and the activations are staged in
+// shared memory in the same permuted order.  After every group the fp32 block sum is folded
+// into the running row sums with the group's scale, and the bias term uses per-group
+// activation sums computed once per CTA.  Warp partials are reduced through shared memory in a
+// fixed order; K-slices of one row tile form a thread-block cluster and are reduced through
+// distributed shared memory in rank order, so results are bit-reproducible.
+#include "affine_matvec.h"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
+namespace smelt {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = 8;
+constexpr int kRows = 16;  // rows per CTA (one m16 tile)
+constexpr int kBars = 4;   // K-quarters per weight tile
+
+struct SmemLayout {
+    uint32_t bars, w, sb, xs, xsum, red, total;
+    uint32_t pitch_w, pitch_sb, pitch_x;
+};
+
+template <int GROUP>
+__host__ __device__ inline SmemLayout make_layout(int nw, int nb, int ks, int batch_rows) {
+    SmemLayout L;
+    const int gs = ks / GROUP;
+    L.pitch_w = (uint32_t)(ks / 2 + GROUP / 2);          // ≡ GROUP/2 (mod 128): conflict-free row stride
+    L.pitch_sb = (uint32_t)((gs | 1) * 4);               // odd number of {scale,bias} words per row
+    L.pitch_x = (uint32_t)(ks * 2 + 16);                 // ≡ 16 (mod 128)
+    uint32_t off = 0;
+    L.bars = off; off += 64;
+    L.w = off; off += (uint32_t)nw * kRows * L.pitch_w;
+    off = (off + 15u) & ~15u;
+    L.sb = off; off += (uint32_t)nw * kRows * L.pitch_sb;
+    off = (off + 15u) & ~15u;
+    L.xs = off; off += (uint32_t)batch_rows * L.pitch_x;
+    off = (off + 15u) & ~15u;
+    L.xsum = off; off += (uint32_t)gs * nb * 4;
+    off = (off + 15u) & ~15u;
+    L.red = off; off += (uint32_t)kWarps * 32 * 4 * (nb / 8) * nw * 4;
+    L.total = off;
+    return L;
+}
+
+// Eight nibbles of one packed word -> four half2 of exact integers:
+// {n0,n4} {n1,n5} {n2,n6} {n3,n7}.
+__device__ __forceinline__ void dequant8(uint32_t w, uint32_t p[4]) {
+    const uint32_t kMagic = 0x64006400u;  // half2(1024, 1024)
+    const __half2 k1024 = u32_as_h2(0x64006400u);
+    const __half2 k16th = u32_as_h2(0x2C002C00u);   // half2(1/16)
+    const __half2 km64 = u32_as_h2(0xD400D400u);    // half2(-64)
+    uint32_t lo = lop3_and_or(w, 0x000F000Fu, kMagic);
+    uint32_t hi = lop3_and_or(w, 0x00F000F0u, kMagic);
+    uint32_t w2 = w >> 8;
+    uint32_t lo2 = lop3_and_or(w2, 0x000F000Fu, kMagic);
+    uint32_t hi2 = lop3_and_or(w2, 0x00F000F0u, kMagic);
+    p[0] = h2_as_u32(__hsub2(u32_as_h2(lo), k1024));
+    p[1] = h2_as_u32(__hfma2(u32_as_h2(hi), k16th, km64));
+    p[2] = h2_as_u32(__hsub2(u32_as_h2(lo2), k1024));
+    p[3] = h2_as_u32(__hfma2(u32_as_h2(hi2), k16th, km64));
+}
+
+template <int N>
+struct WordLoad;
+template <>
+struct WordLoad<1> {
+    static __device__ __forceinline__ void ld(const uint8_t* p, uint32_t w[1]) { w[0] = *reinterpret_cast<const uint32_t*>(p); }
+};
+template <>
+struct WordLoad<2> {
+    static __device__ __forceinline__ void ld(const uint8_t* p, uint32_t w[2]) {
+        uint2 v = *reinterpret_cast<const uint2*>(p);
+        w[0] = v.x; w[1] = v.y;
+    }
+};
+template <>
+struct WordLoad<4> {
+    static __device__ __forceinline__ void ld(const uint8_t* p, uint32_t w[4]) {
+        uint4 v = *reinterpret_cast<const uint4*>(p);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    }
+};
+
+template <int MODE, int GROUP, int NBT>
+__global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a) {
+    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    constexpr int NB = NBT * 8;
+    constexpr int WPT = GROUP / 32;  // packed words per thread per row per group
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * kRows;
+    const int k0 = blockIdx.y * a.ks;                       // first column of this CTA's slice
+    const int ks = min(a.ks, a.cols - k0);                  // columns in this slice
+    const int gs = ks / GROUP;                              // groups in this slice
+    const int groups_total = a.cols / GROUP;
+    const SmemLayout L = make_layout<GROUP>(NW, NB, a.ks, a.batch);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
+    uint8_t* sw = smem + L.w;
+    uint32_t* ssb = reinterpret_cast<uint32_t*>(smem + L.sb);
+    uint8_t* sx = smem + L.xs;
+    float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
+    float* sred = reinterpret_cast<float*>(smem + L.red);
+
+    const int gq = (gs + kBars - 1) / kBars;                // groups per K-quarter
+
+    if (tid == 0) {
+        for (int q = 0; q < kBars; ++q) mbar_init(&bars[q], NW * kRows);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // ── weight prefetch: independent of the upstream kernel, issued before the PDL wait ──
+    if (tid < NW * kRows) {
+        const int set = tid / kRows, r = tid % kRows;
+        const bool valid = row0 + r < a.rows;
+        const uint8_t* src = a.w[set] + (size_t)(row0 + r) * (a.cols / 2) + k0 / 2;
+        uint8_t* dst = sw + (size_t)(set * kRows + r) * L.pitch_w;
+        for (int q = 0; q < kBars; ++q) {
+            const int c0 = min(q * gq, gs) * (GROUP / 2), c1 = min((q + 1) * gq, gs) * (GROUP / 2);
+            const uint32_t bytes = valid ? (uint32_t)(c1 - c0) : 0u;
+            mbar_arrive_expect_tx(&bars[q], bytes);
+            if (bytes) bulk_g2s(dst + c0, src + c0, bytes, &bars[q]);
+        }
+    }
+    // {scale,bias} pairs of the slice, interleaved so one 32-bit read serves a group.
+    for (int i = tid; i < NW * kRows * gs; i += kThreads) {
+        const int set = i / (kRows * gs), r = (i / gs) % kRows, gi = i % gs;
+        uint32_t v = 0;
+        if (row0 + r < a.rows) {
+            const size_t idx = (size_t)(row0 + r) * groups_total + k0 / GROUP + gi;
+            v = (uint32_t)__half_as_ushort(a.s[set][idx]) | ((uint32_t)__half_as_ushort(a.b[set][idx]) << 16);
+        }
+        ssb[(size_t)(set * kRows + r) * (L.pitch_sb / 4) + gi] = v;
+    }
+
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(a.dyn)) {
+        // The copies already in flight must land before the CTA (and its shared memory) retires.
+        for (int q = 0; q < kBars; ++q) (void)mbar_wait_bounded(&bars[q], 0);
+        return;
+    }
+
+    // ── activations: permuted copy into shared memory + per-group sums ──
+    {
+        const int chunks = ks / 8;                       // 8-column chunks per batch row
+        const int total = a.batch * chunks;
+        constexpr int CPG = GROUP / 8;                   // chunks per group
+        for (int base = 0; base < total; base += kThreads) {
+            const int i = base + tid;
+            float sum = 0.f;
+            int b = 0, c8 = 0;
+            if (i < total) {
+                b = i / chunks; c8 = i % chunks;
+                const uint4 v = *reinterpret_cast<const uint4*>(a.x + (size_t)b * a.cols + k0 + c8 * 8);
+                const __half2 h0 = u32_as_h2(v.x), h1 = u32_as_h2(v.y), h2 = u32_as_h2(v.z), h3 = u32_as_h2(v.w);
+                const float2 f0 = __half22float2(h0), f1 = __half22float2(h1), f2 = __half22float2(h2), f3 = __half22float2(h3);
+                sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+                uint4 o;  // x0 x4 | x1 x5 | x2 x6 | x3 x7
+                o.x = __byte_perm(v.x, v.z, 0x5410);
+                o.y = __byte_perm(v.x, v.z, 0x7632);
+                o.z = __byte_perm(v.y, v.w, 0x5410);
+                o.w = __byte_perm(v.y, v.w, 0x7632);
+                *reinterpret_cast<uint4*>(sx + (size_t)b * L.pitch_x + c8 * 16) = o;
+            }
+#pragma unroll
+            for (int o = 1; o < CPG; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (i < total && (c8 % CPG) == 0) sxsum[(c8 / CPG) * NB + b] = sum;
+        }
+        for (int i = tid; i < gs * NB; i += kThreads)
+            if ((i % NB) >= a.batch) sxsum[i] = 0.f;
+    }
+    __syncthreads();
+
+    // ── main loop: this warp's groups ──
+    float acc[NW][NBT][4];
+#pragma unroll
+    for (int s = 0; s < NW; ++s)
+#pragma unroll
+        for (int n = 0; n < NBT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[s][n][i] = 0.f;
+
+    bool ok = true;
+    int waited = -1;
+    for (int gi = warp; gi < gs; gi += kWarps) {
+        const int q = gi / gq;
+        while (waited < q) {
+            ++waited;
+            if (!mbar_wait_bounded(&bars[waited], 0)) ok = false;
+        }
+        // activation fragments for this group (rows of x = batch index g, g+8)
+        uint32_t xb[NBT][WPT * 4];
+#pragma unroll
+        for (int n = 0; n < NBT; ++n) {
+            const int b = n * 8 + g;
+            if (b < a.batch) {
+                const uint8_t* px = sx + (size_t)b * L.pitch_x + (size_t)(gi * GROUP + t * (GROUP / 4)) * 2;
+#pragma unroll
+                for (int j = 0; j < WPT; ++j) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(px + j * 16);
+                    xb[n][4 * j + 0] = v.x; xb[n][4 * j + 1] = v.y; xb[n][4 * j + 2] = v.z; xb[n][4 * j + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < WPT * 4; ++j) xb[n][j] = 0u;
+            }
+        }
+#pragma unroll
+        for (int s = 0; s < NW; ++s) {
+            uint32_t wa[WPT], wb[WPT];
+            const uint8_t* pw = sw + (size_t)(s * kRows + g) * L.pitch_w + gi * (GROUP / 2) + t * (GROUP / 8);
+            WordLoad<WPT>::ld(pw, wa);
+            WordLoad<WPT>::ld(pw + 8 * (size_t)L.pitch_w, wb);
+            float c[NBT][4];
+#pragma unroll
+            for (int n = 0; n < NBT; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+#pragma unroll
+            for (int j = 0; j < WPT; ++j) {
+                uint32_t pa[4], pb[4];
+                dequant8(wa[j], pa);
+                dequant8(wb[j], pb);
+#pragma unroll
+                for (int n = 0; n < NBT; ++n) {
+                    mma16816(c[n], pa[0], pb[0], pa[1], pb[1], xb[n][4 * j + 0], xb[n][4 * j + 1]);
+                    mma16816(c[n], pa[2], pb[2], pa[3], pb[3], xb[n][4 * j + 2], xb[n][4 * j + 3]);
+                }
+            }
+            const uint32_t sb0 = ssb[(size_t)(s * kRows + g) * (L.pitch_sb / 4) + gi];
+            const uint32_t sb1 = ssb[(size_t)(s * kRows + g + 8) * (L.pitch_sb / 4) + gi];
+            const float s0 = __half2float(__ushort_as_half((unsigned short)(sb0 & 0xFFFFu)));
+            const float b0 = __half2float(__ushort_as_half((unsigned short)(sb0 >> 16)));
+            const float s1 = __half2float(__ushort_as_half((unsigned short)(sb1 & 0xFFFFu)));
+            const float b1 = __half2float(__ushort_as_half((unsigned short)(sb1 >> 16)));
+#pragma unroll
+            for (int n = 0; n < NBT; ++n) {
+                const float2 xs = *reinterpret_cast<const float2*>(sxsum + gi * NB + n * 8 + 2 * t);
+                acc[s][n][0] += s0 * c[n][0] + b0 * xs.x;
+                acc[s][n][1] += s0 * c[n][1] + b0 * xs.y;
+                acc[s][n][2] += s1 * c[n][2] + b1 * xs.x;
+                acc[s][n][3] += s1 * c[n][3] + b1 * xs.y;
+            }
+        }
+    }
+    // A warp with no group in the last quarters still has to see every copy land.
+    while (waited < kBars - 1) {
+        ++waited;
+        if (!mbar_wait_bounded(&bars[waited], 0)) ok = false;
+    }
+    if (!ok && lane == 0 && a.err) atomicOr(a.err, KERR_BARRIER_TIMEOUT);
+
+    // ── fixed-order reduction across the CTA's warps ──
+    constexpr int VPT = NW * NBT * 4;  // values per thread
+    {
+        float* dst = sred + (size_t)(warp * 32 + lane) * VPT;
+#pragma unroll
+        for (int s = 0; s < NW; ++s)
+#pragma unroll
+            for (int n = 0; n < NBT; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[(s * NBT + n) * 4 + i] = acc[s][n][i];
+    }
+    __syncthreads();
+    float tot[VPT];
+    if (warp == 0) {
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) sum += sred[(size_t)(w * 32 + lane) * VPT + v];
+            tot[v] = sum;
+        }
+    }
+
+    // ── fixed-order reduction across the K-slices (cluster ranks) through distributed smem ──
+    if (a.nsplit > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        const unsigned rank = cluster.block_rank();
+        cluster.sync();  // every CTA of the cluster is done reading its own sred
+        if (warp == 0 && rank != 0) {
+            float* remote = cluster.map_shared_rank(sred, 0);
+#pragma unroll
+            for (int v = 0; v < VPT; ++v) remote[(size_t)(rank * 32 + lane) * VPT + v] = tot[v];
+        }
+        cluster.sync();
+        if (rank != 0) return;
+        if (warp == 0) {
+            for (int r = 1; r < a.nsplit; ++r)
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) tot[v] += sred[(size_t)(r * 32 + lane) * VPT + v];
+        }
+    }
+    if (warp != 0) return;
+
+    // ── epilogue: thread (g,t) owns rows g, g+8 and batch columns 2t, 2t+1 of every n-tile ──
+#pragma unroll
+    for (int n = 0; n < NBT; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = row0 + g + (i >> 1) * 8;
+            const int b = n * 8 + 2 * t + (i & 1);
+            if (row >= a.rows || b >= a.batch) continue;
+            const size_t o = (size_t)b * a.rows + row;
+            const float v0 = tot[(0 * NBT + n) * 4 + i];
+            if (MODE == kAffinePlain) {
+                a.y[o] = __float2half_rn(v0);
+            } else if (MODE == kAffineAdd) {
+                // half(acc) first, then an fp16 add with the residual (lut_matvec.metal:1802-1803)
+                a.y[o] = __hadd(__float2half_rn(v0), a.residual[o]);
+            } else if (MODE == kAffineGateUp) {
+                const float v1 = tot[(1 * NBT + n) * 4 + i];
+                a.y[o] = __float2half_rn(v0 / (1.0f + expf(-v0)) * v1);  // lut_matvec.metal:2228
+            } else {
+                a.y[o] = __float2half_rn(v0);
+                a.y2[o] = __float2half_rn(tot[(1 * NBT + n) * 4 + i]);
+            }
+        }
+}
+
+template <int MODE, int GROUP, int NBT>
+cudaError_t launch_t(const Launch& l, AffineArgs a) {
+    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    // K-slice: at most 4096 columns, an equal number of groups per slice where possible.
+    const int groups = a.cols / GROUP;
+    int max_gs = 4096 / GROUP, nsplit = 1;
+    SmemLayout L;
+    for (;; max_gs /= 2) {
+        if (max_gs == 0) return cudaErrorInvalidValue;
+        nsplit = (groups + max_gs - 1) / max_gs;
+        if (nsplit > 8) return cudaErrorInvalidValue;
+        const int gs = (groups + nsplit - 1) / nsplit;
+        nsplit = (groups + gs - 1) / gs;
+        a.ks = gs * GROUP;
+        L = make_layout<GROUP>(NW, NBT * 8, a.ks, a.batch);
+        if (L.total <= 200u * 1024u) break;
+    }
+    a.nsplit = nsplit;
+    a.dyn = dev_dyn(l);
+    auto kern = affine_mma_kernel<MODE, GROUP, NBT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((a.rows + kRows - 1) / kRows, nsplit, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L.total;
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (nsplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = nsplit;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (l.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
+template <int MODE, int GROUP>
+cudaError_t launch_nb(const Launch& l, const AffineArgs& a) {
+    if (a.batch <= 8) return launch_t<MODE, GROUP, 1>(l, a);
+    if (a.batch <= 16) return launch_t<MODE, GROUP, 2>(l, a);
+    return cudaErrorInvalidValue;
+}
+
+template <int MODE>
+cudaError_t launch_group(const Launch& l, const AffineArgs& a, int group) {
+    switch (group) {
+        case 32: return launch_nb<MODE, 32>(l, a);
+        case 64: return launch_nb<MODE, 64>(l, a);
+        case 128: return launch_nb<MODE, 128>(l, a);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int group) {
+    if (args.rows <= 0 || args.cols <= 0 || args.batch <= 0 || args.cols % group != 0) return cudaErrorInvalidValue;
+    // Batches beyond 16 rows are processed in passes of 16 (weights re-streamed per pass).
+    if (args.batch > 16) {
+        for (int b0 = 0; b0 < args.batch; b0 += 16) {
+            AffineArgs s = args;
+            s.batch = args.batch - b0 < 16 ? args.batch - b0 : 16;
+            s.x = args.x + (size_t)b0 * args.cols;
+            s.y = args.y + (size_t)b0 * args.rows;
+            if (args.y2) s.y2 = args.y2 + (size_t)b0 * args.rows;
+            if (args.residual) s.residual = args.residual + (size_t)b0 * args.rows;
+            cudaError_t e = launch_affine(l, mode, s, group);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    switch (mode) {
+        case kAffinePlain: return launch_group<kAffinePlain>(l, args, group);
+        case kAffineAdd: return launch_group<kAffineAdd>(l, args, group);
+        case kAffineGateUp: return launch_group<kAffineGateUp>(l, args, group);
+        case kAffineDual: return launch_group<kAffineDual>(l, args, group);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace smelt

@@ -1,0 +1,330 @@
+// Single-token GQA attention over an fp16 KV cache: split-K flash-decode for sm_100a.
+//
+// Replaces the reference's attention_decode family (Resources/Shaders/attention.metal:217-314
+// generic three-pass kernel, :981-1065 one-pass online softmax, :1071-1206 two-pass split-K,
+// :1211-1309 D128 sdpa) with one kernel pair.  Semantics follow the reference oracle
+// (Tests/SmeltCompilerTests/RegionExactnessTests.swift:1414-1475): scores = (q.k) * scale over
+// keys [seqStart, seqLen), softmax in fp32, output rounded to fp16 once; K and V are laid out
+// [n_kv, capacity, head_dim] per sequence and GQA maps query head h to KV head h / (n_q/n_kv).
+//
+// Data path.  Grid = (splits, n_kv, batch); a CTA of four warps owns a contiguous key range
+// of one KV head and all query heads that share it, so K and V are read from HBM exactly
+// once.  A warp walks 16-key tiles.  S^T = K·Q^T and O^T = V^T·P^T both run on
+// mma.sync.m16n8k16 (keys or head dims on M, the <= 8 grouped query heads on N), which keeps
+// the CUDA cores free for loads and the online softmax; K fragments are 16-byte loads used
+// directly as the A operand (the contraction order over head_dim is permuted consistently in
+// Q), V is loaded 16 bytes per key and paired across keys with byte permutes, and P is
+// transposed into B-operand layout with movmatrix.  Probabilities are rounded to fp16 for
+// the tensor pipe and the denominator is accumulated from the rounded values, so the weights
+// sum to one exactly.  Warp states are merged in shared memory; splits write fp32 partial
+// (max, sum, O) triples to a scratch buffer that a second kernel merges in split order.
+#include "glue.h"
+
+namespace smelt {
+
+namespace {
+
+constexpr int kAttnThreads = 128;
+constexpr int kAttnWarps = 4;
+constexpr int kMaxSplits = 64;
+constexpr float kNegBig = -1.0e30f;
+
+struct AttnDev {
+    AttnArgs a;
+    int nsplits;
+    float* part_o;   // [batch*n_q, nsplits, head_dim]
+    float* part_ml;  // [batch*n_q, nsplits, 2]
+    DevDyn dyn;
+};
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+__device__ __forceinline__ void key_range(const AttnDev& p, uint32_t& seq_start, uint32_t& seq_len) {
+    seq_len = p.a.seq_from_pos ? dyn_position(p.dyn) + 1u : p.a.seq_len;
+    if (seq_len > p.a.capacity) seq_len = p.a.capacity;
+    seq_start = 0;
+    if (p.a.sliding_window > 0 && p.a.sliding_window < seq_len) seq_start = seq_len - p.a.sliding_window;
+}
+
+template <int D, int NH>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev p) {
+    constexpr int MT = D / 16;  // m-tiles of O^T
+    constexpr int KJ = D / 32;  // 16-byte chunks per thread per K row
+    constexpr int VC = D / 64;  // 16-byte chunks per thread per V row
+    extern __shared__ __align__(16) float smem_f[];
+
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(p.dyn)) return;
+
+    const AttnArgs& a = p.a;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int ratio = a.n_q / a.n_kv;
+
+    uint32_t seq_start, seq_len;
+    key_range(p, seq_start, seq_len);
+    const uint32_t n = seq_len - seq_start;
+    uint32_t per = (n + p.nsplits - 1) / p.nsplits;
+    per = (per + 15u) & ~15u;
+    const uint32_t k_begin = min(seq_len, seq_start + (uint32_t)split * per);
+    const uint32_t k_end = min(seq_len, k_begin + per);
+
+    const __half* Kb = a.k_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
+    const __half* Vb = a.v_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
+
+    // Q^T fragments: thread (g,t) keeps head g's dims [32j + 8t, +8) for every j.
+    uint32_t qf[NH][D / 8];
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+        const int hl = nh * 8 + g;
+        if (hl < ratio) {
+            const __half* qh = a.q + ((size_t)b * a.n_q + (size_t)kvh * ratio + hl) * D;
+#pragma unroll
+            for (int j = 0; j < KJ; ++j) {
+                const uint4 v = *reinterpret_cast<const uint4*>(qh + 32 * j + 8 * t);
+                qf[nh][4 * j + 0] = v.x; qf[nh][4 * j + 1] = v.y; qf[nh][4 * j + 2] = v.z; qf[nh][4 * j + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) qf[nh][j] = 0u;
+        }
+    }
+    const float scale2 = a.scale * 1.4426950408889634f;
+
+    float m_run[NH][2], l_run[NH][2], o[NH][MT][4];
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+        m_run[nh][0] = m_run[nh][1] = kNegBig;
+        l_run[nh][0] = l_run[nh][1] = 0.f;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) o[nh][i][0] = o[nh][i][1] = o[nh][i][2] = o[nh][i][3] = 0.f;
+    }
+
+    for (uint32_t kt = k_begin + warp * 16; kt < k_end; kt += kAttnWarps * 16) {
+        const uint32_t last = k_end - 1;
+        const uint32_t key_a = min(kt + g, last), key_b = min(kt + g + 8, last);
+        const bool valid_a = kt + g < k_end, valid_b = kt + g + 8 < k_end;
+        // V rows this thread contracts over: k-slots 2t, 2t+1, 2t+8, 2t+9 of the tile
+        uint32_t kv[4] = {min(kt + 2 * t, last), min(kt + 2 * t + 1, last), min(kt + 2 * t + 8, last), min(kt + 2 * t + 9, last)};
+
+        // ── S^T = K · Q^T ──
+        float s[NH][4];
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
+        const __half* ka_p = Kb + (size_t)key_a * D + 8 * t;
+        const __half* kb_p = Kb + (size_t)key_b * D + 8 * t;
+#pragma unroll
+        for (int j = 0; j < KJ; ++j) {
+            const uint4 ka = *reinterpret_cast<const uint4*>(ka_p + 32 * j);
+            const uint4 kb = *reinterpret_cast<const uint4*>(kb_p + 32 * j);
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) {
+                mma16816(s[nh], ka.x, kb.x, ka.y, kb.y, qf[nh][4 * j + 0], qf[nh][4 * j + 1]);
+                mma16816(s[nh], ka.z, kb.z, ka.w, kb.w, qf[nh][4 * j + 2], qf[nh][4 * j + 3]);
+            }
+        }
+
+        // ── online softmax per query head (columns 2t, 2t+1 of the tile) ──
+        uint32_t pb0[NH], pb1[NH];
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+            float v0 = valid_a ? s[nh][0] * scale2 : kNegBig, v1 = valid_a ? s[nh][1] * scale2 : kNegBig;
+            float v2 = valid_b ? s[nh][2] * scale2 : kNegBig, v3 = valid_b ? s[nh][3] * scale2 : kNegBig;
+            float mx0 = fmaxf(v0, v2), mx1 = fmaxf(v1, v3);
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
+            const float mn0 = fmaxf(m_run[nh][0], mx0), mn1 = fmaxf(m_run[nh][1], mx1);
+            const float c0 = exp2f(m_run[nh][0] - mn0), c1 = exp2f(m_run[nh][1] - mn1);
+            m_run[nh][0] = mn0; m_run[nh][1] = mn1;
+            const __half2 pa = __floats2half2_rn(valid_a ? exp2f(v0 - mn0) : 0.f, valid_a ? exp2f(v1 - mn1) : 0.f);
+            const __half2 pb = __floats2half2_rn(valid_b ? exp2f(v2 - mn0) : 0.f, valid_b ? exp2f(v3 - mn1) : 0.f);
+            const float2 paf = __half22float2(pa), pbf = __half22float2(pb);
+            l_run[nh][0] = l_run[nh][0] * c0 + (paf.x + pbf.x);
+            l_run[nh][1] = l_run[nh][1] * c1 + (paf.y + pbf.y);
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                o[nh][i][0] *= c0; o[nh][i][2] *= c0;
+                o[nh][i][1] *= c1; o[nh][i][3] *= c1;
+            }
+            pb0[nh] = movmatrix_trans(h2_as_u32(pa));  // {P[key 2t][head g], P[key 2t+1][head g]}
+            pb1[nh] = movmatrix_trans(h2_as_u32(pb));  // keys 2t+8, 2t+9
+        }
+
+        // ── O^T += V^T · P^T ──
+#pragma unroll
+        for (int c = 0; c < VC; ++c) {
+            uint4 vv[4];
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                vv[kk] = *reinterpret_cast<const uint4*>(Vb + (size_t)kv[kk] * D + 64 * c + 8 * g);
+            const uint32_t r0[4] = {vv[0].x, vv[0].y, vv[0].z, vv[0].w};
+            const uint32_t r1[4] = {vv[1].x, vv[1].y, vv[1].z, vv[1].w};
+            const uint32_t r2[4] = {vv[2].x, vv[2].y, vv[2].z, vv[2].w};
+            const uint32_t r3[4] = {vv[3].x, vv[3].y, vv[3].z, vv[3].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t a0 = __byte_perm(r0[e], r1[e], 0x5410), a1 = __byte_perm(r0[e], r1[e], 0x7632);
+                const uint32_t a2 = __byte_perm(r2[e], r3[e], 0x5410), a3 = __byte_perm(r2[e], r3[e], 0x7632);
+#pragma unroll
+                for (int nh = 0; nh < NH; ++nh) mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pb0[nh], pb1[nh]);
+            }
+        }
+    }
+
+    // per-thread partial denominators cover keys g, g+8 only: finish the sum over g
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh)
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l_run[nh][0] += __shfl_xor_sync(0xffffffffu, l_run[nh][0], off);
+            l_run[nh][1] += __shfl_xor_sync(0xffffffffu, l_run[nh][1], off);
+        }
+
+    // ── merge the four warps through shared memory ──
+    constexpr int HN = NH * 8;
+    float* s_o = smem_f;                                  // [warps][HN][D]
+    float* s_ml = smem_f + kAttnWarps * HN * D;           // [warps][HN][2]
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+        if (g == 0) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                s_ml[((warp * HN) + nh * 8 + 2 * t + c) * 2 + 0] = m_run[nh][c];
+                s_ml[((warp * HN) + nh * 8 + 2 * t + c) * 2 + 1] = l_run[nh][c];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int head = nh * 8 + 2 * t + (c & 1);
+                const int j = 2 * i + (c >> 1);                      // index among this thread's dims
+                const int dim = 64 * (j >> 3) + 8 * g + (j & 7);
+                s_o[(size_t)(warp * HN + head) * D + dim] = o[nh][i][c];
+            }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < ratio * D; idx += kAttnThreads) {
+        const int h = idx / D, d = idx % D;
+        float mstar = kNegBig;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) mstar = fmaxf(mstar, s_ml[(w * HN + h) * 2]);
+        float acc = 0.f, lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float f = exp2f(s_ml[(w * HN + h) * 2] - mstar);
+            acc += s_o[(size_t)(w * HN + h) * D + d] * f;
+            lsum += s_ml[(w * HN + h) * 2 + 1] * f;
+        }
+        const size_t qh = (size_t)b * a.n_q + (size_t)kvh * ratio + h;
+        if (p.nsplits == 1) {
+            a.out[qh * D + d] = __float2half_rn(acc / lsum);
+        } else {
+            p.part_o[(qh * p.nsplits + split) * D + d] = acc;
+            if (d == 0) {
+                p.part_ml[(qh * p.nsplits + split) * 2 + 0] = mstar;
+                p.part_ml[(qh * p.nsplits + split) * 2 + 1] = lsum;
+            }
+        }
+    }
+}
+
+// Merge the per-split partials of one (sequence, query head) in split order.
+__global__ void attn_merge_kernel(const AttnDev p) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(p.dyn)) return;
+    const int D = p.a.head_dim;
+    const size_t qh = blockIdx.x;
+    float mstar = kNegBig;
+    for (int s = 0; s < p.nsplits; ++s) mstar = fmaxf(mstar, p.part_ml[(qh * p.nsplits + s) * 2]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f, lsum = 0.f;
+        for (int s = 0; s < p.nsplits; ++s) {
+            const float f = exp2f(p.part_ml[(qh * p.nsplits + s) * 2] - mstar);
+            acc += p.part_o[(qh * p.nsplits + s) * D + d] * f;
+            lsum += p.part_ml[(qh * p.nsplits + s) * 2 + 1] * f;
+        }
+        p.a.out[qh * D + d] = __float2half_rn(acc / lsum);
+    }
+}
+
+template <int D, int NH>
+cudaError_t launch_decode_t(const Launch& l, const AttnDev& p) {
+    const size_t smem = (size_t)kAttnWarps * NH * 8 * (D + 2) * sizeof(float);
+    auto kern = attn_decode_kernel<D, NH>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.nsplits, p.a.n_kv, p.a.batch);
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = l.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+}  // namespace
+
+int attention_max_splits() { return kMaxSplits; }
+
+size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits) {
+    return (size_t)batch * n_q * max_splits * (head_dim + 2) * sizeof(float);
+}
+
+cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
+    if (a.n_q <= 0 || a.n_kv <= 0 || a.n_q % a.n_kv != 0 || a.batch <= 0) return cudaErrorInvalidValue;
+    const int ratio = a.n_q / a.n_kv;
+    if (ratio > 16 || (a.head_dim != 64 && a.head_dim != 128 && a.head_dim != 256)) return cudaErrorInvalidValue;
+    const uint32_t n_max = a.seq_from_pos ? a.capacity : (a.seq_len < a.capacity ? a.seq_len : a.capacity);
+    if (n_max == 0) return cudaErrorInvalidValue;
+    const int sm = a.sm_count > 0 ? a.sm_count : 148;
+    int want = (3 * sm + a.n_kv * a.batch - 1) / (a.n_kv * a.batch);
+    int by_len = (int)((n_max + 127u) / 128u);
+    int nsplits = want < by_len ? want : by_len;
+    if (nsplits < 1) nsplits = 1;
+    if (nsplits > kMaxSplits) nsplits = kMaxSplits;
+    while (nsplits > 1 && attention_scratch_bytes(a.n_q, a.head_dim, a.batch, nsplits) > a.scratch_bytes) --nsplits;
+    AttnDev p;
+    p.a = a;
+    p.nsplits = nsplits;
+    p.part_o = reinterpret_cast<float*>(a.scratch);
+    p.part_ml = p.part_o ? p.part_o + (size_t)a.batch * a.n_q * nsplits * a.head_dim : nullptr;
+    p.dyn = dev_dyn(l);
+    cudaError_t e;
+    const int nh = ratio > 8 ? 2 : 1;
+#define SMELT_ATTN_CASE(DD)                                                                 \
+    case DD: e = nh == 1 ? launch_decode_t<DD, 1>(l, p) : launch_decode_t<DD, 2>(l, p); break;
+    switch (a.head_dim) {
+        SMELT_ATTN_CASE(64)
+        SMELT_ATTN_CASE(128)
+        SMELT_ATTN_CASE(256)
+        default: return cudaErrorInvalidValue;
+    }
+#undef SMELT_ATTN_CASE
+    if (e != cudaSuccess || nsplits == 1) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.batch * a.n_q);
+    cfg.blockDim = dim3(a.head_dim < 128 ? 64 : 128);
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = l.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+}
+
+}  // namespace smelt

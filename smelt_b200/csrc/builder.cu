@@ -1,0 +1,211 @@
+// Decoder table builder: writes the per-token SmeltDispatchRecord sequence the reference
+// compiler emits for a plain attention decoder (Sources/SmeltCompiler/TopLevelEmitter.swift
+// :89-930 generatePlanned; Sources/SmeltCompiler/AttentionPlugin.swift:105-560 emitLayer;
+// record encoding Sources/SmeltCompiler/SmeltCodeEmitter.swift:348 toRecord), allocates the
+// slots it binds (numbers follow SmeltFixedSlot, Sources/SmeltCompiler/SmeltBufferPlan.swift
+// :129-198) and registers the pipeline names.  It stands in for the build-time Swift
+// compiler, which is outside the decode path.
+#include <cmath>
+#include <cstring>
+#include <map>
+
+#include "runtime.h"
+
+using namespace smelt;
+
+namespace {
+
+enum FixedSlot : int {
+    kHiddenA = 0, kHiddenB = 1, kNormOut = 8, kFfnInt = 13, kFfnDown = 14, kLogits = 16, kArgmax = 17,
+    kAttnQ = 20, kAttnK = 21, kAttnV = 22, kAttnOut = 23, kWeights = 30,
+    kTokenId = 33, kPosition = 34, kArgmaxScratch = 35, kKvBase = 40,
+};
+
+uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+struct Emitter {
+    smelt_cuda_ctx* ctx;
+    smelt_dispatch_record* out;
+    size_t cap, n = 0;
+    std::map<std::string, int> pipes;
+    smelt_status status = SMELT_OK;
+
+    int pipe(const std::string& name) {
+        auto it = pipes.find(name);
+        if (it != pipes.end()) return it->second;
+        const int idx = (int)pipes.size();
+        if (ctx) {
+            smelt_status s = smelt_cuda_register_pipeline(ctx, idx, name.c_str());
+            if (s && !status) status = s;
+        }
+        pipes[name] = idx;
+        return idx;
+    }
+    smelt_dispatch_record* next() {
+        static smelt_dispatch_record scratch;
+        smelt_dispatch_record* r = (out && n < cap) ? &out[n] : &scratch;
+        memset(r, 0, sizeof(*r));
+        ++n;
+        return r;
+    }
+    void swap() { next()->op_kind = SMELT_OP_SWAP; }
+};
+
+struct Rec {
+    smelt_dispatch_record* r;
+    Rec(Emitter& e, const std::string& name, uint32_t gx = 1, uint32_t gy = 1) : r(e.next()) {
+        r->op_kind = SMELT_OP_DISPATCH;
+        r->pipeline = (uint16_t)e.pipe(name);
+        r->grid[0] = gx; r->grid[1] = gy; r->grid[2] = 1;
+        r->threadgroup[0] = 64; r->threadgroup[1] = 1; r->threadgroup[2] = 1;
+    }
+    Rec& buf(int binding, int slot, uint64_t offset = 0) {
+        smelt_buffer_record& b = r->buf[r->buffer_count++];
+        b.slot = (int16_t)slot; b.binding_index = (uint8_t)binding; b.offset_kind = 0; b.offset = offset;
+        return *this;
+    }
+    Rec& con(int binding, uint8_t kind, uint32_t value = 0) {
+        smelt_constant_record& c = r->con[r->constant_count++];
+        c.kind = kind; c.binding_index = (uint8_t)binding; c.value = value;
+        return *this;
+    }
+    Rec& u32(int binding, uint32_t v) { return con(binding, SMELT_CONST_LITERAL_U32, v); }
+    Rec& f32(int binding, float v) { return con(binding, SMELT_CONST_LITERAL_F32, f32_bits(v)); }
+    Rec& affine(int first, const smelt_affine_ref& w) {
+        return buf(first, kWeights, w.packed).buf(first + 1, kWeights, w.scales).buf(first + 2, kWeights, w.biases);
+    }
+};
+
+std::string shaped(const char* base, int cols, int rows, int group, bool batched) {
+    return std::string(base) + "_c" + std::to_string(cols) + "_r" + std::to_string(rows) + "_g" + std::to_string(group) + (batched ? "_batched" : "");
+}
+
+}  // namespace
+
+extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d,
+                                                 const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
+                                                 smelt_dispatch_record* records, size_t* n_records) {
+    if (!d || !layers || !n_records) return SMELT_ERR_BAD_ARGUMENT;
+    if (d->layers <= 0 || d->hidden <= 0 || d->inter <= 0 || d->n_q <= 0 || d->n_kv <= 0 || d->n_q % d->n_kv || d->head_dim <= 0 ||
+        d->vocab <= 0 || batch == 0 || batch > 64 || capacity == 0 || d->layers > 100)
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: bad model description");
+    const bool dry = records == nullptr;
+    const int H = d->hidden, I = d->inter, D = d->head_dim, G = d->group, B = (int)batch;
+    const int qd = d->n_q * D, kvd = d->n_kv * D, L = d->layers, V = d->vocab;
+    const bool tp = d->tp_world > 1;
+    const bool fuse = d->fuse_residual && !tp;
+    const bool bt = B > 1;  // batched kernel names bind actualBatch instead of numRows
+
+    if (!dry) {
+        if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
+        if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+        if (kKvBase + 2 * L > (int)ctx->slots.size()) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: too many layers for the slot table");
+        if (!ctx->slots[kWeights].ptr) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: upload the weights image to slot 30 first");
+        const int chunk = 2048, parts = (V + chunk - 1) / chunk;
+        struct { int slot; size_t bytes; } plan[] = {
+            {kHiddenA, (size_t)B * H * 2}, {kHiddenB, (size_t)B * H * 2}, {kNormOut, (size_t)B * H * 2},
+            {kFfnInt, (size_t)B * I * 2}, {kFfnDown, (size_t)B * H * 2}, {kLogits, (size_t)B * V * 2},
+            {kArgmax, (size_t)B * 4 < 8 ? 8 : (size_t)B * 4}, {kAttnQ, (size_t)B * qd * 2}, {kAttnK, (size_t)B * kvd * 2},
+            {kAttnV, (size_t)B * kvd * 2}, {kAttnOut, (size_t)B * qd * 2}, {kTokenId, (size_t)B * 4},
+            {kPosition, 8}, {kArgmaxScratch, (size_t)parts * B * 8},
+        };
+        for (auto& p : plan) {
+            smelt_status s = smelt_cuda_alloc_slot(ctx, p.slot, p.bytes);
+            if (s) return s;
+        }
+        const size_t kv_bytes = (size_t)B * d->n_kv * capacity * D * 2;  // heads * capacity * headDim * 2 per sequence
+        for (int l = 0; l < 2 * L; ++l) {
+            smelt_status s = smelt_cuda_alloc_slot(ctx, kKvBase + l, kv_bytes);
+            if (s) return s;
+        }
+        smelt_cuda_runtime_config cfg = {};
+        cfg.token_id_slot = kTokenId; cfg.position_slot = kPosition; cfg.weights_slot = kWeights; cfg.argmax_slot = kArgmax;
+        cfg.cur_slot = kHiddenA; cfg.alt_slot = kHiddenB; cfg.cache_seq_capacity = capacity; cfg.context_limit = capacity;
+        cfg.vocab_size = (uint32_t)V; cfg.batch = batch;
+        smelt_status s = smelt_cuda_configure(ctx, &cfg);
+        if (s) return s;
+        ctx->pipelines.clear();
+    }
+
+    Emitter e{dry ? nullptr : ctx, records, dry ? 0 : *n_records};
+    const float log2_theta = log2f(d->rope_theta);
+    const float scale = 1.0f / sqrtf((float)D);
+    auto matvec_name = [&](int cols, int rows) {
+        return bt ? shaped("affine_matvec", cols, rows, G, true) : "affine_matvec:" + std::to_string(cols) + ":" + std::to_string(G);
+    };
+    auto count_const = [&](Rec& r, int binding, int rows) { r.u32(binding, bt ? (uint32_t)B : (uint32_t)rows); };
+
+    // embedding gather -> hiddenA (TopLevelEmitter.swift:164-228)
+    Rec(e, "embedding_gather", (H + 63) / 64, B).buf(0, kWeights, d->embedding).buf(1, kTokenId).buf(2, SMELT_SLOT_CUR).u32(3, H);
+
+    for (int l = 0; l < L; ++l) {
+        const smelt_layer_ref& w = layers[l];
+        const int kslot = kKvBase + l, vslot = kKvBase + L + l;
+        // input norm (TopLevelEmitter.swift:316-326)
+        Rec(e, "rms_norm_1pw", B).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, w.input_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
+        // Q projection; fused dual K/V projection (AttentionPlugin.swift:105-300)
+        { Rec r(e, matvec_name(H, qd), (qd + 7) / 8); r.affine(0, w.q).buf(3, kNormOut).buf(4, kAttnQ); count_const(r, 5, qd); }
+        {
+            Rec r(e, bt ? shaped("fused_dual_affine_matvec", H, kvd, G, true) : "fused_dual_affine_matvec:" + std::to_string(H) + ":" + std::to_string(G), (kvd + 7) / 8);
+            r.affine(0, w.k).affine(3, w.v).buf(6, kNormOut).buf(7, kAttnK).buf(8, kAttnV);
+            count_const(r, 9, kvd);
+        }
+        // RoPE on Q, fused RoPE + K append, V append (AttentionPlugin.swift:300-560; analytic mode :344-346)
+        Rec(e, "apply_rope", (qd + 63) / 64, B).buf(0, kAttnQ).buf(1, kAttnQ).buf(2, kAttnQ)
+            .u32(3, D).u32(4, D).u32(5, d->n_q).u32(6, 1).con(7, SMELT_CONST_POSITION).f32(8, log2_theta).u32(9, 1);
+        {
+            Rec r(e, "rope_kv_cache_update", (kvd + 63) / 64, B);
+            r.buf(0, kslot).buf(1, kAttnK).buf(2, kAttnK).buf(3, kAttnK).con(4, SMELT_CONST_CACHE_SEQ_CAPACITY).u32(5, D)
+                .con(6, SMELT_CONST_POSITION).u32(7, d->n_kv);
+            // split-half layout over the full head, analytic trig: exactly the eight constants a record holds
+            r.u32(8, D).u32(9, 1).f32(10, log2_theta).u32(11, 1);
+        }
+        Rec(e, "kv_cache_update", (kvd + 63) / 64, B).buf(0, vslot).buf(1, kAttnV).con(2, SMELT_CONST_CACHE_SEQ_CAPACITY).u32(3, D)
+            .con(4, SMELT_CONST_POSITION).u32(5, d->n_kv);
+        // attention decode (AttentionPlugin.swift:738-984): one threadgroup per query head
+        Rec(e, "attention_decode", d->n_q, B).buf(0, kAttnQ).buf(1, kslot).buf(2, vslot).buf(3, kAttnQ).buf(4, kAttnOut)
+            .u32(5, D).con(6, SMELT_CONST_CACHE_SEQ_CAPACITY).con(7, SMELT_CONST_POSITION_PLUS1).u32(8, d->n_kv).f32(9, scale).u32(10, 0);
+        // O projection + residual (TopLevelEmitter.swift:417-429)
+        if (fuse) {
+            Rec r(e, bt ? shaped("fused_affine_matvec_add", qd, H, G, true) : "fused_affine_matvec_add:" + std::to_string(qd) + ":" + std::to_string(G), (H + 7) / 8);
+            r.affine(0, w.o).buf(3, kAttnOut).buf(4, SMELT_SLOT_ALT).buf(5, SMELT_SLOT_CUR);
+            count_const(r, 6, H);
+        } else {
+            { Rec r(e, matvec_name(qd, H), (H + 7) / 8); r.affine(0, w.o).buf(3, kAttnOut).buf(4, kNormOut); count_const(r, 5, H); }
+            if (tp) Rec(e, "smelt_tp_all_reduce").buf(0, kNormOut).u32(1, (uint32_t)(B * H));
+            Rec(e, "elementwise_add", (B * H + 63) / 64).buf(0, SMELT_SLOT_CUR).buf(1, kNormOut).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)(B * H));
+        }
+        e.swap();
+        // post-attention norm + FFN (TopLevelEmitter.swift:1021-1322 emitSwiGLU)
+        Rec(e, "rms_norm_1pw", B).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, w.post_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
+        {
+            Rec r(e, bt ? shaped("fused_affine_gate_up_swiglu", H, I, G, true) : "fused_affine_gate_up_swiglu:" + std::to_string(H) + ":" + std::to_string(G), (I + 7) / 8);
+            r.affine(0, w.gate).affine(3, w.up).buf(6, kNormOut).buf(7, kFfnInt);
+            count_const(r, 8, I);
+        }
+        if (fuse) {
+            Rec r(e, bt ? shaped("fused_affine_matvec_add", I, H, G, true) : "fused_affine_matvec_add:" + std::to_string(I) + ":" + std::to_string(G), (H + 7) / 8);
+            r.affine(0, w.down).buf(3, kFfnInt).buf(4, SMELT_SLOT_ALT).buf(5, SMELT_SLOT_CUR);
+            count_const(r, 6, H);
+        } else {
+            { Rec r(e, matvec_name(I, H), (H + 7) / 8); r.affine(0, w.down).buf(3, kFfnInt).buf(4, kFfnDown); count_const(r, 5, H); }
+            if (tp) Rec(e, "smelt_tp_all_reduce").buf(0, kFfnDown).u32(1, (uint32_t)(B * H));
+            Rec(e, "elementwise_add", (B * H + 63) / 64).buf(0, SMELT_SLOT_CUR).buf(1, kFfnDown).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)(B * H));
+        }
+        e.swap();
+    }
+    // final norm, LM head, argmax (TopLevelEmitter.swift:657-930)
+    Rec(e, "rms_norm_1pw", B).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, d->final_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
+    Rec(e, "fp16_matvec", V, B).buf(0, kWeights, d->lm_head).buf(1, kNormOut).buf(2, kLogits).u32(3, H);
+    const int chunk = 2048, parts = (V + chunk - 1) / chunk;
+    Rec(e, "argmax_fp16_partials", parts, B).buf(0, kLogits).buf(1, kArgmaxScratch).u32(2, V).u32(3, chunk);
+    Rec(e, "argmax_key_reduce", 1, B).buf(0, kArgmaxScratch).buf(1, kArgmax).u32(2, parts);
+
+    const size_t need = e.n;
+    if (!dry && need > *n_records) {
+        *n_records = need;
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: record buffer too small");
+    }
+    *n_records = need;
+    return e.status;
+}

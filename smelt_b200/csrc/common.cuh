@@ -1,0 +1,139 @@
+// Shared device/host helpers for the libsmelt_cuda kernels (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace smelt {
+
+// Per-launch dynamic state shared by every kernel the dispatch interpreter launches.
+// `dyn` points at the context's device-resident {token, position} pair so that a captured
+// CUDA graph can be replayed for every token without re-recording kernel parameters; when it
+// is null the literal position is used.  The guard fields mirror the reference's
+// "skip unless position+1 < / >= literal" constants
+// (Sources/SmeltSchema/SmeltDispatchTable.swift:80-83): a guarded kernel returns at once when
+// its condition is false.
+struct DynState {
+    int32_t token;
+    uint32_t position;
+};
+
+struct Launch {
+    cudaStream_t stream = nullptr;
+    const DynState* dyn = nullptr;  // device pointer or null
+    uint32_t position = 0;          // used when dyn == null
+    uint32_t guard_lt = 0;          // 0 = no guard; else run only if position+1 <  guard_lt
+    uint32_t guard_ge = 0;          // 0 = no guard; else run only if position+1 >= guard_ge
+    uint32_t arg_pos = 0;           // literal position argument of the kernel, when arg_pos_valid
+    uint32_t arg_pos_valid = 0;
+    bool pdl = false;               // launch with programmatic stream serialization
+};
+
+struct DevDyn {
+    const DynState* dyn;
+    uint32_t position;
+    uint32_t guard_lt;
+    uint32_t guard_ge;
+    uint32_t arg_pos;
+    uint32_t arg_pos_valid;
+};
+
+inline DevDyn dev_dyn(const Launch& l) {
+    return DevDyn{l.dyn, l.position, l.guard_lt, l.guard_ge, l.arg_pos, l.arg_pos_valid};
+}
+
+// The token position of the step being decoded (drives guards and "position" constants).
+__device__ __forceinline__ uint32_t dyn_position(const DevDyn& d) { return d.dyn ? d.dyn->position : d.position; }
+// The kernel's own position argument: a literal from the record when one was bound, else the
+// step position.
+__device__ __forceinline__ uint32_t dyn_arg_position(const DevDyn& d) {
+    return d.arg_pos_valid ? d.arg_pos : dyn_position(d);
+}
+
+// True when the launch must be skipped.  Only valid after the grid dependency has resolved
+// (the position may be written by the preceding kernel in the stream).
+__device__ __forceinline__ bool dyn_skip(const DevDyn& d) {
+    if (d.guard_lt == 0 && d.guard_ge == 0) return false;
+    uint32_t p1 = dyn_position(d) + 1u;
+    if (d.guard_lt != 0 && !(p1 < d.guard_lt)) return true;
+    if (d.guard_ge != 0 && !(p1 >= d.guard_ge)) return true;
+    return false;
+}
+
+// Programmatic dependent launch: wait for the upstream grid (and its memory) / allow the
+// downstream grid to start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// mma.sync m16n8k16, fp16 operands, fp32 accumulate.
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// (a & b) | c in one LOP3.
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// ── mbarrier + bulk async copy (TMA, untiled) ───────────────────────────────
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^22 polls (each poll itself blocks for a hardware-defined
+// time slice) and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// Global -> shared bulk copy; dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Error word shared by all kernels of a context: 0 = ok; kernels OR in a code when a bounded
+// wait gives up so the host can report it instead of hanging.
+enum : uint32_t { KERR_BARRIER_TIMEOUT = 1u, KERR_FLAG_TIMEOUT = 2u };
+
+}  // namespace smelt

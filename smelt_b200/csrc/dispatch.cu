@@ -1,0 +1,750 @@
+// Pipeline registry, SmeltDispatchRecord interpreter, per-token decode step and CUDA-graph replay.
+//
+// The interpreter keeps the contract of SmeltRuntime.emitDecodeDispatchRecord
+// (Sources/SmeltRuntime/SmeltRuntime.swift:3187-3247): buffers are bound by binding index from
+// slot-indexed allocations at literal or position-scaled byte offsets, constants are resolved
+// by kind, guard constants may skip the dispatch, swap records exchange cur and alt.  What a
+// kernel name means (which binding is which operand) follows the Metal kernel signatures the
+// handlers cite.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "affine_matvec.h"
+#include "glue.h"
+#include "runtime.h"
+
+using namespace smelt;
+
+static_assert(sizeof(smelt_buffer_record) == 16, "SmeltBufferRecord is 16 bytes");
+static_assert(sizeof(smelt_constant_record) == 8, "SmeltConstantRecord is 8 bytes");
+static_assert(sizeof(smelt_dispatch_record) == 360, "SmeltDispatchRecord is 360 bytes");
+static_assert(offsetof(smelt_dispatch_record, pipeline) == 2 && offsetof(smelt_dispatch_record, style) == 4 &&
+                  offsetof(smelt_dispatch_record, buffer_count) == 5 && offsetof(smelt_dispatch_record, constant_count) == 6 &&
+                  offsetof(smelt_dispatch_record, min_seq_len) == 8 && offsetof(smelt_dispatch_record, grid) == 12 &&
+                  offsetof(smelt_dispatch_record, threadgroup) == 24 && offsetof(smelt_dispatch_record, buf) == 40 &&
+                  offsetof(smelt_dispatch_record, con) == 296,
+              "SmeltDispatchRecord field offsets");
+
+namespace smelt {
+
+namespace {
+
+bool starts_with(const std::string& s, const char* p) { return s.rfind(p, 0) == 0; }
+
+// Consumes "_c{C}_r{R}_g{G}" at the front of `rest`.
+bool parse_shape(std::string& rest, Pipeline* p) {
+    int c = 0, r = 0, g = 0, n = 0;
+    if (sscanf(rest.c_str(), "_c%d_r%d_g%d%n", &c, &r, &g, &n) == 3 && n > 0) {
+        p->cols = c; p->rows = r; p->group = g; p->fixed_shape = true;
+        rest = rest.substr(n);
+        return true;
+    }
+    return false;
+}
+
+bool parse_affine(const std::string& name, const char* base, PipeKind kind, Pipeline* p) {
+    if (!starts_with(name, base)) return false;
+    std::string rest = name.substr(strlen(base));
+    if (!rest.empty() && rest[0] != '_') return false;
+    Pipeline q = *p;
+    q.kind = kind;
+    if (!rest.empty()) {
+        if (!parse_shape(rest, &q)) return false;
+        if (starts_with(rest, "_rows4")) rest = rest.substr(6);
+        if (starts_with(rest, "_batched")) { q.batched = true; rest.clear(); }  // _batched, _batched_full, _batched_tile3, _batched_sg4_bt5, _batched_ext_b5 ...
+        if (!rest.empty()) return false;
+    }
+    *p = q;
+    return true;
+}
+
+}  // namespace
+
+bool parse_pipeline(const char* entry, Pipeline* out) {
+    if (!entry || !out) return false;
+    Pipeline p;
+    std::string e(entry);
+    std::string name = e;
+    size_t colon = e.find(':');
+    if (colon != std::string::npos) {
+        name = e.substr(0, colon);
+        int c = 0, g = 0;
+        if (sscanf(e.c_str() + colon, ":%d:%d", &c, &g) != 2 || c <= 0 || g <= 0) return false;
+        p.cols = c; p.group = g;
+    }
+    p.name = name;
+    // Longest prefixes first.
+    if (parse_affine(name, "fused_affine_gate_up_swiglu", PK_AFFINE_GATEUP, &p) ||
+        parse_affine(name, "fused_affine_matvec_add", PK_AFFINE_ADD, &p) ||
+        parse_affine(name, "fused_dual_affine_matvec", PK_AFFINE_DUAL, &p) ||
+        parse_affine(name, "affine_matvec", PK_AFFINE_MATVEC, &p)) {
+        if (p.cols <= 0 || (p.group != 32 && p.group != 64 && p.group != 128) || p.cols % p.group) return false;
+        *out = p;
+        return true;
+    }
+    struct Simple { const char* name; PipeKind kind; int bits; bool batched; };
+    static const Simple table[] = {
+        {"fp16_matvec", PK_FP16_MATVEC, 0, false},
+        {"embedding_gather", PK_EMBEDDING_GATHER, 0, false},
+        {"affine_embedding_gather", PK_AFFINE_EMBEDDING_GATHER, 0, false},
+        {"argmax_fp16_partials", PK_ARGMAX_PARTIALS, 0, false},
+        {"argmax_key_reduce", PK_ARGMAX_REDUCE, 0, false},
+        {"argmax_fp16", PK_ARGMAX_SINGLE, 0, false},
+        {"signed_binary_matvec_g128_rows8", PK_SIGNED_MATVEC, 1, false},
+        {"signed_binary_matvec_g128_rows8_batched_b4", PK_SIGNED_MATVEC, 1, true},
+        {"signed_ternary_matvec_g128_rows8", PK_SIGNED_MATVEC, 2, false},
+        {"signed_ternary_matvec_g128_rows8_batched_b4", PK_SIGNED_MATVEC, 2, true},
+        {"signed_binary_matvec_add_g128_rows8", PK_SIGNED_ADD, 1, false},
+        {"signed_binary_gate_up_swiglu_g128_rows8", PK_SIGNED_GATEUP, 1, false},
+        {"signed_binary_gate_up_swiglu_g128_rows8_batched_b4", PK_SIGNED_GATEUP, 1, true},
+        {"signed_ternary_affine_matvec_g128_rows8", PK_SIGNED_TERNARY_AFFINE, 2, false},
+        {"kv_cache_update", PK_KV_UPDATE, 0, false},
+        {"apply_rope", PK_APPLY_ROPE, 0, false},
+        {"rope_kv_cache_update", PK_ROPE_KV_UPDATE, 0, false},
+        {"attention_decode", PK_ATTN_GENERIC, 0, false},
+        {"rms_norm_1pw", PK_RMS_NORM, 0, false},
+        {"per_head_rms_norm", PK_PER_HEAD_NORM, 0, false},
+        {"elementwise_add", PK_ADD, 0, false},
+        {"swiglu_fused", PK_SWIGLU, 0, false},
+        {"smelt_tp_all_reduce", PK_TP_ALL_REDUCE, 0, false},
+    };
+    for (const Simple& s : table)
+        if (name == s.name) {
+            p.kind = s.kind; p.bits = s.bits; p.batched = s.batched;
+            *out = p;
+            return true;
+        }
+    // In-place shape-specialised decode attention:
+    // attention_decode_d{D}_h{H}_kv{KV}[_sdpa] (Resources/Shaders/attention.metal:422-977, :1211-1309)
+    // and attention_decode_mlx_vector_d256 (:981-1065, head counts bound as constants 5 and 6).
+    {
+        int d = 0, h = 0, kv = 0, n = 0;
+        if (sscanf(name.c_str(), "attention_decode_d%d_h%d_kv%d%n", &d, &h, &kv, &n) == 3) {
+            std::string rest = name.substr(n);
+            if ((rest.empty() || rest == "_sdpa") && (d == 64 || d == 128 || d == 256) && kv > 0 && h % kv == 0 && h / kv <= 16) {
+                p.kind = PK_ATTN_INPLACE; p.head_dim = d; p.n_q = h; p.n_kv = kv;
+                *out = p;
+                return true;
+            }
+            return false;
+        }
+        if (name == "attention_decode_mlx_vector_d256") {
+            p.kind = PK_ATTN_INPLACE; p.head_dim = 256;
+            *out = p;
+            return true;
+        }
+    }
+    return false;
+}
+
+namespace {
+
+struct RBuf {
+    bool present = false;
+    uint8_t* ptr = nullptr;   // base + resolved offset (literal, or position * stride when known on the host)
+    size_t avail = 0;         // bytes from ptr to the end of the slot
+    bool pos_strided = false; // offset is position * stride and position is only known on the device
+    uint64_t stride = 0;
+};
+struct RConst {
+    bool present = false;
+    uint8_t kind = 0;
+    uint32_t value = 0;
+};
+
+struct Resolved {
+    RBuf buf[32];
+    RConst con[32];
+    uint32_t guard_lt = 0, guard_ge = 0;
+    bool skip = false;
+};
+
+struct Interp {
+    smelt_cuda_ctx* ctx;
+    bool device_pos;    // graph capture: position lives on the device
+    uint32_t position;  // host copy (valid when !device_pos)
+    int cur, alt;
+    int launches = 0;
+};
+
+smelt_status resolve(Interp& in, const smelt_dispatch_record& rec, Resolved* out) {
+    smelt_cuda_ctx* ctx = in.ctx;
+    if (rec.buffer_count > 16 || rec.constant_count > 8) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record: buffer/constant count out of range");
+    for (int i = 0; i < rec.buffer_count; ++i) {
+        const smelt_buffer_record& b = rec.buf[i];
+        int slot = b.slot == SMELT_SLOT_CUR ? in.cur : (b.slot == SMELT_SLOT_ALT ? in.alt : b.slot);
+        if (slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].ptr)
+            return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "record binds slot " + std::to_string(slot) + " which is not allocated");
+        if (b.binding_index >= 32) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record: buffer binding index out of range");
+        RBuf& r = out->buf[b.binding_index];
+        r.present = true;
+        uint64_t off = b.offset;
+        if (b.offset_kind == 1) {
+            if (in.device_pos) { r.pos_strided = true; r.stride = b.offset; off = 0; }
+            else off = (uint64_t)in.position * b.offset;
+        } else if (b.offset_kind != 0) {
+            return fail(ctx, SMELT_ERR_UNSUPPORTED, "record: prefill offset kinds are outside the decode path");
+        }
+        if (off > ctx->slots[slot].bytes)
+            return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "record: offset " + std::to_string(off) + " is outside slot " + std::to_string(slot));
+        r.ptr = (uint8_t*)ctx->slots[slot].ptr + off;
+        r.avail = ctx->slots[slot].bytes - off;
+    }
+    for (int i = 0; i < rec.constant_count; ++i) {
+        const smelt_constant_record& c = rec.con[i];
+        switch (c.kind) {
+            case SMELT_CONST_SKIP_UNLESS_POS1_LT:
+                if (in.device_pos) out->guard_lt = c.value;
+                else if (!(in.position + 1u < c.value)) out->skip = true;
+                break;
+            case SMELT_CONST_SKIP_UNLESS_POS1_GE:
+                if (in.device_pos) out->guard_ge = c.value;
+                else if (!(in.position + 1u >= c.value)) out->skip = true;
+                break;
+            case SMELT_CONST_LITERAL_U32: case SMELT_CONST_LITERAL_F32: case SMELT_CONST_POSITION:
+            case SMELT_CONST_POSITION_PLUS1: case SMELT_CONST_CACHE_SEQ_CAPACITY:
+                break;
+            default:
+                return fail(ctx, SMELT_ERR_UNSUPPORTED, "record: constant kind " + std::to_string(c.kind) + " is outside the decode path");
+        }
+        if (c.binding_index != 255) {
+            if (c.binding_index >= 32) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record: constant binding index out of range");
+            RConst& r = out->con[c.binding_index];
+            r.present = true; r.kind = c.kind; r.value = c.value;
+        }
+    }
+    return SMELT_OK;
+}
+
+// A constant that must be known on the host (shapes, counts).
+bool host_u32(const Interp& in, const Resolved& r, int idx, uint32_t* v) {
+    const RConst& c = r.con[idx];
+    if (!c.present) return false;
+    switch (c.kind) {
+        case SMELT_CONST_LITERAL_U32: case SMELT_CONST_LITERAL_F32:
+        case SMELT_CONST_SKIP_UNLESS_POS1_LT: case SMELT_CONST_SKIP_UNLESS_POS1_GE:
+            *v = c.value; return true;
+        case SMELT_CONST_CACHE_SEQ_CAPACITY: *v = in.ctx->cfg.cache_seq_capacity; return true;
+        case SMELT_CONST_POSITION: if (in.device_pos) return false; *v = in.position; return true;
+        case SMELT_CONST_POSITION_PLUS1: if (in.device_pos) return false; *v = in.position + 1u; return true;
+        default: return false;
+    }
+}
+float as_f32(uint32_t bits) { float f; memcpy(&f, &bits, 4); return f; }
+
+Launch make_launch(const Interp& in, const Resolved& r) {
+    Launch l;
+    l.stream = in.ctx->stream;
+    l.pdl = in.ctx->pdl;
+    if (in.device_pos) {
+        l.dyn = in.ctx->dyn_dev;
+        l.guard_lt = r.guard_lt;
+        l.guard_ge = r.guard_ge;
+    } else {
+        l.position = in.position;
+    }
+    return l;
+}
+
+// Binds a "position"-valued kernel argument: the step position when the constant is dynamic,
+// else the literal.
+bool bind_pos_arg(const Interp& in, const Resolved& r, int idx, Launch* l) {
+    const RConst& c = r.con[idx];
+    if (!c.present) return false;
+    if (c.kind == SMELT_CONST_POSITION) return true;
+    uint32_t v;
+    if (!host_u32(in, r, idx, &v)) return false;
+    l->arg_pos = v;
+    l->arg_pos_valid = 1;
+    return true;
+}
+
+#define NEED_BUF(i)                                                                                        \
+    if (!r.buf[i].present) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": buffer binding " #i " is missing"); \
+    if (r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": position-scaled offset on binding " #i " cannot be captured")
+#define NEED_U32(i, var)                                                                                   \
+    uint32_t var = 0;                                                                                      \
+    if (!host_u32(in, r, i, &var)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": constant binding " #i " is missing or not host-resolvable")
+#define NEED_BYTES(i, n)                                                                                   \
+    if (r.buf[i].avail < (size_t)(n)) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": binding " #i " needs " + std::to_string((size_t)(n)) + " bytes, slot has " + std::to_string(r.buf[i].avail))
+
+int batch_of(const smelt_dispatch_record& rec) { return rec.grid[1] > 0 ? (int)rec.grid[1] : 1; }
+
+smelt_status run_affine(Interp& in, const Pipeline& p, const smelt_dispatch_record& rec, const Resolved& r) {
+    smelt_cuda_ctx* ctx = in.ctx;
+    // binding layouts: lut_matvec.metal:1157-1165 (matvec), :1718-1727 (add), :2152-2163 (gate/up), :1824-1836 (dual)
+    int ix, iy, iy2 = -1, ires = -1, icount;
+    int nw = 1;
+    switch (p.kind) {
+        case PK_AFFINE_MATVEC: ix = 3; iy = 4; icount = 5; break;
+        case PK_AFFINE_ADD: ix = 3; iy = 4; ires = 5; icount = 6; break;
+        case PK_AFFINE_GATEUP: nw = 2; ix = 6; iy = 7; icount = 8; break;
+        default: nw = 2; ix = 6; iy = 7; iy2 = 8; icount = 9; break;
+    }
+    int rows = p.rows, batch = 1;
+    if (!p.fixed_shape) { NEED_U32(icount, nrows); rows = (int)nrows; }
+    else if (p.batched) { NEED_U32(icount, nb); batch = (int)nb; }
+    if (rows <= 0 || batch <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": rows and batch must be positive");
+    const int groups = p.cols / p.group;
+    AffineArgs a = {};
+    for (int s = 0; s < nw; ++s) {
+        const int b0 = 3 * s;
+        if (!r.buf[b0].present || !r.buf[b0 + 1].present || !r.buf[b0 + 2].present)
+            return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": weight bindings are missing");
+        if (r.buf[b0].avail < (size_t)rows * p.cols / 2 || r.buf[b0 + 1].avail < (size_t)rows * groups * 2 || r.buf[b0 + 2].avail < (size_t)rows * groups * 2)
+            return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": weight tensor extends past the weights slot");
+        a.w[s] = r.buf[b0].ptr; a.s[s] = (const __half*)r.buf[b0 + 1].ptr; a.b[s] = (const __half*)r.buf[b0 + 2].ptr;
+        if ((uintptr_t)a.w[s] & 15u) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": packed weights must be 16-byte aligned");
+    }
+    NEED_BUF(ix); NEED_BUF(iy);
+    NEED_BYTES(ix, (size_t)batch * p.cols * 2); NEED_BYTES(iy, (size_t)batch * rows * 2);
+    a.x = (const __half*)r.buf[ix].ptr; a.y = (__half*)r.buf[iy].ptr;
+    if (iy2 >= 0) { NEED_BUF(iy2); NEED_BYTES(iy2, (size_t)batch * rows * 2); a.y2 = (__half*)r.buf[iy2].ptr; }
+    if (ires >= 0) { NEED_BUF(ires); NEED_BYTES(ires, (size_t)batch * rows * 2); a.residual = (const __half*)r.buf[ires].ptr; }
+    a.rows = rows; a.cols = p.cols; a.batch = batch; a.err = ctx->err_dev;
+    const int mode = p.kind == PK_AFFINE_MATVEC ? kAffinePlain : p.kind == PK_AFFINE_ADD ? kAffineAdd : p.kind == PK_AFFINE_GATEUP ? kAffineGateUp : kAffineDual;
+    in.launches += (batch + 15) / 16;
+    return check_cuda(ctx, launch_affine(make_launch(in, r), mode, a, p.group), p.name.c_str());
+}
+
+smelt_status run_signed(Interp& in, const Pipeline& p, const smelt_dispatch_record& rec, const Resolved& r) {
+    smelt_cuda_ctx* ctx = in.ctx;
+    // signed_quant.metal:574-583 (matvec), :662-672 (add), :625-636 (gate/up); signed_quant_precise.metal:41-50
+    SignedArgs a = {};
+    int ix, iy, irows, ires = -1, mode = kSignedPlain;
+    if (p.kind == PK_SIGNED_MATVEC) { ix = 2; iy = 3; irows = 4; }
+    else if (p.kind == PK_SIGNED_ADD) { ix = 2; iy = 3; ires = 4; irows = 5; mode = kSignedAdd; }
+    else if (p.kind == PK_SIGNED_GATEUP) { ix = 4; iy = 5; irows = 6; mode = kSignedGateUp; }
+    else { ix = 3; iy = 4; irows = 5; }  // ternary affine: binding 2 repeats the scales as the bias source
+    NEED_U32(irows, rows); NEED_U32(irows + 1, cols);
+    int batch = batch_of(rec);
+    if (p.batched) { NEED_U32(irows + 2, nb); batch = (int)nb; }
+    if (cols == 0 || cols % 128 || rows == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a positive multiple of 128");
+    const size_t code_bytes = (size_t)rows * cols * p.bits / 8, scale_bytes = (size_t)rows * (cols / 128) * 2;
+    NEED_BUF(0); NEED_BUF(1); NEED_BYTES(0, code_bytes); NEED_BYTES(1, scale_bytes);
+    a.codes[0] = r.buf[0].ptr; a.scales[0] = (const __half*)r.buf[1].ptr;
+    if (mode == kSignedGateUp) {
+        NEED_BUF(2); NEED_BUF(3); NEED_BYTES(2, code_bytes); NEED_BYTES(3, scale_bytes);
+        a.codes[1] = r.buf[2].ptr; a.scales[1] = (const __half*)r.buf[3].ptr;
+    }
+    NEED_BUF(ix); NEED_BUF(iy);
+    NEED_BYTES(ix, (size_t)batch * cols * 2); NEED_BYTES(iy, (size_t)batch * rows * 2);
+    a.x = (const __half*)r.buf[ix].ptr; a.y = (__half*)r.buf[iy].ptr;
+    if (ires >= 0) { NEED_BUF(ires); NEED_BYTES(ires, (size_t)batch * rows * 2); a.residual = (const __half*)r.buf[ires].ptr; }
+    a.rows = (int)rows; a.cols = (int)cols; a.batch = batch; a.bits = p.bits;
+    in.launches += 1;
+    return check_cuda(ctx, launch_signed(make_launch(in, r), mode, a), p.name.c_str());
+}
+
+smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_record& rec, const Resolved& r) {
+    smelt_cuda_ctx* ctx = in.ctx;
+    AttnArgs a = {};
+    int iseq;
+    NEED_BUF(0); NEED_BUF(1); NEED_BUF(2);
+    a.batch = batch_of(rec);
+    a.k_cache = (const __half*)r.buf[1].ptr; a.v_cache = (const __half*)r.buf[2].ptr;
+    a.q = (const __half*)r.buf[0].ptr;
+    if (p.kind == PK_ATTN_GENERIC) {
+        // attention.metal:217-229: 0 q, 1 K, 2 V, 3 mask (unused), 4 out, 5 headDim, 6 capacity, 7 seqLen,
+        // 8 numKVHeads, 9 scale, 10 slidingWindow; numQHeads = threadgroups in x.
+        NEED_BUF(4);
+        NEED_U32(5, d); NEED_U32(6, cap); NEED_U32(8, nkv); NEED_U32(9, scale_bits);
+        uint32_t window = 0;
+        (void)host_u32(in, r, 10, &window);
+        a.out = (__half*)r.buf[4].ptr; a.head_dim = (int)d; a.capacity = cap; a.n_kv = (int)nkv; a.n_q = (int)rec.grid[0];
+        a.scale = as_f32(scale_bits); a.sliding_window = window;
+        iseq = 7;
+    } else {
+        // in place: 0 q/out, 1 K, 2 V, 3 seqLen, 4 capacity (attention.metal:422-431, :1211-1218);
+        // the mlx_vector form adds 5 qHeads, 6 kvHeads (:981-989).
+        NEED_U32(4, cap);
+        a.out = (__half*)r.buf[0].ptr; a.head_dim = p.head_dim; a.capacity = cap; a.n_q = p.n_q; a.n_kv = p.n_kv;
+        if (p.n_q == 0) { NEED_U32(5, nq); NEED_U32(6, nkv); a.n_q = (int)nq; a.n_kv = (int)nkv; }
+        a.scale = 1.0f / sqrtf((float)p.head_dim);
+        iseq = 3;
+    }
+    const RConst& cs = r.con[iseq];
+    if (!cs.present) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": seqLen constant is missing");
+    if (cs.kind == SMELT_CONST_POSITION_PLUS1 && in.device_pos) a.seq_from_pos = 1;
+    else {
+        NEED_U32(iseq, sl);
+        a.seq_len = sl;
+        if (sl == 0 || sl > a.capacity) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": seqLen must be in 1..capacity");
+    }
+    if (a.n_kv <= 0 || a.n_q <= 0 || a.n_q % a.n_kv || a.n_q / a.n_kv > 16 || (a.head_dim != 64 && a.head_dim != 128 && a.head_dim != 256))
+        return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": head_dim in {64,128,256}, GQA ratio <= 16");
+    a.seq_stride = (size_t)a.n_kv * a.capacity * a.head_dim;
+    NEED_BYTES(1, a.seq_stride * 2 * a.batch); NEED_BYTES(2, a.seq_stride * 2 * a.batch);
+    NEED_BYTES(0, (size_t)a.batch * a.n_q * a.head_dim * 2);
+    a.scratch = ctx->attn_scratch; a.scratch_bytes = ctx->attn_scratch_bytes; a.sm_count = ctx->sm_count;
+    in.launches += 2;
+    return check_cuda(ctx, launch_attention_decode(make_launch(in, r), a), p.name.c_str());
+}
+
+smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
+    smelt_cuda_ctx* ctx = in.ctx;
+    if (rec.pipeline >= ctx->pipelines.size() || ctx->pipelines[rec.pipeline].kind == PK_NONE)
+        return fail(ctx, SMELT_ERR_UNKNOWN_PIPELINE, "record names pipeline index " + std::to_string(rec.pipeline) + " which is not registered");
+    const Pipeline& p = ctx->pipelines[rec.pipeline];
+    Resolved r;
+    smelt_status s = resolve(in, rec, &r);
+    if (s) return s;
+    if (r.skip) return SMELT_OK;
+    Launch l = make_launch(in, r);
+    switch (p.kind) {
+        case PK_AFFINE_MATVEC: case PK_AFFINE_ADD: case PK_AFFINE_GATEUP: case PK_AFFINE_DUAL:
+            return run_affine(in, p, rec, r);
+        case PK_SIGNED_MATVEC: case PK_SIGNED_ADD: case PK_SIGNED_GATEUP: case PK_SIGNED_TERNARY_AFFINE:
+            return run_signed(in, p, rec, r);
+        case PK_ATTN_GENERIC: case PK_ATTN_INPLACE:
+            return run_attention(in, p, rec, r);
+        case PK_FP16_MATVEC: {
+            // lut_matvec.metal:799-803: 0 W, 1 x, 2 y, 3 cols; one threadgroup per row.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, cols);
+            const int rows = (int)rec.grid[0], batch = batch_of(rec);
+            if (rows <= 0 || cols == 0 || cols % 8) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "fp16_matvec: cols must be a positive multiple of 8");
+            NEED_BYTES(0, (size_t)rows * cols * 2); NEED_BYTES(1, (size_t)batch * cols * 2); NEED_BYTES(2, (size_t)batch * rows * 2);
+            in.launches += (batch + 7) / 8;
+            return check_cuda(ctx, launch_fp16_matvec(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, rows, (int)cols, batch, ctx->sm_count), "fp16_matvec");
+        }
+        case PK_EMBEDDING_GATHER: {
+            // lut_matvec.metal:951-956: 0 table, 1 token id, 2 out, 3 hidden.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, hidden);
+            const int batch = batch_of(rec);
+            NEED_BYTES(1, (size_t)batch * 4); NEED_BYTES(2, (size_t)batch * hidden * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_embedding_gather(l, (const __half*)r.buf[0].ptr, (const int32_t*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)hidden, batch, 1), "embedding_gather");
+        }
+        case PK_AFFINE_EMBEDDING_GATHER: {
+            // lut_matvec.metal:994-1002: 0 W, 1 scales, 2 biases, 3 token id, 4 out, 5 cols, 6 groupSize.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_U32(5, cols); NEED_U32(6, group);
+            if (cols == 0 || group == 0 || cols % group || cols % 2) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "affine_embedding_gather: bad cols/group");
+            NEED_BYTES(4, (size_t)cols * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_affine_embedding_gather(l, r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const int32_t*)r.buf[3].ptr, (__half*)r.buf[4].ptr, (int)cols, (int)group), "affine_embedding_gather");
+        }
+        case PK_ARGMAX_PARTIALS: {
+            // lut_matvec.metal:8901-8906: 0 logits, 1 partials, 2 vocab, 3 chunk.
+            NEED_BUF(0); NEED_BUF(1); NEED_U32(2, vocab); NEED_U32(3, chunk);
+            const int batch = batch_of(rec);
+            if (vocab == 0 || chunk == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "argmax_fp16_partials: vocab and chunk must be positive");
+            const size_t parts = (vocab + chunk - 1) / chunk;
+            NEED_BYTES(0, (size_t)batch * vocab * 2); NEED_BYTES(1, parts * batch * 8);
+            in.launches += 1;
+            return check_cuda(ctx, launch_argmax_partials(l, (const __half*)r.buf[0].ptr, (uint64_t*)r.buf[1].ptr, (int)vocab, (int)chunk, batch), "argmax_fp16_partials");
+        }
+        case PK_ARGMAX_REDUCE: {
+            // lut_matvec.metal:8938-8942: 0 partials, 1 out, 2 numPartials.
+            NEED_BUF(0); NEED_BUF(1); NEED_U32(2, parts);
+            const int batch = batch_of(rec);
+            NEED_BYTES(0, (size_t)parts * batch * 8); NEED_BYTES(1, (size_t)batch * 4);
+            in.launches += 1;
+            return check_cuda(ctx, launch_argmax_reduce(l, (const uint64_t*)r.buf[0].ptr, (int32_t*)r.buf[1].ptr, (int)parts, batch, 1), "argmax_key_reduce");
+        }
+        case PK_ARGMAX_SINGLE: {
+            // single-threadgroup argmax_fp16: 0 logits, 1 out, 2 vocab.
+            NEED_BUF(0); NEED_BUF(1); NEED_U32(2, vocab);
+            const int batch = batch_of(rec);
+            const int chunk = 2048;
+            const size_t parts = (vocab + chunk - 1) / chunk;
+            if (parts * batch * 8 > ctx->argmax_scratch_bytes) return fail(ctx, SMELT_ERR_UNSUPPORTED, "argmax_fp16: vocab too large");
+            in.launches += 2;
+            s = check_cuda(ctx, launch_argmax_partials(l, (const __half*)r.buf[0].ptr, ctx->argmax_scratch, (int)vocab, chunk, batch), "argmax_fp16");
+            if (s) return s;
+            return check_cuda(ctx, launch_argmax_reduce(l, ctx->argmax_scratch, (int32_t*)r.buf[1].ptr, (int)parts, batch, 1), "argmax_fp16");
+        }
+        case PK_KV_UPDATE: {
+            // attention.metal:122-129: 0 cache, 1 new, 2 capacity, 3 headDim, 4 pos, 5 numHeads.
+            NEED_BUF(0); NEED_BUF(1); NEED_U32(2, cap); NEED_U32(3, d); NEED_U32(5, heads);
+            if (!bind_pos_arg(in, r, 4, &l)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "kv_cache_update: position constant is missing");
+            const int batch = batch_of(rec);
+            const size_t seq = (size_t)heads * cap * d;
+            NEED_BYTES(0, seq * 2 * batch); NEED_BYTES(1, (size_t)batch * heads * d * 2);
+            if (!in.device_pos && (l.arg_pos_valid ? l.arg_pos : in.position) >= cap) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "kv_cache_update: position beyond the cache capacity");
+            in.launches += 1;
+            return check_cuda(ctx, launch_kv_cache_update(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, nullptr, nullptr, cap, (int)d, (int)heads, 0, 0, 0.f, 0, 0, 0, batch, seq), "kv_cache_update");
+        }
+        case PK_APPLY_ROPE: {
+            // attention.metal:48-59: 0 data, 1 cos, 2 sin, 3 headDim, 4 ropeDim, 5 numHeads, 6 layout,
+            // 7 position, 8 log2(theta) f32, 9 mathMode.
+            NEED_BUF(0); NEED_U32(3, d); NEED_U32(4, rope); NEED_U32(5, heads); NEED_U32(6, layout);
+            uint32_t mode = 0, base_bits = 0;
+            (void)host_u32(in, r, 9, &mode); (void)host_u32(in, r, 8, &base_bits);
+            if (!bind_pos_arg(in, r, 7, &l)) { if (mode == 1) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "apply_rope: position constant is missing"); l.arg_pos = 0; l.arg_pos_valid = 1; }
+            const int batch = batch_of(rec);
+            NEED_BYTES(0, (size_t)batch * heads * d * 2);
+            const __half *cos_t = nullptr, *sin_t = nullptr;
+            size_t stride = 0;
+            if (mode != 1) {
+                if (!r.buf[1].present || !r.buf[2].present) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "apply_rope: table mode needs cos/sin bindings");
+                cos_t = (const __half*)r.buf[1].ptr; sin_t = (const __half*)r.buf[2].ptr;
+                if (r.buf[1].pos_strided) stride = r.buf[1].stride / 2;  // table row per position, resolved on the device
+            }
+            if (rope > d || d == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "apply_rope: ropeDim must not exceed headDim");
+            in.launches += 1;
+            return check_cuda(ctx, launch_apply_rope(l, (__half*)r.buf[0].ptr, cos_t, sin_t, (int)d, (int)rope, (int)heads, (int)layout, as_f32(base_bits), (int)mode, stride, batch), "apply_rope");
+        }
+        case PK_ROPE_KV_UPDATE: {
+            // attention.metal:141-154: 0 cache, 1 new, 2 cos, 3 sin, 4 capacity, 5 headDim, 6 pos, 7 numHeads,
+            // 8 ropeDim, 9 layout, 10 log2(theta), 11 mathMode.
+            NEED_BUF(0); NEED_BUF(1); NEED_U32(4, cap); NEED_U32(5, d); NEED_U32(7, heads); NEED_U32(8, rope); NEED_U32(9, layout);
+            uint32_t mode = 0, base_bits = 0;
+            (void)host_u32(in, r, 11, &mode); (void)host_u32(in, r, 10, &base_bits);
+            if (!bind_pos_arg(in, r, 6, &l)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "rope_kv_cache_update: position constant is missing");
+            const int batch = batch_of(rec);
+            const size_t seq = (size_t)heads * cap * d;
+            NEED_BYTES(0, seq * 2 * batch); NEED_BYTES(1, (size_t)batch * heads * d * 2);
+            if (!in.device_pos && (l.arg_pos_valid ? l.arg_pos : in.position) >= cap) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "rope_kv_cache_update: position beyond the cache capacity");
+            const __half *cos_t = nullptr, *sin_t = nullptr;
+            size_t stride = 0;
+            if (mode != 1) {
+                if (!r.buf[2].present || !r.buf[3].present) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "rope_kv_cache_update: table mode needs cos/sin bindings");
+                cos_t = (const __half*)r.buf[2].ptr; sin_t = (const __half*)r.buf[3].ptr;
+                if (r.buf[2].pos_strided) stride = r.buf[2].stride / 2;
+            }
+            in.launches += 1;
+            return check_cuda(ctx, launch_kv_cache_update(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, cos_t, sin_t, cap, (int)d, (int)heads, (int)rope, (int)layout, as_f32(base_bits), (int)mode, 1, stride, batch, seq), "rope_kv_cache_update");
+        }
+        case PK_RMS_NORM: {
+            // norms.metal:9-14: 0 in, 1 weight, 2 out, 3 dim, 4 eps; one threadgroup per row.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, dim); NEED_U32(4, eps_bits);
+            const int batch = rec.grid[0] > 0 ? (int)rec.grid[0] : 1;
+            NEED_BYTES(0, (size_t)batch * dim * 2); NEED_BYTES(1, (size_t)dim * 2); NEED_BYTES(2, (size_t)batch * dim * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_rms_norm_1pw(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)dim, as_f32(eps_bits), batch), "rms_norm_1pw");
+        }
+        case PK_PER_HEAD_NORM: {
+            // attention_fused.metal:93-98: 0 in, 1 weight, 2 out, 3 headDim, 4 eps; one threadgroup per head.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, d); NEED_U32(4, eps_bits);
+            const int heads = (int)rec.grid[0];
+            if (heads <= 0 || d == 0 || d > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "per_head_rms_norm: bad shape");
+            NEED_BYTES(0, (size_t)heads * d * 2); NEED_BYTES(2, (size_t)heads * d * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_per_head_rms_norm(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, heads, (int)d, as_f32(eps_bits)), "per_head_rms_norm");
+        }
+        case PK_ADD: {
+            // activations.metal:56-61: 0 a, 1 b, 2 out, 3 count.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, count);
+            NEED_BYTES(0, (size_t)count * 2); NEED_BYTES(1, (size_t)count * 2); NEED_BYTES(2, (size_t)count * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_elementwise_add(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int64_t)count), "elementwise_add");
+        }
+        case PK_SWIGLU: {
+            // activations_precise.metal:9-14: 0 gate, 1 up, 2 out, 3 count.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, count);
+            NEED_BYTES(0, (size_t)count * 2); NEED_BYTES(1, (size_t)count * 2); NEED_BYTES(2, (size_t)count * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_swiglu_fused(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int64_t)count), "swiglu_fused");
+        }
+        case PK_TP_ALL_REDUCE: {
+            NEED_BUF(0); NEED_U32(1, count);
+            NEED_BYTES(0, (size_t)count * 2);
+            if (ctx->tp_world <= 1) return SMELT_OK;
+            in.launches += 1;
+            return tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
+        }
+        default:
+            return fail(ctx, SMELT_ERR_UNKNOWN_PIPELINE, p.name + ": no handler");
+    }
+}
+
+smelt_status interpret(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n, bool device_pos, uint32_t position) {
+    Interp in;
+    in.ctx = ctx; in.device_pos = device_pos; in.position = position;
+    in.cur = ctx->cfg.cur_slot; in.alt = ctx->cfg.alt_slot;
+    for (size_t i = 0; i < n; ++i) {
+        const smelt_dispatch_record& rec = table[i];
+        if (rec.op_kind == SMELT_OP_SWAP) { int t = in.cur; in.cur = in.alt; in.alt = t; continue; }
+        if (rec.op_kind != SMELT_OP_DISPATCH) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record " + std::to_string(i) + ": unknown op kind");
+        smelt_status s = run_record(in, rec);
+        if (s) { ctx->err = "record " + std::to_string(i) + ": " + ctx->err; return s; }
+    }
+    ctx->launch_count = in.launches;
+    return SMELT_OK;
+}
+
+smelt_status check_step(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position) {
+    if (!ctx->configured) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "context is not configured");
+    // SmeltRuntime.swift:3176-3183: position in [0, contextLimit), token in [0, vocabSize)
+    if (position < 0 || (uint32_t)position >= ctx->cfg.context_limit || (uint32_t)position >= ctx->cfg.cache_seq_capacity)
+        return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "position out of range [0, " + std::to_string(ctx->cfg.context_limit) + ")");
+    if (tokens)
+        for (uint32_t b = 0; b < ctx->cfg.batch; ++b)
+            if (tokens[b] < 0 || (uint32_t)tokens[b] >= ctx->cfg.vocab_size)
+                return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "tokenId out of range [0, " + std::to_string(ctx->cfg.vocab_size) + ")");
+    return SMELT_OK;
+}
+
+struct TokenPack {
+    int32_t t[64];
+};
+
+__global__ void set_dynamic_kernel(TokenPack pack, int32_t position, int batch, int32_t* token_slot,
+                                   int32_t* position_slot, DynState* dyn) {
+    if (threadIdx.x < batch) token_slot[threadIdx.x] = pack.t[threadIdx.x];
+    if (threadIdx.x == 0) {
+        position_slot[0] = position;
+        dyn->token = pack.t[0];
+        dyn->position = (uint32_t)position;
+    }
+}
+
+// Writes token ids and position into their slots (prepareDecodeDynamicState,
+// SmeltRuntime.swift:3171-3184) and into the device dynamic state.  The values travel as
+// kernel parameters, so no host staging buffer has to outlive the call.
+smelt_status write_dynamic(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position) {
+    const uint32_t B = ctx->cfg.batch;
+    Slot& ts = ctx->slots[ctx->cfg.token_id_slot];
+    Slot& ps = ctx->slots[ctx->cfg.position_slot];
+    if (!ts.ptr || ts.bytes < B * 4 || !ps.ptr || ps.bytes < 4) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "token / position slots are missing or too small");
+    TokenPack pack = {};
+    for (uint32_t b = 0; b < B; ++b) pack.t[b] = tokens[b];
+    set_dynamic_kernel<<<1, 64, 0, ctx->stream>>>(pack, position, (int)B, (int32_t*)ts.ptr, (int32_t*)ps.ptr, ctx->dyn_dev);
+    return check_cuda(ctx, cudaGetLastError(), "write dynamic state");
+}
+
+// Tail of a captured token: feed argmax back as the next token, advance the position and
+// append the ids to the generated ring.
+__global__ void advance_kernel(const int32_t* argmax, int32_t* token_slot, int32_t* position_slot, DynState* dyn,
+                               int32_t* ring, uint32_t* count, uint32_t capacity, int batch) {
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        const uint32_t step = *count;
+        for (int b = 0; b < batch; ++b) {
+            const int32_t t = argmax[b];
+            token_slot[b] = t;
+            if (step < capacity) ring[(size_t)step * batch + b] = t;
+        }
+        dyn->token = argmax[0];
+        dyn->position += 1u;
+        position_slot[0] = (int32_t)dyn->position;
+        *count = step + 1u;
+    }
+}
+
+}  // namespace
+}  // namespace smelt
+
+extern "C" {
+
+int smelt_cuda_pipeline_supported(const char* name) {
+    Pipeline p;
+    std::string e(name ? name : "");
+    if (parse_pipeline(e.c_str(), &p)) return 1;
+    // generic affine names need the ":cols:group" suffix to be launchable; accept the bare name too
+    if (e.find(':') == std::string::npos && parse_pipeline((e + ":64:64").c_str(), &p)) return 1;
+    return 0;
+}
+
+smelt_status smelt_cuda_register_pipeline(smelt_cuda_ctx* ctx, int index, const char* name) {
+    if (!ctx || !name || index < 0 || index > 65535) return SMELT_ERR_BAD_ARGUMENT;
+    Pipeline p;
+    if (!parse_pipeline(name, &p))
+        return fail(ctx, SMELT_ERR_UNKNOWN_PIPELINE, std::string("pipeline '") + name + "' is not an implemented kernel");
+    if ((size_t)index >= ctx->pipelines.size()) ctx->pipelines.resize(index + 1);
+    ctx->pipelines[index] = p;
+    return SMELT_OK;
+}
+
+smelt_status smelt_cuda_enqueue_decode(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records,
+                                       const int32_t* tokens, int32_t position) {
+    if (!ctx || !table || !tokens) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    smelt_status s = check_step(ctx, tokens, position);
+    if (s) return s;
+    s = write_dynamic(ctx, tokens, position);
+    if (s) return s;
+    return interpret(ctx, table, n_records, false, (uint32_t)position);
+}
+
+smelt_status smelt_cuda_decode_step(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records,
+                                    const int32_t* tokens, int32_t position, int32_t* out_tokens) {
+    smelt_status s = smelt_cuda_enqueue_decode(ctx, table, n_records, tokens, position);
+    if (s) return s;
+    const uint32_t B = ctx->cfg.batch;
+    Slot& as = ctx->slots[ctx->cfg.argmax_slot];
+    if (!as.ptr || as.bytes < B * 4) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "argmax slot is missing or too small");
+    cudaMemcpyAsync(ctx->h_pinned + 128, as.ptr, B * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "decode step");
+    if (s) return s;
+    if (out_tokens)
+        for (uint32_t b = 0; b < B; ++b) out_tokens[b] = ctx->h_pinned[128 + b];
+    return SMELT_OK;
+}
+
+smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records) {
+    if (!ctx || !table) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!ctx->configured) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "context is not configured");
+    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; }
+    if (ctx->graph) { cudaGraphDestroy(ctx->graph); ctx->graph = nullptr; }
+    const uint32_t B = ctx->cfg.batch;
+    if (!ctx->gen_ring) {
+        ctx->gen_capacity = 65536;
+        if (cudaMalloc(&ctx->gen_ring, (size_t)ctx->gen_capacity * 64 * 4) != cudaSuccess || cudaMalloc(&ctx->gen_count, 4) != cudaSuccess)
+            return fail(ctx, SMELT_ERR_ALLOC, "graph: generated-token ring");
+        cudaMemset(ctx->gen_count, 0, 4);
+    }
+    Slot& as = ctx->slots[ctx->cfg.argmax_slot];
+    Slot& ts = ctx->slots[ctx->cfg.token_id_slot];
+    Slot& ps = ctx->slots[ctx->cfg.position_slot];
+    if (!as.ptr || !ts.ptr || !ps.ptr) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "graph: argmax / token / position slots are not allocated");
+    smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph: pre-capture sync");
+    if (s) return s;
+    s = check_cuda(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    if (s) return s;
+    ctx->capturing = true;
+    s = interpret(ctx, table, n_records, true, 0);
+    if (!s) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = ctx->pdl ? 1 : 0;
+        s = check_cuda(ctx, cudaLaunchKernelEx(&cfg, advance_kernel, (const int32_t*)as.ptr, (int32_t*)ts.ptr, (int32_t*)ps.ptr, ctx->dyn_dev, ctx->gen_ring, ctx->gen_count, ctx->gen_capacity, (int)B), "advance kernel");
+        ctx->launch_count += 1;
+    }
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    if (s) { if (g) cudaGraphDestroy(g); return s; }
+    s = check_cuda(ctx, e, "cudaStreamEndCapture");
+    if (s) return s;
+    ctx->graph = g;
+    return check_cuda(ctx, cudaGraphInstantiate(&ctx->graph_exec, g, 0), "cudaGraphInstantiate");
+}
+
+smelt_status smelt_cuda_graph_seed(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position) {
+    if (!ctx || !tokens) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    smelt_status s = check_step(ctx, tokens, position);
+    if (s) return s;
+    s = write_dynamic(ctx, tokens, position);
+    if (s) return s;
+    if (ctx->gen_count) cudaMemsetAsync(ctx->gen_count, 0, 4, ctx->stream);
+    return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph seed");
+}
+
+smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* out_tokens) {
+    if (!ctx || n_steps <= 0) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!ctx->graph_exec) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "no graph has been built");
+    const uint32_t B = ctx->cfg.batch;
+    if (out_tokens) cudaMemsetAsync(ctx->gen_count, 0, 4, ctx->stream);
+    if (out_tokens && (uint32_t)n_steps > ctx->gen_capacity) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "graph decode: too many steps for one readback");
+    for (int i = 0; i < n_steps; ++i) {
+        smelt_status s = check_cuda(ctx, cudaGraphLaunch(ctx->graph_exec, ctx->stream), "cudaGraphLaunch");
+        if (s) return s;
+    }
+    if (!out_tokens) return SMELT_OK;
+    smelt_status s = check_cuda(ctx, cudaMemcpyAsync(out_tokens, ctx->gen_ring, (size_t)n_steps * B * 4, cudaMemcpyDeviceToHost, ctx->stream), "graph readback");
+    if (s) return s;
+    return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph decode");
+}
+
+int smelt_cuda_last_launch_count(const smelt_cuda_ctx* ctx) { return ctx ? ctx->launch_count : 0; }
+
+}  // extern "C"

@@ -1,0 +1,54 @@
+// Launchers of the glue, attention and low-bit kernels (glue.cu, attention.cu, signed_matvec.cu).
+#pragma once
+#include "common.cuh"
+
+namespace smelt {
+
+cudaError_t launch_rms_norm_1pw(const Launch& l, const __half* x, const __half* w, __half* y, int dim, float eps, int batch);
+cudaError_t launch_per_head_rms_norm(const Launch& l, const __half* x, const __half* w, __half* y, int heads, int head_dim, float eps);
+cudaError_t launch_elementwise_add(const Launch& l, const __half* a, const __half* b, __half* y, int64_t n);
+cudaError_t launch_swiglu_fused(const Launch& l, const __half* gate, const __half* up, __half* y, int64_t n);
+cudaError_t launch_embedding_gather(const Launch& l, const __half* table, const int32_t* token, __half* y, int hidden, int batch, int token_stride);
+cudaError_t launch_affine_embedding_gather(const Launch& l, const uint8_t* w, const __half* s, const __half* b, const int32_t* token, __half* y, int cols, int group);
+cudaError_t launch_affine_dequant(const Launch& l, const uint8_t* w, const __half* s, const __half* b, float* out32, __half* out16, int rows, int cols, int group);
+cudaError_t launch_signed_dequant(const Launch& l, const uint8_t* codes, const __half* s, float* out, int rows, int cols, int bits, int group, int* bad);
+cudaError_t launch_apply_rope(const Launch& l, __half* qk, const __half* cos_t, const __half* sin_t, int head_dim, int rope_dim, int heads, int layout, float base_log2, int math_mode, size_t table_stride, int batch);
+cudaError_t launch_kv_cache_update(const Launch& l, __half* cache, const __half* new_kv, const __half* cos_t, const __half* sin_t, uint32_t capacity, int head_dim, int heads, int rope_dim, int layout, float base_log2, int math_mode, int do_rope, size_t table_stride, int batch, size_t seq_stride);
+cudaError_t launch_argmax_partials(const Launch& l, const __half* logits, uint64_t* partials, int vocab, int chunk, int batch);
+cudaError_t launch_argmax_reduce(const Launch& l, const uint64_t* partials, int32_t* out, int n, int batch, int out_stride);
+cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x, __half* y, int rows, int cols, int batch, int sm_count);
+
+// attention.cu — split-K flash-decode.  scratch holds fp32 partials; see attention_scratch_bytes.
+struct AttnArgs {
+    const __half* q;        // [batch, n_q, head_dim]
+    const __half* k_cache;  // [batch][n_kv, capacity, head_dim]
+    const __half* v_cache;
+    __half* out;            // [batch, n_q, head_dim]; may alias q
+    int n_q, n_kv, head_dim, batch;
+    uint32_t capacity;
+    uint32_t seq_len;       // used when seq_from_pos == 0
+    int seq_from_pos;       // 1: seq_len = position + 1 (read through the dynamic state)
+    float scale;
+    uint32_t sliding_window;
+    size_t seq_stride;      // elements between consecutive sequences' caches
+    void* scratch;
+    size_t scratch_bytes;
+    int sm_count;
+};
+size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits);
+int attention_max_splits();
+cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a);
+
+// signed_matvec.cu — binary1 / ternary2, group 128.
+enum SignedMode : int { kSignedPlain = 0, kSignedAdd = 1, kSignedGateUp = 2 };
+struct SignedArgs {
+    const uint8_t* codes[2];
+    const __half* scales[2];
+    const __half* x;
+    __half* y;
+    const __half* residual;
+    int rows, cols, batch, bits;
+};
+cudaError_t launch_signed(const Launch& l, int mode, const SignedArgs& a);
+
+}  // namespace smelt

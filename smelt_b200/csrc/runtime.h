@@ -1,0 +1,100 @@
+// Internal state of a libsmelt_cuda context (host side).
+#pragma once
+
+#include <string>
+#include <vector>
+
+#include "../../include/smelt_cuda.h"
+#include "common.cuh"
+
+namespace smelt {
+
+struct Slot {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+enum PipeKind : int {
+    PK_NONE = 0,
+    PK_AFFINE_MATVEC,
+    PK_AFFINE_ADD,
+    PK_AFFINE_GATEUP,
+    PK_AFFINE_DUAL,
+    PK_FP16_MATVEC,
+    PK_EMBEDDING_GATHER,
+    PK_AFFINE_EMBEDDING_GATHER,
+    PK_ARGMAX_PARTIALS,
+    PK_ARGMAX_REDUCE,
+    PK_ARGMAX_SINGLE,
+    PK_SIGNED_MATVEC,
+    PK_SIGNED_ADD,
+    PK_SIGNED_GATEUP,
+    PK_SIGNED_TERNARY_AFFINE,
+    PK_KV_UPDATE,
+    PK_APPLY_ROPE,
+    PK_ROPE_KV_UPDATE,
+    PK_ATTN_GENERIC,
+    PK_ATTN_INPLACE,
+    PK_RMS_NORM,
+    PK_PER_HEAD_NORM,
+    PK_ADD,
+    PK_SWIGLU,
+    PK_TP_ALL_REDUCE,
+};
+
+struct Pipeline {
+    PipeKind kind = PK_NONE;
+    std::string name;
+    int cols = 0, rows = 0, group = 0;  // from "name:cols:group" or "_c{C}_r{R}_g{G}"
+    bool fixed_shape = false;            // rows come from the name, no numRows constant
+    bool batched = false;                // x is [B, C], an actualBatch constant is bound
+    int bits = 0;                        // signed kernels: 1 or 2
+    int n_q = 0, n_kv = 0, head_dim = 0; // shape-specialised attention names
+};
+
+// Parses a manifest pipeline entry; returns false when the kernel is not implemented.
+bool parse_pipeline(const char* entry, Pipeline* out);
+
+}  // namespace smelt
+
+struct smelt_cuda_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    std::string err;
+    std::vector<smelt::Slot> slots;
+    std::vector<smelt::Pipeline> pipelines;
+    smelt_cuda_runtime_config cfg = {};
+    bool configured = false;
+    bool pdl = true;
+
+    smelt::DynState* dyn_dev = nullptr;  // {token, position} read by graph-replayed kernels
+    uint32_t* err_dev = nullptr;         // device error word
+    void* attn_scratch = nullptr;
+    size_t attn_scratch_bytes = 0;
+    uint64_t* argmax_scratch = nullptr;
+    size_t argmax_scratch_bytes = 0;
+
+    int32_t* h_pinned = nullptr;  // pinned staging: tokens in, tokens out
+    size_t h_pinned_count = 0;
+
+    // graph replay
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;
+    int32_t* gen_ring = nullptr;   // device: generated ids, step-major
+    uint32_t* gen_count = nullptr; // device: steps written
+    uint32_t gen_capacity = 0;
+    int launch_count = 0;
+    bool capturing = false;
+
+    // tensor parallel
+    void* nccl_comm = nullptr;
+    int tp_rank = 0, tp_world = 1;
+};
+
+namespace smelt {
+smelt_status fail(smelt_cuda_ctx* ctx, smelt_status code, const std::string& msg);
+smelt_status check_cuda(smelt_cuda_ctx* ctx, cudaError_t e, const char* what);
+smelt_status tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data, size_t count, cudaStream_t stream);
+void tp_destroy(smelt_cuda_ctx* ctx);
+}  // namespace smelt

@@ -1,0 +1,25 @@
+"""Shared test helpers: the error metric and device round trips."""
+import numpy as np
+
+REL_TOL = 2e-3  # matvec / attention outputs: max relative error against the oracle
+
+
+def rel_err(got, ref) -> float:
+    """max_i |got_i - ref_i| / max(|ref_i|, rms(ref)/8).
+
+    A plain relative error is undefined where an output crosses zero; the floor of one eighth
+    of the output RMS keeps the metric relative for ordinary elements and bounds the absolute
+    error of near-zero ones (two correct fp32 summation orders already differ there by about
+    1e-4 of the RMS)."""
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    floor = np.sqrt(np.mean(ref * ref)) / 8.0
+    return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), max(floor, 1e-30))))
+
+
+def ulp_diff_f16(a, b) -> np.ndarray:
+    """Distance in fp16 ulps (monotone integer mapping of the bit patterns)."""
+    def key(x):
+        u = np.asarray(x, np.float16).view(np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
+    return np.abs(key(a) - key(b))

@@ -1,0 +1,408 @@
+"""Parity of every CUDA kernel against the CPU oracle, called through the C ABI on a B200."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from smelt_b200 import capi, synth
+from helpers import REL_TOL, rel_err, ulp_diff_f16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = capi.Context(0)
+    yield c
+    assert c.device_error() == 0
+    c.close()
+
+
+def dev(ctx, *arrs):
+    return [ctx.to_device(a) for a in arrs]
+
+
+# ── bit-exact unpack / dequant ──────────────────────────────────────────────
+@pytest.mark.parametrize("rows,cols,group", [(4096, 1024, 64), (257, 512, 64), (64, 256, 32), (16, 1536, 128)])
+def test_affine_dequant_bit_exact(ctx, oracle, rows, cols, group):
+    w, s, b = synth.affine_u4(0, "deq", rows, cols, group)
+    dw, ds, db = dev(ctx, w, s, b)
+    o32, o16 = ctx.alloc(rows * cols * 4), ctx.alloc(rows * cols * 2)
+    ctx.call("affine_dequantize", dw, ds, db, o32, o16, rows, cols, group)
+    got32 = o32.download(np.float32, (rows, cols))
+    got16 = o16.download(np.float16, (rows, cols))
+    assert np.array_equal(got32.view(np.uint32), oracle.affine_dequantize(w, s, b, cols, group).view(np.uint32))
+    assert np.array_equal(got16.view(np.uint16), oracle.affine_dequantize_f16(w, s, b, rows, cols, group).view(np.uint16))
+
+
+@pytest.mark.parametrize("fmt,maker", [(1, synth.binary1), (2, synth.ternary2)])
+def test_signed_dequant_bit_exact(ctx, oracle, fmt, maker):
+    rows, cols = 64, 5120
+    codes, scales = maker(1, "sdeq", rows, cols)
+    dc, ds = dev(ctx, codes, scales)
+    out = ctx.alloc(rows * cols * 4)
+    bad = C.c_int(-1)
+    ctx.call("signed_dequantize", fmt, dc, ds, out, rows, cols, C.byref(bad))
+    got = out.download(np.float32, (rows, cols))
+    ref = np.stack([oracle.signed_dequantize_row(fmt, codes[r], scales[r], cols, cols, 128) for r in range(rows)])
+    assert bad.value == 0
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+
+
+def test_signed_dequant_flags_ternary_code_three(ctx):
+    codes = np.full((1, 32), 0b11100100, np.uint8)  # every fourth code is the reserved value 3
+    scales = np.ones((1, 1), np.float16)
+    dc, ds = dev(ctx, codes, scales)
+    out = ctx.alloc(128 * 4)
+    bad = C.c_int(0)
+    ctx.call("signed_dequantize", 2, dc, ds, out, 1, 128, C.byref(bad))
+    assert bad.value == 1
+
+
+# ── affine matvec family ────────────────────────────────────────────────────
+AFFINE_SHAPES = [
+    (4096, 1024, 64, 1),    # BASELINE config 0
+    (257, 512, 64, 1),      # row tail (RegionExactnessTests)
+    (5, 256, 64, 5),        # tiny, batch tail
+    (2048, 2048, 64, 4), (512, 2048, 64, 8), (2048, 6144, 64, 16),  # config 1
+    (1024, 4096, 64, 1), (512, 12288, 64, 1), (256, 12288, 64, 8),  # config 4 (K split over a cluster)
+    (128, 1536, 128, 3), (96, 512, 32, 2), (64, 1024, 64, 20),
+]
+
+
+@pytest.mark.parametrize("rows,cols,group,batch", AFFINE_SHAPES)
+def test_affine_matvec(ctx, oracle, rows, cols, group, batch):
+    w, s, b = synth.affine_u4(0, "mv", rows, cols, group)
+    x = synth.activations(0, "x", batch, cols)
+    dw, ds, db, dx = dev(ctx, w, s, b, x)
+    y = ctx.alloc(batch * rows * 2 + 64).fill(0xFF)
+    ctx.call("affine_matvec", dw, ds, db, dx, y, rows, cols, group, batch)
+    got = y.download(np.float16, (batch, rows))
+    ref = oracle.affine_matvec(w, s, b, x, rows, cols, group)
+    assert rel_err(got, ref) < REL_TOL
+    canary = y.download(np.uint8, (64,), offset=batch * rows * 2)
+    assert np.all(canary == 0xFF)  # nothing written past the output
+
+
+def test_affine_matvec_reference_fixture(ctx, oracle):
+    """The reference's own production-shape check (PrefillKernelTests.swift:11982-12061): 4096x1024, abs tol 0.02."""
+    rows, cols, g = 4096, 1024, 64
+    w, s, b = synth.ref_affine_fixture(rows, cols, g, 1)
+    x = synth.ref_float16_vector(cols, float(synth.REGION_SEED_PRIMARY), 0.5)
+    dw, ds, db, dx = dev(ctx, w, s, b, x)
+    y = ctx.alloc(rows * 2)
+    ctx.call("affine_matvec", dw, ds, db, dx, y, rows, cols, g, 1)
+    got = y.download(np.float16, (rows,)).astype(np.float32)
+    ref = oracle.affine_matvec(w, s, b, x, rows, cols, g)[0].astype(np.float32)
+    assert np.max(np.abs(got - ref)) < 0.02
+    assert np.max(np.abs(got)) > 1e-2
+
+
+def test_affine_batched_equals_iterated_bitwise(ctx):
+    """Batched == iterated, bit for bit (the reference pins this GPU-vs-GPU, PrefillKernelTests.swift:9101-9993)."""
+    rows, cols, g, batch = 512, 2048, 64, 8
+    w, s, b = synth.affine_u4(3, "bi", rows, cols, g)
+    x = synth.activations(3, "x", batch, cols)
+    dw, ds, db, dx = dev(ctx, w, s, b, x)
+    y = ctx.alloc(batch * rows * 2)
+    ctx.call("affine_matvec", dw, ds, db, dx, y, rows, cols, g, batch)
+    batched = y.download(np.uint16, (batch, rows))
+    y1 = ctx.alloc(rows * 2)
+    for i in range(batch):
+        ctx.call("affine_matvec", dw, ds, db, dx.at(i * cols * 2), y1, rows, cols, g, 1)
+        assert np.array_equal(y1.download(np.uint16, (rows,)), batched[i])
+    ctx.call("affine_matvec", dw, ds, db, dx, y, rows, cols, g, batch)
+    assert np.array_equal(y.download(np.uint16, (batch, rows)), batched)  # run-to-run determinism
+
+
+@pytest.mark.parametrize("rows,cols,batch", [(2048, 6144, 1), (257, 512, 3), (512, 12288, 8)])
+def test_affine_matvec_add(ctx, oracle, rows, cols, batch):
+    w, s, b = synth.affine_u4(1, "add", rows, cols, 64)
+    x = synth.activations(1, "x", batch, cols)
+    res = synth.activations(1, "res", batch, rows)
+    dw, ds, db, dx, dr = dev(ctx, w, s, b, x, res)
+    ctx.call("affine_matvec_add", dw, ds, db, dx, dr, dr, rows, cols, 64, batch)  # in place on the residual
+    got = dr.download(np.float16, (batch, rows))
+    ref = oracle.affine_matvec_add(w, s, b, x, res, rows, cols, 64)
+    assert rel_err(got, ref) < REL_TOL
+
+
+@pytest.mark.parametrize("rows,cols,batch", [(6144, 2048, 1), (261, 512, 4), (1024, 4096, 16)])
+def test_affine_gate_up_swiglu(ctx, oracle, rows, cols, batch):
+    gw, gs, gb = synth.affine_u4(2, "gate", rows, cols, 64)
+    uw, us, ub = synth.affine_u4(2, "up", rows, cols, 64)
+    x = synth.activations(2, "x", batch, cols)
+    d = dev(ctx, gw, gs, gb, uw, us, ub, x)
+    y = ctx.alloc(batch * rows * 2)
+    ctx.call("affine_gate_up_swiglu", *d, y, rows, cols, 64, batch)
+    got = y.download(np.float16, (batch, rows))
+    ref = oracle.affine_gate_up_swiglu(gw, gs, gb, uw, us, ub, x, rows, cols, 64, round_gate_up=False)
+    assert rel_err(got, ref) < REL_TOL
+
+
+def test_affine_dual_matvec(ctx, oracle):
+    rows, cols, batch = 512, 2048, 2
+    a = synth.affine_u4(4, "k", rows, cols, 64)
+    b = synth.affine_u4(4, "v", rows, cols, 64)
+    x = synth.activations(4, "x", batch, cols)
+    d = dev(ctx, *a, *b, x)
+    y0, y1 = ctx.alloc(batch * rows * 2), ctx.alloc(batch * rows * 2)
+    ctx.call("affine_dual_matvec", *d, y0, y1, rows, cols, 64, batch)
+    assert rel_err(y0.download(np.float16, (batch, rows)), oracle.affine_matvec(*a, x, rows, cols, 64)) < REL_TOL
+    assert rel_err(y1.download(np.float16, (batch, rows)), oracle.affine_matvec(*b, x, rows, cols, 64)) < REL_TOL
+
+
+def test_affine_rejects_bad_arguments(ctx):
+    d = ctx.alloc(4096)
+    assert ctx.call_status("affine_matvec", d, d, d, d, d, 16, 100, 64, 1) == capi.BAD_ARGUMENT  # cols % group
+    assert ctx.call_status("affine_matvec", d, d, d, d, d, 16, 128, 48, 1) == capi.BAD_ARGUMENT  # group
+    assert ctx.call_status("affine_matvec", d, d, d, None, d, 16, 128, 64, 1) == capi.BAD_ARGUMENT
+    assert ctx.call_status("affine_matvec", d.at(8), d, d, d, d, 16, 128, 64, 1) == capi.BAD_ARGUMENT  # alignment
+    assert "16-byte" in ctx.last_error()
+
+
+# ── dense fp16 matvec (LM head) ─────────────────────────────────────────────
+@pytest.mark.parametrize("rows,cols,batch", [(4099, 4096, 1), (1000, 2048, 8), (333, 1024, 11)])
+def test_fp16_matvec(ctx, oracle, rows, cols, batch):
+    w = synth.normal_f16(5, "head", (rows, cols), 0.02)
+    x = synth.activations(5, "x", batch, cols)
+    dw, dx = dev(ctx, w, x)
+    y = ctx.alloc(batch * rows * 2)
+    ctx.call("fp16_matvec", dw, dx, y, rows, cols, batch)
+    got = y.download(np.float16, (batch, rows))
+    assert rel_err(got, oracle.fp16_matvec(w, x, rows, cols)) < REL_TOL
+
+
+def test_fp16_matvec_clamps(ctx):
+    w = np.full((8, 64), 60000.0, np.float16)
+    x = np.ones(64, np.float16)
+    dw, dx = dev(ctx, w, x)
+    y = ctx.alloc(16)
+    ctx.call("fp16_matvec", dw, dx, y, 8, 64, 1)
+    assert np.all(y.download(np.float16, (8,)) == np.float16(65504))
+
+
+# ── binary / ternary ────────────────────────────────────────────────────────
+def _ref_signed_case(fmt):
+    """SignedQuantKernelTests.swift:989-1047: rows 5, cols 256, batch 5."""
+    rows, cols, batches = 5, 256, 5
+    r = np.arange(rows)[:, None]
+    c = np.arange(cols)[None, :]
+    code = ((r * 13 + c * 7) & 1 if fmt == 1 else (r * 13 + c * 7) % 3).astype(np.uint8)
+    codes = synth.pack_codes(code, fmt)
+    scales = (np.float32(0.03125) * ((np.arange(rows * 2) % 5) + 1)).astype(np.float16).reshape(rows, 2)
+    x = (np.sin((np.arange(batches * cols) * 17 + 3).astype(np.float32)) * np.float32(0.75)).astype(np.float16).reshape(batches, cols)
+    return rows, cols, batches, codes, scales, x
+
+
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_signed_matvec_reference_fixture(ctx, oracle, fmt):
+    rows, cols, batches, codes, scales, x = _ref_signed_case(fmt)
+    dc, ds, dx = dev(ctx, codes, scales, x)
+    y = ctx.alloc(batches * rows * 2)
+    ctx.call("signed_matvec", fmt, dc, ds, dx, y, rows, cols, batches)
+    got = y.download(np.float16, (batches, rows)).astype(np.float32)
+    ref = oracle.signed_matvec(fmt, codes, scales, x, rows, cols, f32=True)
+    assert np.all(np.abs(got - ref) <= np.maximum(0.02, np.abs(ref) * 0.01))  # the reference's tolerance
+    assert rel_err(got, ref) < REL_TOL
+
+
+def test_ternary_matches_mlx_golden_bits(ctx):
+    """SignedQuantKernelTests.swift:87-106, :143-164: operands are dyadic, so any fp32 order gives these bits."""
+    for rows, cols, batches, unit, expected in [
+        (9, 512, 1, 0.03125, [0xb190, 0x3468, 0xb0b0, 0x2e20, 0xa580, 0x3370, 0xb518, 0x3498, 0xb170]),
+        (9, 5120, 3, 0.00390625, [0xa160, 0x9dc0, 0x2420, 0xa160, 0x9dc0, 0x2420, 0xa160, 0x9dc0, 0x2420,
+                                  0x2520, 0xa650, 0x1cc0, 0x2520, 0xa650, 0x1cc0, 0x2520, 0xa650, 0x1cc0,
+                                  0x2280, 0x1700, 0xa360, 0x2280, 0x1700, 0xa360, 0x2280, 0x1700, 0xa360]),
+    ]:
+        r = np.arange(rows)[:, None]
+        c = np.arange(cols)[None, :]
+        codes = synth.pack_codes(((r * 13 + c * 7) % 3).astype(np.uint8), 2)
+        groups = cols // 128
+        scales = (np.float32(unit) * ((np.arange(rows * groups) % 5) + 1)).astype(np.float16).reshape(rows, groups)
+        i = np.arange(batches * cols)
+        x = (((i * 17 + 3) % 31 - 15).astype(np.float32) / 16).astype(np.float16).reshape(batches, cols)
+        dc, ds, dx = dev(ctx, codes, scales, x)
+        y = ctx.alloc(batches * rows * 2)
+        ctx.call("signed_matvec", 2, dc, ds, dx, y, rows, cols, batches)
+        assert y.download(np.uint16, (batches * rows,)).tolist() == expected
+
+
+@pytest.mark.parametrize("fmt,maker", [(1, synth.binary1), (2, synth.ternary2)])
+@pytest.mark.parametrize("rows,cols", [(1024, 5120), (512, 17408)])
+def test_signed_matvec_27b_shapes(ctx, oracle, fmt, maker, rows, cols):
+    codes, scales = maker(6, "sm", rows, cols)
+    x = synth.activations(6, "x", 1, cols)
+    dc, ds, dx = dev(ctx, codes, scales, x)
+    y = ctx.alloc(rows * 2)
+    ctx.call("signed_matvec", fmt, dc, ds, dx, y, rows, cols, 1)
+    assert rel_err(y.download(np.float16, (1, rows)), oracle.signed_matvec(fmt, codes, scales, x, rows, cols)) < REL_TOL
+
+
+@pytest.mark.parametrize("fmt,maker", [(1, synth.binary1), (2, synth.ternary2)])
+def test_signed_matvec_add_and_gate_up(ctx, oracle, fmt, maker):
+    rows, cols, batch = 261, 1024, 3
+    gc, gs = maker(7, "g", rows, cols)
+    uc, us = maker(7, "u", rows, cols)
+    x = synth.activations(7, "x", batch, cols)
+    res = synth.activations(7, "r", batch, rows)
+    dgc, dgs, duc, dus, dx, dr = dev(ctx, gc, gs, uc, us, x, res)
+    y = ctx.alloc(batch * rows * 2)
+    ctx.call("signed_matvec_add", fmt, dgc, dgs, dx, dr, y, rows, cols, batch)
+    assert rel_err(y.download(np.float16, (batch, rows)), oracle.signed_matvec_add(fmt, gc, gs, x, res, rows, cols)) < REL_TOL
+    ctx.call("signed_gate_up_swiglu", fmt, dgc, dgs, duc, dus, dx, y, rows, cols, batch)
+    got = y.download(np.float16, (batch, rows))
+    staged = oracle.signed_gate_up_swiglu(fmt, gc, gs, uc, us, x, rows, cols, staged=True)
+    plain = oracle.signed_gate_up_swiglu(fmt, gc, gs, uc, us, x, rows, cols, staged=False).astype(np.float32)
+    assert rel_err(got, staged) < 4e-3  # a one-ulp flip of gate or up moves the staged fp16 chain by a few ulp
+    g32 = got.astype(np.float32)
+    assert np.all(np.abs(g32 - plain) <= np.maximum(0.03, np.abs(plain) * 0.015))  # the reference's tolerance (:1227-1232)
+
+
+# ── attention ───────────────────────────────────────────────────────────────
+@pytest.mark.parametrize("seq_len,window", [(32, 0), (32, 8), (192, 0), (1, 0), (17, 0)])
+def test_attention_reference_fixture(ctx, oracle, seq_len, window):
+    """RegionExactnessTests.swift:1271-1357: 4 q heads, 2 kv heads, head_dim 128."""
+    n_q, n_kv, d = 4, 2, 128
+    cap = max(seq_len, 64)
+    q, k, v = synth.ref_attention_inputs(n_q, n_kv, d, cap, 1)
+    dq, dk, dv = dev(ctx, q, k, v)
+    out = ctx.alloc(n_q * d * 2)
+    ctx.call("attention_decode", dq, dk, dv, out, n_q, n_kv, d, cap, seq_len, C.c_float(1 / np.sqrt(d)), window, 1, 0)
+    got = out.download(np.float16, (n_q, d))
+    ref = oracle.attention_decode(q, k, v, n_q, n_kv, d, cap, seq_len, sliding_window=window)
+    assert rel_err(got, ref) < REL_TOL
+    assert np.max(np.abs(got.astype(np.float32))) > 1e-3
+
+
+@pytest.mark.parametrize("n_q,n_kv,d", [(16, 4, 128), (8, 2, 256), (32, 8, 128), (16, 1, 64)])
+@pytest.mark.parametrize("ctx_len,batch", [(1024, 1), (4096, 1), (1000, 8), (32768, 1)])
+def test_attention_config3(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
+    if ctx_len == 32768 and (n_q, n_kv, d) not in [(16, 4, 128), (8, 2, 256)]:
+        pytest.skip("long context is covered on the two benchmark head shapes")
+    cap = ctx_len + 8
+    k = synth.kv_cache(8, "k", batch, n_kv, cap, d)
+    v = synth.kv_cache(8, "v", batch, n_kv, cap, d)
+    q = synth.activations(8, "q", batch, n_q, d)
+    dq, dk, dv = dev(ctx, q, k, v)
+    out = ctx.alloc(batch * n_q * d * 2)
+    ctx.call("attention_decode", dq, dk, dv, out, n_q, n_kv, d, cap, ctx_len, C.c_float(1 / np.sqrt(d)), 0, batch, C.c_size_t(n_kv * cap * d))
+    got = out.download(np.float16, (batch, n_q, d))
+    for b in range(batch):
+        ref = oracle.attention_decode(q[b], k[b], v[b], n_q, n_kv, d, cap, ctx_len)
+        assert rel_err(got[b], ref) < REL_TOL
+
+
+def test_attention_in_place(ctx, oracle):
+    n_q, n_kv, d, cap, seq = 16, 4, 128, 600, 555
+    k = synth.kv_cache(9, "k", 1, n_kv, cap, d)[0]
+    v = synth.kv_cache(9, "v", 1, n_kv, cap, d)[0]
+    q = synth.activations(9, "q", n_q, d)
+    dq, dk, dv = dev(ctx, q, k, v)
+    ctx.call("attention_decode", dq, dk, dv, dq, n_q, n_kv, d, cap, seq, C.c_float(1 / np.sqrt(d)), 0, 1, 0)
+    assert rel_err(dq.download(np.float16, (n_q, d)), oracle.attention_decode(q, k, v, n_q, n_kv, d, cap, seq)) < REL_TOL
+
+
+# ── glue ────────────────────────────────────────────────────────────────────
+@pytest.mark.parametrize("dim,batch", [(2048, 1), (4096, 3), (5120, 1), (100, 2)])
+def test_rms_norm_1pw(ctx, oracle, dim, batch):
+    x = synth.activations(10, "x", batch, dim)
+    w = (synth.activations(10, "w", dim).astype(np.float32) * 0.1).astype(np.float16)
+    dx, dw = dev(ctx, x, w)
+    y = ctx.alloc(batch * dim * 2)
+    ctx.call("rms_norm_1pw", dx, dw, y, dim, C.c_float(1e-6), batch)
+    got = y.download(np.float16, (batch, dim))
+    for b in range(batch):
+        ref = oracle.rms_norm_1pw(x[b], w, 1e-6, two_stage=True)
+        d = ulp_diff_f16(got[b], ref)
+        assert d.max() <= 1 and np.mean(d > 0) < 0.01  # summation order may move rsqrt by an fp32 ulp
+        assert rel_err(got[b], oracle.rms_norm_1pw(x[b], w, 1e-6, two_stage=False)) < REL_TOL
+
+
+def test_per_head_rms_norm(ctx, oracle):
+    heads, d = 16, 128
+    x = synth.activations(11, "x", heads, d)
+    w = (1 + synth.activations(11, "w", d).astype(np.float32) * 0.1).astype(np.float16)
+    dx, dw = dev(ctx, x, w)
+    ctx.call("per_head_rms_norm", dx, dw, dx, heads, d, C.c_float(1e-6))
+    d_ulp = ulp_diff_f16(dx.download(np.float16, (heads, d)), oracle.per_head_rms_norm(x, w, heads, d, 1e-6))
+    assert d_ulp.max() <= 1 and np.mean(d_ulp > 0) < 0.01
+
+
+def test_elementwise_add_and_swiglu(ctx, oracle):
+    n = 6144 * 3 + 5
+    a, b = synth.activations(12, "a", n), synth.activations(12, "b", n)
+    da, db = dev(ctx, a, b)
+    y = ctx.alloc(n * 2)
+    ctx.call("elementwise_add", da, db, y, C.c_size_t(n))
+    assert np.array_equal(y.download(np.uint16, (n,)), oracle.elementwise_add(a, b).view(np.uint16))
+    a4 = (a.astype(np.float32) * 4).astype(np.float16)
+    da4 = ctx.to_device(a4)
+    ctx.call("swiglu_fused", da4, db, y, C.c_size_t(n))
+    d = ulp_diff_f16(y.download(np.float16, (n,)), oracle.swiglu_staged(a4, b))
+    assert d.max() <= 2 and np.mean(d > 0) < 0.02  # expf differs from the host's by an ulp at most
+
+
+def test_embedding_gathers(ctx, oracle):
+    vocab, hidden = 1000, 2048
+    table = synth.normal_f16(13, "emb", (vocab, hidden), 0.02)
+    tok = np.array([7, 999, 0], np.int32)
+    dt, dtok = dev(ctx, table, tok)
+    y = ctx.alloc(3 * hidden * 2)
+    ctx.call("embedding_gather", dt, dtok, y, hidden, 3)
+    assert np.array_equal(y.download(np.uint16, (3, hidden)), table[tok].view(np.uint16))
+    w, s, b = synth.affine_u4(13, "aemb", vocab, hidden, 64)
+    dw, ds, db = dev(ctx, w, s, b)
+    ctx.call("affine_embedding_gather", dw, ds, db, dtok.at(4), y, hidden, 64)
+    ref = oracle.affine_dequantize_f16(w[999:1000], s[999:1000], b[999:1000], 1, hidden, 64)
+    assert np.array_equal(y.download(np.uint16, (1, hidden)), ref.view(np.uint16))
+
+
+@pytest.mark.parametrize("layout", [0, 1, 2])
+def test_rope_table_mode_bit_exact(ctx, oracle, layout):
+    heads, d, rope = 4, 128, 64
+    qk = synth.ref_float16_vector(heads * d, float(synth.REGION_SEED_PRIMARY), 0.5, 0.1)
+    cos = synth.ref_float16_vector(rope, float(synth.REGION_SEED_SECONDARY), 0.9, phase=0.0237)
+    sin = synth.ref_float16_vector(rope, float(synth.REGION_SEED_TERTIARY), 0.9, phase=0.0193)
+    dq, dc, dsn = dev(ctx, qk, cos, sin)
+    ctx.call("apply_rope", dq, dc, dsn, d, rope, heads, layout, 0, C.c_float(0), 0, 1)
+    ref = oracle.apply_rope(qk, d, rope, heads, layout, 0, math_mode=0, cos=cos, sin=sin)
+    assert np.array_equal(dq.download(np.uint16, (heads * d,)), ref.view(np.uint16))
+
+
+@pytest.mark.parametrize("position", [0, 1, 77, 4095, 32767])
+def test_rope_analytic_and_kv_append(ctx, oracle, position):
+    heads, d, cap = 8, 128, 32768
+    base_log2 = float(np.log2(np.float32(1e6)))
+    qk = synth.activations(14, "qk", heads, d)
+    dq = ctx.to_device(qk)
+    ctx.call("apply_rope", dq, None, None, d, d, heads, 1, position, C.c_float(base_log2), 1, 1)
+    ref = oracle.apply_rope(qk, d, d, heads, 1, position, base_log2, 1)
+    du = ulp_diff_f16(dq.download(np.float16, (heads, d)), ref.reshape(heads, d))
+    assert du.max() <= 1 and np.mean(du > 0) < 0.02  # device sincosf / exp2f vs the host's
+    cache = ctx.alloc(heads * cap * d * 2).fill(0)
+    new = ctx.to_device(qk)
+    ctx.call("kv_cache_update", cache, new, cap, d, position, heads, 1, 0)
+    row = cache.download(np.uint16, (heads, cap, d))
+    assert np.array_equal(row[:, position, :], qk.view(np.uint16))
+    assert row.sum(dtype=np.uint64) == qk.view(np.uint16).sum(dtype=np.uint64)  # nothing else touched
+    ctx.call("rope_kv_cache_update", cache, new, None, None, cap, d, position, heads, d, 1, C.c_float(base_log2), 1, 1, 0)
+    got = cache.download(np.float16, (heads, cap, d))[:, position, :]
+    assert ulp_diff_f16(got, ref.reshape(heads, d)).max() <= 1
+    assert ctx.call_status("kv_cache_update", cache, new, cap, d, cap, heads, 1, 0) == capi.OUT_OF_RANGE
+
+
+def test_argmax_ties_and_full_vocab(ctx, oracle):
+    out = ctx.alloc(8 * 4)
+    for arr in [np.array([1, 3, 3, 2], np.float16), np.array([0x8000, 0x0000, 0x8000], np.uint16).view(np.float16),
+                np.array([-5, -2, -2], np.float16), np.full(5000, -65504, np.float16)]:
+        d = ctx.to_device(arr)
+        ctx.call("argmax_f16", d, out, arr.size, 1)
+        assert int(out.download(np.int32, (1,))[0]) == oracle.argmax_f16(arr)
+    logits = synth.activations(15, "logits", 3, 151936)
+    logits[1, 150000] = logits[1, 17] = np.float16(9.0)
+    d = ctx.to_device(logits)
+    ctx.call("argmax_f16", d, out, 151936, 3)
+    got = out.download(np.int32, (3,))
+    assert got.tolist() == [oracle.argmax_f16(logits[b]) for b in range(3)]
+    assert got[1] == 17
