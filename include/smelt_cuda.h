@@ -177,6 +177,15 @@ SMELT_CUDA_API smelt_status smelt_cuda_graph_seed(smelt_cuda_ctx* ctx, const int
 /* Replay n_steps tokens.  When out_tokens != NULL, waits and returns the n_steps * batch
  * generated ids (step-major). */
 SMELT_CUDA_API smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* out_tokens);
+/* One token through the captured graph with host buffers: tokens and position travel in,
+ * the graph is replayed once, the argmax ids are read back and the call waits — the
+ * graph-backed equivalent of smelt_cuda_decode_step. */
+SMELT_CUDA_API smelt_status smelt_cuda_graph_step(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position, int32_t* out_tokens);
+/* Device-side stopwatch on the context's stream (the gpuStartTime / gpuEndTime pair of
+ * profileDecodeStep, SmeltRuntime.swift:3279-3318): start records an event, stop records a
+ * second one, waits for it and returns the elapsed milliseconds between the two. */
+SMELT_CUDA_API smelt_status smelt_cuda_timer_start(smelt_cuda_ctx* ctx);
+SMELT_CUDA_API smelt_status smelt_cuda_timer_stop(smelt_cuda_ctx* ctx, float* out_ms);
 /* Number of kernel launches one interpretation of the last built / enqueued table issues. */
 SMELT_CUDA_API int smelt_cuda_last_launch_count(const smelt_cuda_ctx* ctx);
 

@@ -745,6 +745,26 @@ smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* 
     return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph decode");
 }
 
+smelt_status smelt_cuda_graph_step(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position, int32_t* out_tokens) {
+    if (!ctx || !tokens) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!ctx->graph_exec) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "no graph has been built");
+    smelt_status s = check_step(ctx, tokens, position);
+    if (s) return s;
+    s = write_dynamic(ctx, tokens, position);
+    if (s) return s;
+    s = check_cuda(ctx, cudaGraphLaunch(ctx->graph_exec, ctx->stream), "cudaGraphLaunch");
+    if (s) return s;
+    const uint32_t B = ctx->cfg.batch;
+    Slot& as = ctx->slots[ctx->cfg.argmax_slot];
+    cudaMemcpyAsync(ctx->h_pinned + 128, as.ptr, B * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph step");
+    if (s) return s;
+    if (out_tokens)
+        for (uint32_t b = 0; b < B; ++b) out_tokens[b] = ctx->h_pinned[128 + b];
+    return SMELT_OK;
+}
+
 int smelt_cuda_last_launch_count(const smelt_cuda_ctx* ctx) { return ctx ? ctx->launch_count : 0; }
 
 }  // extern "C"

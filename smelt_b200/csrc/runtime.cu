@@ -74,6 +74,7 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     ok = ok && cudaMalloc(&ctx->attn_scratch, ctx->attn_scratch_bytes) == cudaSuccess;
     ctx->argmax_scratch_bytes = 64 * 1024 * sizeof(uint64_t);
     ok = ok && cudaMalloc(&ctx->argmax_scratch, ctx->argmax_scratch_bytes) == cudaSuccess;
+    ok = ok && cudaEventCreate(&ctx->ev_start) == cudaSuccess && cudaEventCreate(&ctx->ev_stop) == cudaSuccess;
     if (!ok) {
         smelt_cuda_destroy(ctx);
         return SMELT_ERR_ALLOC;
@@ -97,6 +98,8 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gen_ring);
     cudaFree(ctx->gen_count);
+    if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+    if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -125,6 +128,19 @@ smelt_status smelt_cuda_device_error(smelt_cuda_ctx* ctx, uint32_t* out_flags) {
         return fail(ctx, SMELT_ERR_DEVICE_TIMEOUT, "a kernel's bounded wait gave up (flags " + std::to_string(*out_flags) + ")");
     }
     return SMELT_OK;
+}
+
+smelt_status smelt_cuda_timer_start(smelt_cuda_ctx* ctx) {
+    CTX_OR_FAIL();
+    return check_cuda(ctx, cudaEventRecord(ctx->ev_start, ctx->stream), "timer start");
+}
+smelt_status smelt_cuda_timer_stop(smelt_cuda_ctx* ctx, float* out_ms) {
+    CTX_OR_FAIL();
+    if (!out_ms) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "out_ms is null");
+    smelt_status s = check_cuda(ctx, cudaEventRecord(ctx->ev_stop, ctx->stream), "timer stop");
+    if (!s) s = check_cuda(ctx, cudaEventSynchronize(ctx->ev_stop), "timer sync");
+    if (!s) s = check_cuda(ctx, cudaEventElapsedTime(out_ms, ctx->ev_start, ctx->ev_stop), "timer elapsed");
+    return s;
 }
 
 smelt_status smelt_cuda_malloc(smelt_cuda_ctx* ctx, size_t bytes, void** out_dev) {

@@ -86,6 +86,7 @@ struct smelt_cuda_ctx {
     uint32_t gen_capacity = 0;
     int launch_count = 0;
     bool capturing = false;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
 
     // tensor parallel
     void* nccl_comm = nullptr;
