@@ -86,7 +86,7 @@ class SyntheticPackage:
                   "o": (c.hidden, c.n_q * c.head_dim), "gate": (c.inter, c.hidden), "up": (c.inter, c.hidden),
                   "down": (c.hidden, c.inter)}
         rows, cols = shapes[name]
-        return synth.affine_u4(self.seed, f"layer{layer}.{name}", rows, cols, c.group)
+        return synth.affine_u4_model(self.seed, f"layer{layer}.{name}", rows, cols, c.group)
 
     def norm_delta(self, name: str) -> np.ndarray:
         """Stored norm weight (w - 1): weight == 1 plus small seeded noise, so the stored tensor is near zero."""
