@@ -214,10 +214,18 @@ typedef struct {
 } smelt_decoder_desc;
 /* Allocates the activation / KV / scratch slots for `desc` at `capacity` positions and
  * `batch` sequences, registers the pipelines, configures the context and writes the table.
- * records may be NULL to query the count through *n_records. */
+ * With ctx == NULL nothing is allocated: the call only writes the records (or, with
+ * records == NULL, returns their count through *n_records); pipeline indices are
+ * assigned in order of first use and listed by smelt_cuda_decoder_pipelines. */
 SMELT_CUDA_API smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc,
                                                      const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
                                                      smelt_dispatch_record* records, size_t* n_records);
+
+/* The manifest.pipelines array matching the table smelt_cuda_build_decoder writes for `desc`
+ * and `batch`: names in index order, newline separated.  *needed_bytes receives the size of
+ * the text including its terminator; out may be NULL to query it. */
+SMELT_CUDA_API smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_desc* desc, uint32_t batch, char* out,
+                                                         size_t out_bytes, size_t* needed_bytes);
 
 /* ── tensor parallelism (no counterpart in the reference, which is single-device) ──
  * One process per GPU.  Rank 0 creates an id, the caller ships it to the other ranks, every

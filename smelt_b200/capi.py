@@ -92,7 +92,7 @@ def declared_symbols() -> list[str]:
 
 def _ctype_of(param: str):
     if "*" in param or "[" in param:
-        return C.c_char_p if param.startswith("const char") else C.c_void_p
+        return C.c_char_p if param.startswith("const char") else C.c_void_p  # char* out buffers stay void*
     t = param.rsplit(" ", 1)[0].replace("const ", "").strip()
     return {"int": C.c_int, "int32_t": C.c_int32, "uint32_t": C.c_uint32, "size_t": C.c_size_t, "float": C.c_float,
             "uint64_t": C.c_uint64}[t]

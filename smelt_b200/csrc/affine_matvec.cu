@@ -7,23 +7,27 @@
 //
 //   y[b, r] = sum_g ( s[r,g] * sum_{k in g} q[r,k] * x[b,k]  +  b[r,g] * sum_{k in g} x[b,k] )
 //
-// Data path.  A CTA owns 16 output rows and one K-slice (<= 4096 columns).  Its whole packed
-// weight tile is fetched with untiled bulk async copies (one per row and K-quarter) that
-// complete on four mbarriers, so the copies are issued before the programmatic-dependent-
-// launch wait and overlap the tail of the kernel that produces x.  Eight warps split the
-// slice's groups; a warp dequantises a 16-row x GROUP-column block in registers (two LOP3 and
-// two HFMA2 per eight nibbles give exact fp16 integers 0..15) and multiplies it with up to 8
-// (or 16) activation rows by mma.sync.m16n8k16 with fp32 accumulators: the tensor pipe is used
-// as a wide FMA unit so the CUDA cores only pay for the unpack.  The k order inside an MMA is
-// permuted (nibbles i and i+4 of a word share a half2) and the activations are staged in
-// shared memory in the same permuted order.  After every group the fp32 block sum is folded
-// into the running row sums with the group's scale, and the bias term uses per-group
-// activation sums computed once per CTA.  Warp partials are reduced through shared memory in a
-// fixed order; K-slices of one row tile form a thread-block cluster and are reduced through
-// distributed shared memory in rank order, so results are bit-reproducible.
+// Data path.  A CTA owns 16 output rows and one K-slice.  Its whole packed weight tile is
+// fetched with 16-byte cp.async copies (512 contiguous bytes per warp instruction, L1
+// bypassed) committed as four K-quarter groups, so compute on the first quarter starts while
+// the rest is in flight; the copies and the scale / bias loads are issued before the
+// programmatic-dependent-launch wait and therefore overlap the tail of the kernel that
+// produces x.  Eight warps split the slice's groups; a warp dequantises a 16-row x
+// GROUP-column block in registers (two LOP3 and two HFMA2 per eight nibbles give exact fp16
+// integers 0..15) and multiplies it with up to 8 (or 16) activation rows by
+// mma.sync.m16n8k16 with fp32 accumulators: the tensor pipe is used as a wide FMA unit so the
+// CUDA cores only pay for the unpack.  The k order inside an MMA is permuted (nibbles i and
+// i+4 of a word share a half2) and the activations are staged in shared memory in the same
+// permuted order.  After every group the fp32 block sum is folded into the running row sums
+// with the group's scale, and the bias term uses per-group activation sums computed once per
+// CTA.  Warp partials are reduced through shared memory in a fixed order; K-slices of one row
+// tile form a thread-block cluster and are reduced through distributed shared memory in rank
+// order, so results are bit-reproducible.
 #include "affine_matvec.h"
 
 #include <cooperative_groups.h>
+
+#include <cstdlib>
 
 namespace cg = cooperative_groups;
 
@@ -34,7 +38,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 constexpr int kRows = 16;  // rows per CTA (one m16 tile)
-constexpr int kBars = 4;   // K-quarters per weight tile
+constexpr int kQuarters = 4;  // cp.async commit groups per weight tile
 
 struct SmemLayout {
     uint32_t bars, w, sb, xs, xsum, red, total;
@@ -46,7 +50,7 @@ __host__ __device__ inline SmemLayout make_layout(int nw, int nb, int ks, int ba
     SmemLayout L;
     const int gs = ks / GROUP;
     L.pitch_w = (uint32_t)(ks / 2 + GROUP / 2);          // ≡ GROUP/2 (mod 128): conflict-free row stride
-    L.pitch_sb = (uint32_t)((gs | 1) * 4);               // odd number of {scale,bias} words per row
+    L.pitch_sb = (uint32_t)((gs | 1) * 8);               // odd number of fp32 {scale,bias} pairs per row
     L.pitch_x = (uint32_t)(ks * 2 + 16);                 // ≡ 16 (mod 128)
     uint32_t off = 0;
     L.bars = off; off += 64;
@@ -117,85 +121,102 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
     const int gs = ks / GROUP;                              // groups in this slice
     const int groups_total = a.cols / GROUP;
     const SmemLayout L = make_layout<GROUP>(NW, NB, a.ks, a.batch);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
     uint8_t* sw = smem + L.w;
-    uint32_t* ssb = reinterpret_cast<uint32_t*>(smem + L.sb);
+    float2* ssb = reinterpret_cast<float2*>(smem + L.sb);
     uint8_t* sx = smem + L.xs;
     float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
     float* sred = reinterpret_cast<float*>(smem + L.red);
 
-    const int gq = (gs + kBars - 1) / kBars;                // groups per K-quarter
-
-    if (tid == 0) {
-        for (int q = 0; q < kBars; ++q) mbar_init(&bars[q], NW * kRows);
-        mbar_fence_init();
-    }
-    __syncthreads();
+    const int gq = (gs + kQuarters - 1) / kQuarters;        // groups per K-quarter
 
     // ── weight prefetch: independent of the upstream kernel, issued before the PDL wait ──
-    if (tid < NW * kRows) {
-        const int set = tid / kRows, r = tid % kRows;
-        const bool valid = row0 + r < a.rows;
-        const uint8_t* src = a.w[set] + (size_t)(row0 + r) * (a.cols / 2) + k0 / 2;
-        uint8_t* dst = sw + (size_t)(set * kRows + r) * L.pitch_w;
-        for (int q = 0; q < kBars; ++q) {
-            const int c0 = min(q * gq, gs) * (GROUP / 2), c1 = min((q + 1) * gq, gs) * (GROUP / 2);
-            const uint32_t bytes = valid ? (uint32_t)(c1 - c0) : 0u;
-            mbar_arrive_expect_tx(&bars[q], bytes);
-            if (bytes) bulk_g2s(dst + c0, src + c0, bytes, &bars[q]);
+    // A warp copies one row segment at a time, 512 contiguous bytes per instruction.
+    for (int q = 0; q < kQuarters; ++q) {
+        const int c0 = min(q * gq, gs) * (GROUP / 32), c1 = min((q + 1) * gq, gs) * (GROUP / 32);  // 16-byte chunks
+#pragma unroll
+        for (int rr = warp; rr < NW * kRows; rr += kWarps) {  // rr = set * 16 + row
+            const int set = rr / kRows, r = rr % kRows;
+            if (row0 + r < a.rows) {
+                const uint8_t* src = a.w[set] + (size_t)(row0 + r) * (a.cols / 2) + k0 / 2;
+                uint8_t* dst = sw + (size_t)rr * L.pitch_w;
+                for (int c = c0 + lane; c < c1; c += 32) cp_async16(dst + c * 16, src + c * 16);
+            }
         }
+        cp_async_commit();
     }
-    // {scale,bias} pairs of the slice, interleaved so one 32-bit read serves a group.
-    for (int i = tid; i < NW * kRows * gs; i += kThreads) {
-        const int set = i / (kRows * gs), r = (i / gs) % kRows, gi = i % gs;
-        uint32_t v = 0;
-        if (row0 + r < a.rows) {
-            const size_t idx = (size_t)(row0 + r) * groups_total + k0 / GROUP + gi;
-            v = (uint32_t)__half_as_ushort(a.s[set][idx]) | ((uint32_t)__half_as_ushort(a.b[set][idx]) << 16);
+    // {scale, bias} of every (row, group) of the slice as fp32 pairs, so the main loop reads
+    // one 64-bit word per row and converts nothing.
+    {
+        const bool vec = ((groups_total * 2) % 16 == 0) && ((k0 / GROUP * 2) % 16 == 0) && (gs % 8 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(a.s[0]) | reinterpret_cast<uintptr_t>(a.b[0]) |
+                           reinterpret_cast<uintptr_t>(a.s[NW - 1]) | reinterpret_cast<uintptr_t>(a.b[NW - 1])) & 15u) == 0;
+#pragma unroll
+        for (int rr = warp; rr < NW * kRows; rr += kWarps) {
+            const int set = rr / kRows, r = rr % kRows;
+            float2* dst = ssb + (size_t)rr * (L.pitch_sb / 8);
+            const bool valid = row0 + r < a.rows;
+            const size_t base = (size_t)(row0 + r) * groups_total + k0 / GROUP;
+            if (vec) {
+                for (int c = lane; c < gs / 8; c += 32) {  // 8 groups = 16 bytes of scales
+                    uint4 sv = make_uint4(0, 0, 0, 0), bv = make_uint4(0, 0, 0, 0);
+                    if (valid) {
+                        sv = __ldg(reinterpret_cast<const uint4*>(a.s[set] + base + c * 8));
+                        bv = __ldg(reinterpret_cast<const uint4*>(a.b[set] + base + c * 8));
+                    }
+                    const uint32_t sw4[4] = {sv.x, sv.y, sv.z, sv.w}, bw4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 sf = __half22float2(u32_as_h2(sw4[j])), bf = __half22float2(u32_as_h2(bw4[j]));
+                        dst[c * 8 + 2 * j] = make_float2(sf.x, bf.x);
+                        dst[c * 8 + 2 * j + 1] = make_float2(sf.y, bf.y);
+                    }
+                }
+            } else {
+                for (int gi = lane; gi < gs; gi += 32)
+                    dst[gi] = valid ? make_float2(__half2float(a.s[set][base + gi]), __half2float(a.b[set][base + gi])) : make_float2(0.f, 0.f);
+            }
         }
-        ssb[(size_t)(set * kRows + r) * (L.pitch_sb / 4) + gi] = v;
     }
 
     pdl_trigger();
     pdl_wait();
     if (dyn_skip(a.dyn)) {
-        // The copies already in flight must land before the CTA (and its shared memory) retires.
-        for (int q = 0; q < kBars; ++q) (void)mbar_wait_bounded(&bars[q], 0);
+        cp_async_wait<0>();  // copies in flight must land before the CTA's shared memory retires
         return;
     }
 
     // ── activations: permuted copy into shared memory + per-group sums ──
     {
-        const int chunks = ks / 8;                       // 8-column chunks per batch row
-        const int total = a.batch * chunks;
-        constexpr int CPG = GROUP / 8;                   // chunks per group
-        for (int base = 0; base < total; base += kThreads) {
-            const int i = base + tid;
-            float sum = 0.f;
-            int b = 0, c8 = 0;
-            if (i < total) {
-                b = i / chunks; c8 = i % chunks;
-                const uint4 v = *reinterpret_cast<const uint4*>(a.x + (size_t)b * a.cols + k0 + c8 * 8);
-                const __half2 h0 = u32_as_h2(v.x), h1 = u32_as_h2(v.y), h2 = u32_as_h2(v.z), h3 = u32_as_h2(v.w);
-                const float2 f0 = __half22float2(h0), f1 = __half22float2(h1), f2 = __half22float2(h2), f3 = __half22float2(h3);
-                sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
-                uint4 o;  // x0 x4 | x1 x5 | x2 x6 | x3 x7
-                o.x = __byte_perm(v.x, v.z, 0x5410);
-                o.y = __byte_perm(v.x, v.z, 0x7632);
-                o.z = __byte_perm(v.y, v.w, 0x5410);
-                o.w = __byte_perm(v.y, v.w, 0x7632);
-                *reinterpret_cast<uint4*>(sx + (size_t)b * L.pitch_x + c8 * 16) = o;
-            }
+        const int chunks = ks / 8;  // 8-column chunks per batch row
+        constexpr int CPG = GROUP / 8;  // chunks per group
+        for (int b = 0; b < a.batch; ++b) {
+            const __half* xr = a.x + (size_t)b * a.cols + k0;
+            uint8_t* xd = sx + (size_t)b * L.pitch_x;
+            for (int base = 0; base < chunks; base += kThreads) {
+                const int c8 = base + tid;
+                float sum = 0.f;
+                if (c8 < chunks) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                    const float2 f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
+                    const float2 f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
+                    sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+                    uint4 o;  // x0 x4 | x1 x5 | x2 x6 | x3 x7
+                    o.x = __byte_perm(v.x, v.z, 0x5410);
+                    o.y = __byte_perm(v.x, v.z, 0x7632);
+                    o.z = __byte_perm(v.y, v.w, 0x5410);
+                    o.w = __byte_perm(v.y, v.w, 0x7632);
+                    *reinterpret_cast<uint4*>(xd + c8 * 16) = o;
+                }
 #pragma unroll
-            for (int o = 1; o < CPG; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (i < total && (c8 % CPG) == 0) sxsum[(c8 / CPG) * NB + b] = sum;
+                for (int o = 1; o < CPG; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (c8 < chunks && (c8 % CPG) == 0) sxsum[(c8 / CPG) * NB + b] = sum;
+            }
         }
         for (int i = tid; i < gs * NB; i += kThreads)
             if ((i % NB) >= a.batch) sxsum[i] = 0.f;
     }
-    __syncthreads();
 
-    // ── main loop: this warp's groups ──
+    // ── main loop: this warp's groups, quarter by quarter ──
     float acc[NW][NBT][4];
 #pragma unroll
     for (int s = 0; s < NW; ++s)
@@ -204,73 +225,66 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[s][n][i] = 0.f;
 
-    bool ok = true;
-    int waited = -1;
-    for (int gi = warp; gi < gs; gi += kWarps) {
-        const int q = gi / gq;
-        while (waited < q) {
-            ++waited;
-            if (!mbar_wait_bounded(&bars[waited], 0)) ok = false;
-        }
-        // activation fragments for this group (rows of x = batch index g, g+8)
-        uint32_t xb[NBT][WPT * 4];
-#pragma unroll
-        for (int n = 0; n < NBT; ++n) {
-            const int b = n * 8 + g;
-            if (b < a.batch) {
-                const uint8_t* px = sx + (size_t)b * L.pitch_x + (size_t)(gi * GROUP + t * (GROUP / 4)) * 2;
-#pragma unroll
-                for (int j = 0; j < WPT; ++j) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(px + j * 16);
-                    xb[n][4 * j + 0] = v.x; xb[n][4 * j + 1] = v.y; xb[n][4 * j + 2] = v.z; xb[n][4 * j + 3] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < WPT * 4; ++j) xb[n][j] = 0u;
-            }
-        }
-#pragma unroll
-        for (int s = 0; s < NW; ++s) {
-            uint32_t wa[WPT], wb[WPT];
-            const uint8_t* pw = sw + (size_t)(s * kRows + g) * L.pitch_w + gi * (GROUP / 2) + t * (GROUP / 8);
-            WordLoad<WPT>::ld(pw, wa);
-            WordLoad<WPT>::ld(pw + 8 * (size_t)L.pitch_w, wb);
-            float c[NBT][4];
-#pragma unroll
-            for (int n = 0; n < NBT; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
-#pragma unroll
-            for (int j = 0; j < WPT; ++j) {
-                uint32_t pa[4], pb[4];
-                dequant8(wa[j], pa);
-                dequant8(wb[j], pb);
-#pragma unroll
-                for (int n = 0; n < NBT; ++n) {
-                    mma16816(c[n], pa[0], pb[0], pa[1], pb[1], xb[n][4 * j + 0], xb[n][4 * j + 1]);
-                    mma16816(c[n], pa[2], pb[2], pa[3], pb[3], xb[n][4 * j + 2], xb[n][4 * j + 3]);
-                }
-            }
-            const uint32_t sb0 = ssb[(size_t)(s * kRows + g) * (L.pitch_sb / 4) + gi];
-            const uint32_t sb1 = ssb[(size_t)(s * kRows + g + 8) * (L.pitch_sb / 4) + gi];
-            const float s0 = __half2float(__ushort_as_half((unsigned short)(sb0 & 0xFFFFu)));
-            const float b0 = __half2float(__ushort_as_half((unsigned short)(sb0 >> 16)));
-            const float s1 = __half2float(__ushort_as_half((unsigned short)(sb1 & 0xFFFFu)));
-            const float b1 = __half2float(__ushort_as_half((unsigned short)(sb1 >> 16)));
+    for (int q = 0; q < kQuarters; ++q) {
+        // Quarter q is complete once every thread has waited for its own copies of the first
+        // q+1 commit groups and the CTA has synchronised (which also publishes x and the scales).
+        if (q == 0) cp_async_wait<3>();
+        else if (q == 1) cp_async_wait<2>();
+        else if (q == 2) cp_async_wait<1>();
+        else cp_async_wait<0>();
+        __syncthreads();
+        const int g_hi = min((q + 1) * gq, gs);
+        for (int gi = min(q * gq, gs) + warp; gi < g_hi; gi += kWarps) {
+            // activation fragments for this group (rows of x = batch index g, g+8)
+            uint32_t xb[NBT][WPT * 4];
 #pragma unroll
             for (int n = 0; n < NBT; ++n) {
-                const float2 xs = *reinterpret_cast<const float2*>(sxsum + gi * NB + n * 8 + 2 * t);
-                acc[s][n][0] += s0 * c[n][0] + b0 * xs.x;
-                acc[s][n][1] += s0 * c[n][1] + b0 * xs.y;
-                acc[s][n][2] += s1 * c[n][2] + b1 * xs.x;
-                acc[s][n][3] += s1 * c[n][3] + b1 * xs.y;
+                const int b = n * 8 + g;
+                if (b < a.batch) {
+                    const uint8_t* px = sx + (size_t)b * L.pitch_x + (size_t)(gi * GROUP + t * (GROUP / 4)) * 2;
+#pragma unroll
+                    for (int j = 0; j < WPT; ++j) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(px + j * 16);
+                        xb[n][4 * j + 0] = v.x; xb[n][4 * j + 1] = v.y; xb[n][4 * j + 2] = v.z; xb[n][4 * j + 3] = v.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < WPT * 4; ++j) xb[n][j] = 0u;
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < NW; ++s) {
+                uint32_t wa[WPT], wb[WPT];
+                const uint8_t* pw = sw + (size_t)(s * kRows + g) * L.pitch_w + gi * (GROUP / 2) + t * (GROUP / 8);
+                WordLoad<WPT>::ld(pw, wa);
+                WordLoad<WPT>::ld(pw + 8 * (size_t)L.pitch_w, wb);
+                float c[NBT][4];
+#pragma unroll
+                for (int n = 0; n < NBT; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+#pragma unroll
+                for (int j = 0; j < WPT; ++j) {
+                    uint32_t pa[4], pb[4];
+                    dequant8(wa[j], pa);
+                    dequant8(wb[j], pb);
+#pragma unroll
+                    for (int n = 0; n < NBT; ++n) {
+                        mma16816(c[n], pa[0], pb[0], pa[1], pb[1], xb[n][4 * j + 0], xb[n][4 * j + 1]);
+                        mma16816(c[n], pa[2], pb[2], pa[3], pb[3], xb[n][4 * j + 2], xb[n][4 * j + 3]);
+                    }
+                }
+                const float2 f0 = ssb[(size_t)(s * kRows + g) * (L.pitch_sb / 8) + gi];      // {scale, bias}, row g
+                const float2 f1 = ssb[(size_t)(s * kRows + g + 8) * (L.pitch_sb / 8) + gi];  // row g+8
+#pragma unroll
+                for (int n = 0; n < NBT; ++n) {
+                    const float2 xs = *reinterpret_cast<const float2*>(sxsum + gi * NB + n * 8 + 2 * t);
+                    acc[s][n][0] += f0.x * c[n][0] + f0.y * xs.x;
+                    acc[s][n][1] += f0.x * c[n][1] + f0.y * xs.y;
+                    acc[s][n][2] += f1.x * c[n][2] + f1.y * xs.x;
+                    acc[s][n][3] += f1.x * c[n][3] + f1.y * xs.y;
+                }
             }
         }
     }
-    // A warp with no group in the last quarters still has to see every copy land.
-    while (waited < kBars - 1) {
-        ++waited;
-        if (!mbar_wait_bounded(&bars[waited], 0)) ok = false;
-    }
-    if (!ok && lane == 0 && a.err) atomicOr(a.err, KERR_BARRIER_TIMEOUT);
 
     // ── fixed-order reduction across the CTA's warps ──
     constexpr int VPT = NW * NBT * 4;  // values per thread
@@ -340,12 +354,24 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
         }
 }
 
+// Largest K-slice a CTA stages (columns).  Smaller slices mean smaller tiles, more resident
+// CTAs per SM and more of them per matrix; SMELT_AFFINE_KS overrides the default for tuning.
+int max_slice_cols() {
+    static int v = [] {
+        const char* e = getenv("SMELT_AFFINE_KS");
+        int n = e ? atoi(e) : 0;
+        return (n >= 64 && n <= 8192) ? n : 4096;
+    }();
+    return v;
+}
+
 template <int MODE, int GROUP, int NBT>
 cudaError_t launch_t(const Launch& l, AffineArgs a) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
     // K-slice: at most 4096 columns, an equal number of groups per slice where possible.
     const int groups = a.cols / GROUP;
-    int max_gs = 4096 / GROUP, nsplit = 1;
+    int max_gs = max_slice_cols() / GROUP, nsplit = 1;
+    if (max_gs < 1) max_gs = 1;
     SmemLayout L;
     for (;; max_gs /= 2) {
         if (max_gs == 0) return cudaErrorInvalidValue;

@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstring>
 #include <map>
+#include <vector>
 
 #include "runtime.h"
 
@@ -82,14 +83,16 @@ std::string shaped(const char* base, int cols, int rows, int group, bool batched
 
 }  // namespace
 
-extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d,
-                                                 const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
-                                                 smelt_dispatch_record* records, size_t* n_records) {
+static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
+                                       uint32_t capacity, uint32_t batch, smelt_dispatch_record* records,
+                                       size_t* n_records, std::vector<std::string>* names) {
     if (!d || !layers || !n_records) return SMELT_ERR_BAD_ARGUMENT;
     if (d->layers <= 0 || d->hidden <= 0 || d->inter <= 0 || d->n_q <= 0 || d->n_kv <= 0 || d->n_q % d->n_kv || d->head_dim <= 0 ||
         d->vocab <= 0 || batch == 0 || batch > 64 || capacity == 0 || d->layers > 100)
         return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: bad model description");
-    const bool dry = records == nullptr;
+    // With a null context nothing is allocated or registered: the call only writes (or counts)
+    // the records, which lets host-side tooling and CPU tests inspect the table.
+    const bool dry = ctx == nullptr;
     const int H = d->hidden, I = d->inter, D = d->head_dim, G = d->group, B = (int)batch;
     const int qd = d->n_q * D, kvd = d->n_kv * D, L = d->layers, V = d->vocab;
     const bool tp = d->tp_world > 1;
@@ -97,7 +100,7 @@ extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smel
     const bool bt = B > 1;  // batched kernel names bind actualBatch instead of numRows
 
     if (!dry) {
-        if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
+        if (!records) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: a context needs a record buffer (query the count with a null context)");
         if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
         if (kKvBase + 2 * L > (int)ctx->slots.size()) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: too many layers for the slot table");
         if (!ctx->slots[kWeights].ptr) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: upload the weights image to slot 30 first");
@@ -127,7 +130,7 @@ extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smel
         ctx->pipelines.clear();
     }
 
-    Emitter e{dry ? nullptr : ctx, records, dry ? 0 : *n_records};
+    Emitter e{ctx, records, records ? *n_records : 0};
     const float log2_theta = log2f(d->rope_theta);
     const float scale = 1.0f / sqrtf((float)D);
     auto matvec_name = [&](int cols, int rows) {
@@ -202,10 +205,35 @@ extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smel
     Rec(e, "argmax_key_reduce", 1, B).buf(0, kArgmaxScratch).buf(1, kArgmax).u32(2, parts);
 
     const size_t need = e.n;
-    if (!dry && need > *n_records) {
+    if (records && need > *n_records) {
         *n_records = need;
         return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: record buffer too small");
     }
     *n_records = need;
+    if (names) {
+        names->assign(e.pipes.size(), std::string());
+        for (auto& kv : e.pipes) (*names)[kv.second] = kv.first;
+    }
     return e.status;
+}
+
+extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d,
+                                                 const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
+                                                 smelt_dispatch_record* records, size_t* n_records) {
+    return build_decoder_impl(ctx, d, layers, capacity, batch, records, n_records, nullptr);
+}
+
+extern "C" smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_desc* d, uint32_t batch, char* out, size_t out_bytes,
+                                                     size_t* needed_bytes) {
+    if (!d || !needed_bytes) return SMELT_ERR_BAD_ARGUMENT;
+    std::vector<smelt_layer_ref> layers(d->layers > 0 && d->layers <= 100 ? d->layers : 1);
+    std::vector<std::string> names;
+    size_t n = 0;
+    smelt_status s = build_decoder_impl(nullptr, d, layers.data(), 1, batch, nullptr, &n, &names);
+    if (s) return s;
+    std::string joined;
+    for (size_t i = 0; i < names.size(); ++i) joined += names[i] + "\n";
+    *needed_bytes = joined.size() + 1;
+    if (out && out_bytes >= joined.size() + 1) memcpy(out, joined.c_str(), joined.size() + 1);
+    return SMELT_OK;
 }

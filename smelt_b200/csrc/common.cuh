@@ -132,6 +132,16 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                  : "memory");
 }
 
+// 16-byte asynchronous global -> shared copy that bypasses L1 (streamed weights are used once).
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Error word shared by all kernels of a context: 0 = ok; kernels OR in a code when a bounded
 // wait gives up so the host can report it instead of hanging.
 enum : uint32_t { KERR_BARRIER_TIMEOUT = 1u, KERR_FLAG_TIMEOUT = 2u };
