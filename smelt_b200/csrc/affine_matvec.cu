@@ -35,8 +35,6 @@ namespace smelt {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = 8;
 constexpr int kRows = 16;  // rows per CTA (one m16 tile)
 constexpr int kQuarters = 4;  // cp.async commit groups per weight tile
 
@@ -46,14 +44,14 @@ struct SmemLayout {
 };
 
 template <int GROUP>
-__host__ __device__ inline SmemLayout make_layout(int nw, int nb, int ks, int batch_rows) {
+__host__ __device__ inline SmemLayout make_layout(int nw, int nb, int ks, int batch_rows, int kWarps) {
     SmemLayout L;
     const int gs = ks / GROUP;
     L.pitch_w = (uint32_t)(ks / 2 + GROUP / 2);          // ≡ GROUP/2 (mod 128): conflict-free row stride
-    L.pitch_sb = (uint32_t)((gs | 1) * 8);               // odd number of fp32 {scale,bias} pairs per row
+    L.pitch_sb = (uint32_t)((gs | 1) * 4);               // odd number of fp16 {scale,bias} pairs per row
     L.pitch_x = (uint32_t)(ks * 2 + 16);                 // ≡ 16 (mod 128)
     uint32_t off = 0;
-    L.bars = off; off += 64;
+    L.bars = off; off += 256;  // a block of zeros (B operand of threads past the batch)
     L.w = off; off += (uint32_t)nw * kRows * L.pitch_w;
     off = (off + 15u) & ~15u;
     L.sb = off; off += (uint32_t)nw * kRows * L.pitch_sb;
@@ -62,7 +60,11 @@ __host__ __device__ inline SmemLayout make_layout(int nw, int nb, int ks, int ba
     off = (off + 15u) & ~15u;
     L.xsum = off; off += (uint32_t)gs * nb * 4;
     off = (off + 15u) & ~15u;
-    L.red = off; off += (uint32_t)kWarps * 32 * 4 * (nb / 8) * nw * 4;
+    L.red = L.w;  // the reduction buffer reuses the weight tile once every warp is done with it
+    {
+        const uint32_t red_bytes = (uint32_t)kWarps * 32 * 4 * (nb / 8) * nw * 4;
+        if (L.w + red_bytes > off) off = L.w + red_bytes;
+    }
     L.total = off;
     return L;
 }
@@ -106,8 +108,9 @@ struct WordLoad<4> {
     }
 };
 
-template <int MODE, int GROUP, int NBT>
-__global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a) {
+template <int MODE, int GROUP, int NBT, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) affine_mma_kernel(const AffineArgs a) {
+    constexpr int kThreads = kWarps * 32;
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
     constexpr int NB = NBT * 8;
     constexpr int WPT = GROUP / 32;  // packed words per thread per row per group
@@ -120,9 +123,10 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
     const int ks = min(a.ks, a.cols - k0);                  // columns in this slice
     const int gs = ks / GROUP;                              // groups in this slice
     const int groups_total = a.cols / GROUP;
-    const SmemLayout L = make_layout<GROUP>(NW, NB, a.ks, a.batch);
+    const SmemLayout L = make_layout<GROUP>(NW, NB, a.ks, a.batch, kWarps);
+    uint8_t* szero = smem + L.bars;
     uint8_t* sw = smem + L.w;
-    float2* ssb = reinterpret_cast<float2*>(smem + L.sb);
+    uint32_t* ssb = reinterpret_cast<uint32_t*>(smem + L.sb);
     uint8_t* sx = smem + L.xs;
     float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
     float* sred = reinterpret_cast<float*>(smem + L.red);
@@ -144,8 +148,8 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
         }
         cp_async_commit();
     }
-    // {scale, bias} of every (row, group) of the slice as fp32 pairs, so the main loop reads
-    // one 64-bit word per row and converts nothing.
+    // {scale, bias} of every (row, group) of the slice as fp16 pairs: one 32-bit read per row in
+    // the main loop.
     {
         const bool vec = ((groups_total * 2) % 16 == 0) && ((k0 / GROUP * 2) % 16 == 0) && (gs % 8 == 0) &&
                          ((reinterpret_cast<uintptr_t>(a.s[0]) | reinterpret_cast<uintptr_t>(a.b[0]) |
@@ -153,7 +157,7 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
 #pragma unroll
         for (int rr = warp; rr < NW * kRows; rr += kWarps) {
             const int set = rr / kRows, r = rr % kRows;
-            float2* dst = ssb + (size_t)rr * (L.pitch_sb / 8);
+            uint32_t* dst = ssb + (size_t)rr * (L.pitch_sb / 4);
             const bool valid = row0 + r < a.rows;
             const size_t base = (size_t)(row0 + r) * groups_total + k0 / GROUP;
             if (vec) {
@@ -166,14 +170,13 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
                     const uint32_t sw4[4] = {sv.x, sv.y, sv.z, sv.w}, bw4[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float2 sf = __half22float2(u32_as_h2(sw4[j])), bf = __half22float2(u32_as_h2(bw4[j]));
-                        dst[c * 8 + 2 * j] = make_float2(sf.x, bf.x);
-                        dst[c * 8 + 2 * j + 1] = make_float2(sf.y, bf.y);
+                        dst[c * 8 + 2 * j] = __byte_perm(sw4[j], bw4[j], 0x5410);      // {scale, bias} of group 2j
+                        dst[c * 8 + 2 * j + 1] = __byte_perm(sw4[j], bw4[j], 0x7632);  // group 2j+1
                     }
                 }
             } else {
                 for (int gi = lane; gi < gs; gi += 32)
-                    dst[gi] = valid ? make_float2(__half2float(a.s[set][base + gi]), __half2float(a.b[set][base + gi])) : make_float2(0.f, 0.f);
+                    dst[gi] = valid ? ((uint32_t)__half_as_ushort(a.s[set][base + gi]) | ((uint32_t)__half_as_ushort(a.b[set][base + gi]) << 16)) : 0u;
             }
         }
     }
@@ -214,6 +217,7 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
         }
         for (int i = tid; i < gs * NB; i += kThreads)
             if ((i % NB) >= a.batch) sxsum[i] = 0.f;
+        if (tid < GROUP / 8) reinterpret_cast<uint4*>(szero)[tid] = make_uint4(0, 0, 0, 0);  // read by threads past the batch
     }
 
     // ── main loop: this warp's groups, quarter by quarter ──
@@ -225,6 +229,27 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[s][n][i] = 0.f;
 
+    // Per-thread base pointers; inside the loop everything advances by compile-time strides.
+    const uint8_t* pw_base[NW];
+    const uint32_t* psb_base[NW];
+#pragma unroll
+    for (int s = 0; s < NW; ++s) {
+        pw_base[s] = sw + (size_t)(s * kRows + g) * L.pitch_w + t * (GROUP / 8);
+        psb_base[s] = ssb + (size_t)(s * kRows + g) * (L.pitch_sb / 4);
+    }
+    const size_t w_row8 = 8 * (size_t)L.pitch_w;        // rows g -> g+8
+    const size_t sb_row8 = 8 * (size_t)(L.pitch_sb / 4);
+    // Batch rows this thread feeds as the B operand; threads past the batch read a row of zeros.
+    const uint8_t* px_base[NBT];
+    int px_stride[NBT];
+#pragma unroll
+    for (int n = 0; n < NBT; ++n) {
+        const int b = n * 8 + g;
+        px_base[n] = b < a.batch ? sx + (size_t)b * L.pitch_x + t * (GROUP / 2) : szero;
+        px_stride[n] = b < a.batch ? GROUP * 2 : 0;
+    }
+    const float* pxs_base = sxsum + 2 * t;
+
     for (int q = 0; q < kQuarters; ++q) {
         // Quarter q is complete once every thread has waited for its own copies of the first
         // q+1 commit groups and the CTA has synchronised (which also publishes x and the scales).
@@ -234,33 +259,30 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
         else cp_async_wait<0>();
         __syncthreads();
         const int g_hi = min((q + 1) * gq, gs);
+#pragma unroll 1
         for (int gi = min(q * gq, gs) + warp; gi < g_hi; gi += kWarps) {
-            // activation fragments for this group (rows of x = batch index g, g+8)
             uint32_t xb[NBT][WPT * 4];
 #pragma unroll
             for (int n = 0; n < NBT; ++n) {
-                const int b = n * 8 + g;
-                if (b < a.batch) {
-                    const uint8_t* px = sx + (size_t)b * L.pitch_x + (size_t)(gi * GROUP + t * (GROUP / 4)) * 2;
+                const uint8_t* px = px_base[n] + gi * px_stride[n];
 #pragma unroll
-                    for (int j = 0; j < WPT; ++j) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(px + j * 16);
-                        xb[n][4 * j + 0] = v.x; xb[n][4 * j + 1] = v.y; xb[n][4 * j + 2] = v.z; xb[n][4 * j + 3] = v.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < WPT * 4; ++j) xb[n][j] = 0u;
+                for (int j = 0; j < WPT; ++j) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(px + j * 16);
+                    xb[n][4 * j + 0] = v.x; xb[n][4 * j + 1] = v.y; xb[n][4 * j + 2] = v.z; xb[n][4 * j + 3] = v.w;
                 }
             }
+            float2 xs[NBT];
+#pragma unroll
+            for (int n = 0; n < NBT; ++n) xs[n] = *reinterpret_cast<const float2*>(pxs_base + gi * NB + n * 8);
 #pragma unroll
             for (int s = 0; s < NW; ++s) {
                 uint32_t wa[WPT], wb[WPT];
-                const uint8_t* pw = sw + (size_t)(s * kRows + g) * L.pitch_w + gi * (GROUP / 2) + t * (GROUP / 8);
+                const uint8_t* pw = pw_base[s] + (size_t)gi * (GROUP / 2);
                 WordLoad<WPT>::ld(pw, wa);
-                WordLoad<WPT>::ld(pw + 8 * (size_t)L.pitch_w, wb);
+                WordLoad<WPT>::ld(pw + w_row8, wb);
+                const float2 f0 = __half22float2(u32_as_h2(psb_base[s][gi]));            // {scale, bias}, row g
+                const float2 f1 = __half22float2(u32_as_h2(psb_base[s][gi + sb_row8]));  // row g+8
                 float c[NBT][4];
-#pragma unroll
-                for (int n = 0; n < NBT; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
 #pragma unroll
                 for (int j = 0; j < WPT; ++j) {
                     uint32_t pa[4], pb[4];
@@ -268,19 +290,17 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
                     dequant8(wb[j], pb);
 #pragma unroll
                     for (int n = 0; n < NBT; ++n) {
-                        mma16816(c[n], pa[0], pb[0], pa[1], pb[1], xb[n][4 * j + 0], xb[n][4 * j + 1]);
+                        if (j == 0) mma16816_zero(c[n], pa[0], pb[0], pa[1], pb[1], xb[n][0], xb[n][1]);
+                        else mma16816(c[n], pa[0], pb[0], pa[1], pb[1], xb[n][4 * j + 0], xb[n][4 * j + 1]);
                         mma16816(c[n], pa[2], pb[2], pa[3], pb[3], xb[n][4 * j + 2], xb[n][4 * j + 3]);
                     }
                 }
-                const float2 f0 = ssb[(size_t)(s * kRows + g) * (L.pitch_sb / 8) + gi];      // {scale, bias}, row g
-                const float2 f1 = ssb[(size_t)(s * kRows + g + 8) * (L.pitch_sb / 8) + gi];  // row g+8
 #pragma unroll
                 for (int n = 0; n < NBT; ++n) {
-                    const float2 xs = *reinterpret_cast<const float2*>(sxsum + gi * NB + n * 8 + 2 * t);
-                    acc[s][n][0] += f0.x * c[n][0] + f0.y * xs.x;
-                    acc[s][n][1] += f0.x * c[n][1] + f0.y * xs.y;
-                    acc[s][n][2] += f1.x * c[n][2] + f1.y * xs.x;
-                    acc[s][n][3] += f1.x * c[n][3] + f1.y * xs.y;
+                    acc[s][n][0] = fmaf(f0.x, c[n][0], acc[s][n][0]); acc[s][n][0] = fmaf(f0.y, xs[n].x, acc[s][n][0]);
+                    acc[s][n][1] = fmaf(f0.x, c[n][1], acc[s][n][1]); acc[s][n][1] = fmaf(f0.y, xs[n].y, acc[s][n][1]);
+                    acc[s][n][2] = fmaf(f1.x, c[n][2], acc[s][n][2]); acc[s][n][2] = fmaf(f1.y, xs[n].x, acc[s][n][2]);
+                    acc[s][n][3] = fmaf(f1.x, c[n][3], acc[s][n][3]); acc[s][n][3] = fmaf(f1.y, xs[n].y, acc[s][n][3]);
                 }
             }
         }
@@ -288,6 +308,7 @@ __global__ void __launch_bounds__(kThreads) affine_mma_kernel(const AffineArgs a
 
     // ── fixed-order reduction across the CTA's warps ──
     constexpr int VPT = NW * NBT * 4;  // values per thread
+    __syncthreads();  // sred aliases the weight tile: wait until no warp reads weights any more
     {
         float* dst = sred + (size_t)(warp * 32 + lane) * VPT;
 #pragma unroll
@@ -365,10 +386,11 @@ int max_slice_cols() {
     return v;
 }
 
-template <int MODE, int GROUP, int NBT>
+template <int MODE, int GROUP, int NBT, int WARPS>
 cudaError_t launch_t(const Launch& l, AffineArgs a) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    // K-slice: at most 4096 columns, an equal number of groups per slice where possible.
+    // K-slice: an equal number of groups per slice, at most max_slice_cols() columns, shrunk
+    // further until the tile fits in shared memory.
     const int groups = a.cols / GROUP;
     int max_gs = max_slice_cols() / GROUP, nsplit = 1;
     if (max_gs < 1) max_gs = 1;
@@ -380,17 +402,17 @@ cudaError_t launch_t(const Launch& l, AffineArgs a) {
         const int gs = (groups + nsplit - 1) / nsplit;
         nsplit = (groups + gs - 1) / gs;
         a.ks = gs * GROUP;
-        L = make_layout<GROUP>(NW, NBT * 8, a.ks, a.batch);
+        L = make_layout<GROUP>(NW, NBT * 8, a.ks, a.batch, WARPS);
         if (L.total <= 200u * 1024u) break;
     }
     a.nsplit = nsplit;
     a.dyn = dev_dyn(l);
-    auto kern = affine_mma_kernel<MODE, GROUP, NBT>;
+    auto kern = affine_mma_kernel<MODE, GROUP, NBT, WARPS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((a.rows + kRows - 1) / kRows, nsplit, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(WARPS * 32, 1, 1);
     cfg.dynamicSmemBytes = L.total;
     cfg.stream = l.stream;
     cudaLaunchAttribute attr[2];
@@ -412,10 +434,19 @@ cudaError_t launch_t(const Launch& l, AffineArgs a) {
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
+// Warps per CTA: 16 by default; SMELT_AFFINE_WARPS=8 selects the 8-warp build for tuning.
+int warps_per_cta() {
+    static int v = [] {
+        const char* e = getenv("SMELT_AFFINE_WARPS");
+        return (e && atoi(e) == 8) ? 8 : 16;
+    }();
+    return v;
+}
+
 template <int MODE, int GROUP>
 cudaError_t launch_nb(const Launch& l, const AffineArgs& a) {
-    if (a.batch <= 8) return launch_t<MODE, GROUP, 1>(l, a);
-    if (a.batch <= 16) return launch_t<MODE, GROUP, 2>(l, a);
+    if (a.batch <= 8) return warps_per_cta() == 8 ? launch_t<MODE, GROUP, 1, 8>(l, a) : launch_t<MODE, GROUP, 1, 16>(l, a);
+    if (a.batch <= 16) return launch_t<MODE, GROUP, 2, 8>(l, a);
     return cudaErrorInvalidValue;
 }
 
