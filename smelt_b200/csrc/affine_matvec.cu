@@ -478,6 +478,11 @@ cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int
         }
         return cudaSuccess;
     }
+    {
+        bool handled = false;
+        cudaError_t e = launch_affine_stream(l, mode, args, group, &handled);
+        if (handled || e != cudaSuccess) return e;
+    }
     switch (mode) {
         case kAffinePlain: return launch_group<kAffinePlain>(l, args, group);
         case kAffineAdd: return launch_group<kAffineAdd>(l, args, group);

@@ -21,10 +21,12 @@ struct AffineArgs {
     const __half* residual;  // add mode: [batch, rows]; may alias y
     int rows, cols, batch;
     int ks, nsplit;        // filled by the launcher
+    int sm_count;          // SMs of the device (0 = assume 148)
     uint32_t* err;         // device error word (may be null)
     DevDyn dyn;            // filled by the launcher
 };
 
 cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int group);
+cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
 
 }  // namespace smelt

@@ -1,0 +1,323 @@
+// Streaming (persistent, multistage) form of the group-64 affine u4 matvec for batch <= 8.
+//
+// Same arithmetic and the same reference kernels as affine_matvec.cu
+// (Resources/Shaders/lut_matvec.metal:1157-1287, :1718-1817, :2152-2233, :1824-1908); what
+// changes is how the weight stream is organised, because at B200 bandwidth the per-tile fixed
+// work of the one-tile-per-CTA kernel (activation staging, barriers, load/compute phases that
+// line up across the CTAs of an SM) costs more than the arithmetic.
+//
+// A persistent CTA of eight warps walks 32-row tiles (tile index = blockIdx.x + i * gridDim.x).
+// The packed weights, scales and biases of a tile arrive as a continuous sequence of stages of
+// 512 columns through a ring of cp.async buffers (16-byte copies, 256 contiguous bytes per
+// row); the ring keeps running across tile boundaries, so HBM requests are always in flight
+// while the tensor pipe works on the oldest stage.  The activations are staged once per CTA
+// (permuted for the MMA operand order, with their per-group sums), not once per tile.  Warp
+// (wm, wk) owns the 16 rows of m-tile wm and groups 2wk, 2wk+1 of every stage; its fp32 row
+// sums live in registers for the whole K loop and the four K-partials of a tile are added in
+// a fixed order through shared memory, so results are bit-reproducible.  The first stages are
+// requested before the programmatic-dependent-launch wait: weight traffic overlaps the tail
+// of the kernel that produces x.
+#include <cstdlib>
+
+#include "affine_matvec.h"
+
+namespace smelt {
+
+namespace {
+
+constexpr int kGroup = 64;
+constexpr int kTileRows = 32;
+constexpr int kStageCols = 512;                       // 8 groups
+constexpr int kThreads = 256;
+constexpr int kRowBytes = kStageCols / 2;             // 256 packed bytes per row per stage
+constexpr int kPitchW = kRowBytes + 32;               // ≡ 32 (mod 128): conflict-free LDS.64 across rows
+constexpr int kSetW = kTileRows * kPitchW;            // 9216
+constexpr int kSetS = kTileRows * 16;                 // 8 fp16 scales per row
+constexpr int kSetBytes = kSetW + 2 * kSetS;          // 10240: [W | scales | biases]
+
+struct StreamLayout {
+    uint32_t zero, ring, xs, xsum, red, total, pitch_x, stage_bytes;
+};
+
+__host__ __device__ inline StreamLayout stream_layout(int nw, int stages, int cols, int batch) {
+    StreamLayout L;
+    L.stage_bytes = (uint32_t)nw * kSetBytes;
+    L.pitch_x = (uint32_t)cols * 2 + 16;              // ≡ 16 (mod 128)
+    uint32_t off = 0;
+    L.zero = off; off += 256;
+    L.ring = off; off += (uint32_t)stages * L.stage_bytes;
+    L.xs = off; off += (uint32_t)batch * L.pitch_x;
+    off = (off + 15u) & ~15u;
+    L.xsum = off; off += (uint32_t)(cols / kGroup) * 8 * 4;
+    L.red = off; off += 2u * 4u * 32u * (uint32_t)(4 * nw) * 4u;
+    L.total = off;
+    return L;
+}
+
+__device__ __forceinline__ void dequant8s(uint32_t w, uint32_t p[4]) {
+    const uint32_t kMagic = 0x64006400u;              // half2(1024, 1024)
+    const __half2 k1024 = u32_as_h2(0x64006400u);
+    const __half2 k16th = u32_as_h2(0x2C002C00u);     // half2(1/16)
+    const __half2 km64 = u32_as_h2(0xD400D400u);      // half2(-64)
+    const uint32_t lo = lop3_and_or(w, 0x000F000Fu, kMagic);
+    const uint32_t hi = lop3_and_or(w, 0x00F000F0u, kMagic);
+    const uint32_t w2 = w >> 8;
+    const uint32_t lo2 = lop3_and_or(w2, 0x000F000Fu, kMagic);
+    const uint32_t hi2 = lop3_and_or(w2, 0x00F000F0u, kMagic);
+    p[0] = h2_as_u32(__hsub2(u32_as_h2(lo), k1024));          // {n0, n4}
+    p[1] = h2_as_u32(__hfma2(u32_as_h2(hi), k16th, km64));    // {n1, n5}
+    p[2] = h2_as_u32(__hsub2(u32_as_h2(lo2), k1024));         // {n2, n6}
+    p[3] = h2_as_u32(__hfma2(u32_as_h2(hi2), k16th, km64));   // {n3, n7}
+}
+
+template <int MODE, int STAGES>
+__global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const AffineArgs a) {
+    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int wm = warp >> 2, wk = warp & 3;
+    const StreamLayout L = stream_layout(NW, STAGES, a.cols, a.batch);
+    uint8_t* ring = smem + L.ring;
+    uint8_t* sx = smem + L.xs;
+    float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
+    float* sred = reinterpret_cast<float*>(smem + L.red);
+
+    const int tiles_total = (a.rows + kTileRows - 1) / kTileRows;
+    const int spt = a.cols / kStageCols;  // stages per tile
+    const int my_tiles = blockIdx.x < tiles_total ? (tiles_total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int total_stages = my_tiles * spt;
+    const int groups_total = a.cols / kGroup;
+
+    // ── producer side: every thread copies a fixed part of each stage ──
+    const int ld_chunk = tid & 15, ld_row = tid >> 4;  // rows ld_row and ld_row + 16, 16-byte chunk ld_chunk
+    int f_tile = blockIdx.x, f_ks = 0, f_n = 0;        // next stage to request
+    auto fetch = [&]() {
+        if (f_n < total_stages) {
+            uint8_t* st = ring + (size_t)(f_n % STAGES) * L.stage_bytes;
+            const int row0 = f_tile * kTileRows;
+#pragma unroll
+            for (int s = 0; s < NW; ++s) {
+                uint8_t* dst = st + s * kSetBytes;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int r = ld_row + 16 * h;
+                    if (row0 + r < a.rows)
+                        cp_async16(dst + r * kPitchW + ld_chunk * 16,
+                                   a.w[s] + (size_t)(row0 + r) * (a.cols / 2) + (size_t)f_ks * kRowBytes + ld_chunk * 16);
+                }
+                if (warp < 2 && row0 + lane < a.rows) {  // warp 0: scales, warp 1: biases; one 16-byte chunk per row
+                    const __half* src = (warp == 0 ? a.s[s] : a.b[s]) + (size_t)(row0 + lane) * groups_total + f_ks * 8;
+                    cp_async16(dst + kSetW + warp * kSetS + lane * 16, src);
+                }
+            }
+            ++f_n;
+            if (++f_ks == spt) { f_ks = 0; f_tile += gridDim.x; }
+        }
+        cp_async_commit();  // always commit so that group counting stays uniform
+    };
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) fetch();
+
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(a.dyn)) {
+        cp_async_wait<0>();  // copies in flight must land before the CTA's shared memory retires
+        return;
+    }
+
+    // ── activations: permuted copy into shared memory + per-group sums, once per CTA ──
+    {
+        const int chunks = a.cols / 8;
+        for (int b = 0; b < a.batch; ++b) {
+            const __half* xr = a.x + (size_t)b * a.cols;
+            uint8_t* xd = sx + (size_t)b * L.pitch_x;
+            for (int base = 0; base < chunks; base += kThreads) {
+                const int c8 = base + tid;
+                float sum = 0.f;
+                if (c8 < chunks) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                    const float2 f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
+                    const float2 f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
+                    sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+                    uint4 o;  // x0 x4 | x1 x5 | x2 x6 | x3 x7
+                    o.x = __byte_perm(v.x, v.z, 0x5410);
+                    o.y = __byte_perm(v.x, v.z, 0x7632);
+                    o.z = __byte_perm(v.y, v.w, 0x5410);
+                    o.w = __byte_perm(v.y, v.w, 0x7632);
+                    *reinterpret_cast<uint4*>(xd + c8 * 16) = o;
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                if (c8 < chunks && (c8 & 7) == 0) sxsum[(c8 >> 3) * 8 + b] = sum;
+            }
+        }
+        for (int i = tid; i < groups_total * 8; i += kThreads)
+            if ((i & 7) >= a.batch) sxsum[i] = 0.f;
+        if (tid < 16) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
+    }
+
+    // ── consumer side ──
+    // B operand: batch row g of x, or a block of zeros for threads past the batch.
+    const uint8_t* px_base = g < a.batch ? sx + (size_t)g * L.pitch_x + t * 32 : smem + L.zero;
+    const int px_stride = g < a.batch ? kGroup * 2 : 0;
+    const float* pxs_base = sxsum + 2 * t;
+    const int w_off = (wm * 16 + g) * kPitchW + wk * 64 + t * 8;  // this thread's first word in a set's W block
+    const int s_off = kSetW + (wm * 16 + g) * 16 + wk * 4;         // its {scale g0, scale g1} word; biases kSetS later
+
+    float acc[NW][4];
+#pragma unroll
+    for (int s = 0; s < NW; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
+
+    int c_tile = blockIdx.x, c_ks = 0;
+    for (int n = 0; n < total_stages; ++n) {
+        cp_async_wait<STAGES - 2>();  // this thread's copies of stage n have landed
+        __syncthreads();              // ... everyone's have, and everyone is done with stage n-1
+        fetch();                      // refill the buffer stage n-1 used
+        const uint8_t* st = ring + (size_t)(n % STAGES) * L.stage_bytes;
+#pragma unroll
+        for (int gg = 0; gg < 2; ++gg) {
+            const int gi = c_ks * 8 + wk * 2 + gg;  // group index within the row
+            const uint8_t* px = px_base + gi * px_stride;
+            const uint4 x0 = *reinterpret_cast<const uint4*>(px), x1 = *reinterpret_cast<const uint4*>(px + 16);
+            const float2 xs = *reinterpret_cast<const float2*>(pxs_base + gi * 8);
+#pragma unroll
+            for (int s = 0; s < NW; ++s) {
+                const uint8_t* base = st + s * kSetBytes;
+                const uint2 wa = *reinterpret_cast<const uint2*>(base + w_off + gg * 32);
+                const uint2 wb = *reinterpret_cast<const uint2*>(base + w_off + gg * 32 + 8 * kPitchW);
+                uint32_t pa[4], pb[4];
+                float c[4];
+                dequant8s(wa.x, pa); dequant8s(wb.x, pb);
+                mma16816_zero(c, pa[0], pb[0], pa[1], pb[1], x0.x, x0.y);
+                mma16816(c, pa[2], pb[2], pa[3], pb[3], x0.z, x0.w);
+                dequant8s(wa.y, pa); dequant8s(wb.y, pb);
+                mma16816(c, pa[0], pb[0], pa[1], pb[1], x1.x, x1.y);
+                mma16816(c, pa[2], pb[2], pa[3], pb[3], x1.z, x1.w);
+                const float2 sa = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off)));
+                const float2 ba = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off + kSetS)));
+                const float2 sb = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off + 8 * 16)));
+                const float2 bb = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off + kSetS + 8 * 16)));
+                const float s0 = gg ? sa.y : sa.x, b0 = gg ? ba.y : ba.x, s1 = gg ? sb.y : sb.x, b1 = gg ? bb.y : bb.x;
+                acc[s][0] = fmaf(s0, c[0], acc[s][0]); acc[s][0] = fmaf(b0, xs.x, acc[s][0]);
+                acc[s][1] = fmaf(s0, c[1], acc[s][1]); acc[s][1] = fmaf(b0, xs.y, acc[s][1]);
+                acc[s][2] = fmaf(s1, c[2], acc[s][2]); acc[s][2] = fmaf(b1, xs.x, acc[s][2]);
+                acc[s][3] = fmaf(s1, c[3], acc[s][3]); acc[s][3] = fmaf(b1, xs.y, acc[s][3]);
+            }
+        }
+        if (++c_ks == spt) {
+            // ── tile done: add the four K-partials of each m-tile in a fixed order, write out ──
+            float* dst = sred + (size_t)((wm * 4 + wk) * 32 + lane) * (4 * NW);
+#pragma unroll
+            for (int s = 0; s < NW; ++s)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { dst[s * 4 + i] = acc[s][i]; acc[s][i] = 0.f; }
+            __syncthreads();
+            if (wk == 0) {
+                float tot[NW][4];
+#pragma unroll
+                for (int s = 0; s < NW; ++s)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) v += sred[(size_t)((wm * 4 + k) * 32 + lane) * (4 * NW) + s * 4 + i];
+                        tot[s][i] = v;
+                    }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = c_tile * kTileRows + wm * 16 + g + (i >> 1) * 8;
+                    const int b = 2 * t + (i & 1);
+                    if (row >= a.rows || b >= a.batch) continue;
+                    const size_t o = (size_t)b * a.rows + row;
+                    const float v0 = tot[0][i];
+                    if (MODE == kAffinePlain) a.y[o] = __float2half_rn(v0);
+                    else if (MODE == kAffineAdd) a.y[o] = __hadd(__float2half_rn(v0), a.residual[o]);  // lut_matvec.metal:1802-1803
+                    else if (MODE == kAffineGateUp) a.y[o] = __float2half_rn(v0 / (1.0f + expf(-v0)) * tot[NW - 1][i]);  // :2228
+                    else { a.y[o] = __float2half_rn(v0); a.y2[o] = __float2half_rn(tot[NW - 1][i]); }
+                }
+            }
+            c_ks = 0;
+            c_tile += gridDim.x;
+        }
+    }
+    cp_async_wait<0>();
+}
+
+int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+template <int MODE, int STAGES>
+cudaError_t launch_stream_t(const Launch& l, AffineArgs a, int ctas_per_sm) {
+    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    const StreamLayout L = stream_layout(NW, STAGES, a.cols, a.batch);
+    a.dyn = dev_dyn(l);
+    auto kern = affine_stream_kernel<MODE, STAGES>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
+    if (e != cudaSuccess) return e;
+    const int tiles = (a.rows + kTileRows - 1) / kTileRows;
+    const int sm = a.sm_count > 0 ? a.sm_count : 148;
+    int grid = sm * ctas_per_sm;
+    if (grid > tiles) grid = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L.total;
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = l.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
+template <int MODE>
+cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handled) {
+    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    // Ring depth: as deep as leaves room for two CTAs per SM (about 113 KB each).
+    static const int forced = env_int("SMELT_AFFINE_STAGES", 0);
+    const uint32_t budget2 = 113u * 1024u, budget1 = 226u * 1024u;
+    const int pref = forced ? forced : (NW == 2 ? 4 : 6);
+    const int order[3] = {pref, 4, 3};
+    for (int i = 0; i < 3; ++i) {
+        const int st = order[i];
+        if (st != 3 && st != 4 && st != 6) continue;
+        const uint32_t total = stream_layout(NW, st, a.cols, a.batch).total;
+        if (total > budget1) continue;
+        const int per_sm = total <= budget2 ? 2 : 1;
+        *handled = true;
+        if (st == 6) return launch_stream_t<MODE, 6>(l, a, per_sm);
+        if (st == 4) return launch_stream_t<MODE, 4>(l, a, per_sm);
+        return launch_stream_t<MODE, 3>(l, a, per_sm);
+    }
+    *handled = false;
+    return cudaSuccess;
+}
+
+}  // namespace
+
+// Launches the streaming kernel when the shape is eligible (group 64, batch <= 8, cols a
+// multiple of 512, 16-byte aligned operands, activations small enough to stay resident);
+// *handled tells the caller whether it did.
+cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& a, int group, bool* handled) {
+    *handled = false;
+    static const int disabled = env_int("SMELT_AFFINE_NO_STREAM", 0);
+    if (disabled || group != kGroup || a.batch > 8 || a.cols % kStageCols != 0) return cudaSuccess;
+    const int nw = (mode == kAffineGateUp || mode == kAffineDual) ? 2 : 1;
+    for (int s = 0; s < nw; ++s)
+        if ((reinterpret_cast<uintptr_t>(a.w[s]) | reinterpret_cast<uintptr_t>(a.s[s]) | reinterpret_cast<uintptr_t>(a.b[s])) & 15u) return cudaSuccess;
+    if (reinterpret_cast<uintptr_t>(a.x) & 15u) return cudaSuccess;
+    switch (mode) {
+        case kAffinePlain: return launch_stream_mode<kAffinePlain>(l, a, handled);
+        case kAffineAdd: return launch_stream_mode<kAffineAdd>(l, a, handled);
+        case kAffineGateUp: return launch_stream_mode<kAffineGateUp>(l, a, handled);
+        case kAffineDual: return launch_stream_mode<kAffineDual>(l, a, handled);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace smelt

@@ -302,7 +302,7 @@ smelt_status run_affine(Interp& in, const Pipeline& p, const smelt_dispatch_reco
     a.x = (const __half*)r.buf[ix].ptr; a.y = (__half*)r.buf[iy].ptr;
     if (iy2 >= 0) { NEED_BUF(iy2); NEED_BYTES(iy2, (size_t)batch * rows * 2); a.y2 = (__half*)r.buf[iy2].ptr; }
     if (ires >= 0) { NEED_BUF(ires); NEED_BYTES(ires, (size_t)batch * rows * 2); a.residual = (const __half*)r.buf[ires].ptr; }
-    a.rows = rows; a.cols = p.cols; a.batch = batch; a.err = ctx->err_dev;
+    a.rows = rows; a.cols = p.cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
     const int mode = p.kind == PK_AFFINE_MATVEC ? kAffinePlain : p.kind == PK_AFFINE_ADD ? kAffineAdd : p.kind == PK_AFFINE_GATEUP ? kAffineGateUp : kAffineDual;
     in.launches += (batch + 15) / 16;
     return check_cuda(ctx, launch_affine(make_launch(in, r), mode, a, p.group), p.name.c_str());

@@ -303,7 +303,7 @@ static smelt_status affine_common(smelt_cuda_ctx* ctx, int mode, const void* w0,
     a.w[0] = (const uint8_t*)w0; a.s[0] = (const __half*)s0; a.b[0] = (const __half*)b0;
     a.w[1] = (const uint8_t*)w1; a.s[1] = (const __half*)s1; a.b[1] = (const __half*)b1;
     a.x = (const __half*)x; a.y = (__half*)y; a.y2 = (__half*)y2; a.residual = (const __half*)residual;
-    a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev;
+    a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
     return check_cuda(ctx, launch_affine(typed_launch(ctx), mode, a, group), "affine matvec launch");
 }
 
