@@ -6,15 +6,15 @@
 // work of the one-tile-per-CTA kernel (activation staging, barriers, load/compute phases that
 // line up across the CTAs of an SM) costs more than the arithmetic.
 //
-// A persistent CTA of eight warps walks 32-row tiles (tile index = blockIdx.x + i * gridDim.x).
+// A persistent CTA of eight warps walks 16-row tiles (tile index = blockIdx.x + i * gridDim.x).
 // The packed weights, scales and biases of a tile arrive as a continuous sequence of stages of
-// 512 columns through a ring of cp.async buffers (16-byte copies, 256 contiguous bytes per
+// 1024 columns through a ring of cp.async buffers (16-byte copies, 512 contiguous bytes per
 // row); the ring keeps running across tile boundaries, so HBM requests are always in flight
 // while the tensor pipe works on the oldest stage.  The activations are staged once per CTA
 // (permuted for the MMA operand order, with their per-group sums), not once per tile.  Warp
-// (wm, wk) owns the 16 rows of m-tile wm and groups 2wk, 2wk+1 of every stage; its fp32 row
-// sums live in registers for the whole K loop and the four K-partials of a tile are added in
-// a fixed order through shared memory, so results are bit-reproducible.  The first stages are
+// wk owns groups 2wk, 2wk+1 of every stage; its fp32 row sums live in registers for the whole
+// K loop and the eight K-partials of a tile are added in a fixed order through shared memory,
+// so results are bit-reproducible.  The first stages are
 // requested before the programmatic-dependent-launch wait: weight traffic overlaps the tail
 // of the kernel that produces x.
 #include <cstdlib>
@@ -26,14 +26,14 @@ namespace smelt {
 namespace {
 
 constexpr int kGroup = 64;
-constexpr int kTileRows = 32;
-constexpr int kStageCols = 512;                       // 8 groups
+constexpr int kTileRows = 16;
+constexpr int kStageCols = 1024;                      // 16 groups, two per warp
 constexpr int kThreads = 256;
-constexpr int kRowBytes = kStageCols / 2;             // 256 packed bytes per row per stage
+constexpr int kRowBytes = kStageCols / 2;             // 512 packed bytes per row per stage
 constexpr int kPitchW = kRowBytes + 32;               // ≡ 32 (mod 128): conflict-free LDS.64 across rows
-constexpr int kSetW = kTileRows * kPitchW;            // 9216
-constexpr int kSetS = kTileRows * 16;                 // 8 fp16 scales per row
-constexpr int kSetBytes = kSetW + 2 * kSetS;          // 10240: [W | scales | biases]
+constexpr int kSetW = kTileRows * kPitchW;            // 8704
+constexpr int kSetS = kTileRows * 32;                 // 16 fp16 scales per row
+constexpr int kSetBytes = kSetW + 2 * kSetS;          // 9728: [W | scales | biases]
 
 struct StreamLayout {
     uint32_t zero, ring, xs, xsum, red, total, pitch_x, stage_bytes;
@@ -49,7 +49,7 @@ __host__ __device__ inline StreamLayout stream_layout(int nw, int stages, int co
     L.xs = off; off += (uint32_t)batch * L.pitch_x;
     off = (off + 15u) & ~15u;
     L.xsum = off; off += (uint32_t)(cols / kGroup) * 8 * 4;
-    L.red = off; off += 2u * 4u * 32u * (uint32_t)(4 * nw) * 4u;
+    L.red = off; off += 8u * 32u * (uint32_t)(4 * nw) * 4u;
     L.total = off;
     return L;
 }
@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int wm = warp >> 2, wk = warp & 3;
+    const int wk = warp;  // this warp's share of every stage: groups 2wk, 2wk+1
     const StreamLayout L = stream_layout(NW, STAGES, a.cols, a.batch);
     uint8_t* ring = smem + L.ring;
     uint8_t* sx = smem + L.xs;
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
     const int groups_total = a.cols / kGroup;
 
     // ── producer side: every thread copies a fixed part of each stage ──
-    const int ld_chunk = tid & 15, ld_row = tid >> 4;  // rows ld_row and ld_row + 16, 16-byte chunk ld_chunk
+    const int ld_chunk = tid & 31, ld_row = tid >> 5;  // rows ld_row and ld_row + 8, 16-byte chunk ld_chunk
     int f_tile = blockIdx.x, f_ks = 0, f_n = 0;        // next stage to request
     auto fetch = [&]() {
         if (f_n < total_stages) {
@@ -101,13 +101,13 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
                 uint8_t* dst = st + s * kSetBytes;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int r = ld_row + 16 * h;
+                    const int r = ld_row + 8 * h;
                     if (row0 + r < a.rows)
                         cp_async16(dst + r * kPitchW + ld_chunk * 16,
                                    a.w[s] + (size_t)(row0 + r) * (a.cols / 2) + (size_t)f_ks * kRowBytes + ld_chunk * 16);
                 }
-                if (warp < 2 && row0 + lane < a.rows) {  // warp 0: scales, warp 1: biases; one 16-byte chunk per row
-                    const __half* src = (warp == 0 ? a.s[s] : a.b[s]) + (size_t)(row0 + lane) * groups_total + f_ks * 8;
+                if (warp < 2 && row0 + (lane >> 1) < a.rows) {  // warp 0: scales, warp 1: biases; two 16-byte chunks per row
+                    const __half* src = (warp == 0 ? a.s[s] : a.b[s]) + (size_t)(row0 + (lane >> 1)) * groups_total + f_ks * 16 + (lane & 1) * 8;
                     cp_async16(dst + kSetW + warp * kSetS + lane * 16, src);
                 }
             }
@@ -163,8 +163,8 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
     const uint8_t* px_base = g < a.batch ? sx + (size_t)g * L.pitch_x + t * 32 : smem + L.zero;
     const int px_stride = g < a.batch ? kGroup * 2 : 0;
     const float* pxs_base = sxsum + 2 * t;
-    const int w_off = (wm * 16 + g) * kPitchW + wk * 64 + t * 8;  // this thread's first word in a set's W block
-    const int s_off = kSetW + (wm * 16 + g) * 16 + wk * 4;         // its {scale g0, scale g1} word; biases kSetS later
+    const int w_off = g * kPitchW + wk * 64 + t * 8;  // this thread's first word in a set's W block
+    const int s_off = kSetW + g * 32 + wk * 4;         // its {scale g0, scale g1} word; biases kSetS later
 
     float acc[NW][4];
 #pragma unroll
@@ -176,9 +176,18 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
         __syncthreads();              // ... everyone's have, and everyone is done with stage n-1
         fetch();                      // refill the buffer stage n-1 used
         const uint8_t* st = ring + (size_t)(n % STAGES) * L.stage_bytes;
+        float2 sa[NW], ba[NW], sb[NW], bb[NW];  // {group 2wk, group 2wk+1}: scale / bias of row g (a) and row g+8 (b)
+#pragma unroll
+        for (int s = 0; s < NW; ++s) {
+            const uint8_t* base = st + s * kSetBytes + s_off;
+            sa[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base)));
+            ba[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + kSetS)));
+            sb[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + 8 * 32)));
+            bb[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + kSetS + 8 * 32)));
+        }
 #pragma unroll
         for (int gg = 0; gg < 2; ++gg) {
-            const int gi = c_ks * 8 + wk * 2 + gg;  // group index within the row
+            const int gi = c_ks * 16 + wk * 2 + gg;  // group index within the row
             const uint8_t* px = px_base + gi * px_stride;
             const uint4 x0 = *reinterpret_cast<const uint4*>(px), x1 = *reinterpret_cast<const uint4*>(px + 16);
             const float2 xs = *reinterpret_cast<const float2*>(pxs_base + gi * 8);
@@ -195,11 +204,7 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
                 dequant8s(wa.y, pa); dequant8s(wb.y, pb);
                 mma16816(c, pa[0], pb[0], pa[1], pb[1], x1.x, x1.y);
                 mma16816(c, pa[2], pb[2], pa[3], pb[3], x1.z, x1.w);
-                const float2 sa = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off)));
-                const float2 ba = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off + kSetS)));
-                const float2 sb = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off + 8 * 16)));
-                const float2 bb = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off + kSetS + 8 * 16)));
-                const float s0 = gg ? sa.y : sa.x, b0 = gg ? ba.y : ba.x, s1 = gg ? sb.y : sb.x, b1 = gg ? bb.y : bb.x;
+                const float s0 = gg ? sa[s].y : sa[s].x, b0 = gg ? ba[s].y : ba[s].x, s1 = gg ? sb[s].y : sb[s].x, b1 = gg ? bb[s].y : bb[s].x;
                 acc[s][0] = fmaf(s0, c[0], acc[s][0]); acc[s][0] = fmaf(b0, xs.x, acc[s][0]);
                 acc[s][1] = fmaf(s0, c[1], acc[s][1]); acc[s][1] = fmaf(b0, xs.y, acc[s][1]);
                 acc[s][2] = fmaf(s1, c[2], acc[s][2]); acc[s][2] = fmaf(b1, xs.x, acc[s][2]);
@@ -207,8 +212,8 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
             }
         }
         if (++c_ks == spt) {
-            // ── tile done: add the four K-partials of each m-tile in a fixed order, write out ──
-            float* dst = sred + (size_t)((wm * 4 + wk) * 32 + lane) * (4 * NW);
+            // ── tile done: add the eight K-partials in a fixed order, write out ──
+            float* dst = sred + (size_t)(wk * 32 + lane) * (4 * NW);
 #pragma unroll
             for (int s = 0; s < NW; ++s)
 #pragma unroll
@@ -222,12 +227,12 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
                     for (int i = 0; i < 4; ++i) {
                         float v = 0.f;
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) v += sred[(size_t)((wm * 4 + k) * 32 + lane) * (4 * NW) + s * 4 + i];
+                        for (int k = 0; k < 8; ++k) v += sred[(size_t)(k * 32 + lane) * (4 * NW) + s * 4 + i];
                         tot[s][i] = v;
                     }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int row = c_tile * kTileRows + wm * 16 + g + (i >> 1) * 8;
+                    const int row = c_tile * kTileRows + g + (i >> 1) * 8;
                     const int b = 2 * t + (i & 1);
                     if (row >= a.rows || b >= a.batch) continue;
                     const size_t o = (size_t)b * a.rows + row;
