@@ -137,7 +137,7 @@ def run_ours(args):
     pkg = package.SyntheticPackage(cfg, SEED)
     keep = rank == 0 and world == 1 and not args.no_cpu_baseline
     image, desc, layers = package.build_image(pkg, rank, world, keep_for_oracle=keep)
-    dec = package.Decoder(ctx, image, desc, layers, capacity, B)
+    dec = package.Decoder(ctx, image, desc, layers, capacity, B, fuse_residual=3 if args.table == "fused" else 0)
     del image
     dec.build_graph()
     gen_s = time.time() - t0
@@ -203,6 +203,7 @@ def run_ours(args):
             "dtype": "u4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
             "config": {"workload": "config4: full 36-layer 4096/12288 decoder, affine u4 g64, greedy decode after a 512-token prompt",
                        "batch": B, "prompt_len": PROMPT_LEN, "parallelism": f"tp{world}",
+                       "table": args.table + (" (norm+QKV, RoPE+append, O+add, norm+gate/up+SwiGLU, down+add per layer)" if args.table == "fused" else " (the reference emitter's record sequence)"),
                        "l2_policy": "inputs larger than L2: each step streams %.2f GB of weights per GPU" % (tb["total"] / 1e9)},
             "e2e": {"value": args.steps * B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B + 4, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": launches,
@@ -314,6 +315,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--table", default="fused", choices=["fused", "reference"],
+                    help="fused: the builder's fused record table; reference: the reference emitter's record sequence")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     result = run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -210,7 +210,9 @@ typedef struct {
     uint64_t embedding, lm_head, final_norm;
     int32_t tp_world;   /* 1 = single GPU; >1 inserts an all-reduce after the O and down projections */
     int32_t tp_rank;
-    int32_t fuse_residual; /* 1 = emit fused_affine_matvec_add instead of matvec + elementwise_add (tp_world == 1 only) */
+    int32_t fuse_residual; /* bit 0: emit fused_affine_matvec_add instead of matvec + elementwise_add (tp_world == 1 only);
+                              bit 1: fold each RMS norm into the projection that follows it (one Q/K/V launch, one
+                              gate/up launch) and RoPE + KV append into one launch (the smelt_* extension kernels) */
 } smelt_decoder_desc;
 /* Allocates the activation / KV / scratch slots for `desc` at `capacity` positions and
  * `batch` sequences, registers the pipelines, configures the context and writes the table.
@@ -262,6 +264,35 @@ SMELT_CUDA_API smelt_status smelt_cuda_affine_dual_matvec(smelt_cuda_ctx* ctx, c
                                                           const void* b0_dev, const void* w1_dev, const void* s1_dev,
                                                           const void* b1_dev, const void* x_dev, void* y0_dev,
                                                           void* y1_dev, int rows, int cols, int group, int batch);
+/* Fused forms used by the decoder builder's fused table (no single counterpart in the
+ * reference; each is the composition of the reference kernels it names, with the same
+ * rounding points).
+ * affine_multi_matvec: rms_norm_1pw (norms.metal:9-67; skipped when norm_w_dev is NULL)
+ * followed by up to three affine_matvec launches that share x (for example the Q, K and V
+ * projections) in one kernel.  Needs group 64, cols a multiple of 1024, batch <= 8, every
+ * tensor but the last with rows a multiple of 16. */
+typedef struct {
+    const void* w_dev;
+    const void* scales_dev;
+    const void* biases_dev;
+    void* y_dev; /* [batch, rows] */
+    int32_t rows;
+} smelt_affine_tensor;
+SMELT_CUDA_API smelt_status smelt_cuda_affine_multi_matvec(smelt_cuda_ctx* ctx, const smelt_affine_tensor* tensors, int n_tensors,
+                                                           const void* x_dev, const void* norm_w_dev, float eps, int cols,
+                                                           int group, int batch);
+/* rms_norm_1pw followed by fused_affine_gate_up_swiglu in one kernel. */
+SMELT_CUDA_API smelt_status smelt_cuda_rmsnorm_affine_gate_up_swiglu(smelt_cuda_ctx* ctx, const void* gw_dev, const void* gs_dev,
+                                                                     const void* gb_dev, const void* uw_dev, const void* us_dev,
+                                                                     const void* ub_dev, const void* x_dev, const void* norm_w_dev,
+                                                                     float eps, void* y_dev, int rows, int cols, int group, int batch);
+/* apply_rope on Q + rope_kv_cache_update on K + kv_cache_update on V (attention.metal:48-209)
+ * in one kernel; analytic trig, ropeDim == headDim, layout 0 (adjacent) or 1 (split-half). */
+SMELT_CUDA_API smelt_status smelt_cuda_rope_qkv_append(smelt_cuda_ctx* ctx, void* q_dev, const void* k_new_dev, const void* v_new_dev,
+                                                       void* k_cache_dev, void* v_cache_dev, uint32_t capacity, int head_dim,
+                                                       int n_q, int n_kv, int layout, uint32_t position, float base_log2, int batch,
+                                                       size_t kv_seq_stride);
+
 /* Whole-tensor dequant probe: out_f32[rows*cols] and/or out_f16 (either may be NULL) —
  * SmeltAffineU4.dequantizeRow (SmeltAffineU4.swift:141-161), bit-exact. */
 SMELT_CUDA_API smelt_status smelt_cuda_affine_dequantize(smelt_cuda_ctx* ctx, const void* w_dev, const void* scales_dev,

@@ -61,6 +61,13 @@ class AffineRef(C.Structure):
     _fields_ = [("packed", C.c_uint64), ("scales", C.c_uint64), ("biases", C.c_uint64)]
 
 
+class AffineTensor(C.Structure):
+    """``smelt_affine_tensor``: one weight tensor and its output for ``affine_multi_matvec``."""
+
+    _fields_ = [("w_dev", C.c_void_p), ("scales_dev", C.c_void_p), ("biases_dev", C.c_void_p), ("y_dev", C.c_void_p),
+                ("rows", C.c_int32)]
+
+
 class LayerRef(C.Structure):
     _fields_ = [("input_norm", C.c_uint64), ("post_norm", C.c_uint64), ("q", AffineRef), ("k", AffineRef),
                 ("v", AffineRef), ("o", AffineRef), ("gate", AffineRef), ("up", AffineRef), ("down", AffineRef)]

@@ -482,6 +482,7 @@ cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int
         bool handled = false;
         cudaError_t e = launch_affine_stream(l, mode, args, group, &handled);
         if (handled || e != cudaSuccess) return e;
+        if (args.norm_w || args.nseg > 1) return cudaErrorNotSupported;  // only the streaming kernel fuses these
     }
     switch (mode) {
         case kAffinePlain: return launch_group<kAffinePlain>(l, args, group);

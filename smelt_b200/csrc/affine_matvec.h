@@ -11,6 +11,15 @@ enum AffineMode : int {
     kAffineDual = 3,    // y = half(acc0), y2 = half(acc1)             fused_dual_affine_matvec
 };
 
+// One row range of a multi-tensor launch (plain mode only): e.g. Q | K | V sharing x.
+struct AffineSeg {
+    const uint8_t* w;
+    const __half* s;
+    const __half* b;
+    __half* y;     // [batch, rows] of this segment
+    int rows;      // a multiple of 16 for every segment but the last
+};
+
 struct AffineArgs {
     const uint8_t* w[2];   // packed nibbles [rows, cols/2]; [1] = up / second matrix
     const __half* s[2];    // scales [rows, cols/group]
@@ -20,6 +29,13 @@ struct AffineArgs {
     __half* y2;            // dual mode: second output
     const __half* residual;  // add mode: [batch, rows]; may alias y
     int rows, cols, batch;
+    // Streaming kernel only.  norm_w != null: x is RMS-normalised while it is staged, with
+    // the rounding points of rms_norm_1pw (half(x*rs) times half(1+w)).  nseg > 1: plain mode
+    // over several tensors; rows is then the total row count.
+    const __half* norm_w;
+    float norm_eps;
+    int nseg;
+    AffineSeg seg[3];
     int ks, nsplit;        // filled by the launcher
     int sm_count;          // SMs of the device (0 = assume 148)
     uint32_t* err;         // device error word (may be null)

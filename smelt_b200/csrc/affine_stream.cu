@@ -71,7 +71,7 @@ __device__ __forceinline__ void dequant8s(uint32_t w, uint32_t p[4]) {
 }
 
 template <int MODE, int STAGES>
-__global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const AffineArgs a) {
+__global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_kernel(const AffineArgs a) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -83,11 +83,20 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
     float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
     float* sred = reinterpret_cast<float*>(smem + L.red);
 
-    const int tiles_total = (a.rows + kTileRows - 1) / kTileRows;
+    const int tiles_total = a.nseg > 1 ? a.ks : (a.rows + kTileRows - 1) / kTileRows;  // ks carries the tile count of a multi-segment launch
     const int spt = a.cols / kStageCols;  // stages per tile
     const int my_tiles = blockIdx.x < tiles_total ? (tiles_total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const int total_stages = my_tiles * spt;
     const int groups_total = a.cols / kGroup;
+
+    // Plain mode may cover up to three tensors (segments) that share x; a tile belongs to one.
+    const int seg_end0 = (a.seg[0].rows + kTileRows - 1) / kTileRows;
+    const int seg_end1 = seg_end0 + (a.nseg > 1 ? (a.seg[1].rows + kTileRows - 1) / kTileRows : 0);
+    auto seg_of = [&](int tile, int& first_tile) {
+        const int sg = (a.nseg > 1 && tile >= seg_end0) + (a.nseg > 2 && tile >= seg_end1);
+        first_tile = sg == 0 ? 0 : (sg == 1 ? seg_end0 : seg_end1);
+        return sg;
+    };
 
     // ── producer side: every thread copies a fixed part of each stage ──
     const int ld_chunk = tid & 31, ld_row = tid >> 5;  // rows ld_row and ld_row + 8, 16-byte chunk ld_chunk
@@ -95,19 +104,34 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
     auto fetch = [&]() {
         if (f_n < total_stages) {
             uint8_t* st = ring + (size_t)(f_n % STAGES) * L.stage_bytes;
-            const int row0 = f_tile * kTileRows;
+            int row0 = f_tile * kTileRows, rows = a.rows;
+            const uint8_t* wsrc[NW];
+            const __half* ssrc[NW];
+            const __half* bsrc[NW];
+            if (NW == 1) {
+                int first;
+                const int sg = seg_of(f_tile, first);
+                row0 = (f_tile - first) * kTileRows;
+                rows = sg == 0 ? a.seg[0].rows : (sg == 1 ? a.seg[1].rows : a.seg[2].rows);
+                wsrc[0] = sg == 0 ? a.seg[0].w : (sg == 1 ? a.seg[1].w : a.seg[2].w);
+                ssrc[0] = sg == 0 ? a.seg[0].s : (sg == 1 ? a.seg[1].s : a.seg[2].s);
+                bsrc[0] = sg == 0 ? a.seg[0].b : (sg == 1 ? a.seg[1].b : a.seg[2].b);
+            } else {
+#pragma unroll
+                for (int s = 0; s < NW; ++s) { wsrc[s] = a.w[s]; ssrc[s] = a.s[s]; bsrc[s] = a.b[s]; }
+            }
 #pragma unroll
             for (int s = 0; s < NW; ++s) {
                 uint8_t* dst = st + s * kSetBytes;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int r = ld_row + 8 * h;
-                    if (row0 + r < a.rows)
+                    if (row0 + r < rows)
                         cp_async16(dst + r * kPitchW + ld_chunk * 16,
-                                   a.w[s] + (size_t)(row0 + r) * (a.cols / 2) + (size_t)f_ks * kRowBytes + ld_chunk * 16);
+                                   wsrc[s] + (size_t)(row0 + r) * (a.cols / 2) + (size_t)f_ks * kRowBytes + ld_chunk * 16);
                 }
-                if (warp < 2 && row0 + (lane >> 1) < a.rows) {  // warp 0: scales, warp 1: biases; two 16-byte chunks per row
-                    const __half* src = (warp == 0 ? a.s[s] : a.b[s]) + (size_t)(row0 + (lane >> 1)) * groups_total + f_ks * 16 + (lane & 1) * 8;
+                if (warp < 2 && row0 + (lane >> 1) < rows) {  // warp 0: scales, warp 1: biases; two 16-byte chunks per row
+                    const __half* src = (warp == 0 ? ssrc[s] : bsrc[s]) + (size_t)(row0 + (lane >> 1)) * groups_total + f_ks * 16 + (lane & 1) * 8;
                     cp_async16(dst + kSetW + warp * kSetS + lane * 16, src);
                 }
             }
@@ -132,11 +156,42 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
         for (int b = 0; b < a.batch; ++b) {
             const __half* xr = a.x + (size_t)b * a.cols;
             uint8_t* xd = sx + (size_t)b * L.pitch_x;
+            float rs = 0.f;
+            if (a.norm_w) {
+                // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass
+                float ss = 0.f;
+                for (int c8 = tid; c8 < chunks; c8 += kThreads) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                    const float2 f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
+                    const float2 f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
+                    ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
+                }
+                ss = warp_sum(ss);
+                __syncthreads();  // sred is free here (no tile has been reduced yet) and between batch rows
+                if (lane == 0) sred[warp] = ss;
+                __syncthreads();
+                float tot = 0.f;
+#pragma unroll
+                for (int w8 = 0; w8 < 8; ++w8) tot += sred[w8];
+                rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
+            }
             for (int base = 0; base < chunks; base += kThreads) {
                 const int c8 = base + tid;
                 float sum = 0.f;
                 if (c8 < chunks) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                    uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                    if (a.norm_w) {
+                        const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
+                        uint32_t* vp = &v.x;
+                        const uint32_t* wp = &wv.x;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 xf = __half22float2(u32_as_h2(vp[j])), wf = __half22float2(u32_as_h2(wp[j]));
+                            const __half2 n = __floats2half2_rn(xf.x * rs, xf.y * rs);
+                            const __half2 dw = __floats2half2_rn(1.0f + wf.x, 1.0f + wf.y);
+                            vp[j] = h2_as_u32(__hmul2(dw, n));
+                        }
+                    }
                     const float2 f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
                     const float2 f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
                     sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
@@ -231,14 +286,22 @@ __global__ void __launch_bounds__(kThreads, 2) affine_stream_kernel(const Affine
                         tot[s][i] = v;
                     }
 #pragma unroll
+                int first = 0, rows = a.rows;
+                __half* yout = a.y;
+                if (NW == 1) {
+                    const int sg = seg_of(c_tile, first);
+                    rows = sg == 0 ? a.seg[0].rows : (sg == 1 ? a.seg[1].rows : a.seg[2].rows);
+                    yout = sg == 0 ? a.seg[0].y : (sg == 1 ? a.seg[1].y : a.seg[2].y);
+                }
+#pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int row = c_tile * kTileRows + g + (i >> 1) * 8;
+                    const int row = (c_tile - first) * kTileRows + g + (i >> 1) * 8;
                     const int b = 2 * t + (i & 1);
-                    if (row >= a.rows || b >= a.batch) continue;
-                    const size_t o = (size_t)b * a.rows + row;
+                    if (row >= rows || b >= a.batch) continue;
+                    const size_t o = (size_t)b * rows + row;
                     const float v0 = tot[0][i];
-                    if (MODE == kAffinePlain) a.y[o] = __float2half_rn(v0);
-                    else if (MODE == kAffineAdd) a.y[o] = __hadd(__float2half_rn(v0), a.residual[o]);  // lut_matvec.metal:1802-1803
+                    if (MODE == kAffinePlain) yout[o] = __float2half_rn(v0);
+                    else if (MODE == kAffineAdd) yout[o] = __hadd(__float2half_rn(v0), a.residual[o]);  // lut_matvec.metal:1802-1803
                     else if (MODE == kAffineGateUp) a.y[o] = __float2half_rn(v0 / (1.0f + expf(-v0)) * tot[NW - 1][i]);  // :2228
                     else { a.y[o] = __float2half_rn(v0); a.y2[o] = __float2half_rn(tot[NW - 1][i]); }
                 }
@@ -263,7 +326,14 @@ cudaError_t launch_stream_t(const Launch& l, AffineArgs a, int ctas_per_sm) {
     auto kern = affine_stream_kernel<MODE, STAGES>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
     if (e != cudaSuccess) return e;
-    const int tiles = (a.rows + kTileRows - 1) / kTileRows;
+    if (NW == 1 && a.nseg <= 1) {
+        a.nseg = 1;
+        a.seg[0].w = a.w[0]; a.seg[0].s = a.s[0]; a.seg[0].b = a.b[0]; a.seg[0].y = a.y; a.seg[0].rows = a.rows;
+    }
+    int tiles = 0;
+    if (NW == 1) for (int i = 0; i < a.nseg; ++i) tiles += (a.seg[i].rows + kTileRows - 1) / kTileRows;
+    else tiles = (a.rows + kTileRows - 1) / kTileRows;
+    a.ks = tiles;
     const int sm = a.sm_count > 0 ? a.sm_count : 148;
     int grid = sm * ctas_per_sm;
     if (grid > tiles) grid = tiles;
@@ -285,7 +355,7 @@ cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handl
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
     // Ring depth: as deep as leaves room for two CTAs per SM (about 113 KB each).
     static const int forced = env_int("SMELT_AFFINE_STAGES", 0);
-    const uint32_t budget2 = 113u * 1024u, budget1 = 226u * 1024u;
+    const uint32_t budget3 = 75u * 1024u, budget2 = 113u * 1024u, budget1 = 226u * 1024u;
     const int pref = forced ? forced : (NW == 2 ? 4 : 6);
     const int order[3] = {pref, 4, 3};
     for (int i = 0; i < 3; ++i) {
@@ -293,7 +363,7 @@ cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handl
         if (st != 3 && st != 4 && st != 6) continue;
         const uint32_t total = stream_layout(NW, st, a.cols, a.batch).total;
         if (total > budget1) continue;
-        const int per_sm = total <= budget2 ? 2 : 1;
+        const int per_sm = (st == 3 && total <= budget3) ? 3 : (total <= budget2 ? 2 : 1);
         *handled = true;
         if (st == 6) return launch_stream_t<MODE, 6>(l, a, per_sm);
         if (st == 4) return launch_stream_t<MODE, 4>(l, a, per_sm);
@@ -313,8 +383,17 @@ cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& a,
     static const int disabled = env_int("SMELT_AFFINE_NO_STREAM", 0);
     if (disabled || group != kGroup || a.batch > 8 || a.cols % kStageCols != 0) return cudaSuccess;
     const int nw = (mode == kAffineGateUp || mode == kAffineDual) ? 2 : 1;
-    for (int s = 0; s < nw; ++s)
-        if ((reinterpret_cast<uintptr_t>(a.w[s]) | reinterpret_cast<uintptr_t>(a.s[s]) | reinterpret_cast<uintptr_t>(a.b[s])) & 15u) return cudaSuccess;
+    if (a.nseg > 1) {
+        if (nw != 1 || a.nseg > 3 || mode != kAffinePlain) return cudaErrorInvalidValue;
+        for (int i = 0; i < a.nseg; ++i) {
+            if ((reinterpret_cast<uintptr_t>(a.seg[i].w) | reinterpret_cast<uintptr_t>(a.seg[i].s) | reinterpret_cast<uintptr_t>(a.seg[i].b)) & 15u) return cudaSuccess;
+            if (i + 1 < a.nseg && a.seg[i].rows % kTileRows != 0) return cudaSuccess;
+        }
+    } else {
+        for (int s = 0; s < nw; ++s)
+            if ((reinterpret_cast<uintptr_t>(a.w[s]) | reinterpret_cast<uintptr_t>(a.s[s]) | reinterpret_cast<uintptr_t>(a.b[s])) & 15u) return cudaSuccess;
+    }
+    if (a.norm_w && (reinterpret_cast<uintptr_t>(a.norm_w) & 15u)) return cudaSuccess;
     if (reinterpret_cast<uintptr_t>(a.x) & 15u) return cudaSuccess;
     switch (mode) {
         case kAffinePlain: return launch_stream_mode<kAffinePlain>(l, a, handled);

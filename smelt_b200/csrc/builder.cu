@@ -96,7 +96,10 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
     const int H = d->hidden, I = d->inter, D = d->head_dim, G = d->group, B = (int)batch;
     const int qd = d->n_q * D, kvd = d->n_kv * D, L = d->layers, V = d->vocab;
     const bool tp = d->tp_world > 1;
-    const bool fuse = d->fuse_residual && !tp;
+    const bool fuse = (d->fuse_residual & 1) && !tp;
+    // bit 1: fold the norms into the projections (one QKV launch, one gate/up launch) and RoPE /
+    // KV append into one launch; needs the shapes the streaming matvec kernel accepts.
+    const bool fuse2 = (d->fuse_residual & 2) && G == 64 && H % 1024 == 0 && qd % 16 == 0 && kvd % 16 == 0 && B <= 8 && D % 2 == 0;
     const bool bt = B > 1;  // batched kernel names bind actualBatch instead of numRows
 
     if (!dry) {
@@ -144,6 +147,13 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
     for (int l = 0; l < L; ++l) {
         const smelt_layer_ref& w = layers[l];
         const int kslot = kKvBase + l, vslot = kKvBase + L + l;
+        if (fuse2) {
+            Rec r(e, "smelt_rmsnorm_affine_qkv:" + std::to_string(H) + ":64", ((qd + 2 * kvd) + 15) / 16);
+            r.affine(0, w.q).affine(3, w.k).affine(6, w.v).buf(9, SMELT_SLOT_CUR).buf(10, kWeights, w.input_norm)
+                .buf(11, kAttnQ).buf(12, kAttnK).buf(13, kAttnV).u32(14, qd).u32(15, kvd).f32(16, d->eps).u32(17, B);
+            Rec(e, "smelt_rope_qkv_append", ((qd + 2 * kvd) / 2 + 127) / 128, B).buf(0, kAttnQ).buf(1, kAttnK).buf(2, kAttnV).buf(3, kslot).buf(4, vslot)
+                .u32(7, D).u32(8, d->n_q).u32(9, d->n_kv).con(10, SMELT_CONST_CACHE_SEQ_CAPACITY).con(11, SMELT_CONST_POSITION).u32(12, 1).f32(13, log2_theta);
+        } else {
         // input norm (TopLevelEmitter.swift:316-326)
         Rec(e, "rms_norm_1pw", B).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, w.input_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
         // Q projection; fused dual K/V projection (AttentionPlugin.swift:105-300)
@@ -165,6 +175,7 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
         }
         Rec(e, "kv_cache_update", (kvd + 63) / 64, B).buf(0, vslot).buf(1, kAttnV).con(2, SMELT_CONST_CACHE_SEQ_CAPACITY).u32(3, D)
             .con(4, SMELT_CONST_POSITION).u32(5, d->n_kv);
+        }
         // attention decode (AttentionPlugin.swift:738-984): one threadgroup per query head
         Rec(e, "attention_decode", d->n_q, B).buf(0, kAttnQ).buf(1, kslot).buf(2, vslot).buf(3, kAttnQ).buf(4, kAttnOut)
             .u32(5, D).con(6, SMELT_CONST_CACHE_SEQ_CAPACITY).con(7, SMELT_CONST_POSITION_PLUS1).u32(8, d->n_kv).f32(9, scale).u32(10, 0);
@@ -180,11 +191,16 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
         }
         e.swap();
         // post-attention norm + FFN (TopLevelEmitter.swift:1021-1322 emitSwiGLU)
+        if (fuse2) {
+            Rec r(e, "smelt_rmsnorm_affine_gate_up_swiglu:" + std::to_string(H) + ":64", (I + 15) / 16);
+            r.affine(0, w.gate).affine(3, w.up).buf(6, SMELT_SLOT_CUR).buf(7, kFfnInt).u32(8, I).buf(9, kWeights, w.post_norm).f32(10, d->eps).u32(11, B);
+        } else {
         Rec(e, "rms_norm_1pw", B).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, w.post_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
         {
             Rec r(e, bt ? shaped("fused_affine_gate_up_swiglu", H, I, G, true) : "fused_affine_gate_up_swiglu:" + std::to_string(H) + ":" + std::to_string(G), (I + 7) / 8);
             r.affine(0, w.gate).affine(3, w.up).buf(6, kNormOut).buf(7, kFfnInt);
             count_const(r, 8, I);
+        }
         }
         if (fuse) {
             Rec r(e, bt ? shaped("fused_affine_matvec_add", I, H, G, true) : "fused_affine_matvec_add:" + std::to_string(I) + ":" + std::to_string(G), (H + 7) / 8);

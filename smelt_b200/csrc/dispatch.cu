@@ -83,6 +83,13 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         *out = p;
         return true;
     }
+    // Fused extension kernels emitted by the decoder builder's fused table (group 64 only).
+    if (name == "smelt_rmsnorm_affine_qkv" || name == "smelt_rmsnorm_affine_gate_up_swiglu") {
+        if (p.cols <= 0 || p.group != 64 || p.cols % 1024) return false;
+        p.kind = name == "smelt_rmsnorm_affine_qkv" ? PK_FUSED_NORM_QKV : PK_FUSED_NORM_GATEUP;
+        *out = p;
+        return true;
+    }
     struct Simple { const char* name; PipeKind kind; int bits; bool batched; };
     static const Simple table[] = {
         {"fp16_matvec", PK_FP16_MATVEC, 0, false},
@@ -108,6 +115,7 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"elementwise_add", PK_ADD, 0, false},
         {"swiglu_fused", PK_SWIGLU, 0, false},
         {"smelt_tp_all_reduce", PK_TP_ALL_REDUCE, 0, false},
+        {"smelt_rope_qkv_append", PK_ROPE_QKV_APPEND, 0, false},
     };
     for (const Simple& s : table)
         if (name == s.name) {
@@ -536,6 +544,70 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             NEED_BYTES(0, (size_t)count * 2); NEED_BYTES(1, (size_t)count * 2); NEED_BYTES(2, (size_t)count * 2);
             in.launches += 1;
             return check_cuda(ctx, launch_swiglu_fused(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int64_t)count), "swiglu_fused");
+        }
+        case PK_FUSED_NORM_QKV: {
+            // 0-2 Q, 3-5 K, 6-8 V (W, scales, biases), 9 x, 10 norm weight, 11-13 outputs;
+            // constants 14 rows of Q, 15 rows of K and of V, 16 eps, 17 batch.
+            for (int i = 0; i <= 13; ++i)
+                if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": buffer binding missing");
+            NEED_U32(14, rows_q); NEED_U32(15, rows_kv); NEED_U32(16, eps_bits); NEED_U32(17, nb);
+            if (rows_q == 0 || rows_kv == 0 || nb == 0 || nb > 8) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows / batch");
+            AffineArgs a = {};
+            const uint32_t rows[3] = {rows_q, rows_kv, rows_kv};
+            const int groups = p.cols / p.group;
+            a.nseg = 3;
+            for (int i = 0; i < 3; ++i) {
+                if (r.buf[3 * i].avail < (size_t)rows[i] * p.cols / 2 || r.buf[3 * i + 1].avail < (size_t)rows[i] * groups * 2 || r.buf[3 * i + 2].avail < (size_t)rows[i] * groups * 2)
+                    return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": weight tensor extends past the weights slot");
+                if (r.buf[11 + i].avail < (size_t)nb * rows[i] * 2) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": output slot too small");
+                a.seg[i].w = r.buf[3 * i].ptr; a.seg[i].s = (const __half*)r.buf[3 * i + 1].ptr; a.seg[i].b = (const __half*)r.buf[3 * i + 2].ptr;
+                a.seg[i].y = (__half*)r.buf[11 + i].ptr; a.seg[i].rows = (int)rows[i];
+                a.rows += (int)rows[i];
+            }
+            NEED_BYTES(9, (size_t)nb * p.cols * 2); NEED_BYTES(10, (size_t)p.cols * 2);
+            a.w[0] = a.seg[0].w; a.s[0] = a.seg[0].s; a.b[0] = a.seg[0].b; a.y = a.seg[0].y;
+            a.x = (const __half*)r.buf[9].ptr; a.norm_w = (const __half*)r.buf[10].ptr; a.norm_eps = as_f32(eps_bits);
+            a.cols = p.cols; a.batch = (int)nb; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+            in.launches += 1;
+            cudaError_t e = launch_affine(l, kAffinePlain, a, p.group);
+            if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": shape not eligible for the fused kernel");
+            return check_cuda(ctx, e, p.name.c_str());
+        }
+        case PK_FUSED_NORM_GATEUP: {
+            // 0-2 gate, 3-5 up, 6 x, 7 y, 9 norm weight; constants 8 rows, 10 eps, 11 batch.
+            for (int i = 0; i <= 7; ++i)
+                if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": buffer binding missing");
+            NEED_BUF(9); NEED_U32(8, rows); NEED_U32(10, eps_bits); NEED_U32(11, nb);
+            if (rows == 0 || nb == 0 || nb > 8) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows / batch");
+            const int groups = p.cols / p.group;
+            AffineArgs a = {};
+            for (int s2 = 0; s2 < 2; ++s2) {
+                if (r.buf[3 * s2].avail < (size_t)rows * p.cols / 2 || r.buf[3 * s2 + 1].avail < (size_t)rows * groups * 2 || r.buf[3 * s2 + 2].avail < (size_t)rows * groups * 2)
+                    return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": weight tensor extends past the weights slot");
+                a.w[s2] = r.buf[3 * s2].ptr; a.s[s2] = (const __half*)r.buf[3 * s2 + 1].ptr; a.b[s2] = (const __half*)r.buf[3 * s2 + 2].ptr;
+            }
+            NEED_BYTES(6, (size_t)nb * p.cols * 2); NEED_BYTES(7, (size_t)nb * rows * 2); NEED_BYTES(9, (size_t)p.cols * 2);
+            a.x = (const __half*)r.buf[6].ptr; a.y = (__half*)r.buf[7].ptr; a.norm_w = (const __half*)r.buf[9].ptr; a.norm_eps = as_f32(eps_bits);
+            a.rows = (int)rows; a.cols = p.cols; a.batch = (int)nb; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+            in.launches += 1;
+            cudaError_t e = launch_affine(l, kAffineGateUp, a, p.group);
+            if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": shape not eligible for the fused kernel");
+            return check_cuda(ctx, e, p.name.c_str());
+        }
+        case PK_ROPE_QKV_APPEND: {
+            // 0 q (in place), 1 new K, 2 new V, 3 K cache, 4 V cache; constants 7 headDim, 8 q heads,
+            // 9 kv heads, 10 capacity, 11 position, 12 layout, 13 log2(theta).
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4);
+            NEED_U32(7, d); NEED_U32(8, nq); NEED_U32(9, nkv); NEED_U32(10, cap); NEED_U32(12, layout); NEED_U32(13, base_bits);
+            if (!bind_pos_arg(in, r, 11, &l)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "smelt_rope_qkv_append: position constant is missing");
+            if (d == 0 || d % 2 || nq == 0 || nkv == 0 || layout > 1) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "smelt_rope_qkv_append: bad shape or layout");
+            const int batch = batch_of(rec);
+            const size_t seq = (size_t)nkv * cap * d;
+            NEED_BYTES(0, (size_t)batch * nq * d * 2); NEED_BYTES(1, (size_t)batch * nkv * d * 2); NEED_BYTES(2, (size_t)batch * nkv * d * 2);
+            NEED_BYTES(3, seq * 2 * batch); NEED_BYTES(4, seq * 2 * batch);
+            if (!in.device_pos && (l.arg_pos_valid ? l.arg_pos : in.position) >= cap) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "smelt_rope_qkv_append: position beyond the cache capacity");
+            in.launches += 1;
+            return check_cuda(ctx, launch_rope_qkv_append(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (__half*)r.buf[4].ptr, cap, (int)d, (int)nq, (int)nkv, (int)layout, as_f32(base_bits), batch, seq), "smelt_rope_qkv_append");
         }
         case PK_TP_ALL_REDUCE: {
             NEED_BUF(0); NEED_U32(1, count);

@@ -255,6 +255,48 @@ __global__ void kv_cache_update_kernel(__half* cache, const __half* new_kv, cons
     if (!rotated_second) dst[dim] = src[dim];
 }
 
+// RoPE on Q (in place), RoPE on the new K row written into the K cache, and the new V row
+// copied into the V cache, in one launch: the work of apply_rope + rope_kv_cache_update +
+// kv_cache_update (attention.metal:48-209) for full-head rotation (ropeDim == headDim,
+// adjacent or split-half pairs, analytic trig).  One thread per pair.
+__global__ void rope_qkv_append_kernel(__half* q, const __half* k_new, const __half* v_new, __half* k_cache,
+                                       __half* v_cache, uint32_t capacity, int head_dim, int n_q, int n_kv, int layout,
+                                       float base_log2, size_t seq_stride, DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const uint32_t pos = dyn_arg_position(dyn);
+    if (pos >= capacity) return;
+    const int half = head_dim / 2;
+    const int item = blockIdx.x * blockDim.x + threadIdx.x;
+    const int total = (n_q + 2 * n_kv) * half;
+    if (item >= total) return;
+    const int head = item / half, p = item % half, b = blockIdx.y;
+    if (head >= n_q + n_kv) {  // V: copy two elements
+        const int h = head - n_q - n_kv;
+        const __half2 v = reinterpret_cast<const __half2*>(v_new + ((size_t)b * n_kv + h) * head_dim)[p];
+        reinterpret_cast<__half2*>(v_cache + (size_t)b * seq_stride + ((size_t)h * capacity + pos) * head_dim)[p] = v;
+        return;
+    }
+    int d0, d1, c0i, c1i;
+    rope_indices(layout, p, half, head_dim, d0, d1, c0i, c1i);
+    float c0, s0, c1, s1;
+    rope_trig(p, half, pos, base_log2, 1, nullptr, nullptr, c0i, c1i, c0, s0, c1, s1);
+    if (head < n_q) {
+        __half* v = q + ((size_t)b * n_q + head) * head_dim;
+        const float x0 = __half2float(v[d0]), x1 = __half2float(v[d1]);
+        v[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c0), __fmul_rn(x1, s0)));
+        v[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s1), __fmul_rn(x1, c1)));
+    } else {
+        const int h = head - n_q;
+        const __half* src = k_new + ((size_t)b * n_kv + h) * head_dim;
+        __half* dst = k_cache + (size_t)b * seq_stride + ((size_t)h * capacity + pos) * head_dim;
+        const float x0 = __half2float(src[d0]), x1 = __half2float(src[d1]);
+        dst[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c0), __fmul_rn(x1, s0)));
+        dst[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x1, c1), __fmul_rn(x0, s1)));
+    }
+}
+
 // Argmax over fp16 logits with the reference's ordered key
 // (Resources/Shaders/lut_matvec.metal:4045-4074): ties keep the lowest index, -0 == +0.
 __device__ __forceinline__ uint64_t argmax_key(__half v, uint32_t index) {
@@ -444,6 +486,15 @@ cudaError_t launch_kv_cache_update(const Launch& l, __half* cache, const __half*
     SMELT_LAUNCH(kv_cache_update_kernel, dim3((heads * head_dim + 127) / 128, batch), dim3(128), 0, cache, new_kv,
                  cos_t, sin_t, capacity, head_dim, heads, rope_dim, layout, base_log2, math_mode, do_rope,
                  table_stride, seq_stride, dev_dyn(l));
+}
+
+cudaError_t launch_rope_qkv_append(const Launch& l, __half* q, const __half* k_new, const __half* v_new, __half* k_cache,
+                                   __half* v_cache, uint32_t capacity, int head_dim, int n_q, int n_kv, int layout,
+                                   float base_log2, int batch, size_t seq_stride) {
+    if (layout == 2 || head_dim % 2) return cudaErrorInvalidValue;
+    const int total = (n_q + 2 * n_kv) * head_dim / 2;
+    SMELT_LAUNCH(rope_qkv_append_kernel, dim3((total + 127) / 128, batch), dim3(128), 0, q, k_new, v_new, k_cache, v_cache,
+                 capacity, head_dim, n_q, n_kv, layout, base_log2, seq_stride, dev_dyn(l));
 }
 
 cudaError_t launch_argmax_partials(const Launch& l, const __half* logits, uint64_t* partials, int vocab, int chunk,

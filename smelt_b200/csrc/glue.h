@@ -14,6 +14,7 @@ cudaError_t launch_affine_dequant(const Launch& l, const uint8_t* w, const __hal
 cudaError_t launch_signed_dequant(const Launch& l, const uint8_t* codes, const __half* s, float* out, int rows, int cols, int bits, int group, int* bad);
 cudaError_t launch_apply_rope(const Launch& l, __half* qk, const __half* cos_t, const __half* sin_t, int head_dim, int rope_dim, int heads, int layout, float base_log2, int math_mode, size_t table_stride, int batch);
 cudaError_t launch_kv_cache_update(const Launch& l, __half* cache, const __half* new_kv, const __half* cos_t, const __half* sin_t, uint32_t capacity, int head_dim, int heads, int rope_dim, int layout, float base_log2, int math_mode, int do_rope, size_t table_stride, int batch, size_t seq_stride);
+cudaError_t launch_rope_qkv_append(const Launch& l, __half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache, uint32_t capacity, int head_dim, int n_q, int n_kv, int layout, float base_log2, int batch, size_t seq_stride);
 cudaError_t launch_argmax_partials(const Launch& l, const __half* logits, uint64_t* partials, int vocab, int chunk, int batch);
 cudaError_t launch_argmax_reduce(const Launch& l, const uint64_t* partials, int32_t* out, int n, int batch, int out_stride);
 cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x, __half* y, int rows, int cols, int batch, int sm_count);

@@ -330,6 +330,57 @@ smelt_status smelt_cuda_affine_dual_matvec(smelt_cuda_ctx* ctx, const void* w0, 
     return affine_common(ctx, kAffineDual, w0, s0, b0, w1, s1, b1, x, y0, y1, nullptr, rows, cols, group, batch);
 }
 
+smelt_status smelt_cuda_affine_multi_matvec(smelt_cuda_ctx* ctx, const smelt_affine_tensor* tensors, int n_tensors, const void* x,
+                                            const void* norm_w, float eps, int cols, int group, int batch) {
+    CTX_OR_FAIL();
+    if (!tensors || n_tensors < 1 || n_tensors > 3 || !x || cols <= 0 || batch <= 0)
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "affine multi matvec: 1..3 tensors, positive cols and batch");
+    AffineArgs a = {};
+    a.nseg = n_tensors;
+    for (int i = 0; i < n_tensors; ++i) {
+        const smelt_affine_tensor& t = tensors[i];
+        if (!t.w_dev || !t.scales_dev || !t.biases_dev || !t.y_dev || t.rows <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "affine multi matvec: null tensor field");
+        a.seg[i].w = (const uint8_t*)t.w_dev; a.seg[i].s = (const __half*)t.scales_dev; a.seg[i].b = (const __half*)t.biases_dev;
+        a.seg[i].y = (__half*)t.y_dev; a.seg[i].rows = t.rows;
+        a.rows += t.rows;
+    }
+    a.w[0] = a.seg[0].w; a.s[0] = a.seg[0].s; a.b[0] = a.seg[0].b; a.y = a.seg[0].y;
+    a.x = (const __half*)x; a.norm_w = (const __half*)norm_w; a.norm_eps = eps;
+    a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+    if (n_tensors == 1 && !norm_w) a.nseg = 0;
+    cudaError_t e = launch_affine(typed_launch(ctx), kAffinePlain, a, group);
+    if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "affine multi matvec: needs group 64, cols % 1024 == 0, batch <= 8, 16-byte aligned operands, rows % 16 == 0 for all but the last tensor");
+    return check_cuda(ctx, e, "affine multi matvec launch");
+}
+
+smelt_status smelt_cuda_rmsnorm_affine_gate_up_swiglu(smelt_cuda_ctx* ctx, const void* gw, const void* gs, const void* gb, const void* uw,
+                                                      const void* us, const void* ub, const void* x, const void* norm_w, float eps,
+                                                      void* y, int rows, int cols, int group, int batch) {
+    CTX_OR_FAIL();
+    if (!gw || !gs || !gb || !uw || !us || !ub || !x || !norm_w || !y || rows <= 0 || cols <= 0 || batch <= 0)
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "rmsnorm gate/up: null pointer or bad shape");
+    AffineArgs a = {};
+    a.w[0] = (const uint8_t*)gw; a.s[0] = (const __half*)gs; a.b[0] = (const __half*)gb;
+    a.w[1] = (const uint8_t*)uw; a.s[1] = (const __half*)us; a.b[1] = (const __half*)ub;
+    a.x = (const __half*)x; a.y = (__half*)y; a.norm_w = (const __half*)norm_w; a.norm_eps = eps;
+    a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+    cudaError_t e = launch_affine(typed_launch(ctx), kAffineGateUp, a, group);
+    if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "rmsnorm gate/up: needs group 64, cols % 1024 == 0, batch <= 8, 16-byte aligned operands");
+    return check_cuda(ctx, e, "rmsnorm gate/up launch");
+}
+
+smelt_status smelt_cuda_rope_qkv_append(smelt_cuda_ctx* ctx, void* q, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                                        uint32_t capacity, int head_dim, int n_q, int n_kv, int layout, uint32_t position,
+                                        float base_log2, int batch, size_t kv_seq_stride) {
+    CTX_OR_FAIL();
+    if (!q || !k_new || !v_new || !k_cache || !v_cache || head_dim <= 0 || head_dim % 2 || n_q <= 0 || n_kv <= 0 || batch <= 0 || (layout != 0 && layout != 1))
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "rope qkv append: bad arguments (layout 0 or 1, even head_dim)");
+    if (position >= capacity) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "rope qkv append: position must be below capacity");
+    Launch l = typed_launch(ctx);
+    l.position = position;
+    return check_cuda(ctx, launch_rope_qkv_append(l, (__half*)q, (const __half*)k_new, (const __half*)v_new, (__half*)k_cache, (__half*)v_cache, capacity, head_dim, n_q, n_kv, layout, base_log2, batch, kv_seq_stride ? kv_seq_stride : (size_t)n_kv * capacity * head_dim), "rope qkv append");
+}
+
 smelt_status smelt_cuda_affine_dequantize(smelt_cuda_ctx* ctx, const void* w, const void* s, const void* b,
                                           void* out_f32, void* out_f16, int rows, int cols, int group) {
     CTX_OR_FAIL();

@@ -40,6 +40,9 @@ enum PipeKind : int {
     PK_ADD,
     PK_SWIGLU,
     PK_TP_ALL_REDUCE,
+    PK_FUSED_NORM_QKV,
+    PK_FUSED_NORM_GATEUP,
+    PK_ROPE_QKV_APPEND,
 };
 
 struct Pipeline {

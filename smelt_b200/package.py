@@ -158,7 +158,7 @@ class Decoder:
     then ``decode_step`` per token or replay a captured graph."""
 
     def __init__(self, ctx: capi.Context, image: np.ndarray, desc: capi.DecoderDesc, layers, capacity: int, batch: int = 1,
-                 fuse_residual: bool = False):
+                 fuse_residual: int = 0):
         self.ctx, self.desc, self.layers, self.capacity, self.batch = ctx, desc, layers, capacity, batch
         desc.fuse_residual = int(fuse_residual)
         ctx.call("upload_weights", WEIGHTS_SLOT, image, C.c_size_t(image.nbytes))

@@ -152,6 +152,88 @@ def test_affine_dual_matvec(ctx, oracle):
     assert rel_err(y1.download(np.float16, (batch, rows)), oracle.affine_matvec(*b, x, rows, cols, 64)) < REL_TOL
 
 
+# ── fused extension kernels: same rounding points as the kernels they replace ──
+def _multi(ctx, tensors, x, norm_w, eps, cols, batch):
+    arr = (capi.AffineTensor * len(tensors))()
+    outs = []
+    for i, (w, s, b, rows) in enumerate(tensors):
+        dw, ds, db = dev(ctx, w, s, b)
+        y = ctx.alloc(batch * rows * 2).fill(0xFF)
+        arr[i] = capi.AffineTensor(dw.ptr, ds.ptr, db.ptr, y.ptr, rows)
+        outs.append((y, rows, (dw, ds, db)))
+    dx = ctx.to_device(x)
+    dn = ctx.to_device(norm_w) if norm_w is not None else None
+    st = ctx.call_status("affine_multi_matvec", C.cast(arr, C.c_void_p), len(tensors), dx, dn, C.c_float(eps), cols, 64, batch)
+    return st, [y.download(np.float16, (batch, rows)) for y, rows, _ in outs]
+
+
+@pytest.mark.parametrize("rows,cols,batch,norm", [((4096, 1024, 1024), 4096, 1, True), ((256, 64, 72), 1024, 3, True),
+                                                  ((512, 128, 128), 2048, 8, False), ((48, 16, 5), 1024, 1, True)])
+def test_affine_multi_matvec(ctx, oracle, rows, cols, batch, norm):
+    eps = 1e-6
+    tensors = [(*synth.affine_u4(21, f"t{i}", r, cols, 64), r) for i, r in enumerate(rows)]
+    x = synth.activations(21, "x", batch, cols)
+    nw = synth.normal_f16(21, "norm", (cols,), 0.1) if norm else None
+    st, got = _multi(ctx, tensors, x, nw, eps, cols, batch)
+    assert st == 0, ctx.last_error()
+    xn = np.stack([oracle.rms_norm_1pw(x[b], nw, eps) for b in range(batch)]) if norm else x
+    for (w, s, b, r), g in zip(tensors, got):
+        assert rel_err(g, oracle.affine_matvec(w, s, b, xn, r, cols, 64)) < REL_TOL
+
+
+def test_affine_multi_matvec_rejects_ineligible_shapes(ctx):
+    t = [(*synth.affine_u4(22, "a", 24, 1024, 64), 24), (*synth.affine_u4(22, "b", 16, 1024, 64), 16)]
+    x = synth.activations(22, "x", 1, 1024)
+    st, _ = _multi(ctx, t, x, None, 1e-6, 1024, 1)  # first tensor's rows are not a multiple of 16
+    assert st in (capi.BAD_ARGUMENT, capi.UNSUPPORTED)
+    t = [(*synth.affine_u4(22, "c", 16, 512, 64), 16)]
+    st, _ = _multi(ctx, t, synth.activations(22, "x2", 1, 512), None, 1e-6, 512, 1)  # cols % 1024
+    assert st in (capi.BAD_ARGUMENT, capi.UNSUPPORTED)
+
+
+@pytest.mark.parametrize("rows,cols,batch", [(12288, 4096, 1), (200, 1024, 4), (1024, 2048, 8)])
+def test_rmsnorm_affine_gate_up_swiglu(ctx, oracle, rows, cols, batch):
+    eps = 1e-6
+    gw, gs, gb = synth.affine_u4(23, "gate", rows, cols, 64)
+    uw, us, ub = synth.affine_u4(23, "up", rows, cols, 64)
+    x = synth.activations(23, "x", batch, cols)
+    nw = synth.normal_f16(23, "norm", (cols,), 0.1)
+    d = dev(ctx, gw, gs, gb, uw, us, ub, x, nw)
+    y = ctx.alloc(batch * rows * 2)
+    ctx.call("rmsnorm_affine_gate_up_swiglu", *d, C.c_float(eps), y, rows, cols, 64, batch)
+    xn = np.stack([oracle.rms_norm_1pw(x[b], nw, eps) for b in range(batch)])
+    ref = oracle.affine_gate_up_swiglu(gw, gs, gb, uw, us, ub, xn, rows, cols, 64, round_gate_up=False)
+    assert rel_err(y.download(np.float16, (batch, rows)), ref) < REL_TOL
+
+
+@pytest.mark.parametrize("position,layout", [(0, 1), (77, 1), (4095, 0), (32767, 1)])
+def test_rope_qkv_append_is_the_three_kernels(ctx, oracle, position, layout):
+    nq, nkv, d, cap = 8, 2, 128, 32768
+    base_log2 = float(np.log2(np.float32(1e6)))
+    q = synth.activations(24, "q", nq, d)
+    k = synth.activations(24, "k", nkv, d)
+    v = synth.activations(24, "v", nkv, d)
+    dq, dk, dv = dev(ctx, q, k, v)
+    kc = ctx.alloc(nkv * cap * d * 2).fill(0)
+    vc = ctx.alloc(nkv * cap * d * 2).fill(0)
+    ctx.call("rope_qkv_append", dq, dk, dv, kc, vc, cap, d, nq, nkv, layout, position, C.c_float(base_log2), 1, 0)
+    # the separate kernels on the same inputs: bit-identical results
+    dq2, dk2, dv2 = dev(ctx, q, k, v)
+    kc2 = ctx.alloc(nkv * cap * d * 2).fill(0)
+    vc2 = ctx.alloc(nkv * cap * d * 2).fill(0)
+    ctx.call("apply_rope", dq2, None, None, d, d, nq, layout, position, C.c_float(base_log2), 1, 1)
+    ctx.call("rope_kv_cache_update", kc2, dk2, None, None, cap, d, position, nkv, d, layout, C.c_float(base_log2), 1, 1, 0)
+    ctx.call("kv_cache_update", vc2, dv2, cap, d, position, nkv, 1, 0)
+    assert np.array_equal(dq.download(np.uint16, (nq, d)), dq2.download(np.uint16, (nq, d)))
+    assert np.array_equal(kc.download(np.uint16, (nkv, cap, d)), kc2.download(np.uint16, (nkv, cap, d)))
+    assert np.array_equal(vc.download(np.uint16, (nkv, cap, d)), vc2.download(np.uint16, (nkv, cap, d)))
+    # and the oracle
+    assert np.array_equal(dq.download(np.uint16, (nq * d,)), oracle.apply_rope(q, d, d, nq, layout, position, base_log2, 1).view(np.uint16).ravel())
+    refk = oracle.rope_kv_cache_update(np.zeros((nkv, cap, d), np.float16), k, cap, d, position, nkv, d, layout, base_log2, 1)
+    assert np.array_equal(kc.download(np.uint16, (nkv, cap, d)), refk.view(np.uint16).reshape(nkv, cap, d))
+    assert ctx.call_status("rope_qkv_append", dq, dk, dv, kc, vc, cap, d, nq, nkv, layout, cap, C.c_float(base_log2), 1, 0) == capi.OUT_OF_RANGE
+
+
 def test_affine_rejects_bad_arguments(ctx):
     d = ctx.alloc(4096)
     assert ctx.call_status("affine_matvec", d, d, d, d, d, 16, 100, 64, 1) == capi.BAD_ARGUMENT  # cols % group

@@ -21,7 +21,7 @@ def ctx():
     c.close()
 
 
-def make(ctx, cfg, seed, capacity, batch=1, fuse=False):
+def make(ctx, cfg, seed, capacity, batch=1, fuse=0):
     pkg = package.SyntheticPackage(cfg, seed)
     image, desc, layers = package.build_image(pkg, keep_for_oracle=True)
     return pkg, package.Decoder(ctx, image, desc, layers, capacity, batch, fuse_residual=fuse)
@@ -36,7 +36,8 @@ def test_decode_step_matches_oracle(ctx, oracle, cfg):
         got_tok = dec.decode_step([tok], pos)[0]
         ref_tok, ref_logits = ref.decode_step(int(tok), pos, want_logits=True)
         got_logits = dec.logits()[0]
-        assert rel_err(got_logits, ref_logits) < 2e-2, f"logits diverged at position {pos}"
+        err = rel_err(got_logits, ref_logits)
+        assert err < 2e-2, f"logits diverged at position {pos}: {err}"
         top2 = np.sort(ref_logits.astype(np.float32))[-2:]
         if top2[1] - top2[0] > 4 * np.spacing(np.float16(top2[1])):
             assert got_tok == ref_tok
@@ -57,6 +58,24 @@ def test_greedy_tokens_match_oracle_eager_graph_and_fused(ctx, oracle):
     assert first_bad is None or margins[first_bad] < 0.02, (first_bad, margins[first_bad] if first_bad is not None else None)
     _, fused = make(ctx, cfg, 5, cap, fuse=True)
     assert np.array_equal(fused.generate(prompt, n_dec, use_graph=True)[:, 0], graph), "fused residual add must not change tokens"
+
+
+def test_fused_table_keeps_tokens_and_logits(ctx, oracle):
+    """Norm folded into the projections, one Q/K/V launch, one RoPE + append launch: the same
+    rounding points, so the same greedy tokens as the reference-shaped table."""
+    cfg, cap, n_dec = MID, 64, 24
+    prompt = synth.rng_for(6, "prompt").integers(0, cfg.vocab, size=9).astype(np.int32)
+    _, plain = make(ctx, cfg, 6, cap)
+    want = plain.generate(prompt, n_dec, use_graph=True)[:, 0]
+    logits_plain = plain.logits()[0].copy()
+    _, fused = make(ctx, cfg, 6, cap, fuse=3)
+    assert len(fused.table) < len(plain.table) - 6 * cfg.layers
+    eager = fused.generate(prompt, n_dec, use_graph=False)[:, 0]
+    assert rel_err(fused.logits()[0], logits_plain) < 5e-3
+    fused.reset_cache()
+    graph = fused.generate(prompt, n_dec, use_graph=True)[:, 0]
+    assert np.array_equal(eager, graph)
+    assert np.array_equal(graph, want)
 
 
 def test_batch_of_independent_sequences(ctx, oracle):
