@@ -159,20 +159,8 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
             float rs = 0.f;
             if (a.norm_w) {
                 // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass
-                float ss = 0.f;
-                for (int c8 = tid; c8 < chunks; c8 += kThreads) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
-                    const float2 f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
-                    const float2 f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
-                    ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
-                }
-                ss = warp_sum(ss);
-                __syncthreads();  // sred is free here (no tile has been reduced yet) and between batch rows
-                if (lane == 0) sred[warp] = ss;
-                __syncthreads();
-                float tot = 0.f;
-#pragma unroll
-                for (int w8 = 0; w8 < 8; ++w8) tot += sred[w8];
+                // sred is free here: no tile has been reduced yet
+                const float tot = cta256_sumsq_f16(xr, a.cols, sred);
                 rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
             }
             for (int base = 0; base < chunks; base += kThreads) {
@@ -182,15 +170,8 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
                     uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
                     if (a.norm_w) {
                         const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
-                        uint32_t* vp = &v.x;
-                        const uint32_t* wp = &wv.x;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 xf = __half22float2(u32_as_h2(vp[j])), wf = __half22float2(u32_as_h2(wp[j]));
-                            const __half2 n = __floats2half2_rn(xf.x * rs, xf.y * rs);
-                            const __half2 dw = __floats2half2_rn(1.0f + wf.x, 1.0f + wf.y);
-                            vp[j] = h2_as_u32(__hmul2(dw, n));
-                        }
+                        v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
+                        v.z = rms_norm_1pw_pair(v.z, wv.z, rs); v.w = rms_norm_1pw_pair(v.w, wv.w, rs);
                     }
                     const float2 f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
                     const float2 f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
@@ -285,7 +266,6 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
                         for (int k = 0; k < 8; ++k) v += sred[(size_t)(k * 32 + lane) * (4 * NW) + s * 4 + i];
                         tot[s][i] = v;
                     }
-#pragma unroll
                 int first = 0, rows = a.rows;
                 __half* yout = a.y;
                 if (NW == 1) {

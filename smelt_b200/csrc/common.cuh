@@ -77,6 +77,20 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h);
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u);
+
+// Sum of squares of one fp16 row (cols a multiple of 8, 16-byte aligned) by a CTA of 256
+// threads, in a fixed order, so that every kernel that norms a row gets the same bits:
+// thread t folds the 8-element chunks t, t + 256, ... into one FMA chain, lanes combine by
+// xor-shuffle, the eight warp sums are added in warp order.  scratch: 8 floats of shared
+// memory that no thread reads or writes around the call.
+__device__ __forceinline__ float cta256_sumsq_f16(const __half* xr, int cols, float* scratch);
+
+// rms_norm_1pw's element step (Resources/Shaders/norms.metal:58-63) on two lanes:
+// half(x * rs) times half(1 + w) as an fp16 product.
+__device__ __forceinline__ uint32_t rms_norm_1pw_pair(uint32_t x2, uint32_t w2, float rs);
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // mma.sync m16n8k16, fp16 operands, fp32 accumulate.
@@ -106,6 +120,35 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+__device__ __forceinline__ float cta256_sumsq_f16(const __half* xr, int cols, float* scratch) {
+    float ss = 0.f;
+    for (int c8 = threadIdx.x; c8 < cols / 8; c8 += 256) {
+        const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(u32_as_h2(u[j]));
+            ss = __fmaf_rn(f.x, f.x, ss);
+            ss = __fmaf_rn(f.y, f.y, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot = __fadd_rn(tot, scratch[w]);
+    return tot;
+}
+
+__device__ __forceinline__ uint32_t rms_norm_1pw_pair(uint32_t x2, uint32_t w2, float rs) {
+    const float2 xf = __half22float2(u32_as_h2(x2)), wf = __half22float2(u32_as_h2(w2));
+    const __half2 n = __floats2half2_rn(__fmul_rn(xf.x, rs), __fmul_rn(xf.y, rs));
+    const __half2 dw = __floats2half2_rn(__fadd_rn(1.0f, wf.x), __fadd_rn(1.0f, wf.y));
+    return h2_as_u32(__hmul2(dw, n));
+}
 
 // ── mbarrier + bulk async copy (TMA, untiled) ───────────────────────────────
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

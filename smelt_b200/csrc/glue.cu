@@ -43,6 +43,28 @@ __global__ void rms_norm_1pw_kernel(const __half* __restrict__ x, const __half* 
     }
 }
 
+// The same norm for rows of 8k elements at 16-byte alignment: 256 threads, 16-byte loads and
+// stores, and the reduction order the matvec kernels with a folded norm use, so that a folded
+// norm and this kernel give the same bits.
+__global__ void __launch_bounds__(256) rms_norm_1pw_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                               __half* __restrict__ y, int dim, float eps, DevDyn dyn) {
+    __shared__ float scratch[8];
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const __half* xr = x + (size_t)blockIdx.x * dim;
+    __half* yr = y + (size_t)blockIdx.x * dim;
+    const float tot = cta256_sumsq_f16(xr, dim, scratch);
+    const float rs = __frcp_rn(__fsqrt_rn(tot / (float)dim + eps));
+    for (int c8 = threadIdx.x; c8 < dim / 8; c8 += 256) {
+        uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + c8 * 8);
+        v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
+        v.z = rms_norm_1pw_pair(v.z, wv.z, rs); v.w = rms_norm_1pw_pair(v.w, wv.w, rs);
+        *reinterpret_cast<uint4*>(yr + c8 * 8) = v;
+    }
+}
+
 // per_head_rms_norm (Resources/Shaders/attention_fused.metal:93-145): direct weight,
 // y = w * half(x * rs) as an fp16 product; one CTA per (batch row, head).
 __global__ void per_head_rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
@@ -428,6 +450,9 @@ cudaError_t launch_cfg(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttri
 
 cudaError_t launch_rms_norm_1pw(const Launch& l, const __half* x, const __half* w, __half* y, int dim, float eps,
                                 int batch) {
+    if (dim % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0) {
+        SMELT_LAUNCH(rms_norm_1pw_vec_kernel, dim3(batch), dim3(256), 0, x, w, y, dim, eps, dev_dyn(l));
+    }
     int threads = dim >= 4096 ? 1024 : (dim >= 1024 ? 512 : 256);
     SMELT_LAUNCH(rms_norm_1pw_kernel, dim3(batch), dim3(threads), 0, x, w, y, dim, eps, dev_dyn(l));
 }

@@ -153,6 +153,16 @@ def test_affine_dual_matvec(ctx, oracle):
 
 
 # ── fused extension kernels: same rounding points as the kernels they replace ──
+def _device_norm(ctx, x, nw, eps):
+    """rms_norm_1pw on the device (itself checked against the oracle below): a folded norm uses the
+    same reduction order, so the kernels that fold it are compared on these exact activations."""
+    batch, cols = x.shape
+    dx, dn = dev(ctx, x, nw)
+    dy = ctx.alloc(batch * cols * 2)
+    ctx.call("rms_norm_1pw", dx, dn, dy, cols, C.c_float(eps), batch)
+    return dy.download(np.float16, (batch, cols)), dy
+
+
 def _multi(ctx, tensors, x, norm_w, eps, cols, batch):
     arr = (capi.AffineTensor * len(tensors))()
     outs = []
@@ -176,9 +186,12 @@ def test_affine_multi_matvec(ctx, oracle, rows, cols, batch, norm):
     nw = synth.normal_f16(21, "norm", (cols,), 0.1) if norm else None
     st, got = _multi(ctx, tensors, x, nw, eps, cols, batch)
     assert st == 0, ctx.last_error()
-    xn = np.stack([oracle.rms_norm_1pw(x[b], nw, eps) for b in range(batch)]) if norm else x
+    xn, dxn = _device_norm(ctx, x, nw, eps) if norm else (x, ctx.to_device(x))
     for (w, s, b, r), g in zip(tensors, got):
         assert rel_err(g, oracle.affine_matvec(w, s, b, xn, r, cols, 64)) < REL_TOL
+        y = ctx.alloc(batch * r * 2)
+        ctx.call("affine_matvec", *dev(ctx, w, s, b), dxn, y, r, cols, 64, batch)
+        assert np.array_equal(g.view(np.uint16), y.download(np.uint16, (batch, r))), "one launch per tensor must give the same bits"
 
 
 def test_affine_multi_matvec_rejects_ineligible_shapes(ctx):
@@ -187,7 +200,8 @@ def test_affine_multi_matvec_rejects_ineligible_shapes(ctx):
     st, _ = _multi(ctx, t, x, None, 1e-6, 1024, 1)  # first tensor's rows are not a multiple of 16
     assert st in (capi.BAD_ARGUMENT, capi.UNSUPPORTED)
     t = [(*synth.affine_u4(22, "c", 16, 512, 64), 16)]
-    st, _ = _multi(ctx, t, synth.activations(22, "x2", 1, 512), None, 1e-6, 512, 1)  # cols % 1024
+    nw = synth.normal_f16(22, "norm", (512,), 0.1)
+    st, _ = _multi(ctx, t, synth.activations(22, "x2", 1, 512), nw, 1e-6, 512, 1)  # fused norm needs cols % 1024 == 0
     assert st in (capi.BAD_ARGUMENT, capi.UNSUPPORTED)
 
 
@@ -201,9 +215,12 @@ def test_rmsnorm_affine_gate_up_swiglu(ctx, oracle, rows, cols, batch):
     d = dev(ctx, gw, gs, gb, uw, us, ub, x, nw)
     y = ctx.alloc(batch * rows * 2)
     ctx.call("rmsnorm_affine_gate_up_swiglu", *d, C.c_float(eps), y, rows, cols, 64, batch)
-    xn = np.stack([oracle.rms_norm_1pw(x[b], nw, eps) for b in range(batch)])
+    xn, dxn = _device_norm(ctx, x, nw, eps)
     ref = oracle.affine_gate_up_swiglu(gw, gs, gb, uw, us, ub, xn, rows, cols, 64, round_gate_up=False)
     assert rel_err(y.download(np.float16, (batch, rows)), ref) < REL_TOL
+    y2 = ctx.alloc(batch * rows * 2)
+    ctx.call("affine_gate_up_swiglu", *d[:6], dxn, y2, rows, cols, 64, batch)
+    assert np.array_equal(y.download(np.uint16, (batch, rows)), y2.download(np.uint16, (batch, rows)))
 
 
 @pytest.mark.parametrize("position,layout", [(0, 1), (77, 1), (4095, 0), (32767, 1)])

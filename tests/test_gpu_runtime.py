@@ -36,8 +36,12 @@ def test_decode_step_matches_oracle(ctx, oracle, cfg):
         got_tok = dec.decode_step([tok], pos)[0]
         ref_tok, ref_logits = ref.decode_step(int(tok), pos, want_logits=True)
         got_logits = dec.logits()[0]
-        err = rel_err(got_logits, ref_logits)
-        assert err < 2e-2, f"logits diverged at position {pos}: {err}"
+        # Every kernel output may differ from the oracle's by an fp16 ulp (other fp32 summation
+        # order), and the differences travel through the layers: bound the worst logit error by
+        # one percent of the logits' RMS.
+        ref32 = ref_logits.astype(np.float32)
+        err = float(np.max(np.abs(got_logits.astype(np.float32) - ref32)) / np.sqrt(np.mean(ref32 * ref32)))
+        assert err < 1e-2, f"logits diverged at position {pos}: {err}"
         top2 = np.sort(ref_logits.astype(np.float32))[-2:]
         if top2[1] - top2[0] > 4 * np.spacing(np.float16(top2[1])):
             assert got_tok == ref_tok
@@ -71,7 +75,7 @@ def test_fused_table_keeps_tokens_and_logits(ctx, oracle):
     _, fused = make(ctx, cfg, 6, cap, fuse=3)
     assert len(fused.table) < len(plain.table) - 6 * cfg.layers
     eager = fused.generate(prompt, n_dec, use_graph=False)[:, 0]
-    assert rel_err(fused.logits()[0], logits_plain) < 5e-3
+    assert np.array_equal(fused.logits()[0].view(np.uint16), logits_plain.view(np.uint16)), "same rounding points, same bits"
     fused.reset_cache()
     graph = fused.generate(prompt, n_dec, use_graph=True)[:, 0]
     assert np.array_equal(eager, graph)
