@@ -331,6 +331,17 @@ SMELT_CUDA_API smelt_status smelt_cuda_attention_decode(smelt_cuda_ctx* ctx, con
                                                         const void* v_cache_dev, void* out_dev, int n_q, int n_kv,
                                                         int head_dim, uint32_t capacity, uint32_t seq_len, float scale,
                                                         uint32_t sliding_window, int batch, size_t kv_seq_stride);
+/* smelt_cuda_attention_decode with the split partials in a fixed 8 MiB device array instead of
+ * the context's allocation; same arguments, same results bit for bit.  This entry point has
+ * no counterpart in the reference.  It makes no device allocation on any call: the address of
+ * the array is looked up once per device on the first call (make that call before any stream
+ * capture begins).  Accepts batch * n_q * (head_dim + 2) <= 32768 and returns
+ * SMELT_ERR_OUT_OF_RANGE beyond that.  Nothing in the array has to start at zero, so it is
+ * never cleared.  All calls on one device share the array: calls that overlap in time race. */
+SMELT_CUDA_API smelt_status smelt_cuda_attention_decode_static(smelt_cuda_ctx* ctx, const void* q_dev, const void* k_cache_dev,
+                                                               const void* v_cache_dev, void* out_dev, int n_q, int n_kv,
+                                                               int head_dim, uint32_t capacity, uint32_t seq_len, float scale,
+                                                               uint32_t sliding_window, int batch, size_t kv_seq_stride);
 /* kv_cache_update / rope_kv_cache_update (attention.metal:122-209). cos/sin may be NULL in analytic mode. */
 SMELT_CUDA_API smelt_status smelt_cuda_kv_cache_update(smelt_cuda_ctx* ctx, void* cache_dev, const void* new_kv_dev,
                                                        uint32_t capacity, int head_dim, uint32_t position, int heads,
