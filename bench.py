@@ -118,7 +118,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", 0)) if world > 1 else 0
     cfg = package.FULL_MODEL
     B = args.batch
-    capacity = PROMPT_LEN + args.warmup + 2 * args.steps + 16
+    capacity = args.prompt_len + args.warmup + 2 * args.steps + 16
     ctx = capi.Context(local)
 
     if world > 1:
@@ -142,10 +142,10 @@ def run_ours(args):
     dec.build_graph()
     gen_s = time.time() - t0
 
-    prompts = np.stack([np.random.Generator(np.random.Philox(key=[SEED, 1000 + b])).integers(0, cfg.vocab, size=PROMPT_LEN) for b in range(B)]).astype(np.int32)
-    for i in range(PROMPT_LEN):  # the reference's no-prefill path: one decode step per prompt token
+    prompts = np.stack([np.random.Generator(np.random.Philox(key=[SEED, 1000 + b])).integers(0, cfg.vocab, size=args.prompt_len) for b in range(B)]).astype(np.int32)
+    for i in range(args.prompt_len):  # the reference's no-prefill path: one decode step per prompt token
         dec.graph_seed(prompts[:, i], i)
-        if i + 1 < PROMPT_LEN:
+        if i + 1 < args.prompt_len:
             dec.graph_decode(1, read=False)
 
     def barrier():
@@ -169,7 +169,7 @@ def run_ours(args):
     launches = ctx.lib.smelt_cuda_last_launch_count(ctx.h) * args.steps
 
     # ── e2e: K steps through the public graph_step call with host token buffers ──
-    pos = PROMPT_LEN - 1 + args.warmup + args.steps
+    pos = args.prompt_len - 1 + args.warmup + args.steps
     cur = np.zeros(B, np.int32)
     out = np.zeros(B, np.int32)
     ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, package.ARGMAX_SLOT, 0, cur.ctypes.data_as(C.c_void_p), B * 4))
@@ -193,16 +193,21 @@ def run_ours(args):
     if rank == 0:
         peak, peak_kind = measured_peaks()
         tok_s = args.steps * B / (dev_ms / 1e3)
-        ctx_len = PROMPT_LEN + args.warmup + args.steps // 2
+        ctx_len = args.prompt_len + args.warmup + args.steps // 2
         tb = token_bytes(cfg, ctx_len, B, world)
-        roof = kernel_roofline(ctx, dec, cfg, desc, world, peak, peak_kind)
+        wptr = C.c_void_p()
+        ctx._check(ctx.lib.smelt_cuda_slot_ptr(ctx.h, package.WEIGHTS_SLOT, C.byref(wptr), None))
+        base = wptr.value
+        tensors = [(base + L.gate.packed, base + L.gate.scales, base + L.gate.biases, base + L.up.packed, base + L.up.scales, base + L.up.biases)
+                   for L in (dec.layers[l] for l in range(cfg.layers))]
+        roof = kernel_roofline(ctx, tensors, desc.inter, desc.hidden, desc.group, peak, peak_kind)
         result = {
             "metric": "decode tok/s at batch 1 (1/2/4/8 B200); qmv achieved HBM GB/s vs 8 TB/s",
             "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "config4: full 36-layer 4096/12288 decoder, affine u4 g64, greedy decode after a 512-token prompt",
-                       "batch": B, "prompt_len": PROMPT_LEN, "parallelism": f"tp{world}",
+            "config": {"workload": "config4: full 36-layer 4096/12288 decoder, affine u4 g64, greedy decode after a %d-token prompt" % args.prompt_len,
+                       "batch": B, "prompt_len": args.prompt_len, "parallelism": f"tp{world}",
                        "table": args.table + (" (norm+QKV, RoPE+append, O+add, norm+gate/up+SwiGLU, down+add per layer)" if args.table == "fused" else " (the reference emitter's record sequence)"),
                        "l2_policy": "inputs larger than L2: each step streams %.2f GB of weights per GPU" % (tb["total"] / 1e9)},
             "e2e": {"value": args.steps * B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B + 4, "d2h_bytes_per_step": 4 * B},
@@ -223,40 +228,62 @@ def run_ours(args):
     return result
 
 
-def kernel_roofline(ctx, dec, cfg, desc, world, peak, peak_kind):
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at the full shape
+# (12288 x 4096 x 2), from the ncu capture summarised in profiles/; scaled by the weight bytes
+# for other shapes (the traffic is the weight stream).
+GATE_UP_TRAFFIC_FULL = 56.84e6
+
+
+def kernel_roofline(ctx, tensors, I, H, G, peak, peak_kind, reps=6):
     """The dominant kernel alone: the fused gate/up SwiGLU matvec (two [inter, hidden] u4 matrices
     per launch), launched over every layer's weights in turn so that consecutive launches never
-    share cached weights (36 x 56 MB per GPU >> L2), timed with CUDA events on the library's stream."""
-    from smelt_b200 import package
-
-    I, H, G = desc.inter, desc.hidden, desc.group
-    wptr, _ = C.c_void_p(), None
-    ctx._check(ctx.lib.smelt_cuda_slot_ptr(ctx.h, package.WEIGHTS_SLOT, C.byref(wptr), None))
-    base = wptr.value
+    share cached weights (the set is larger than L2), timed with CUDA events on the library's
+    stream.  tensors: per layer the six device addresses gate (w, s, b), up (w, s, b)."""
     x = ctx.to_device(np.random.default_rng(1).standard_normal(H).astype(np.float16))
     y = ctx.alloc(I * 2)
-    reps = 6
     def launch_all():
-        for l in range(cfg.layers):
-            L = dec.layers[l]
-            ctx.call("affine_gate_up_swiglu", base + L.gate.packed, base + L.gate.scales, base + L.gate.biases,
-                     base + L.up.packed, base + L.up.scales, base + L.up.biases, x, y, I, H, G, 1)
-    launch_all()
+        for t in tensors:
+            ctx.call("affine_gate_up_swiglu", *t, x, y, I, H, G, 1)
+    for _ in range(3):
+        launch_all()
     ctx.synchronize()
     ms = C.c_float(0)
     ctx.call("timer_start")
     for _ in range(reps):
         launch_all()
     ctx._check(ctx.lib.smelt_cuda_timer_stop(ctx.h, C.byref(ms)))
-    n = reps * cfg.layers
+    n = reps * len(tensors)
     per_launch_s = ms.value / 1e3 / n
     alg_bytes = 2 * I * H * 0.5625 + H * 2 + I * 2
     achieved = alg_bytes / per_launch_s / 1e9
-    return {"bound": "hbm", "kernel": "affine_mma_kernel<gate_up, g64, batch<=8> (fused_affine_gate_up_swiglu %dx%d x2)" % (I, H),
+    traffic = GATE_UP_TRAFFIC_FULL * (I * H) / (12288 * 4096) if GATE_UP_TRAFFIC_FULL else None
+    return {"bound": "hbm", "kernel": "affine_stream_kernel<gate_up> (fused_affine_gate_up_swiglu %dx%d x2, u4 g64, batch 1)" % (I, H),
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
             "frac_of_8tbs": achieved / 8000.0, "bytes_per_launch": alg_bytes, "us_per_launch": per_launch_s * 1e6,
-            "launches_timed": n, "traffic": None,
-            "note": "timed back to back with host launches; inside the decode graph the same kernel overlaps its weight prefetch with its predecessor"}
+            "launches_timed": n, "traffic": traffic,
+            "note": "timed alone, back to back, over %d distinct weight sets (%.0f MB, larger than L2)" % (len(tensors), len(tensors) * alg_bytes / 1e6)}
+
+
+def run_kernel_only(args):
+    """Only the dominant kernel, on a few layers' worth of synthetic gate/up weights: the small
+    case for profiler captures (a few hundred MB on the device)."""
+    from smelt_b200 import capi, package, synth
+
+    cfg = package.FULL_MODEL
+    I, H, G = cfg.inter, cfg.hidden, 64
+    ctx = capi.Context(0)
+    tensors = []
+    for l in range(args.kernel_layers):
+        gate = synth.affine_u4_model(SEED, f"k{l}.gate", I, H, G)
+        up = synth.affine_u4_model(SEED, f"k{l}.up", I, H, G)
+        tensors.append(tuple(ctx.to_device(a) for a in (*gate, *up)))
+    peak, peak_kind = measured_peaks()
+    roof = kernel_roofline(ctx, tensors, I, H, G, peak, peak_kind, reps=args.steps)
+    ctx.synchronize()
+    return {"metric": "qmv achieved HBM GB/s (gate/up kernel alone)", "value": roof["achieved"], "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": roof["us_per_launch"] / 1e3, "higher_is_better": True,
+            "config": {"workload": "kernel-only: fused gate/up SwiGLU matvec over %d weight sets" % args.kernel_layers},
+            "gpu_launches": (args.steps + 3) * args.kernel_layers, "roofline": roof}
 
 
 def cpu_baseline(pkg, cfg, budget_s: float, threads: int | None = None):
@@ -315,11 +342,17 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens decoded before the timed region (512 = the headline configuration; smaller for profiler captures)")
     ap.add_argument("--table", default="fused", choices=["fused", "reference"],
                     help="fused: the builder's fused record table; reference: the reference emitter's record sequence")
+    ap.add_argument("--kernel-only", action="store_true", help="time only the dominant kernel on a few synthetic weight sets (profiler captures)")
+    ap.add_argument("--kernel-layers", type=int, default=6)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.kernel_only:
+        result = run_kernel_only(args)
+    else:
+        result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result is not None:
         print(json.dumps(result), flush=True)
 
