@@ -221,11 +221,16 @@ def run_ours(args):
         }
         if keep:
             result["cpu_baseline"] = cpu_baseline(pkg, cfg, budget_s=25.0)
+    if result is not None:
+        print(json.dumps(result), flush=True)  # before any teardown, so that the line survives whatever follows
     ctx.synchronize()
     if dist is not None:
         dist.barrier()
+    dec.ctx = None
+    ctx.close()  # graphs, then the communicator
+    if dist is not None:
         dist.destroy_process_group()
-    return result
+    return None
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at the full shape

@@ -87,9 +87,13 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-    tp_destroy(ctx);
+    // Graphs first: a communicator waits for every graph that captured one of its collectives
+    // to be released before ncclCommDestroy returns.
     if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
     if (ctx->graph) cudaGraphDestroy(ctx->graph);
+    ctx->graph_exec = nullptr;
+    ctx->graph = nullptr;
+    tp_destroy(ctx);
     for (auto& s : ctx->slots)
         if (s.ptr) cudaFree(s.ptr);
     cudaFree(ctx->dyn_dev);

@@ -1,0 +1,31 @@
+"""Two-GPU tensor-parallel parity (skipped on a one-GPU box): see tp_worker.py."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu_count() -> int:
+    try:
+        out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
+    except (OSError, subprocess.TimeoutExpired):
+        return 0
+    return sum(1 for line in out.splitlines() if line.startswith("GPU "))
+
+
+def test_two_gpu_decode_matches_one_gpu():
+    if _gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "tp_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env)
+    assert p.returncode == 0 and "TP_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
