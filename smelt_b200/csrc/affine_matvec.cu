@@ -480,7 +480,9 @@ cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int
     }
     {
         bool handled = false;
-        cudaError_t e = launch_affine_stream(l, mode, args, group, &handled);
+        cudaError_t e = launch_affine_imma(l, mode, args, group, &handled);  // batch 1 and 2
+        if (handled || e != cudaSuccess) return e;
+        e = launch_affine_stream(l, mode, args, group, &handled);
         if (handled || e != cudaSuccess) return e;
         if (args.norm_w || args.nseg > 1) return cudaErrorNotSupported;  // only the streaming kernel fuses these
     }

@@ -44,5 +44,6 @@ struct AffineArgs {
 
 cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int group);
 cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
+cudaError_t launch_affine_imma(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
 
 }  // namespace smelt

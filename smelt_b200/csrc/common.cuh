@@ -80,8 +80,8 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h);
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u);
 
-// Sum of squares of one fp16 row (cols a multiple of 8, 16-byte aligned) by a CTA of 256
-// threads, in a fixed order, so that every kernel that norms a row gets the same bits:
+// Sum of squares of one fp16 row (cols a multiple of 8, 16-byte aligned) by the first 256
+// threads of a CTA (of 256 threads or more), in a fixed order, so that every kernel that norms a row gets the same bits:
 // thread t folds the 8-element chunks t, t + 256, ... into one FMA chain, lanes combine by
 // xor-shuffle, the eight warp sums are added in warp order.  scratch: 8 floats of shared
 // memory that no thread reads or writes around the call.
@@ -123,7 +123,7 @@ __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_c
 
 __device__ __forceinline__ float cta256_sumsq_f16(const __half* xr, int cols, float* scratch) {
     float ss = 0.f;
-    for (int c8 = threadIdx.x; c8 < cols / 8; c8 += 256) {
+    for (int c8 = threadIdx.x < 256 ? (int)threadIdx.x : cols; c8 < cols / 8; c8 += 256) {  // threads past 255 only join the barriers
         const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
         const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -135,7 +135,7 @@ __device__ __forceinline__ float cta256_sumsq_f16(const __half* xr, int cols, fl
     }
     ss = warp_sum(ss);
     __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = ss;
+    if ((threadIdx.x & 31) == 0 && threadIdx.x < 256) scratch[threadIdx.x >> 5] = ss;
     __syncthreads();
     float tot = 0.f;
 #pragma unroll

@@ -98,9 +98,55 @@ def test_affine_matvec_reference_fixture(ctx, oracle):
     assert np.max(np.abs(got)) > 1e-2
 
 
+# batch 1 and 2 run on the integer-MMA kernel: every mode, row / K tails, long K, few chunks per warp
+IMMA_SHAPES = [(4096, 4096, 1), (4096, 12288, 1), (100, 128, 2), (48, 256, 1), (1000, 2048, 2), (6144, 4096, 2), (16, 8192, 1)]
+
+
+@pytest.mark.parametrize("rows,cols,batch", IMMA_SHAPES)
+def test_affine_integer_mma_modes(ctx, oracle, rows, cols, batch):
+    a = synth.affine_u4(30, "a", rows, cols, 64)
+    b = synth.affine_u4(30, "b", rows, cols, 64)
+    x = synth.activations(30, "x", batch, cols)
+    res = synth.activations(30, "res", batch, rows)
+    d = dev(ctx, *a, *b, x, res)
+    y0, y1 = ctx.alloc(batch * rows * 2 + 64).fill(0xFF), ctx.alloc(batch * rows * 2)
+    ctx.call("affine_matvec", *d[:3], d[6], y0, rows, cols, 64, batch)
+    ref_a = oracle.affine_matvec(*a, x, rows, cols, 64)
+    assert rel_err(y0.download(np.float16, (batch, rows)), ref_a) < REL_TOL
+    assert np.all(y0.download(np.uint8, (64,), offset=batch * rows * 2) == 0xFF)
+    # against the fp32 oracle the fixed-point activations cost less than fp16 output rounding
+    ref32 = oracle.affine_matvec(*a, x, rows, cols, 64, f32=True)
+    assert rel_err(y0.download(np.float16, (batch, rows)), ref32) < 6e-4
+    ctx.call("affine_matvec_add", *d[:3], d[6], d[7], y1, rows, cols, 64, batch)
+    assert rel_err(y1.download(np.float16, (batch, rows)), oracle.affine_matvec_add(*a, x, res, rows, cols, 64)) < REL_TOL
+    ctx.call("affine_dual_matvec", *d[:7], y0, y1, rows, cols, 64, batch)
+    assert rel_err(y0.download(np.float16, (batch, rows)), ref_a) < REL_TOL
+    assert rel_err(y1.download(np.float16, (batch, rows)), oracle.affine_matvec(*b, x, rows, cols, 64)) < REL_TOL
+    ctx.call("affine_gate_up_swiglu", *d[:7], y0, rows, cols, 64, batch)
+    ref = oracle.affine_gate_up_swiglu(*a, *b, x, rows, cols, 64, round_gate_up=False)
+    assert rel_err(y0.download(np.float16, (batch, rows)), ref) < REL_TOL
+
+
+def test_affine_integer_mma_extreme_activations(ctx, oracle):
+    """One huge activation sets the fixed-point scale of the row; the small ones must still count."""
+    rows, cols = 256, 4096
+    w, s, b = synth.affine_u4(31, "w", rows, cols, 64)
+    x = (synth.activations(31, "x", 2, cols).astype(np.float32) * 1e-3).astype(np.float16)
+    x[0, 77] = np.float16(900.0)
+    x[1, :] = 0
+    x[1, 5] = np.float16(6e-5)
+    dw, ds, db, dx = dev(ctx, w, s, b, x)
+    y = ctx.alloc(2 * rows * 2)
+    ctx.call("affine_matvec", dw, ds, db, dx, y, rows, cols, 64, 2)
+    assert rel_err(y.download(np.float16, (2, rows)), oracle.affine_matvec(w, s, b, x, rows, cols, 64)) < REL_TOL
+    x[:] = 0
+    ctx.call("affine_matvec", dw, ds, db, ctx.to_device(x), y, rows, cols, 64, 2)
+    assert not np.any(y.download(np.uint16, (2, rows)) & 0x7FFF)  # all-zero activations give (signed) zeros
+
+
 def test_affine_batched_equals_iterated_bitwise(ctx):
     """Batched == iterated, bit for bit (the reference pins this GPU-vs-GPU, PrefillKernelTests.swift:9101-9993)."""
-    rows, cols, g, batch = 512, 2048, 64, 8
+    rows, cols, g, batch = 512, 2048, 64, 2
     w, s, b = synth.affine_u4(3, "bi", rows, cols, g)
     x = synth.activations(3, "x", batch, cols)
     dw, ds, db, dx = dev(ctx, w, s, b, x)
@@ -199,9 +245,9 @@ def test_affine_multi_matvec_rejects_ineligible_shapes(ctx):
     x = synth.activations(22, "x", 1, 1024)
     st, _ = _multi(ctx, t, x, None, 1e-6, 1024, 1)  # first tensor's rows are not a multiple of 16
     assert st in (capi.BAD_ARGUMENT, capi.UNSUPPORTED)
-    t = [(*synth.affine_u4(22, "c", 16, 512, 64), 16)]
-    nw = synth.normal_f16(22, "norm", (512,), 0.1)
-    st, _ = _multi(ctx, t, synth.activations(22, "x2", 1, 512), nw, 1e-6, 512, 1)  # fused norm needs cols % 1024 == 0
+    t = [(*synth.affine_u4(22, "c", 16, 192, 64), 16)]
+    nw = synth.normal_f16(22, "norm", (192,), 0.1)
+    st, _ = _multi(ctx, t, synth.activations(22, "x2", 1, 192), nw, 1e-6, 192, 1)  # a folded norm needs cols % 128 == 0
     assert st in (capi.BAD_ARGUMENT, capi.UNSUPPORTED)
 
 
