@@ -15,11 +15,11 @@
 // The int32 accumulators start at the bit pattern of 1.5 * 2^23, so that reinterpreted as
 // floats they read 12582912 + C and one FADD recovers C; no integer-to-float conversion runs.
 //
-// One persistent CTA of 16 warps per SM walks 16-row tiles.  Inside a tile warp w owns a
-// contiguous K range and streams it through its own ring of cp.async stages (128 columns
-// each: 16 rows x 64 bytes of nibbles, swizzled so that the fragment loads are conflict free,
-// plus the two groups' scales and biases).  A warp only waits for its own copies, so the main
-// loop has no CTA-wide barrier; the rings keep running across tiles.  The 16 K-partials of a
+// One persistent CTA per SM walks 16-row tiles.  Inside a tile warp w owns a contiguous K
+// range and streams it through its own ring of cp.async stages (two or four groups each: 16
+// rows x 64 or 128 bytes of nibbles, swizzled so that the fragment loads are conflict free,
+// plus the groups' scales and biases).  A warp only waits for its own copies, so the main
+// loop has no CTA-wide barrier; the rings keep running across tiles.  The K-partials of a
 // tile are added in warp order through shared memory (one barrier per tile), so results are
 // bit-reproducible.  Shared memory and registers are sized so that the CTAs of the next
 // launch fit beside this one: with programmatic dependent launch they become resident while
@@ -35,45 +35,54 @@ namespace {
 
 constexpr int kGroup = 64;
 constexpr int kTileRows = 16;
-constexpr int kChunkCols = 128;                        // two groups per ring stage
-constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
-constexpr int kSetW = kTileRows * (kChunkCols / 2);    // 1024 bytes of nibbles
-constexpr int kSetS = kTileRows * 4;                   // 2 fp16 scales per row
-constexpr int kSetBytes = kSetW + 2 * kSetS;           // 1152: [W | scales | biases]
 constexpr int kDigits = 4;
-constexpr uint32_t kMagic = 0x4B400000u;               // float 12582912 = 1.5 * 2^23
-constexpr float kMagicF = 12582912.0f;
+constexpr float kMagicF = 12582912.0f;                 // 1.5 * 2^23, bit pattern 0x4B400000
+
+// Geometry of one variant: WARPS warps per CTA, GPS groups (of 64 columns) per ring stage.
+template <int WARPS, int GPS>
+struct Geo {
+    static constexpr int kThreads = WARPS * 32;
+    static constexpr int kStageCols = GPS * kGroup;
+    static constexpr int kPitch = GPS * 32;                 // packed bytes per row per stage (64 or 128)
+    static constexpr int kSetW = kTileRows * kPitch;
+    static constexpr int kRowS = GPS * 2;                   // bytes of scales (or biases) per row per stage
+    static constexpr int kSetS = kTileRows * kRowS;
+    static constexpr int kSetBytes = kSetW + 2 * kSetS;     // [W | scales | biases]; a multiple of 128
+};
 
 struct ImmaLayout {
     uint32_t zero, xq, pitch_x, xsum, xscale, red, ring, stage_bytes, total;
 };
 
-__host__ __device__ inline ImmaLayout imma_layout(int nw, int depth, int cols, int batch) {
+__host__ __device__ inline ImmaLayout imma_layout(int nw, int depth, int warps, int set_bytes, int cols, int batch, int teams) {
     ImmaLayout L;
-    L.stage_bytes = (uint32_t)nw * kSetBytes;
+    L.stage_bytes = (uint32_t)nw * set_bytes;
     L.pitch_x = (uint32_t)cols + 64u;                  // one byte per column per plane; ≡ 64 (mod 128)
     uint32_t off = 0;
     L.zero = off; off += 64;
     L.xq = off; off += (uint32_t)(kDigits * batch) * L.pitch_x;
     L.xsum = off; off += (uint32_t)(cols / kGroup) * 2u * 4u;       // [group][batch slot 0/1]
     L.xscale = off; off += 16;
-    L.red = off; off += 2u * (uint32_t)nw * 2u * kTileRows * kWarps * 4u;  // [buffer][set][batch][row][warp]
+    L.red = off; off += (uint32_t)teams * 2u * (uint32_t)nw * 2u * kTileRows * 16u * 4u;  // [team][buffer][set][batch][row][warp slot, 16]
     off = (off + 127u) & ~127u;
-    L.ring = off; off += (uint32_t)kWarps * depth * L.stage_bytes;
+    L.ring = off; off += (uint32_t)warps * depth * L.stage_bytes;
     L.total = off;
     return L;
 }
 
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// D = A (u8, 16 x 32) * B (s8, 32 x 8) + C; C may name one register four times.
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1, int c0, int c1, int c2, int c3) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
 }
 
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
 }
 
 // Largest |v| of the eight fp16 values in a 16-byte word, as a float.
@@ -99,25 +108,36 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
-template <int MODE, int DEPTH>
-__global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineArgs a) {
+// TG tile groups per CTA: the CTA's warps form TG teams of WARPS / TG warps; each team walks its
+// own tiles (splitting K among its warps) and only synchronises with itself.
+template <int MODE, int DEPTH, int WARPS, int GPS, int TG>
+__global__ void __launch_bounds__(WARPS * 32, 1) affine_imma_kernel(const AffineArgs a) {
+    using G = Geo<WARPS, GPS>;
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    constexpr int kThreads = G::kThreads;
+    constexpr int LPR = G::kPitch / 16;   // lanes that copy one row of a stage (4 or 8)
+    constexpr int RPI = 32 / LPR;         // rows per copy instruction (8 or 4)
+    constexpr int NI = kTileRows / RPI;   // copy instructions per set and stage (2 or 4)
+    constexpr int WG = WARPS / TG;        // warps per team
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const ImmaLayout L = imma_layout(NW, DEPTH, a.cols, a.batch);
+    const int team = warp / WG, wl = warp % WG;
+    const ImmaLayout L = imma_layout(NW, DEPTH, WARPS, G::kSetBytes, a.cols, a.batch, TG);
     uint8_t* xq = smem + L.xq;
     float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
     float* sxscale = reinterpret_cast<float*>(smem + L.xscale);
-    float* sred = reinterpret_cast<float*>(smem + L.red);
+    float* sred0 = reinterpret_cast<float*>(smem + L.red);                      // staging scratch (whole CTA)
+    float* sred = sred0 + (size_t)team * (2 * NW * 2 * kTileRows * 16);          // this team's K-partials
     uint8_t* ring = smem + L.ring + (size_t)warp * DEPTH * L.stage_bytes;
 
     const int tiles_total = a.ks;  // filled by the launcher
-    const int nchunks = a.cols / kChunkCols;
-    const int cpw = (nchunks + kWarps - 1) / kWarps;  // chunks per warp: a contiguous K range
-    const int c_begin = min(warp * cpw, nchunks);
+    const int nchunks = a.cols / G::kStageCols;
+    const int cpw = (nchunks + WG - 1) / WG;  // stages per warp and tile: a contiguous K range
+    const int c_begin = min(wl * cpw, nchunks);
     const int cnt = min(c_begin + cpw, nchunks) - c_begin;
-    const int my_tiles = (int)blockIdx.x < tiles_total ? (tiles_total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int tile0 = (int)blockIdx.x * TG + team, tile_step = (int)gridDim.x * TG;
+    const int my_tiles = tile0 < tiles_total ? (tiles_total - 1 - tile0) / tile_step + 1 : 0;
     const int total_stages = my_tiles * cnt;
     const int groups_total = a.cols / kGroup;
 
@@ -131,47 +151,62 @@ __global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineAr
     };
 
     // ── producer side: each warp copies the stages it will consume ──
-    const int sw = ((g >> 1) & 1) << 1;  // 16-byte chunk swizzle of rows g and g + 8
-    int f_tile = blockIdx.x, f_j = 0, f_n = 0, f_slot = 0;
+    const int fr = lane / LPR, fc = lane % LPR;
+    const int fsw = GPS == 2 ? ((fr >> 1) & 1) << 1 : (fr & 3) << 1;  // 16-byte chunk swizzle of this lane's rows
+    const uint32_t f_dst = fr * G::kPitch + ((fc ^ fsw) * 16);
+    const uint32_t f_sdst = G::kSetW + (lane >> 4) * G::kSetS + (lane & 15) * G::kRowS;
+    int f_tile = tile0, f_j = 0, f_n = 0, f_slot = 0;
+    // per tile: the tensors and this lane's byte offsets into them (stage 0 of the warp's K range)
+    const uint8_t* f_w[NW];
+    const __half* f_sb[NW];
+    uint32_t f_woff = 0, f_soff = 0, f_rows_ok = 0;  // bit h: copy row fr + RPI * h; bit 8: copy the scale piece
+    auto fetch_tile = [&]() {
+        int row0 = f_tile * kTileRows, rows = a.rows;
+        if (NW == 1) {
+            int first;
+            const int sg = seg_of(f_tile, first);
+            row0 = (f_tile - first) * kTileRows;
+            rows = sg == 0 ? a.seg[0].rows : (sg == 1 ? a.seg[1].rows : a.seg[2].rows);
+            f_w[0] = sg == 0 ? a.seg[0].w : (sg == 1 ? a.seg[1].w : a.seg[2].w);
+            const __half* ss = sg == 0 ? a.seg[0].s : (sg == 1 ? a.seg[1].s : a.seg[2].s);
+            const __half* bb = sg == 0 ? a.seg[0].b : (sg == 1 ? a.seg[1].b : a.seg[2].b);
+            f_sb[0] = lane < 16 ? ss : bb;
+        } else {
+#pragma unroll
+            for (int s = 0; s < NW; ++s) { f_w[s] = a.w[s]; f_sb[s] = lane < 16 ? a.s[s] : a.b[s]; }
+        }
+        f_woff = (uint32_t)(row0 + fr) * (uint32_t)(a.cols / 2) + (uint32_t)c_begin * G::kPitch + fc * 16;
+        f_soff = ((uint32_t)(row0 + (lane & 15)) * (uint32_t)groups_total + (uint32_t)c_begin * GPS) * 2u;
+        f_rows_ok = 0;
+#pragma unroll
+        for (int h = 0; h < NI; ++h) f_rows_ok |= (row0 + fr + RPI * h < rows ? 1u : 0u) << h;
+        f_rows_ok |= (row0 + (lane & 15) < rows ? 1u : 0u) << 8;
+    };
+    if (total_stages > 0) fetch_tile();
     auto fetch = [&]() {
         if (f_n < total_stages) {
             uint8_t* st = ring + (size_t)f_slot * L.stage_bytes;
-            int row0 = f_tile * kTileRows, rows = a.rows;
-            const uint8_t* wsrc[NW];
-            const __half* ssrc[NW];
-            const __half* bsrc[NW];
-            if (NW == 1) {
-                int first;
-                const int sg = seg_of(f_tile, first);
-                row0 = (f_tile - first) * kTileRows;
-                rows = sg == 0 ? a.seg[0].rows : (sg == 1 ? a.seg[1].rows : a.seg[2].rows);
-                wsrc[0] = sg == 0 ? a.seg[0].w : (sg == 1 ? a.seg[1].w : a.seg[2].w);
-                ssrc[0] = sg == 0 ? a.seg[0].s : (sg == 1 ? a.seg[1].s : a.seg[2].s);
-                bsrc[0] = sg == 0 ? a.seg[0].b : (sg == 1 ? a.seg[1].b : a.seg[2].b);
-            } else {
-#pragma unroll
-                for (int s = 0; s < NW; ++s) { wsrc[s] = a.w[s]; ssrc[s] = a.s[s]; bsrc[s] = a.b[s]; }
-            }
-            const int ch = c_begin + f_j;
+            const uint32_t woff = f_woff + (uint32_t)f_j * G::kPitch;
+            const uint32_t soff = f_soff + (uint32_t)f_j * G::kRowS;
 #pragma unroll
             for (int s = 0; s < NW; ++s) {
-                uint8_t* dst = st + s * kSetBytes;
+                uint8_t* dst = st + s * G::kSetBytes;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int r = g + 8 * h;
-                    if (row0 + r < rows)
-                        cp_async16(dst + r * 64 + ((t ^ sw) * 16),
-                                   wsrc[s] + (size_t)(row0 + r) * (a.cols / 2) + (size_t)ch * 64 + t * 16);
-                }
-                const int r = lane & 15;  // lanes 0-15: the rows' two scales; lanes 16-31: their two biases
-                if (row0 + r < rows) {
-                    const __half* src = (lane < 16 ? ssrc[s] : bsrc[s]) + (size_t)(row0 + r) * groups_total + ch * 2;
-                    cp_async4(dst + kSetW + (lane >> 4) * kSetS + r * 4, src);
+                for (int h = 0; h < NI; ++h)
+                    if (f_rows_ok & (1u << h))
+                        cp_async16(dst + f_dst + h * RPI * G::kPitch, f_w[s] + woff + (uint32_t)(h * RPI) * (uint32_t)(a.cols / 2));
+                if (f_rows_ok & 0x100u) {
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(f_sb[s]) + soff;
+                    if (GPS == 2) cp_async4(dst + f_sdst, src); else cp_async8(dst + f_sdst, src);
                 }
             }
             ++f_n;
             f_slot = f_slot + 1 == DEPTH ? 0 : f_slot + 1;
-            if (++f_j == cnt) { f_j = 0; f_tile += gridDim.x; }
+            if (++f_j == cnt) {
+                f_j = 0;
+                f_tile += tile_step;
+                if (f_n < total_stages) fetch_tile();
+            }
         }
         cp_async_commit();  // always commit so that group counting stays uniform
     };
@@ -197,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineAr
             if (a.norm_w) {
                 // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass;
                 // sred is free here: no tile has been reduced yet
-                const float tot = cta256_sumsq_f16(xr, a.cols, sred);
+                const float tot = cta256_sumsq_f16(xr, a.cols, sred0);
                 rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
             }
             auto load8 = [&](int c8) {
@@ -213,11 +248,11 @@ __global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineAr
             for (int c8 = tid; c8 < chunks; c8 += kThreads) m = fmaxf(m, amax8(load8(c8)));
             m = warp_max(m);
             __syncthreads();
-            if (lane == 0) sred[16 + warp] = m;
+            if (lane == 0) sred0[16 + warp] = m;
             __syncthreads();
             float mx = 0.f;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, sred[16 + w]);
+            for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sred0[16 + w]);
             // S = 2^(e-126) > mx; X = x * 2^26 / S; results are scaled back by S / 2^26
             const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
             const bool live = e >= 26u && e < 255u;
@@ -263,12 +298,17 @@ __global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineAr
     const uint8_t* pb_base = bvalid ? xq + (size_t)g * L.pitch_x + t * 16 : smem + L.zero + t * 16;
     const int pb_stride = bvalid ? kGroup : 0;
     const float* pxs = sxsum + (t >> 1);  // this lane's columns belong to batch row t / 2
-    const int w_off0 = g * 64 + (((t >> 1) ^ sw) * 16) + (t & 1) * 8;        // group 0 of the stage, row g
-    const int w_off1 = g * 64 + (((2 + (t >> 1)) ^ sw) * 16) + (t & 1) * 8;  // group 1
-    const int s_off = kSetW + g * 4;
-    const int b_off = kSetW + kSetS + g * 4 + (t & 1) * 2;  // the bias product of group t & 1 is this lane's
+    const int csw = GPS == 2 ? ((g >> 1) & 1) << 1 : (g & 3) << 1;
+    int w_off[GPS];
+#pragma unroll
+    for (int gg = 0; gg < GPS; ++gg) w_off[gg] = g * G::kPitch + (((2 * gg + (t >> 1)) ^ csw) * 16) + (t & 1) * 8;
+    const int s_off = G::kSetW + g * G::kRowS;
+    // the bias products of groups (t & 1) * GPS / 2 ... of a stage are this lane's
+    const int bias_g0 = (t & 1) * (GPS / 2);
+    const int b_off = G::kSetW + G::kSetS + g * G::kRowS + bias_g0 * 2;
+    const int magic = 0x4B400000;
 
-    int c_tile = blockIdx.x, slot = 0;
+    int c_tile = tile0, slot = 0;
     for (int ti = 0; ti < my_tiles; ++ti) {
         float acc[NW][2], bacc[NW][2];
 #pragma unroll
@@ -279,32 +319,37 @@ __global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineAr
             fetch();                     // refill the buffer the previous stage used
             const uint8_t* st = ring + (size_t)slot * L.stage_bytes;
             slot = slot + 1 == DEPTH ? 0 : slot + 1;
-            const int grp0 = (c_begin + j) * 2;
-            const float xs = pxs[(grp0 + (t & 1)) * 2];
+            const int grp0 = (c_begin + j) * GPS;
 #pragma unroll
-            for (int s = 0; s < NW; ++s) {
-                const uint8_t* base = st + s * kSetBytes;
-                bacc[s][0] = fmaf(__half2float(*reinterpret_cast<const __half*>(base + b_off)), xs, bacc[s][0]);
-                bacc[s][1] = fmaf(__half2float(*reinterpret_cast<const __half*>(base + b_off + 32)), xs, bacc[s][1]);
+            for (int q = 0; q < GPS / 2; ++q) {
+                const float xs = pxs[(grp0 + bias_g0 + q) * 2];
+#pragma unroll
+                for (int s = 0; s < NW; ++s) {
+                    const uint8_t* base = st + s * G::kSetBytes + b_off + q * 2;
+                    bacc[s][0] = fmaf(__half2float(*reinterpret_cast<const __half*>(base)), xs, bacc[s][0]);
+                    bacc[s][1] = fmaf(__half2float(*reinterpret_cast<const __half*>(base + 8 * G::kRowS)), xs, bacc[s][1]);
+                }
             }
 #pragma unroll
-            for (int gg = 0; gg < 2; ++gg) {
+            for (int gg = 0; gg < GPS; ++gg) {
                 const uint4 xb = *reinterpret_cast<const uint4*>(pb_base + (grp0 + gg) * pb_stride);
 #pragma unroll
                 for (int s = 0; s < NW; ++s) {
-                    const uint8_t* base = st + s * kSetBytes;
-                    const uint2 wa = *reinterpret_cast<const uint2*>(base + (gg ? w_off1 : w_off0));
-                    const uint2 wb = *reinterpret_cast<const uint2*>(base + (gg ? w_off1 : w_off0) + 8 * 64);
-                    int c[4] = {(int)kMagic, (int)kMagic, (int)kMagic, (int)kMagic};
-                    mma_u8s8(c, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, xb.x, xb.y);
-                    mma_u8s8(c, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, xb.z, xb.w);
-                    const float2 sa = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off)));
-                    const float2 sb = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + s_off + 32)));
+                    const uint8_t* base = st + s * G::kSetBytes;
+                    const uint2 wa = *reinterpret_cast<const uint2*>(base + w_off[gg]);
+                    const uint2 wb = *reinterpret_cast<const uint2*>(base + w_off[gg] + 8 * G::kPitch);
+                    int c[4];
+                    mma_u8s8(c, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, xb.x, xb.y,
+                             magic, magic, magic, magic);
+                    mma_u8s8(c, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, xb.z, xb.w,
+                             c[0], c[1], c[2], c[3]);
+                    const float sa = __half2float(*reinterpret_cast<const __half*>(base + s_off + gg * 2));
+                    const float sb = __half2float(*reinterpret_cast<const __half*>(base + s_off + 8 * G::kRowS + gg * 2));
                     // columns 2t, 2t+1 hold neighbouring digit planes: 128 * high + low
                     const float va = fmaf(__int_as_float(c[0]) - kMagicF, 128.f, __int_as_float(c[1]) - kMagicF);
                     const float vb = fmaf(__int_as_float(c[2]) - kMagicF, 128.f, __int_as_float(c[3]) - kMagicF);
-                    acc[s][0] = fmaf(gg ? sa.y : sa.x, va, acc[s][0]);
-                    acc[s][1] = fmaf(gg ? sb.y : sb.x, vb, acc[s][1]);
+                    acc[s][0] = fmaf(sa, va, acc[s][0]);
+                    acc[s][1] = fmaf(sb, vb, acc[s][1]);
                 }
             }
         }
@@ -319,19 +364,20 @@ __global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineAr
                 const float tot = (t & 1) ? fmaf(other, 16384.f, mine) : fmaf(mine, 16384.f, other);
                 const float bs = bacc[s][h] + __shfl_xor_sync(0xffffffffu, bacc[s][h], 1);
                 if ((t & 1) == 0)
-                    sred[((((buf * NW + s) * 2 + (t >> 1)) * kTileRows) + g + 8 * h) * kWarps + warp] = fmaf(tot, xscale, bs);
+                    sred[((((buf * NW + s) * 2 + (t >> 1)) * kTileRows) + g + 8 * h) * 16 + wl] = fmaf(tot, xscale, bs);
             }
-        __syncthreads();
-        if (warp == (ti & (kWarps - 1))) {
-            // add the 16 K-partials in warp order, write out: lane -> (batch row, tile row)
+        if (TG == 1) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(WG * 32) : "memory");
+        if (wl == (ti % WG)) {
+            // add the K-partials in warp order, write out: lane -> (batch row, tile row)
             const int b = lane >> 4, r = lane & 15;
             float tot[NW];
 #pragma unroll
             for (int s = 0; s < NW; ++s) {
-                const float4* p = reinterpret_cast<const float4*>(sred + ((((buf * NW + s) * 2 + b) * kTileRows) + r) * kWarps);
+                const float4* p = reinterpret_cast<const float4*>(sred + ((((buf * NW + s) * 2 + b) * kTileRows) + r) * 16);
                 float v = 0.f;
 #pragma unroll
-                for (int q = 0; q < kWarps / 4; ++q) {
+                for (int q = 0; q < WG / 4; ++q) {
                     const float4 f = p[q];
                     v += f.x; v += f.y; v += f.z; v += f.w;
                 }
@@ -354,7 +400,7 @@ __global__ void __launch_bounds__(kThreads, 2) affine_imma_kernel(const AffineAr
                 else { a.y[o] = __float2half_rn(v0); a.y2[o] = __float2half_rn(tot[NW - 1]); }
             }
         }
-        c_tile += gridDim.x;
+        c_tile += tile_step;
     }
     cp_async_wait<0>();
 }
@@ -364,12 +410,14 @@ int env_int(const char* name, int dflt) {
     return e ? atoi(e) : dflt;
 }
 
-template <int MODE, int DEPTH>
+template <int MODE, int DEPTH, int WARPS, int GPS, int TG>
 cudaError_t launch_imma_t(const Launch& l, AffineArgs a) {
+    using G = Geo<WARPS, GPS>;
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    const ImmaLayout L = imma_layout(NW, DEPTH, a.cols, a.batch);
+    const ImmaLayout L = imma_layout(NW, DEPTH, WARPS, G::kSetBytes, a.cols, a.batch, TG);
+    if (L.total > 226u * 1024u) return cudaErrorNotSupported;  // digit planes too large to stay resident
     a.dyn = dev_dyn(l);
-    auto kern = affine_imma_kernel<MODE, DEPTH>;
+    auto kern = affine_imma_kernel<MODE, DEPTH, WARPS, GPS, TG>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
     if (e != cudaSuccess) return e;
     if (NW == 1 && a.nseg <= 1) {
@@ -382,8 +430,9 @@ cudaError_t launch_imma_t(const Launch& l, AffineArgs a) {
     a.ks = tiles;
     const int sm = a.sm_count > 0 ? a.sm_count : 148;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles < sm ? tiles : sm, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    const int want = (tiles + TG - 1) / TG;
+    cfg.gridDim = dim3(want < sm ? want : sm, 1, 1);
+    cfg.blockDim = dim3(G::kThreads, 1, 1);
     cfg.dynamicSmemBytes = L.total;
     cfg.stream = l.stream;
     cudaLaunchAttribute attr[1];
@@ -394,17 +443,23 @@ cudaError_t launch_imma_t(const Launch& l, AffineArgs a) {
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
+// Variant 0: 16 warps on one tile, two groups per stage; variant 1: 8 warps, four groups per
+// stage (needs cols % 256 == 0); variant 2: two teams of 8 warps, each on its own tile, two
+// groups per stage.  Ring depth: stages each warp keeps in flight + 1.
 template <int MODE>
 cudaError_t launch_imma_mode(const Launch& l, const AffineArgs& a, bool* handled) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    static const int forced = env_int("SMELT_IMMA_DEPTH", 0);
-    const int depth = forced ? forced : (NW == 2 ? 3 : 4);
-    if (depth != 3 && depth != 4 && depth != 6) return cudaErrorInvalidValue;
-    if (imma_layout(NW, depth, a.cols, a.batch).total > 226u * 1024u) return cudaSuccess;  // activations too large to stay resident
+    static const int variant_env = env_int("SMELT_IMMA_VARIANT", 1);
+    static const int depth_env = env_int("SMELT_IMMA_DEPTH", 0);
+    const int variant = (variant_env == 1 && a.cols % 256 != 0) ? 0 : variant_env;
+    const int depth = depth_env ? depth_env : (NW == 2 ? 3 : 4);
+    cudaError_t e;
+    if (variant == 0) e = depth == 3 ? launch_imma_t<MODE, 3, 16, 2, 1>(l, a) : launch_imma_t<MODE, 4, 16, 2, 1>(l, a);
+    else if (variant == 1) e = depth == 3 ? launch_imma_t<MODE, 3, 8, 4, 1>(l, a) : launch_imma_t<MODE, 4, 8, 4, 1>(l, a);
+    else e = depth == 3 ? launch_imma_t<MODE, 3, 16, 2, 2>(l, a) : launch_imma_t<MODE, 4, 16, 2, 2>(l, a);
+    if (e == cudaErrorNotSupported) return cudaSuccess;  // not handled: the caller falls back
     *handled = true;
-    if (depth == 3) return launch_imma_t<MODE, 3>(l, a);
-    if (depth == 4) return launch_imma_t<MODE, 4>(l, a);
-    return launch_imma_t<MODE, 6>(l, a);
+    return e;
 }
 
 }  // namespace
@@ -415,7 +470,7 @@ cudaError_t launch_imma_mode(const Launch& l, const AffineArgs& a, bool* handled
 cudaError_t launch_affine_imma(const Launch& l, int mode, const AffineArgs& a, int group, bool* handled) {
     *handled = false;
     static const int disabled = env_int("SMELT_AFFINE_NO_IMMA", 0);
-    if (disabled || group != kGroup || a.batch > 2 || a.cols % kChunkCols != 0) return cudaSuccess;
+    if (disabled || group != kGroup || a.batch > 2 || a.cols % 128 != 0) return cudaSuccess;
     const int nw = (mode == kAffineGateUp || mode == kAffineDual) ? 2 : 1;
     if (a.nseg > 1) {
         if (nw != 1 || a.nseg > 3 || mode != kAffinePlain) return cudaErrorInvalidValue;
