@@ -226,16 +226,35 @@ __global__ void __launch_bounds__(WARPS * 32, 1) affine_imma_kernel(const Affine
         if (tid < 4) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
         if (a.batch == 1)
             for (int i = tid; i < groups_total; i += kThreads) sxsum[i * 2 + 1] = 0.f;
+        // Rows of up to 4096 activations stay in registers between the passes (two 16-byte words
+        // per thread, the chunk order of cta256_sumsq_f16); longer rows are read again per pass.
+        const bool cached = kThreads == 256 && chunks <= 2 * 256;
         for (int b = 0; b < a.batch; ++b) {
             const __half* xr = a.x + (size_t)b * a.cols;
+            uint4 xc[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    if (tid + 256 * i < chunks) xc[i] = *reinterpret_cast<const uint4*>(xr + (tid + 256 * i) * 8);
+            }
             float rs = 0.f;
             if (a.norm_w) {
                 // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass;
                 // sred is free here: no tile has been reduced yet
-                const float tot = cta256_sumsq_f16(xr, a.cols, sred0);
+                const float tot = cached ? cta256_sum_finish(sumsq8(sumsq8(0.f, xc[0]), xc[1]), sred0) : cta256_sumsq_f16(xr, a.cols, sred0);
                 rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
+                if (cached) {
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+                        if (tid + 256 * i < chunks) {
+                            const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + (tid + 256 * i) * 8);
+                            xc[i].x = rms_norm_1pw_pair(xc[i].x, wv.x, rs); xc[i].y = rms_norm_1pw_pair(xc[i].y, wv.y, rs);
+                            xc[i].z = rms_norm_1pw_pair(xc[i].z, wv.z, rs); xc[i].w = rms_norm_1pw_pair(xc[i].w, wv.w, rs);
+                        }
+                }
             }
             auto load8 = [&](int c8) {
+                if (cached) return c8 < 256 ? xc[0] : xc[1];  // c8 = tid or tid + 256
                 uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
                 if (a.norm_w) {
                     const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
@@ -440,6 +459,7 @@ cudaError_t launch_imma_t(const Launch& l, AffineArgs a) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(kern);
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 

@@ -431,6 +431,7 @@ cudaError_t launch_t(const Launch& l, AffineArgs a) {
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
+    prefer_max_shared(kern);
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 

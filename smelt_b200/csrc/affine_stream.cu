@@ -327,6 +327,7 @@ cudaError_t launch_stream_t(const Launch& l, AffineArgs a, int ctas_per_sm) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(kern);
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 

@@ -281,6 +281,7 @@ cudaError_t launch_decode_t(const Launch& l, const AttnDev& p) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(kern);
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
@@ -332,6 +333,7 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(attn_merge_kernel);
     return cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
 }
 

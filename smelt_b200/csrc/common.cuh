@@ -121,18 +121,21 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
-__device__ __forceinline__ float cta256_sumsq_f16(const __half* xr, int cols, float* scratch) {
-    float ss = 0.f;
-    for (int c8 = threadIdx.x < 256 ? (int)threadIdx.x : cols; c8 < cols / 8; c8 += 256) {  // threads past 255 only join the barriers
-        const uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+// One 16-byte word (eight fp16 values) folded into a running sum of squares, as an FMA chain.
+__device__ __forceinline__ float sumsq8(float ss, const uint4& v) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(u32_as_h2(u[j]));
-            ss = __fmaf_rn(f.x, f.x, ss);
-            ss = __fmaf_rn(f.y, f.y, ss);
-        }
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(u32_as_h2(u[j]));
+        ss = __fmaf_rn(f.x, f.x, ss);
+        ss = __fmaf_rn(f.y, f.y, ss);
     }
+    return ss;
+}
+
+// The per-thread sums of the first 256 threads combined: lanes by xor-shuffle, then the eight
+// warp sums in warp order.  Every thread of the CTA must call it (two barriers inside).
+__device__ __forceinline__ float cta256_sum_finish(float ss, float* scratch) {
     ss = warp_sum(ss);
     __syncthreads();
     if ((threadIdx.x & 31) == 0 && threadIdx.x < 256) scratch[threadIdx.x >> 5] = ss;
@@ -141,6 +144,13 @@ __device__ __forceinline__ float cta256_sumsq_f16(const __half* xr, int cols, fl
 #pragma unroll
     for (int w = 0; w < 8; ++w) tot = __fadd_rn(tot, scratch[w]);
     return tot;
+}
+
+__device__ __forceinline__ float cta256_sumsq_f16(const __half* xr, int cols, float* scratch) {
+    float ss = 0.f;
+    for (int c8 = threadIdx.x < 256 ? (int)threadIdx.x : cols; c8 < cols / 8; c8 += 256)  // threads past 255 only join the barriers
+        ss = sumsq8(ss, *reinterpret_cast<const uint4*>(xr + c8 * 8));
+    return cta256_sum_finish(ss, scratch);
 }
 
 __device__ __forceinline__ uint32_t rms_norm_1pw_pair(uint32_t x2, uint32_t w2, float rs) {
@@ -197,5 +207,14 @@ __device__ __forceinline__ void cp_async_wait() {
 // Error word shared by all kernels of a context: 0 = ok; kernels OR in a code when a bounded
 // wait gives up so the host can report it instead of hanging.
 enum : uint32_t { KERR_BARRIER_TIMEOUT = 1u, KERR_FLAG_TIMEOUT = 2u };
+
+// Every kernel of a decode step asks for the same shared-memory carve-out (the largest): an SM
+// drains before it changes its L1 / shared-memory split, so kernels that prefer different
+// splits can neither overlap nor follow each other without a gap.
+template <typename Kernel>
+inline cudaError_t prefer_max_shared(Kernel kernel) {
+    return cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributePreferredSharedMemoryCarveout,
+                                (int)cudaSharedmemCarveoutMaxShared);
+}
 
 }  // namespace smelt

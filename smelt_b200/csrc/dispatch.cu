@@ -672,6 +672,7 @@ smelt_status write_dynamic(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t p
     if (!ts.ptr || ts.bytes < B * 4 || !ps.ptr || ps.bytes < 4) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "token / position slots are missing or too small");
     TokenPack pack = {};
     for (uint32_t b = 0; b < B; ++b) pack.t[b] = tokens[b];
+    prefer_max_shared(set_dynamic_kernel);
     set_dynamic_kernel<<<1, 64, 0, ctx->stream>>>(pack, position, (int)B, (int32_t*)ts.ptr, (int32_t*)ps.ptr, ctx->dyn_dev);
     return check_cuda(ctx, cudaGetLastError(), "write dynamic state");
 }
@@ -776,6 +777,7 @@ smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_re
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr; cfg.numAttrs = ctx->pdl ? 1 : 0;
+        prefer_max_shared(advance_kernel);
         s = check_cuda(ctx, cudaLaunchKernelEx(&cfg, advance_kernel, (const int32_t*)as.ptr, (int32_t*)ts.ptr, (int32_t*)ps.ptr, ctx->dyn_dev, ctx->gen_ring, ctx->gen_count, ctx->gen_capacity, (int)B), "advance kernel");
         ctx->launch_count += 1;
     }

@@ -443,6 +443,7 @@ cudaError_t launch_cfg(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttri
         cudaLaunchConfig_t cfg;                                      \
         cudaLaunchAttribute attr[1];                                 \
         launch_cfg(l, cfg, attr, grid, block, smem);                 \
+        prefer_max_shared(kernel);                                   \
         return cudaLaunchKernelEx(&cfg, kernel, __VA_ARGS__);        \
     } while (0)
 
@@ -548,9 +549,11 @@ cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x
         cudaError_t e;
         if (nb == 1) {
             e = cudaFuncSetAttribute(fp16_matvec_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            prefer_max_shared(fp16_matvec_kernel<1>);
             if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fp16_matvec_kernel<1>, w, x + (size_t)b0 * cols, y + (size_t)b0 * rows, rows, cols, nb, dev_dyn(l));
         } else {
             e = cudaFuncSetAttribute(fp16_matvec_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            prefer_max_shared(fp16_matvec_kernel<8>);
             if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fp16_matvec_kernel<8>, w, x + (size_t)b0 * cols, y + (size_t)b0 * rows, rows, cols, nb, dev_dyn(l));
         }
         if (e != cudaSuccess) return e;

@@ -60,6 +60,7 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     if (!ctx) return SMELT_ERR_ALLOC;
     ctx->device = device_ordinal;
     ctx->sm_count = prop.multiProcessorCount;
+    if (const char* e = getenv("SMELT_NO_PDL")) ctx->pdl = atoi(e) == 0;  // diagnostic: launch without programmatic dependent launch
     ctx->slots.resize(256);
     bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->dyn_dev, sizeof(DynState)) == cudaSuccess;

@@ -114,6 +114,7 @@ cudaError_t launch_nb(const Launch& l, const SignedArgs& a) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(kern);
     return cudaLaunchKernelEx(&cfg, kern, a, dev_dyn(l));
 }
 
