@@ -186,6 +186,16 @@ SMELT_CUDA_API smelt_status smelt_cuda_graph_step(smelt_cuda_ctx* ctx, const int
  * second one, waits for it and returns the elapsed milliseconds between the two. */
 SMELT_CUDA_API smelt_status smelt_cuda_timer_start(smelt_cuda_ctx* ctx);
 SMELT_CUDA_API smelt_status smelt_cuda_timer_stop(smelt_cuda_ctx* ctx, float* out_ms);
+/* Caller-driven capture: every launch made through this context between capture_begin and
+ * capture_end (typed launchers, smelt_cuda_enqueue_decode) is recorded instead of run, the way
+ * encodeTrunkDecode records into a caller-owned encoder without committing it
+ * (SmeltRuntime.swift:5029-5091).  capture_replay runs the recorded sequence `warmup` times
+ * untimed, then `reps` times between two events, and returns the mean device time of one
+ * replay in milliseconds.  Nothing may allocate or synchronise between begin and end; a new
+ * capture_begin discards the previous recording. */
+SMELT_CUDA_API smelt_status smelt_cuda_capture_begin(smelt_cuda_ctx* ctx);
+SMELT_CUDA_API smelt_status smelt_cuda_capture_end(smelt_cuda_ctx* ctx);
+SMELT_CUDA_API smelt_status smelt_cuda_capture_replay(smelt_cuda_ctx* ctx, int warmup, int reps, float* out_ms_per_replay);
 /* Number of kernel launches one interpretation of the last built / enqueued table issues. */
 SMELT_CUDA_API int smelt_cuda_last_launch_count(const smelt_cuda_ctx* ctx);
 

@@ -88,6 +88,8 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->user_graph_exec) cudaGraphExecDestroy(ctx->user_graph_exec);
+    ctx->user_graph_exec = nullptr;
     // Graphs first: a communicator waits for every graph that captured one of its collectives
     // to be released before ncclCommDestroy returns.
     if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
@@ -133,6 +135,44 @@ smelt_status smelt_cuda_device_error(smelt_cuda_ctx* ctx, uint32_t* out_flags) {
         return fail(ctx, SMELT_ERR_DEVICE_TIMEOUT, "a kernel's bounded wait gave up (flags " + std::to_string(*out_flags) + ")");
     }
     return SMELT_OK;
+}
+
+smelt_status smelt_cuda_capture_begin(smelt_cuda_ctx* ctx) {
+    CTX_OR_FAIL();
+    if (ctx->capturing) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "capture_begin: a capture is already open");
+    if (ctx->user_graph_exec) { cudaGraphExecDestroy(ctx->user_graph_exec); ctx->user_graph_exec = nullptr; }
+    smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "capture_begin: sync");
+    if (s) return s;
+    s = check_cuda(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    if (!s) ctx->capturing = true;
+    return s;
+}
+
+smelt_status smelt_cuda_capture_end(smelt_cuda_ctx* ctx) {
+    CTX_OR_FAIL();
+    if (!ctx->capturing) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "capture_end: no capture is open");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    smelt_status s = check_cuda(ctx, cudaStreamEndCapture(ctx->stream, &g), "cudaStreamEndCapture");
+    if (s) return s;
+    s = check_cuda(ctx, cudaGraphInstantiate(&ctx->user_graph_exec, g, 0), "cudaGraphInstantiate");
+    cudaGraphDestroy(g);
+    return s;
+}
+
+smelt_status smelt_cuda_capture_replay(smelt_cuda_ctx* ctx, int warmup, int reps, float* out_ms) {
+    CTX_OR_FAIL();
+    if (!ctx->user_graph_exec || reps <= 0 || warmup < 0 || !out_ms) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "capture_replay: nothing recorded, or bad counts");
+    smelt_status s = SMELT_OK;
+    for (int i = 0; i < warmup && !s; ++i) s = check_cuda(ctx, cudaGraphLaunch(ctx->user_graph_exec, ctx->stream), "cudaGraphLaunch");
+    if (!s) s = check_cuda(ctx, cudaEventRecord(ctx->ev_start, ctx->stream), "capture_replay: start event");
+    for (int i = 0; i < reps && !s; ++i) s = check_cuda(ctx, cudaGraphLaunch(ctx->user_graph_exec, ctx->stream), "cudaGraphLaunch");
+    if (!s) s = check_cuda(ctx, cudaEventRecord(ctx->ev_stop, ctx->stream), "capture_replay: stop event");
+    if (!s) s = check_cuda(ctx, cudaEventSynchronize(ctx->ev_stop), "capture_replay: sync");
+    float ms = 0.f;
+    if (!s) s = check_cuda(ctx, cudaEventElapsedTime(&ms, ctx->ev_start, ctx->ev_stop), "capture_replay: elapsed");
+    if (!s) *out_ms = ms / (float)reps;
+    return s;
 }
 
 smelt_status smelt_cuda_timer_start(smelt_cuda_ctx* ctx) {
@@ -291,7 +331,7 @@ smelt_status smelt_cuda_configure(smelt_cuda_ctx* ctx, const smelt_cuda_runtime_
 static Launch typed_launch(smelt_cuda_ctx* ctx) {
     Launch l;
     l.stream = ctx->stream;
-    l.pdl = false;
+    l.pdl = ctx->capturing && ctx->pdl;  // inside a capture the launches chain like a decode table's
     return l;
 }
 

@@ -84,6 +84,7 @@ struct smelt_cuda_ctx {
     // graph replay
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
+    cudaGraphExec_t user_graph_exec = nullptr;  // smelt_cuda_capture_begin / _end / _replay
     int32_t* gen_ring = nullptr;   // device: generated ids, step-major
     uint32_t* gen_count = nullptr; // device: steps written
     uint32_t gen_capacity = 0;

@@ -158,3 +158,21 @@ def test_skip_guards_follow_position(ctx):
             out = np.empty(32, np.float16)
             ctx.call("read_slot", 203, C.c_size_t(0), out, C.c_size_t(64))
             assert bool(out.any()) == ran[i], (pos, i)
+
+
+def test_capture_replay_runs_the_recorded_launches(ctx, oracle):
+    rows, cols = 512, 2048
+    w, s, b = synth.affine_u4(9, "cap", rows, cols, 64)
+    x = synth.activations(9, "x", 1, cols)
+    dw, ds, db, dx = (ctx.to_device(a) for a in (w, s, b, x))
+    y = ctx.alloc(rows * 2).fill(0)
+    ctx.call("capture_begin")
+    ctx.call("affine_matvec", dw, ds, db, dx, y, rows, cols, 64, 1)
+    assert ctx.call_status("capture_begin") == capi.BAD_ARGUMENT  # already open
+    ctx.call("capture_end")
+    assert not np.any(y.download(np.uint16, (rows,)))  # recorded, not run
+    ms = C.c_float(-1)
+    ctx._check(ctx.lib.smelt_cuda_capture_replay(ctx.h, 1, 3, C.byref(ms)))
+    assert 0 < ms.value < 50
+    assert rel_err(y.download(np.float16, (1, rows)), oracle.affine_matvec(w, s, b, x, rows, cols, 64)) < 2e-3
+    assert ctx.call_status("capture_end") == capi.BAD_ARGUMENT  # nothing open
