@@ -249,14 +249,16 @@ def kernel_roofline(ctx, tensors, I, H, G, peak, peak_kind, reps=6):
     def launch_all():
         for t in tensors:
             ctx.call("affine_gate_up_swiglu", *t, x, y, I, H, G, 1)
-    for _ in range(3):
-        launch_all()
+    launch_all()  # eager once: sets the kernel attributes
     ctx.synchronize()
+    # one pass over every weight set recorded, then replayed between two CUDA events on the
+    # library's stream: no host launch overhead inside the timed region
+    ctx.call("capture_begin")
+    launch_all()
+    ctx.call("capture_end")
     ms = C.c_float(0)
-    ctx.call("timer_start")
-    for _ in range(reps):
-        launch_all()
-    ctx._check(ctx.lib.smelt_cuda_timer_stop(ctx.h, C.byref(ms)))
+    ctx._check(ctx.lib.smelt_cuda_capture_replay(ctx.h, 3, reps, C.byref(ms)))
+    ms = C.c_float(ms.value * reps)
     n = reps * len(tensors)
     per_launch_s = ms.value / 1e3 / n
     alg_bytes = 2 * I * H * 0.5625 + H * 2 + I * 2
@@ -266,7 +268,7 @@ def kernel_roofline(ctx, tensors, I, H, G, peak, peak_kind, reps=6):
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
             "frac_of_8tbs": achieved / 8000.0, "bytes_per_launch": alg_bytes, "us_per_launch": per_launch_s * 1e6,
             "launches_timed": n, "traffic": traffic,
-            "note": "timed alone, back to back, over %d distinct weight sets (%.0f MB, larger than L2)" % (len(tensors), len(tensors) * alg_bytes / 1e6)}
+            "note": "timed alone: a recorded pass over %d distinct weight sets (%.0f MB, larger than L2) replayed back to back" % (len(tensors), len(tensors) * alg_bytes / 1e6)}
 
 
 def run_kernel_only(args):

@@ -51,5 +51,6 @@ struct SignedArgs {
     int rows, cols, batch, bits;
 };
 cudaError_t launch_signed(const Launch& l, int mode, const SignedArgs& a);
+cudaError_t launch_signed_imma(const Launch& l, int mode, const SignedArgs& a, int sm_count, bool* handled);
 
 }  // namespace smelt

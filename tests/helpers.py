@@ -23,3 +23,14 @@ def ulp_diff_f16(a, b) -> np.ndarray:
         u = np.asarray(x, np.float16).view(np.uint16).astype(np.int32)
         return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
     return np.abs(key(a) - key(b))
+
+
+def add_rel_err(got, ref, summand) -> float:
+    """Error metric for y = half(half(acc) + residual): where acc and the residual cancel, the
+    fp16 rounding of acc (|acc| 2^-11) is large next to |y|, so the error is measured against
+    max(|y|, |acc|) with the same floor as rel_err.  summand: the oracle's acc as fp16."""
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    acc = np.asarray(summand, np.float64).reshape(-1)
+    floor = np.sqrt(np.mean(ref * ref)) / 8.0
+    return float(np.max(np.abs(got - ref) / np.maximum(np.maximum(np.abs(ref), np.abs(acc)), max(floor, 1e-30))))

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from smelt_b200 import capi, synth
-from helpers import REL_TOL, rel_err, ulp_diff_f16
+from helpers import REL_TOL, add_rel_err, rel_err, ulp_diff_f16
 
 pytestmark = pytest.mark.gpu
 
@@ -402,6 +402,29 @@ def test_signed_matvec_add_and_gate_up(ctx, oracle, fmt, maker):
     assert rel_err(got, staged) < 4e-3  # a one-ulp flip of gate or up moves the staged fp16 chain by a few ulp
     g32 = got.astype(np.float32)
     assert np.all(np.abs(g32 - plain) <= np.maximum(0.03, np.abs(plain) * 0.015))  # the reference's tolerance (:1227-1232)
+
+
+@pytest.mark.parametrize("fmt,maker", [(1, synth.binary1), (2, synth.ternary2)])
+@pytest.mark.parametrize("rows,cols,batch", [(1024, 5120, 2), (100, 512, 1), (48, 1536, 2), (17408, 5120, 1)])
+def test_signed_integer_mma_modes(ctx, oracle, fmt, maker, rows, cols, batch):
+    """Batch 1 and 2 with cols % 512 == 0 run on the integer-MMA kernel: every mode, row tails, uneven K split."""
+    gc, gs = maker(32, "g", rows, cols)
+    uc, us = maker(32, "u", rows, cols)
+    x = synth.activations(32, "x", batch, cols)
+    res = synth.activations(32, "r", batch, rows)
+    dgc, dgs, duc, dus, dx, dr = dev(ctx, gc, gs, uc, us, x, res)
+    y = ctx.alloc(batch * rows * 2 + 64).fill(0xFF)
+    ctx.call("signed_matvec", fmt, dgc, dgs, dx, y, rows, cols, batch)
+    got = y.download(np.float16, (batch, rows))
+    assert rel_err(got, oracle.signed_matvec(fmt, gc, gs, x, rows, cols)) < REL_TOL
+    assert rel_err(got, oracle.signed_matvec(fmt, gc, gs, x, rows, cols, f32=True)) < 6e-4  # fp16 output rounding only
+    assert np.all(y.download(np.uint8, (64,), offset=batch * rows * 2) == 0xFF)
+    ctx.call("signed_matvec_add", fmt, dgc, dgs, dx, dr, y, rows, cols, batch)
+    assert add_rel_err(y.download(np.float16, (batch, rows)), oracle.signed_matvec_add(fmt, gc, gs, x, res, rows, cols),
+                       oracle.signed_matvec(fmt, gc, gs, x, rows, cols)) < REL_TOL
+    ctx.call("signed_gate_up_swiglu", fmt, dgc, dgs, duc, dus, dx, y, rows, cols, batch)
+    staged = oracle.signed_gate_up_swiglu(fmt, gc, gs, uc, us, x, rows, cols, staged=True)
+    assert rel_err(y.download(np.float16, (batch, rows)), staged) < 4e-3
 
 
 # ── attention ───────────────────────────────────────────────────────────────
