@@ -341,6 +341,15 @@ SMELT_CUDA_API smelt_status smelt_cuda_attention_decode(smelt_cuda_ctx* ctx, con
                                                         const void* v_cache_dev, void* out_dev, int n_q, int n_kv,
                                                         int head_dim, uint32_t capacity, uint32_t seq_len, float scale,
                                                         uint32_t sliding_window, int batch, size_t kv_seq_stride);
+/* Extension (no single reference kernel): apply_rope on q, rope_kv_cache_update of the new K
+ * row, kv_cache_update of the new V row (attention.metal:48-209, full-head analytic mode,
+ * layout 0 adjacent / 1 split-half) and attention_decode over keys [.., position] in one
+ * launch, with the rounding points of the four kernels.  q is not modified; out may alias q. */
+SMELT_CUDA_API smelt_status smelt_cuda_rope_attention_decode(smelt_cuda_ctx* ctx, const void* q_dev, const void* k_new_dev,
+                                                             const void* v_new_dev, void* k_cache_dev, void* v_cache_dev,
+                                                             void* out_dev, int n_q, int n_kv, int head_dim, uint32_t capacity,
+                                                             uint32_t position, float scale, uint32_t sliding_window, int layout,
+                                                             float base_log2, int batch, size_t kv_seq_stride);
 /* smelt_cuda_attention_decode with the split partials in a fixed 8 MiB device array instead of
  * the context's allocation; same arguments, same results bit for bit.  This entry point has
  * no counterpart in the reference.  It makes no device allocation on any call: the address of

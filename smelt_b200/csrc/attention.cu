@@ -19,6 +19,7 @@
 // significant bits of p and stays within fp32-accumulation error of the oracle.  Warp states are merged in shared memory; splits write fp32 partial
 // (max, sum, O) triples to a scratch buffer that a second kernel merges in split order.
 #include "glue.h"
+#include "rope.cuh"
 
 namespace smelt {
 
@@ -77,13 +78,62 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
     const __half* Kb = a.k_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
     const __half* Vb = a.v_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
 
+    // ── folded RoPE / KV append (apply_rope, rope_kv_cache_update, kv_cache_update of
+    // Resources/Shaders/attention.metal:48-209, full-head analytic mode): the new token is key
+    // seq_len - 1.  cos / sin of the position once per CTA, the group's query heads rotated
+    // into shared memory, and the CTA whose key range holds the new key writes its K and V rows.
+    const __half* q_src = a.q + ((size_t)b * a.n_q + (size_t)kvh * ratio) * D;
+    int q_pitch = D;
+    if (a.k_new) {
+        constexpr int HALF = D / 2;
+        float* s_cos = smem_f;
+        float* s_sin = smem_f + HALF;
+        __half* s_q = reinterpret_cast<__half*>(smem_f + 2 * HALF);
+        const uint32_t pos = seq_len - 1u;
+        if (tid < HALF) {
+            int d0, d1, c0i, c1i;
+            float c0, s0, c1, s1;
+            rope_indices(a.rope_layout, tid, HALF, D, d0, d1, c0i, c1i);
+            rope_trig(tid, HALF, pos, a.rope_base_log2, 1, nullptr, nullptr, c0i, c1i, c0, s0, c1, s1);
+            s_cos[tid] = c0; s_sin[tid] = s0;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < ratio * HALF; idx += kAttnThreads) {
+            const int h = idx / HALF, pr = idx % HALF;
+            int d0, d1, c0i, c1i;
+            rope_indices(a.rope_layout, pr, HALF, D, d0, d1, c0i, c1i);
+            const float c = s_cos[pr], sn = s_sin[pr];
+            const float x0 = __half2float(q_src[h * D + d0]), x1 = __half2float(q_src[h * D + d1]);
+            s_q[h * D + d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)));
+            s_q[h * D + d1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)));
+        }
+        if (k_begin <= pos && pos < k_end && pos < a.capacity) {
+            const __half* kn = a.k_new + ((size_t)b * a.n_kv + kvh) * D;
+            const __half* vn = a.v_new + ((size_t)b * a.n_kv + kvh) * D;
+            __half* kd = const_cast<__half*>(Kb) + (size_t)pos * D;
+            __half* vd = const_cast<__half*>(Vb) + (size_t)pos * D;
+            for (int pr = tid; pr < HALF; pr += kAttnThreads) {
+                int d0, d1, c0i, c1i;
+                rope_indices(a.rope_layout, pr, HALF, D, d0, d1, c0i, c1i);
+                const float c = s_cos[pr], sn = s_sin[pr];
+                const float x0 = __half2float(kn[d0]), x1 = __half2float(kn[d1]);
+                kd[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)));
+                kd[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, sn)));
+                reinterpret_cast<__half2*>(vd)[pr] = reinterpret_cast<const __half2*>(vn)[pr];
+            }
+            __threadfence_block();
+        }
+        __syncthreads();  // rotated q and the new cache rows are visible to the whole CTA
+        q_src = s_q;
+    }
+
     // Q^T fragments: thread (g,t) keeps head g's dims [32j + 8t, +8) for every j.
     uint32_t qf[NH][D / 8];
 #pragma unroll
     for (int nh = 0; nh < NH; ++nh) {
         const int hl = nh * 8 + g;
         if (hl < ratio) {
-            const __half* qh = a.q + ((size_t)b * a.n_q + (size_t)kvh * ratio + hl) * D;
+            const __half* qh = q_src + (size_t)hl * q_pitch;
 #pragma unroll
             for (int j = 0; j < KJ; ++j) {
                 const uint4 v = *reinterpret_cast<const uint4*>(qh + 32 * j + 8 * t);
@@ -94,6 +144,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
             for (int j = 0; j < D / 8; ++j) qf[nh][j] = 0u;
         }
     }
+    if (a.k_new) __syncthreads();  // the rotated q lives where the warps later exchange their states
     const float scale2 = a.scale * 1.4426950408889634f;
 
     float m_run[NH][2], l_run[NH][2], o[NH][MT][4];
@@ -243,6 +294,32 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
             }
         }
     }
+    if (p.nsplits == 1 || !a.counters) return;
+
+    // ── the last split of this (sequence, KV head) to arrive merges the partials in split
+    // order (the arithmetic of attn_merge_kernel) and leaves the counter at zero ──
+    __threadfence();
+    __syncthreads();
+    int* counter = a.counters + (size_t)b * a.n_kv + kvh;
+    int* s_ticket = reinterpret_cast<int*>(smem_f);
+    if (tid == 0) *s_ticket = atomicAdd(counter, 1);
+    __syncthreads();
+    if (*s_ticket != p.nsplits - 1) return;
+    if (tid == 0) *counter = 0;
+    __threadfence();
+    for (int idx = tid; idx < ratio * D; idx += kAttnThreads) {
+        const int h = idx / D, d = idx % D;
+        const size_t qh = (size_t)b * a.n_q + (size_t)kvh * ratio + h;
+        float mstar = kNegBig;
+        for (int s2 = 0; s2 < p.nsplits; ++s2) mstar = fmaxf(mstar, __ldcg(p.part_ml + (qh * p.nsplits + s2) * 2));
+        float acc = 0.f, lsum = 0.f;
+        for (int s2 = 0; s2 < p.nsplits; ++s2) {
+            const float f = exp2f(__ldcg(p.part_ml + (qh * p.nsplits + s2) * 2) - mstar);
+            acc += __ldcg(p.part_o + (qh * p.nsplits + s2) * D + d) * f;
+            lsum += __ldcg(p.part_ml + (qh * p.nsplits + s2) * 2 + 1) * f;
+        }
+        a.out[qh * D + d] = __float2half_rn(acc / lsum);
+    }
 }
 
 // Merge the per-split partials of one (sequence, query head) in split order.
@@ -323,7 +400,7 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
         default: return cudaErrorInvalidValue;
     }
 #undef SMELT_ATTN_CASE
-    if (e != cudaSuccess || nsplits == 1) return e;
+    if (e != cudaSuccess || nsplits == 1 || a.counters) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.batch * a.n_q);
     cfg.blockDim = dim3(a.head_dim < 128 ? 64 : 128);

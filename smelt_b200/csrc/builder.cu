@@ -151,8 +151,10 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
             Rec r(e, "smelt_rmsnorm_affine_qkv:" + std::to_string(H) + ":64", ((qd + 2 * kvd) + 15) / 16);
             r.affine(0, w.q).affine(3, w.k).affine(6, w.v).buf(9, SMELT_SLOT_CUR).buf(10, kWeights, w.input_norm)
                 .buf(11, kAttnQ).buf(12, kAttnK).buf(13, kAttnV).u32(14, qd).u32(15, kvd).f32(16, d->eps).u32(17, B);
-            Rec(e, "smelt_rope_qkv_append", ((qd + 2 * kvd) / 2 + 127) / 128, B).buf(0, kAttnQ).buf(1, kAttnK).buf(2, kAttnV).buf(3, kslot).buf(4, vslot)
-                .u32(7, D).u32(8, d->n_q).u32(9, d->n_kv).con(10, SMELT_CONST_CACHE_SEQ_CAPACITY).con(11, SMELT_CONST_POSITION).u32(12, 1).f32(13, log2_theta);
+            // RoPE, K/V append and attention in one launch
+            Rec(e, "smelt_rope_attention_decode", d->n_q, B).buf(0, kAttnQ).buf(1, kslot).buf(2, vslot).buf(4, kAttnOut).buf(11, kAttnK).buf(12, kAttnV)
+                .u32(5, D).con(6, SMELT_CONST_CACHE_SEQ_CAPACITY).con(7, SMELT_CONST_POSITION_PLUS1).u32(8, d->n_kv).f32(9, scale).u32(10, 0)
+                .u32(13, 1).f32(14, log2_theta);
         } else {
         // input norm (TopLevelEmitter.swift:316-326)
         Rec(e, "rms_norm_1pw", B).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, w.input_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
@@ -175,10 +177,10 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
         }
         Rec(e, "kv_cache_update", (kvd + 63) / 64, B).buf(0, vslot).buf(1, kAttnV).con(2, SMELT_CONST_CACHE_SEQ_CAPACITY).u32(3, D)
             .con(4, SMELT_CONST_POSITION).u32(5, d->n_kv);
-        }
         // attention decode (AttentionPlugin.swift:738-984): one threadgroup per query head
         Rec(e, "attention_decode", d->n_q, B).buf(0, kAttnQ).buf(1, kslot).buf(2, vslot).buf(3, kAttnQ).buf(4, kAttnOut)
             .u32(5, D).con(6, SMELT_CONST_CACHE_SEQ_CAPACITY).con(7, SMELT_CONST_POSITION_PLUS1).u32(8, d->n_kv).f32(9, scale).u32(10, 0);
+        }
         // O projection + residual (TopLevelEmitter.swift:417-429)
         if (fuse) {
             Rec r(e, bt ? shaped("fused_affine_matvec_add", qd, H, G, true) : "fused_affine_matvec_add:" + std::to_string(qd) + ":" + std::to_string(G), (H + 7) / 8);

@@ -116,6 +116,7 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"swiglu_fused", PK_SWIGLU, 0, false},
         {"smelt_tp_all_reduce", PK_TP_ALL_REDUCE, 0, false},
         {"smelt_rope_qkv_append", PK_ROPE_QKV_APPEND, 0, false},
+        {"smelt_rope_attention_decode", PK_ATTN_ROPE, 0, false},
     };
     for (const Simple& s : table)
         if (name == s.name) {
@@ -353,7 +354,7 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
     a.batch = batch_of(rec);
     a.k_cache = (const __half*)r.buf[1].ptr; a.v_cache = (const __half*)r.buf[2].ptr;
     a.q = (const __half*)r.buf[0].ptr;
-    if (p.kind == PK_ATTN_GENERIC) {
+    if (p.kind == PK_ATTN_GENERIC || p.kind == PK_ATTN_ROPE) {
         // attention.metal:217-229: 0 q, 1 K, 2 V, 3 mask (unused), 4 out, 5 headDim, 6 capacity, 7 seqLen,
         // 8 numKVHeads, 9 scale, 10 slidingWindow; numQHeads = threadgroups in x.
         NEED_BUF(4);
@@ -363,6 +364,14 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
         a.out = (__half*)r.buf[4].ptr; a.head_dim = (int)d; a.capacity = cap; a.n_kv = (int)nkv; a.n_q = (int)rec.grid[0];
         a.scale = as_f32(scale_bits); a.sliding_window = window;
         iseq = 7;
+        if (p.kind == PK_ATTN_ROPE) {
+            // the generic bindings plus 11 new K, 12 new V, 13 pair layout, 14 log2(theta)
+            NEED_BUF(11); NEED_BUF(12); NEED_U32(13, layout); NEED_U32(14, base_bits);
+            if (layout > 1) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": layout must be 0 or 1");
+            a.k_new = (const __half*)r.buf[11].ptr; a.v_new = (const __half*)r.buf[12].ptr;
+            a.rope_layout = (int)layout; a.rope_base_log2 = as_f32(base_bits);
+            NEED_BYTES(11, (size_t)a.batch * nkv * d * 2); NEED_BYTES(12, (size_t)a.batch * nkv * d * 2);
+        }
     } else {
         // in place: 0 q/out, 1 K, 2 V, 3 seqLen, 4 capacity (attention.metal:422-431, :1211-1218);
         // the mlx_vector form adds 5 qHeads, 6 kvHeads (:981-989).
@@ -386,7 +395,9 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
     NEED_BYTES(1, a.seq_stride * 2 * a.batch); NEED_BYTES(2, a.seq_stride * 2 * a.batch);
     NEED_BYTES(0, (size_t)a.batch * a.n_q * a.head_dim * 2);
     a.scratch = ctx->attn_scratch; a.scratch_bytes = ctx->attn_scratch_bytes; a.sm_count = ctx->sm_count;
-    in.launches += 2;
+    if ((size_t)a.batch * a.n_kv <= 4096) a.counters = ctx->attn_counters;
+    if (p.kind == PK_ATTN_ROPE && !a.counters) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": too many (sequence, KV head) pairs");
+    in.launches += 1;
     return check_cuda(ctx, launch_attention_decode(make_launch(in, r), a), p.name.c_str());
 }
 
@@ -405,7 +416,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             return run_affine(in, p, rec, r);
         case PK_SIGNED_MATVEC: case PK_SIGNED_ADD: case PK_SIGNED_GATEUP: case PK_SIGNED_TERNARY_AFFINE:
             return run_signed(in, p, rec, r);
-        case PK_ATTN_GENERIC: case PK_ATTN_INPLACE:
+        case PK_ATTN_GENERIC: case PK_ATTN_INPLACE: case PK_ATTN_ROPE:
             return run_attention(in, p, rec, r);
         case PK_FP16_MATVEC: {
             // lut_matvec.metal:799-803: 0 W, 1 x, 2 y, 3 cols; one threadgroup per row.

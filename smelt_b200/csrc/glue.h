@@ -35,6 +35,16 @@ struct AttnArgs {
     void* scratch;
     size_t scratch_bytes;
     int sm_count;
+    // Optional.  counters != null: one zeroed int per (sequence, KV head); the last split of a
+    // head to finish merges the partials itself (no merge launch) and leaves its counter at zero.
+    int* counters;
+    // k_new != null: RoPE on q, RoPE + append of the new K row and append of the new V row
+    // (apply_rope + rope_kv_cache_update + kv_cache_update, full-head analytic mode) happen
+    // inside the kernel; the new token sits at key index seq_len - 1.
+    const __half* k_new;    // [batch, n_kv, head_dim]
+    const __half* v_new;
+    int rope_layout;        // 0 adjacent pairs, 1 split-half
+    float rope_base_log2;
 };
 size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits);
 int attention_max_splits();

@@ -73,6 +73,8 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     // no launch ever allocates (64 splits x 64 heads x batch 8 x (256+2) floats = 34 MB).
     ctx->attn_scratch_bytes = attention_scratch_bytes(64, 256, 8, attention_max_splits());
     ok = ok && cudaMalloc(&ctx->attn_scratch, ctx->attn_scratch_bytes) == cudaSuccess;
+    ok = ok && cudaMalloc(&ctx->attn_counters, 4096 * sizeof(int)) == cudaSuccess;
+    ok = ok && cudaMemset(ctx->attn_counters, 0, 4096 * sizeof(int)) == cudaSuccess;
     ctx->argmax_scratch_bytes = 64 * 1024 * sizeof(uint64_t);
     ok = ok && cudaMalloc(&ctx->argmax_scratch, ctx->argmax_scratch_bytes) == cudaSuccess;
     ok = ok && cudaEventCreate(&ctx->ev_start) == cudaSuccess && cudaEventCreate(&ctx->ev_stop) == cudaSuccess;
@@ -102,6 +104,7 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     cudaFree(ctx->dyn_dev);
     cudaFree(ctx->err_dev);
     cudaFree(ctx->attn_scratch);
+    cudaFree(ctx->attn_counters);
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gen_ring);
     cudaFree(ctx->gen_count);
@@ -503,7 +506,29 @@ smelt_status smelt_cuda_attention_decode(smelt_cuda_ctx* ctx, const void* q, con
     a.seq_from_pos = 0; a.scale = scale; a.sliding_window = sliding_window;
     a.seq_stride = kv_seq_stride ? kv_seq_stride : (size_t)n_kv * capacity * head_dim;
     a.scratch = ctx->attn_scratch; a.scratch_bytes = ctx->attn_scratch_bytes; a.sm_count = ctx->sm_count;
+    if ((size_t)batch * n_kv <= 4096) a.counters = ctx->attn_counters;
     return check_cuda(ctx, launch_attention_decode(typed_launch(ctx), a), "attention decode launch");
+}
+
+smelt_status smelt_cuda_rope_attention_decode(smelt_cuda_ctx* ctx, const void* q, const void* k_new, const void* v_new, void* k_cache,
+                                              void* v_cache, void* out, int n_q, int n_kv, int head_dim, uint32_t capacity,
+                                              uint32_t position, float scale, uint32_t sliding_window, int layout,
+                                              float base_log2, int batch, size_t kv_seq_stride) {
+    CTX_OR_FAIL();
+    if (!q || !k_new || !v_new || !k_cache || !v_cache || !out || n_q <= 0 || n_kv <= 0 || n_q % n_kv || batch <= 0 || (layout != 0 && layout != 1))
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "rope attention decode: bad arguments (layout 0 or 1, n_q % n_kv == 0)");
+    if (position >= capacity) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "rope attention decode: position must be below capacity");
+    if (n_q / n_kv > 16 || (head_dim != 64 && head_dim != 128 && head_dim != 256) || (size_t)batch * n_kv > 4096)
+        return fail(ctx, SMELT_ERR_UNSUPPORTED, "rope attention decode: head_dim in {64,128,256}, GQA ratio <= 16");
+    AttnArgs a = {};
+    a.q = (const __half*)q; a.k_cache = (const __half*)k_cache; a.v_cache = (const __half*)v_cache; a.out = (__half*)out;
+    a.k_new = (const __half*)k_new; a.v_new = (const __half*)v_new; a.rope_layout = layout; a.rope_base_log2 = base_log2;
+    a.n_q = n_q; a.n_kv = n_kv; a.head_dim = head_dim; a.batch = batch; a.capacity = capacity; a.seq_len = position + 1;
+    a.seq_from_pos = 0; a.scale = scale; a.sliding_window = sliding_window;
+    a.seq_stride = kv_seq_stride ? kv_seq_stride : (size_t)n_kv * capacity * head_dim;
+    a.scratch = ctx->attn_scratch; a.scratch_bytes = ctx->attn_scratch_bytes; a.sm_count = ctx->sm_count;
+    a.counters = ctx->attn_counters;
+    return check_cuda(ctx, launch_attention_decode(typed_launch(ctx), a), "rope attention decode launch");
 }
 
 smelt_status smelt_cuda_kv_cache_update(smelt_cuda_ctx* ctx, void* cache, const void* new_kv, uint32_t capacity,

@@ -43,6 +43,7 @@ enum PipeKind : int {
     PK_FUSED_NORM_QKV,
     PK_FUSED_NORM_GATEUP,
     PK_ROPE_QKV_APPEND,
+    PK_ATTN_ROPE,
 };
 
 struct Pipeline {
@@ -75,6 +76,7 @@ struct smelt_cuda_ctx {
     uint32_t* err_dev = nullptr;         // device error word
     void* attn_scratch = nullptr;
     size_t attn_scratch_bytes = 0;
+    int* attn_counters = nullptr;  // one zeroed int per (sequence, KV head): in-kernel merge of attention splits
     uint64_t* argmax_scratch = nullptr;
     size_t argmax_scratch_bytes = 0;
 

@@ -461,6 +461,42 @@ def test_attention_config3(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
         assert rel_err(got[b], ref) < REL_TOL
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,position,batch,layout", [(32, 8, 128, 0, 1, 1), (32, 8, 128, 530, 1, 1), (16, 4, 128, 4095, 2, 1),
+                                                              (8, 2, 256, 777, 1, 0), (16, 1, 64, 129, 3, 1)])
+def test_rope_attention_decode_is_the_four_kernels(ctx, oracle, n_q, n_kv, d, position, batch, layout):
+    """RoPE on q, RoPE + append of K, append of V and attention in one launch: the bits of the
+    four separate launches, with the new token as the last key."""
+    cap = position + 9
+    base_log2 = float(np.log2(np.float32(1e6)))
+    k = synth.kv_cache(33, "k", batch, n_kv, cap, d)
+    v = synth.kv_cache(33, "v", batch, n_kv, cap, d)
+    q = synth.activations(33, "q", batch, n_q, d)
+    kn = (synth.activations(33, "kn", batch, n_kv, d).astype(np.float32) / np.sqrt(d)).astype(np.float16)
+    vn = (synth.activations(33, "vn", batch, n_kv, d).astype(np.float32) / np.sqrt(d)).astype(np.float16)
+    stride = C.c_size_t(n_kv * cap * d)
+    scale = C.c_float(1 / np.sqrt(d))
+    # separate launches
+    dq, dk, dv, dkn, dvn = dev(ctx, q, k, v, kn, vn)
+    want = ctx.alloc(batch * n_q * d * 2)
+    ctx.call("rope_qkv_append", dq, dkn, dvn, dk, dv, cap, d, n_q, n_kv, layout, position, C.c_float(base_log2), batch, stride)
+    ctx.call("attention_decode", dq, dk, dv, want, n_q, n_kv, d, cap, position + 1, scale, 0, batch, stride)
+    # one launch
+    dq2, dk2, dv2 = dev(ctx, q, k, v)
+    got = ctx.alloc(batch * n_q * d * 2).fill(0xFF)
+    ctx.call("rope_attention_decode", dq2, dkn, dvn, dk2, dv2, got, n_q, n_kv, d, cap, position, scale, 0, layout, C.c_float(base_log2), batch, stride)
+    assert np.array_equal(got.download(np.uint16, (batch, n_q, d)), want.download(np.uint16, (batch, n_q, d)))
+    assert np.array_equal(dk2.download(np.uint16, (batch, n_kv, cap, d)), dk.download(np.uint16, (batch, n_kv, cap, d)))
+    assert np.array_equal(dv2.download(np.uint16, (batch, n_kv, cap, d)), dv.download(np.uint16, (batch, n_kv, cap, d)))
+    assert np.array_equal(dq2.download(np.uint16, (batch, n_q, d)), q.view(np.uint16))  # q itself is left alone
+    # twice in a row: the split counters are back at zero
+    ctx.call("rope_attention_decode", dq2, dkn, dvn, dk2, dv2, got.fill(0), n_q, n_kv, d, cap, position, scale, 0, layout, C.c_float(base_log2), batch, stride)
+    assert np.array_equal(got.download(np.uint16, (batch, n_q, d)), want.download(np.uint16, (batch, n_q, d)))
+    # and in place
+    ctx.call("rope_attention_decode", dq2, dkn, dvn, dk2, dv2, dq2, n_q, n_kv, d, cap, position, scale, 0, layout, C.c_float(base_log2), batch, stride)
+    assert np.array_equal(dq2.download(np.uint16, (batch, n_q, d)), want.download(np.uint16, (batch, n_q, d)))
+    assert ctx.call_status("rope_attention_decode", dq2, dkn, dvn, dk2, dv2, got, n_q, n_kv, d, cap, cap, scale, 0, layout, C.c_float(base_log2), batch, stride) == capi.OUT_OF_RANGE
+
+
 def test_attention_in_place(ctx, oracle):
     n_q, n_kv, d, cap, seq = 16, 4, 128, 600, 555
     k = synth.kv_cache(9, "k", 1, n_kv, cap, d)[0]

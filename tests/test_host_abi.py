@@ -53,7 +53,7 @@ def test_dispatch_record_layout():
     ("attention_decode_d256_h16_kv4", True), ("attention_decode_d128_h16_kv2_sdpa", True), ("attention_decode_mlx_vector_d256", True),
     ("rms_norm_1pw", True), ("per_head_rms_norm", True), ("elementwise_add", True), ("swiglu_fused", True),
     # outside the hot path: no silent default (MatvecKernelTable.swift:258-270)
-    ("smelt_rmsnorm_affine_qkv:4096:64", True), ("smelt_rmsnorm_affine_gate_up_swiglu:4096:64", True), ("smelt_rope_qkv_append", True),
+    ("smelt_rmsnorm_affine_qkv:4096:64", True), ("smelt_rmsnorm_affine_gate_up_swiglu:4096:64", True), ("smelt_rope_qkv_append", True), ("smelt_rope_attention_decode", True),
     ("smelt_rmsnorm_affine_qkv:4096:32", False), ("smelt_rmsnorm_affine_qkv:512:64", False),
     ("fused_lut_matvec", False), ("tqh_matvec", False), ("attention_decode_softcap", False), ("affine_matvec:4096:48", False),
     ("attention_decode_mlx_vector_2pass_1_d256_b128", False), ("recurrence_step", False), ("", False),
@@ -107,9 +107,11 @@ def test_decoder_table_variants():
     table_f, names_f = _table(cfg, 1, fuse=True)
     assert "fused_affine_matvec_add:2048:64" in names_f and "elementwise_add" not in names_f
     table_x, names_x = _table(cfg, 1, fuse=3)
-    assert [names_x[r.pipeline] if r.op_kind == 0 else "<swap>" for r in table_x][1:9] == [
-        "smelt_rmsnorm_affine_qkv:2048:64", "smelt_rope_qkv_append", "attention_decode", "fused_affine_matvec_add:2048:64", "<swap>",
+    assert [names_x[r.pipeline] if r.op_kind == 0 else "<swap>" for r in table_x][1:8] == [
+        "smelt_rmsnorm_affine_qkv:2048:64", "smelt_rope_attention_decode", "fused_affine_matvec_add:2048:64", "<swap>",
         "smelt_rmsnorm_affine_gate_up_swiglu:2048:64", "fused_affine_matvec_add:6144:64", "<swap>"]
+    att = table_x[2]
+    assert att.buffer_count == 6 and att.constant_count == 8  # every constant slot of a record is in use
     qkv = table_x[1]
     assert qkv.buffer_count == 14 and qkv.constant_count == 4
     small = package.DecoderConfig(layers=1, hidden=512, inter=1536, n_q=8, n_kv=2, head_dim=64, vocab=1000)
