@@ -18,10 +18,16 @@
 // as an fp16 high part plus an fp16 low part (two MMAs), so the weighted sum keeps about 22
 // significant bits of p and stays within fp32-accumulation error of the oracle.  Warp states are merged in shared memory; splits write fp32 partial
 // (max, sum, O) triples to a scratch buffer that a second kernel merges in split order.
+#include <cooperative_groups.h>
+
+#include <cstdlib>
+
 #include "glue.h"
 #include "rope.cuh"
 
 namespace smelt {
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -33,6 +39,7 @@ constexpr float kNegBig = -1.0e30f;
 struct AttnDev {
     AttnArgs a;
     int nsplits;
+    int cluster;     // 1: the splits of a KV head are one thread-block cluster and merge through distributed shared memory
     float* part_o;   // [batch*n_q, nsplits, head_dim]
     float* part_ml;  // [batch*n_q, nsplits, 2]
     DevDyn dyn;
@@ -91,11 +98,15 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
         __half* s_q = reinterpret_cast<__half*>(smem_f + 2 * HALF);
         const uint32_t pos = seq_len - 1u;
         if (tid < HALF) {
-            int d0, d1, c0i, c1i;
-            float c0, s0, c1, s1;
-            rope_indices(a.rope_layout, tid, HALF, D, d0, d1, c0i, c1i);
-            rope_trig(tid, HALF, pos, a.rope_base_log2, 1, nullptr, nullptr, c0i, c1i, c0, s0, c1, s1);
-            s_cos[tid] = c0; s_sin[tid] = s0;
+            if (a.rope_table) {  // cos | sin of this token's position, computed once per token
+                s_cos[tid] = a.rope_table[tid]; s_sin[tid] = a.rope_table[HALF + tid];
+            } else {
+                int d0, d1, c0i, c1i;
+                float c0, s0, c1, s1;
+                rope_indices(a.rope_layout, tid, HALF, D, d0, d1, c0i, c1i);
+                rope_trig(tid, HALF, pos, a.rope_base_log2, 1, nullptr, nullptr, c0i, c1i, c0, s0, c1, s1);
+                s_cos[tid] = c0; s_sin[tid] = s0;
+            }
         }
         __syncthreads();
         for (int idx = tid; idx < ratio * HALF; idx += kAttnThreads) {
@@ -163,6 +174,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
         // V rows this thread contracts over: k-slots 2t, 2t+1, 2t+8, 2t+9 of the tile
         uint32_t kv[4] = {min(kt + 2 * t, last), min(kt + 2 * t + 1, last), min(kt + 2 * t + 8, last), min(kt + 2 * t + 9, last)};
 
+        // every load of the tile is issued before any arithmetic: one memory round trip per tile
+        uint4 vv[VC][4];
+#pragma unroll
+        for (int c = 0; c < VC; ++c)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                vv[c][kk] = *reinterpret_cast<const uint4*>(Vb + (size_t)kv[kk] * D + 64 * c + 8 * g);
+
         // ── S^T = K · Q^T ──
         float s[NH][4];
 #pragma unroll
@@ -217,14 +236,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
         // ── O^T += V^T · P^T ──
 #pragma unroll
         for (int c = 0; c < VC; ++c) {
-            uint4 vv[4];
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-                vv[kk] = *reinterpret_cast<const uint4*>(Vb + (size_t)kv[kk] * D + 64 * c + 8 * g);
-            const uint32_t r0[4] = {vv[0].x, vv[0].y, vv[0].z, vv[0].w};
-            const uint32_t r1[4] = {vv[1].x, vv[1].y, vv[1].z, vv[1].w};
-            const uint32_t r2[4] = {vv[2].x, vv[2].y, vv[2].z, vv[2].w};
-            const uint32_t r3[4] = {vv[3].x, vv[3].y, vv[3].z, vv[3].w};
+            const uint32_t r0[4] = {vv[c][0].x, vv[c][0].y, vv[c][0].z, vv[c][0].w};
+            const uint32_t r1[4] = {vv[c][1].x, vv[c][1].y, vv[c][1].z, vv[c][1].w};
+            const uint32_t r2[4] = {vv[c][2].x, vv[c][2].y, vv[c][2].z, vv[c][2].w};
+            const uint32_t r3[4] = {vv[c][3].x, vv[c][3].y, vv[c][3].z, vv[c][3].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const uint32_t a0 = __byte_perm(r0[e], r1[e], 0x5410), a1 = __byte_perm(r0[e], r1[e], 0x7632);
@@ -286,6 +301,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
         const size_t qh = (size_t)b * a.n_q + (size_t)kvh * ratio + h;
         if (p.nsplits == 1) {
             a.out[qh * D + d] = __float2half_rn(acc / lsum);
+        } else if (p.cluster) {
+            float* c_o = smem_f + kAttnWarps * HN * (D + 2);  // [16][D] then [16][2]
+            c_o[idx] = acc;
+            if (d == 0) { c_o[16 * D + 2 * h] = mstar; c_o[16 * D + 2 * h + 1] = lsum; }
         } else {
             p.part_o[(qh * p.nsplits + split) * D + d] = acc;
             if (d == 0) {
@@ -293,6 +312,30 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
                 p.part_ml[(qh * p.nsplits + split) * 2 + 1] = lsum;
             }
         }
+    }
+    if (p.nsplits > 1 && p.cluster) {
+        // ── merge across the cluster: rank r finishes a slice of the (head, dim) outputs from
+        // every rank's partials, in rank order (the arithmetic of attn_merge_kernel) ──
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        float* c_o = smem_f + kAttnWarps * HN * (D + 2);
+        const int items = ratio * D, per_rank = (items + p.nsplits - 1) / p.nsplits;
+        const int hi = min(items, (split + 1) * per_rank);
+        for (int idx = split * per_rank + tid; idx < hi; idx += kAttnThreads) {
+            const int h = idx / D, d = idx % D;
+            float mstar = kNegBig;
+            for (int s2 = 0; s2 < p.nsplits; ++s2) mstar = fmaxf(mstar, cluster.map_shared_rank(c_o, s2)[16 * D + 2 * h]);
+            float acc = 0.f, lsum = 0.f;
+            for (int s2 = 0; s2 < p.nsplits; ++s2) {
+                const float* rc = cluster.map_shared_rank(c_o, s2);
+                const float f = exp2f(rc[16 * D + 2 * h] - mstar);
+                acc += rc[idx] * f;
+                lsum += rc[16 * D + 2 * h + 1] * f;
+            }
+            a.out[((size_t)b * a.n_q + (size_t)kvh * ratio + h) * D + d] = __float2half_rn(acc / lsum);
+        }
+        cluster.sync();  // nobody leaves while a peer still reads its shared memory
+        return;
     }
     if (p.nsplits == 1 || !a.counters) return;
 
@@ -322,6 +365,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev
     }
 }
 
+// cos | sin of the current position for the half pairs of a head (analytic full-head RoPE),
+// once per token; the attention launches of every layer read it.
+__global__ void rope_table_kernel(float* table, int half, float base_log2, DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    const int p = threadIdx.x;
+    if (p >= half) return;
+    int d0, d1, c0i, c1i;
+    float c0, s0, c1, s1;
+    rope_indices(1, p, half, 2 * half, d0, d1, c0i, c1i);
+    rope_trig(p, half, dyn_position(dyn), base_log2, 1, nullptr, nullptr, c0i, c1i, c0, s0, c1, s1);
+    table[p] = c0; table[half + p] = s0;
+}
+
 // Merge the per-split partials of one (sequence, query head) in split order.
 __global__ void attn_merge_kernel(const AttnDev p) {
     pdl_trigger();
@@ -344,7 +401,7 @@ __global__ void attn_merge_kernel(const AttnDev p) {
 
 template <int D, int NH>
 cudaError_t launch_decode_t(const Launch& l, const AttnDev& p) {
-    const size_t smem = (size_t)kAttnWarps * NH * 8 * (D + 2) * sizeof(float);
+    const size_t smem = ((size_t)kAttnWarps * NH * 8 + 16) * (D + 2) * sizeof(float);
     auto kern = attn_decode_kernel<D, NH>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -353,11 +410,22 @@ cudaError_t launch_decode_t(const Launch& l, const AttnDev& p) {
     cfg.blockDim = dim3(kAttnThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = l.stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (l.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.cluster) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = p.nsplits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = l.pdl ? 1 : 0;
+    cfg.numAttrs = na;
     prefer_max_shared(kern);
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
@@ -370,6 +438,21 @@ size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits)
     return (size_t)batch * n_q * max_splits * (head_dim + 2) * sizeof(float);
 }
 
+cudaError_t launch_rope_table(const Launch& l, float* table, int half, float base_log2) {
+    if (half <= 0 || half > 128) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(128);
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(rope_table_kernel);
+    return cudaLaunchKernelEx(&cfg, rope_table_kernel, table, half, base_log2, dev_dyn(l));
+}
+
 cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     if (a.n_q <= 0 || a.n_kv <= 0 || a.n_q % a.n_kv != 0 || a.batch <= 0) return cudaErrorInvalidValue;
     const int ratio = a.n_q / a.n_kv;
@@ -378,14 +461,20 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     if (n_max == 0) return cudaErrorInvalidValue;
     const int sm = a.sm_count > 0 ? a.sm_count : 148;
     int want = (3 * sm + a.n_kv * a.batch - 1) / (a.n_kv * a.batch);
-    int by_len = (int)((n_max + 127u) / 128u);
+    int by_len = (int)((n_max + 63u) / 64u);  // at least one 16-key tile per warp and split
     int nsplits = want < by_len ? want : by_len;
     if (nsplits < 1) nsplits = 1;
     if (nsplits > kMaxSplits) nsplits = kMaxSplits;
     while (nsplits > 1 && attention_scratch_bytes(a.n_q, a.head_dim, a.batch, nsplits) > a.scratch_bytes) --nsplits;
+    // Short contexts are latency bound: up to eight splits of a KV head run as one thread-block
+    // cluster and merge through distributed shared memory, with no partials in global memory.
+    static const char* no_cluster = getenv("SMELT_ATTN_NO_CLUSTER");
+    const bool cluster = n_max <= 4096 && by_len >= 2 && !(no_cluster && atoi(no_cluster));
+    if (cluster) nsplits = by_len < 8 ? by_len : 8;
     AttnDev p;
     p.a = a;
     p.nsplits = nsplits;
+    p.cluster = cluster ? 1 : 0;
     p.part_o = reinterpret_cast<float*>(a.scratch);
     p.part_ml = p.part_o ? p.part_o + (size_t)a.batch * a.n_q * nsplits * a.head_dim : nullptr;
     p.dyn = dev_dyn(l);
@@ -400,7 +489,7 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
         default: return cudaErrorInvalidValue;
     }
 #undef SMELT_ATTN_CASE
-    if (e != cudaSuccess || nsplits == 1 || a.counters) return e;
+    if (e != cudaSuccess || nsplits == 1 || a.counters || cluster) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.batch * a.n_q);
     cfg.blockDim = dim3(a.head_dim < 128 ? 64 : 128);

@@ -175,6 +175,8 @@ struct Interp {
     uint32_t position;  // host copy (valid when !device_pos)
     int cur, alt;
     int launches = 0;
+    int rope_half = 0;       // the position's cos | sin table holds this many pairs ...
+    float rope_base = 0.f;   // ... for this log2(theta); 0 pairs = not written in this interpretation
 };
 
 smelt_status resolve(Interp& in, const smelt_dispatch_record& rec, Resolved* out) {
@@ -370,6 +372,18 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
             if (layout > 1) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": layout must be 0 or 1");
             a.k_new = (const __half*)r.buf[11].ptr; a.v_new = (const __half*)r.buf[12].ptr;
             a.rope_layout = (int)layout; a.rope_base_log2 = as_f32(base_bits);
+            if (d / 2 <= 128 && r.con[7].present && r.con[7].kind == SMELT_CONST_POSITION_PLUS1) {
+                // the new token sits at the step position in every layer: cos | sin once per token
+                if (in.rope_half != (int)d / 2 || in.rope_base != a.rope_base_log2) {
+                    Launch lt = make_launch(in, r);
+                    lt.guard_lt = lt.guard_ge = 0;
+                    smelt_status st = check_cuda(ctx, launch_rope_table(lt, ctx->rope_table, (int)d / 2, a.rope_base_log2), "rope table");
+                    if (st) return st;
+                    in.rope_half = (int)d / 2; in.rope_base = a.rope_base_log2;
+                    in.launches += 1;
+                }
+                a.rope_table = ctx->rope_table;
+            }
             NEED_BYTES(11, (size_t)a.batch * nkv * d * 2); NEED_BYTES(12, (size_t)a.batch * nkv * d * 2);
         }
     } else {

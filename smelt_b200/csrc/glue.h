@@ -45,10 +45,12 @@ struct AttnArgs {
     const __half* v_new;
     int rope_layout;        // 0 adjacent pairs, 1 split-half
     float rope_base_log2;
+    const float* rope_table;  // optional: cos[half] | sin[half] of the position (launch_rope_table)
 };
 size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits);
 int attention_max_splits();
 cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a);
+cudaError_t launch_rope_table(const Launch& l, float* table, int half, float base_log2);
 
 // signed_matvec.cu — binary1 / ternary2, group 128.
 enum SignedMode : int { kSignedPlain = 0, kSignedAdd = 1, kSignedGateUp = 2 };

@@ -73,6 +73,7 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     // no launch ever allocates (64 splits x 64 heads x batch 8 x (256+2) floats = 34 MB).
     ctx->attn_scratch_bytes = attention_scratch_bytes(64, 256, 8, attention_max_splits());
     ok = ok && cudaMalloc(&ctx->attn_scratch, ctx->attn_scratch_bytes) == cudaSuccess;
+    ok = ok && cudaMalloc(&ctx->rope_table, 256 * sizeof(float)) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->attn_counters, 4096 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(ctx->attn_counters, 0, 4096 * sizeof(int)) == cudaSuccess;
     ctx->argmax_scratch_bytes = 64 * 1024 * sizeof(uint64_t);
@@ -105,6 +106,7 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     cudaFree(ctx->err_dev);
     cudaFree(ctx->attn_scratch);
     cudaFree(ctx->attn_counters);
+    cudaFree(ctx->rope_table);
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gen_ring);
     cudaFree(ctx->gen_count);

@@ -76,6 +76,7 @@ struct smelt_cuda_ctx {
     uint32_t* err_dev = nullptr;         // device error word
     void* attn_scratch = nullptr;
     size_t attn_scratch_bytes = 0;
+    float* rope_table = nullptr;   // cos | sin of the current position (256 floats), written once per interpretation
     int* attn_counters = nullptr;  // one zeroed int per (sequence, KV head): in-kernel merge of attention splits
     uint64_t* argmax_scratch = nullptr;
     size_t argmax_scratch_bytes = 0;
