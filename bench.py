@@ -132,12 +132,15 @@ def run_ours(args):
         dist.broadcast(t, 0)
         ident = t.cpu().numpy()
         ctx._check(ctx.lib.smelt_cuda_tp_init(ctx.h, rank, world, ident.ctypes.data_as(C.c_void_p)))
+        if args.collective == "peer":
+            package.open_tp_exchange(ctx, dist, world)
 
     t0 = time.time()
     pkg = package.SyntheticPackage(cfg, SEED)
     keep = rank == 0 and world == 1 and not args.no_cpu_baseline
     image, desc, layers = package.build_image(pkg, rank, world, keep_for_oracle=keep)
-    dec = package.Decoder(ctx, image, desc, layers, capacity, B, fuse_residual=3 if args.table == "fused" else 0)
+    fuse = (3 if args.table == "fused" else 0) | (4 if world > 1 and args.collective == "peer" else 0)
+    dec = package.Decoder(ctx, image, desc, layers, capacity, B, fuse_residual=fuse)
     del image
     dec.build_graph()
     gen_s = time.time() - t0
@@ -207,7 +210,7 @@ def run_ours(args):
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
             "config": {"workload": "config4: full 36-layer 4096/12288 decoder, affine u4 g64, greedy decode after a %d-token prompt" % args.prompt_len,
-                       "batch": B, "prompt_len": args.prompt_len, "parallelism": f"tp{world}",
+                       "batch": B, "prompt_len": args.prompt_len, "parallelism": f"tp{world}" + (f" ({args.collective} all-reduce)" if world > 1 else ""),
                        "table": args.table + (" (norm+QKV, RoPE+append, O+add, norm+gate/up+SwiGLU, down+add per layer)" if args.table == "fused" else " (the reference emitter's record sequence)"),
                        "l2_policy": "inputs larger than L2: each step streams %.2f GB of weights per GPU" % (tb["total"] / 1e9)},
             "e2e": {"value": args.steps * B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B + 4, "d2h_bytes_per_step": 4 * B},
@@ -352,6 +355,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens decoded before the timed region (512 = the headline configuration; smaller for profiler captures)")
     ap.add_argument("--table", default="fused", choices=["fused", "reference"],
                     help="fused: the builder's fused record table; reference: the reference emitter's record sequence")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: all-reduce + residual add as one peer-memory launch, or ncclAllReduce + elementwise_add")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant kernel on a few synthetic weight sets (profiler captures)")
     ap.add_argument("--kernel-layers", type=int, default=6)
     args = ap.parse_args()

@@ -222,7 +222,9 @@ typedef struct {
     int32_t tp_rank;
     int32_t fuse_residual; /* bit 0: emit fused_affine_matvec_add instead of matvec + elementwise_add (tp_world == 1 only);
                               bit 1: fold each RMS norm into the projection that follows it (one Q/K/V launch, one
-                              gate/up launch) and RoPE + KV append into one launch (the smelt_* extension kernels) */
+                              gate/up launch) and RoPE + KV append + attention into one launch (the smelt_*
+                              extension kernels); bit 2 (tp_world > 1): all-reduce + residual add as one
+                              smelt_tp_reduce_add record */
 } smelt_decoder_desc;
 /* Allocates the activation / KV / scratch slots for `desc` at `capacity` positions and
  * `batch` sequences, registers the pipelines, configures the context and writes the table.
@@ -247,6 +249,18 @@ SMELT_CUDA_API smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_des
 SMELT_CUDA_API smelt_status smelt_cuda_tp_unique_id(uint8_t id[SMELT_TP_ID_BYTES]);
 SMELT_CUDA_API smelt_status smelt_cuda_tp_init(smelt_cuda_ctx* ctx, int rank, int world, const uint8_t id[SMELT_TP_ID_BYTES]);
 SMELT_CUDA_API smelt_status smelt_cuda_tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data_dev, size_t count);
+/* Peer-memory exchange for the fused all-reduce + residual add ("smelt_tp_reduce_add": buffer 0
+ * this rank's partial, 1 residual, 2 out, constant 3 = element count): every rank publishes the
+ * IPC handle of its exchange buffer (exchange_handle), the caller gathers the handles of all
+ * ranks in rank order and every rank maps them (exchange_open).  A reduction is then one launch
+ * per rank: partials are pushed into the peers' buffers over NVLink, a sequence flag follows,
+ * each rank adds the partials in rank order in fp32, rounds once to fp16 and adds the residual.
+ * Waits are bounded; a peer that never arrives sets bit 8 of the device error word
+ * (smelt_cuda_device_error).  Without open exchange buffers the record falls back to
+ * ncclAllReduce followed by elementwise_add. */
+#define SMELT_TP_HANDLE_BYTES 64
+SMELT_CUDA_API smelt_status smelt_cuda_tp_exchange_handle(smelt_cuda_ctx* ctx, uint8_t handle[SMELT_TP_HANDLE_BYTES]);
+SMELT_CUDA_API smelt_status smelt_cuda_tp_exchange_open(smelt_cuda_ctx* ctx, const uint8_t* handles_in_rank_order);
 
 /* ── typed launchers (asynchronous on the context's stream) ──────────────────
  * Packed-weight layouts are the package's: affine u4 = two nibbles per byte, low nibble =

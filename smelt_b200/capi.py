@@ -25,6 +25,8 @@ CONST_LITERAL_U32, CONST_LITERAL_F32, CONST_POSITION, CONST_POSITION_PLUS1 = 0, 
 CONST_SKIP_UNLESS_POS1_LT, CONST_SKIP_UNLESS_POS1_GE, CONST_CACHE_SEQ_CAPACITY = 10, 11, 12
 SLOT_CUR, SLOT_ALT = -1, -2
 TP_ID_BYTES = 128
+TP_HANDLE_BYTES = 64
+TP_HANDLE_BYTES = 64
 
 
 class SmeltError(RuntimeError):

@@ -31,8 +31,8 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int kAttnThreads = 128;
-constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = 8;
 constexpr int kMaxSplits = 64;
 constexpr float kNegBig = -1.0e30f;
 
@@ -461,7 +461,7 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     if (n_max == 0) return cudaErrorInvalidValue;
     const int sm = a.sm_count > 0 ? a.sm_count : 148;
     int want = (3 * sm + a.n_kv * a.batch - 1) / (a.n_kv * a.batch);
-    int by_len = (int)((n_max + 63u) / 64u);  // at least one 16-key tile per warp and split
+    int by_len = (int)((n_max + 127u) / 128u);  // at least one 16-key tile per warp and split
     int nsplits = want < by_len ? want : by_len;
     if (nsplits < 1) nsplits = 1;
     if (nsplits > kMaxSplits) nsplits = kMaxSplits;

@@ -99,6 +99,7 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
     const bool fuse = (d->fuse_residual & 1) && !tp;
     // bit 1: fold the norms into the projections (one QKV launch, one gate/up launch) and RoPE /
     // KV append into one launch; needs the shapes the streaming matvec kernel accepts.
+    const bool fuse_tp = (d->fuse_residual & 4) != 0;  // bit 2: all-reduce and residual add in one launch over peer memory
     const bool fuse2 = (d->fuse_residual & 2) && G == 64 && H % 1024 == 0 && qd % 16 == 0 && kvd % 16 == 0 && B <= 8 && D % 2 == 0;
     const bool bt = B > 1;  // batched kernel names bind actualBatch instead of numRows
 
@@ -188,8 +189,11 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
             count_const(r, 6, H);
         } else {
             { Rec r(e, matvec_name(qd, H), (H + 7) / 8); r.affine(0, w.o).buf(3, kAttnOut).buf(4, kNormOut); count_const(r, 5, H); }
+            if (tp && fuse_tp) Rec(e, "smelt_tp_reduce_add").buf(0, kNormOut).buf(1, SMELT_SLOT_CUR).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)(B * H));
+            else {
             if (tp) Rec(e, "smelt_tp_all_reduce").buf(0, kNormOut).u32(1, (uint32_t)(B * H));
             Rec(e, "elementwise_add", (B * H + 63) / 64).buf(0, SMELT_SLOT_CUR).buf(1, kNormOut).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)(B * H));
+            }
         }
         e.swap();
         // post-attention norm + FFN (TopLevelEmitter.swift:1021-1322 emitSwiGLU)
@@ -210,8 +214,11 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
             count_const(r, 6, H);
         } else {
             { Rec r(e, matvec_name(I, H), (H + 7) / 8); r.affine(0, w.down).buf(3, kFfnInt).buf(4, kFfnDown); count_const(r, 5, H); }
+            if (tp && fuse_tp) Rec(e, "smelt_tp_reduce_add").buf(0, kFfnDown).buf(1, SMELT_SLOT_CUR).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)(B * H));
+            else {
             if (tp) Rec(e, "smelt_tp_all_reduce").buf(0, kFfnDown).u32(1, (uint32_t)(B * H));
             Rec(e, "elementwise_add", (B * H + 63) / 64).buf(0, SMELT_SLOT_CUR).buf(1, kFfnDown).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)(B * H));
+            }
         }
         e.swap();
     }

@@ -115,6 +115,7 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"elementwise_add", PK_ADD, 0, false},
         {"swiglu_fused", PK_SWIGLU, 0, false},
         {"smelt_tp_all_reduce", PK_TP_ALL_REDUCE, 0, false},
+        {"smelt_tp_reduce_add", PK_TP_REDUCE_ADD, 0, false},
         {"smelt_rope_qkv_append", PK_ROPE_QKV_APPEND, 0, false},
         {"smelt_rope_attention_decode", PK_ATTN_ROPE, 0, false},
     };
@@ -640,6 +641,21 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             if (ctx->tp_world <= 1) return SMELT_OK;
             in.launches += 1;
             return tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
+        }
+        case PK_TP_REDUCE_ADD: {
+            // 0 this rank's partial (reduced in place on the fallback path), 1 residual, 2 out, 3 count
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, count);
+            NEED_BYTES(0, (size_t)count * 2); NEED_BYTES(1, (size_t)count * 2); NEED_BYTES(2, (size_t)count * 2);
+            if (ctx->tp_world > 1) {
+                bool handled = false;
+                smelt_status st = tp_reduce_add(ctx, l, r.buf[0].ptr, r.buf[1].ptr, r.buf[2].ptr, count, &handled);
+                if (st || handled) { in.launches += 1; return st; }
+                st = tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
+                if (st) return st;
+                in.launches += 1;
+            }
+            in.launches += 1;
+            return check_cuda(ctx, launch_elementwise_add(l, (const __half*)r.buf[1].ptr, (const __half*)r.buf[0].ptr, (__half*)r.buf[2].ptr, (int64_t)count), "smelt_tp_reduce_add");
         }
         default:
             return fail(ctx, SMELT_ERR_UNKNOWN_PIPELINE, p.name + ": no handler");

@@ -44,6 +44,7 @@ enum PipeKind : int {
     PK_FUSED_NORM_GATEUP,
     PK_ROPE_QKV_APPEND,
     PK_ATTN_ROPE,
+    PK_TP_REDUCE_ADD,
 };
 
 struct Pipeline {
@@ -97,6 +98,7 @@ struct smelt_cuda_ctx {
 
     // tensor parallel
     void* nccl_comm = nullptr;
+    void* tp_peer = nullptr;   // peer-memory exchange state (tp.cu)
     int tp_rank = 0, tp_world = 1;
 };
 
@@ -105,4 +107,6 @@ smelt_status fail(smelt_cuda_ctx* ctx, smelt_status code, const std::string& msg
 smelt_status check_cuda(smelt_cuda_ctx* ctx, cudaError_t e, const char* what);
 smelt_status tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data, size_t count, cudaStream_t stream);
 void tp_destroy(smelt_cuda_ctx* ctx);
+smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* partial, const void* residual, void* out, size_t count,
+                           bool* handled);
 }  // namespace smelt

@@ -225,6 +225,21 @@ class Decoder:
         return out
 
 
+def open_tp_exchange(ctx: capi.Context, dist, world: int) -> None:
+    """Every rank publishes the IPC handle of its exchange buffer, gathers the others' through
+    ``torch.distributed`` and maps them: enables the fused all-reduce + residual add records."""
+    import torch
+
+    handle = np.zeros(capi.TP_HANDLE_BYTES, np.uint8)
+    ctx._check(ctx.lib.smelt_cuda_tp_exchange_handle(ctx.h, handle.ctypes.data_as(C.c_void_p)))
+    mine = torch.from_numpy(handle).cuda()
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    allh = np.ascontiguousarray(torch.stack(gathered).cpu().numpy())
+    ctx._check(ctx.lib.smelt_cuda_tp_exchange_open(ctx.h, allh.ctypes.data_as(C.c_void_p)))
+    dist.barrier()
+
+
 def oracle_model(oracle, pkg: SyntheticPackage, capacity: int):
     """The CPU oracle's decoder over the same synthetic tensors (test / baseline use only; the
     oracle module is passed in so that this package never imports it)."""

@@ -116,6 +116,9 @@ def test_decoder_table_variants():
     assert qkv.buffer_count == 14 and qkv.constant_count == 4
     small = package.DecoderConfig(layers=1, hidden=512, inter=1536, n_q=8, n_kv=2, head_dim=64, vocab=1000)
     assert not any(n.startswith("smelt_rmsnorm") for n in _table(small, 1, fuse=3)[1])  # hidden % 1024: reference-shaped records
+    table_pm, names_pm = _table(cfg, 1, tp=2, fuse=6)
+    seq_pm = [names_pm[r.pipeline] for r in table_pm if r.op_kind == 0]
+    assert seq_pm.count("smelt_tp_reduce_add") == 2 and "smelt_tp_all_reduce" not in seq_pm and "elementwise_add" not in seq_pm
     table_tp, names_tp = _table(cfg, 1, tp=2)
     seq = [names_tp[r.pipeline] for r in table_tp if r.op_kind == 0]
     assert seq.count("smelt_tp_all_reduce") == 2  # after O and after down

@@ -38,7 +38,9 @@ def main():
     pkg = package.SyntheticPackage(cfg, 7)
     prompt, n_dec = np.array([5, 17, 99, 4000], np.int32), 12
     results = {}
-    for fuse in (0, 2):
+    for fuse in (0, 2, 6):
+        if fuse == 6:  # all-reduce + residual add over peer memory
+            package.open_tp_exchange(ctx, dist, world)
         image, desc, layers = package.build_image(pkg, rank, world)
         dec = package.Decoder(ctx, image, desc, layers, 64, 1, fuse_residual=fuse)
         eager = dec.generate(prompt, n_dec, use_graph=False)[:, 0]
@@ -47,6 +49,11 @@ def main():
         assert np.array_equal(eager, graph), (fuse, eager, graph)
         results[fuse] = graph
     assert np.array_equal(results[0], results[2])
+    # two ranks: the sum of two fp16 partials rounded once is what the fp16 all-reduce returns too
+    assert world != 2 or np.array_equal(results[6], results[2])
+    flags = C.c_uint32(0)
+    ctx._check(ctx.lib.smelt_cuda_device_error(ctx.h, C.byref(flags)))
+    assert flags.value == 0, "a bounded device wait gave up"
     # every rank holds the same tokens
     tt = torch.from_numpy(results[0].astype(np.int64)).cuda()
     lo, hi = tt.clone(), tt.clone()
