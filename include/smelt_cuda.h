@@ -196,6 +196,11 @@ SMELT_CUDA_API smelt_status smelt_cuda_timer_stop(smelt_cuda_ctx* ctx, float* ou
 SMELT_CUDA_API smelt_status smelt_cuda_capture_begin(smelt_cuda_ctx* ctx);
 SMELT_CUDA_API smelt_status smelt_cuda_capture_end(smelt_cuda_ctx* ctx);
 SMELT_CUDA_API smelt_status smelt_cuda_capture_replay(smelt_cuda_ctx* ctx, int warmup, int reps, float* out_ms_per_replay);
+/* Experimental, off by default (also SMELT_PHASES=1 in the environment): smelt_cuda_graph_build
+ * turns every run of consecutive integer-MMA matvec and attention records into phases of one
+ * persistent cooperative kernel separated by grid barriers (bounded waits; a barrier that gives
+ * up sets bit 9 of the device error word).  Same device code per phase, same results bit for bit. */
+SMELT_CUDA_API smelt_status smelt_cuda_enable_phases(smelt_cuda_ctx* ctx, int on);
 /* Number of kernel launches one interpretation of the last built / enqueued table issues. */
 SMELT_CUDA_API int smelt_cuda_last_launch_count(const smelt_cuda_ctx* ctx);
 

@@ -1,0 +1,447 @@
+// Device side of the integer-MMA affine u4 matvec (see affine_imma.cu for the description):
+// shared by the stand-alone kernel and the multi-phase decode kernel.
+#pragma once
+#include "affine_matvec.h"
+
+namespace smelt {
+namespace imma {
+
+constexpr int kGroup = 64;
+constexpr int kTileRows = 16;
+constexpr int kDigits = 4;
+constexpr float kMagicF = 12582912.0f;                 // 1.5 * 2^23, bit pattern 0x4B400000
+
+// Geometry of one variant: WARPS warps per CTA, GPS groups (of 64 columns) per ring stage.
+template <int WARPS, int GPS>
+struct Geo {
+    static constexpr int kThreads = WARPS * 32;
+    static constexpr int kStageCols = GPS * kGroup;
+    static constexpr int kPitch = GPS * 32;                 // packed bytes per row per stage (64 or 128)
+    static constexpr int kSetW = kTileRows * kPitch;
+    static constexpr int kRowS = GPS * 2;                   // bytes of scales (or biases) per row per stage
+    static constexpr int kSetS = kTileRows * kRowS;
+    static constexpr int kSetBytes = kSetW + 2 * kSetS;     // [W | scales | biases]; a multiple of 128
+};
+
+struct ImmaLayout {
+    uint32_t zero, xq, pitch_x, xsum, xscale, red, ring, stage_bytes, total;
+};
+
+__host__ __device__ inline ImmaLayout imma_layout(int nw, int depth, int warps, int set_bytes, int cols, int batch, int teams) {
+    ImmaLayout L;
+    L.stage_bytes = (uint32_t)nw * set_bytes;
+    L.pitch_x = (uint32_t)cols + 64u;                  // one byte per column per plane; ≡ 64 (mod 128)
+    uint32_t off = 0;
+    L.zero = off; off += 64;
+    L.xq = off; off += (uint32_t)(kDigits * batch) * L.pitch_x;
+    L.xsum = off; off += (uint32_t)(cols / kGroup) * 2u * 4u;       // [group][batch slot 0/1]
+    L.xscale = off; off += 16;
+    L.red = off; off += (uint32_t)teams * 2u * (uint32_t)nw * 2u * kTileRows * 16u * 4u;  // [team][buffer][set][batch][row][warp slot, 16]
+    off = (off + 127u) & ~127u;
+    L.ring = off; off += (uint32_t)warps * depth * L.stage_bytes;
+    L.total = off;
+    return L;
+}
+
+// D = A (u8, 16 x 32) * B (s8, 32 x 8) + C; C may name one register four times.
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1, int c0, int c1, int c2, int c3) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+// Largest |v| of the eight fp16 values in a 16-byte word, as a float.
+__device__ __forceinline__ float amax8(const uint4& v) {
+    const __half2 m = __hmax2(__hmax2(__habs2(u32_as_h2(v.x)), __habs2(u32_as_h2(v.y))),
+                              __hmax2(__habs2(u32_as_h2(v.z)), __habs2(u32_as_h2(v.w))));
+    const float2 f = __half22float2(m);
+    return fmaxf(f.x, f.y);
+}
+
+// Four signed base-128 digits of X (|X| < 2^27), least significant first, each in [-64, 63]
+// except the last, which takes what remains.  With Y = X + 64 (1 + 128 + 128^2) the 7-bit
+// fields of Y are digit + 64 and Y >> 21 is the last digit, so the three low digits come out
+// biased by 64 here and the bias is taken off four bytes at a time after packing.
+constexpr int kDigitBias = 64 + 64 * 128 + 64 * 128 * 128;
+__device__ __forceinline__ void digits128_biased(int X, int (&d)[4]) {
+    const int Y = X + kDigitBias;
+    d[0] = Y & 127;
+    d[1] = (Y >> 7) & 127;
+    d[2] = (Y >> 14) & 127;
+    d[3] = Y >> 21;
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// The activations of one launch as digit planes + per-group sums, once per CTA (all threads
+// call it).  Kept out of line: its register needs must not shape the allocation of the
+// streaming loop.
+template <int WARPS>
+__device__ __noinline__ void stage_activations(const __half* x, const __half* norm_w, float norm_eps, int cols, int batch,
+                                               const ImmaLayout L, uint8_t* smem) {
+    struct { const __half* x; const __half* norm_w; float norm_eps; int cols, batch; } a = {x, norm_w, norm_eps, cols, batch};
+    constexpr int kThreads = WARPS * 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint8_t* xq = smem + L.xq;
+    float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
+    float* sxscale = reinterpret_cast<float*>(smem + L.xscale);
+    float* sred0 = reinterpret_cast<float*>(smem + L.red);
+    const int groups_total = a.cols / kGroup;
+
+        const int chunks = a.cols / 8;
+        if (tid < 4) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
+        if (a.batch == 1)
+            for (int i = tid; i < groups_total; i += kThreads) sxsum[i * 2 + 1] = 0.f;
+        // Rows of up to 12288 activations stay in registers between the passes (six 16-byte words
+        // per thread, the chunk order of cta256_sumsq_f16); longer rows are read again per pass.
+        constexpr int XR = 6;
+        const bool cached = kThreads == 256 && chunks <= XR * 256;
+        for (int b = 0; b < a.batch; ++b) {
+            const __half* xr = a.x + (size_t)b * a.cols;
+            uint4 xc[XR];
+#pragma unroll
+            for (int i = 0; i < XR; ++i) xc[i] = make_uint4(0, 0, 0, 0);
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < XR; ++i)
+                    if (tid + 256 * i < chunks) xc[i] = *reinterpret_cast<const uint4*>(xr + (tid + 256 * i) * 8);
+            }
+            float rs = 0.f;
+            if (a.norm_w) {
+                // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass;
+                // sred is free here: no tile has been reduced yet
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < XR; ++i) ss = sumsq8(ss, xc[i]);  // words past the row are zero: no contribution
+                const float tot = cached ? cta256_sum_finish(ss, sred0) : cta256_sumsq_f16(xr, a.cols, sred0);
+                rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
+                if (cached) {
+#pragma unroll
+                    for (int i = 0; i < XR; ++i)
+                        if (tid + 256 * i < chunks) {
+                            const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + (tid + 256 * i) * 8);
+                            xc[i].x = rms_norm_1pw_pair(xc[i].x, wv.x, rs); xc[i].y = rms_norm_1pw_pair(xc[i].y, wv.y, rs);
+                            xc[i].z = rms_norm_1pw_pair(xc[i].z, wv.z, rs); xc[i].w = rms_norm_1pw_pair(xc[i].w, wv.w, rs);
+                        }
+                }
+            }
+            auto load8 = [&](int c8) {  // uncached path: read (and normalise) again
+                uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                if (a.norm_w) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
+                    v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
+                    v.z = rms_norm_1pw_pair(v.z, wv.z, rs); v.w = rms_norm_1pw_pair(v.w, wv.w, rs);
+                }
+                return v;
+            };
+            float m = 0.f;
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < XR; ++i) m = fmaxf(m, amax8(xc[i]));  // words past the row are zero
+            } else {
+                for (int c8 = tid; c8 < chunks; c8 += kThreads) m = fmaxf(m, amax8(load8(c8)));
+            }
+            m = warp_max(m);
+            __syncthreads();
+            if (lane == 0) sred0[16 + warp] = m;
+            __syncthreads();
+            float mx = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sred0[16 + w]);
+            // S = 2^(e-126) > mx; X = x * 2^26 / S; results are scaled back by S / 2^26
+            const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
+            const bool live = e >= 26u && e < 255u;
+            const float inv = live ? __uint_as_float((279u - e) << 23) : 0.f;
+            const float inv16 = inv * 0.0625f;
+            if (tid == 0) sxscale[b] = live ? __uint_as_float((e - 25u) << 23) : 0.f;
+            // eight activations -> four digit planes (even columns | odd columns) + their share of the group sum
+            auto quantise = [&](int c8, const uint4& v, bool valid) {
+                float sum = 0.f;
+                if (valid) {
+                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+                    int de[4][4], dq[4][4];  // [pair][digit]: even / odd column of each pair
+                    float fs[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(u32_as_h2(u[j]));
+                        fs[j] = f.x + f.y;
+                        digits128_biased(__float2int_rn(f.x * inv), de[j]);
+                        digits128_biased(__float2int_rn(f.y * inv16), dq[j]);
+                    }
+                    sum = (fs[0] + fs[1]) + (fs[2] + fs[3]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint2 o;
+                        o.x = pack4(de[0][k], de[1][k], de[2][k], de[3][k]);
+                        o.y = pack4(dq[0][k], dq[1][k], dq[2][k], dq[3][k]);
+                        if (k < 3) { o.x = __vsub4(o.x, 0x40404040u); o.y = __vsub4(o.y, 0x40404040u); }
+                        *reinterpret_cast<uint2*>(xq + (size_t)(4 * b + 3 - k) * L.pitch_x + (size_t)c8 * 8) = o;
+                    }
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                if (valid && (c8 & 7) == 0) sxsum[(c8 >> 3) * 2 + b] = sum;
+            };
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < XR; ++i)
+                    if (256 * i < chunks) quantise(tid + 256 * i, xc[i], tid + 256 * i < chunks);
+            } else {
+                for (int base = 0; base < chunks; base += kThreads) {
+                    const int c8 = base + tid;
+                    quantise(c8, c8 < chunks ? load8(c8) : make_uint4(0, 0, 0, 0), c8 < chunks);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+// TG tile groups per CTA: the CTA's warps form TG teams of WARPS / TG warps; each team walks its
+// own tiles (splitting K among its warps) and only synchronises with itself.
+// Sync is called once, by every thread of every CTA, between the first weight requests and the
+// first read of the activations: the programmatic-dependent-launch wait of a stand-alone
+// launch, or the grid barrier that separates two phases of a multi-phase kernel.
+template <int MODE, int DEPTH, int WARPS, int GPS, int TG, class Sync>
+__device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* smem, Sync sync) {
+    using G = Geo<WARPS, GPS>;
+    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    constexpr int kThreads = G::kThreads;
+    constexpr int LPR = G::kPitch / 16;   // lanes that copy one row of a stage (4 or 8)
+    constexpr int RPI = 32 / LPR;         // rows per copy instruction (8 or 4)
+    constexpr int NI = kTileRows / RPI;   // copy instructions per set and stage (2 or 4)
+    constexpr int WG = WARPS / TG;        // warps per team
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int team = warp / WG, wl = warp % WG;
+    const ImmaLayout L = imma_layout(NW, DEPTH, WARPS, G::kSetBytes, a.cols, a.batch, TG);
+    uint8_t* xq = smem + L.xq;
+    float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
+    float* sxscale = reinterpret_cast<float*>(smem + L.xscale);
+    float* sred0 = reinterpret_cast<float*>(smem + L.red);                      // staging scratch (whole CTA)
+    float* sred = sred0 + (size_t)team * (2 * NW * 2 * kTileRows * 16);          // this team's K-partials
+    uint8_t* ring = smem + L.ring + (size_t)warp * DEPTH * L.stage_bytes;
+
+    const int tiles_total = a.ks;  // filled by the launcher
+    const int nchunks = a.cols / G::kStageCols;
+    // stages per warp and tile: contiguous K ranges whose sizes differ by at most one
+    const int base_cnt = nchunks / WG, extra = nchunks % WG;
+    const int c_begin = wl * base_cnt + min(wl, extra);
+    const int cnt = base_cnt + (wl < extra ? 1 : 0);
+    const int tile0 = (int)blockIdx.x * TG + team, tile_step = (int)gridDim.x * TG;
+    const int my_tiles = tile0 < tiles_total ? (tiles_total - 1 - tile0) / tile_step + 1 : 0;
+    const int total_stages = my_tiles * cnt;
+    const int groups_total = a.cols / kGroup;
+
+    // Plain mode may cover up to three tensors (segments) that share x; a tile belongs to one.
+    const int seg_end0 = (a.seg[0].rows + kTileRows - 1) / kTileRows;
+    const int seg_end1 = seg_end0 + (a.nseg > 1 ? (a.seg[1].rows + kTileRows - 1) / kTileRows : 0);
+    auto seg_of = [&](int tile, int& first_tile) {
+        const int sg = (a.nseg > 1 && tile >= seg_end0) + (a.nseg > 2 && tile >= seg_end1);
+        first_tile = sg == 0 ? 0 : (sg == 1 ? seg_end0 : seg_end1);
+        return sg;
+    };
+
+    // ── producer side: each warp copies the stages it will consume ──
+    const int fr = lane / LPR, fc = lane % LPR;
+    const int fsw = GPS == 2 ? ((fr >> 1) & 1) << 1 : (fr & 3) << 1;  // 16-byte chunk swizzle of this lane's rows
+    const uint32_t f_dst = fr * G::kPitch + ((fc ^ fsw) * 16);
+    const uint32_t f_sdst = G::kSetW + (lane >> 4) * G::kSetS + (lane & 15) * G::kRowS;
+    int f_tile = tile0, f_j = 0, f_n = 0, f_slot = 0;
+    // per tile: the tensors and this lane's byte offsets into them (stage 0 of the warp's K range)
+    const uint8_t* f_w[NW];
+    const __half* f_sb[NW];
+    uint32_t f_woff = 0, f_soff = 0, f_rows_ok = 0;  // bit h: copy row fr + RPI * h; bit 8: copy the scale piece
+    auto fetch_tile = [&]() {
+        int row0 = f_tile * kTileRows, rows = a.rows;
+        if (NW == 1) {
+            int first;
+            const int sg = seg_of(f_tile, first);
+            row0 = (f_tile - first) * kTileRows;
+            rows = sg == 0 ? a.seg[0].rows : (sg == 1 ? a.seg[1].rows : a.seg[2].rows);
+            f_w[0] = sg == 0 ? a.seg[0].w : (sg == 1 ? a.seg[1].w : a.seg[2].w);
+            const __half* ss = sg == 0 ? a.seg[0].s : (sg == 1 ? a.seg[1].s : a.seg[2].s);
+            const __half* bb = sg == 0 ? a.seg[0].b : (sg == 1 ? a.seg[1].b : a.seg[2].b);
+            f_sb[0] = lane < 16 ? ss : bb;
+        } else {
+#pragma unroll
+            for (int s = 0; s < NW; ++s) { f_w[s] = a.w[s]; f_sb[s] = lane < 16 ? a.s[s] : a.b[s]; }
+        }
+        f_woff = (uint32_t)(row0 + fr) * (uint32_t)(a.cols / 2) + (uint32_t)c_begin * G::kPitch + fc * 16;
+        f_soff = ((uint32_t)(row0 + (lane & 15)) * (uint32_t)groups_total + (uint32_t)c_begin * GPS) * 2u;
+        f_rows_ok = 0;
+#pragma unroll
+        for (int h = 0; h < NI; ++h) f_rows_ok |= (row0 + fr + RPI * h < rows ? 1u : 0u) << h;
+        f_rows_ok |= (row0 + (lane & 15) < rows ? 1u : 0u) << 8;
+    };
+    if (total_stages > 0) fetch_tile();
+    auto fetch = [&]() {
+        if (f_n < total_stages) {
+            uint8_t* st = ring + (size_t)f_slot * L.stage_bytes;
+            const uint32_t woff = f_woff + (uint32_t)f_j * G::kPitch;
+            const uint32_t soff = f_soff + (uint32_t)f_j * G::kRowS;
+#pragma unroll
+            for (int s = 0; s < NW; ++s) {
+                uint8_t* dst = st + s * G::kSetBytes;
+#pragma unroll
+                for (int h = 0; h < NI; ++h)
+                    if (f_rows_ok & (1u << h))
+                        cp_async16(dst + f_dst + h * RPI * G::kPitch, f_w[s] + woff + (uint32_t)(h * RPI) * (uint32_t)(a.cols / 2));
+                if (f_rows_ok & 0x100u) {
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(f_sb[s]) + soff;
+                    if (GPS == 2) cp_async4(dst + f_sdst, src); else cp_async8(dst + f_sdst, src);
+                }
+            }
+            ++f_n;
+            f_slot = f_slot + 1 == DEPTH ? 0 : f_slot + 1;
+            if (++f_j == cnt) {
+                f_j = 0;
+                f_tile += tile_step;
+                if (f_n < total_stages) fetch_tile();
+            }
+        }
+        cp_async_commit();  // always commit so that group counting stays uniform
+    };
+#pragma unroll
+    for (int i = 0; i < DEPTH - 1; ++i) fetch();
+
+    sync();
+    if (dyn_skip(a.dyn)) {
+        cp_async_wait<0>();  // copies in flight must land before the CTA's shared memory retires
+        return;
+    }
+
+    stage_activations<WARPS>(a.x, a.norm_w, a.norm_eps, a.cols, a.batch, L, smem);
+
+    // ── consumer side ──
+    // B operand: digit plane g (batch g / 4, digit 3 - g % 4), or zeros past the batch.
+    const bool bvalid = g < kDigits * a.batch;
+    const uint8_t* pb_base = bvalid ? xq + (size_t)g * L.pitch_x + t * 16 : smem + L.zero + t * 16;
+    const int pb_stride = bvalid ? kGroup : 0;
+    const float* pxs = sxsum + (t >> 1);  // this lane's columns belong to batch row t / 2
+    const int csw = GPS == 2 ? ((g >> 1) & 1) << 1 : (g & 3) << 1;
+    int w_off[GPS];
+#pragma unroll
+    for (int gg = 0; gg < GPS; ++gg) w_off[gg] = g * G::kPitch + (((2 * gg + (t >> 1)) ^ csw) * 16) + (t & 1) * 8;
+    const int s_off = G::kSetW + g * G::kRowS;
+    // the bias products of groups (t & 1) * GPS / 2 ... of a stage are this lane's
+    const int bias_g0 = (t & 1) * (GPS / 2);
+    const int b_off = G::kSetW + G::kSetS + g * G::kRowS + bias_g0 * 2;
+    const int magic = 0x4B400000;
+
+    int c_tile = tile0, slot = 0;
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        float acc[NW][2], bacc[NW][2];
+#pragma unroll
+        for (int s = 0; s < NW; ++s) acc[s][0] = acc[s][1] = bacc[s][0] = bacc[s][1] = 0.f;
+        for (int j = 0; j < cnt; ++j) {
+            cp_async_wait<DEPTH - 2>();  // this lane's copies of the stage have landed
+            __syncwarp();                // ... every lane's have, and every lane is done with the previous stage
+            fetch();                     // refill the buffer the previous stage used
+            const uint8_t* st = ring + (size_t)slot * L.stage_bytes;
+            slot = slot + 1 == DEPTH ? 0 : slot + 1;
+            const int grp0 = (c_begin + j) * GPS;
+#pragma unroll
+            for (int q = 0; q < GPS / 2; ++q) {
+                const float xs = pxs[(grp0 + bias_g0 + q) * 2];
+#pragma unroll
+                for (int s = 0; s < NW; ++s) {
+                    const uint8_t* base = st + s * G::kSetBytes + b_off + q * 2;
+                    bacc[s][0] = fmaf(__half2float(*reinterpret_cast<const __half*>(base)), xs, bacc[s][0]);
+                    bacc[s][1] = fmaf(__half2float(*reinterpret_cast<const __half*>(base + 8 * G::kRowS)), xs, bacc[s][1]);
+                }
+            }
+#pragma unroll
+            for (int gg = 0; gg < GPS; ++gg) {
+                const uint4 xb = *reinterpret_cast<const uint4*>(pb_base + (grp0 + gg) * pb_stride);
+#pragma unroll
+                for (int s = 0; s < NW; ++s) {
+                    const uint8_t* base = st + s * G::kSetBytes;
+                    const uint2 wa = *reinterpret_cast<const uint2*>(base + w_off[gg]);
+                    const uint2 wb = *reinterpret_cast<const uint2*>(base + w_off[gg] + 8 * G::kPitch);
+                    int c[4];
+                    mma_u8s8(c, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, xb.x, xb.y,
+                             magic, magic, magic, magic);
+                    mma_u8s8(c, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, xb.z, xb.w,
+                             c[0], c[1], c[2], c[3]);
+                    const float sa = __half2float(*reinterpret_cast<const __half*>(base + s_off + gg * 2));
+                    const float sb = __half2float(*reinterpret_cast<const __half*>(base + s_off + 8 * G::kRowS + gg * 2));
+                    // columns 2t, 2t+1 hold neighbouring digit planes: 128 * high + low
+                    const float va = fmaf(__int_as_float(c[0]) - kMagicF, 128.f, __int_as_float(c[1]) - kMagicF);
+                    const float vb = fmaf(__int_as_float(c[2]) - kMagicF, 128.f, __int_as_float(c[3]) - kMagicF);
+                    acc[s][0] = fmaf(sa, va, acc[s][0]);
+                    acc[s][1] = fmaf(sb, vb, acc[s][1]);
+                }
+            }
+        }
+        // ── tile done: lanes t = 0,1 (2,3) hold the upper and lower digit pairs of batch row 0 (1) ──
+        const int buf = ti & 1;
+        const float xscale = sxscale[t >> 1];
+#pragma unroll
+        for (int s = 0; s < NW; ++s)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float mine = acc[s][h], other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                const float tot = (t & 1) ? fmaf(other, 16384.f, mine) : fmaf(mine, 16384.f, other);
+                const float bs = bacc[s][h] + __shfl_xor_sync(0xffffffffu, bacc[s][h], 1);
+                if ((t & 1) == 0)
+                    sred[((((buf * NW + s) * 2 + (t >> 1)) * kTileRows) + g + 8 * h) * 16 + wl] = fmaf(tot, xscale, bs);
+            }
+        if (TG == 1) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(WG * 32) : "memory");
+        if (wl == (ti % WG)) {
+            // add the K-partials in warp order, write out: lane -> (batch row, tile row)
+            const int b = lane >> 4, r = lane & 15;
+            float tot[NW];
+#pragma unroll
+            for (int s = 0; s < NW; ++s) {
+                const float4* p = reinterpret_cast<const float4*>(sred + ((((buf * NW + s) * 2 + b) * kTileRows) + r) * 16);
+                float v = 0.f;
+#pragma unroll
+                for (int q = 0; q < WG / 4; ++q) {
+                    const float4 f = p[q];
+                    v += f.x; v += f.y; v += f.z; v += f.w;
+                }
+                tot[s] = v;
+            }
+            int first = 0, rows = a.rows;
+            __half* yout = a.y;
+            if (NW == 1) {
+                const int sg = seg_of(c_tile, first);
+                rows = sg == 0 ? a.seg[0].rows : (sg == 1 ? a.seg[1].rows : a.seg[2].rows);
+                yout = sg == 0 ? a.seg[0].y : (sg == 1 ? a.seg[1].y : a.seg[2].y);
+            }
+            const int row = (c_tile - first) * kTileRows + r;
+            if (row < rows && b < a.batch) {
+                const size_t o = (size_t)b * rows + row;
+                const float v0 = tot[0];
+                if (MODE == kAffinePlain) yout[o] = __float2half_rn(v0);
+                else if (MODE == kAffineAdd) yout[o] = __hadd(__float2half_rn(v0), a.residual[o]);  // lut_matvec.metal:1802-1803
+                else if (MODE == kAffineGateUp) a.y[o] = __float2half_rn(v0 / (1.0f + expf(-v0)) * tot[NW - 1]);  // :2228
+                else { a.y[o] = __float2half_rn(v0); a.y2[o] = __float2half_rn(tot[NW - 1]); }
+            }
+        }
+        c_tile += tile_step;
+    }
+    cp_async_wait<0>();
+}
+
+struct PdlSync {
+    __device__ __forceinline__ void operator()() const {
+        pdl_trigger();
+        pdl_wait();
+    }
+};
+
+}  // namespace imma
+}  // namespace smelt

@@ -483,6 +483,7 @@ cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int
         bool handled = false;
         cudaError_t e = launch_affine_imma(l, mode, args, group, &handled);  // batch 1 and 2
         if (handled || e != cudaSuccess) return e;
+        if (cudaError_t fe = flush_phases(l)) return fe;  // every other affine path is a real launch
         e = launch_affine_stream(l, mode, args, group, &handled);
         if (handled || e != cudaSuccess) return e;
         if (args.norm_w || args.nseg > 1) return cudaErrorNotSupported;  // only the streaming kernel fuses these

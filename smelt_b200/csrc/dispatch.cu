@@ -13,6 +13,7 @@
 #include "affine_matvec.h"
 #include "glue.h"
 #include "runtime.h"
+#include "phases.h"
 
 using namespace smelt;
 
@@ -250,6 +251,7 @@ Launch make_launch(const Interp& in, const Resolved& r) {
     l.stream = in.ctx->stream;
     l.pdl = in.ctx->pdl;
     if (in.device_pos) {
+        if (in.ctx->phases_on) l.phases = &in.ctx->recorder;  // graph capture: eligible launches become phases
         l.dyn = in.ctx->dyn_dev;
         l.guard_lt = r.guard_lt;
         l.guard_ge = r.guard_ge;
@@ -640,6 +642,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             NEED_BYTES(0, (size_t)count * 2);
             if (ctx->tp_world <= 1) return SMELT_OK;
             in.launches += 1;
+            if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
             return tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
         }
         case PK_TP_REDUCE_ADD: {
@@ -650,6 +653,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
                 bool handled = false;
                 smelt_status st = tp_reduce_add(ctx, l, r.buf[0].ptr, r.buf[1].ptr, r.buf[2].ptr, count, &handled);
                 if (st || handled) { in.launches += 1; return st; }
+                if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
                 st = tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
                 if (st) return st;
                 in.launches += 1;
@@ -672,6 +676,15 @@ smelt_status interpret(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, 
         if (rec.op_kind != SMELT_OP_DISPATCH) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record " + std::to_string(i) + ": unknown op kind");
         smelt_status s = run_record(in, rec);
         if (s) { ctx->err = "record " + std::to_string(i) + ": " + ctx->err; return s; }
+    }
+    if (device_pos && ctx->phases_on) {
+        Launch lf;
+        lf.stream = ctx->stream;
+        lf.phases = &ctx->recorder;
+        smelt_status s = check_cuda(ctx, flush_phases(lf), "multi-phase launch");
+        if (s) return s;
+        in.launches = in.launches - ctx->recorder.recorded + ctx->recorder.launches;  // recorded phases did not launch; the flushes did
+        ctx->recorder.recorded = ctx->recorder.launches = 0;
     }
     ctx->launch_count = in.launches;
     return SMELT_OK;

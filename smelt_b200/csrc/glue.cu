@@ -397,6 +397,8 @@ __global__ void __launch_bounds__(256) fp16_matvec_kernel(const __half* __restri
 
 cudaError_t launch_cfg(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block,
                        size_t smem) {
+    cudaError_t fe = flush_phases(l);
+    if (fe != cudaSuccess) return fe;
     cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -416,7 +418,8 @@ cudaError_t launch_cfg(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttri
     do {                                                             \
         cudaLaunchConfig_t cfg;                                      \
         cudaLaunchAttribute attr[1];                                 \
-        launch_cfg(l, cfg, attr, grid, block, smem);                 \
+        cudaError_t ce = launch_cfg(l, cfg, attr, grid, block, smem); \
+        if (ce != cudaSuccess) return ce;                            \
         prefer_max_shared(kernel);                                   \
         return cudaLaunchKernelEx(&cfg, kernel, __VA_ARGS__);        \
     } while (0)

@@ -47,6 +47,15 @@ struct AttnArgs {
     float rope_base_log2;
     const float* rope_table;  // optional: cos[half] | sin[half] of the position (launch_rope_table)
 };
+// What one attention launch (or one attention phase of the multi-phase kernel) works from.
+struct AttnDev {
+    AttnArgs a;
+    int nsplits;
+    int cluster;     // 1: the splits of a KV head are one thread-block cluster and merge through distributed shared memory
+    float* part_o;   // [batch*n_q, nsplits, head_dim]
+    float* part_ml;  // [batch*n_q, nsplits, 2]
+    DevDyn dyn;
+};
 size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits);
 int attention_max_splits();
 cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a);

@@ -74,6 +74,11 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     ctx->attn_scratch_bytes = attention_scratch_bytes(64, 256, 8, attention_max_splits());
     ok = ok && cudaMalloc(&ctx->attn_scratch, ctx->attn_scratch_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->rope_table, 256 * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc((void**)&ctx->recorder.barrier, sizeof(uint32_t)) == cudaSuccess;
+    ctx->recorder.err = ctx->err_dev;
+    ctx->recorder.sm_count = ctx->sm_count;
+    ctx->recorder.prog.n = 0;
+    if (const char* e = getenv("SMELT_PHASES")) ctx->phases_on = atoi(e) != 0;
     ok = ok && cudaMalloc(&ctx->attn_counters, 4096 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(ctx->attn_counters, 0, 4096 * sizeof(int)) == cudaSuccess;
     ctx->argmax_scratch_bytes = 64 * 1024 * sizeof(uint64_t);
@@ -107,6 +112,7 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     cudaFree(ctx->attn_scratch);
     cudaFree(ctx->attn_counters);
     cudaFree(ctx->rope_table);
+    cudaFree(ctx->recorder.barrier);
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gen_ring);
     cudaFree(ctx->gen_count);
@@ -139,6 +145,12 @@ smelt_status smelt_cuda_device_error(smelt_cuda_ctx* ctx, uint32_t* out_flags) {
         cudaMemset(ctx->err_dev, 0, 4);
         return fail(ctx, SMELT_ERR_DEVICE_TIMEOUT, "a kernel's bounded wait gave up (flags " + std::to_string(*out_flags) + ")");
     }
+    return SMELT_OK;
+}
+
+smelt_status smelt_cuda_enable_phases(smelt_cuda_ctx* ctx, int on) {
+    if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
+    ctx->phases_on = on != 0;
     return SMELT_OK;
 }
 

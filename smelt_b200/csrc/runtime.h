@@ -6,6 +6,7 @@
 
 #include "../../include/smelt_cuda.h"
 #include "common.cuh"
+#include "phases.h"
 
 namespace smelt {
 
@@ -99,6 +100,8 @@ struct smelt_cuda_ctx {
     // tensor parallel
     void* nccl_comm = nullptr;
     void* tp_peer = nullptr;   // peer-memory exchange state (tp.cu)
+    bool phases_on = false;    // graph capture turns runs of eligible launches into one multi-phase kernel
+    smelt::PhaseRecorder recorder;
     int tp_rank = 0, tp_world = 1;
 };
 

@@ -158,6 +158,7 @@ smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* par
     TpPeerState* st = (TpPeerState*)ctx->tp_peer;
     if (!st || !st->open || count == 0 || count % 8 || count > (size_t)kTpMaxCount) return SMELT_OK;
     if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out)) & 15u) return SMELT_OK;
+    if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
     TpExchange ex = {};
     const size_t data_bytes = (size_t)2 * ctx->tp_world * kTpMaxCount * sizeof(__half);
     for (int r = 0; r < ctx->tp_world; ++r) {

@@ -176,3 +176,24 @@ def test_capture_replay_runs_the_recorded_launches(ctx, oracle):
     assert 0 < ms.value < 50
     assert rel_err(y.download(np.float16, (1, rows)), oracle.affine_matvec(w, s, b, x, rows, cols, 64)) < 2e-3
     assert ctx.call_status("capture_end") == capi.BAD_ARGUMENT  # nothing open
+
+
+def test_multi_phase_kernel_keeps_every_bit(ctx, oracle):
+    """The experimental multi-phase kernel runs the same device code per record: same tokens, same logits."""
+    cfg, cap, n_dec = MID, 64, 16
+    prompt = synth.rng_for(8, "prompt").integers(0, cfg.vocab, size=7).astype(np.int32)
+    _, plain = make(ctx, cfg, 8, cap, fuse=3)
+    want = plain.generate(prompt, n_dec, use_graph=True)[:, 0]
+    logits = plain.logits()[0].copy()
+    ctx.call("enable_phases", 1)
+    try:
+        _, phased = make(ctx, cfg, 8, cap, fuse=3)
+        got = phased.generate(prompt, n_dec, use_graph=True)[:, 0]
+        assert ctx.lib.smelt_cuda_last_launch_count(ctx.h) < 3 * cfg.layers + 12  # the layers' launches collapsed
+        assert np.array_equal(got, want)
+        assert np.array_equal(phased.logits()[0].view(np.uint16), logits.view(np.uint16))
+        flags = C.c_uint32(0)
+        ctx._check(ctx.lib.smelt_cuda_device_error(ctx.h, C.byref(flags)))
+        assert flags.value == 0
+    finally:
+        ctx.call("enable_phases", 0)
