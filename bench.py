@@ -138,8 +138,9 @@ def run_ours(args):
     t0 = time.time()
     pkg = package.SyntheticPackage(cfg, SEED)
     keep = rank == 0 and world == 1 and not args.no_cpu_baseline
-    image, desc, layers = package.build_image(pkg, rank, world, keep_for_oracle=keep)
-    fuse = (3 if args.table == "fused" else 0) | (4 if world > 1 and args.collective == "peer" else 0)
+    peer = world > 1 and args.collective == "peer"
+    image, desc, layers = package.build_image(pkg, rank, world, keep_for_oracle=keep, vocab_parallel=peer)
+    fuse = (3 if args.table == "fused" else 0) | (12 if peer else 0)  # 4: fused all-reduce + add, 8: vocab-parallel LM head
     dec = package.Decoder(ctx, image, desc, layers, capacity, B, fuse_residual=fuse)
     del image
     dec.build_graph()

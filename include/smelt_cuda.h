@@ -229,7 +229,8 @@ typedef struct {
                               bit 1: fold each RMS norm into the projection that follows it (one Q/K/V launch, one
                               gate/up launch) and RoPE + KV append + attention into one launch (the smelt_*
                               extension kernels); bit 2 (tp_world > 1): all-reduce + residual add as one
-                              smelt_tp_reduce_add record */
+                              smelt_tp_reduce_add record; bit 3 (tp_world > 1): lm_head addresses this rank's
+                              vocab / tp_world rows and the ranks exchange their best keys (smelt_tp_argmax) */
 } smelt_decoder_desc;
 /* Allocates the activation / KV / scratch slots for `desc` at `capacity` positions and
  * `batch` sequences, registers the pipelines, configures the context and writes the table.
@@ -258,7 +259,8 @@ SMELT_CUDA_API smelt_status smelt_cuda_tp_all_reduce_f16(smelt_cuda_ctx* ctx, vo
  * this rank's partial, 1 residual, 2 out, constant 3 = element count): every rank publishes the
  * IPC handle of its exchange buffer (exchange_handle), the caller gathers the handles of all
  * ranks in rank order and every rank maps them (exchange_open).  A reduction is then one launch
- * per rank: partials are pushed into the peers' buffers over NVLink, a sequence flag follows,
+ * per rank: partials are pushed into the peers' buffers over NVLink in 8-byte stores that carry
+ * their sequence number (no fence, no separate flag),
  * each rank adds the partials in rank order in fp32, rounds once to fp16 and adds the residual.
  * Waits are bounded; a peer that never arrives sets bit 8 of the device error word
  * (smelt_cuda_device_error).  Without open exchange buffers the record falls back to

@@ -67,145 +67,19 @@ __device__ __forceinline__ float amax8(const uint4& v) {
 }
 
 // Four signed base-128 digits of X (|X| < 2^27), least significant first, each in [-64, 63]
-// except the last, which takes what remains.  With Y = X + 64 (1 + 128 + 128^2) the 7-bit
-// fields of Y are digit + 64 and Y >> 21 is the last digit, so the three low digits come out
-// biased by 64 here and the bias is taken off four bytes at a time after packing.
-constexpr int kDigitBias = 64 + 64 * 128 + 64 * 128 * 128;
-__device__ __forceinline__ void digits128_biased(int X, int (&d)[4]) {
-    const int Y = X + kDigitBias;
-    d[0] = Y & 127;
-    d[1] = (Y >> 7) & 127;
-    d[2] = (Y >> 14) & 127;
-    d[3] = Y >> 21;
+// except the last, which takes what remains.
+__device__ __forceinline__ void digits128(int X, int (&d)[4]) {
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        d[k] = ((X + 64) & 127) - 64;
+        X = (X - d[k]) >> 7;
+    }
+    d[3] = X;
 }
 
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
-
-// The activations of one launch as digit planes + per-group sums, once per CTA (all threads
-// call it).  Kept out of line: its register needs must not shape the allocation of the
-// streaming loop.
-template <int WARPS>
-__device__ __noinline__ void stage_activations(const __half* x, const __half* norm_w, float norm_eps, int cols, int batch,
-                                               const ImmaLayout L, uint8_t* smem) {
-    struct { const __half* x; const __half* norm_w; float norm_eps; int cols, batch; } a = {x, norm_w, norm_eps, cols, batch};
-    constexpr int kThreads = WARPS * 32;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint8_t* xq = smem + L.xq;
-    float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
-    float* sxscale = reinterpret_cast<float*>(smem + L.xscale);
-    float* sred0 = reinterpret_cast<float*>(smem + L.red);
-    const int groups_total = a.cols / kGroup;
-
-        const int chunks = a.cols / 8;
-        if (tid < 4) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
-        if (a.batch == 1)
-            for (int i = tid; i < groups_total; i += kThreads) sxsum[i * 2 + 1] = 0.f;
-        // Rows of up to 12288 activations stay in registers between the passes (six 16-byte words
-        // per thread, the chunk order of cta256_sumsq_f16); longer rows are read again per pass.
-        constexpr int XR = 6;
-        const bool cached = kThreads == 256 && chunks <= XR * 256;
-        for (int b = 0; b < a.batch; ++b) {
-            const __half* xr = a.x + (size_t)b * a.cols;
-            uint4 xc[XR];
-#pragma unroll
-            for (int i = 0; i < XR; ++i) xc[i] = make_uint4(0, 0, 0, 0);
-            if (cached) {
-#pragma unroll
-                for (int i = 0; i < XR; ++i)
-                    if (tid + 256 * i < chunks) xc[i] = *reinterpret_cast<const uint4*>(xr + (tid + 256 * i) * 8);
-            }
-            float rs = 0.f;
-            if (a.norm_w) {
-                // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass;
-                // sred is free here: no tile has been reduced yet
-                float ss = 0.f;
-#pragma unroll
-                for (int i = 0; i < XR; ++i) ss = sumsq8(ss, xc[i]);  // words past the row are zero: no contribution
-                const float tot = cached ? cta256_sum_finish(ss, sred0) : cta256_sumsq_f16(xr, a.cols, sred0);
-                rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
-                if (cached) {
-#pragma unroll
-                    for (int i = 0; i < XR; ++i)
-                        if (tid + 256 * i < chunks) {
-                            const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + (tid + 256 * i) * 8);
-                            xc[i].x = rms_norm_1pw_pair(xc[i].x, wv.x, rs); xc[i].y = rms_norm_1pw_pair(xc[i].y, wv.y, rs);
-                            xc[i].z = rms_norm_1pw_pair(xc[i].z, wv.z, rs); xc[i].w = rms_norm_1pw_pair(xc[i].w, wv.w, rs);
-                        }
-                }
-            }
-            auto load8 = [&](int c8) {  // uncached path: read (and normalise) again
-                uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
-                if (a.norm_w) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
-                    v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
-                    v.z = rms_norm_1pw_pair(v.z, wv.z, rs); v.w = rms_norm_1pw_pair(v.w, wv.w, rs);
-                }
-                return v;
-            };
-            float m = 0.f;
-            if (cached) {
-#pragma unroll
-                for (int i = 0; i < XR; ++i) m = fmaxf(m, amax8(xc[i]));  // words past the row are zero
-            } else {
-                for (int c8 = tid; c8 < chunks; c8 += kThreads) m = fmaxf(m, amax8(load8(c8)));
-            }
-            m = warp_max(m);
-            __syncthreads();
-            if (lane == 0) sred0[16 + warp] = m;
-            __syncthreads();
-            float mx = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sred0[16 + w]);
-            // S = 2^(e-126) > mx; X = x * 2^26 / S; results are scaled back by S / 2^26
-            const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
-            const bool live = e >= 26u && e < 255u;
-            const float inv = live ? __uint_as_float((279u - e) << 23) : 0.f;
-            const float inv16 = inv * 0.0625f;
-            if (tid == 0) sxscale[b] = live ? __uint_as_float((e - 25u) << 23) : 0.f;
-            // eight activations -> four digit planes (even columns | odd columns) + their share of the group sum
-            auto quantise = [&](int c8, const uint4& v, bool valid) {
-                float sum = 0.f;
-                if (valid) {
-                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-                    int de[4][4], dq[4][4];  // [pair][digit]: even / odd column of each pair
-                    float fs[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 f = __half22float2(u32_as_h2(u[j]));
-                        fs[j] = f.x + f.y;
-                        digits128_biased(__float2int_rn(f.x * inv), de[j]);
-                        digits128_biased(__float2int_rn(f.y * inv16), dq[j]);
-                    }
-                    sum = (fs[0] + fs[1]) + (fs[2] + fs[3]);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint2 o;
-                        o.x = pack4(de[0][k], de[1][k], de[2][k], de[3][k]);
-                        o.y = pack4(dq[0][k], dq[1][k], dq[2][k], dq[3][k]);
-                        if (k < 3) { o.x = __vsub4(o.x, 0x40404040u); o.y = __vsub4(o.y, 0x40404040u); }
-                        *reinterpret_cast<uint2*>(xq + (size_t)(4 * b + 3 - k) * L.pitch_x + (size_t)c8 * 8) = o;
-                    }
-                }
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-                if (valid && (c8 & 7) == 0) sxsum[(c8 >> 3) * 2 + b] = sum;
-            };
-            if (cached) {
-#pragma unroll
-                for (int i = 0; i < XR; ++i)
-                    if (256 * i < chunks) quantise(tid + 256 * i, xc[i], tid + 256 * i < chunks);
-            } else {
-                for (int base = 0; base < chunks; base += kThreads) {
-                    const int c8 = base + tid;
-                    quantise(c8, c8 < chunks ? load8(c8) : make_uint4(0, 0, 0, 0), c8 < chunks);
-                }
-            }
-        }
-        __syncthreads();
-    }
 
 // TG tile groups per CTA: the CTA's warps form TG teams of WARPS / TG warps; each team walks its
 // own tiles (splitting K among its warps) and only synchronises with itself.
@@ -234,10 +108,9 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
 
     const int tiles_total = a.ks;  // filled by the launcher
     const int nchunks = a.cols / G::kStageCols;
-    // stages per warp and tile: contiguous K ranges whose sizes differ by at most one
-    const int base_cnt = nchunks / WG, extra = nchunks % WG;
-    const int c_begin = wl * base_cnt + min(wl, extra);
-    const int cnt = base_cnt + (wl < extra ? 1 : 0);
+    const int cpw = (nchunks + WG - 1) / WG;  // stages per warp and tile: a contiguous K range
+    const int c_begin = min(wl * cpw, nchunks);
+    const int cnt = min(c_begin + cpw, nchunks) - c_begin;
     const int tile0 = (int)blockIdx.x * TG + team, tile_step = (int)gridDim.x * TG;
     const int my_tiles = tile0 < tiles_total ? (tiles_total - 1 - tile0) / tile_step + 1 : 0;
     const int total_stages = my_tiles * cnt;
@@ -321,7 +194,96 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
         return;
     }
 
-    stage_activations<WARPS>(a.x, a.norm_w, a.norm_eps, a.cols, a.batch, L, smem);
+    // ── activations: digit planes + per-group sums, once per CTA ──
+    {
+        const int chunks = a.cols / 8;
+        if (tid < 4) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
+        if (a.batch == 1)
+            for (int i = tid; i < groups_total; i += kThreads) sxsum[i * 2 + 1] = 0.f;
+        // Rows of up to 4096 activations stay in registers between the passes (two 16-byte words
+        // per thread, the chunk order of cta256_sumsq_f16); longer rows are read again per pass.
+        const bool cached = kThreads == 256 && chunks <= 2 * 256;
+        for (int b = 0; b < a.batch; ++b) {
+            const __half* xr = a.x + (size_t)b * a.cols;
+            uint4 xc[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    if (tid + 256 * i < chunks) xc[i] = *reinterpret_cast<const uint4*>(xr + (tid + 256 * i) * 8);
+            }
+            float rs = 0.f;
+            if (a.norm_w) {
+                // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass;
+                // sred is free here: no tile has been reduced yet
+                const float tot = cached ? cta256_sum_finish(sumsq8(sumsq8(0.f, xc[0]), xc[1]), sred0) : cta256_sumsq_f16(xr, a.cols, sred0);
+                rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
+                if (cached) {
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+                        if (tid + 256 * i < chunks) {
+                            const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + (tid + 256 * i) * 8);
+                            xc[i].x = rms_norm_1pw_pair(xc[i].x, wv.x, rs); xc[i].y = rms_norm_1pw_pair(xc[i].y, wv.y, rs);
+                            xc[i].z = rms_norm_1pw_pair(xc[i].z, wv.z, rs); xc[i].w = rms_norm_1pw_pair(xc[i].w, wv.w, rs);
+                        }
+                }
+            }
+            auto load8 = [&](int c8) {
+                if (cached) return c8 < 256 ? xc[0] : xc[1];  // c8 = tid or tid + 256
+                uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                if (a.norm_w) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
+                    v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
+                    v.z = rms_norm_1pw_pair(v.z, wv.z, rs); v.w = rms_norm_1pw_pair(v.w, wv.w, rs);
+                }
+                return v;
+            };
+            float m = 0.f;
+            for (int c8 = tid; c8 < chunks; c8 += kThreads) m = fmaxf(m, amax8(load8(c8)));
+            m = warp_max(m);
+            __syncthreads();
+            if (lane == 0) sred0[16 + warp] = m;
+            __syncthreads();
+            float mx = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sred0[16 + w]);
+            // S = 2^(e-126) > mx; X = x * 2^26 / S; results are scaled back by S / 2^26
+            const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
+            const bool live = e >= 26u && e < 255u;
+            const float inv = live ? __uint_as_float((279u - e) << 23) : 0.f;
+            const float inv16 = inv * 0.0625f;
+            if (tid == 0) sxscale[b] = live ? __uint_as_float((e - 25u) << 23) : 0.f;
+            for (int base = 0; base < chunks; base += kThreads) {
+                const int c8 = base + tid;
+                float sum = 0.f;
+                if (c8 < chunks) {
+                    const uint4 v = load8(c8);
+                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+                    int de[4][4], dq[4][4];  // [pair][digit]: even / odd column of each pair
+                    float fs[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(u32_as_h2(u[j]));
+                        fs[j] = f.x + f.y;
+                        digits128(__float2int_rn(f.x * inv), de[j]);
+                        digits128(__float2int_rn(f.y * inv16), dq[j]);
+                    }
+                    sum = (fs[0] + fs[1]) + (fs[2] + fs[3]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint2 o;
+                        o.x = pack4(de[0][k], de[1][k], de[2][k], de[3][k]);
+                        o.y = pack4(dq[0][k], dq[1][k], dq[2][k], dq[3][k]);
+                        *reinterpret_cast<uint2*>(xq + (size_t)(4 * b + 3 - k) * L.pitch_x + (size_t)c8 * 8) = o;
+                    }
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                if (c8 < chunks && (c8 & 7) == 0) sxsum[(c8 >> 3) * 2 + b] = sum;
+            }
+        }
+        __syncthreads();
+    }
 
     // ── consumer side ──
     // B operand: digit plane g (batch g / 4, digit 3 - g % 4), or zeros past the batch.

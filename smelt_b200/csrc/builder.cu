@@ -224,10 +224,15 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
     }
     // final norm, LM head, argmax (TopLevelEmitter.swift:657-930)
     Rec(e, "rms_norm_1pw", B).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, d->final_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
-    Rec(e, "fp16_matvec", V, B).buf(0, kWeights, d->lm_head).buf(1, kNormOut).buf(2, kLogits).u32(3, H);
-    const int chunk = 2048, parts = (V + chunk - 1) / chunk;
-    Rec(e, "argmax_fp16_partials", parts, B).buf(0, kLogits).buf(1, kArgmaxScratch).u32(2, V).u32(3, chunk);
-    Rec(e, "argmax_key_reduce", 1, B).buf(0, kArgmaxScratch).buf(1, kArgmax).u32(2, parts);
+    // bit 3 (tp_world > 1): the LM head is split by vocab rows (lm_head addresses this rank's
+    // slice), logits hold the slice, and the ranks exchange their best keys
+    const bool vocab_par = tp && (d->fuse_residual & 8) && V % d->tp_world == 0;
+    const int Vl = vocab_par ? V / d->tp_world : V;
+    Rec(e, "fp16_matvec", Vl, B).buf(0, kWeights, d->lm_head).buf(1, kNormOut).buf(2, kLogits).u32(3, H);
+    const int chunk = 2048, parts = (Vl + chunk - 1) / chunk;
+    Rec(e, "argmax_fp16_partials", parts, B).buf(0, kLogits).buf(1, kArgmaxScratch).u32(2, Vl).u32(3, chunk);
+    if (vocab_par) Rec(e, "smelt_tp_argmax", 1, B).buf(0, kArgmaxScratch).buf(1, kArgmax).u32(2, parts).u32(3, (uint32_t)(d->tp_rank * Vl));
+    else Rec(e, "argmax_key_reduce", 1, B).buf(0, kArgmaxScratch).buf(1, kArgmax).u32(2, parts);
 
     const size_t need = e.n;
     if (records && need > *n_records) {

@@ -117,6 +117,7 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"swiglu_fused", PK_SWIGLU, 0, false},
         {"smelt_tp_all_reduce", PK_TP_ALL_REDUCE, 0, false},
         {"smelt_tp_reduce_add", PK_TP_REDUCE_ADD, 0, false},
+        {"smelt_tp_argmax", PK_TP_ARGMAX, 0, false},
         {"smelt_rope_qkv_append", PK_ROPE_QKV_APPEND, 0, false},
         {"smelt_rope_attention_decode", PK_ATTN_ROPE, 0, false},
     };
@@ -644,6 +645,15 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             in.launches += 1;
             if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
             return tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
+        }
+        case PK_TP_ARGMAX: {
+            // 0 this rank's partial keys (argmax_fp16_partials over its vocab slice), 1 out token ids;
+            // 2 partials per sequence, 3 first vocab row of the slice
+            NEED_BUF(0); NEED_BUF(1); NEED_U32(2, parts); NEED_U32(3, offset);
+            const int batch = batch_of(rec);
+            NEED_BYTES(0, (size_t)batch * parts * 8); NEED_BYTES(1, (size_t)batch * 4);
+            in.launches += 1;
+            return tp_argmax(ctx, l, r.buf[0].ptr, r.buf[1].ptr, (int)parts, offset, batch);
         }
         case PK_TP_REDUCE_ADD: {
             // 0 this rank's partial (reduced in place on the fallback path), 1 residual, 2 out, 3 count

@@ -46,6 +46,7 @@ enum PipeKind : int {
     PK_ROPE_QKV_APPEND,
     PK_ATTN_ROPE,
     PK_TP_REDUCE_ADD,
+    PK_TP_ARGMAX,
 };
 
 struct Pipeline {
@@ -110,6 +111,7 @@ smelt_status fail(smelt_cuda_ctx* ctx, smelt_status code, const std::string& msg
 smelt_status check_cuda(smelt_cuda_ctx* ctx, cudaError_t e, const char* what);
 smelt_status tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data, size_t count, cudaStream_t stream);
 void tp_destroy(smelt_cuda_ctx* ctx);
+smelt_status tp_argmax(smelt_cuda_ctx* ctx, const Launch& l, const void* partials, void* out, int n, uint32_t offset, int batch);
 smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* partial, const void* residual, void* out, size_t count,
                            bool* handled);
 }  // namespace smelt

@@ -61,82 +61,116 @@ smelt_status tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data, size_t count, cu
 
 // ── all-reduce + residual add over peer memory ──────────────────────────────
 // Every rank owns an exchange buffer that its peers can write (CUDA IPC mapping over NVLink):
-//   data  [2 buffers][world sources][kTpMaxCount fp16]   partial row-parallel outputs
-//   flags [2 buffers][world sources] uint32               sequence number of the data beside it
-// One launch per reduction, one CTA per rank: the CTA pushes its partial into slot [rank] of
-// every peer's buffer (plain remote stores, no loads cross NVLink), fences, publishes the
-// reduction's sequence number in every peer's flag, waits (bounded) until all of its own
-// flags carry that number, then adds the world's partials in rank order in fp32, rounds once
-// to fp16 and adds the residual as elementwise_add does.  Every rank adds the same values in
-// the same order, so the replicated hidden state stays bit-identical across ranks.  Two
-// buffers alternate: a rank cannot be more than one reduction ahead of a peer, because it
-// cannot finish reduction k + 1 before every peer has published k + 1.
+//   ll [2 buffers][world sources][kTpMaxCount / 2] of {two fp16 values, sequence number}
+// One launch per reduction, one CTA per rank.  The CTA pushes its partial into slot [rank] of
+// every rank's buffer as 8-byte stores that carry four bytes of data and the reduction's
+// sequence number together (no fence and no separate flag: a word is valid as soon as its
+// number matches, the way NCCL's low-latency protocol packs data and flag); nothing is loaded
+// across NVLink.  It then polls its own buffer (bounded) word by word, adds the world's
+// partials in rank order in fp32, rounds once to fp16 and adds the residual as elementwise_add
+// does.  Every rank adds the same values in the same order, so the replicated hidden state
+// stays bit-identical across ranks.  Two buffers alternate: a rank cannot be more than one
+// reduction ahead of a peer, because it cannot finish reduction k + 1 before every peer has
+// pushed k + 1, which the peer does after it has finished reading k.
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpMaxCount = 8 * 8192;            // elements per reduction (batch 8 x hidden 8192)
-constexpr uint32_t kTpSpinLimit = 1u << 21;      // about a second of polling, then give up with an error flag
+constexpr uint32_t kTpSpinLimit = 1u << 21;      // about a second of polling per word, then give up with an error flag
 
 struct TpExchange {
-    __half* data[kTpMaxWorld];      // data region of every rank's buffer, as mapped into this process
-    uint32_t* flags[kTpMaxWorld];   // flag region of every rank's buffer
-    uint32_t* seq;                  // this rank's reduction counter (device memory)
+    uint2* ll[kTpMaxWorld];   // every rank's buffer, as mapped into this process
+    uint32_t* seq;            // this rank's reduction counter (device memory)
     int rank, world;
 };
 
-__host__ __device__ inline size_t tp_data_index(int buf, int src, int world) { return ((size_t)buf * world + src) * kTpMaxCount; }
+__host__ __device__ inline size_t tp_ll_index(int buf, int src, int world) { return ((size_t)buf * world + src) * (kTpMaxCount / 2); }
+
+__device__ __forceinline__ void st_volatile_v2(uint2* p, uint32_t a, uint32_t b) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_volatile_v2(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 
 __global__ void __launch_bounds__(1024) tp_reduce_add_kernel(TpExchange ex, const __half* partial, const __half* residual, __half* out,
                                                              int count, uint32_t* err, DevDyn dyn) {
     pdl_trigger();
     pdl_wait();
     if (dyn_skip(dyn)) return;
-    __shared__ uint32_t s_seq;
     const int tid = threadIdx.x;
-    if (tid == 0) s_seq = *ex.seq + 1u;
+    const uint32_t seq = *ex.seq + 1u;  // read by every thread before thread 0 overwrites it at the end
     __syncthreads();
-    const uint32_t seq = s_seq;
     const int buf = (int)(seq & 1u);
-    // push this rank's partial into every rank's buffer (its own included)
-    const int chunks = count / 8;
-    for (int r = 0; r < ex.world; ++r) {
-        uint4* dst = reinterpret_cast<uint4*>(ex.data[r] + tp_data_index(buf, ex.rank, ex.world));
-        for (int i = tid; i < chunks; i += blockDim.x) dst[i] = reinterpret_cast<const uint4*>(partial)[i];
+    const int words = count / 2;
+    const uint32_t* pw = reinterpret_cast<const uint32_t*>(partial);
+    for (int i = tid; i < words; i += blockDim.x) {
+        const uint32_t v = pw[i];
+        for (int r = 0; r < ex.world; ++r) st_volatile_v2(ex.ll[r] + tp_ll_index(buf, ex.rank, ex.world) + i, v, seq);
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < ex.world) {
-        volatile uint32_t* f = ex.flags[tid] + buf * ex.world + ex.rank;
-        *f = seq;  // tells rank tid that this rank's data for this reduction has landed
-    }
-    // wait for every source's flag in this rank's own buffer
-    if (tid < ex.world) {
-        volatile uint32_t* f = ex.flags[ex.rank] + buf * ex.world + tid;
-        uint32_t spins = 0;
-        while ((int32_t)(*f - seq) < 0 && ++spins < kTpSpinLimit) {}
-        if (spins >= kTpSpinLimit && err) atomicOr(err, 0x100u);  // peer never arrived: results are not valid
-    }
-    __syncthreads();
-    __threadfence_system();
-    const __half* mine = ex.data[ex.rank];
-    for (int i = tid; i < chunks; i += blockDim.x) {
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    const uint2* mine = ex.ll[ex.rank];
+    bool gave_up = false;
+    for (int i = tid; i < words; i += blockDim.x) {
+        float acc0 = 0.f, acc1 = 0.f;
         for (int r = 0; r < ex.world; ++r) {
-            const uint4 v = __ldcv(reinterpret_cast<const uint4*>(mine + tp_data_index(buf, r, ex.world)) + i);
-            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(u32_as_h2(u[j]));
-                acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
-            }
+            const uint2* src = mine + tp_ll_index(buf, r, ex.world) + i;
+            uint2 v = ld_volatile_v2(src);
+            uint32_t spins = 0;
+            while (v.y != seq && !gave_up && ++spins < kTpSpinLimit) v = ld_volatile_v2(src);
+            gave_up |= v.y != seq;
+            const float2 f = __half22float2(u32_as_h2(v.x));
+            acc0 += f.x; acc1 += f.y;
         }
-        const uint4 rv = reinterpret_cast<const uint4*>(residual)[i];
-        const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)  // half(sum) + residual as an fp16 add (activations.metal elementwise_add)
-            o[j] = h2_as_u32(__hadd2(__floats2half2_rn(acc[2 * j], acc[2 * j + 1]), u32_as_h2(ru[j])));
-        reinterpret_cast<uint4*>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        // half(sum) + residual as an fp16 add (activations.metal elementwise_add)
+        const uint32_t rv = reinterpret_cast<const uint32_t*>(residual)[i];
+        reinterpret_cast<uint32_t*>(out)[i] = h2_as_u32(__hadd2(__floats2half2_rn(acc0, acc1), u32_as_h2(rv)));
+    }
+    if (gave_up && err) atomicOr(err, 0x100u);  // a peer never arrived: results are not valid
+    if (tid == 0) *ex.seq = seq;
+}
+
+// Vocab-parallel argmax: every rank holds the ordered keys (lut_matvec.metal:4045-4074) of its
+// slice of the logits; the best local key, with the slice's offset folded into its index half,
+// goes to every rank through the same packed words, and every rank takes the largest.
+__global__ void __launch_bounds__(256) tp_argmax_kernel(TpExchange ex, uint2* const* regions, const uint64_t* partials, int32_t* out,
+                                                        int n, uint32_t offset, int batch, uint32_t* err, DevDyn dyn) {
+    __shared__ uint64_t sbest[8];
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const int tid = threadIdx.x;
+    const uint32_t seq = *ex.seq + 1u;
+    __syncthreads();
+    const int buf = (int)(seq & 1u);
+    for (int b = 0; b < batch; ++b) {
+        uint64_t best = 0;
+        for (int i = tid; i < n; i += blockDim.x) { const uint64_t k = partials[(size_t)b * n + i]; best = k > best ? k : best; }
+        for (int o = 16; o > 0; o >>= 1) { const uint64_t other = __shfl_xor_sync(0xffffffffu, best, o); best = other > best ? other : best; }
+        if ((tid & 31) == 0) sbest[tid >> 5] = best;
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < 8; ++w) best = sbest[w] > best ? sbest[w] : best;
+            best -= offset;  // index half is 0xFFFFFFFF - index: the slice's first row is global row `offset`
+            for (int r = 0; r < ex.world; ++r) {
+                uint2* dst = regions[r] + ((size_t)(buf * ex.world + ex.rank) * 8 + b) * 2;
+                st_volatile_v2(dst, (uint32_t)best, seq);
+                st_volatile_v2(dst + 1, (uint32_t)(best >> 32), seq);
+            }
+            uint64_t top = 0;
+            bool gave_up = false;
+            for (int r = 0; r < ex.world; ++r) {
+                const uint2* src = regions[ex.rank] + ((size_t)(buf * ex.world + r) * 8 + b) * 2;
+                uint2 lo = ld_volatile_v2(src), hi = ld_volatile_v2(src + 1);
+                uint32_t spins = 0;
+                while ((lo.y != seq || hi.y != seq) && !gave_up && ++spins < kTpSpinLimit) { lo = ld_volatile_v2(src); hi = ld_volatile_v2(src + 1); }
+                gave_up |= lo.y != seq || hi.y != seq;
+                const uint64_t k = ((uint64_t)hi.x << 32) | lo.x;
+                top = k > top ? k : top;
+            }
+            if (gave_up && err) atomicOr(err, 0x100u);
+            out[b] = (int32_t)(0xFFFFFFFFu - (uint32_t)top);
+        }
+        __syncthreads();
     }
     if (tid == 0) *ex.seq = seq;
 }
@@ -145,10 +179,14 @@ struct TpPeerState {
     void* local = nullptr;               // this rank's exchange buffer
     void* mapped[kTpMaxWorld] = {};      // every rank's buffer as mapped here ([rank] = local)
     uint32_t* seq = nullptr;
+    uint2** argmax_regions = nullptr;    // device array: every rank's argmax words, as mapped here
     bool open = false;
 };
 
-size_t tp_exchange_bytes(int world) { return (size_t)2 * world * kTpMaxCount * sizeof(__half) + 2 * world * sizeof(uint32_t) + 256; }
+constexpr size_t kTpArgmaxBytes = (size_t)2 * kTpMaxWorld * 8 * 2 * sizeof(uint2);  // [buffer][source][sequence, 8][2 words]
+
+size_t tp_ll_bytes(int world) { return (size_t)2 * world * (kTpMaxCount / 2) * sizeof(uint2); }
+size_t tp_exchange_bytes(int world) { return tp_ll_bytes(world) + kTpArgmaxBytes; }
 
 // Fused all-reduce + residual add when the exchange buffers are open and the shape fits;
 // *handled tells the caller whether it ran.
@@ -156,15 +194,11 @@ smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* par
                            size_t count, bool* handled) {
     *handled = false;
     TpPeerState* st = (TpPeerState*)ctx->tp_peer;
-    if (!st || !st->open || count == 0 || count % 8 || count > (size_t)kTpMaxCount) return SMELT_OK;
-    if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out)) & 15u) return SMELT_OK;
+    if (!st || !st->open || count == 0 || count % 2 || count > (size_t)kTpMaxCount) return SMELT_OK;
+    if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out)) & 3u) return SMELT_OK;
     if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
     TpExchange ex = {};
-    const size_t data_bytes = (size_t)2 * ctx->tp_world * kTpMaxCount * sizeof(__half);
-    for (int r = 0; r < ctx->tp_world; ++r) {
-        ex.data[r] = (__half*)st->mapped[r];
-        ex.flags[r] = (uint32_t*)((char*)st->mapped[r] + data_bytes);
-    }
+    for (int r = 0; r < ctx->tp_world; ++r) ex.ll[r] = (uint2*)st->mapped[r];
     ex.seq = st->seq; ex.rank = ctx->tp_rank; ex.world = ctx->tp_world;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1);
@@ -181,8 +215,32 @@ smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* par
                                               (int)count, ctx->err_dev, dev_dyn(l)), "tp reduce add");
 }
 
+// Cross-rank argmax over vocab slices (see tp_argmax_kernel); needs the open exchange.
+smelt_status tp_argmax(smelt_cuda_ctx* ctx, const Launch& l, const void* partials, void* out, int n, uint32_t offset, int batch) {
+    TpPeerState* st = (TpPeerState*)ctx->tp_peer;
+    if (!st || !st->open) return fail(ctx, SMELT_ERR_UNSUPPORTED, "smelt_tp_argmax: the peer exchange is not open (smelt_cuda_tp_exchange_open)");
+    if (batch <= 0 || batch > 8 || n <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "smelt_tp_argmax: batch 1..8");
+    if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
+    TpExchange ex = {};
+    for (int r = 0; r < ctx->tp_world; ++r) ex.ll[r] = (uint2*)st->mapped[r];
+    ex.seq = st->seq; ex.rank = ctx->tp_rank; ex.world = ctx->tp_world;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(256);
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(tp_argmax_kernel);
+    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, tp_argmax_kernel, ex, (uint2* const*)st->argmax_regions, (const uint64_t*)partials,
+                                              (int32_t*)out, n, offset, batch, ctx->err_dev, dev_dyn(l)), "tp argmax");
+}
+
 void tp_destroy(smelt_cuda_ctx* ctx) {
     if (TpPeerState* st = (TpPeerState*)ctx->tp_peer) {
+        cudaFree(st->argmax_regions);
         for (int r = 0; r < ctx->tp_world && r < kTpMaxWorld; ++r)
             if (st->mapped[r] && st->mapped[r] != st->local) cudaIpcCloseMemHandle(st->mapped[r]);
         cudaFree(st->local);
@@ -261,6 +319,12 @@ smelt_status smelt_cuda_tp_exchange_open(smelt_cuda_ctx* ctx, const uint8_t* han
         smelt_status s = check_cuda(ctx, cudaIpcOpenMemHandle(&st->mapped[r], h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
         if (s) return s;
     }
+    // the argmax words sit behind the reduction words of every rank's buffer
+    uint2* regions[kTpMaxWorld] = {};
+    for (int r = 0; r < ctx->tp_world; ++r) regions[r] = (uint2*)((char*)st->mapped[r] + tp_ll_bytes(ctx->tp_world));
+    if (!st->argmax_regions && cudaMalloc((void**)&st->argmax_regions, sizeof(regions)) != cudaSuccess) return fail(ctx, SMELT_ERR_ALLOC, "tp exchange: allocation failed");
+    smelt_status s2 = check_cuda(ctx, cudaMemcpy(st->argmax_regions, regions, sizeof(regions), cudaMemcpyHostToDevice), "tp exchange: upload");
+    if (s2) return s2;
     st->open = true;
     return SMELT_OK;
 }

@@ -119,11 +119,14 @@ def shard_cols(t, rank: int, world: int, group: int):
     return np.ascontiguousarray(packed[:, cs]), np.ascontiguousarray(scales[:, gs]), np.ascontiguousarray(biases[:, gs])
 
 
-def build_image(pkg: SyntheticPackage, tp_rank: int = 0, tp_world: int = 1, keep_for_oracle: bool = False):
+def build_image(pkg: SyntheticPackage, tp_rank: int = 0, tp_world: int = 1, keep_for_oracle: bool = False,
+                vocab_parallel: bool = False):
     """Lay the (optionally tensor-parallel-sharded) synthetic decoder out as a weights image.
 
     Returns (image bytes, DecoderDesc, LayerRef array).  Column-parallel: Q by query head,
     K/V by KV head, gate/up by rows; row-parallel: O and down by group-aligned column ranges.
+    vocab_parallel (tp_world > 1): the image holds only this rank's vocab / tp_world rows of the
+    LM head (pair it with bit 3 of the decoder's fuse flags).
     """
     c = pkg.cfg
     assert c.n_kv % tp_world == 0 and c.inter % (tp_world * c.group) == 0
@@ -146,6 +149,10 @@ def build_image(pkg: SyntheticPackage, tp_rank: int = 0, tp_world: int = 1, keep
     emb, head, fin = pkg.embedding(), pkg.lm_head(), pkg.norm_delta("final_norm")
     if keep is not None:
         keep["globals"] = (emb, head, fin)
+    if vocab_parallel and tp_world > 1:
+        assert c.vocab % tp_world == 0
+        rows = c.vocab // tp_world
+        head = np.ascontiguousarray(head[tp_rank * rows:(tp_rank + 1) * rows])
     desc = capi.DecoderDesc(layers=c.layers, hidden=c.hidden, inter=c.inter // tp_world, n_q=c.n_q // tp_world,
                             n_kv=c.n_kv // tp_world, head_dim=c.head_dim, vocab=c.vocab, group=c.group, eps=c.eps,
                             rope_theta=c.rope_theta, embedding=img.add(emb), lm_head=img.add(head),

@@ -119,6 +119,11 @@ def test_decoder_table_variants():
     table_pm, names_pm = _table(cfg, 1, tp=2, fuse=6)
     seq_pm = [names_pm[r.pipeline] for r in table_pm if r.op_kind == 0]
     assert seq_pm.count("smelt_tp_reduce_add") == 2 and "smelt_tp_all_reduce" not in seq_pm and "elementwise_add" not in seq_pm
+    table_vp, names_vp = _table(package.DecoderConfig(layers=1, hidden=2048, inter=6144, n_q=16, n_kv=4, head_dim=128, vocab=1000), 1, tp=2, fuse=14)
+    seq_vp = [names_vp[r.pipeline] for r in table_vp if r.op_kind == 0]
+    assert seq_vp[-3:] == ["fp16_matvec", "argmax_fp16_partials", "smelt_tp_argmax"]
+    head = next(r for r in table_vp if r.op_kind == 0 and names_vp[r.pipeline] == "fp16_matvec")
+    assert head.grid[0] == 500  # this rank's half of the vocabulary
     table_tp, names_tp = _table(cfg, 1, tp=2)
     seq = [names_tp[r.pipeline] for r in table_tp if r.op_kind == 0]
     assert seq.count("smelt_tp_all_reduce") == 2  # after O and after down

@@ -38,10 +38,10 @@ def main():
     pkg = package.SyntheticPackage(cfg, 7)
     prompt, n_dec = np.array([5, 17, 99, 4000], np.int32), 12
     results = {}
-    for fuse in (0, 2, 6):
+    for fuse in (0, 2, 6, 14):
         if fuse == 6:  # all-reduce + residual add over peer memory
             package.open_tp_exchange(ctx, dist, world)
-        image, desc, layers = package.build_image(pkg, rank, world)
+        image, desc, layers = package.build_image(pkg, rank, world, vocab_parallel=bool(fuse & 8))  # 14: + vocab-parallel LM head
         dec = package.Decoder(ctx, image, desc, layers, 64, 1, fuse_residual=fuse)
         eager = dec.generate(prompt, n_dec, use_graph=False)[:, 0]
         dec.reset_cache()
@@ -51,6 +51,7 @@ def main():
     assert np.array_equal(results[0], results[2])
     # two ranks: the sum of two fp16 partials rounded once is what the fp16 all-reduce returns too
     assert world != 2 or np.array_equal(results[6], results[2])
+    assert np.array_equal(results[14], results[6]), "the vocab-parallel argmax must pick the same ids"
     flags = C.c_uint32(0)
     ctx._check(ctx.lib.smelt_cuda_device_error(ctx.h, C.byref(flags)))
     assert flags.value == 0, "a bounded device wait gave up"
