@@ -188,6 +188,14 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
 #pragma unroll
     for (int i = 0; i < DEPTH - 1; ++i) fetch();
 
+    // The norm weights are weights too: requested before the wait, like the first stages.
+    uint4 nwv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (a.norm_w && kThreads == 256 && a.cols / 8 <= 2 * 256) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            if (tid + 256 * i < a.cols / 8) nwv[i] = *reinterpret_cast<const uint4*>(a.norm_w + (tid + 256 * i) * 8);
+    }
+
     sync();
     if (dyn_skip(a.dyn)) {
         cp_async_wait<0>();  // copies in flight must land before the CTA's shared memory retires
@@ -221,7 +229,7 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
                         if (tid + 256 * i < chunks) {
-                            const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + (tid + 256 * i) * 8);
+                            const uint4 wv = nwv[i];
                             xc[i].x = rms_norm_1pw_pair(xc[i].x, wv.x, rs); xc[i].y = rms_norm_1pw_pair(xc[i].y, wv.y, rs);
                             xc[i].z = rms_norm_1pw_pair(xc[i].z, wv.z, rs); xc[i].w = rms_norm_1pw_pair(xc[i].w, wv.w, rs);
                         }

@@ -55,6 +55,32 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
     const __half* Kb = a.k_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
     const __half* Vb = a.v_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
 
+    // One tile = 16 keys: K rows g and g + 8 (16-byte pieces that are A fragments as they come)
+    // and the four V rows this thread contracts over.
+    uint4 tka[KJ], tkb[KJ], vv[VC][4];
+    auto tile_loads = [&](uint32_t kt) {
+        const uint32_t last = k_end - 1;
+        const __half* ka_p = Kb + (size_t)min(kt + g, last) * D + 8 * t;
+        const __half* kb_p = Kb + (size_t)min(kt + g + 8, last) * D + 8 * t;
+#pragma unroll
+        for (int j = 0; j < KJ; ++j) {
+            tka[j] = *reinterpret_cast<const uint4*>(ka_p + 32 * j);
+            tkb[j] = *reinterpret_cast<const uint4*>(kb_p + 32 * j);
+        }
+        // V rows: k-slots 2t, 2t+1, 2t+8, 2t+9 of the tile
+        const uint32_t kv[4] = {min(kt + 2 * t, last), min(kt + 2 * t + 1, last), min(kt + 2 * t + 8, last), min(kt + 2 * t + 9, last)};
+#pragma unroll
+        for (int c = 0; c < VC; ++c)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                vv[c][kk] = *reinterpret_cast<const uint4*>(Vb + (size_t)kv[kk] * D + 64 * c + 8 * g);
+    };
+    // The first tile of every warp is requested before the RoPE prologue, whose own round trips
+    // it then overlaps, unless it holds the new token's row, which this CTA is about to write.
+    const uint32_t kt0 = k_begin + warp * 16;
+    const bool preloaded = D <= 128 && kt0 < k_end && (!a.k_new || kt0 + 16 <= seq_len - 1u);
+    if (preloaded) tile_loads(kt0);
+
     // ── folded RoPE / KV append (apply_rope, rope_kv_cache_update, kv_cache_update of
     // Resources/Shaders/attention.metal:48-209, full-head analytic mode): the new token is key
     // seq_len - 1.  cos / sin of the position once per CTA, the group's query heads rotated
@@ -138,30 +164,17 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
     }
 
     for (uint32_t kt = k_begin + warp * 16; kt < k_end; kt += kAttnWarps * 16) {
-        const uint32_t last = k_end - 1;
-        const uint32_t key_a = min(kt + g, last), key_b = min(kt + g + 8, last);
         const bool valid_a = kt + g < k_end, valid_b = kt + g + 8 < k_end;
-        // V rows this thread contracts over: k-slots 2t, 2t+1, 2t+8, 2t+9 of the tile
-        uint32_t kv[4] = {min(kt + 2 * t, last), min(kt + 2 * t + 1, last), min(kt + 2 * t + 8, last), min(kt + 2 * t + 9, last)};
-
         // every load of the tile is issued before any arithmetic: one memory round trip per tile
-        uint4 vv[VC][4];
-#pragma unroll
-        for (int c = 0; c < VC; ++c)
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-                vv[c][kk] = *reinterpret_cast<const uint4*>(Vb + (size_t)kv[kk] * D + 64 * c + 8 * g);
+        if (!(preloaded && kt == kt0)) tile_loads(kt);
 
         // ── S^T = K · Q^T ──
         float s[NH][4];
 #pragma unroll
         for (int nh = 0; nh < NH; ++nh) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
-        const __half* ka_p = Kb + (size_t)key_a * D + 8 * t;
-        const __half* kb_p = Kb + (size_t)key_b * D + 8 * t;
 #pragma unroll
         for (int j = 0; j < KJ; ++j) {
-            const uint4 ka = *reinterpret_cast<const uint4*>(ka_p + 32 * j);
-            const uint4 kb = *reinterpret_cast<const uint4*>(kb_p + 32 * j);
+            const uint4 ka = tka[j], kb = tkb[j];
 #pragma unroll
             for (int nh = 0; nh < NH; ++nh) {
                 mma16816(s[nh], ka.x, kb.x, ka.y, kb.y, qf[nh][4 * j + 0], qf[nh][4 * j + 1]);
