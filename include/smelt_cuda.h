@@ -268,6 +268,16 @@ SMELT_CUDA_API smelt_status smelt_cuda_tp_all_reduce_f16(smelt_cuda_ctx* ctx, vo
 #define SMELT_TP_HANDLE_BYTES 64
 SMELT_CUDA_API smelt_status smelt_cuda_tp_exchange_handle(smelt_cuda_ctx* ctx, uint8_t handle[SMELT_TP_HANDLE_BYTES]);
 SMELT_CUDA_API smelt_status smelt_cuda_tp_exchange_open(smelt_cuda_ctx* ctx, const uint8_t* handles_in_rank_order);
+/* Diagnostic: makes this context rank 0 of `world` ranks whose other exchange buffers are local
+ * allocations that nobody ever writes.  A smelt_tp_reduce_add or smelt_tp_argmax launched
+ * afterwards therefore runs into its bounded wait, sets bit 8 of the device error word and
+ * returns, leaving the context usable: the way to exercise the give-up path on one GPU without
+ * a peer that fails.  smelt_cuda_tp_reduce_add is the typed form of the record. */
+SMELT_CUDA_API smelt_status smelt_cuda_tp_exchange_open_loopback(smelt_cuda_ctx* ctx, int world);
+SMELT_CUDA_API smelt_status smelt_cuda_tp_reduce_add(smelt_cuda_ctx* ctx, const void* partial_dev, const void* residual_dev,
+                                                     void* out_dev, size_t count);
+/* Clears the device error word (after smelt_cuda_device_error has been read). */
+SMELT_CUDA_API smelt_status smelt_cuda_clear_device_error(smelt_cuda_ctx* ctx);
 
 /* ── typed launchers (asynchronous on the context's stream) ──────────────────
  * Packed-weight layouts are the package's: affine u4 = two nibbles per byte, low nibble =

@@ -148,6 +148,13 @@ smelt_status smelt_cuda_device_error(smelt_cuda_ctx* ctx, uint32_t* out_flags) {
     return SMELT_OK;
 }
 
+smelt_status smelt_cuda_clear_device_error(smelt_cuda_ctx* ctx) {
+    CTX_OR_FAIL();
+    smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    if (!s) s = check_cuda(ctx, cudaMemset(ctx->err_dev, 0, sizeof(uint32_t)), "clear error word");
+    return s;
+}
+
 smelt_status smelt_cuda_enable_phases(smelt_cuda_ctx* ctx, int on) {
     if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
     ctx->phases_on = on != 0;

@@ -181,6 +181,7 @@ struct TpPeerState {
     uint32_t* seq = nullptr;
     uint2** argmax_regions = nullptr;    // device array: every rank's argmax words, as mapped here
     bool open = false;
+    bool loopback = false;               // diagnostic set-up: every buffer is a local allocation
 };
 
 constexpr size_t kTpArgmaxBytes = (size_t)2 * kTpMaxWorld * 8 * 2 * sizeof(uint2);  // [buffer][source][sequence, 8][2 words]
@@ -242,7 +243,7 @@ void tp_destroy(smelt_cuda_ctx* ctx) {
     if (TpPeerState* st = (TpPeerState*)ctx->tp_peer) {
         cudaFree(st->argmax_regions);
         for (int r = 0; r < ctx->tp_world && r < kTpMaxWorld; ++r)
-            if (st->mapped[r] && st->mapped[r] != st->local) cudaIpcCloseMemHandle(st->mapped[r]);
+            if (st->mapped[r] && st->mapped[r] != st->local) { if (st->loopback) cudaFree(st->mapped[r]); else cudaIpcCloseMemHandle(st->mapped[r]); }
         cudaFree(st->local);
         cudaFree(st->seq);
         delete st;
@@ -327,6 +328,39 @@ smelt_status smelt_cuda_tp_exchange_open(smelt_cuda_ctx* ctx, const uint8_t* han
     if (s2) return s2;
     st->open = true;
     return SMELT_OK;
+}
+
+smelt_status smelt_cuda_tp_exchange_open_loopback(smelt_cuda_ctx* ctx, int world) {
+    if (!ctx || world < 2 || world > kTpMaxWorld) return SMELT_ERR_BAD_ARGUMENT;
+    if (ctx->tp_peer) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "tp exchange: already set up");
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    TpPeerState* st = new (std::nothrow) TpPeerState();
+    if (!st) return SMELT_ERR_ALLOC;
+    const size_t bytes = tp_exchange_bytes(world);
+    bool ok = cudaMalloc((void**)&st->seq, sizeof(uint32_t)) == cudaSuccess && cudaMemset(st->seq, 0, sizeof(uint32_t)) == cudaSuccess;
+    for (int r = 0; r < world && ok; ++r) ok = cudaMalloc(&st->mapped[r], bytes) == cudaSuccess && cudaMemset(st->mapped[r], 0, bytes) == cudaSuccess;
+    uint2* regions[kTpMaxWorld] = {};
+    for (int r = 0; r < world; ++r) regions[r] = (uint2*)((char*)st->mapped[r] + tp_ll_bytes(world));
+    ok = ok && cudaMalloc((void**)&st->argmax_regions, sizeof(regions)) == cudaSuccess &&
+         cudaMemcpy(st->argmax_regions, regions, sizeof(regions), cudaMemcpyHostToDevice) == cudaSuccess;
+    st->local = st->mapped[0];
+    st->loopback = true;
+    st->open = ok;
+    ctx->tp_peer = st;
+    ctx->tp_world = world;
+    ctx->tp_rank = 0;
+    return ok ? SMELT_OK : fail(ctx, SMELT_ERR_ALLOC, "tp exchange: allocation failed");
+}
+
+smelt_status smelt_cuda_tp_reduce_add(smelt_cuda_ctx* ctx, const void* partial, const void* residual, void* out, size_t count) {
+    if (!ctx || !partial || !residual || !out) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    Launch l;
+    l.stream = ctx->stream;
+    bool handled = false;
+    smelt_status s = tp_reduce_add(ctx, l, partial, residual, out, count, &handled);
+    if (!s && !handled) return fail(ctx, SMELT_ERR_UNSUPPORTED, "tp reduce add: the exchange is not open, or count is odd / too large");
+    return s;
 }
 
 smelt_status smelt_cuda_tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data_dev, size_t count) {

@@ -197,3 +197,26 @@ def test_multi_phase_kernel_keeps_every_bit(ctx, oracle):
         assert flags.value == 0
     finally:
         ctx.call("enable_phases", 0)
+
+
+def test_exchange_wait_gives_up_and_reports():
+    """A reduction whose peer never arrives runs into its bounded wait, raises bit 8 of the device
+    error word and returns; the context keeps working.  (The peer is a local buffer nobody writes.)"""
+    c = capi.Context(0)
+    try:
+        c.call("tp_exchange_open_loopback", 2)
+        n = 4096
+        part = c.to_device(synth.activations(12, "p", 1, n))
+        res = c.to_device(synth.activations(12, "r", 1, n))
+        out = c.alloc(n * 2)
+        c.call("tp_reduce_add", part, res, out, C.c_size_t(n))
+        c.synchronize()
+        assert c.device_error() & 0x100
+        c.call("clear_device_error")
+        assert c.device_error() == 0
+        y = c.alloc(n * 2)
+        c.call("elementwise_add", part, res, y, n)  # the context is still usable
+        want = (synth.activations(12, "p", 1, n).astype(np.float16) + synth.activations(12, "r", 1, n).astype(np.float16))
+        assert np.array_equal(y.download(np.float16, (1, n)), want)
+    finally:
+        c.close()
