@@ -211,9 +211,11 @@ def test_exchange_wait_gives_up_and_reports():
         out = c.alloc(n * 2)
         c.call("tp_reduce_add", part, res, out, C.c_size_t(n))
         c.synchronize()
-        assert c.device_error() & 0x100
-        c.call("clear_device_error")
+        with pytest.raises(capi.SmeltError) as caught:  # reading a non-zero error word reports DEVICE_TIMEOUT and clears it
+            c.device_error()
+        assert caught.value.status == capi.DEVICE_TIMEOUT and "256" in str(caught.value)
         assert c.device_error() == 0
+        c.call("clear_device_error")
         y = c.alloc(n * 2)
         c.call("elementwise_add", part, res, y, n)  # the context is still usable
         want = (synth.activations(12, "p", 1, n).astype(np.float16) + synth.activations(12, "r", 1, n).astype(np.float16))
