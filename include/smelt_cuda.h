@@ -310,8 +310,9 @@ SMELT_CUDA_API smelt_status smelt_cuda_affine_dual_matvec(smelt_cuda_ctx* ctx, c
  * rounding points).
  * affine_multi_matvec: rms_norm_1pw (norms.metal:9-67; skipped when norm_w_dev is NULL)
  * followed by up to three affine_matvec launches that share x (for example the Q, K and V
- * projections) in one kernel.  Needs group 64, cols a multiple of 1024, batch <= 8, every
- * tensor but the last with rows a multiple of 16. */
+ * projections) in one kernel.  Needs group 64, cols a multiple of 1024, every tensor but the
+ * last with rows a multiple of 16.  More than eight batch rows run as several passes over the
+ * weights. */
 typedef struct {
     const void* w_dev;
     const void* scales_dev;

@@ -474,6 +474,7 @@ cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int
             s.y = args.y + (size_t)b0 * args.rows;
             if (args.y2) s.y2 = args.y2 + (size_t)b0 * args.rows;
             if (args.residual) s.residual = args.residual + (size_t)b0 * args.rows;
+            for (int i = 0; i < args.nseg && i < 3; ++i) s.seg[i].y = args.seg[i].y + (size_t)b0 * args.seg[i].rows;
             cudaError_t e = launch_affine(l, mode, s, group);
             if (e != cudaSuccess) return e;
         }

@@ -1,4 +1,5 @@
-// Streaming (persistent, multistage) form of the group-64 affine u4 matvec for batch <= 8.
+// Streaming (persistent, multistage) form of the group-64 affine u4 matvec for batch <= 16
+// (eight batch rows per pass).
 //
 // Same arithmetic and the same reference kernels as affine_matvec.cu
 // (Resources/Shaders/lut_matvec.metal:1157-1287, :1718-1817, :2152-2233, :1824-1908); what
@@ -143,6 +144,10 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) fetch();
 
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L.zero + 64);  // past the 32 zero bytes the MMA reads
+    if (tid == 0) { mbar_init(xbar, 1); mbar_fence_init(); }
+    __syncthreads();
+
     pdl_trigger();
     pdl_wait();
     if (dyn_skip(a.dyn)) {
@@ -153,21 +158,35 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
     // ── activations: permuted copy into shared memory + per-group sums, once per CTA ──
     {
         const int chunks = a.cols / 8;
+        // Raw copy of every batch row first, everything in flight at once (one load latency for
+        // the whole block instead of one per row and pass); the permutation below stays inside a
+        // 16-byte chunk, so it is done in place.
+        // One bulk copy per row, tracked by an mbarrier of their own, so the wait does not also
+        // wait for the weight stages requested above.
+        if (tid == 0) {
+            mbar_arrive_expect_tx(xbar, (uint32_t)a.batch * (uint32_t)a.cols * 2u);
+            for (int b = 0; b < a.batch; ++b)
+                bulk_g2s(sx + (size_t)b * L.pitch_x, a.x + (size_t)b * a.cols, (uint32_t)a.cols * 2u, xbar);
+        }
+        if (!mbar_wait_bounded(xbar, 0)) {  // gave up: report, let the weight copies land, leave
+            if (tid == 0 && a.err) atomicOr(a.err, KERR_BARRIER_TIMEOUT);
+            cp_async_wait<0>();
+            return;
+        }
         for (int b = 0; b < a.batch; ++b) {
-            const __half* xr = a.x + (size_t)b * a.cols;
             uint8_t* xd = sx + (size_t)b * L.pitch_x;
             float rs = 0.f;
             if (a.norm_w) {
                 // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass
                 // sred is free here: no tile has been reduced yet
-                const float tot = cta256_sumsq_f16(xr, a.cols, sred);
+                const float tot = cta256_sumsq_f16(reinterpret_cast<const __half*>(xd), a.cols, sred);
                 rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
             }
             for (int base = 0; base < chunks; base += kThreads) {
                 const int c8 = base + tid;
                 float sum = 0.f;
                 if (c8 < chunks) {
-                    uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
+                    uint4 v = *reinterpret_cast<const uint4*>(xd + c8 * 16);
                     if (a.norm_w) {
                         const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
                         v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
@@ -191,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
         }
         for (int i = tid; i < groups_total * 8; i += kThreads)
             if ((i & 7) >= a.batch) sxsum[i] = 0.f;
-        if (tid < 16) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
+        if (tid < 2) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
     }
 
     // ── consumer side ──
@@ -334,35 +353,39 @@ cudaError_t launch_stream_t(const Launch& l, AffineArgs a, int ctas_per_sm) {
 template <int MODE>
 cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handled) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    // Ring depth: as deep as leaves room for two CTAs per SM (about 113 KB each).
+    // Ring depth: the preferred one if two CTAs per SM fit beside it (about 113 KB each), else a
+    // shallower one that lets them; when the activations leave room for one CTA only, the deepest
+    // ring that fits (the ring then is all that hides the HBM latency).
     static const int forced = env_int("SMELT_AFFINE_STAGES", 0);
     const uint32_t budget3 = 75u * 1024u, budget2 = 113u * 1024u, budget1 = 226u * 1024u;
     const int pref = forced ? forced : (NW == 2 ? 4 : 6);
-    const int order[3] = {pref, 4, 3};
-    for (int i = 0; i < 3; ++i) {
-        const int st = order[i];
-        if (st != 3 && st != 4 && st != 6) continue;
-        const uint32_t total = stream_layout(NW, st, a.cols, a.batch).total;
-        if (total > budget1) continue;
-        const int per_sm = (st == 3 && total <= budget3) ? 3 : (total <= budget2 ? 2 : 1);
-        *handled = true;
-        if (st == 6) return launch_stream_t<MODE, 6>(l, a, per_sm);
-        if (st == 4) return launch_stream_t<MODE, 4>(l, a, per_sm);
-        return launch_stream_t<MODE, 3>(l, a, per_sm);
-    }
+    const int order[2][3] = {{pref, 4, 3}, {forced ? forced : 6, 4, 3}};
+    for (int pass = 0; pass < 2; ++pass)
+        for (int i = 0; i < 3; ++i) {
+            const int st = order[pass][i];
+            if (st != 3 && st != 4 && st != 6) continue;
+            const uint32_t total = stream_layout(NW, st, a.cols, a.batch).total;
+            if (total > (pass == 0 ? budget2 : budget1)) continue;
+            const int per_sm = (st == 3 && total <= budget3) ? 3 : (total <= budget2 ? 2 : 1);
+            *handled = true;
+            if (st == 6) return launch_stream_t<MODE, 6>(l, a, per_sm);
+            if (st == 4) return launch_stream_t<MODE, 4>(l, a, per_sm);
+            return launch_stream_t<MODE, 3>(l, a, per_sm);
+        }
     *handled = false;
     return cudaSuccess;
 }
 
 }  // namespace
 
-// Launches the streaming kernel when the shape is eligible (group 64, batch <= 8, cols a
-// multiple of 512, 16-byte aligned operands, activations small enough to stay resident);
+// Launches the streaming kernel when the shape is eligible (group 64, batch <= 16, cols a
+// multiple of 1024, 16-byte aligned operands; up to eight batch rows per pass, fewer when the
+// activations would not stay resident);
 // *handled tells the caller whether it did.
 cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& a, int group, bool* handled) {
     *handled = false;
     static const int disabled = env_int("SMELT_AFFINE_NO_STREAM", 0);
-    if (disabled || group != kGroup || a.batch > 8 || a.cols % kStageCols != 0) return cudaSuccess;
+    if (disabled || group != kGroup || a.batch > 16 || a.cols % kStageCols != 0) return cudaSuccess;
     const int nw = (mode == kAffineGateUp || mode == kAffineDual) ? 2 : 1;
     if (a.nseg > 1) {
         if (nw != 1 || a.nseg > 3 || mode != kAffinePlain) return cudaErrorInvalidValue;
@@ -376,13 +399,36 @@ cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& a,
     }
     if (a.norm_w && (reinterpret_cast<uintptr_t>(a.norm_w) & 15u)) return cudaSuccess;
     if (reinterpret_cast<uintptr_t>(a.x) & 15u) return cudaSuccess;
-    switch (mode) {
-        case kAffinePlain: return launch_stream_mode<kAffinePlain>(l, a, handled);
-        case kAffineAdd: return launch_stream_mode<kAffineAdd>(l, a, handled);
-        case kAffineGateUp: return launch_stream_mode<kAffineGateUp>(l, a, handled);
-        case kAffineDual: return launch_stream_mode<kAffineDual>(l, a, handled);
-        default: return cudaErrorInvalidValue;
+    // Rows of the batch that fit in shared memory beside the shallowest ring go in one pass;
+    // a larger batch (or very wide activations) takes up to four passes over the same weights,
+    // which the later passes find in L2 for the matrices of a decoder layer.
+    int bmax = a.batch < 8 ? a.batch : 8;
+    while (bmax > 0 && stream_layout(nw, 3, a.cols, bmax).total > 226u * 1024u) --bmax;
+    if (bmax == 0) return cudaSuccess;
+    const int passes = (a.batch + bmax - 1) / bmax;
+    if (passes > 4) return cudaSuccess;
+    // Eight rows or fewer that need two passes: the general kernel's K split over a cluster is as fast.
+    if (passes > 1 && a.batch <= 8 && !a.norm_w && a.nseg <= 1) return cudaSuccess;
+    const int per_pass = (a.batch + passes - 1) / passes;
+    for (int b0 = 0; b0 < a.batch; b0 += per_pass) {
+        AffineArgs p = a;
+        p.batch = a.batch - b0 < per_pass ? a.batch - b0 : per_pass;
+        p.x = a.x + (size_t)b0 * a.cols;
+        if (a.y) p.y = a.y + (size_t)b0 * a.rows;
+        if (a.y2) p.y2 = a.y2 + (size_t)b0 * a.rows;
+        if (a.residual) p.residual = a.residual + (size_t)b0 * a.rows;
+        for (int i = 0; i < a.nseg && i < 3; ++i) p.seg[i].y = a.seg[i].y + (size_t)b0 * a.seg[i].rows;
+        cudaError_t e;
+        switch (mode) {
+            case kAffinePlain: e = launch_stream_mode<kAffinePlain>(l, p, handled); break;
+            case kAffineAdd: e = launch_stream_mode<kAffineAdd>(l, p, handled); break;
+            case kAffineGateUp: e = launch_stream_mode<kAffineGateUp>(l, p, handled); break;
+            case kAffineDual: e = launch_stream_mode<kAffineDual>(l, p, handled); break;
+            default: return cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess || !*handled) return e;
     }
+    return cudaSuccess;
 }
 
 }  // namespace smelt

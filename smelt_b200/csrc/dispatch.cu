@@ -580,7 +580,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             for (int i = 0; i <= 13; ++i)
                 if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": buffer binding missing");
             NEED_U32(14, rows_q); NEED_U32(15, rows_kv); NEED_U32(16, eps_bits); NEED_U32(17, nb);
-            if (rows_q == 0 || rows_kv == 0 || nb == 0 || nb > 8) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows / batch");
+            if (rows_q == 0 || rows_kv == 0 || nb == 0 || nb > 64) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows / batch");
             AffineArgs a = {};
             const uint32_t rows[3] = {rows_q, rows_kv, rows_kv};
             const int groups = p.cols / p.group;
@@ -607,7 +607,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             for (int i = 0; i <= 7; ++i)
                 if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": buffer binding missing");
             NEED_BUF(9); NEED_U32(8, rows); NEED_U32(10, eps_bits); NEED_U32(11, nb);
-            if (rows == 0 || nb == 0 || nb > 8) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows / batch");
+            if (rows == 0 || nb == 0 || nb > 64) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows / batch");
             const int groups = p.cols / p.group;
             AffineArgs a = {};
             for (int s2 = 0; s2 < 2; ++s2) {

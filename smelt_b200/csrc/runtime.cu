@@ -418,7 +418,7 @@ smelt_status smelt_cuda_affine_multi_matvec(smelt_cuda_ctx* ctx, const smelt_aff
     a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
     if (n_tensors == 1 && !norm_w) a.nseg = 0;
     cudaError_t e = launch_affine(typed_launch(ctx), kAffinePlain, a, group);
-    if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "affine multi matvec: needs group 64, cols % 1024 == 0, batch <= 8, 16-byte aligned operands, rows % 16 == 0 for all but the last tensor");
+    if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "affine multi matvec: needs group 64, cols % 1024 == 0, 16-byte aligned operands, rows % 16 == 0 for all but the last tensor");
     return check_cuda(ctx, e, "affine multi matvec launch");
 }
 
@@ -434,7 +434,7 @@ smelt_status smelt_cuda_rmsnorm_affine_gate_up_swiglu(smelt_cuda_ctx* ctx, const
     a.x = (const __half*)x; a.y = (__half*)y; a.norm_w = (const __half*)norm_w; a.norm_eps = eps;
     a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
     cudaError_t e = launch_affine(typed_launch(ctx), kAffineGateUp, a, group);
-    if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "rmsnorm gate/up: needs group 64, cols % 1024 == 0, batch <= 8, 16-byte aligned operands");
+    if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "rmsnorm gate/up: needs group 64, cols % 1024 == 0, 16-byte aligned operands");
     return check_cuda(ctx, e, "rmsnorm gate/up launch");
 }
 

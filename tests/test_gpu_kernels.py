@@ -67,6 +67,7 @@ AFFINE_SHAPES = [
     (2048, 2048, 64, 4), (512, 2048, 64, 8), (2048, 6144, 64, 16),  # config 1
     (1024, 4096, 64, 1), (512, 12288, 64, 1), (256, 12288, 64, 8),  # config 4 (K split over a cluster)
     (128, 1536, 128, 3), (96, 512, 32, 2), (64, 1024, 64, 20),
+    (4096, 512, 64, 1), (4096, 1536, 64, 1), (4096, 3072, 64, 2), (512, 4096, 64, 1),  # per-rank shards, 4 / 8 ranks
 ]
 
 
@@ -161,7 +162,8 @@ def test_affine_batched_equals_iterated_bitwise(ctx):
     assert np.array_equal(y.download(np.uint16, (batch, rows)), batched)  # run-to-run determinism
 
 
-@pytest.mark.parametrize("rows,cols,batch", [(2048, 6144, 1), (257, 512, 3), (512, 12288, 8)])
+@pytest.mark.parametrize("rows,cols,batch", [(2048, 6144, 1), (257, 512, 3), (512, 12288, 8), (330, 12288, 13), (2048, 6144, 16),
+                                             (4096, 1536, 1), (4096, 512, 1), (4096, 1536, 8)])
 def test_affine_matvec_add(ctx, oracle, rows, cols, batch):
     w, s, b = synth.affine_u4(1, "add", rows, cols, 64)
     x = synth.activations(1, "x", batch, cols)
@@ -224,7 +226,8 @@ def _multi(ctx, tensors, x, norm_w, eps, cols, batch):
 
 
 @pytest.mark.parametrize("rows,cols,batch,norm", [((4096, 1024, 1024), 4096, 1, True), ((256, 64, 72), 1024, 3, True),
-                                                  ((512, 128, 128), 2048, 8, False), ((48, 16, 5), 1024, 1, True)])
+                                                  ((512, 128, 128), 2048, 8, False), ((48, 16, 5), 1024, 1, True),
+                                                  ((256, 64, 40), 4096, 11, True), ((512, 128, 128), 4096, 1, True)])
 def test_affine_multi_matvec(ctx, oracle, rows, cols, batch, norm):
     eps = 1e-6
     tensors = [(*synth.affine_u4(21, f"t{i}", r, cols, 64), r) for i, r in enumerate(rows)]
@@ -251,7 +254,7 @@ def test_affine_multi_matvec_rejects_ineligible_shapes(ctx):
     assert st in (capi.BAD_ARGUMENT, capi.UNSUPPORTED)
 
 
-@pytest.mark.parametrize("rows,cols,batch", [(12288, 4096, 1), (200, 1024, 4), (1024, 2048, 8)])
+@pytest.mark.parametrize("rows,cols,batch", [(12288, 4096, 1), (200, 1024, 4), (1024, 2048, 8), (520, 4096, 16), (1536, 4096, 1)])
 def test_rmsnorm_affine_gate_up_swiglu(ctx, oracle, rows, cols, batch):
     eps = 1e-6
     gw, gs, gb = synth.affine_u4(23, "gate", rows, cols, 64)
@@ -307,7 +310,7 @@ def test_affine_rejects_bad_arguments(ctx):
 
 
 # ── dense fp16 matvec (LM head) ─────────────────────────────────────────────
-@pytest.mark.parametrize("rows,cols,batch", [(4099, 4096, 1), (1000, 2048, 8), (333, 1024, 11)])
+@pytest.mark.parametrize("rows,cols,batch", [(4099, 4096, 1), (1000, 2048, 8), (333, 1024, 11), (18992, 4096, 1)])
 def test_fp16_matvec(ctx, oracle, rows, cols, batch):
     w = synth.normal_f16(5, "head", (rows, cols), 0.02)
     x = synth.activations(5, "x", batch, cols)
@@ -443,7 +446,7 @@ def test_attention_reference_fixture(ctx, oracle, seq_len, window):
     assert np.max(np.abs(got.astype(np.float32))) > 1e-3
 
 
-@pytest.mark.parametrize("n_q,n_kv,d", [(16, 4, 128), (8, 2, 256), (32, 8, 128), (16, 1, 64)])
+@pytest.mark.parametrize("n_q,n_kv,d", [(16, 4, 128), (8, 2, 256), (32, 8, 128), (16, 1, 64), (4, 1, 128), (8, 2, 128)])
 @pytest.mark.parametrize("ctx_len,batch", [(1024, 1), (4096, 1), (1000, 8), (32768, 1)])
 def test_attention_config3(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
     if ctx_len == 32768 and (n_q, n_kv, d) not in [(16, 4, 128), (8, 2, 256)]:
@@ -462,7 +465,7 @@ def test_attention_config3(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,position,batch,layout", [(32, 8, 128, 0, 1, 1), (32, 8, 128, 530, 1, 1), (16, 4, 128, 4095, 2, 1),
-                                                              (8, 2, 256, 777, 1, 0), (16, 1, 64, 129, 3, 1)])
+                                                              (8, 2, 256, 777, 1, 0), (16, 1, 64, 129, 3, 1), (4, 1, 128, 600, 1, 1), (8, 2, 128, 5000, 1, 1)])
 def test_rope_attention_decode_is_the_four_kernels(ctx, oracle, n_q, n_kv, d, position, batch, layout):
     """RoPE on q, RoPE + append of K, append of V and attention in one launch: the bits of the
     four separate launches, with the new token as the last key."""

@@ -14,6 +14,7 @@ import torch.multiprocessing as mp
 from smelt_b200 import package, synth
 
 CFG = package.DecoderConfig(layers=2, hidden=256, inter=512, n_q=4, n_kv=2, head_dim=64, vocab=512)
+CFG4 = package.DecoderConfig(layers=2, hidden=256, inter=1024, n_q=8, n_kv=4, head_dim=64, vocab=512)  # one KV head per rank at 4 ranks
 SEED, CAP, STEPS = 21, 16, 5
 
 
@@ -31,8 +32,7 @@ def _all_reduce_f16(partial: np.ndarray) -> np.ndarray:
     return t.numpy().astype(np.float16)
 
 
-def _sharded_decode(oracle, rank: int, world: int):
-    c = CFG
+def _sharded_decode(oracle, c, rank: int, world: int):
     pkg = package.SyntheticPackage(c, SEED)
     nq, nkv, D, H, I, G = c.n_q // world, c.n_kv // world, c.head_dim, c.hidden, c.inter // world, c.group
     shard = {}
@@ -69,13 +69,13 @@ def _sharded_decode(oracle, rank: int, world: int):
     return tokens, np.stack(out)
 
 
-def _worker(rank: int, world: int, port: int, ret):
+def _worker(rank: int, world: int, port: int, ret, cfg):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         import oracle
 
-        tokens, logits = _sharded_decode(oracle, rank, world)
+        tokens, logits = _sharded_decode(oracle, cfg, rank, world)
         # every rank ends with the same (replicated) hidden state, hence the same logits
         t = torch.from_numpy(logits.astype(np.float32))
         lo, hi = t.clone(), t.clone()
@@ -83,7 +83,7 @@ def _worker(rank: int, world: int, port: int, ret):
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         assert torch.equal(lo, hi), "ranks disagree on the replicated logits"
         if rank == 0:
-            pkg = package.SyntheticPackage(CFG, SEED)
+            pkg = package.SyntheticPackage(cfg, SEED)
             ref = package.oracle_model(oracle, pkg, CAP)
             for pos, tok in enumerate(tokens):
                 ref_tok, ref_logits = ref.decode_step(int(tok), pos, want_logits=True)
@@ -95,12 +95,25 @@ def _worker(rank: int, world: int, port: int, ret):
         dist.destroy_process_group()
 
 
-def test_two_rank_sharded_decode_matches_the_full_model():
-    world = 2
+@pytest.mark.parametrize("world,cfg", [(2, CFG), (4, CFG4)])
+def test_sharded_decode_matches_the_full_model(world, cfg):
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), ret, cfg), nprocs=world, join=True)
         assert ret.get("ok")
+
+
+def test_shards_of_the_benchmark_model_at_4_and_8_ranks():
+    """Per-rank geometry of the 36-layer benchmark decoder: head counts, column shards on group
+    boundaries, LM-head row shards."""
+    cfg = package.DecoderConfig(layers=1, hidden=4096, inter=12288, n_q=32, n_kv=8, head_dim=128, vocab=1024)
+    pkg = package.SyntheticPackage(cfg, SEED)
+    for world in (4, 8):
+        for rank in (world - 1,):
+            _, desc, _ = package.build_image(pkg, rank, world)
+            assert (desc.n_q, desc.n_kv, desc.inter) == (32 // world, 8 // world, 12288 // world)
+            assert (desc.tp_world, desc.tp_rank) == (world, rank)
+            assert desc.inter % 128 == 0 and (desc.n_q * cfg.head_dim) % 128 == 0  # integer-MMA kernel eligibility
 
 
 def test_shards_tile_the_full_tensors():
