@@ -29,7 +29,6 @@ namespace {
 constexpr int kGroup = 64;
 constexpr int kTileRows = 16;
 constexpr int kStageCols = 1024;                      // 16 groups, two per warp
-constexpr int kThreads = 256;
 constexpr int kRowBytes = kStageCols / 2;             // 512 packed bytes per row per stage
 constexpr int kPitchW = kRowBytes + 32;               // ≡ 32 (mod 128): conflict-free LDS.64 across rows
 constexpr int kSetW = kTileRows * kPitchW;            // 8704
@@ -40,7 +39,7 @@ struct StreamLayout {
     uint32_t zero, ring, xs, xsum, red, total, pitch_x, stage_bytes;
 };
 
-__host__ __device__ inline StreamLayout stream_layout(int nw, int stages, int cols, int batch) {
+__host__ __device__ inline StreamLayout stream_layout(int nw, int stages, int cols, int batch, int warps = 8) {
     StreamLayout L;
     L.stage_bytes = (uint32_t)nw * kSetBytes;
     L.pitch_x = (uint32_t)cols * 2 + 16;              // ≡ 16 (mod 128)
@@ -50,7 +49,7 @@ __host__ __device__ inline StreamLayout stream_layout(int nw, int stages, int co
     L.xs = off; off += (uint32_t)batch * L.pitch_x;
     off = (off + 15u) & ~15u;
     L.xsum = off; off += (uint32_t)(cols / kGroup) * 8 * 4;
-    L.red = off; off += 8u * 32u * (uint32_t)(4 * nw) * 4u;
+    L.red = off; off += (uint32_t)warps * 32u * (uint32_t)(4 * nw) * 4u;
     L.total = off;
     return L;
 }
@@ -71,14 +70,18 @@ __device__ __forceinline__ void dequant8s(uint32_t w, uint32_t p[4]) {
     p[3] = h2_as_u32(__hfma2(u32_as_h2(hi2), k16th, km64));   // {n3, n7}
 }
 
-template <int MODE, int STAGES>
-__global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_kernel(const AffineArgs a) {
+// WARPS = 8: warp wk owns groups 2wk, 2wk+1 of every stage and up to three CTAs share an SM;
+// WARPS = 16: one group per warp, for launches whose activations leave room for one CTA only.
+template <int MODE, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 1 : (STAGES == 3 ? 3 : 2)) affine_stream_kernel(const AffineArgs a) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    constexpr int kThreads = WARPS * 32;
+    constexpr int GPW = 16 / WARPS;  // groups of a stage per warp (2 or 1)
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int wk = warp;  // this warp's share of every stage: groups 2wk, 2wk+1
-    const StreamLayout L = stream_layout(NW, STAGES, a.cols, a.batch);
+    const int wk = warp;  // this warp's share of every stage: groups GPW * wk ...
+    const StreamLayout L = stream_layout(NW, STAGES, a.cols, a.batch, WARPS);
     uint8_t* ring = smem + L.ring;
     uint8_t* sx = smem + L.xs;
     float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
@@ -100,7 +103,7 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
     };
 
     // ── producer side: every thread copies a fixed part of each stage ──
-    const int ld_chunk = tid & 31, ld_row = tid >> 5;  // rows ld_row and ld_row + 8, 16-byte chunk ld_chunk
+    const int ld_chunk = tid & 31, ld_row = tid >> 5;  // 16-byte chunk ld_chunk of row ld_row (and of row ld_row + 8 with eight warps)
     int f_tile = blockIdx.x, f_ks = 0, f_n = 0;        // next stage to request
     auto fetch = [&]() {
         if (f_n < total_stages) {
@@ -125,7 +128,7 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
             for (int s = 0; s < NW; ++s) {
                 uint8_t* dst = st + s * kSetBytes;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+                for (int h = 0; h < GPW; ++h) {
                     const int r = ld_row + 8 * h;
                     if (row0 + r < rows)
                         cp_async16(dst + r * kPitchW + ld_chunk * 16,
@@ -218,8 +221,8 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
     const uint8_t* px_base = g < a.batch ? sx + (size_t)g * L.pitch_x + t * 32 : smem + L.zero;
     const int px_stride = g < a.batch ? kGroup * 2 : 0;
     const float* pxs_base = sxsum + 2 * t;
-    const int w_off = g * kPitchW + wk * 64 + t * 8;  // this thread's first word in a set's W block
-    const int s_off = kSetW + g * 32 + wk * 4;         // its {scale g0, scale g1} word; biases kSetS later
+    const int w_off = g * kPitchW + wk * (GPW * 32) + t * 8;  // this thread's first word in a set's W block
+    const int s_off = kSetW + g * 32 + wk * (GPW * 2);  // its scale(s); biases kSetS later
 
     float acc[NW][4];
 #pragma unroll
@@ -231,18 +234,25 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
         __syncthreads();              // ... everyone's have, and everyone is done with stage n-1
         fetch();                      // refill the buffer stage n-1 used
         const uint8_t* st = ring + (size_t)(n % STAGES) * L.stage_bytes;
-        float2 sa[NW], ba[NW], sb[NW], bb[NW];  // {group 2wk, group 2wk+1}: scale / bias of row g (a) and row g+8 (b)
+        float2 sa[NW], ba[NW], sb[NW], bb[NW];  // {first, second group of this warp}: scale / bias of row g (a) and row g+8 (b)
 #pragma unroll
         for (int s = 0; s < NW; ++s) {
             const uint8_t* base = st + s * kSetBytes + s_off;
-            sa[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base)));
-            ba[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + kSetS)));
-            sb[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + 8 * 32)));
-            bb[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + kSetS + 8 * 32)));
+            if (GPW == 2) {
+                sa[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base)));
+                ba[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + kSetS)));
+                sb[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + 8 * 32)));
+                bb[s] = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(base + kSetS + 8 * 32)));
+            } else {
+                sa[s] = make_float2(__half2float(*reinterpret_cast<const __half*>(base)), 0.f);
+                ba[s] = make_float2(__half2float(*reinterpret_cast<const __half*>(base + kSetS)), 0.f);
+                sb[s] = make_float2(__half2float(*reinterpret_cast<const __half*>(base + 8 * 32)), 0.f);
+                bb[s] = make_float2(__half2float(*reinterpret_cast<const __half*>(base + kSetS + 8 * 32)), 0.f);
+            }
         }
 #pragma unroll
-        for (int gg = 0; gg < 2; ++gg) {
-            const int gi = c_ks * 16 + wk * 2 + gg;  // group index within the row
+        for (int gg = 0; gg < GPW; ++gg) {
+            const int gi = c_ks * 16 + wk * GPW + gg;  // group index within the row
             const uint8_t* px = px_base + gi * px_stride;
             const uint4 x0 = *reinterpret_cast<const uint4*>(px), x1 = *reinterpret_cast<const uint4*>(px + 16);
             const float2 xs = *reinterpret_cast<const float2*>(pxs_base + gi * 8);
@@ -267,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
             }
         }
         if (++c_ks == spt) {
-            // ── tile done: add the eight K-partials in a fixed order, write out ──
+            // ── tile done: add the warps' K-partials in a fixed order, write out ──
             float* dst = sred + (size_t)(wk * 32 + lane) * (4 * NW);
 #pragma unroll
             for (int s = 0; s < NW; ++s)
@@ -282,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, STAGES == 3 ? 3 : 2) affine_stream_k
                     for (int i = 0; i < 4; ++i) {
                         float v = 0.f;
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) v += sred[(size_t)(k * 32 + lane) * (4 * NW) + s * 4 + i];
+                        for (int k = 0; k < WARPS; ++k) v += sred[(size_t)(k * 32 + lane) * (4 * NW) + s * 4 + i];
                         tot[s][i] = v;
                     }
                 int first = 0, rows = a.rows;
@@ -317,12 +327,12 @@ int env_int(const char* name, int dflt) {
     return e ? atoi(e) : dflt;
 }
 
-template <int MODE, int STAGES>
+template <int MODE, int STAGES, int WARPS>
 cudaError_t launch_stream_t(const Launch& l, AffineArgs a, int ctas_per_sm) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    const StreamLayout L = stream_layout(NW, STAGES, a.cols, a.batch);
+    const StreamLayout L = stream_layout(NW, STAGES, a.cols, a.batch, WARPS);
     a.dyn = dev_dyn(l);
-    auto kern = affine_stream_kernel<MODE, STAGES>;
+    auto kern = affine_stream_kernel<MODE, STAGES, WARPS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
     if (e != cudaSuccess) return e;
     if (NW == 1 && a.nseg <= 1) {
@@ -338,7 +348,7 @@ cudaError_t launch_stream_t(const Launch& l, AffineArgs a, int ctas_per_sm) {
     if (grid > tiles) grid = tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(WARPS * 32, 1, 1);
     cfg.dynamicSmemBytes = L.total;
     cfg.stream = l.stream;
     cudaLaunchAttribute attr[1];
@@ -357,6 +367,7 @@ cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handl
     // shallower one that lets them; when the activations leave room for one CTA only, the deepest
     // ring that fits (the ring then is all that hides the HBM latency).
     static const int forced = env_int("SMELT_AFFINE_STAGES", 0);
+    static const bool narrow = env_int("SMELT_AFFINE_STREAM_WARPS", 8) != 16;  // 8: keep eight warps at one CTA per SM
     const uint32_t budget3 = 75u * 1024u, budget2 = 113u * 1024u, budget1 = 226u * 1024u;
     const int pref = forced ? forced : (NW == 2 ? 4 : 6);
     const int order[2][3] = {{pref, 4, 3}, {forced ? forced : 6, 4, 3}};
@@ -364,13 +375,18 @@ cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handl
         for (int i = 0; i < 3; ++i) {
             const int st = order[pass][i];
             if (st != 3 && st != 4 && st != 6) continue;
-            const uint32_t total = stream_layout(NW, st, a.cols, a.batch).total;
+            const uint32_t total = stream_layout(NW, st, a.cols, a.batch, pass == 0 ? 8 : 16).total;
             if (total > (pass == 0 ? budget2 : budget1)) continue;
-            const int per_sm = (st == 3 && total <= budget3) ? 3 : (total <= budget2 ? 2 : 1);
             *handled = true;
-            if (st == 6) return launch_stream_t<MODE, 6>(l, a, per_sm);
-            if (st == 4) return launch_stream_t<MODE, 4>(l, a, per_sm);
-            return launch_stream_t<MODE, 3>(l, a, per_sm);
+            if (pass == 1 && !narrow) {  // one CTA per SM: sixteen warps
+                if (st == 6) return launch_stream_t<MODE, 6, 16>(l, a, 1);
+                if (st == 4) return launch_stream_t<MODE, 4, 16>(l, a, 1);
+                return launch_stream_t<MODE, 3, 16>(l, a, 1);
+            }
+            const int per_sm = (st == 3 && total <= budget3) ? 3 : (total <= budget2 ? 2 : 1);
+            if (st == 6) return launch_stream_t<MODE, 6, 8>(l, a, per_sm);
+            if (st == 4) return launch_stream_t<MODE, 4, 8>(l, a, per_sm);
+            return launch_stream_t<MODE, 3, 8>(l, a, per_sm);
         }
     *handled = false;
     return cudaSuccess;
@@ -403,7 +419,7 @@ cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& a,
     // a larger batch (or very wide activations) takes up to four passes over the same weights,
     // which the later passes find in L2 for the matrices of a decoder layer.
     int bmax = a.batch < 8 ? a.batch : 8;
-    while (bmax > 0 && stream_layout(nw, 3, a.cols, bmax).total > 226u * 1024u) --bmax;
+    while (bmax > 0 && stream_layout(nw, 3, a.cols, bmax, 16).total > 226u * 1024u) --bmax;
     if (bmax == 0) return cudaSuccess;
     const int passes = (a.batch + bmax - 1) / bmax;
     if (passes > 4) return cudaSuccess;
