@@ -1,6 +1,6 @@
 """Per-kernel bandwidth of the decode kernels at the benchmark configurations.
 
-    python -m smelt_b200.kernel_bench [--configs 0,1,2,3,4] [--reps 20] [--markdown]
+    python -m smelt_b200.kernel_bench [--configs 0,1,2,3,4] [--reps 20] [--markdown] [--only CASE]
 
 Every case launches its kernel over enough distinct copies of its weights (or KV caches) to
 exceed the 126 MB L2, records one pass over all copies with smelt_cuda_capture_begin / _end
@@ -38,9 +38,10 @@ def copies_for(nbytes: float, cap: int = 128) -> int:
 
 
 class Bench:
-    def __init__(self, reps: int):
+    def __init__(self, reps: int, only: str = ""):
         self.ctx = capi.Context(0)
         self.reps = reps
+        self.only = only  # substring of "<mode> <rows>x<cols> b<batch>": run only the affine cases it matches
         self.peak, self.peak_kind = measured_peak()
         self.rows: list[dict] = []
 
@@ -69,6 +70,8 @@ class Bench:
     # ── affine u4 family ──
     def affine(self, config, rows, cols, batch, mode="matvec", copies=None):
         ctx, G = self.ctx, 64
+        if self.only and self.only not in f"{mode} {rows}x{cols} b{batch}":
+            return
         nmat = 2 if mode in ("gate_up", "dual") else 1
         alg = nmat * rows * cols * 0.5625 + batch * cols * 2 + batch * rows * 2 * (2 if mode == "dual" else 1) + (batch * rows * 2 if mode == "add" else 0)
         n = copies or copies_for(alg)
@@ -179,9 +182,10 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--markdown", action="store_true", help="print a markdown table after the JSON lines")
     ap.add_argument("--quick", action="store_true", help="fewer attention cases")
+    ap.add_argument("--only", default="", help='with --configs 4: only the affine cases whose "<mode> <rows>x<cols> b<batch>" contains this (small runs for profiler captures)')
     args = ap.parse_args()
     want = {c.strip() for c in args.configs.split(",")}
-    b = Bench(args.reps)
+    b = Bench(args.reps, args.only)
     if "0" in want:
         b.affine("config0", 4096, 1024, 1)
     if "1" in want:
@@ -204,7 +208,8 @@ def main():
         b.affine("config4", 1024, 4096, 1, "dual")
         b.affine("config4", 12288, 4096, 8, "gate_up")
         b.affine("config4", 4096, 12288, 8, "add")
-        b.lm_head("config4", 151936, 4096)
+        if not args.only:
+            b.lm_head("config4", 151936, 4096)
     if args.markdown:
         print("\n| config | kernel | shape | batch | MB / launch | us / launch | GB/s | of %s peak %.0f GB/s |" % (b.peak_kind, b.peak))
         print("|---|---|---|---|---|---|---|---|")
