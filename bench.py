@@ -306,7 +306,7 @@ def cpu_baseline(pkg, cfg, budget_s: float, threads: int | None = None):
     if threads:
         oracle.set_num_threads(threads)
     cores = oracle.num_threads()
-    m = package.oracle_model(oracle, pkg, 64)
+    m = oracle.model_from_package(pkg, 64)
     rng = np.random.Generator(np.random.Philox(key=[SEED, 1000]))
     prompt = rng.integers(0, cfg.vocab, size=4)
     t0 = time.perf_counter()

@@ -169,13 +169,17 @@ SMELT_CUDA_API smelt_status smelt_cuda_enqueue_decode(smelt_cuda_ctx* ctx, const
                                                       const int32_t* tokens, int32_t position);
 /* Capture the table once into a CUDA graph whose kernels read token and position from device
  * memory; each replay decodes one token and feeds the argmax result back as the next token
- * on the device, so a run of greedy steps needs no host round trip.  Rebuild after any slot
- * resize. */
+ * on the device, so a run of greedy steps needs no host round trip.  Allocating an existing
+ * slot again or resizing a slot drops every graph of the context (their kernels hold the old
+ * device pointers): graph_step / graph_decode / capture_replay then fail with
+ * SMELT_ERR_BAD_ARGUMENT until the graph is built again. */
 SMELT_CUDA_API smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records);
 /* Set the device-resident token(s) and position the next replay starts from. */
 SMELT_CUDA_API smelt_status smelt_cuda_graph_seed(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position);
 /* Replay n_steps tokens.  When out_tokens != NULL, waits and returns the n_steps * batch
- * generated ids (step-major). */
+ * generated ids (step-major).  Needs a graph_seed (or graph_step) first; a run that would pass
+ * min(context_limit, cache_seq_capacity) is refused with SMELT_ERR_OUT_OF_RANGE before any replay
+ * (positions are bounds-checked as in SmeltRuntime.swift:3176-3183). */
 SMELT_CUDA_API smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* out_tokens);
 /* One token through the captured graph with host buffers: tokens and position travel in,
  * the graph is replayed once, the argmax ids are read back and the call waits — the
@@ -196,11 +200,6 @@ SMELT_CUDA_API smelt_status smelt_cuda_timer_stop(smelt_cuda_ctx* ctx, float* ou
 SMELT_CUDA_API smelt_status smelt_cuda_capture_begin(smelt_cuda_ctx* ctx);
 SMELT_CUDA_API smelt_status smelt_cuda_capture_end(smelt_cuda_ctx* ctx);
 SMELT_CUDA_API smelt_status smelt_cuda_capture_replay(smelt_cuda_ctx* ctx, int warmup, int reps, float* out_ms_per_replay);
-/* Experimental, off by default (also SMELT_PHASES=1 in the environment): smelt_cuda_graph_build
- * turns every run of consecutive integer-MMA matvec and attention records into phases of one
- * persistent cooperative kernel separated by grid barriers (bounded waits; a barrier that gives
- * up sets bit 9 of the device error word).  Same device code per phase, same results bit for bit. */
-SMELT_CUDA_API smelt_status smelt_cuda_enable_phases(smelt_cuda_ctx* ctx, int on);
 /* Number of kernel launches one interpretation of the last built / enqueued table issues. */
 SMELT_CUDA_API int smelt_cuda_last_launch_count(const smelt_cuda_ctx* ctx);
 

@@ -321,3 +321,30 @@ class Model:
         margins = np.zeros(n_decode, np.float32)
         _check(lib().so_model_generate(self._m, _p(prompt), prompt.size, n_decode, _p(toks), _p(margins)), "model_generate")
         return toks, margins
+
+
+def model_from_package(pkg, capacity: int) -> Model:
+    """The decoder above over the tensors of a synthetic package (any object with ``cfg``,
+    ``tensors``, ``layer_tensor``, ``norm_delta``, ``embedding`` and ``lm_head``, such as
+    ``smelt_b200.package.SyntheticPackage``).  Lives here so that the product package holds no
+    oracle adapter."""
+    c = pkg.cfg
+    m = Model(c.as_dict(), capacity)
+    emb, head, fin = pkg.tensors.get("globals") or (pkg.embedding(), pkg.lm_head(), pkg.norm_delta("final_norm"))
+    m.set_globals(emb, head, fin)
+    for l in range(c.layers):
+        t = {name: pkg.tensors.get((l, name)) or pkg.layer_tensor(l, name) for name in Model.WHICH}
+        norms = pkg.tensors.get((l, "norms")) or (pkg.norm_delta(f"layer{l}.input_norm"), pkg.norm_delta(f"layer{l}.post_norm"))
+        m.set_layer(l, t, *norms)
+    return m
+
+
+def top2(logits) -> tuple[int, int, float]:
+    """(best id, runner-up id, margin) of fp16 logits under the argmax ordering: larger value
+    first, lower index on ties, -0 == +0."""
+    v = np.asarray(logits, np.float32)
+    best = int(np.argmax(v))
+    w = v.copy()
+    w[best] = -np.inf
+    second = int(np.argmax(w))
+    return best, second, float(v[best] - v[second])

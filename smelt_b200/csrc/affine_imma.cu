@@ -28,7 +28,6 @@
 #include <cstdlib>
 
 #include "affine_imma.cuh"
-#include "phases.h"
 
 namespace smelt {
 
@@ -40,11 +39,6 @@ template <int MODE, int DEPTH, int WARPS, int GPS, int TG>
 __global__ void __launch_bounds__(WARPS * 32, 1) affine_imma_kernel(const AffineArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     affine_imma_body<MODE, DEPTH, WARPS, GPS, TG>(a, smem, PdlSync());
-}
-
-int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return e ? atoi(e) : dflt;
 }
 
 template <int MODE, int DEPTH, int WARPS, int GPS, int TG>
@@ -65,12 +59,6 @@ cudaError_t launch_imma_t(const Launch& l, AffineArgs a) {
     if (NW == 1) for (int i = 0; i < a.nseg; ++i) tiles += (a.seg[i].rows + kTileRows - 1) / kTileRows;
     else tiles = (a.rows + kTileRows - 1) / kTileRows;
     a.ks = tiles;
-    if (l.phases) {
-        // the multi-phase kernel instantiates the default variant of each mode
-        const bool as_phase = WARPS == 8 && GPS == 4 && TG == 1 && (NW == 2 ? (MODE == kAffineGateUp && DEPTH == 3) : (MODE != kAffineDual && DEPTH == 4));
-        if (as_phase) return record_affine_phase(l, MODE, a, L.total);
-        if (cudaError_t fe = flush_phases(l)) return fe;
-    }
     const int sm = a.sm_count > 0 ? a.sm_count : 148;
     cudaLaunchConfig_t cfg = {};
     const int want = (tiles + TG - 1) / TG;
@@ -87,20 +75,14 @@ cudaError_t launch_imma_t(const Launch& l, AffineArgs a) {
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
-// Variant 0: 16 warps on one tile, two groups per stage; variant 1: 8 warps, four groups per
-// stage (needs cols % 256 == 0); variant 2: two teams of 8 warps, each on its own tile, two
-// groups per stage.  Ring depth: stages each warp keeps in flight + 1.
+// Eight warps on one tile, four groups (256 columns) per ring stage; when the columns are a
+// multiple of 128 only, sixteen warps with two groups per stage.  Ring depth = stages each warp
+// keeps in flight + 1: three for the two-matrix modes, four otherwise.
 template <int MODE>
 cudaError_t launch_imma_mode(const Launch& l, const AffineArgs& a, bool* handled) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    static const int variant_env = env_int("SMELT_IMMA_VARIANT", 1);
-    static const int depth_env = env_int("SMELT_IMMA_DEPTH", 0);
-    const int variant = (variant_env == 1 && a.cols % 256 != 0) ? 0 : variant_env;
-    const int depth = depth_env ? depth_env : (NW == 2 ? 3 : 4);
-    cudaError_t e;
-    if (variant == 0) e = depth == 3 ? launch_imma_t<MODE, 3, 16, 2, 1>(l, a) : launch_imma_t<MODE, 4, 16, 2, 1>(l, a);
-    else if (variant == 1) e = depth == 3 ? launch_imma_t<MODE, 3, 8, 4, 1>(l, a) : launch_imma_t<MODE, 4, 8, 4, 1>(l, a);
-    else e = depth == 3 ? launch_imma_t<MODE, 3, 16, 2, 2>(l, a) : launch_imma_t<MODE, 4, 16, 2, 2>(l, a);
+    constexpr int DEPTH = NW == 2 ? 3 : 4;
+    const cudaError_t e = a.cols % 256 != 0 ? launch_imma_t<MODE, DEPTH, 16, 2, 1>(l, a) : launch_imma_t<MODE, DEPTH, 8, 4, 1>(l, a);
     if (e == cudaErrorNotSupported) return cudaSuccess;  // not handled: the caller falls back
     *handled = true;
     return e;
@@ -113,8 +95,7 @@ cudaError_t launch_imma_mode(const Launch& l, const AffineArgs& a, bool* handled
 // rows, digit planes small enough to stay resident); *handled tells the caller whether it did.
 cudaError_t launch_affine_imma(const Launch& l, int mode, const AffineArgs& a, int group, bool* handled) {
     *handled = false;
-    static const int disabled = env_int("SMELT_AFFINE_NO_IMMA", 0);
-    if (disabled || group != kGroup || a.batch > 2 || a.cols % 128 != 0) return cudaSuccess;
+    if (group != kGroup || a.batch > 2 || a.cols % 128 != 0) return cudaSuccess;
     const int nw = (mode == kAffineGateUp || mode == kAffineDual) ? 2 : 1;
     if (a.nseg > 1) {
         if (nw != 1 || a.nseg > 3 || mode != kAffinePlain) return cudaErrorInvalidValue;

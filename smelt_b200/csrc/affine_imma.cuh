@@ -85,7 +85,7 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 // own tiles (splitting K among its warps) and only synchronises with itself.
 // Sync is called once, by every thread of every CTA, between the first weight requests and the
 // first read of the activations: the programmatic-dependent-launch wait of a stand-alone
-// launch, or the grid barrier that separates two phases of a multi-phase kernel.
+// launch.
 template <int MODE, int DEPTH, int WARPS, int GPS, int TG, class Sync>
 __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* smem, Sync sync) {
     using G = Geo<WARPS, GPS>;

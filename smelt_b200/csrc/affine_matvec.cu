@@ -376,15 +376,8 @@ __global__ void __launch_bounds__(kWarps * 32, kWarps == 16 ? 2 : 3) affine_mma_
 }
 
 // Largest K-slice a CTA stages (columns).  Smaller slices mean smaller tiles, more resident
-// CTAs per SM and more of them per matrix; SMELT_AFFINE_KS overrides the default for tuning.
-int max_slice_cols() {
-    static int v = [] {
-        const char* e = getenv("SMELT_AFFINE_KS");
-        int n = e ? atoi(e) : 0;
-        return (n >= 64 && n <= 8192) ? n : 4096;
-    }();
-    return v;
-}
+// CTAs per SM and more of them per matrix.
+constexpr int kMaxSliceCols = 4096;
 
 template <int MODE, int GROUP, int NBT, int WARPS>
 cudaError_t launch_t(const Launch& l, AffineArgs a) {
@@ -392,7 +385,7 @@ cudaError_t launch_t(const Launch& l, AffineArgs a) {
     // K-slice: an equal number of groups per slice, at most max_slice_cols() columns, shrunk
     // further until the tile fits in shared memory.
     const int groups = a.cols / GROUP;
-    int max_gs = max_slice_cols() / GROUP, nsplit = 1;
+    int max_gs = kMaxSliceCols / GROUP, nsplit = 1;
     if (max_gs < 1) max_gs = 1;
     SmemLayout L;
     for (;; max_gs /= 2) {
@@ -435,18 +428,9 @@ cudaError_t launch_t(const Launch& l, AffineArgs a) {
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
-// Warps per CTA: 16 by default; SMELT_AFFINE_WARPS=8 selects the 8-warp build for tuning.
-int warps_per_cta() {
-    static int v = [] {
-        const char* e = getenv("SMELT_AFFINE_WARPS");
-        return (e && atoi(e) == 8) ? 8 : 16;
-    }();
-    return v;
-}
-
 template <int MODE, int GROUP>
 cudaError_t launch_nb(const Launch& l, const AffineArgs& a) {
-    if (a.batch <= 8) return warps_per_cta() == 8 ? launch_t<MODE, GROUP, 1, 8>(l, a) : launch_t<MODE, GROUP, 1, 16>(l, a);
+    if (a.batch <= 8) return launch_t<MODE, GROUP, 1, 16>(l, a);
     if (a.batch <= 16) return launch_t<MODE, GROUP, 2, 8>(l, a);
     return cudaErrorInvalidValue;
 }
@@ -484,7 +468,6 @@ cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int
         bool handled = false;
         cudaError_t e = launch_affine_imma(l, mode, args, group, &handled);  // batch 1 and 2
         if (handled || e != cudaSuccess) return e;
-        if (cudaError_t fe = flush_phases(l)) return fe;  // every other affine path is a real launch
         e = launch_affine_stream(l, mode, args, group, &handled);
         if (handled || e != cudaSuccess) return e;
         if (args.norm_w || args.nseg > 1) return cudaErrorNotSupported;  // only the streaming kernel fuses these

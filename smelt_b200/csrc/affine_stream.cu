@@ -70,8 +70,7 @@ __device__ __forceinline__ void dequant8s(uint32_t w, uint32_t p[4]) {
     p[3] = h2_as_u32(__hfma2(u32_as_h2(hi2), k16th, km64));   // {n3, n7}
 }
 
-// WARPS = 8: warp wk owns groups 2wk, 2wk+1 of every stage and up to three CTAs share an SM;
-// WARPS = 16: one group per warp, for launches whose activations leave room for one CTA only.
+// Eight warps: warp wk owns groups 2wk, 2wk+1 of every stage and up to three CTAs share an SM.
 template <int MODE, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 1 : (STAGES == 3 ? 3 : 2)) affine_stream_kernel(const AffineArgs a) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
@@ -322,11 +321,6 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 1 : (STAGES == 3 ? 3
     cp_async_wait<0>();
 }
 
-int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return e ? atoi(e) : dflt;
-}
-
 template <int MODE, int STAGES, int WARPS>
 cudaError_t launch_stream_t(const Launch& l, AffineArgs a, int ctas_per_sm) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
@@ -366,23 +360,14 @@ cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handl
     // Ring depth: the preferred one if two CTAs per SM fit beside it (about 113 KB each), else a
     // shallower one that lets them; when the activations leave room for one CTA only, the deepest
     // ring that fits (the ring then is all that hides the HBM latency).
-    static const int forced = env_int("SMELT_AFFINE_STAGES", 0);
-    static const bool narrow = env_int("SMELT_AFFINE_STREAM_WARPS", 8) != 16;  // 8: keep eight warps at one CTA per SM
     const uint32_t budget3 = 75u * 1024u, budget2 = 113u * 1024u, budget1 = 226u * 1024u;
-    const int pref = forced ? forced : (NW == 2 ? 4 : 6);
-    const int order[2][3] = {{pref, 4, 3}, {forced ? forced : 6, 4, 3}};
+    const int order[2][3] = {{NW == 2 ? 4 : 6, 4, 3}, {6, 4, 3}};
     for (int pass = 0; pass < 2; ++pass)
         for (int i = 0; i < 3; ++i) {
             const int st = order[pass][i];
-            if (st != 3 && st != 4 && st != 6) continue;
-            const uint32_t total = stream_layout(NW, st, a.cols, a.batch, pass == 0 ? 8 : 16).total;
+            const uint32_t total = stream_layout(NW, st, a.cols, a.batch, 8).total;
             if (total > (pass == 0 ? budget2 : budget1)) continue;
             *handled = true;
-            if (pass == 1 && !narrow) {  // one CTA per SM: sixteen warps
-                if (st == 6) return launch_stream_t<MODE, 6, 16>(l, a, 1);
-                if (st == 4) return launch_stream_t<MODE, 4, 16>(l, a, 1);
-                return launch_stream_t<MODE, 3, 16>(l, a, 1);
-            }
             const int per_sm = (st == 3 && total <= budget3) ? 3 : (total <= budget2 ? 2 : 1);
             if (st == 6) return launch_stream_t<MODE, 6, 8>(l, a, per_sm);
             if (st == 4) return launch_stream_t<MODE, 4, 8>(l, a, per_sm);
@@ -400,8 +385,7 @@ cudaError_t launch_stream_mode(const Launch& l, const AffineArgs& a, bool* handl
 // *handled tells the caller whether it did.
 cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& a, int group, bool* handled) {
     *handled = false;
-    static const int disabled = env_int("SMELT_AFFINE_NO_STREAM", 0);
-    if (disabled || group != kGroup || a.batch > 16 || a.cols % kStageCols != 0) return cudaSuccess;
+    if (group != kGroup || a.batch > 16 || a.cols % kStageCols != 0) return cudaSuccess;
     const int nw = (mode == kAffineGateUp || mode == kAffineDual) ? 2 : 1;
     if (a.nseg > 1) {
         if (nw != 1 || a.nseg > 3 || mode != kAffinePlain) return cudaErrorInvalidValue;
@@ -419,7 +403,7 @@ cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& a,
     // a larger batch (or very wide activations) takes up to four passes over the same weights,
     // which the later passes find in L2 for the matrices of a decoder layer.
     int bmax = a.batch < 8 ? a.batch : 8;
-    while (bmax > 0 && stream_layout(nw, 3, a.cols, bmax, 16).total > 226u * 1024u) --bmax;
+    while (bmax > 0 && stream_layout(nw, 3, a.cols, bmax, 8).total > 226u * 1024u) --bmax;
     if (bmax == 0) return cudaSuccess;
     const int passes = (a.batch + bmax - 1) / bmax;
     if (passes > 4) return cudaSuccess;

@@ -22,7 +22,6 @@
 
 #include "affine_imma.cuh"
 #include "attention.cuh"
-#include "phases.h"
 
 namespace smelt {
 
@@ -111,7 +110,6 @@ size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits)
 
 cudaError_t launch_rope_table(const Launch& l, float* table, int half, float base_log2) {
     if (half <= 0 || half > 128) return cudaErrorInvalidValue;
-    if (cudaError_t fe = flush_phases(l)) return fe;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1);
     cfg.blockDim = dim3(128);
@@ -140,16 +138,8 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     while (nsplits > 1 && attention_scratch_bytes(a.n_q, a.head_dim, a.batch, nsplits) > a.scratch_bytes) --nsplits;
     // Short contexts are latency bound: up to eight splits of a KV head run as one thread-block
     // cluster and merge through distributed shared memory, with no partials in global memory.
-    static const char* no_cluster = getenv("SMELT_ATTN_NO_CLUSTER");
-    bool cluster = n_max <= 4096 && by_len >= 2 && !(no_cluster && atoi(no_cluster));
+    const bool cluster = n_max <= 4096 && by_len >= 2;
     if (cluster) nsplits = by_len < 8 ? by_len : 8;
-    // As a phase of the multi-phase kernel the same splits merge through the ticket path: same
-    // partition of the keys, same merge order, same bits.
-    static const char* phases_env = getenv("SMELT_PHASES");
-    const bool attn_phase_ok = !(phases_env && atoi(phases_env) == 2);  // 2: matvecs as phases, attention as its own launch
-    const bool as_phase = l.phases && attn_phase_ok && a.counters && a.head_dim == 128 && ratio <= 8 &&
-                          attention_scratch_bytes(a.n_q, a.head_dim, a.batch, nsplits) <= a.scratch_bytes;
-    if (as_phase) cluster = false;
     AttnDev p;
     p.a = a;
     p.nsplits = nsplits;
@@ -157,9 +147,7 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     p.part_o = reinterpret_cast<float*>(a.scratch);
     p.part_ml = p.part_o ? p.part_o + (size_t)a.batch * a.n_q * nsplits * a.head_dim : nullptr;
     p.dyn = dev_dyn(l);
-    if (as_phase) return record_attention_phase(l, p, attn_smem_bytes<128, 1>());
-    cudaError_t e = flush_phases(l);
-    if (e != cudaSuccess) return e;
+    cudaError_t e = cudaSuccess;
     const int nh = ratio > 8 ? 2 : 1;
 #define SMELT_ATTN_CASE(DD)                                                                 \
     case DD: e = nh == 1 ? launch_decode_t<DD, 1>(l, p) : launch_decode_t<DD, 2>(l, p); break;

@@ -28,7 +28,6 @@ struct Launch {
     uint32_t arg_pos = 0;           // literal position argument of the kernel, when arg_pos_valid
     uint32_t arg_pos_valid = 0;
     bool pdl = false;               // launch with programmatic stream serialization
-    struct PhaseRecorder* phases = nullptr;  // non-null: launches that can run as a phase of the multi-phase kernel are recorded there
 };
 
 struct DevDyn {
@@ -208,10 +207,6 @@ __device__ __forceinline__ void cp_async_wait() {
 // Error word shared by all kernels of a context: 0 = ok; kernels OR in a code when a bounded
 // wait gives up so the host can report it instead of hanging.
 enum : uint32_t { KERR_BARRIER_TIMEOUT = 1u, KERR_FLAG_TIMEOUT = 2u };
-
-// Launches the phases recorded for the multi-phase decode kernel, if any (decode_phases.cu).
-// Every real launch of a decode step calls it first, so stream order stays the record order.
-cudaError_t flush_phases(const Launch& l);
 
 // Every kernel of a decode step asks for the same shared-memory carve-out (the largest): an SM
 // drains before it changes its L1 / shared-memory split, so kernels that prefer different

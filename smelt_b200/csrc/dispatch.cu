@@ -13,7 +13,6 @@
 #include "affine_matvec.h"
 #include "glue.h"
 #include "runtime.h"
-#include "phases.h"
 
 using namespace smelt;
 
@@ -252,7 +251,6 @@ Launch make_launch(const Interp& in, const Resolved& r) {
     l.stream = in.ctx->stream;
     l.pdl = in.ctx->pdl;
     if (in.device_pos) {
-        if (in.ctx->phases_on) l.phases = &in.ctx->recorder;  // graph capture: eligible launches become phases
         l.dyn = in.ctx->dyn_dev;
         l.guard_lt = r.guard_lt;
         l.guard_ge = r.guard_ge;
@@ -643,7 +641,6 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             NEED_BYTES(0, (size_t)count * 2);
             if (ctx->tp_world <= 1) return SMELT_OK;
             in.launches += 1;
-            if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
             return tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
         }
         case PK_TP_ARGMAX: {
@@ -663,7 +660,6 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
                 bool handled = false;
                 smelt_status st = tp_reduce_add(ctx, l, r.buf[0].ptr, r.buf[1].ptr, r.buf[2].ptr, count, &handled);
                 if (st || handled) { in.launches += 1; return st; }
-                if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
                 st = tp_all_reduce_f16(ctx, r.buf[0].ptr, count, ctx->stream);
                 if (st) return st;
                 in.launches += 1;
@@ -686,15 +682,6 @@ smelt_status interpret(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, 
         if (rec.op_kind != SMELT_OP_DISPATCH) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record " + std::to_string(i) + ": unknown op kind");
         smelt_status s = run_record(in, rec);
         if (s) { ctx->err = "record " + std::to_string(i) + ": " + ctx->err; return s; }
-    }
-    if (device_pos && ctx->phases_on) {
-        Launch lf;
-        lf.stream = ctx->stream;
-        lf.phases = &ctx->recorder;
-        smelt_status s = check_cuda(ctx, flush_phases(lf), "multi-phase launch");
-        if (s) return s;
-        in.launches = in.launches - ctx->recorder.recorded + ctx->recorder.launches;  // recorded phases did not launch; the flushes did
-        ctx->recorder.recorded = ctx->recorder.launches = 0;
     }
     ctx->launch_count = in.launches;
     return SMELT_OK;
@@ -852,6 +839,7 @@ smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_re
     s = check_cuda(ctx, e, "cudaStreamEndCapture");
     if (s) return s;
     ctx->graph = g;
+    ctx->graph_pos_known = false;
     return check_cuda(ctx, cudaGraphInstantiate(&ctx->graph_exec, g, 0), "cudaGraphInstantiate");
 }
 
@@ -863,6 +851,8 @@ smelt_status smelt_cuda_graph_seed(smelt_cuda_ctx* ctx, const int32_t* tokens, i
     s = write_dynamic(ctx, tokens, position);
     if (s) return s;
     if (ctx->gen_count) cudaMemsetAsync(ctx->gen_count, 0, 4, ctx->stream);
+    ctx->graph_next_pos = (uint32_t)position;
+    ctx->graph_pos_known = true;
     return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph seed");
 }
 
@@ -871,6 +861,13 @@ smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* 
     if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
     if (!ctx->graph_exec) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "no graph has been built");
     const uint32_t B = ctx->cfg.batch;
+    // The position advances on the device; the host mirrors it so that a run past the context
+    // limit or the cache capacity is refused (SmeltRuntime.swift:3176-3183) instead of clamped.
+    if (!ctx->graph_pos_known) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "graph decode: seed the graph first (smelt_cuda_graph_seed)");
+    const uint32_t limit = ctx->cfg.context_limit < ctx->cfg.cache_seq_capacity ? ctx->cfg.context_limit : ctx->cfg.cache_seq_capacity;
+    if ((uint64_t)ctx->graph_next_pos + (uint64_t)n_steps > (uint64_t)limit)
+        return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "graph decode: " + std::to_string(n_steps) + " steps from position " + std::to_string(ctx->graph_next_pos) + " pass the limit of " + std::to_string(limit) + " positions");
+    ctx->graph_next_pos += (uint32_t)n_steps;
     if (out_tokens) cudaMemsetAsync(ctx->gen_count, 0, 4, ctx->stream);
     if (out_tokens && (uint32_t)n_steps > ctx->gen_capacity) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "graph decode: too many steps for one readback");
     for (int i = 0; i < n_steps; ++i) {
@@ -893,6 +890,8 @@ smelt_status smelt_cuda_graph_step(smelt_cuda_ctx* ctx, const int32_t* tokens, i
     if (s) return s;
     s = check_cuda(ctx, cudaGraphLaunch(ctx->graph_exec, ctx->stream), "cudaGraphLaunch");
     if (s) return s;
+    ctx->graph_next_pos = (uint32_t)position + 1u;
+    ctx->graph_pos_known = true;
     const uint32_t B = ctx->cfg.batch;
     Slot& as = ctx->slots[ctx->cfg.argmax_slot];
     cudaMemcpyAsync(ctx->h_pinned + 128, as.ptr, B * 4, cudaMemcpyDeviceToHost, ctx->stream);

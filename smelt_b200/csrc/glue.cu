@@ -397,8 +397,6 @@ __global__ void __launch_bounds__(256) fp16_matvec_kernel(const __half* __restri
 
 cudaError_t launch_cfg(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block,
                        size_t smem) {
-    cudaError_t fe = flush_phases(l);
-    if (fe != cudaSuccess) return fe;
     cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

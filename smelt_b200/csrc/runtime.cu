@@ -60,7 +60,6 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     if (!ctx) return SMELT_ERR_ALLOC;
     ctx->device = device_ordinal;
     ctx->sm_count = prop.multiProcessorCount;
-    if (const char* e = getenv("SMELT_NO_PDL")) ctx->pdl = atoi(e) == 0;  // diagnostic: launch without programmatic dependent launch
     ctx->slots.resize(256);
     bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->dyn_dev, sizeof(DynState)) == cudaSuccess;
@@ -74,11 +73,6 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     ctx->attn_scratch_bytes = attention_scratch_bytes(64, 256, 8, attention_max_splits());
     ok = ok && cudaMalloc(&ctx->attn_scratch, ctx->attn_scratch_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->rope_table, 256 * sizeof(float)) == cudaSuccess;
-    ok = ok && cudaMalloc((void**)&ctx->recorder.barrier, sizeof(uint32_t)) == cudaSuccess;
-    ctx->recorder.err = ctx->err_dev;
-    ctx->recorder.sm_count = ctx->sm_count;
-    ctx->recorder.prog.n = 0;
-    if (const char* e = getenv("SMELT_PHASES")) ctx->phases_on = atoi(e) != 0;
     ok = ok && cudaMalloc(&ctx->attn_counters, 4096 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(ctx->attn_counters, 0, 4096 * sizeof(int)) == cudaSuccess;
     ctx->argmax_scratch_bytes = 64 * 1024 * sizeof(uint64_t);
@@ -112,7 +106,6 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     cudaFree(ctx->attn_scratch);
     cudaFree(ctx->attn_counters);
     cudaFree(ctx->rope_table);
-    cudaFree(ctx->recorder.barrier);
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gen_ring);
     cudaFree(ctx->gen_count);
@@ -153,12 +146,6 @@ smelt_status smelt_cuda_clear_device_error(smelt_cuda_ctx* ctx) {
     smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
     if (!s) s = check_cuda(ctx, cudaMemset(ctx->err_dev, 0, sizeof(uint32_t)), "clear error word");
     return s;
-}
-
-smelt_status smelt_cuda_enable_phases(smelt_cuda_ctx* ctx, int on) {
-    if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
-    ctx->phases_on = on != 0;
-    return SMELT_OK;
 }
 
 smelt_status smelt_cuda_capture_begin(smelt_cuda_ctx* ctx) {
@@ -239,6 +226,21 @@ smelt_status smelt_cuda_memset(smelt_cuda_ctx* ctx, void* dst_dev, int value, si
 }
 
 // ── slots ───────────────────────────────────────────────────────────────────
+// A captured graph holds the device pointers of the slots as they were at capture.  When a
+// slot's allocation is about to be replaced or freed, every graph of the context is dropped, so
+// that a later replay reports "no graph has been built" instead of touching freed memory
+// (the reference's rule that a buffer handle cached across a grow is stale,
+// SmeltRuntime.swift:5101-5103).  Refused while a capture is open.
+static smelt_status drop_graphs_for_slot_change(smelt_cuda_ctx* ctx, const char* what) {
+    if (ctx->capturing) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, std::string(what) + ": a slot cannot change while a capture is open");
+    if (!ctx->graph_exec && !ctx->graph && !ctx->user_graph_exec) return SMELT_OK;
+    smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), what);
+    if (ctx->user_graph_exec) { cudaGraphExecDestroy(ctx->user_graph_exec); ctx->user_graph_exec = nullptr; }
+    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; }
+    if (ctx->graph) { cudaGraphDestroy(ctx->graph); ctx->graph = nullptr; }
+    return s;
+}
+
 static smelt_status slot_ok(smelt_cuda_ctx* ctx, int slot, bool must_exist) {
     if (slot < 0 || slot >= (int)ctx->slots.size()) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "slot index " + std::to_string(slot) + " out of range");
     if (must_exist && !ctx->slots[slot].ptr) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "slot " + std::to_string(slot) + " is not allocated");
@@ -251,6 +253,8 @@ smelt_status smelt_cuda_alloc_slot(smelt_cuda_ctx* ctx, int slot, size_t bytes) 
     if (s) return s;
     Slot& sl = ctx->slots[slot];
     if (sl.ptr) {
+        s = drop_graphs_for_slot_change(ctx, "alloc_slot");
+        if (s) return s;
         cudaStreamSynchronize(ctx->stream);
         cudaFree(sl.ptr);
         sl = Slot();
@@ -268,6 +272,8 @@ smelt_status smelt_cuda_resize_slot(smelt_cuda_ctx* ctx, int slot, size_t bytes,
     smelt_status s = slot_ok(ctx, slot, true);
     if (s) return s;
     Slot& sl = ctx->slots[slot];
+    s = drop_graphs_for_slot_change(ctx, "resize_slot");
+    if (s) return s;
     if (preserve_bytes > sl.bytes) preserve_bytes = sl.bytes;
     if (preserve_bytes > bytes) preserve_bytes = bytes;
     void* p = nullptr;
@@ -291,6 +297,8 @@ smelt_status smelt_cuda_resize_kv_slot(smelt_cuda_ctx* ctx, int slot, int heads,
     if (heads <= 0 || head_dim <= 0 || live_len > old_capacity || live_len > new_capacity ||
         (size_t)heads * old_capacity * head_dim * 2 > sl.bytes)
         return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "resize_kv_slot: geometry does not match the slot");
+    s = drop_graphs_for_slot_change(ctx, "resize_kv_slot");
+    if (s) return s;
     const size_t bytes = (size_t)heads * new_capacity * head_dim * 2;
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);

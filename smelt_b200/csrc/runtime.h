@@ -6,7 +6,6 @@
 
 #include "../../include/smelt_cuda.h"
 #include "common.cuh"
-#include "phases.h"
 
 namespace smelt {
 
@@ -95,14 +94,14 @@ struct smelt_cuda_ctx {
     uint32_t* gen_count = nullptr; // device: steps written
     uint32_t gen_capacity = 0;
     int launch_count = 0;
+    uint32_t graph_next_pos = 0;   // host mirror of the device position the next replay decodes at
+    bool graph_pos_known = false;  // set by graph_seed / graph_step
     bool capturing = false;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
 
     // tensor parallel
     void* nccl_comm = nullptr;
     void* tp_peer = nullptr;   // peer-memory exchange state (tp.cu)
-    bool phases_on = false;    // graph capture turns runs of eligible launches into one multi-phase kernel
-    smelt::PhaseRecorder recorder;
     int tp_rank = 0, tp_world = 1;
 };
 

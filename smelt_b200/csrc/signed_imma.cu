@@ -409,8 +409,7 @@ cudaError_t launch_signed_imma_bits(const Launch& l, int mode, const SignedArgs&
 // the caller whether it did.
 cudaError_t launch_signed_imma(const Launch& l, int mode, const SignedArgs& a, int sm_count, bool* handled) {
     *handled = false;
-    static const char* off = getenv("SMELT_SIGNED_NO_IMMA");
-    if ((off && atoi(off)) || a.batch > 2 || a.cols % (kGPS * kGroup) != 0 || (a.bits != 1 && a.bits != 2)) return cudaSuccess;
+    if (a.batch > 2 || a.cols % (kGPS * kGroup) != 0 || (a.bits != 1 && a.bits != 2)) return cudaSuccess;
     const int nw = mode == kSignedGateUp ? 2 : 1;
     for (int s = 0; s < nw; ++s)
         if ((reinterpret_cast<uintptr_t>(a.codes[s]) | reinterpret_cast<uintptr_t>(a.scales[s])) & 15u) return cudaSuccess;

@@ -141,7 +141,6 @@ cudaError_t launch_bits(const Launch& l, int mode, const SignedArgs& a) {
 
 cudaError_t launch_signed(const Launch& l, int mode, const SignedArgs& a) {
     if (a.rows <= 0 || a.cols <= 0 || a.batch <= 0 || a.cols % kGroup != 0) return cudaErrorInvalidValue;
-    if (cudaError_t fe = flush_phases(l)) return fe;
     {
         bool handled = false;
         cudaError_t e = launch_signed_imma(l, mode, a, 0, &handled);  // batch 1 and 2, cols % 512 == 0

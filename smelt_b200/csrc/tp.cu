@@ -197,7 +197,6 @@ smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* par
     TpPeerState* st = (TpPeerState*)ctx->tp_peer;
     if (!st || !st->open || count == 0 || count % 2 || count > (size_t)kTpMaxCount) return SMELT_OK;
     if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out)) & 3u) return SMELT_OK;
-    if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
     TpExchange ex = {};
     for (int r = 0; r < ctx->tp_world; ++r) ex.ll[r] = (uint2*)st->mapped[r];
     ex.seq = st->seq; ex.rank = ctx->tp_rank; ex.world = ctx->tp_world;
@@ -221,7 +220,6 @@ smelt_status tp_argmax(smelt_cuda_ctx* ctx, const Launch& l, const void* partial
     TpPeerState* st = (TpPeerState*)ctx->tp_peer;
     if (!st || !st->open) return fail(ctx, SMELT_ERR_UNSUPPORTED, "smelt_tp_argmax: the peer exchange is not open (smelt_cuda_tp_exchange_open)");
     if (batch <= 0 || batch > 8 || n <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "smelt_tp_argmax: batch 1..8");
-    if (cudaError_t fe = flush_phases(l)) return check_cuda(ctx, fe, "multi-phase launch");
     TpExchange ex = {};
     for (int r = 0; r < ctx->tp_world; ++r) ex.ll[r] = (uint2*)st->mapped[r];
     ex.seq = st->seq; ex.rank = ctx->tp_rank; ex.world = ctx->tp_world;

@@ -246,16 +246,3 @@ def open_tp_exchange(ctx: capi.Context, dist, world: int) -> None:
     ctx._check(ctx.lib.smelt_cuda_tp_exchange_open(ctx.h, allh.ctypes.data_as(C.c_void_p)))
     dist.barrier()
 
-
-def oracle_model(oracle, pkg: SyntheticPackage, capacity: int):
-    """The CPU oracle's decoder over the same synthetic tensors (test / baseline use only; the
-    oracle module is passed in so that this package never imports it)."""
-    c = pkg.cfg
-    m = oracle.Model(c.as_dict(), capacity)
-    emb, head, fin = pkg.tensors.get("globals") or (pkg.embedding(), pkg.lm_head(), pkg.norm_delta("final_norm"))
-    m.set_globals(emb, head, fin)
-    for l in range(c.layers):
-        t = {name: pkg.tensors.get((l, name)) or pkg.layer_tensor(l, name) for name in ("q", "k", "v", "o", "gate", "up", "down")}
-        norms = pkg.tensors.get((l, "norms")) or (pkg.norm_delta(f"layer{l}.input_norm"), pkg.norm_delta(f"layer{l}.post_norm"))
-        m.set_layer(l, t, *norms)
-    return m

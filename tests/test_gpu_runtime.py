@@ -30,7 +30,7 @@ def make(ctx, cfg, seed, capacity, batch=1, fuse=0):
 @pytest.mark.parametrize("cfg", [SMALL, MID])
 def test_decode_step_matches_oracle(ctx, oracle, cfg):
     pkg, dec = make(ctx, cfg, 11, 64)
-    ref = package.oracle_model(oracle, pkg, 64)
+    ref = oracle.model_from_package(pkg, 64)
     prompt = synth.rng_for(11, "prompt").integers(0, cfg.vocab, size=6)
     for pos, tok in enumerate(prompt):
         got_tok = dec.decode_step([tok], pos)[0]
@@ -50,7 +50,7 @@ def test_decode_step_matches_oracle(ctx, oracle, cfg):
 def test_greedy_tokens_match_oracle_eager_graph_and_fused(ctx, oracle):
     cfg, cap, n_dec = SMALL, 96, 48
     pkg, dec = make(ctx, cfg, 5, cap)
-    ref = package.oracle_model(oracle, pkg, cap)
+    ref = oracle.model_from_package(pkg, cap)
     prompt = synth.rng_for(5, "prompt").integers(0, cfg.vocab, size=12).astype(np.int32)
     want, margins = ref.generate(prompt, n_dec)
     eager = dec.generate(prompt, n_dec, use_graph=False)[:, 0]
@@ -87,7 +87,7 @@ def test_batch_of_independent_sequences(ctx, oracle):
     pkg, dec = make(ctx, cfg, 7, cap, batch=B)
     prompts = synth.rng_for(7, "prompts").integers(0, cfg.vocab, size=(B, 5)).astype(np.int32)
     got = dec.generate(prompts, 8, use_graph=True)
-    ref = package.oracle_model(oracle, pkg, cap)
+    ref = oracle.model_from_package(pkg, cap)
     for b in range(B):
         want, margins = ref.generate(prompts[b], 8)
         bad = next((i for i in range(8) if got[i, b] != want[i]), None)
@@ -176,27 +176,6 @@ def test_capture_replay_runs_the_recorded_launches(ctx, oracle):
     assert 0 < ms.value < 50
     assert rel_err(y.download(np.float16, (1, rows)), oracle.affine_matvec(w, s, b, x, rows, cols, 64)) < 2e-3
     assert ctx.call_status("capture_end") == capi.BAD_ARGUMENT  # nothing open
-
-
-def test_multi_phase_kernel_keeps_every_bit(ctx, oracle):
-    """The experimental multi-phase kernel runs the same device code per record: same tokens, same logits."""
-    cfg, cap, n_dec = MID, 64, 16
-    prompt = synth.rng_for(8, "prompt").integers(0, cfg.vocab, size=7).astype(np.int32)
-    _, plain = make(ctx, cfg, 8, cap, fuse=3)
-    want = plain.generate(prompt, n_dec, use_graph=True)[:, 0]
-    logits = plain.logits()[0].copy()
-    ctx.call("enable_phases", 1)
-    try:
-        _, phased = make(ctx, cfg, 8, cap, fuse=3)
-        got = phased.generate(prompt, n_dec, use_graph=True)[:, 0]
-        assert ctx.lib.smelt_cuda_last_launch_count(ctx.h) < 3 * cfg.layers + 12  # the layers' launches collapsed
-        assert np.array_equal(got, want)
-        assert np.array_equal(phased.logits()[0].view(np.uint16), logits.view(np.uint16))
-        flags = C.c_uint32(0)
-        ctx._check(ctx.lib.smelt_cuda_device_error(ctx.h, C.byref(flags)))
-        assert flags.value == 0
-    finally:
-        ctx.call("enable_phases", 0)
 
 
 def test_exchange_wait_gives_up_and_reports():

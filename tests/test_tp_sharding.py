@@ -84,7 +84,7 @@ def _worker(rank: int, world: int, port: int, ret, cfg):
         assert torch.equal(lo, hi), "ranks disagree on the replicated logits"
         if rank == 0:
             pkg = package.SyntheticPackage(cfg, SEED)
-            ref = package.oracle_model(oracle, pkg, CAP)
+            ref = oracle.model_from_package(pkg, CAP)
             for pos, tok in enumerate(tokens):
                 ref_tok, ref_logits = ref.decode_step(int(tok), pos, want_logits=True)
                 r32 = ref_logits.astype(np.float32)
