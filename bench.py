@@ -53,7 +53,11 @@ class ClockSampler:
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device_index: int):
-        self.rows, self.proc, self.device_index = [], None, device_index
+        self.rows, self.proc, self.device_index, self.marks = [], None, device_index, []
+
+    def mark(self):
+        """Brackets the timed region: called when it starts and when it ends."""
+        self.marks.append(time.time())
 
     def start(self):
         try:
@@ -66,7 +70,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([time.time()] + [c.strip() for c in line.split(",")])
 
     def stop(self) -> dict:
         if not self.proc:
@@ -76,25 +80,31 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        # Samples inside the timed region when it is long enough to hold some, else every sample
+        # since the warm-up began (the GPU is under the same load there).
+        lo, hi = (self.marks[0], self.marks[-1]) if len(self.marks) >= 2 else (0.0, float("inf"))
+        inside = [r for r in self.rows if lo <= r[0] <= hi + 0.1]
+        rows, window = (inside, "timed region") if len(inside) >= 2 else (self.rows, "warm-up + timed region")
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        for r in rows:
             try:
-                sm.append(float(r[1])); mx.append(float(r[2]))
+                sm.append(float(r[2])); mx.append(float(r[3]))
             except (ValueError, IndexError):
                 continue
-            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[5:9]):
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[6:10]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
-def token_bytes(cfg, ctx_len: int, batch: int, world: int) -> dict:
+def token_bytes(cfg, ctx_len: int, batch: int, world: int, vocab_parallel: bool) -> dict:
     """Algorithmic bytes one decoded token moves per GPU: packed weights + scales + biases of every
-    linear layer (0.5625 B/weight at group 64), the fp16 LM head, and the live KV prefix."""
+    linear layer (0.5625 B/weight at group 64), the fp16 LM head (this rank's vocab rows when the
+    head is vocab-parallel), and the live KV prefix."""
     per_layer = (cfg.n_q * cfg.head_dim * cfg.hidden * 2 + 2 * cfg.n_kv * cfg.head_dim * cfg.hidden + 3 * cfg.inter * cfg.hidden)
     linear = cfg.layers * per_layer * 0.5625 / world
-    head = cfg.vocab * cfg.hidden * 2
+    head = cfg.vocab * cfg.hidden * 2 / (world if vocab_parallel else 1)
     kv = cfg.layers * 2 * cfg.n_kv * cfg.head_dim * 2 * ctx_len * batch / world
     return {"linear": linear, "lm_head": head, "kv": kv, "total": linear + head + kv}
 
@@ -111,6 +121,57 @@ def setup_dist(n_gpus: int):
     return rank, world, dist
 
 
+GOLDEN = os.path.join(ROOT, "tests", "golden", "full_model_tokens.json")
+
+
+def parity_check(dec, prompts, args, capacity) -> dict:
+    """Teacher-forced replay of the committed known-good tokens (sequence 0; same model, seed and
+    prompt) right after the prompt: the fixture's token goes in at every step, the argmax of every
+    step is compared.  Runs on every rank, so at N > 1 each GPU's tokens are checked."""
+    from smelt_b200 import package
+
+    if not os.path.exists(GOLDEN):
+        return {"checked": 0, "note": "fixture missing"}
+    with open(GOLDEN) as f:
+        gold = json.load(f)
+    if gold["seed"] != SEED or gold["prompt_len"] != args.prompt_len or gold["config"] != package.FULL_MODEL.as_dict():
+        return {"checked": 0, "note": "no fixture for this prompt length"}
+    n = min(gold["n_decode"], capacity - args.prompt_len - 1)
+    tokens = np.array(gold["tokens"][:n], np.int32)
+    got = np.zeros(n, np.int32)
+    cur = dec.graph_decode(1, read=True)[0]  # the prompt's last token was seeded by the caller
+    for i in range(n):
+        got[i] = cur[0]
+        if i + 1 < n:
+            feed = np.array(cur, np.int32)
+            feed[0] = tokens[i]
+            dec.graph_seed(feed, args.prompt_len + i)
+            cur = dec.graph_decode(1, read=True)[0]
+    v = package.compare_greedy(got, tokens, np.array(gold["runner_up"][:n]), np.array(gold["top2_margin"][:n]))
+    v["fixture"] = "tests/golden/full_model_tokens.json"
+    return v
+
+
+def qmv_block(args) -> list:
+    """The metric's second half: achieved HBM GB/s of the quantised matvec kernels alone, one
+    line per shape: config 0 with its weights resident in L2 and rotating through more copies than
+    L2 holds, and the four matvec launches of a config-4 layer (rotating)."""
+    from smelt_b200 import kernel_bench
+
+    b = kernel_bench.Bench(reps=10, quiet=True)
+    try:
+        b.affine("config0 (L2-resident: one weight copy)", 4096, 1024, 1, copies=1)
+        b.affine("config0 (HBM: rotating copies > L2)", 4096, 1024, 1)
+        b.affine("config4 Q|K|V", 6144, 4096, 1, "matvec")
+        b.affine("config4 O + residual", 4096, 4096, 1, "add")
+        b.affine("config4 gate/up + SwiGLU", 12288, 4096, 1, "gate_up")
+        b.affine("config4 down + residual", 4096, 12288, 1, "add")
+    finally:
+        b.ctx.close()
+    keep = ("config", "kernel", "shape", "batch", "bytes_per_launch", "us_per_launch", "achieved_gbs", "frac_of_peak", "frac_of_8tbs", "distinct_operand_sets")
+    return [{k: r[k] for k in keep} for r in b.rows]
+
+
 def run_ours(args):
     from smelt_b200 import capi, package
 
@@ -118,7 +179,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", 0)) if world > 1 else 0
     cfg = package.FULL_MODEL
     B = args.batch
-    capacity = args.prompt_len + args.warmup + 2 * args.steps + 16
+    capacity = args.prompt_len + max(args.warmup + 2 * args.steps, 64) + 16  # room for the 64-step parity replay
     ctx = capi.Context(local)
 
     if world > 1:
@@ -158,19 +219,32 @@ def run_ours(args):
             dist.barrier()
             ctx.synchronize()
 
+    # ── parity, before anything is timed: the known-good greedy tokens of this model, seed and
+    # prompt (a committed fixture written by the CPU restatement of the reference's scalar path)
+    # are replayed teacher-forced on every rank and the argmax of every step is compared ──
+    parity = parity_check(dec, prompts, args, capacity)
+    dec.graph_seed(prompts[:, args.prompt_len - 1], args.prompt_len - 1)  # back to the end of the prompt
+    device_error = ctx.device_error_flags()
+
     ms = C.c_float(0)
-    dec.graph_decode(args.warmup, read=False)
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.start()  # before the warm-up, so that short timed regions still hold samples
+    dec.graph_decode(args.warmup, read=False)
+    barrier()
+    sampler.mark()
     # ── value: K graph replays, inputs resident, CUDA events on the launching stream ──
     ctx.call("timer_start")
     dec.graph_decode(args.steps, read=False)
     ctx._check(ctx.lib.smelt_cuda_timer_stop(ctx.h, C.byref(ms)))
     barrier()
+    sampler.mark()
     dev_ms = float(ms.value)
     launches = ctx.lib.smelt_cuda_last_launch_count(ctx.h) * args.steps
+    # the ids the timed steps generated (device ring): every rank must hold the same ones
+    timed_tokens = np.zeros((min(args.steps, 1024), B), np.int32)
+    ctx._check(ctx.lib.smelt_cuda_graph_generated(ctx.h, timed_tokens.shape[0], timed_tokens.ctypes.data_as(C.c_void_p)))
+    device_error |= ctx.device_error_flags()
 
     # ── e2e: K steps through the public graph_step call with host token buffers ──
     pos = args.prompt_len - 1 + args.warmup + args.steps
@@ -185,20 +259,29 @@ def run_ours(args):
     barrier()
     e2e_s = time.perf_counter() - t1
     clocks = sampler.stop() if rank == 0 else None
+    device_error |= ctx.device_error_flags()
 
+    tokens_match = True
     if dist is not None:
         import torch
 
-        tt = torch.tensor([dev_ms, e2e_s], device="cuda", dtype=torch.float64)
+        tt = torch.tensor([dev_ms, e2e_s, float(device_error != 0), float(bool(parity.get("wrong")))], device="cuda", dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         dev_ms, e2e_s = float(tt[0]), float(tt[1])
+        device_error = device_error or int(tt[2])
+        parity["all_ranks_ok"] = bool(tt[3] == 0)
+        tk = torch.from_numpy(timed_tokens.astype(np.int64)).cuda()
+        lo, hi = tk.clone(), tk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        tokens_match = bool(torch.equal(lo, hi))
 
     result = None
     if rank == 0:
         peak, peak_kind = measured_peaks()
         tok_s = args.steps * B / (dev_ms / 1e3)
         ctx_len = args.prompt_len + args.warmup + args.steps // 2
-        tb = token_bytes(cfg, ctx_len, B, world)
+        tb = token_bytes(cfg, ctx_len, B, world, peer)
         wptr = C.c_void_p()
         ctx._check(ctx.lib.smelt_cuda_slot_ptr(ctx.h, package.WEIGHTS_SLOT, C.byref(wptr), None))
         base = wptr.value
@@ -217,14 +300,21 @@ def run_ours(args):
             "e2e": {"value": args.steps * B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B + 4, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": launches,
             "clocks": clocks,
+            "parity": parity, "tokens_match_across_ranks": tokens_match, "device_error": device_error,
             "roofline": roof,
             "token_roofline": {"bytes_per_token_per_gpu": tb["total"], "achieved_gbs": tb["total"] / (dev_ms / args.steps / 1e3) / 1e9,
                                "peak_gbs": peak, "frac": tb["total"] / (dev_ms / args.steps / 1e3) / 1e9 / peak, "peak_kind": peak_kind,
                                "frac_of_8tbs": tb["total"] / (dev_ms / args.steps / 1e3) / 1e9 / 8000.0},
             "setup_s": gen_s,
         }
+        if world == 1 and not args.no_qmv:
+            result["qmv"] = qmv_block(args)
         if keep:
-            result["cpu_baseline"] = cpu_baseline(pkg, cfg, budget_s=25.0)
+            result["cpu_baseline"] = cpu_baseline(pkg, cfg, budget_s=25.0, prompt_len=args.prompt_len)
+    if device_error or not tokens_match or parity.get("wrong"):
+        # a run whose exchanges timed out, whose ranks disagree or whose tokens are wrong is not a measurement
+        if result is not None:
+            result["invalid"] = "device_error=%s tokens_match=%s parity_wrong=%s" % (device_error, tokens_match, parity.get("wrong"))
     if result is not None:
         print(json.dumps(result), flush=True)  # before any teardown, so that the line survives whatever follows
     ctx.synchronize()
@@ -297,29 +387,38 @@ def run_kernel_only(args):
             "gpu_launches": (args.steps + 3) * args.kernel_layers, "roofline": roof}
 
 
-def cpu_baseline(pkg, cfg, budget_s: float, threads: int | None = None):
+def cpu_baseline(pkg, cfg, budget_s: float, prompt_len: int, threads: int | None = None):
     """The oracle (a port of the reference's scalar CPU path) timed on the host's cores on a bounded
-    sample of the same workload: a short prompt, then a few decode steps."""
+    sample of the same workload: greedy decode steps at the GPU arm's context.  The prompt is not
+    decoded on the CPU (512 steps would take a quarter of an hour); its KV cache is filled with
+    seeded K and V rows of the benchmark's distribution (N(0,1)/sqrt(head_dim)) instead, so every
+    timed step streams the same weights and walks the same number of keys as the GPU arm's."""
     import oracle
-    from smelt_b200 import package
+    from smelt_b200 import synth
 
-    if threads:
-        oracle.set_num_threads(threads)
+    # all the host threads this process may use; a launcher's OMP_NUM_THREADS=1 does not apply
+    oracle.set_num_threads(threads or len(os.sched_getaffinity(0)))
     cores = oracle.num_threads()
-    m = oracle.model_from_package(pkg, 64)
+    max_steps = 24
+    m = oracle.model_from_package(pkg, prompt_len + max_steps + 8)
+    for l in range(cfg.layers):
+        k = synth.kv_cache(SEED, f"cpu_baseline.k{l}", 1, cfg.n_kv, prompt_len, cfg.head_dim)[0]
+        v = synth.kv_cache(SEED, f"cpu_baseline.v{l}", 1, cfg.n_kv, prompt_len, cfg.head_dim)[0]
+        m.fill_kv(l, k, v)
     rng = np.random.Generator(np.random.Philox(key=[SEED, 1000]))
-    prompt = rng.integers(0, cfg.vocab, size=4)
+    tok = int(rng.integers(0, cfg.vocab))
     t0 = time.perf_counter()
-    tok = m.decode_step(int(prompt[0]), 0)
+    tok = m.decode_step(tok, prompt_len)  # untimed in the result: pages the weights in, sizes the sample
     per = time.perf_counter() - t0
-    n = max(1, min(24, int(budget_s / max(per, 1e-3)) - 1))
+    n = max(1, min(max_steps - 1, int(budget_s / max(per, 1e-3)) - 1))
     t0 = time.perf_counter()
     for i in range(n):
-        tok = m.decode_step(int(tok), 1 + i)
+        tok = m.decode_step(int(tok), prompt_len + 1 + i)
     dt = time.perf_counter() - t0
     m.close()
-    return {"value": n / dt, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"{n} greedy decode steps of the full config-4 model at context 2..{n + 1} (no 512-token prompt), OpenMP over output rows"}
+    return {"value": n / dt, "unit": "tok/s", "cores": cores, "kind": "port", "same_config": True,
+            "sample": f"{n} greedy decode steps of the full config-4 model at context {prompt_len + 2}..{prompt_len + 1 + n} "
+                      f"(KV cache of the {prompt_len}-token prompt filled with seeded N(0,1)/sqrt(d) rows, not decoded), OpenMP over output rows on {cores} threads"}
 
 
 def run_reference(args):
@@ -333,14 +432,14 @@ def run_reference(args):
     cfg = package.FULL_MODEL
     pkg = package.SyntheticPackage(cfg, SEED)
     package.build_image(pkg, keep_for_oracle=True)
-    base = cpu_baseline(pkg, cfg, budget_s=150.0)
+    base = cpu_baseline(pkg, cfg, budget_s=min(150.0, 6.0 * max(args.steps, 1)), prompt_len=args.prompt_len)
     tok_s = base["value"]
     return {"impl": "reference", "metric": "decode tok/s at batch 1 (1/2/4/8 B200); qmv achieved HBM GB/s vs 8 TB/s",
             "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 / tok_s, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "config4: full 36-layer 4096/12288 decoder, affine u4 g64, greedy decode", "batch": 1,
-                       "parallelism": "cpu"},
+            "config": {"workload": "config4: full 36-layer 4096/12288 decoder, affine u4 g64, greedy decode after a %d-token prompt" % args.prompt_len,
+                       "batch": 1, "prompt_len": args.prompt_len, "parallelism": "cpu"},
             "cpu_baseline": base, "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
 
@@ -353,6 +452,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-qmv", action="store_true", help="skip the per-shape matvec bandwidth block (N = 1)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens decoded before the timed region (512 = the headline configuration; smaller for profiler captures)")
     ap.add_argument("--table", default="fused", choices=["fused", "reference"],
                     help="fused: the builder's fused record table; reference: the reference emitter's record sequence")

@@ -181,6 +181,11 @@ SMELT_CUDA_API smelt_status smelt_cuda_graph_seed(smelt_cuda_ctx* ctx, const int
  * min(context_limit, cache_seq_capacity) is refused with SMELT_ERR_OUT_OF_RANGE before any replay
  * (positions are bounds-checked as in SmeltRuntime.swift:3176-3183). */
 SMELT_CUDA_API smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* out_tokens);
+/* The ids of the last n_steps replays since the last graph_seed (step-major, n_steps * batch),
+ * read from the device ring without replaying anything: what a run of
+ * smelt_cuda_graph_decode(ctx, n, NULL) calls generated.  Waits for the stream.  (The reference
+ * reads each token back per step, SmeltRuntime.swift:1630-1641; this is the batched form.) */
+SMELT_CUDA_API smelt_status smelt_cuda_graph_generated(smelt_cuda_ctx* ctx, int n_steps, int32_t* out_tokens);
 /* One token through the captured graph with host buffers: tokens and position travel in,
  * the graph is replayed once, the argmax ids are read back and the call waits — the
  * graph-backed equivalent of smelt_cuda_decode_step. */

@@ -266,6 +266,17 @@ def attention_decode(q, k_cache, v_cache, n_q, n_kv, head_dim, capacity, seq_len
     return out
 
 
+def attention_decode_mlx_2pass(q, k_cache, v_cache, n_q, n_kv, capacity, seq_len) -> np.ndarray:
+    """The reference's D256 split-K record pair (interleaved key blocks, fp16 partials)."""
+    q, k_cache, v_cache = _h(q), _h(k_cache), _h(v_cache)
+    partials = np.zeros((n_q, 128, 256), np.float16)
+    stats = np.zeros((2, n_q, 128), np.float32)
+    out = np.zeros((n_q, 256), np.float16)
+    _check(lib().so_attention_decode_mlx_2pass(_p(q), _p(k_cache), _p(v_cache), n_q, n_kv, capacity, seq_len, _p(partials), _p(stats),
+                                               _p(out)), "attention_decode_mlx_2pass")
+    return out
+
+
 # ── whole decoder ────────────────────────────────────────────────────────────
 class Model:
     """Greedy decoder over packed weights held in numpy arrays (kept alive by this object)."""
@@ -308,12 +319,39 @@ class Model:
     def reset(self):
         lib().so_model_reset_cache(self._m)
 
+    def fill_kv(self, layer: int, k, v):
+        """Load positions [0, n) of one layer's caches from [n_kv, n, head_dim] fp16 arrays."""
+        k, v = _h(k), _h(v)
+        _check(lib().so_model_fill_kv(self._m, layer, _p(k), _p(v), k.shape[1]), "model_fill_kv")
+
     def decode_step(self, token: int, position: int, want_logits: bool = False):
         logits = np.zeros(self.cfg["vocab"], np.float16) if want_logits else None
         out = C.c_int32(-1)
         _check(lib().so_model_decode_step(self._m, C.c_int32(token), position, _p(logits) if want_logits else None,
                                           C.byref(out)), "model_decode_step")
         return (out.value, logits) if want_logits else out.value
+
+    def greedy_top2(self, prompt, n_decode: int):
+        """Greedy decode of one sequence from an empty cache; per step the token, the runner-up
+        and the logit margin between the two (lists of n_decode entries).  A teacher-forced replay
+        of these tokens can then tell a tie that any fp32 summation order may break from a
+        wrong token."""
+        self.reset()
+        logits = None
+        for i, t in enumerate(prompt):
+            last = i + 1 == len(prompt)
+            r = self.decode_step(int(t), i, want_logits=last)
+            if last:
+                logits = r[1]
+        toks, second, margin = [], [], []
+        pos = len(prompt)
+        for i in range(n_decode):
+            a, b, m = top2(logits)
+            toks.append(a); second.append(b); margin.append(m)
+            if i + 1 < n_decode:
+                _, logits = self.decode_step(a, pos, want_logits=True)
+                pos += 1
+        return toks, second, margin
 
     def generate(self, prompt, n_decode: int):
         prompt = np.ascontiguousarray(prompt, dtype=np.int32)

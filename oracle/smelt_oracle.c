@@ -671,6 +671,65 @@ SO_API int so_attention_decode(const uint16_t *q, const uint16_t *k_cache, const
     return fail ? SO_ERR_ALLOC : SO_OK;
 }
 
+/* The split-K pair a D256 package dispatches from 1,024 keys on
+ * (Resources/Shaders/attention.metal:1071-1141 first pass, :1146-1206 second pass; emitted by
+ * Sources/SmeltCompiler/AttentionPlugin.swift:865-918): head_dim 256, scale 1/16 folded into
+ * the query, 128 key blocks that interleave the keys (block b owns keys b, b+128, ...), an
+ * online softmax per block, partial outputs materialised as fp16 and (sum, max) kept in fp32;
+ * the second pass weights block b by exp(max_b - max), adds blocks in index order and divides
+ * by the weighted sum of the block sums.  partials [n_q,128,256] fp16 and stats [2][n_q][128]
+ * fp32 are scratch the caller provides (their contents are the reference's intermediate buffers). */
+SO_API int so_attention_decode_mlx_2pass(const uint16_t *q, const uint16_t *k_cache, const uint16_t *v_cache,
+                                         int n_q, int n_kv, int capacity, int seq_len,
+                                         uint16_t *partials, float *stats, uint16_t *out) {
+    enum { D = 256, BLOCKS = 128 };
+    if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || seq_len <= 0 || seq_len > capacity || !partials || !stats)
+        return SO_ERR_GEOMETRY;
+    const float scale = 0.0625f;
+    int gqa = n_q / n_kv;
+#pragma omp parallel for schedule(static)
+    for (int qh = 0; qh < n_q; ++qh) {
+        int kvh = qh / gqa;
+        float qv[D], ov[D];
+        for (int d = 0; d < D; ++d) qv[d] = scale * h2f(q[(size_t)qh * D + d]);
+        for (int block = 0; block < BLOCKS; ++block) {
+            for (int d = 0; d < D; ++d) ov[d] = 0.0f;
+            float mx = -3.402823466e+38f, sum = 0.0f;
+            for (int key = block; key < seq_len; key += BLOCKS) {
+                const uint16_t *kr = k_cache + ((size_t)kvh * capacity + key) * D;
+                const uint16_t *vr = v_cache + ((size_t)kvh * capacity + key) * D;
+                /* 32 lanes x 8 values, lane partials summed (simd_sum) */
+                float score = 0.0f;
+                for (int lane = 0; lane < 32; ++lane) {
+                    float part = 0.0f;
+                    for (int i = 0; i < 8; ++i) part += qv[lane * 8 + i] * h2f(kr[lane * 8 + i]);
+                    score += part;
+                }
+                float nm = score > mx ? score : mx;
+                float factor = expf(mx - nm), e = expf(score - nm);
+                mx = nm;
+                sum = sum * factor + e;
+                for (int d = 0; d < D; ++d) ov[d] = ov[d] * factor + e * h2f(vr[d]);
+            }
+            stats[(size_t)qh * BLOCKS + block] = sum;
+            stats[(size_t)n_q * BLOCKS + (size_t)qh * BLOCKS + block] = mx;
+            for (int d = 0; d < D; ++d) partials[((size_t)qh * BLOCKS + block) * D + d] = f2h(ov[d]);
+        }
+        const float *sums = stats + (size_t)qh * BLOCKS;
+        const float *maxs = stats + (size_t)n_q * BLOCKS + (size_t)qh * BLOCKS;
+        float M = -3.402823466e+38f;
+        for (int b = 0; b < BLOCKS; ++b) if (maxs[b] > M) M = maxs[b];
+        float total = 0.0f;
+        for (int b = 0; b < BLOCKS; ++b) total += expf(maxs[b] - M) * sums[b];
+        for (int d = 0; d < D; ++d) {
+            float acc = 0.0f;
+            for (int b = 0; b < BLOCKS; ++b) acc += expf(maxs[b] - M) * h2f(partials[((size_t)qh * BLOCKS + b) * D + d]);
+            out[(size_t)qh * D + d] = f2h(total == 0.0f ? acc : acc / total);
+        }
+    }
+    return SO_OK;
+}
+
 /* ───────────────────────── whole decoder ─────────────────────────
  * Structure: Sources/SmeltRuntime/Qwen3TTSTalker.swift:229-292 (forwardStep: norm → q/k/v →
  * RoPE → cache append → GQA attention → o → residual → norm → gate/up SwiGLU → down →
@@ -747,6 +806,19 @@ SO_API int so_model_set_norms(so_model_t *m, int layer, const uint16_t *input_no
 SO_API void so_model_reset_cache(so_model_t *m) {
     size_t kv = (size_t)m->n_kv * m->capacity * m->head_dim;
     for (int l = 0; l < m->layers; ++l) { memset(m->k_cache[l], 0, kv * 2); memset(m->v_cache[l], 0, kv * 2); }
+}
+
+/* Benchmark support: loads rows [0, n_positions) of one layer's K and V caches from
+ * [n_kv, n_positions, head_dim] fp16 arrays, so that a timed decode step can start at a long
+ * context without decoding the prompt first (attention then walks n_positions + 1 keys as it
+ * would after a real prompt of that length). */
+SO_API int so_model_fill_kv(so_model_t *m, int layer, const uint16_t *k, const uint16_t *v, int n_positions) {
+    if (layer < 0 || layer >= m->layers || n_positions < 0 || n_positions > m->capacity) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < m->n_kv; ++h) {
+        memcpy(m->k_cache[layer] + (size_t)h * m->capacity * m->head_dim, k + (size_t)h * n_positions * m->head_dim, (size_t)n_positions * m->head_dim * 2);
+        memcpy(m->v_cache[layer] + (size_t)h * m->capacity * m->head_dim, v + (size_t)h * n_positions * m->head_dim, (size_t)n_positions * m->head_dim * 2);
+    }
+    return SO_OK;
 }
 
 /* One decode step for one sequence.  Writes fp16 logits [vocab] when logits != NULL and

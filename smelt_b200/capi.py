@@ -224,6 +224,14 @@ class Context:
         self._check(self.lib.smelt_cuda_device_error(self.h, C.byref(flags)))
         return flags.value
 
+    def device_error_flags(self) -> int:
+        """The device error word, read and cleared, without raising when it is non-zero."""
+        flags = C.c_uint32(0)
+        st = self.lib.smelt_cuda_device_error(self.h, C.byref(flags))
+        if st not in (OK, DEVICE_TIMEOUT):
+            self._check(st)
+        return flags.value
+
     @property
     def stream(self) -> int:
         return self.lib.smelt_cuda_stream(self.h)

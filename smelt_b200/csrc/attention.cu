@@ -69,6 +69,30 @@ __global__ void attn_merge_kernel(const AttnDev p) {
     }
 }
 
+// attention_decode_mlx_vector_2pass_2_d256_b128 (Resources/Shaders/attention.metal:1146-1206):
+// out = sum_b exp(max_b - M) partial_b / sum_b exp(max_b - M) sum_b over the 128 key blocks of
+// one query head, M the largest block maximum; blocks in index order; a head whose total is
+// zero keeps the unnormalised sum, as the reference does.
+__global__ void attn_mlx_reduce_kernel(const __half* partials, const float* stats, __half* out, int n_q, int D, DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const int qh = blockIdx.x;
+    const float* sums = stats + (size_t)qh * kMlxBlocks;
+    const float* maxs = stats + (size_t)n_q * kMlxBlocks + (size_t)qh * kMlxBlocks;
+    float M = -3.402823466e+38f;
+    for (int b = 0; b < kMlxBlocks; ++b) M = fmaxf(M, maxs[b]);
+    float total = 0.f;
+    for (int b = 0; b < kMlxBlocks; ++b)
+        if (sums[b] != 0.f) total += expf(maxs[b] - M) * sums[b];
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        for (int b = 0; b < kMlxBlocks; ++b)
+            if (sums[b] != 0.f) acc += expf(maxs[b] - M) * __half2float(partials[((size_t)qh * kMlxBlocks + b) * D + d]);
+        out[(size_t)qh * D + d] = __float2half_rn(total == 0.f ? acc : acc / total);
+    }
+}
+
 template <int D, int NH>
 cudaError_t launch_decode_t(const Launch& l, const AttnDev& p) {
     const size_t smem = attn_smem_bytes<D, NH>();
@@ -138,7 +162,15 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     while (nsplits > 1 && attention_scratch_bytes(a.n_q, a.head_dim, a.batch, nsplits) > a.scratch_bytes) --nsplits;
     // Short contexts are latency bound: up to eight splits of a KV head run as one thread-block
     // cluster and merge through distributed shared memory, with no partials in global memory.
-    const bool cluster = n_max <= 4096 && by_len >= 2;
+    bool cluster = n_max <= 4096 && by_len >= 2;
+    if (a.mlx_partials) {
+        // two-pass pair: the partials go to the record's own buffers, the second record merges
+        if (a.batch != 1 || !a.mlx_stats) return cudaErrorInvalidValue;
+        cluster = false;
+        nsplits = want < by_len ? want : by_len;
+        if (nsplits < 1) nsplits = 1;
+        if (nsplits > kMaxSplits) nsplits = kMaxSplits;
+    }
     if (cluster) nsplits = by_len < 8 ? by_len : 8;
     AttnDev p;
     p.a = a;
@@ -158,7 +190,7 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
         default: return cudaErrorInvalidValue;
     }
 #undef SMELT_ATTN_CASE
-    if (e != cudaSuccess || nsplits == 1 || a.counters || cluster) return e;
+    if (e != cudaSuccess || nsplits == 1 || a.counters || cluster || a.mlx_partials) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.batch * a.n_q);
     cfg.blockDim = dim3(a.head_dim < 128 ? 64 : 128);
@@ -170,6 +202,21 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     cfg.numAttrs = l.pdl ? 1 : 0;
     prefer_max_shared(attn_merge_kernel);
     return cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+}
+
+cudaError_t launch_attention_mlx_reduce(const Launch& l, const __half* partials, const float* stats, __half* out, int n_q, int head_dim) {
+    if (n_q <= 0 || head_dim <= 0) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_q);
+    cfg.blockDim = dim3(head_dim < 256 ? 128 : 256);
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = l.pdl ? 1 : 0;
+    prefer_max_shared(attn_mlx_reduce_kernel);
+    return cudaLaunchKernelEx(&cfg, attn_mlx_reduce_kernel, partials, stats, out, n_q, head_dim, dev_dyn(l));
 }
 
 }  // namespace smelt

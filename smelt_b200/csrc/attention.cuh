@@ -1,5 +1,4 @@
-// Device side of the flash-decode attention kernel (see attention.cu for the description):
-// shared by the stand-alone kernel and the multi-phase decode kernel.
+// Device side of the flash-decode attention kernel (see attention.cu for the description).
 #pragma once
 #include <cooperative_groups.h>
 
@@ -15,6 +14,7 @@ namespace cg = cooperative_groups;
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = 8;
 constexpr int kMaxSplits = 64;
+constexpr int kMlxBlocks = 128;  // key blocks of the reference's two-pass pair (attention_decode_mlx_vector_2pass_*_d256_b128)
 constexpr float kNegBig = -1.0e30f;
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
@@ -282,7 +282,16 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
             lsum += s_ml[(w * HN + h) * 2 + 1] * f;
         }
         const size_t qh = (size_t)b * a.n_q + (size_t)kvh * ratio + h;
-        if (p.nsplits == 1) {
+        if (a.mlx_partials) {
+            // First half of the reference's two-pass pair (Resources/Shaders/attention.metal:1071-1141):
+            // block `split` of this head in the reference's buffers: fp16 partial [n_q, 128, D],
+            // fp32 stats [2][n_q][128] = sum of exp(score - max), then max, in natural-log units.
+            a.mlx_partials[(qh * kMlxBlocks + split) * D + d] = __float2half_rn(acc);
+            if (d == 0) {
+                a.mlx_stats[qh * kMlxBlocks + split] = lsum;
+                a.mlx_stats[(size_t)a.n_q * kMlxBlocks + qh * kMlxBlocks + split] = lsum > 0.f ? mstar * 0.6931471805599453f : -3.402823466e+38f;
+            }
+        } else if (p.nsplits == 1) {
             a.out[qh * D + d] = __float2half_rn(acc / lsum);
         } else if (p.cluster) {
             float* c_o = smem_f + kAttnWarps * HN * (D + 2);  // [16][D] then [16][2]
@@ -295,6 +304,18 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
                 p.part_ml[(qh * p.nsplits + split) * 2 + 1] = lsum;
             }
         }
+    }
+    if (a.mlx_partials) {
+        // blocks no split owns are empty: sum 0, max -FLT_MAX, as a block without keys leaves them
+        for (int idx = tid; idx < ratio * kMlxBlocks; idx += kAttnThreads) {
+            const int h = idx / kMlxBlocks, j = idx % kMlxBlocks;
+            if (j >= p.nsplits && j % p.nsplits == split) {
+                const size_t qh = (size_t)b * a.n_q + (size_t)kvh * ratio + h;
+                a.mlx_stats[qh * kMlxBlocks + j] = 0.f;
+                a.mlx_stats[(size_t)a.n_q * kMlxBlocks + qh * kMlxBlocks + j] = -3.402823466e+38f;
+            }
+        }
+        return;
     }
     if (p.nsplits > 1 && p.cluster) {
         // ── merge across the cluster: rank r finishes a slice of the (head, dim) outputs from

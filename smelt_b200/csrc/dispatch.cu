@@ -140,6 +140,13 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             }
             return false;
         }
+        // The split-K record pair a D256 package emits from 1,024 keys on
+        // (Resources/Shaders/attention.metal:1071-1206; Sources/SmeltCompiler/AttentionPlugin.swift:865-918).
+        if (name == "attention_decode_mlx_vector_2pass_1_d256_b128" || name == "attention_decode_mlx_vector_2pass_2_d256_b128") {
+            p.kind = name.find("2pass_1") != std::string::npos ? PK_ATTN_MLX_2PASS_1 : PK_ATTN_MLX_2PASS_2; p.head_dim = 256;
+            *out = p;
+            return true;
+        }
         if (name == "attention_decode_mlx_vector_d256") {
             p.kind = PK_ATTN_INPLACE; p.head_dim = 256;
             *out = p;
@@ -388,6 +395,17 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
             }
             NEED_BYTES(11, (size_t)a.batch * nkv * d * 2); NEED_BYTES(12, (size_t)a.batch * nkv * d * 2);
         }
+    } else if (p.kind == PK_ATTN_MLX_2PASS_1) {
+        // attention.metal:1071-1083: 0 q, 1 K, 2 V, 3 partials (fp16 [qHeads, 128, 256]), 4 stats
+        // (fp32 [2][qHeads][128]), 5 seqLen, 6 capacity, 7 qHeads, 8 kvHeads; scale 1/16 is fixed.
+        NEED_BUF(3); NEED_BUF(4);
+        NEED_U32(6, cap); NEED_U32(7, nq); NEED_U32(8, nkv);
+        if (a.batch != 1) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": one sequence per record");
+        a.head_dim = 256; a.capacity = cap; a.n_q = (int)nq; a.n_kv = (int)nkv; a.scale = 0.0625f;
+        NEED_BYTES(3, (size_t)nq * 128 * 256 * 2); NEED_BYTES(4, (size_t)2 * nq * 128 * 4);
+        a.mlx_partials = (__half*)r.buf[3].ptr; a.mlx_stats = (float*)r.buf[4].ptr;
+        a.out = nullptr;
+        iseq = 5;
     } else {
         // in place: 0 q/out, 1 K, 2 V, 3 seqLen, 4 capacity (attention.metal:422-431, :1211-1218);
         // the mlx_vector form adds 5 qHeads, 6 kvHeads (:981-989).
@@ -411,7 +429,7 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
     NEED_BYTES(1, a.seq_stride * 2 * a.batch); NEED_BYTES(2, a.seq_stride * 2 * a.batch);
     NEED_BYTES(0, (size_t)a.batch * a.n_q * a.head_dim * 2);
     a.scratch = ctx->attn_scratch; a.scratch_bytes = ctx->attn_scratch_bytes; a.sm_count = ctx->sm_count;
-    if ((size_t)a.batch * a.n_kv <= 4096) a.counters = ctx->attn_counters;
+    if ((size_t)a.batch * a.n_kv <= 4096 && !a.mlx_partials) a.counters = ctx->attn_counters;
     if (p.kind == PK_ATTN_ROPE && !a.counters) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": too many (sequence, KV head) pairs");
     in.launches += 1;
     return check_cuda(ctx, launch_attention_decode(make_launch(in, r), a), p.name.c_str());
@@ -432,8 +450,16 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             return run_affine(in, p, rec, r);
         case PK_SIGNED_MATVEC: case PK_SIGNED_ADD: case PK_SIGNED_GATEUP: case PK_SIGNED_TERNARY_AFFINE:
             return run_signed(in, p, rec, r);
-        case PK_ATTN_GENERIC: case PK_ATTN_INPLACE: case PK_ATTN_ROPE:
+        case PK_ATTN_GENERIC: case PK_ATTN_INPLACE: case PK_ATTN_ROPE: case PK_ATTN_MLX_2PASS_1:
             return run_attention(in, p, rec, r);
+        case PK_ATTN_MLX_2PASS_2: {
+            // attention.metal:1146-1153: 0 partials, 1 stats, 2 out, 3 qHeads.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, nq);
+            if (nq == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": qHeads must be positive");
+            NEED_BYTES(0, (size_t)nq * 128 * 256 * 2); NEED_BYTES(1, (size_t)2 * nq * 128 * 4); NEED_BYTES(2, (size_t)nq * 256 * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_attention_mlx_reduce(l, (const __half*)r.buf[0].ptr, (const float*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)nq, 256), p.name.c_str());
+        }
         case PK_FP16_MATVEC: {
             // lut_matvec.metal:799-803: 0 W, 1 x, 2 y, 3 cols; one threadgroup per row.
             NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, cols);
@@ -878,6 +904,21 @@ smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* 
     smelt_status s = check_cuda(ctx, cudaMemcpyAsync(out_tokens, ctx->gen_ring, (size_t)n_steps * B * 4, cudaMemcpyDeviceToHost, ctx->stream), "graph readback");
     if (s) return s;
     return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph decode");
+}
+
+smelt_status smelt_cuda_graph_generated(smelt_cuda_ctx* ctx, int n_steps, int32_t* out_tokens) {
+    if (!ctx || n_steps <= 0 || !out_tokens) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!ctx->gen_ring) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "no graph has been built");
+    uint32_t count = 0;
+    smelt_status s = check_cuda(ctx, cudaMemcpyAsync(&count, ctx->gen_count, 4, cudaMemcpyDeviceToHost, ctx->stream), "graph generated: count");
+    if (!s) s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph generated: sync");
+    if (s) return s;
+    if (count > ctx->gen_capacity) count = ctx->gen_capacity;
+    if ((uint32_t)n_steps > count) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "graph generated: only " + std::to_string(count) + " steps were replayed since the last seed");
+    const uint32_t B = ctx->cfg.batch;
+    s = check_cuda(ctx, cudaMemcpyAsync(out_tokens, ctx->gen_ring + (size_t)(count - (uint32_t)n_steps) * B, (size_t)n_steps * B * 4, cudaMemcpyDeviceToHost, ctx->stream), "graph generated: readback");
+    return s ? s : check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph generated: sync");
 }
 
 smelt_status smelt_cuda_graph_step(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position, int32_t* out_tokens) {

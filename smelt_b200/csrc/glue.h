@@ -46,8 +46,13 @@ struct AttnArgs {
     int rope_layout;        // 0 adjacent pairs, 1 split-half
     float rope_base_log2;
     const float* rope_table;  // optional: cos[half] | sin[half] of the position (launch_rope_table)
+    // mlx_partials != null (batch 1): the launch is the first half of the reference's two-pass
+    // pair; every split writes its state as one of the 128 key blocks of the reference's
+    // buffers (fp16 partials [n_q, 128, head_dim], fp32 stats [2][n_q][128]) and nothing merges.
+    __half* mlx_partials;
+    float* mlx_stats;
 };
-// What one attention launch (or one attention phase of the multi-phase kernel) works from.
+// What one attention launch works from.
 struct AttnDev {
     AttnArgs a;
     int nsplits;
@@ -60,6 +65,8 @@ size_t attention_scratch_bytes(int n_q, int head_dim, int batch, int max_splits)
 int attention_max_splits();
 cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a);
 cudaError_t launch_rope_table(const Launch& l, float* table, int half, float base_log2);
+// Second half of the two-pass pair: out[n_q, head_dim] from the 128 blocks of partials / stats.
+cudaError_t launch_attention_mlx_reduce(const Launch& l, const __half* partials, const float* stats, __half* out, int n_q, int head_dim);
 
 // signed_matvec.cu — binary1 / ternary2, group 128.
 enum SignedMode : int { kSignedPlain = 0, kSignedAdd = 1, kSignedGateUp = 2 };

@@ -35,6 +35,8 @@ enum PipeKind : int {
     PK_ROPE_KV_UPDATE,
     PK_ATTN_GENERIC,
     PK_ATTN_INPLACE,
+    PK_ATTN_MLX_2PASS_1,
+    PK_ATTN_MLX_2PASS_2,
     PK_RMS_NORM,
     PK_PER_HEAD_NORM,
     PK_ADD,

@@ -38,9 +38,10 @@ def copies_for(nbytes: float, cap: int = 128) -> int:
 
 
 class Bench:
-    def __init__(self, reps: int, only: str = ""):
+    def __init__(self, reps: int, only: str = "", quiet: bool = False):
         self.ctx = capi.Context(0)
         self.reps = reps
+        self.quiet = quiet  # collect rows without printing them
         self.only = only  # substring of "<mode> <rows>x<cols> b<batch>": run only the affine cases it matches
         self.peak, self.peak_kind = measured_peak()
         self.rows: list[dict] = []
@@ -65,7 +66,8 @@ class Bench:
                "peak_gbs": self.peak, "peak_kind": self.peak_kind, "frac_of_8tbs": round(gbs / 8000.0, 4),
                "launches_timed": launches * self.reps, "distinct_operand_sets": launches}
         self.rows.append(row)
-        print(json.dumps(row), flush=True)
+        if not self.quiet:
+            print(json.dumps(row), flush=True)
 
     # ── affine u4 family ──
     def affine(self, config, rows, cols, batch, mode="matvec", copies=None):

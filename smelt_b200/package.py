@@ -207,6 +207,37 @@ class Decoder:
         for l in range(2 * self.desc.layers):
             self.ctx.call("zero_slot", KV_BASE_SLOT + l)
 
+    def teacher_forced(self, prompt, teacher, use_graph: bool = True) -> np.ndarray:
+        """Scores a given continuation: feeds the prompt, then ``teacher[i - 1]`` at decode step i
+        whatever the model itself chose, and returns the argmax of every step, shape
+        ``[len(teacher), batch]``.  prompt ``[batch, n_prompt]``, teacher ``[n_steps, batch]``
+        (the last teacher row is only compared, never fed)."""
+        prompt = np.asarray(prompt, dtype=np.int32).reshape(self.batch, -1)
+        teacher = np.asarray(teacher, dtype=np.int32).reshape(-1, self.batch)
+        n_prompt = prompt.shape[1]
+        if use_graph and not self.graph_ready:
+            self.build_graph()
+
+        def step(tokens, pos):
+            if not use_graph:
+                return self.decode_step(tokens, pos)
+            self.graph_seed(tokens, pos)
+            return self.graph_decode(1, read=True)[0]
+
+        cur = None
+        for i in range(n_prompt):
+            if use_graph and i + 1 < n_prompt:
+                self.graph_seed(prompt[:, i], i)
+                self.graph_decode(1, read=False)
+            else:
+                cur = step(prompt[:, i], i)
+        out = np.zeros((teacher.shape[0], self.batch), np.int32)
+        for i in range(teacher.shape[0]):
+            out[i] = cur
+            if i + 1 < teacher.shape[0]:
+                cur = step(teacher[i], n_prompt + i)
+        return out
+
     def generate(self, prompt, n_decode: int, use_graph: bool = True) -> np.ndarray:
         """Feed the prompt token by token (the reference does the same without a prefill table,
         Sources/SmeltRuntime/SmeltModel.swift:619-631), then n_decode greedy steps."""
@@ -246,3 +277,18 @@ def open_tp_exchange(ctx: capi.Context, dist, world: int) -> None:
     ctx._check(ctx.lib.smelt_cuda_tp_exchange_open(ctx.h, allh.ctypes.data_as(C.c_void_p)))
     dist.barrier()
 
+
+
+def compare_greedy(got, tokens, runner_up, margins, tie: float = 0.02) -> dict:
+    """Verdict of a teacher-forced replay against known-good greedy tokens of one sequence.
+
+    A step counts as identical when the ids are equal.  A differing id is a tie break, not an
+    error, only when the known-good top-2 logit margin of that step is below ``tie`` (two fp16
+    ulps at the magnitude of these logits) AND the id is the known-good runner-up; everything
+    else lands in ``wrong``."""
+    got, tokens, runner_up, margins = (np.asarray(a).reshape(-1) for a in (got, tokens, runner_up, margins))
+    diff = np.nonzero(got != tokens)[0]
+    wrong = [int(i) for i in diff if not (margins[i] < tie and got[i] == runner_up[i])]
+    first = int(diff[0]) if diff.size else None
+    return {"checked": int(tokens.size), "identical": int(tokens.size - diff.size), "tie_breaks": int(diff.size - len(wrong)),
+            "wrong": wrong, "first_mismatch": first, "margin": float(margins[first]) if first is not None else None}

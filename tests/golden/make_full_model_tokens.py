@@ -34,27 +34,6 @@ def prompt_tokens(vocab: int, n: int, b: int = 0) -> np.ndarray:
     return np.random.Generator(np.random.Philox(key=[SEED, 1000 + b])).integers(0, vocab, size=n).astype(np.int32)
 
 
-def greedy(model, prompt, n_decode):
-    """Greedy decode of one sequence; per step (token, runner-up, margin) from the logits."""
-    model.reset()
-    logits = None
-    for i, t in enumerate(prompt):
-        last = i + 1 == len(prompt)
-        r = model.decode_step(int(t), i, want_logits=last)
-        if last:
-            logits = r[1]
-    toks, second, margin = [], [], []
-    pos = len(prompt)
-    for i in range(n_decode):
-        a, b, m = oracle.top2(logits)
-        toks.append(a); second.append(b); margin.append(m)
-        if i + 1 < n_decode:
-            tok, logits = model.decode_step(a, pos, want_logits=True)
-            assert tok == oracle.top2(logits)[0]
-            pos += 1
-    return toks, second, margin
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch8", action="store_true")
@@ -68,7 +47,7 @@ def main():
     rows = []
     for b in range(batch):
         t0 = time.time()
-        rows.append(greedy(model, prompt_tokens(cfg.vocab, n_prompt, b), n_decode))
+        rows.append(model.greedy_top2(prompt_tokens(cfg.vocab, n_prompt, b), n_decode))
         print("sequence %d generated in %.0f s: %s" % (b, time.time() - t0, rows[-1][0]), flush=True)
     out = {"seed": SEED, "prompt_len": n_prompt, "n_decode": n_decode, "config": cfg.as_dict(),
            "prompt_rng": "numpy Philox(key=[seed, 1000 + b]).integers(0, vocab, prompt_len), b = sequence index"}

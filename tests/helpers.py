@@ -17,6 +17,18 @@ def rel_err(got, ref) -> float:
     return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), max(floor, 1e-30))))
 
 
+def inf_err(got, ref) -> float:
+    """max_i |got_i - ref_i| / max_i |ref_i|: never larger than rel_err (whose denominators are
+    at most the largest |ref_i|), asserted beside it with a tighter bound so that the slack the
+    floor in rel_err gives near-zero outputs is visible."""
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    return float(np.max(np.abs(got - ref)) / max(float(np.max(np.abs(ref))), 1e-30))
+
+
+INF_TOL = 1e-3  # matvec / attention outputs: largest absolute error over the largest |output|
+
+
 def ulp_diff_f16(a, b) -> np.ndarray:
     """Distance in fp16 ulps (monotone integer mapping of the bit patterns)."""
     def key(x):

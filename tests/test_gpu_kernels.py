@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from smelt_b200 import capi, synth
-from helpers import REL_TOL, add_rel_err, rel_err, ulp_diff_f16
+from helpers import INF_TOL, REL_TOL, add_rel_err, inf_err, rel_err, ulp_diff_f16
 
 pytestmark = pytest.mark.gpu
 
@@ -81,6 +81,7 @@ def test_affine_matvec(ctx, oracle, rows, cols, group, batch):
     got = y.download(np.float16, (batch, rows))
     ref = oracle.affine_matvec(w, s, b, x, rows, cols, group)
     assert rel_err(got, ref) < REL_TOL
+    assert inf_err(got, ref) < INF_TOL
     canary = y.download(np.uint8, (64,), offset=batch * rows * 2)
     assert np.all(canary == 0xFF)  # nothing written past the output
 
@@ -97,6 +98,45 @@ def test_affine_matvec_reference_fixture(ctx, oracle):
     ref = oracle.affine_matvec(w, s, b, x, rows, cols, g)[0].astype(np.float32)
     assert np.max(np.abs(got - ref)) < 0.02
     assert np.max(np.abs(got)) > 1e-2
+
+
+@pytest.mark.parametrize("batch", [1, 4, 8, 16])
+def test_config1_layer_set(ctx, oracle, batch):
+    """BASELINE config 1: the seven matrices of a 2048 / 6144 decoder layer (Q, K, V, O, gate, up,
+    down; 16 x 4 x 128 heads), each at every batch of the config, through the records' kernels:
+    Q as affine_matvec, K | V as fused_dual_affine_matvec, O and down as fused_affine_matvec_add,
+    gate / up as fused_affine_gate_up_swiglu (fp32 gate and up, one rounding)."""
+    H, I, KV, G = 2048, 6144, 512, 64
+    t = {name: synth.affine_u4(21, name, r, c, G) for name, (r, c) in
+         {"q": (H, H), "k": (KV, H), "v": (KV, H), "o": (H, H), "gate": (I, H), "up": (I, H), "down": (H, I)}.items()}
+    x = synth.activations(21, "x", batch, H)
+    xi = synth.activations(21, "xi", batch, I)
+    res = synth.activations(21, "res", batch, H)
+    d = {name: dev(ctx, *t[name]) for name in t}
+    dx, dxi, dres = dev(ctx, x, xi, res)
+    y, y2 = ctx.alloc(batch * I * 2), ctx.alloc(batch * I * 2)
+
+    def check(got_buf, rows, ref):
+        got = got_buf.download(np.float16, (batch, rows))
+        assert rel_err(got, ref) < REL_TOL
+        assert inf_err(got, ref) < INF_TOL
+
+    ctx.call("affine_matvec", *d["q"], dx, y, H, H, G, batch)
+    check(y, H, oracle.affine_matvec(*t["q"], x, H, H, G))
+    ctx.call("affine_dual_matvec", *d["k"], *d["v"], dx, y, y2, KV, H, G, batch)
+    check(y, KV, oracle.affine_matvec(*t["k"], x, KV, H, G))
+    check(y2, KV, oracle.affine_matvec(*t["v"], x, KV, H, G))
+    ctx.call("affine_matvec_add", *d["o"], dx, dres, y, H, H, G, batch)
+    got = y.download(np.float16, (batch, H))
+    assert add_rel_err(got, oracle.affine_matvec_add(*t["o"], x, res, H, H, G), oracle.affine_matvec(*t["o"], x, H, H, G)) < REL_TOL
+    ctx.call("affine_gate_up_swiglu", *d["gate"], *d["up"], dx, y, I, H, G, batch)
+    check(y, I, oracle.affine_gate_up_swiglu(*t["gate"], *t["up"], x, I, H, G, round_gate_up=False))
+    ctx.call("affine_matvec_add", *d["down"], dxi, dres, y, H, I, G, batch)
+    got = y.download(np.float16, (batch, H))
+    assert add_rel_err(got, oracle.affine_matvec_add(*t["down"], xi, res, H, I, G), oracle.affine_matvec(*t["down"], xi, H, I, G)) < REL_TOL
+    for bufs in list(d.values()) + [[dx, dxi, dres, y, y2]]:
+        for b in bufs:
+            b.free()
 
 
 # batch 1 and 2 run on the integer-MMA kernel: every mode, row / K tails, long K, few chunks per warp
@@ -446,11 +486,7 @@ def test_attention_reference_fixture(ctx, oracle, seq_len, window):
     assert np.max(np.abs(got.astype(np.float32))) > 1e-3
 
 
-@pytest.mark.parametrize("n_q,n_kv,d", [(16, 4, 128), (8, 2, 256), (32, 8, 128), (16, 1, 64), (4, 1, 128), (8, 2, 128)])
-@pytest.mark.parametrize("ctx_len,batch", [(1024, 1), (4096, 1), (1000, 8), (32768, 1)])
-def test_attention_config3(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
-    if ctx_len == 32768 and (n_q, n_kv, d) not in [(16, 4, 128), (8, 2, 256)]:
-        pytest.skip("long context is covered on the two benchmark head shapes")
+def _attention_case(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
     cap = ctx_len + 8
     k = synth.kv_cache(8, "k", batch, n_kv, cap, d)
     v = synth.kv_cache(8, "v", batch, n_kv, cap, d)
@@ -462,6 +498,23 @@ def test_attention_config3(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
     for b in range(batch):
         ref = oracle.attention_decode(q[b], k[b], v[b], n_q, n_kv, d, cap, ctx_len)
         assert rel_err(got[b], ref) < REL_TOL
+        assert inf_err(got[b], ref) < INF_TOL
+    for buf in (dq, dk, dv, out):
+        buf.free()
+
+
+@pytest.mark.parametrize("n_q,n_kv,d", [(16, 4, 128), (8, 2, 256)])
+@pytest.mark.parametrize("ctx_len", [1024, 4096, 16384, 32768])
+@pytest.mark.parametrize("batch", [1, 8])
+def test_attention_config3(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
+    """BASELINE config 3, every cell: both head shapes x contexts 1k / 4k / 16k / 32k x batch 1 / 8."""
+    _attention_case(ctx, oracle, n_q, n_kv, d, ctx_len, batch)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d", [(32, 8, 128), (16, 1, 64), (4, 1, 128), (8, 2, 128)])
+@pytest.mark.parametrize("ctx_len,batch", [(1024, 1), (4096, 1), (1000, 8), (5000, 2)])
+def test_attention_other_head_shapes(ctx, oracle, n_q, n_kv, d, ctx_len, batch):
+    _attention_case(ctx, oracle, n_q, n_kv, d, ctx_len, batch)
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,position,batch,layout", [(32, 8, 128, 0, 1, 1), (32, 8, 128, 530, 1, 1), (16, 4, 128, 4095, 2, 1),

@@ -48,20 +48,26 @@ def test_decode_step_matches_oracle(ctx, oracle, cfg):
 
 
 def test_greedy_tokens_match_oracle_eager_graph_and_fused(ctx, oracle):
+    """Teacher-forced: the oracle's token is fed at every step and every step's argmax is
+    compared; a differing id passes only as the oracle's runner-up at a margin under 0.02."""
     cfg, cap, n_dec = SMALL, 96, 48
     pkg, dec = make(ctx, cfg, 5, cap)
     ref = oracle.model_from_package(pkg, cap)
     prompt = synth.rng_for(5, "prompt").integers(0, cfg.vocab, size=12).astype(np.int32)
-    want, margins = ref.generate(prompt, n_dec)
-    eager = dec.generate(prompt, n_dec, use_graph=False)[:, 0]
+    want, runner, margins = ref.greedy_top2(prompt, n_dec)
+    eager = dec.teacher_forced(prompt, want, use_graph=False)[:, 0]
     dec.reset_cache()
-    graph = dec.generate(prompt, n_dec, use_graph=True)[:, 0]
+    graph = dec.teacher_forced(prompt, want, use_graph=True)[:, 0]
     assert np.array_equal(eager, graph), "graph replay must equal eager interpretation"
-    # identical greedy ids wherever the oracle's own top-2 margin exceeds a couple of fp16 ulps
-    first_bad = next((i for i in range(n_dec) if eager[i] != want[i]), None)
-    assert first_bad is None or margins[first_bad] < 0.02, (first_bad, margins[first_bad] if first_bad is not None else None)
+    v = package.compare_greedy(eager, want, runner, margins)
+    print("small model: %d of %d steps identical, %d tie breaks" % (v["identical"], v["checked"], v["tie_breaks"]))
+    assert not v["wrong"], v
     _, fused = make(ctx, cfg, 5, cap, fuse=True)
-    assert np.array_equal(fused.generate(prompt, n_dec, use_graph=True)[:, 0], graph), "fused residual add must not change tokens"
+    assert np.array_equal(fused.teacher_forced(prompt, want, use_graph=True)[:, 0], graph), "fused residual add must not change tokens"
+    # free-running greedy decode equals the teacher-forced ids up to the first step the two differ at
+    free = dec.generate(prompt, n_dec, use_graph=True)[:, 0]
+    split = next((i for i in range(n_dec) if free[i] != want[i]), n_dec)
+    assert np.array_equal(free[:split + 1], graph[:split + 1])
 
 
 def test_fused_table_keeps_tokens_and_logits(ctx, oracle):
@@ -83,15 +89,15 @@ def test_fused_table_keeps_tokens_and_logits(ctx, oracle):
 
 
 def test_batch_of_independent_sequences(ctx, oracle):
-    cfg, cap, B = SMALL, 48, 4
+    cfg, cap, B, n_dec = SMALL, 48, 4, 8
     pkg, dec = make(ctx, cfg, 7, cap, batch=B)
     prompts = synth.rng_for(7, "prompts").integers(0, cfg.vocab, size=(B, 5)).astype(np.int32)
-    got = dec.generate(prompts, 8, use_graph=True)
     ref = oracle.model_from_package(pkg, cap)
+    gold = [ref.greedy_top2(prompts[b], n_dec) for b in range(B)]
+    got = dec.teacher_forced(prompts, np.array([g[0] for g in gold]).T, use_graph=True)
     for b in range(B):
-        want, margins = ref.generate(prompts[b], 8)
-        bad = next((i for i in range(8) if got[i, b] != want[i]), None)
-        assert bad is None or margins[bad] < 0.02
+        v = package.compare_greedy(got[:, b], *gold[b])
+        assert not v["wrong"], (b, v)
 
 
 def test_runtime_errors(ctx):
@@ -101,7 +107,7 @@ def test_runtime_errors(ctx):
     st = ctx.lib.smelt_cuda_decode_step(ctx.h, dec.table, dec.n_records, np.array([SMALL.vocab], np.int32).ctypes.data_as(C.c_void_p), 0, None)
     assert st == capi.OUT_OF_RANGE and "tokenId" in ctx.last_error()
     assert ctx.call_status("register_pipeline", 200, "fused_lut_matvec") == capi.UNKNOWN_PIPELINE
-    assert ctx.call_status("register_pipeline", 200, "attention_decode_mlx_vector_2pass_1_d256_b128") == capi.UNKNOWN_PIPELINE
+    assert ctx.call_status("register_pipeline", 200, "attention_decode_softcap") == capi.UNKNOWN_PIPELINE
     rec = (capi.DispatchRecord * 1)()
     rec[0].pipeline = 999
     st = ctx.lib.smelt_cuda_decode_step(ctx.h, rec, 1, np.array([0], np.int32).ctypes.data_as(C.c_void_p), 0, None)

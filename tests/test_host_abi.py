@@ -56,7 +56,8 @@ def test_dispatch_record_layout():
     ("smelt_rmsnorm_affine_qkv:4096:64", True), ("smelt_rmsnorm_affine_gate_up_swiglu:4096:64", True), ("smelt_rope_qkv_append", True), ("smelt_rope_attention_decode", True),
     ("smelt_rmsnorm_affine_qkv:4096:32", False), ("smelt_rmsnorm_affine_qkv:512:64", False),
     ("fused_lut_matvec", False), ("tqh_matvec", False), ("attention_decode_softcap", False), ("affine_matvec:4096:48", False),
-    ("attention_decode_mlx_vector_2pass_1_d256_b128", False), ("recurrence_step", False), ("", False),
+    ("attention_decode_mlx_vector_2pass_1_d256_b128", True), ("attention_decode_mlx_vector_2pass_2_d256_b128", True),
+    ("attention_decode_mlx_vector_2pass_1_d128_b128", False), ("recurrence_step", False), ("", False),
 ])
 def test_pipeline_names(lib, name, ok):
     assert bool(lib.smelt_cuda_pipeline_supported(name.encode())) == ok

@@ -196,3 +196,21 @@ def test_rms_norm_forms(oracle):
     assert np.max(np.abs(a - b) / np.maximum(np.abs(a), 1e-3)) < 2e-3
     z = np.zeros(2048, np.float16)
     assert np.array_equal(oracle.rms_norm_1pw(x, z, 1e-6, False).view(np.uint16), oracle.rms_norm_1pw(x, z, 1e-6, True).view(np.uint16))
+
+
+def test_two_pass_attention_restatement_agrees_with_the_decode_oracle(oracle):
+    """The reference holds two formulations of single-token attention at head_dim 256: the generic
+    oracle (RegionExactnessTests.swift:1414-1475) and the split-K record pair with 128 interleaved
+    key blocks and fp16 partials (attention.metal:1071-1206).  Their restatements must agree within
+    the matvec / attention tolerance, for a context shorter than, equal to and longer than 128 blocks."""
+    from helpers import REL_TOL, rel_err
+    from smelt_b200 import synth
+
+    n_q, n_kv, d, cap = 4, 2, 256, 1200
+    q = synth.activations(5, "q2p", n_q, d)
+    k = synth.kv_cache(5, "k2p", 1, n_kv, cap, d)[0]
+    v = synth.kv_cache(5, "v2p", 1, n_kv, cap, d)[0]
+    for seq_len in (1, 100, 128, 1100):
+        ref = oracle.attention_decode(q, k, v, n_q, n_kv, d, cap, seq_len, scale=0.0625)
+        two = oracle.attention_decode_mlx_2pass(q, k, v, n_q, n_kv, cap, seq_len)
+        assert rel_err(two, ref) < REL_TOL, seq_len

@@ -30,8 +30,12 @@ def _case(ctx, seed, n_q, n_kv, d, seq_len, batch):
 
 
 def test_static_scratch_matches_the_allocating_entry_point_twice_in_a_row(ctx):
-    # two calls in a row on different shapes: the second reuses the array the first one wrote
-    for seed, (n_q, n_kv, d, seq_len, batch) in enumerate([(32, 8, 128, 4096, 1), (16, 4, 128, 1000, 4)]):
+    # Calls in a row on different shapes: each reuses the array the one before wrote.  Up to 4096
+    # keys the splits of a KV head merge inside a thread-block cluster and the array is not
+    # touched; the cases above 4096 keys are the ones whose partials really live in it (and
+    # are merged by the separate merge kernel, since this entry point owns no counters).
+    for seed, (n_q, n_kv, d, seq_len, batch) in enumerate([(16, 4, 128, 8192, 1), (16, 4, 128, 6000, 4), (8, 2, 256, 20000, 1),
+                                                            (32, 8, 128, 4096, 1), (16, 4, 128, 1000, 4)]):
         dq, dk, dv, args = _case(ctx, 40 + seed, n_q, n_kv, d, seq_len, batch)
         want = ctx.alloc(batch * n_q * d * 2).fill(0)
         got = ctx.alloc(batch * n_q * d * 2).fill(0xFF)
