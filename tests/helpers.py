@@ -27,6 +27,12 @@ def inf_err(got, ref) -> float:
 
 
 INF_TOL = 1e-3  # matvec / attention outputs: largest absolute error over the largest |output|
+# The reference's D256 split-K attention pair hands its partial outputs from the first record to the
+# second as fp16 (Resources/Shaders/attention.metal:1140): every partial carries a 2^-11 relative
+# rounding, which for outputs an eighth of the RMS (the floor of rel_err) is up to 8 * 2^-11 = 4e-3
+# per block before the blocks are combined.  The pair is therefore held to INF_TOL on the
+# largest-output scale and to this looser bound under rel_err.
+TWO_PASS_REL_TOL = 8e-3
 
 
 def ulp_diff_f16(a, b) -> np.ndarray:

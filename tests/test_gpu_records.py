@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from smelt_b200 import capi, synth
-from helpers import INF_TOL, REL_TOL, inf_err, rel_err
+from helpers import INF_TOL, TWO_PASS_REL_TOL, inf_err, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -83,12 +83,12 @@ def test_d256_two_pass_record_pair(ctx, oracle, seq_len):
         record(1, [(PART, 0, 0, 0), (STATS, 1, 0, 0), (OUT, 2, 0, 0)], [(capi.CONST_LITERAL_U32, 3, n_q), guard], grid=(n_q, 1, 1)))
     ref = oracle.attention_decode(q, k, v, n_q, n_kv, d, cap, seq_len, scale=0.0625)
     ref_pair = oracle.attention_decode_mlx_2pass(q, k, v, n_q, n_kv, cap, seq_len)
-    assert rel_err(ref_pair, ref) < REL_TOL  # the reference's own two formulations agree within the tolerance
+    assert rel_err(ref_pair, ref) < TWO_PASS_REL_TOL  # the reference's own two formulations: fp16 partials cost this much
 
     def check():
         got = get(ctx, OUT, np.float16, (n_q, d))
-        assert rel_err(got, ref) < REL_TOL and inf_err(got, ref) < INF_TOL
-        assert rel_err(got, ref_pair) < REL_TOL
+        assert rel_err(got, ref) < TWO_PASS_REL_TOL and inf_err(got, ref) < INF_TOL
+        assert rel_err(got, ref_pair) < TWO_PASS_REL_TOL
         stats = get(ctx, STATS, np.float32, (2, n_q, 128))
         assert np.all(stats[0] >= 0) and np.all((stats[0] == 0) == (stats[1] <= -3e38))  # empty blocks are marked as the reference marks them
         assert np.all(np.sum(stats[0] > 0, axis=1) >= 1)

@@ -202,8 +202,8 @@ def test_two_pass_attention_restatement_agrees_with_the_decode_oracle(oracle):
     """The reference holds two formulations of single-token attention at head_dim 256: the generic
     oracle (RegionExactnessTests.swift:1414-1475) and the split-K record pair with 128 interleaved
     key blocks and fp16 partials (attention.metal:1071-1206).  Their restatements must agree within
-    the matvec / attention tolerance, for a context shorter than, equal to and longer than 128 blocks."""
-    from helpers import REL_TOL, rel_err
+    the bound the fp16 partials allow, for a context shorter than, equal to and longer than 128 blocks."""
+    from helpers import INF_TOL, TWO_PASS_REL_TOL, inf_err, rel_err
     from smelt_b200 import synth
 
     n_q, n_kv, d, cap = 4, 2, 256, 1200
@@ -213,4 +213,4 @@ def test_two_pass_attention_restatement_agrees_with_the_decode_oracle(oracle):
     for seq_len in (1, 100, 128, 1100):
         ref = oracle.attention_decode(q, k, v, n_q, n_kv, d, cap, seq_len, scale=0.0625)
         two = oracle.attention_decode_mlx_2pass(q, k, v, n_q, n_kv, cap, seq_len)
-        assert rel_err(two, ref) < REL_TOL, seq_len
+        assert rel_err(two, ref) < TWO_PASS_REL_TOL and inf_err(two, ref) < INF_TOL, seq_len
