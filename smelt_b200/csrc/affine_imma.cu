@@ -77,12 +77,20 @@ cudaError_t launch_imma_t(const Launch& l, AffineArgs a) {
 
 // Eight warps on one tile, four groups (256 columns) per ring stage; when the columns are a
 // multiple of 128 only, sixteen warps with two groups per stage.  Ring depth = stages each warp
-// keeps in flight + 1: three for the two-matrix modes, four otherwise.
+// keeps in flight + 1: four (measured against three, five, six and eight: an SM keeps about
+// 100 KB of copies outstanding, deeper rings only move waiting from the loop to the requests),
+// three when the digit planes of a long row leave no room for four.
+template <int MODE, int WARPS, int GPS>
+cudaError_t launch_imma_depth(const Launch& l, const AffineArgs& a) {
+    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
+    using G = Geo<WARPS, GPS>;
+    if (imma_layout(NW, 4, WARPS, G::kSetBytes, a.cols, a.batch, 1).total <= 226u * 1024u) return launch_imma_t<MODE, 4, WARPS, GPS, 1>(l, a);
+    return launch_imma_t<MODE, 3, WARPS, GPS, 1>(l, a);
+}
+
 template <int MODE>
 cudaError_t launch_imma_mode(const Launch& l, const AffineArgs& a, bool* handled) {
-    constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    constexpr int DEPTH = NW == 2 ? 3 : 4;
-    const cudaError_t e = a.cols % 256 != 0 ? launch_imma_t<MODE, DEPTH, 16, 2, 1>(l, a) : launch_imma_t<MODE, DEPTH, 8, 4, 1>(l, a);
+    const cudaError_t e = a.cols % 256 != 0 ? launch_imma_depth<MODE, 16, 2>(l, a) : launch_imma_depth<MODE, 8, 4>(l, a);
     if (e == cudaErrorNotSupported) return cudaSuccess;  // not handled: the caller falls back
     *handled = true;
     return e;

@@ -1,5 +1,4 @@
-// Device side of the integer-MMA affine u4 matvec (see affine_imma.cu for the description):
-// shared by the stand-alone kernel and the multi-phase decode kernel.
+// Device side of the integer-MMA affine u4 matvec (see affine_imma.cu for the description).
 #pragma once
 #include "affine_matvec.h"
 
@@ -24,7 +23,7 @@ struct Geo {
 };
 
 struct ImmaLayout {
-    uint32_t zero, xq, pitch_x, xsum, xscale, red, ring, stage_bytes, total;
+    uint32_t zero, xq, pitch_x, xsum, gscale, red, ring, stage_bytes, total;
 };
 
 __host__ __device__ inline ImmaLayout imma_layout(int nw, int depth, int warps, int set_bytes, int cols, int batch, int teams) {
@@ -35,7 +34,7 @@ __host__ __device__ inline ImmaLayout imma_layout(int nw, int depth, int warps, 
     L.zero = off; off += 64;
     L.xq = off; off += (uint32_t)(kDigits * batch) * L.pitch_x;
     L.xsum = off; off += (uint32_t)(cols / kGroup) * 2u * 4u;       // [group][batch slot 0/1]
-    L.xscale = off; off += 16;
+    L.gscale = off; off += (uint32_t)(cols / kGroup) * 2u * 4u;     // [group][batch slot 0/1]: 2^-26 of the group's fixed-point unit
     L.red = off; off += (uint32_t)teams * 2u * (uint32_t)nw * 2u * kTileRows * 16u * 4u;  // [team][buffer][set][batch][row][warp slot, 16]
     off = (off + 127u) & ~127u;
     L.ring = off; off += (uint32_t)warps * depth * L.stage_bytes;
@@ -66,19 +65,22 @@ __device__ __forceinline__ float amax8(const uint4& v) {
     return fmaxf(f.x, f.y);
 }
 
-// Four signed base-128 digits of X (|X| < 2^27), least significant first, each in [-64, 63]
-// except the last, which takes what remains.
-__device__ __forceinline__ void digits128(int X, int (&d)[4]) {
-#pragma unroll
-    for (int k = 0; k < 3; ++k) {
-        d[k] = ((X + 64) & 127) - 64;
-        X = (X - d[k]) >> 7;
-    }
-    d[3] = X;
+// X (|X| < 2^27) as four base-128 digits packed one per byte, least significant first: the low
+// three are the 7-bit fields of the two's-complement value (0..127), the top one is X >> 21
+// (signed).  Every byte is a valid s8 and X = sum digit_k * 128^k.
+__device__ __forceinline__ uint32_t digit_bytes(int X) {
+    const uint32_t u = (uint32_t)X;
+    return (u & 0x7Fu) | ((u << 1) & 0x7F00u) | ((u << 2) & 0x7F0000u) | ((uint32_t)(X >> 21) << 24);
 }
 
-__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+// Four words of digit bytes (one value each) -> four words holding one digit of all four values.
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&o)[4]) {
+    const uint32_t ab_lo = __byte_perm(a, b, 0x5140), ab_hi = __byte_perm(a, b, 0x7362);  // (a0 b0 a1 b1), (a2 b2 a3 b3)
+    const uint32_t cd_lo = __byte_perm(c, d, 0x5140), cd_hi = __byte_perm(c, d, 0x7362);
+    o[0] = __byte_perm(ab_lo, cd_lo, 0x5410);  // a0 b0 c0 d0
+    o[1] = __byte_perm(ab_lo, cd_lo, 0x7632);  // a1 b1 c1 d1
+    o[2] = __byte_perm(ab_hi, cd_hi, 0x5410);
+    o[3] = __byte_perm(ab_hi, cd_hi, 0x7632);
 }
 
 // TG tile groups per CTA: the CTA's warps form TG teams of WARPS / TG warps; each team walks its
@@ -101,7 +103,7 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
     const ImmaLayout L = imma_layout(NW, DEPTH, WARPS, G::kSetBytes, a.cols, a.batch, TG);
     uint8_t* xq = smem + L.xq;
     float* sxsum = reinterpret_cast<float*>(smem + L.xsum);
-    float* sxscale = reinterpret_cast<float*>(smem + L.xscale);
+    float* sgscale = reinterpret_cast<float*>(smem + L.gscale);
     float* sred0 = reinterpret_cast<float*>(smem + L.red);                      // staging scratch (whole CTA)
     float* sred = sred0 + (size_t)team * (2 * NW * 2 * kTileRows * 16);          // this team's K-partials
     uint8_t* ring = smem + L.ring + (size_t)warp * DEPTH * L.stage_bytes;
@@ -190,7 +192,8 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
 
     // The norm weights are weights too: requested before the wait, like the first stages.
     uint4 nwv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-    if (a.norm_w && kThreads == 256 && a.cols / 8 <= 2 * 256) {
+    const bool nw_pre = a.norm_w && kThreads == 256 && a.cols / 8 <= 2 * 256;
+    if (nw_pre) {
 #pragma unroll
         for (int i = 0; i < 2; ++i)
             if (tid + 256 * i < a.cols / 8) nwv[i] = *reinterpret_cast<const uint4*>(a.norm_w + (tid + 256 * i) * 8);
@@ -202,92 +205,105 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
         return;
     }
 
-    // ── activations: digit planes + per-group sums, once per CTA ──
+    // ── activations: digit planes, per-group scales and per-group sums, once per CTA ──
+    // Each group of 64 activations gets its own fixed-point scale: S = the power of two above the
+    // group's largest |x|, X = x * 2^26 / S (odd columns X / 16), so no pass over the whole row
+    // and no CTA-wide reduction comes before the digits.  A thread keeps its 16-byte chunks
+    // (tid, tid + threads, ...) in registers from the one global read to the end.
     {
+        constexpr int XC = 6;  // chunks a thread caches: rows of up to 6 * 8 * threads activations
         const int chunks = a.cols / 8;
         if (tid < 4) reinterpret_cast<uint4*>(smem + L.zero)[tid] = make_uint4(0, 0, 0, 0);
         if (a.batch == 1)
-            for (int i = tid; i < groups_total; i += kThreads) sxsum[i * 2 + 1] = 0.f;
-        // Rows of up to 4096 activations stay in registers between the passes (two 16-byte words
-        // per thread, the chunk order of cta256_sumsq_f16); longer rows are read again per pass.
-        const bool cached = kThreads == 256 && chunks <= 2 * 256;
+            for (int i = tid; i < groups_total; i += kThreads) sxsum[i * 2 + 1] = sgscale[i * 2 + 1] = 0.f;
+        const bool cached = chunks <= XC * kThreads;
         for (int b = 0; b < a.batch; ++b) {
             const __half* xr = a.x + (size_t)b * a.cols;
-            uint4 xc[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            uint4 xc[XC];
             if (cached) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
-                    if (tid + 256 * i < chunks) xc[i] = *reinterpret_cast<const uint4*>(xr + (tid + 256 * i) * 8);
+                for (int i = 0; i < XC; ++i)
+                    xc[i] = tid + kThreads * i < chunks ? *reinterpret_cast<const uint4*>(xr + (size_t)(tid + kThreads * i) * 8) : make_uint4(0, 0, 0, 0);
             }
             float rs = 0.f;
             if (a.norm_w) {
-                // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass;
-                // sred is free here: no tile has been reduced yet
-                const float tot = cached ? cta256_sum_finish(sumsq8(sumsq8(0.f, xc[0]), xc[1]), sred0) : cta256_sumsq_f16(xr, a.cols, sred0);
-                rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
-                if (cached) {
+                // rms_norm_1pw (Resources/Shaders/norms.metal:9-67) folded into the staging pass, with
+                // the summation order of cta256_sumsq_f16: thread t folds chunks t, t + 256, ... in one chain
+                float tot;
+                if (cached && kThreads == 256) {
+                    float ss = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 2; ++i)
-                        if (tid + 256 * i < chunks) {
-                            const uint4 wv = nwv[i];
-                            xc[i].x = rms_norm_1pw_pair(xc[i].x, wv.x, rs); xc[i].y = rms_norm_1pw_pair(xc[i].y, wv.y, rs);
-                            xc[i].z = rms_norm_1pw_pair(xc[i].z, wv.z, rs); xc[i].w = rms_norm_1pw_pair(xc[i].w, wv.w, rs);
-                        }
+                    for (int i = 0; i < XC; ++i)
+                        if (tid + kThreads * i < chunks) ss = sumsq8(ss, xc[i]);
+                    tot = cta256_sum_finish(ss, sred0);
+                } else {
+                    tot = cta256_sumsq_f16(xr, a.cols, sred0);
                 }
+                rs = __frcp_rn(__fsqrt_rn(tot / (float)a.cols + a.norm_eps));
             }
-            auto load8 = [&](int c8) {
-                if (cached) return c8 < 256 ? xc[0] : xc[1];  // c8 = tid or tid + 256
-                uint4 v = *reinterpret_cast<const uint4*>(xr + c8 * 8);
-                if (a.norm_w) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c8 * 8);
-                    v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
-                    v.z = rms_norm_1pw_pair(v.z, wv.z, rs); v.w = rms_norm_1pw_pair(v.w, wv.w, rs);
-                }
+            auto normed = [&](uint4 v, const uint4& wv) {
+                v.x = rms_norm_1pw_pair(v.x, wv.x, rs); v.y = rms_norm_1pw_pair(v.y, wv.y, rs);
+                v.z = rms_norm_1pw_pair(v.z, wv.z, rs); v.w = rms_norm_1pw_pair(v.w, wv.w, rs);
                 return v;
             };
-            float m = 0.f;
-            for (int c8 = tid; c8 < chunks; c8 += kThreads) m = fmaxf(m, amax8(load8(c8)));
-            m = warp_max(m);
-            __syncthreads();
-            if (lane == 0) sred0[16 + warp] = m;
-            __syncthreads();
-            float mx = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sred0[16 + w]);
-            // S = 2^(e-126) > mx; X = x * 2^26 / S; results are scaled back by S / 2^26
-            const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
-            const bool live = e >= 26u && e < 255u;
-            const float inv = live ? __uint_as_float((279u - e) << 23) : 0.f;
-            const float inv16 = inv * 0.0625f;
-            if (tid == 0) sxscale[b] = live ? __uint_as_float((e - 25u) << 23) : 0.f;
-            for (int base = 0; base < chunks; base += kThreads) {
-                const int c8 = base + tid;
+            auto stage_chunk = [&](int c8, uint4 v) {  // called by all 32 lanes together; c8 >= chunks: lane idles
+                const bool on = c8 < chunks;
+                float m = on ? amax8(v) : 0.f;
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));  // the group's eight chunks sit in eight neighbouring lanes
+                // S = 2^(e-126) > m; X = x * 2^26 / S; results are scaled back by S / 2^26
+                const uint32_t e = (__float_as_uint(m) >> 23) & 0xFFu;
+                const bool live = e >= 26u && e < 255u;
+                const float inv = live ? __uint_as_float((279u - e) << 23) : 0.f;
+                const float inv16 = inv * 0.0625f;
                 float sum = 0.f;
-                if (c8 < chunks) {
-                    const uint4 v = load8(c8);
+                if (on) {
                     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-                    int de[4][4], dq[4][4];  // [pair][digit]: even / odd column of each pair
+                    uint32_t de[4], dq[4];  // digit bytes of the even / odd column of each pair
                     float fs[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float2 f = __half22float2(u32_as_h2(u[j]));
                         fs[j] = f.x + f.y;
-                        digits128(__float2int_rn(f.x * inv), de[j]);
-                        digits128(__float2int_rn(f.y * inv16), dq[j]);
+                        de[j] = digit_bytes(__float2int_rn(f.x * inv));
+                        dq[j] = digit_bytes(__float2int_rn(f.y * inv16));
                     }
                     sum = (fs[0] + fs[1]) + (fs[2] + fs[3]);
+                    uint32_t pe[4], pq[4];
+                    transpose4x4(de[0], de[1], de[2], de[3], pe);
+                    transpose4x4(dq[0], dq[1], dq[2], dq[3], pq);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint2 o;
-                        o.x = pack4(de[0][k], de[1][k], de[2][k], de[3][k]);
-                        o.y = pack4(dq[0][k], dq[1][k], dq[2][k], dq[3][k]);
-                        *reinterpret_cast<uint2*>(xq + (size_t)(4 * b + 3 - k) * L.pitch_x + (size_t)c8 * 8) = o;
-                    }
+                    for (int k = 0; k < 4; ++k)
+                        *reinterpret_cast<uint2*>(xq + (size_t)(4 * b + 3 - k) * L.pitch_x + (size_t)c8 * 8) = make_uint2(pe[k], pq[k]);
                 }
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-                if (c8 < chunks && (c8 & 7) == 0) sxsum[(c8 >> 3) * 2 + b] = sum;
+                if (on && (c8 & 7) == 0) {
+                    sxsum[(c8 >> 3) * 2 + b] = sum;
+                    sgscale[(c8 >> 3) * 2 + b] = live ? __uint_as_float((e - 25u) << 23) : 0.f;
+                }
+            };
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < XC; ++i) {
+                    if (kThreads * i >= chunks) break;  // uniform: the whole CTA is past the row
+                    const int c8 = tid + kThreads * i;
+                    uint4 v = xc[i];
+                    if (a.norm_w && c8 < chunks) v = normed(v, (nw_pre && i < 2) ? nwv[i] : *reinterpret_cast<const uint4*>(a.norm_w + (size_t)c8 * 8));
+                    stage_chunk(c8, v);
+                }
+            } else {
+                for (int base = 0; base < chunks; base += kThreads) {
+                    const int c8 = base + tid;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (c8 < chunks) {
+                        v = *reinterpret_cast<const uint4*>(xr + (size_t)c8 * 8);
+                        if (a.norm_w) v = normed(v, *reinterpret_cast<const uint4*>(a.norm_w + (size_t)c8 * 8));
+                    }
+                    stage_chunk(c8, v);
+                }
             }
         }
         __syncthreads();
@@ -299,6 +315,7 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
     const uint8_t* pb_base = bvalid ? xq + (size_t)g * L.pitch_x + t * 16 : smem + L.zero + t * 16;
     const int pb_stride = bvalid ? kGroup : 0;
     const float* pxs = sxsum + (t >> 1);  // this lane's columns belong to batch row t / 2
+    const float* pgs = sgscale + (t >> 1);
     const int csw = GPS == 2 ? ((g >> 1) & 1) << 1 : (g & 3) << 1;
     int w_off[GPS];
 #pragma unroll
@@ -334,6 +351,7 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
 #pragma unroll
             for (int gg = 0; gg < GPS; ++gg) {
                 const uint4 xb = *reinterpret_cast<const uint4*>(pb_base + (grp0 + gg) * pb_stride);
+                const float gsv = pgs[(grp0 + gg) * 2];  // the group's fixed-point unit
 #pragma unroll
                 for (int s = 0; s < NW; ++s) {
                     const uint8_t* base = st + s * G::kSetBytes;
@@ -349,14 +367,13 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
                     // columns 2t, 2t+1 hold neighbouring digit planes: 128 * high + low
                     const float va = fmaf(__int_as_float(c[0]) - kMagicF, 128.f, __int_as_float(c[1]) - kMagicF);
                     const float vb = fmaf(__int_as_float(c[2]) - kMagicF, 128.f, __int_as_float(c[3]) - kMagicF);
-                    acc[s][0] = fmaf(sa, va, acc[s][0]);
-                    acc[s][1] = fmaf(sb, vb, acc[s][1]);
+                    acc[s][0] = fmaf(sa * gsv, va, acc[s][0]);
+                    acc[s][1] = fmaf(sb * gsv, vb, acc[s][1]);
                 }
             }
         }
         // ── tile done: lanes t = 0,1 (2,3) hold the upper and lower digit pairs of batch row 0 (1) ──
         const int buf = ti & 1;
-        const float xscale = sxscale[t >> 1];
 #pragma unroll
         for (int s = 0; s < NW; ++s)
 #pragma unroll
@@ -365,7 +382,7 @@ __device__ __forceinline__ void affine_imma_body(const AffineArgs& a, uint8_t* s
                 const float tot = (t & 1) ? fmaf(other, 16384.f, mine) : fmaf(mine, 16384.f, other);
                 const float bs = bacc[s][h] + __shfl_xor_sync(0xffffffffu, bacc[s][h], 1);
                 if ((t & 1) == 0)
-                    sred[((((buf * NW + s) * 2 + (t >> 1)) * kTileRows) + g + 8 * h) * 16 + wl] = fmaf(tot, xscale, bs);
+                    sred[((((buf * NW + s) * 2 + (t >> 1)) * kTileRows) + g + 8 * h) * 16 + wl] = tot + bs;
             }
         if (TG == 1) __syncthreads();
         else asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(WG * 32) : "memory");

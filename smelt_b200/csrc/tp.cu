@@ -62,11 +62,11 @@ smelt_status tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data, size_t count, cu
 // ── all-reduce + residual add over peer memory ──────────────────────────────
 // Every rank owns an exchange buffer that its peers can write (CUDA IPC mapping over NVLink):
 //   ll [2 buffers][world sources][kTpMaxCount / 2] of {two fp16 values, sequence number}
-// One launch per reduction, one CTA per rank.  The CTA pushes its partial into slot [rank] of
+// One launch per reduction and rank.  A thread pushes one word of its partial into slot [rank] of
 // every rank's buffer as 8-byte stores that carry four bytes of data and the reduction's
 // sequence number together (no fence and no separate flag: a word is valid as soon as its
 // number matches, the way NCCL's low-latency protocol packs data and flag); nothing is loaded
-// across NVLink.  It then polls its own buffer (bounded) word by word, adds the world's
+// across NVLink.  It then polls its own buffer (bounded), adds the world's
 // partials in rank order in fp32, rounds once to fp16 and adds the residual as elementwise_add
 // does.  Every rank adds the same values in the same order, so the replicated hidden state
 // stays bit-identical across ranks.  Two buffers alternate: a rank cannot be more than one
@@ -79,6 +79,7 @@ constexpr uint32_t kTpSpinLimit = 1u << 21;      // about a second of polling pe
 struct TpExchange {
     uint2* ll[kTpMaxWorld];   // every rank's buffer, as mapped into this process
     uint32_t* seq;            // this rank's reduction counter (device memory)
+    uint32_t* ticket;         // CTAs of the running reduction that have finished (zero between launches)
     int rank, world;
 };
 
@@ -93,40 +94,62 @@ __device__ __forceinline__ uint2 ld_volatile_v2(const uint2* p) {
     return v;
 }
 
-__global__ void __launch_bounds__(1024) tp_reduce_add_kernel(TpExchange ex, const __half* partial, const __half* residual, __half* out,
-                                                             int count, uint32_t* err, DevDyn dyn) {
+// One thread per packed word.  The pushes go out first; then the thread requests its word from
+// every source's slot at once (independent loads, one round trip for all of them) and re-requests
+// only the slots whose sequence number has not arrived yet.  The last CTA to finish (ticket)
+// advances the reduction counter: every thread of the launch has read it by then.
+__global__ void __launch_bounds__(256) tp_reduce_add_kernel(TpExchange ex, const __half* partial, const __half* residual, __half* out,
+                                                            int count, uint32_t* err, DevDyn dyn) {
     pdl_trigger();
     pdl_wait();
     if (dyn_skip(dyn)) return;
-    const int tid = threadIdx.x;
-    const uint32_t seq = *ex.seq + 1u;  // read by every thread before thread 0 overwrites it at the end
-    __syncthreads();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t seq = *ex.seq + 1u;
     const int buf = (int)(seq & 1u);
     const int words = count / 2;
-    const uint32_t* pw = reinterpret_cast<const uint32_t*>(partial);
-    for (int i = tid; i < words; i += blockDim.x) {
-        const uint32_t v = pw[i];
-        for (int r = 0; r < ex.world; ++r) st_volatile_v2(ex.ll[r] + tp_ll_index(buf, ex.rank, ex.world) + i, v, seq);
-    }
-    const uint2* mine = ex.ll[ex.rank];
-    bool gave_up = false;
-    for (int i = tid; i < words; i += blockDim.x) {
-        float acc0 = 0.f, acc1 = 0.f;
-        for (int r = 0; r < ex.world; ++r) {
-            const uint2* src = mine + tp_ll_index(buf, r, ex.world) + i;
-            uint2 v = ld_volatile_v2(src);
-            uint32_t spins = 0;
-            while (v.y != seq && !gave_up && ++spins < kTpSpinLimit) v = ld_volatile_v2(src);
-            gave_up |= v.y != seq;
-            const float2 f = __half22float2(u32_as_h2(v.x));
-            acc0 += f.x; acc1 += f.y;
+    if (i < words) {
+        const uint32_t mine = reinterpret_cast<const uint32_t*>(partial)[i];
+#pragma unroll
+        for (int r = 0; r < kTpMaxWorld; ++r)
+            if (r < ex.world) st_volatile_v2(ex.ll[r] + tp_ll_index(buf, ex.rank, ex.world) + i, mine, seq);
+        const uint2* base = ex.ll[ex.rank] + tp_ll_index(buf, 0, ex.world) + i;
+        const size_t stride = kTpMaxCount / 2;  // words between two sources' slots
+        uint2 v[kTpMaxWorld];
+#pragma unroll
+        for (int r = 0; r < kTpMaxWorld; ++r) v[r] = r < ex.world ? ld_volatile_v2(base + r * stride) : make_uint2(0u, seq);
+        uint32_t spins = 0;
+        for (;;) {
+            uint32_t pending = 0;
+#pragma unroll
+            for (int r = 0; r < kTpMaxWorld; ++r) pending |= (v[r].y != seq ? 1u : 0u) << r;
+            if (!pending) break;
+            if (++spins >= kTpSpinLimit) {  // a peer never arrived: results are not valid
+                if (err) atomicOr(err, 0x100u);
+                break;
+            }
+#pragma unroll
+            for (int r = 0; r < kTpMaxWorld; ++r)
+                if (pending & (1u << r)) v[r] = ld_volatile_v2(base + r * stride);
         }
+        float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < kTpMaxWorld; ++r)
+            if (r < ex.world) {
+                const float2 f = __half22float2(u32_as_h2(v[r].x));
+                acc0 += f.x; acc1 += f.y;
+            }
         // half(sum) + residual as an fp16 add (activations.metal elementwise_add)
         const uint32_t rv = reinterpret_cast<const uint32_t*>(residual)[i];
         reinterpret_cast<uint32_t*>(out)[i] = h2_as_u32(__hadd2(__floats2half2_rn(acc0, acc1), u32_as_h2(rv)));
     }
-    if (gave_up && err) atomicOr(err, 0x100u);  // a peer never arrived: results are not valid
-    if (tid == 0) *ex.seq = seq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(ex.ticket, 1u) == gridDim.x - 1u) {
+            *ex.ticket = 0u;
+            *ex.seq = seq;
+        }
+    }
 }
 
 // Vocab-parallel argmax: every rank holds the ordered keys (lut_matvec.metal:4045-4074) of its
@@ -199,10 +222,10 @@ smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* par
     if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out)) & 3u) return SMELT_OK;
     TpExchange ex = {};
     for (int r = 0; r < ctx->tp_world; ++r) ex.ll[r] = (uint2*)st->mapped[r];
-    ex.seq = st->seq; ex.rank = ctx->tp_rank; ex.world = ctx->tp_world;
+    ex.seq = st->seq; ex.ticket = st->seq + 1; ex.rank = ctx->tp_rank; ex.world = ctx->tp_world;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1);
-    cfg.blockDim = dim3(1024);
+    cfg.gridDim = dim3((unsigned)((count / 2 + 255) / 256));
+    cfg.blockDim = dim3(256);
     cfg.stream = l.stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -295,7 +318,7 @@ smelt_status smelt_cuda_tp_exchange_handle(smelt_cuda_ctx* ctx, uint8_t handle[S
         if (!st) return SMELT_ERR_ALLOC;
         const size_t bytes = tp_exchange_bytes(ctx->tp_world);
         bool ok = cudaMalloc(&st->local, bytes) == cudaSuccess && cudaMemset(st->local, 0, bytes) == cudaSuccess;
-        ok = ok && cudaMalloc((void**)&st->seq, sizeof(uint32_t)) == cudaSuccess && cudaMemset(st->seq, 0, sizeof(uint32_t)) == cudaSuccess;
+        ok = ok && cudaMalloc((void**)&st->seq, 2 * sizeof(uint32_t)) == cudaSuccess && cudaMemset(st->seq, 0, 2 * sizeof(uint32_t)) == cudaSuccess;
         ok = ok && cudaDeviceSynchronize() == cudaSuccess;
         if (!ok) { cudaFree(st->local); cudaFree(st->seq); delete st; return fail(ctx, SMELT_ERR_ALLOC, "tp exchange: allocation failed"); }
         ctx->tp_peer = st;
@@ -335,7 +358,7 @@ smelt_status smelt_cuda_tp_exchange_open_loopback(smelt_cuda_ctx* ctx, int world
     TpPeerState* st = new (std::nothrow) TpPeerState();
     if (!st) return SMELT_ERR_ALLOC;
     const size_t bytes = tp_exchange_bytes(world);
-    bool ok = cudaMalloc((void**)&st->seq, sizeof(uint32_t)) == cudaSuccess && cudaMemset(st->seq, 0, sizeof(uint32_t)) == cudaSuccess;
+    bool ok = cudaMalloc((void**)&st->seq, 2 * sizeof(uint32_t)) == cudaSuccess && cudaMemset(st->seq, 0, 2 * sizeof(uint32_t)) == cudaSuccess;
     for (int r = 0; r < world && ok; ++r) ok = cudaMalloc(&st->mapped[r], bytes) == cudaSuccess && cudaMemset(st->mapped[r], 0, bytes) == cudaSuccess;
     uint2* regions[kTpMaxWorld] = {};
     for (int r = 0; r < world; ++r) regions[r] = (uint2*)((char*)st->mapped[r] + tp_ll_bytes(world));

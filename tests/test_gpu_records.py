@@ -88,7 +88,7 @@ def test_d256_two_pass_record_pair(ctx, oracle, seq_len):
     def check():
         got = get(ctx, OUT, np.float16, (n_q, d))
         assert rel_err(got, ref) < TWO_PASS_REL_TOL and inf_err(got, ref) < INF_TOL
-        assert rel_err(got, ref_pair) < TWO_PASS_REL_TOL
+        assert rel_err(got, ref_pair) < 2 * TWO_PASS_REL_TOL  # two independent sets of fp16-rounded partials
         stats = get(ctx, STATS, np.float32, (2, n_q, 128))
         assert np.all(stats[0] >= 0) and np.all((stats[0] == 0) == (stats[1] <= -3e38))  # empty blocks are marked as the reference marks them
         assert np.all(np.sum(stats[0] > 0, axis=1) >= 1)

@@ -71,21 +71,23 @@ def test_greedy_tokens_match_oracle_eager_graph_and_fused(ctx, oracle):
 
 
 def test_fused_table_keeps_tokens_and_logits(ctx, oracle):
-    """Norm folded into the projections, one Q/K/V launch, one RoPE + append launch: the same
-    rounding points, so the same greedy tokens as the reference-shaped table."""
+    """Norm folded into the projections, one Q/K/V launch, one RoPE + append + attention launch:
+    the same rounding points and the same summation order per output row, so the same logits bit
+    for bit as the reference-shaped table, and the oracle's tokens."""
     cfg, cap, n_dec = MID, 64, 24
     prompt = synth.rng_for(6, "prompt").integers(0, cfg.vocab, size=9).astype(np.int32)
-    _, plain = make(ctx, cfg, 6, cap)
-    want = plain.generate(prompt, n_dec, use_graph=True)[:, 0]
+    pkg, plain = make(ctx, cfg, 6, cap)
+    want, runner, margins = oracle.model_from_package(pkg, cap).greedy_top2(prompt, n_dec)
+    got_plain = plain.teacher_forced(prompt, want, use_graph=True)[:, 0]
     logits_plain = plain.logits()[0].copy()
     _, fused = make(ctx, cfg, 6, cap, fuse=3)
     assert len(fused.table) < len(plain.table) - 6 * cfg.layers
-    eager = fused.generate(prompt, n_dec, use_graph=False)[:, 0]
+    eager = fused.teacher_forced(prompt, want, use_graph=False)[:, 0]
     assert np.array_equal(fused.logits()[0].view(np.uint16), logits_plain.view(np.uint16)), "same rounding points, same bits"
     fused.reset_cache()
-    graph = fused.generate(prompt, n_dec, use_graph=True)[:, 0]
-    assert np.array_equal(eager, graph)
-    assert np.array_equal(graph, want)
+    graph = fused.teacher_forced(prompt, want, use_graph=True)[:, 0]
+    assert np.array_equal(eager, graph) and np.array_equal(graph, got_plain)
+    assert not package.compare_greedy(graph, want, runner, margins)["wrong"]
 
 
 def test_batch_of_independent_sequences(ctx, oracle):
