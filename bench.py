@@ -208,6 +208,11 @@ def run_ours(args):
     gen_s = time.time() - t0
 
     prompts = np.stack([np.random.Generator(np.random.Philox(key=[SEED, 1000 + b])).integers(0, cfg.vocab, size=args.prompt_len) for b in range(B)]).astype(np.int32)
+    if dist is not None:
+        # Ranks finish building their weight shards seconds apart; the exchange's bounded wait is
+        # about a second, so every rank waits here until all are ready to decode.
+        ctx.synchronize()
+        dist.barrier()
     for i in range(args.prompt_len):  # the reference's no-prefill path: one decode step per prompt token
         dec.graph_seed(prompts[:, i], i)
         if i + 1 < args.prompt_len:
@@ -265,7 +270,7 @@ def run_ours(args):
     if dist is not None:
         import torch
 
-        tt = torch.tensor([dev_ms, e2e_s, float(device_error != 0), float(bool(parity.get("wrong")))], device="cuda", dtype=torch.float64)
+        tt = torch.tensor([dev_ms, e2e_s, float(device_error), float(bool(parity.get("wrong")))], device="cuda", dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         dev_ms, e2e_s = float(tt[0]), float(tt[1])
         device_error = device_error or int(tt[2])

@@ -55,6 +55,8 @@ def main():
             package.open_tp_exchange(ctx, dist, world)
         image, desc, layers = package.build_image(pkg, rank, world, vocab_parallel=bool(fuse & 8))  # 14: + vocab-parallel LM head
         dec = package.Decoder(ctx, image, desc, layers, 64, 1, fuse_residual=fuse)
+        ctx.synchronize()
+        dist.barrier()  # ranks start decoding together: the exchange's bounded wait is about a second
         eager = dec.teacher_forced(prompt, want, use_graph=False)[:, 0]
         dec.reset_cache()
         graph = dec.teacher_forced(prompt, want, use_graph=True)[:, 0]
