@@ -251,6 +251,40 @@ SMELT_CUDA_API smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const 
 SMELT_CUDA_API smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_desc* desc, uint32_t batch, char* out,
                                                          size_t out_bytes, size_t* needed_bytes);
 
+/* ── package reader ──────────────────────────────────────────────────────────
+ * The part of SmeltRuntime.init between a .smeltpkg directory and the first decoded token
+ * (Sources/SmeltRuntime/SmeltRuntime.swift:668-998): manifest.json (pipelines, buffers.slots,
+ * slotLayout, config.vocabSize, weights.entries: Sources/SmeltSchema/SmeltManifest.swift:26-98,
+ * :806-817, :1649-1768), weights.bin, dispatches.bin.  Prefill tables, model.metallib, checksums
+ * and prepared-prefix snapshots are not read. */
+typedef struct {
+    uint32_t context_capacity; /* positions every KV cache slot holds; 0 = the capacity the slots were compiled for */
+    uint32_t context_limit;    /* 0 = context_capacity */
+} smelt_package_options;
+typedef struct {
+    uint32_t n_records, n_pipelines, n_pipelines_used, n_slots, n_weight_entries;
+    uint32_t vocab_size, hidden_size, num_layers, cache_seq_capacity;
+    int32_t token_id_slot, position_slot, weights_slot, argmax_slot, logits_slot;
+    uint64_t weights_bytes;
+} smelt_package_info;
+/* Host only (no device needed): parses and validates a package the way the loader does and
+ * reports the first problem in err: manifest fields missing, a weight entry outside weights.bin
+ * (SMELT_ERR_OUT_OF_RANGE), dispatches.bin not a multiple of the 360-byte record stride
+ * (SmeltRuntime.swift:6332-6338), a record naming a pipeline index the manifest does not list or
+ * a kernel that is not implemented (SMELT_ERR_UNKNOWN_PIPELINE). */
+SMELT_CUDA_API smelt_status smelt_cuda_inspect_package(const char* package_dir, smelt_package_info* out_info, char* err, size_t err_bytes);
+/* Loads the package into the context: weights.bin into the weights slot, one zero-filled buffer
+ * per manifest slot (KV caches keyCache_<n> / valCache_<n> of shape [heads, capacity, head_dim]
+ * sized for context_capacity, SmeltRuntime.swift:6891-6913), the pipelines the decode table uses
+ * registered under their manifest indices, the runtime configured (token / position / weights
+ * slots from slotLayout, argmax in fixed slot 17, hiddenA / hiddenB = slots 0 / 1 as the double
+ * buffer, SmeltRuntimeConfig.swift:104-150), dispatches.bin kept as the context's decode table. */
+SMELT_CUDA_API smelt_status smelt_cuda_open_package(smelt_cuda_ctx* ctx, const char* package_dir, const smelt_package_options* options,
+                                                    smelt_package_info* out_info);
+/* The decode table of the open package (owned by the context; valid until the next open or destroy):
+ * pass it to smelt_cuda_decode_step / smelt_cuda_enqueue_decode / smelt_cuda_graph_build. */
+SMELT_CUDA_API smelt_status smelt_cuda_package_table(smelt_cuda_ctx* ctx, const smelt_dispatch_record** out_table, size_t* out_n);
+
 /* ── tensor parallelism (no counterpart in the reference, which is single-device) ──
  * One process per GPU.  Rank 0 creates an id, the caller ships it to the other ranks, every
  * rank calls init.  The record interpreter then accepts the pipeline name

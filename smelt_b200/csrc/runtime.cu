@@ -99,6 +99,7 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     ctx->graph_exec = nullptr;
     ctx->graph = nullptr;
     tp_destroy(ctx);
+    package_destroy(ctx);
     for (auto& s : ctx->slots)
         if (s.ptr) cudaFree(s.ptr);
     cudaFree(ctx->dyn_dev);

@@ -65,6 +65,8 @@ bool parse_pipeline(const char* entry, Pipeline* out);
 
 }  // namespace smelt
 
+struct smelt_package_state;
+
 struct smelt_cuda_ctx {
     int device = 0;
     int sm_count = 0;
@@ -105,6 +107,7 @@ struct smelt_cuda_ctx {
     void* nccl_comm = nullptr;
     void* tp_peer = nullptr;   // peer-memory exchange state (tp.cu)
     int tp_rank = 0, tp_world = 1;
+    smelt_package_state* package = nullptr;  // decode table of the open .smeltpkg (package_reader.cu)
 };
 
 namespace smelt {
@@ -112,6 +115,7 @@ smelt_status fail(smelt_cuda_ctx* ctx, smelt_status code, const std::string& msg
 smelt_status check_cuda(smelt_cuda_ctx* ctx, cudaError_t e, const char* what);
 smelt_status tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data, size_t count, cudaStream_t stream);
 void tp_destroy(smelt_cuda_ctx* ctx);
+void package_destroy(smelt_cuda_ctx* ctx);
 smelt_status tp_argmax(smelt_cuda_ctx* ctx, const Launch& l, const void* partials, void* out, int n, uint32_t offset, int batch);
 smelt_status tp_reduce_add(smelt_cuda_ctx* ctx, const Launch& l, const void* partial, const void* residual, void* out, size_t count,
                            bool* handled);

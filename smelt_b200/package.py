@@ -10,6 +10,8 @@ because the text path always runs ``rms_norm_1pw`` (Sources/SmeltCompiler/SmeltC
 from __future__ import annotations
 
 import ctypes as C
+import json
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -261,6 +263,112 @@ class Decoder:
             if i + 1 < n_decode:
                 cur = self.decode_step(cur, n_prompt + i)
         return out
+
+
+def write_package(path: str, cfg: DecoderConfig, image: np.ndarray, desc: capi.DecoderDesc, layers, capacity: int,
+                  fuse_residual: int = 0) -> None:
+    """Writes a ``.smeltpkg`` directory for a synthetic decoder in the reference's wire formats:
+    ``manifest.json`` (top-level and slotLayout keys camelCase, weight entries and buffer slots
+    snake_case, Sources/SmeltSchema/SmeltManifest.swift:26-98, :806-817, :1710-1768),
+    ``weights.bin`` (the image) and ``dispatches.bin`` (the decode table as raw 360-byte records,
+    Sources/SmeltRuntime/SmeltRuntime.swift:6322-6350).  Stands in for the build-time compiler."""
+    lib = capi.load()
+    os.makedirs(path, exist_ok=True)
+    desc.fuse_residual = int(fuse_residual)
+    n = C.c_size_t(0)
+    if lib.smelt_cuda_build_decoder(None, C.byref(desc), layers, capacity, 1, None, C.byref(n)) != 0:
+        raise capi.SmeltError(1, "build_decoder (count) failed")
+    table = (capi.DispatchRecord * n.value)()
+    if lib.smelt_cuda_build_decoder(None, C.byref(desc), layers, capacity, 1, table, C.byref(n)) != 0:
+        raise capi.SmeltError(1, "build_decoder (dry run) failed")
+    need = C.c_size_t(0)
+    lib.smelt_cuda_decoder_pipelines(C.byref(desc), 1, None, C.c_size_t(0), C.byref(need))
+    buf = C.create_string_buffer(need.value)
+    lib.smelt_cuda_decoder_pipelines(C.byref(desc), 1, buf, C.c_size_t(need.value), C.byref(need))
+    pipelines = [p for p in buf.value.decode().split("\n") if p]
+    H, I, D = cfg.hidden, desc.inter, cfg.head_dim
+    qd, kvd = desc.n_q * D, desc.n_kv * D
+    parts = (cfg.vocab + 2047) // 2048
+    slots = [(0, "hiddenA", H * 2, "fp16", [H], "activation"), (1, "hiddenB", H * 2, "fp16", [H], "activation"),
+             (8, "normOutBuf", H * 2, "fp16", [H], "activation"), (13, "ffnIntBuf", I * 2, "fp16", [I], "activation"),
+             (14, "ffnDownBuf", H * 2, "fp16", [H], "activation"), (16, "logits", cfg.vocab * 2, "fp16", [cfg.vocab], "activation"),
+             (17, "argmaxResult", 8, "int32", [2], "activation"), (20, "attnQBuf", qd * 2, "fp16", [qd], "activation"),
+             (21, "attnKBuf", kvd * 2, "fp16", [kvd], "activation"), (22, "attnVBuf", kvd * 2, "fp16", [kvd], "activation"),
+             (23, "attnOutBuf", qd * 2, "fp16", [qd], "activation"), (WEIGHTS_SLOT, "weights", 0, "raw", [], "weight"),
+             (33, "tokenId", 4, "int32", [1], "dynamic"), (34, "position", 8, "int32", [2], "dynamic"),
+             (35, "argmaxScratch", parts * 8, "raw", [parts * 8], "activation")]
+    for l in range(cfg.layers):
+        for base, name in ((KV_BASE_SLOT, "keyCache"), (KV_BASE_SLOT + cfg.layers, "valCache")):
+            slots.append((base + l, f"{name}_{l}", desc.n_kv * capacity * D * 2, "fp16", [desc.n_kv, capacity, D], "state"))
+    entries = []
+
+    def affine_entry(name, ref, rows, cols):
+        groups = cols // cfg.group
+        entries.append({"name": name, "offset": int(ref.packed), "size_bytes": rows * cols // 2, "shape": [rows, cols], "dtype": "affine_u4",
+                        "group_size": cfg.group, "scales_offset": int(ref.scales), "scales_size_bytes": rows * groups * 2,
+                        "biases_offset": int(ref.biases), "biases_size_bytes": rows * groups * 2})
+
+    for l in range(cfg.layers):
+        L = layers[l]
+        for name, rows, cols in (("q", qd, H), ("k", kvd, H), ("v", kvd, H), ("o", H, qd), ("gate", I, H), ("up", I, H), ("down", H, I)):
+            affine_entry(f"layers.{l}.{name}", getattr(L, name), rows, cols)
+        for name in ("input_norm", "post_norm"):
+            entries.append({"name": f"layers.{l}.{name}", "offset": int(getattr(L, name)), "size_bytes": H * 2, "shape": [H], "dtype": "fp16"})
+    rows_head = cfg.vocab // desc.tp_world if (fuse_residual & 8) and desc.tp_world > 1 else cfg.vocab
+    entries += [{"name": "embedding", "offset": int(desc.embedding), "size_bytes": cfg.vocab * H * 2, "shape": [cfg.vocab, H], "dtype": "fp16"},
+                {"name": "lm_head", "offset": int(desc.lm_head), "size_bytes": rows_head * H * 2, "shape": [rows_head, H], "dtype": "fp16"},
+                {"name": "final_norm", "offset": int(desc.final_norm), "size_bytes": H * 2, "shape": [H], "dtype": "fp16"}]
+    manifest = {
+        "version": 1, "kind": "text-generation", "architecture": "text-generation", "modelName": "synthetic-affine-u4-decoder",
+        "config": {"hiddenSize": H, "numLayers": cfg.layers, "vocabSize": cfg.vocab, "staticSeqCapacity": capacity, "ropeDim": D,
+                   "numDeltaLayers": 0, "numAttnLayers": cfg.layers, "deltaNumHeads": 0, "deltaQKVDim": 0, "attnQProjDim": qd,
+                   "attnKProjDim": kvd, "attnVProjDim": kvd, "attnOutDim": qd, "ffnDim": I, "attentionByRole": {}, "turboQuantHPatterns": []},
+        "checksums": {}, "device": {}, "weights": {"total_bytes": int(image.nbytes), "entries": entries},
+        "buffers": {"slots": [{"index": i, "name": n_, "size_bytes": int(b), "dtype": dt, "shape": sh, "category": cat} for i, n_, b, dt, sh, cat in slots]},
+        "pipelines": pipelines,
+        "slotLayout": {"convStateBaseSlot": -1, "recStateBaseSlot": -1, "keyCacheBaseSlot": KV_BASE_SLOT, "valCacheBaseSlot": KV_BASE_SLOT + cfg.layers,
+                       "ropeCosSlot": -1, "ropeSinSlot": -1, "ropeTablePairs": [], "tokenIdSlot": 33, "positionSlot": 34, "weightsSlot": WEIGHTS_SLOT},
+    }
+    with open(os.path.join(path, "manifest.json"), "w") as f:
+        json.dump(manifest, f, sort_keys=True)
+    np.asarray(image, np.uint8).tofile(os.path.join(path, "weights.bin"))
+    with open(os.path.join(path, "dispatches.bin"), "wb") as f:
+        f.write(bytes(table))
+
+
+class PackageSession:
+    """A ``.smeltpkg`` opened by the library's own reader (``smelt_cuda_open_package``): the
+    counterpart of ``SmeltRuntime(packagePath:)`` followed by ``decodeStep``."""
+
+    def __init__(self, ctx: capi.Context, path: str, context_capacity: int = 0):
+        self.ctx = ctx
+        self.info = capi.PackageInfo()
+        opts = capi.PackageOptions(context_capacity=context_capacity, context_limit=0)
+        ctx._check(ctx.lib.smelt_cuda_open_package(ctx.h, path.encode(), C.byref(opts), C.byref(self.info)))
+        table, n = C.c_void_p(), C.c_size_t(0)
+        ctx._check(ctx.lib.smelt_cuda_package_table(ctx.h, C.byref(table), C.byref(n)))
+        self.table, self.n_records = table, n.value
+
+    def decode_step(self, token: int, position: int) -> int:
+        tok, out = np.array([token], np.int32), np.zeros(1, np.int32)
+        self.ctx._check(self.ctx.lib.smelt_cuda_decode_step(self.ctx.h, self.table, self.n_records, tok.ctypes.data_as(C.c_void_p), int(position),
+                                                           out.ctypes.data_as(C.c_void_p)))
+        return int(out[0])
+
+    def build_graph(self):
+        self.ctx._check(self.ctx.lib.smelt_cuda_graph_build(self.ctx.h, self.table, self.n_records))
+
+    def graph_step(self, token: int, position: int) -> int:
+        tok, out = np.array([token], np.int32), np.zeros(1, np.int32)
+        self.ctx._check(self.ctx.lib.smelt_cuda_graph_step(self.ctx.h, tok.ctypes.data_as(C.c_void_p), int(position), out.ctypes.data_as(C.c_void_p)))
+        return int(out[0])
+
+
+def inspect_package(path: str):
+    """(status, PackageInfo, first problem) from the host-only validator."""
+    info, err = capi.PackageInfo(), C.create_string_buffer(512)
+    st = capi.load().smelt_cuda_inspect_package(path.encode(), C.byref(info), err, C.c_size_t(512))
+    return st, info, err.value.decode()
 
 
 def open_tp_exchange(ctx: capi.Context, dist, world: int) -> None:
