@@ -449,6 +449,11 @@ cudaError_t launch_group(const Launch& l, const AffineArgs& a, int group) {
 
 cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int group) {
     if (args.rows <= 0 || args.cols <= 0 || args.batch <= 0 || args.cols % group != 0) return cudaErrorInvalidValue;
+    if (args.batch >= 17) {  // tcgen05 QMM: the weights cross HBM once per 64 batch rows
+        bool handled = false;
+        cudaError_t e = launch_affine_qmm(l, mode, args, group, &handled);
+        if (handled || e != cudaSuccess) return e;
+    }
     // Batches beyond 16 rows are processed in passes of 16 (weights re-streamed per pass).
     if (args.batch > 16) {
         for (int b0 = 0; b0 < args.batch; b0 += 16) {

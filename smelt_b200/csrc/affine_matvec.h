@@ -38,12 +38,20 @@ struct AffineArgs {
     AffineSeg seg[3];
     int ks, nsplit;        // filled by the launcher
     int sm_count;          // SMs of the device (0 = assume 148)
+    // Tensor-memory QMM only: where CTAs that split a row tile's K leave their fp32 sums
+    // (part_scratch_bytes bytes) and count their arrivals (one int per row tile, 4096 of them,
+    // all zero between launches).  Launches that use them must not overlap on the device.
+    float* part_scratch;
+    size_t part_scratch_bytes;
+    int* part_counters;
     uint32_t* err;         // device error word (may be null)
     DevDyn dyn;            // filled by the launcher
 };
 
 cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int group);
 cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
+// Tensor-memory QMM for batches of seventeen rows and more (affine_qmm.cu).
+cudaError_t launch_affine_qmm(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
 cudaError_t launch_affine_imma(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
 
 }  // namespace smelt

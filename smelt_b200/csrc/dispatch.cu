@@ -322,7 +322,7 @@ smelt_status run_affine(Interp& in, const Pipeline& p, const smelt_dispatch_reco
     a.x = (const __half*)r.buf[ix].ptr; a.y = (__half*)r.buf[iy].ptr;
     if (iy2 >= 0) { NEED_BUF(iy2); NEED_BYTES(iy2, (size_t)batch * rows * 2); a.y2 = (__half*)r.buf[iy2].ptr; }
     if (ires >= 0) { NEED_BUF(ires); NEED_BYTES(ires, (size_t)batch * rows * 2); a.residual = (const __half*)r.buf[ires].ptr; }
-    a.rows = rows; a.cols = p.cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+    a.rows = rows; a.cols = p.cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count; a.part_scratch = ctx->qmm_scratch; a.part_scratch_bytes = ctx->qmm_scratch_bytes; a.part_counters = ctx->qmm_counters;
     const int mode = p.kind == PK_AFFINE_MATVEC ? kAffinePlain : p.kind == PK_AFFINE_ADD ? kAffineAdd : p.kind == PK_AFFINE_GATEUP ? kAffineGateUp : kAffineDual;
     in.launches += (batch + 15) / 16;
     return check_cuda(ctx, launch_affine(make_launch(in, r), mode, a, p.group), p.name.c_str());
@@ -620,7 +620,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             NEED_BYTES(9, (size_t)nb * p.cols * 2); NEED_BYTES(10, (size_t)p.cols * 2);
             a.w[0] = a.seg[0].w; a.s[0] = a.seg[0].s; a.b[0] = a.seg[0].b; a.y = a.seg[0].y;
             a.x = (const __half*)r.buf[9].ptr; a.norm_w = (const __half*)r.buf[10].ptr; a.norm_eps = as_f32(eps_bits);
-            a.cols = p.cols; a.batch = (int)nb; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+            a.cols = p.cols; a.batch = (int)nb; a.err = ctx->err_dev; a.sm_count = ctx->sm_count; a.part_scratch = ctx->qmm_scratch; a.part_scratch_bytes = ctx->qmm_scratch_bytes; a.part_counters = ctx->qmm_counters;
             in.launches += 1;
             cudaError_t e = launch_affine(l, kAffinePlain, a, p.group);
             if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": shape not eligible for the fused kernel");
@@ -641,7 +641,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             }
             NEED_BYTES(6, (size_t)nb * p.cols * 2); NEED_BYTES(7, (size_t)nb * rows * 2); NEED_BYTES(9, (size_t)p.cols * 2);
             a.x = (const __half*)r.buf[6].ptr; a.y = (__half*)r.buf[7].ptr; a.norm_w = (const __half*)r.buf[9].ptr; a.norm_eps = as_f32(eps_bits);
-            a.rows = (int)rows; a.cols = p.cols; a.batch = (int)nb; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+            a.rows = (int)rows; a.cols = p.cols; a.batch = (int)nb; a.err = ctx->err_dev; a.sm_count = ctx->sm_count; a.part_scratch = ctx->qmm_scratch; a.part_scratch_bytes = ctx->qmm_scratch_bytes; a.part_counters = ctx->qmm_counters;
             in.launches += 1;
             cudaError_t e = launch_affine(l, kAffineGateUp, a, p.group);
             if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": shape not eligible for the fused kernel");

@@ -73,6 +73,10 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     ctx->attn_scratch_bytes = attention_scratch_bytes(64, 256, 8, attention_max_splits());
     ok = ok && cudaMalloc(&ctx->attn_scratch, ctx->attn_scratch_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->rope_table, 256 * sizeof(float)) == cudaSuccess;
+    ctx->qmm_scratch_bytes = (size_t)24 << 20;  // 148 CTAs x two matrices x 64 batch rows x 128 rows of fp32, with room to spare
+    ok = ok && cudaMalloc(&ctx->qmm_scratch, ctx->qmm_scratch_bytes) == cudaSuccess;
+    ok = ok && cudaMalloc(&ctx->qmm_counters, 4096 * sizeof(int)) == cudaSuccess;
+    ok = ok && cudaMemset(ctx->qmm_counters, 0, 4096 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->attn_counters, 4096 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(ctx->attn_counters, 0, 4096 * sizeof(int)) == cudaSuccess;
     ctx->argmax_scratch_bytes = 64 * 1024 * sizeof(uint64_t);
@@ -106,6 +110,8 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     cudaFree(ctx->err_dev);
     cudaFree(ctx->attn_scratch);
     cudaFree(ctx->attn_counters);
+    cudaFree(ctx->qmm_scratch);
+    cudaFree(ctx->qmm_counters);
     cudaFree(ctx->rope_table);
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gen_ring);
@@ -381,7 +387,7 @@ static smelt_status affine_common(smelt_cuda_ctx* ctx, int mode, const void* w0,
     a.w[0] = (const uint8_t*)w0; a.s[0] = (const __half*)s0; a.b[0] = (const __half*)b0;
     a.w[1] = (const uint8_t*)w1; a.s[1] = (const __half*)s1; a.b[1] = (const __half*)b1;
     a.x = (const __half*)x; a.y = (__half*)y; a.y2 = (__half*)y2; a.residual = (const __half*)residual;
-    a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+    a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count; a.part_scratch = ctx->qmm_scratch; a.part_scratch_bytes = ctx->qmm_scratch_bytes; a.part_counters = ctx->qmm_counters;
     return check_cuda(ctx, launch_affine(typed_launch(ctx), mode, a, group), "affine matvec launch");
 }
 
@@ -424,7 +430,7 @@ smelt_status smelt_cuda_affine_multi_matvec(smelt_cuda_ctx* ctx, const smelt_aff
     }
     a.w[0] = a.seg[0].w; a.s[0] = a.seg[0].s; a.b[0] = a.seg[0].b; a.y = a.seg[0].y;
     a.x = (const __half*)x; a.norm_w = (const __half*)norm_w; a.norm_eps = eps;
-    a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+    a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count; a.part_scratch = ctx->qmm_scratch; a.part_scratch_bytes = ctx->qmm_scratch_bytes; a.part_counters = ctx->qmm_counters;
     if (n_tensors == 1 && !norm_w) a.nseg = 0;
     cudaError_t e = launch_affine(typed_launch(ctx), kAffinePlain, a, group);
     if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "affine multi matvec: needs group 64, cols % 1024 == 0, 16-byte aligned operands, rows % 16 == 0 for all but the last tensor");
@@ -441,7 +447,7 @@ smelt_status smelt_cuda_rmsnorm_affine_gate_up_swiglu(smelt_cuda_ctx* ctx, const
     a.w[0] = (const uint8_t*)gw; a.s[0] = (const __half*)gs; a.b[0] = (const __half*)gb;
     a.w[1] = (const uint8_t*)uw; a.s[1] = (const __half*)us; a.b[1] = (const __half*)ub;
     a.x = (const __half*)x; a.y = (__half*)y; a.norm_w = (const __half*)norm_w; a.norm_eps = eps;
-    a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count;
+    a.rows = rows; a.cols = cols; a.batch = batch; a.err = ctx->err_dev; a.sm_count = ctx->sm_count; a.part_scratch = ctx->qmm_scratch; a.part_scratch_bytes = ctx->qmm_scratch_bytes; a.part_counters = ctx->qmm_counters;
     cudaError_t e = launch_affine(typed_launch(ctx), kAffineGateUp, a, group);
     if (e == cudaErrorNotSupported) return fail(ctx, SMELT_ERR_UNSUPPORTED, "rmsnorm gate/up: needs group 64, cols % 1024 == 0, 16-byte aligned operands");
     return check_cuda(ctx, e, "rmsnorm gate/up launch");
