@@ -38,7 +38,7 @@ namespace {
 constexpr int kRowsPerCta = 128;
 constexpr int kBlockCols = 64;                 // one quantisation group = one A / B tile along K
 constexpr int kStageCols = 256;                // packed columns per cp.async stage
-__host__ __device__ constexpr int raw_stages(int nw, int nb) { return nw == 2 ? 3 : (nb >= 0 ? 4 : 4); }  // cp.async ring depth (all but one in flight), as shared memory allows
+__host__ __device__ constexpr int raw_stages(int nw) { return nw == 2 ? 3 : 4; }  // cp.async ring depth (all but one in flight), as shared memory allows
 constexpr int kTileStages = 2;                 // A / B tile buffers
 constexpr int kProducers = 256;                // eight warps: two threads per weight row (sixteen warps measured slower: the loop is bound by instruction issue)
 constexpr int kThreads = kProducers + 32;
@@ -57,7 +57,7 @@ __host__ __device__ inline QmmLayout qmm_layout(int nw, int nb) {
     uint32_t off = 0;
     L.a_tiles = off; off += (uint32_t)(kTileStages * nw * kATileBytes);
     L.b_tiles = off; off += (uint32_t)(kTileStages * nb * kBlockCols * 2);
-    L.raw = off; off += (uint32_t)(raw_stages(nw, nb) * nw * kRawStageBytes);
+    L.raw = off; off += (uint32_t)(raw_stages(nw) * nw * kRawStageBytes);
     L.xsum = off; off += 8u * (uint32_t)nb * 4u;   // [block & 7][batch row]
     L.bars = off; off += 128;
     L.total = off + 1024;  // slack to align the dynamic base to 1024 bytes (the swizzle atom)
@@ -132,7 +132,7 @@ __device__ __forceinline__ void nibbles_to_half(uint32_t w, uint32_t (&p)[4]) {
 template <int MODE, int NB>
 __global__ void __launch_bounds__(kThreads, 1) affine_qmm_kernel(const AffineArgs a) {
     constexpr int NW = (MODE == kAffineGateUp || MODE == kAffineDual) ? 2 : 1;
-    constexpr int kRawStages = raw_stages(NW, NB);
+    constexpr int kRawStages = raw_stages(NW);
     constexpr int XCH = (NB * 8 + kProducers - 1) / kProducers;  // 16-byte chunks of the B tile per producer thread
     constexpr int CPT = NB / 2;                                   // accumulator columns (batch rows) a thread drains
     constexpr uint32_t kSlotCols = NW * NB;

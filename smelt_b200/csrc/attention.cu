@@ -29,11 +29,19 @@ namespace {
 
 using namespace attn;
 
-template <int D, int NH>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnDev p) {
+template <int D, int NH, int NU>
+__global__ void __launch_bounds__(kAttnThreads, D <= 128 ? 2 : 1) attn_decode_kernel(const AttnDev p) {
     extern __shared__ __align__(16) float smem_f[];
-    attn_decode_body<D, NH>(p, smem_f, blockIdx.x, blockIdx.y, blockIdx.z, imma::PdlSync());
+    attn_decode_body<D, NH, NU>(p, smem_f, blockIdx.x, blockIdx.y, blockIdx.z, imma::PdlSync());
 }
+
+// Ring units per warp: K and V of one tile when no warp gets a second tile; else three (two in
+// flight while one is consumed).  The kernel is bound by the latency of a warp's chain through a
+// tile (scores, softmax, weighted sum), not by copies in flight, so up to head_dim 128 the rings
+// stay under half the shared memory and two CTAs (sixteen warps) share an SM.
+template <int D>
+constexpr int ring_units(bool deep) { return !deep ? 2 : D == 64 ? 6 : 3; }
+constexpr int ctas_per_sm(int head_dim) { return head_dim <= 128 ? 2 : 1; }
 
 // cos | sin of the current position for the half pairs of a head (analytic full-head RoPE),
 // once per token; the attention launches of every layer read it.
@@ -50,23 +58,13 @@ __global__ void rope_table_kernel(float* table, int half, float base_log2, DevDy
 }
 
 // Merge the per-split partials of one (sequence, query head) in split order.
+template <int D>
 __global__ void attn_merge_kernel(const AttnDev p) {
+    __shared__ float s_ml[2 * kMaxSplits];
     pdl_trigger();
     pdl_wait();
     if (dyn_skip(p.dyn)) return;
-    const int D = p.a.head_dim;
-    const size_t qh = blockIdx.x;
-    float mstar = kNegBig;
-    for (int s = 0; s < p.nsplits; ++s) mstar = fmaxf(mstar, p.part_ml[(qh * p.nsplits + s) * 2]);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.f, lsum = 0.f;
-        for (int s = 0; s < p.nsplits; ++s) {
-            const float f = exp2f(p.part_ml[(qh * p.nsplits + s) * 2] - mstar);
-            acc += p.part_o[(qh * p.nsplits + s) * D + d] * f;
-            lsum += p.part_ml[(qh * p.nsplits + s) * 2 + 1] * f;
-        }
-        p.a.out[qh * D + d] = __float2half_rn(acc / lsum);
-    }
+    merge_partials<D>(p, s_ml, blockIdx.x, 1, threadIdx.x, blockDim.x);
 }
 
 // attention_decode_mlx_vector_2pass_2_d256_b128 (Resources/Shaders/attention.metal:1146-1206):
@@ -93,10 +91,10 @@ __global__ void attn_mlx_reduce_kernel(const __half* partials, const float* stat
     }
 }
 
-template <int D, int NH>
+template <int D, int NH, int NU>
 cudaError_t launch_decode_t(const Launch& l, const AttnDev& p) {
-    const size_t smem = attn_smem_bytes<D, NH>();
-    auto kern = attn_decode_kernel<D, NH>;
+    const size_t smem = attn_smem_bytes<D, NH, NU>();
+    auto kern = attn_decode_kernel<D, NH, NU>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -154,23 +152,28 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     const uint32_t n_max = a.seq_from_pos ? a.capacity : (a.seq_len < a.capacity ? a.seq_len : a.capacity);
     if (n_max == 0) return cudaErrorInvalidValue;
     const int sm = a.sm_count > 0 ? a.sm_count : 148;
-    int want = (3 * sm + a.n_kv * a.batch - 1) / (a.n_kv * a.batch);
-    int by_len = (int)((n_max + 127u) / 128u);  // at least one 16-key tile per warp and split
-    int nsplits = want < by_len ? want : by_len;
-    if (nsplits < 1) nsplits = 1;
-    if (nsplits > kMaxSplits) nsplits = kMaxSplits;
-    while (nsplits > 1 && attention_scratch_bytes(a.n_q, a.head_dim, a.batch, nsplits) > a.scratch_bytes) --nsplits;
-    // Short contexts are latency bound: up to eight splits of a KV head run as one thread-block
-    // cluster and merge through distributed shared memory, with no partials in global memory.
-    bool cluster = n_max <= 4096 && by_len >= 2;
+    const int by_len = (int)((n_max + 127u) / 128u);  // at least one 16-key tile per warp and split
+    // The grid runs in waves of as many CTAs as are resident at once: the smallest split count
+    // within 2 % of the best-filled last wave.
+    const int base = a.n_kv * a.batch;
+    const long slots = (long)sm * ctas_per_sm(a.head_dim);
+    int cap = by_len < kMaxSplits ? by_len : kMaxSplits;
     if (a.mlx_partials) {
         // two-pass pair: the partials go to the record's own buffers, the second record merges
         if (a.batch != 1 || !a.mlx_stats) return cudaErrorInvalidValue;
-        cluster = false;
-        nsplits = want < by_len ? want : by_len;
-        if (nsplits < 1) nsplits = 1;
-        if (nsplits > kMaxSplits) nsplits = kMaxSplits;
+    } else {
+        while (cap > 1 && attention_scratch_bytes(a.n_q, a.head_dim, a.batch, cap) > a.scratch_bytes) --cap;
     }
+    auto fill = [&](int n) { const long ctas = (long)n * base; return (double)ctas / (double)(((ctas + slots - 1) / slots) * slots); };
+    double best = 0.0;
+    for (int n = 1; n <= cap; ++n) best = fill(n) > best ? fill(n) : best;
+    int nsplits = 1;
+    while (nsplits < cap && fill(nsplits) < best - 0.02) ++nsplits;
+    // Short contexts are latency bound: up to 4096 keys, eight splits of a KV head run as one
+    // thread-block cluster and merge through distributed shared memory, with no partials in
+    // global memory (measured against one tile per warp and the ticket merge: 11.2 against
+    // 13.9 us at 4096 keys, batch 1).
+    const bool cluster = n_max <= 4096 && by_len >= 2 && !a.mlx_partials;
     if (cluster) nsplits = by_len < 8 ? by_len : 8;
     AttnDev p;
     p.a = a;
@@ -181,8 +184,12 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     p.dyn = dev_dyn(l);
     cudaError_t e = cudaSuccess;
     const int nh = ratio > 8 ? 2 : 1;
-#define SMELT_ATTN_CASE(DD)                                                                 \
-    case DD: e = nh == 1 ? launch_decode_t<DD, 1>(l, p) : launch_decode_t<DD, 2>(l, p); break;
+    const bool deep = (n_max + (uint32_t)nsplits - 1) / (uint32_t)nsplits > (uint32_t)kAttnWarps * 16u;  // some warp walks two tiles or more
+#define SMELT_ATTN_CASE(DD)                                                                                             \
+    case DD:                                                                                                            \
+        e = nh == 1 ? (deep ? launch_decode_t<DD, 1, ring_units<DD>(true)>(l, p) : launch_decode_t<DD, 1, 2>(l, p))     \
+                    : (deep ? launch_decode_t<DD, 2, ring_units<DD>(true)>(l, p) : launch_decode_t<DD, 2, 2>(l, p));    \
+        break;
     switch (a.head_dim) {
         SMELT_ATTN_CASE(64)
         SMELT_ATTN_CASE(128)
@@ -200,8 +207,9 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = l.pdl ? 1 : 0;
-    prefer_max_shared(attn_merge_kernel);
-    return cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+    auto merge = a.head_dim == 64 ? attn_merge_kernel<64> : a.head_dim == 128 ? attn_merge_kernel<128> : attn_merge_kernel<256>;
+    prefer_max_shared(merge);
+    return cudaLaunchKernelEx(&cfg, merge, p);
 }
 
 cudaError_t launch_attention_mlx_reduce(const Launch& l, const __half* partials, const float* stats, __half* out, int n_q, int head_dim) {

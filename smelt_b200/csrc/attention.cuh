@@ -23,6 +23,49 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     return d;
 }
 
+// out = sum_s exp2(m_s - M) O_s / sum_s exp2(m_s - M) l_s over the splits of `heads` consecutive
+// query heads starting at qh0, splits in index order.  The (max, sum) pairs are staged in shared
+// memory first (smem: 2 * heads * nsplits floats), so the loop over the splits carries no load
+// that depends on another: sixteen partial rows are in flight per thread.
+template <int D>
+__device__ __forceinline__ void merge_partials(const AttnDev& p, float* smem, size_t qh0, int heads, int tid, int nthreads) {
+    const int ns = p.nsplits;
+    float* s_m = smem;
+    float* s_l = smem + heads * ns;
+    for (int i = tid; i < heads * ns; i += nthreads) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + qh0 * ns + i);
+        s_m[i] = ml.x; s_l[i] = ml.y;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < heads * D; idx += nthreads) {
+        const int h = idx / D, d = idx % D;
+        const float* hm = s_m + h * ns;
+        const float* hl = s_l + h * ns;
+        float mstar = kNegBig;
+        for (int s2 = 0; s2 < ns; ++s2) mstar = fmaxf(mstar, hm[s2]);
+        const float* po = p.part_o + (qh0 + h) * ns * D + d;
+        float acc = 0.f, lsum = 0.f;
+        int s2 = 0;
+        for (; s2 + 16 <= ns; s2 += 16) {
+            float v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = __ldcg(po + (size_t)(s2 + u) * D);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const float f = exp2f(hm[s2 + u] - mstar);
+                acc += v[u] * f;
+                lsum += hl[s2 + u] * f;
+            }
+        }
+        for (; s2 < ns; ++s2) {
+            const float f = exp2f(hm[s2] - mstar);
+            acc += __ldcg(po + (size_t)s2 * D) * f;
+            lsum += hl[s2] * f;
+        }
+        p.a.out[(qh0 + h) * D + d] = __float2half_rn(acc / lsum);
+    }
+}
+
 __device__ __forceinline__ void key_range(const AttnDev& p, uint32_t& seq_start, uint32_t& seq_len) {
     seq_len = p.a.seq_from_pos ? dyn_position(p.dyn) + 1u : p.a.seq_len;
     if (seq_len > p.a.capacity) seq_len = p.a.capacity;
@@ -32,15 +75,21 @@ __device__ __forceinline__ void key_range(const AttnDev& p, uint32_t& seq_start,
 
 // One (split, KV head, sequence) work item by one CTA of kAttnThreads threads.  Sync is called
 // once by every thread before the first read of q or the caches (see affine_imma.cuh).
-template <int D, int NH, class Sync>
+template <int D, int NU>
+__host__ __device__ constexpr size_t attn_ring_bytes() {
+    return (size_t)kAttnWarps * NU * (D / 16) * 512;
+}
+
+template <int D, int NH, int NU, class Sync>
 __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f, int split, int kvh, int b, Sync sync) {
     constexpr int MT = D / 16;  // m-tiles of O^T
     constexpr int KJ = D / 32;  // 16-byte chunks per thread per K row
     constexpr int VC = D / 64;  // 16-byte chunks per thread per V row
-    sync();
-    if (dyn_skip(p.dyn)) return;
-
     const AttnArgs& a = p.a;
+    // Cache rows below seq_len - 1 that were written before this token's launches began may be
+    // requested before the wait for the previous launch; everything else is read after it.
+    const bool early = a.kv_rows_stable && a.k_new;
+    if (!early) sync();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int ratio = a.n_q / a.n_kv;
 
@@ -55,31 +104,72 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
     const __half* Kb = a.k_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
     const __half* Vb = a.v_cache + (size_t)b * a.seq_stride + (size_t)kvh * a.capacity * D;
 
-    // One tile = 16 keys: K rows g and g + 8 (16-byte pieces that are A fragments as they come)
-    // and the four V rows this thread contracts over.
-    uint4 tka[KJ], tkb[KJ], vv[VC][4];
-    auto tile_loads = [&](uint32_t kt) {
-        const uint32_t last = k_end - 1;
-        const __half* ka_p = Kb + (size_t)min(kt + g, last) * D + 8 * t;
-        const __half* kb_p = Kb + (size_t)min(kt + g + 8, last) * D + 8 * t;
-#pragma unroll
-        for (int j = 0; j < KJ; ++j) {
-            tka[j] = *reinterpret_cast<const uint4*>(ka_p + 32 * j);
-            tkb[j] = *reinterpret_cast<const uint4*>(kb_p + 32 * j);
-        }
-        // V rows: k-slots 2t, 2t+1, 2t+8, 2t+9 of the tile
-        const uint32_t kv[4] = {min(kt + 2 * t, last), min(kt + 2 * t + 1, last), min(kt + 2 * t + 8, last), min(kt + 2 * t + 9, last)};
-#pragma unroll
-        for (int c = 0; c < VC; ++c)
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-                vv[c][kk] = *reinterpret_cast<const uint4*>(Vb + (size_t)kv[kk] * D + 64 * c + 8 * g);
-    };
-    // The first tile of every warp is requested before the RoPE prologue, whose own round trips
-    // it then overlaps, unless it holds the new token's row, which this CTA is about to write.
+    // One tile = 16 keys.  Its K half (rows g and g + 8: 16-byte pieces that are A fragments as
+    // they come) and its V half (the four rows this thread contracts over) are one ring unit
+    // each: D / 16 pieces of 16 bytes per thread, copied with cp.async into this warp's ring of
+    // NU units and read back by the thread that copied them, so a unit needs no barrier, only
+    // this thread's cp.async group count.  NU - 1 units are in flight while one is consumed.
+    constexpr int CH = D / 16;  // 16-byte pieces per thread and unit
+    unsigned char* ring = reinterpret_cast<unsigned char*>(smem_f) + (size_t)warp * NU * CH * 512 + lane * 16;
     const uint32_t kt0 = k_begin + warp * 16;
-    const bool preloaded = D <= 128 && kt0 < k_end && (!a.k_new || kt0 + 16 <= seq_len - 1u);
-    if (preloaded) tile_loads(kt0);
+    const uint32_t k_off = (uint32_t)g * D + 8 * t, v_off = (uint32_t)(2 * t) * D + 8 * g;  // this thread's first piece of a full tile
+    auto issue_unit = [&](int u) {  // unit u of this warp: K (even) or V (odd) of its tile u / 2
+        const uint32_t kt = kt0 + (uint32_t)(u >> 1) * (kAttnWarps * 16);
+        if (kt < k_end) {
+            unsigned char* dst = ring + (size_t)(u % NU) * CH * 512;
+            if (kt + 16 <= k_end) {  // a full tile: rows g, g + 8 of K; rows 2t, 2t+1, 2t+8, 2t+9 of V
+                if ((u & 1) == 0) {
+                    const __half* kp = Kb + (size_t)kt * D + k_off;
+#pragma unroll
+                    for (int j = 0; j < KJ; ++j) {
+                        cp_async16(dst + (2 * j) * 512, kp + 32 * j);
+                        cp_async16(dst + (2 * j + 1) * 512, kp + 8 * D + 32 * j);
+                    }
+                } else {
+                    const __half* vp = Vb + (size_t)kt * D + v_off;
+#pragma unroll
+                    for (int c = 0; c < VC; ++c) {
+                        cp_async16(dst + (4 * c + 0) * 512, vp + 64 * c);
+                        cp_async16(dst + (4 * c + 1) * 512, vp + D + 64 * c);
+                        cp_async16(dst + (4 * c + 2) * 512, vp + 8 * D + 64 * c);
+                        cp_async16(dst + (4 * c + 3) * 512, vp + 9 * D + 64 * c);
+                    }
+                }
+            } else {  // the ragged last tile: rows past the end repeat the last key (their scores are masked)
+                const uint32_t last = k_end - 1;
+                if ((u & 1) == 0) {
+                    const __half* ka_p = Kb + (size_t)min(kt + g, last) * D + 8 * t;
+                    const __half* kb_p = Kb + (size_t)min(kt + g + 8, last) * D + 8 * t;
+#pragma unroll
+                    for (int j = 0; j < KJ; ++j) {
+                        cp_async16(dst + (2 * j) * 512, ka_p + 32 * j);
+                        cp_async16(dst + (2 * j + 1) * 512, kb_p + 32 * j);
+                    }
+                } else {
+                    const uint32_t kv[4] = {min(kt + 2 * t, last), min(kt + 2 * t + 1, last), min(kt + 2 * t + 8, last), min(kt + 2 * t + 9, last)};
+#pragma unroll
+                    for (int c = 0; c < VC; ++c)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            cp_async16(dst + (4 * c + kk) * 512, Vb + (size_t)kv[kk] * D + 64 * c + 8 * g);
+                }
+            }
+        }
+        cp_async_commit();  // always: the group count stays uniform past the last tile
+    };
+    // Units are requested before the RoPE prologue, whose own round trips they then overlap,
+    // up to the tile that holds the new token's row, which this CTA is about to write.
+    int issued = 0;
+    for (; issued < NU - 1; ++issued) {
+        const uint32_t kt = kt0 + (uint32_t)(issued >> 1) * (kAttnWarps * 16);
+        if (a.k_new && kt < k_end && kt + 16 > seq_len - 1u) break;
+        issue_unit(issued);
+    }
+    if (early) sync();
+    if (dyn_skip(p.dyn)) {
+        cp_async_wait<0>();  // copies in flight must land before the CTA's shared memory retires
+        return;
+    }
 
     // ── folded RoPE / KV append (apply_rope, rope_kv_cache_update, kv_cache_update of
     // Resources/Shaders/attention.metal:48-209, full-head analytic mode): the new token is key
@@ -89,45 +179,68 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
     int q_pitch = D;
     if (a.k_new) {
         constexpr int HALF = D / 2;
-        float* s_cos = smem_f;
-        float* s_sin = smem_f + HALF;
-        __half* s_q = reinterpret_cast<__half*>(smem_f + 2 * HALF);
+        constexpr int QI = (16 * HALF + kAttnThreads - 1) / kAttnThreads;  // rotated pairs per thread at the largest group (16 heads)
+        __half* s_q = reinterpret_cast<__half*>(smem_f + attn_ring_bytes<D, NU>() / sizeof(float));  // behind the rings, which are already filling
         const uint32_t pos = seq_len - 1u;
-        if (tid < HALF) {
-            if (a.rope_table) {  // cos | sin of this token's position, computed once per token
-                s_cos[tid] = a.rope_table[tid]; s_sin[tid] = a.rope_table[HALF + tid];
-            } else {
-                int d0, d1, c0i, c1i;
-                float c0, s0, c1, s1;
-                rope_indices(a.rope_layout, tid, HALF, D, d0, d1, c0i, c1i);
-                rope_trig(tid, HALF, pos, a.rope_base_log2, 1, nullptr, nullptr, c0i, c1i, c0, s0, c1, s1);
-                s_cos[tid] = c0; s_sin[tid] = s0;
+        const bool owner = k_begin <= pos && pos < k_end && pos < a.capacity && tid < HALF;  // this thread rotates a pair of the new key
+        const __half* kn = a.k_new + ((size_t)b * a.n_kv + kvh) * D;
+        const __half* vn = a.v_new + ((size_t)b * a.n_kv + kvh) * D;
+        // Every global read of the prologue is requested before any of them is used: the cos / sin
+        // pair of each of this thread's query pairs (from the per-token table when there is one),
+        // the query values, and the new key / value pair: one round trip, not three.
+        float qc[QI], qs[QI];
+        __half qx0[QI], qx1[QI];
+        int qd0[QI], qd1[QI], qh[QI];
+#pragma unroll
+        for (int i = 0; i < QI; ++i) {
+            const int idx = tid + kAttnThreads * i;
+            qh[i] = -1;
+            if (idx < ratio * HALF) {
+                const int h = idx / HALF, pr = idx % HALF;
+                int c0i, c1i;
+                rope_indices(a.rope_layout, pr, HALF, D, qd0[i], qd1[i], c0i, c1i);
+                qh[i] = h;
+                if (a.rope_table) { qc[i] = a.rope_table[pr]; qs[i] = a.rope_table[HALF + pr]; }
+                qx0[i] = q_src[h * D + qd0[i]]; qx1[i] = q_src[h * D + qd1[i]];
             }
         }
-        __syncthreads();
-        for (int idx = tid; idx < ratio * HALF; idx += kAttnThreads) {
-            const int h = idx / HALF, pr = idx % HALF;
-            int d0, d1, c0i, c1i;
-            rope_indices(a.rope_layout, pr, HALF, D, d0, d1, c0i, c1i);
-            const float c = s_cos[pr], sn = s_sin[pr];
-            const float x0 = __half2float(q_src[h * D + d0]), x1 = __half2float(q_src[h * D + d1]);
-            s_q[h * D + d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)));
-            s_q[h * D + d1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)));
+        float kc = 0.f, ks = 0.f;
+        __half kx0 = __half(), kx1 = __half();
+        __half2 vpair = __half2();
+        int kd0 = 0, kd1 = 0;
+        if (owner) {
+            int c0i, c1i;
+            rope_indices(a.rope_layout, tid, HALF, D, kd0, kd1, c0i, c1i);
+            if (a.rope_table) { kc = a.rope_table[tid]; ks = a.rope_table[HALF + tid]; }
+            kx0 = kn[kd0]; kx1 = kn[kd1];
+            vpair = reinterpret_cast<const __half2*>(vn)[tid];
         }
-        if (k_begin <= pos && pos < k_end && pos < a.capacity) {
-            const __half* kn = a.k_new + ((size_t)b * a.n_kv + kvh) * D;
-            const __half* vn = a.v_new + ((size_t)b * a.n_kv + kvh) * D;
+        if (!a.rope_table) {  // no table: cos / sin of the position from the base, per pair
+#pragma unroll
+            for (int i = 0; i < QI; ++i)
+                if (qh[i] >= 0) {
+                    float c1, s1;
+                    rope_trig((tid + kAttnThreads * i) % HALF, HALF, pos, a.rope_base_log2, 1, nullptr, nullptr, 0, 0, qc[i], qs[i], c1, s1);
+                }
+            if (owner) {
+                float c1, s1;
+                rope_trig(tid, HALF, pos, a.rope_base_log2, 1, nullptr, nullptr, 0, 0, kc, ks, c1, s1);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < QI; ++i)
+            if (qh[i] >= 0) {
+                const float x0 = __half2float(qx0[i]), x1 = __half2float(qx1[i]);
+                s_q[qh[i] * D + qd0[i]] = __float2half_rn(__fsub_rn(__fmul_rn(x0, qc[i]), __fmul_rn(x1, qs[i])));
+                s_q[qh[i] * D + qd1[i]] = __float2half_rn(__fadd_rn(__fmul_rn(x0, qs[i]), __fmul_rn(x1, qc[i])));
+            }
+        if (owner) {
             __half* kd = const_cast<__half*>(Kb) + (size_t)pos * D;
             __half* vd = const_cast<__half*>(Vb) + (size_t)pos * D;
-            for (int pr = tid; pr < HALF; pr += kAttnThreads) {
-                int d0, d1, c0i, c1i;
-                rope_indices(a.rope_layout, pr, HALF, D, d0, d1, c0i, c1i);
-                const float c = s_cos[pr], sn = s_sin[pr];
-                const float x0 = __half2float(kn[d0]), x1 = __half2float(kn[d1]);
-                kd[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)));
-                kd[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, sn)));
-                reinterpret_cast<__half2*>(vd)[pr] = reinterpret_cast<const __half2*>(vn)[pr];
-            }
+            const float x0 = __half2float(kx0), x1 = __half2float(kx1);
+            kd[kd0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, kc), __fmul_rn(x1, ks)));
+            kd[kd1] = __float2half_rn(__fadd_rn(__fmul_rn(x1, kc), __fmul_rn(x0, ks)));
+            reinterpret_cast<__half2*>(vd)[tid] = vpair;
             __threadfence_block();
         }
         __syncthreads();  // rotated q and the new cache rows are visible to the whole CTA
@@ -151,7 +264,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
             for (int j = 0; j < D / 8; ++j) qf[nh][j] = 0u;
         }
     }
-    if (a.k_new) __syncthreads();  // the rotated q lives where the warps later exchange their states
+    for (; issued < NU - 1; ++issued) issue_unit(issued);
     const float scale2 = a.scale * 1.4426950408889634f;
 
     float m_run[NH][2], l_run[NH][2], o[NH][MT][4];
@@ -163,10 +276,12 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
         for (int i = 0; i < MT; ++i) o[nh][i][0] = o[nh][i][1] = o[nh][i][2] = o[nh][i][3] = 0.f;
     }
 
-    for (uint32_t kt = k_begin + warp * 16; kt < k_end; kt += kAttnWarps * 16) {
+    int unit = 0;
+    for (uint32_t kt = kt0; kt < k_end; kt += kAttnWarps * 16, unit += 2) {
         const bool valid_a = kt + g < k_end, valid_b = kt + g + 8 < k_end;
-        // every load of the tile is issued before any arithmetic: one memory round trip per tile
-        if (!(preloaded && kt == kt0)) tile_loads(kt);
+        issue_unit(unit + NU - 1);
+        cp_async_wait<NU - 1>();  // this thread's pieces of the K unit have landed
+        const unsigned char* ku = ring + (size_t)(unit % NU) * CH * 512;
 
         // ── S^T = K · Q^T ──
         float s[NH][4];
@@ -174,7 +289,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
         for (int nh = 0; nh < NH; ++nh) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
 #pragma unroll
         for (int j = 0; j < KJ; ++j) {
-            const uint4 ka = tka[j], kb = tkb[j];
+            const uint4 ka = *reinterpret_cast<const uint4*>(ku + (2 * j) * 512), kb = *reinterpret_cast<const uint4*>(ku + (2 * j + 1) * 512);
 #pragma unroll
             for (int nh = 0; nh < NH; ++nh) {
                 mma16816(s[nh], ka.x, kb.x, ka.y, kb.y, qf[nh][4 * j + 0], qf[nh][4 * j + 1]);
@@ -217,12 +332,17 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
         }
 
         // ── O^T += V^T · P^T ──
+        issue_unit(unit + NU);
+        cp_async_wait<NU - 1>();  // the V unit has landed
+        const unsigned char* vu = ring + (size_t)((unit + 1) % NU) * CH * 512;
 #pragma unroll
         for (int c = 0; c < VC; ++c) {
-            const uint32_t r0[4] = {vv[c][0].x, vv[c][0].y, vv[c][0].z, vv[c][0].w};
-            const uint32_t r1[4] = {vv[c][1].x, vv[c][1].y, vv[c][1].z, vv[c][1].w};
-            const uint32_t r2[4] = {vv[c][2].x, vv[c][2].y, vv[c][2].z, vv[c][2].w};
-            const uint32_t r3[4] = {vv[c][3].x, vv[c][3].y, vv[c][3].z, vv[c][3].w};
+            const uint4 v0 = *reinterpret_cast<const uint4*>(vu + (4 * c + 0) * 512), v1 = *reinterpret_cast<const uint4*>(vu + (4 * c + 1) * 512);
+            const uint4 v2 = *reinterpret_cast<const uint4*>(vu + (4 * c + 2) * 512), v3 = *reinterpret_cast<const uint4*>(vu + (4 * c + 3) * 512);
+            const uint32_t r0[4] = {v0.x, v0.y, v0.z, v0.w};
+            const uint32_t r1[4] = {v1.x, v1.y, v1.z, v1.w};
+            const uint32_t r2[4] = {v2.x, v2.y, v2.z, v2.w};
+            const uint32_t r3[4] = {v3.x, v3.y, v3.z, v3.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const uint32_t a0 = __byte_perm(r0[e], r1[e], 0x5410), a1 = __byte_perm(r0[e], r1[e], 0x7632);
@@ -245,7 +365,9 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
             l_run[nh][1] += __shfl_xor_sync(0xffffffffu, l_run[nh][1], off);
         }
 
-    // ── merge the four warps through shared memory ──
+    // ── merge the warps through shared memory, which the rings no longer need ──
+    cp_async_wait<0>();
+    __syncthreads();
     constexpr int HN = NH * 8;
     float* s_o = smem_f;                                  // [warps][HN][D]
     float* s_ml = smem_f + kAttnWarps * HN * D;           // [warps][HN][2]
@@ -327,15 +449,28 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
         const int hi = min(items, (split + 1) * per_rank);
         for (int idx = split * per_rank + tid; idx < hi; idx += kAttnThreads) {
             const int h = idx / D, d = idx % D;
-            float mstar = kNegBig;
-            for (int s2 = 0; s2 < p.nsplits; ++s2) mstar = fmaxf(mstar, cluster.map_shared_rank(c_o, s2)[16 * D + 2 * h]);
-            float acc = 0.f, lsum = 0.f;
-            for (int s2 = 0; s2 < p.nsplits; ++s2) {
-                const float* rc = cluster.map_shared_rank(c_o, s2);
-                const float f = exp2f(rc[16 * D + 2 * h] - mstar);
-                acc += rc[idx] * f;
-                lsum += rc[16 * D + 2 * h + 1] * f;
+            // every rank's (max, sum, O) is requested before any is used: one trip through the
+            // cluster's shared memory, not one per rank
+            float rm[8], rl[8], ro[8];
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2) {
+                rm[s2] = kNegBig; rl[s2] = 0.f; ro[s2] = 0.f;
+                if (s2 < p.nsplits) {
+                    const float* rc = cluster.map_shared_rank(c_o, s2);
+                    rm[s2] = rc[16 * D + 2 * h]; rl[s2] = rc[16 * D + 2 * h + 1]; ro[s2] = rc[idx];
+                }
             }
+            float mstar = kNegBig;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2) mstar = fmaxf(mstar, rm[s2]);
+            float acc = 0.f, lsum = 0.f;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2)
+                if (s2 < p.nsplits) {
+                    const float f = exp2f(rm[s2] - mstar);
+                    acc += ro[s2] * f;
+                    lsum += rl[s2] * f;
+                }
             a.out[((size_t)b * a.n_q + (size_t)kvh * ratio + h) * D + d] = __float2half_rn(acc / lsum);
         }
         cluster.sync();  // nobody leaves while a peer still reads its shared memory
@@ -354,24 +489,16 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
     if (*s_ticket != p.nsplits - 1) return;
     if (tid == 0) *counter = 0;
     __threadfence();
-    for (int idx = tid; idx < ratio * D; idx += kAttnThreads) {
-        const int h = idx / D, d = idx % D;
-        const size_t qh = (size_t)b * a.n_q + (size_t)kvh * ratio + h;
-        float mstar = kNegBig;
-        for (int s2 = 0; s2 < p.nsplits; ++s2) mstar = fmaxf(mstar, __ldcg(p.part_ml + (qh * p.nsplits + s2) * 2));
-        float acc = 0.f, lsum = 0.f;
-        for (int s2 = 0; s2 < p.nsplits; ++s2) {
-            const float f = exp2f(__ldcg(p.part_ml + (qh * p.nsplits + s2) * 2) - mstar);
-            acc += __ldcg(p.part_o + (qh * p.nsplits + s2) * D + d) * f;
-            lsum += __ldcg(p.part_ml + (qh * p.nsplits + s2) * 2 + 1) * f;
-        }
-        a.out[qh * D + d] = __float2half_rn(acc / lsum);
-    }
+    merge_partials<D>(p, smem_f + 4, (size_t)b * a.n_q + (size_t)kvh * ratio, ratio, tid, kAttnThreads);  // + 4: clear of the ticket word
 }
 
-template <int D, int NH>
+// The rings plus the RoPE prologue's scratch (up to 16 rotated query heads) during
+// the key loop; the warps' and the cluster's merge areas afterwards, in the same bytes.
+template <int D, int NH, int NU>
 __host__ __device__ constexpr size_t attn_smem_bytes() {
-    return ((size_t)kAttnWarps * NH * 8 + 16) * (D + 2) * sizeof(float);
+    const size_t loop = attn_ring_bytes<D, NU>() + (size_t)16 * D * sizeof(__half);
+    const size_t merge = ((size_t)kAttnWarps * NH * 8 + 16) * (D + 2) * sizeof(float);
+    return loop > merge ? loop : merge;
 }
 
 }  // namespace attn

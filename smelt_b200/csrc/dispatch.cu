@@ -392,6 +392,9 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
                     in.launches += 1;
                 }
                 a.rope_table = ctx->rope_table;
+                // a decode table appends one row per token to this cache and nothing else writes it:
+                // the rows of earlier tokens are final before this token's first launch
+                a.kv_rows_stable = 1;
             }
             NEED_BYTES(11, (size_t)a.batch * nkv * d * 2); NEED_BYTES(12, (size_t)a.batch * nkv * d * 2);
         }

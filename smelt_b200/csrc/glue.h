@@ -46,6 +46,11 @@ struct AttnArgs {
     int rope_layout;        // 0 adjacent pairs, 1 split-half
     float rope_base_log2;
     const float* rope_table;  // optional: cos[half] | sin[half] of the position (launch_rope_table)
+    // 1 (with k_new): every cache row below seq_len - 1 was written before the launch sequence of
+    // this token began (tokens never overlap: a token's graph launch, or its eager step, starts
+    // after the previous one has completed), so the kernel requests those rows before it waits
+    // for the launch in front of it.
+    int kv_rows_stable;
     // mlx_partials != null (batch 1): the launch is the first half of the reference's two-pass
     // pair; every split writes its state as one of the 128 key blocks of the reference's
     // buffers (fp16 partials [n_q, 128, head_dim], fp32 stats [2][n_q][128]) and nothing merges.

@@ -42,7 +42,7 @@ class Bench:
         self.ctx = capi.Context(0)
         self.reps = reps
         self.quiet = quiet  # collect rows without printing them
-        self.only = only  # substring of "<mode> <rows>x<cols> b<batch>": run only the affine cases it matches
+        self.only = only  # substring of a case label: run only the affine / attention cases it matches
         self.peak, self.peak_kind = measured_peak()
         self.rows: list[dict] = []
 
@@ -50,7 +50,7 @@ class Bench:
         """n device copies of each host array (same content, distinct addresses)."""
         return [[self.ctx.to_device(a) for a in arrays] for _ in range(n)]
 
-    def run(self, config: str, kernel: str, shape: str, batch: int, alg_bytes: float, launches: int, enqueue):
+    def run(self, config: str, kernel: str, shape: str, batch: int, alg_bytes: float, launches: int, enqueue, flops: float = 0.0):
         ctx = self.ctx
         enqueue()  # eager once: validates arguments, sets kernel attributes
         ctx.synchronize()
@@ -65,6 +65,8 @@ class Bench:
                "us_per_launch": round(us, 3), "achieved_gbs": round(gbs, 1), "frac_of_peak": round(gbs / self.peak, 4),
                "peak_gbs": self.peak, "peak_kind": self.peak_kind, "frac_of_8tbs": round(gbs / 8000.0, 4),
                "launches_timed": launches * self.reps, "distinct_operand_sets": launches}
+        if flops:  # multiply-adds x 2 of the contraction: what the tensor pipe is asked for at large batch
+            row["tflops"] = round(flops / (us * 1e-6) / 1e12, 2)
         self.rows.append(row)
         if not self.quiet:
             print(json.dumps(row), flush=True)
@@ -92,7 +94,7 @@ class Bench:
                 else:
                     ctx.call("affine_dual_matvec", *s, x, y, y2, rows, cols, G, batch)
         name = {"matvec": "affine_matvec", "add": "fused_affine_matvec_add", "gate_up": "fused_affine_gate_up_swiglu", "dual": "fused_dual_affine_matvec"}[mode]
-        self.run(config, name, f"{rows}x{cols}" + (" x2" if nmat == 2 else ""), batch, alg, n, enqueue)
+        self.run(config, name, f"{rows}x{cols}" + (" x2" if nmat == 2 else ""), batch, alg, n, enqueue, flops=2.0 * nmat * rows * cols * batch)
         for s in sets:
             for b in s:
                 b.free()
@@ -147,6 +149,8 @@ class Bench:
     # ── attention ──
     def attention(self, config, n_q, n_kv, d, ctx_len, batch):
         ctx = self.ctx
+        if self.only and self.only not in f"attention {n_q}x{n_kv}x{d} ctx{ctx_len} b{batch}":
+            return
         cap = ctx_len
         kv_bytes = 2 * n_kv * d * 2 * ctx_len * batch
         alg = kv_bytes + 2 * n_q * d * 2 * batch
@@ -184,14 +188,14 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--markdown", action="store_true", help="print a markdown table after the JSON lines")
     ap.add_argument("--quick", action="store_true", help="fewer attention cases")
-    ap.add_argument("--only", default="", help='with --configs 4: only the affine cases whose "<mode> <rows>x<cols> b<batch>" contains this (small runs for profiler captures)')
+    ap.add_argument("--only", default="", help='only the affine cases whose "<mode> <rows>x<cols> b<batch>" and the attention cases whose "attention <n_q>x<n_kv>x<d> ctx<len> b<batch>" contain this (small runs for profiler captures)')
     args = ap.parse_args()
     want = {c.strip() for c in args.configs.split(",")}
     b = Bench(args.reps, args.only)
     if "0" in want:
         b.affine("config0", 4096, 1024, 1)
     if "1" in want:
-        for batch in (1, 4, 8, 16):
+        for batch in (1, 4, 8, 16, 32, 64):  # 17 rows and more run on the tcgen05 QMM
             b.layer_set("config1", 2048, 6144, 16, 4, 128, batch)
     if "2" in want:
         for fmt in (1, 2):
@@ -210,6 +214,10 @@ def main():
         b.affine("config4", 1024, 4096, 1, "dual")
         b.affine("config4", 12288, 4096, 8, "gate_up")
         b.affine("config4", 4096, 12288, 8, "add")
+        for batch in (64, 512):  # tcgen05 QMM (prompt chunks, large decode batches)
+            b.affine("config4", 12288, 4096, batch, "gate_up")
+            b.affine("config4", 4096, 12288, batch, "add")
+            b.affine("config4", 4096, 4096, batch, "matvec")
         if not args.only:
             b.lm_head("config4", 151936, 4096)
     if args.markdown:
