@@ -701,15 +701,23 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
     }
 }
 
-smelt_status interpret(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n, bool device_pos, uint32_t position) {
+// full_first: the first record's launches take a full dependency on the work in front of them
+// instead of a programmatic one (a token inside a multi-token graph starts only when the token
+// before it has completed, as a separate graph launch would).
+smelt_status interpret(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n, bool device_pos, uint32_t position, bool full_first = false) {
     Interp in;
     in.ctx = ctx; in.device_pos = device_pos; in.position = position;
     in.cur = ctx->cfg.cur_slot; in.alt = ctx->cfg.alt_slot;
+    bool first = true;
     for (size_t i = 0; i < n; ++i) {
         const smelt_dispatch_record& rec = table[i];
         if (rec.op_kind == SMELT_OP_SWAP) { int t = in.cur; in.cur = in.alt; in.alt = t; continue; }
         if (rec.op_kind != SMELT_OP_DISPATCH) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record " + std::to_string(i) + ": unknown op kind");
+        const bool pdl = ctx->pdl;
+        if (first && full_first) ctx->pdl = false;
         smelt_status s = run_record(in, rec);
+        ctx->pdl = pdl;
+        first = false;
         if (s) { ctx->err = "record " + std::to_string(i) + ": " + ctx->err; return s; }
     }
     ctx->launch_count = in.launches;
@@ -827,13 +835,47 @@ smelt_status smelt_cuda_decode_step(smelt_cuda_ctx* ctx, const smelt_dispatch_re
     return SMELT_OK;
 }
 
+// Captures n_tokens decode steps (the table, then the advance kernel, per token) into one graph.
+static smelt_status capture_tokens(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records, int n_tokens,
+                                   cudaGraph_t* graph, cudaGraphExec_t* exec) {
+    const uint32_t B = ctx->cfg.batch;
+    Slot& as = ctx->slots[ctx->cfg.argmax_slot];
+    Slot& ts = ctx->slots[ctx->cfg.token_id_slot];
+    Slot& ps = ctx->slots[ctx->cfg.position_slot];
+    smelt_status s = check_cuda(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    if (s) return s;
+    ctx->capturing = true;
+    size_t launches = 0;
+    for (int t = 0; t < n_tokens && !s; ++t) {
+        s = interpret(ctx, table, n_records, true, 0, t > 0);
+        if (s) break;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = ctx->pdl ? 1 : 0;
+        prefer_max_shared(advance_kernel);
+        s = check_cuda(ctx, cudaLaunchKernelEx(&cfg, advance_kernel, (const int32_t*)as.ptr, (int32_t*)ts.ptr, (int32_t*)ps.ptr, ctx->dyn_dev, ctx->gen_ring, ctx->gen_count, ctx->gen_capacity, (int)B), "advance kernel");
+        ctx->launch_count += 1;
+        launches = ctx->launch_count;
+    }
+    ctx->launch_count = launches;  // launches of one token
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    if (s) { if (g) cudaGraphDestroy(g); return s; }
+    s = check_cuda(ctx, e, "cudaStreamEndCapture");
+    if (s) return s;
+    *graph = g;
+    return check_cuda(ctx, cudaGraphInstantiate(exec, g, 0), "cudaGraphInstantiate");
+}
+
 smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records) {
     if (!ctx || !table) return SMELT_ERR_BAD_ARGUMENT;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
     if (!ctx->configured) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "context is not configured");
-    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; }
-    if (ctx->graph) { cudaGraphDestroy(ctx->graph); ctx->graph = nullptr; }
-    const uint32_t B = ctx->cfg.batch;
+    destroy_decode_graphs(ctx);
     if (!ctx->gen_ring) {
         ctx->gen_capacity = 65536;
         if (cudaMalloc(&ctx->gen_ring, (size_t)ctx->gen_capacity * 64 * 4) != cudaSuccess || cudaMalloc(&ctx->gen_count, 4) != cudaSuccess)
@@ -846,30 +888,14 @@ smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_re
     if (!as.ptr || !ts.ptr || !ps.ptr) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "graph: argmax / token / position slots are not allocated");
     smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "graph: pre-capture sync");
     if (s) return s;
-    s = check_cuda(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
-    if (s) return s;
-    ctx->capturing = true;
-    s = interpret(ctx, table, n_records, true, 0);
-    if (!s) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.stream = ctx->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = ctx->pdl ? 1 : 0;
-        prefer_max_shared(advance_kernel);
-        s = check_cuda(ctx, cudaLaunchKernelEx(&cfg, advance_kernel, (const int32_t*)as.ptr, (int32_t*)ts.ptr, (int32_t*)ps.ptr, ctx->dyn_dev, ctx->gen_ring, ctx->gen_count, ctx->gen_capacity, (int)B), "advance kernel");
-        ctx->launch_count += 1;
-    }
-    ctx->capturing = false;
-    cudaGraph_t g = nullptr;
-    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
-    if (s) { if (g) cudaGraphDestroy(g); return s; }
-    s = check_cuda(ctx, e, "cudaStreamEndCapture");
-    if (s) return s;
-    ctx->graph = g;
     ctx->graph_pos_known = false;
-    return check_cuda(ctx, cudaGraphInstantiate(&ctx->graph_exec, g, 0), "cudaGraphInstantiate");
+    // One graph of a single token, and one of kGraphBurst tokens that smelt_cuda_graph_decode uses
+    // for runs of that many steps: fewer graph launches, each of which costs the GPU a gap.
+    s = capture_tokens(ctx, table, n_records, 1, &ctx->graph, &ctx->graph_exec);
+    if (s) return s;
+    s = capture_tokens(ctx, table, n_records, kGraphBurst, &ctx->graph_burst, &ctx->graph_burst_exec);
+    if (s) destroy_decode_graphs(ctx);
+    return s;
 }
 
 smelt_status smelt_cuda_graph_seed(smelt_cuda_ctx* ctx, const int32_t* tokens, int32_t position) {
@@ -899,9 +925,11 @@ smelt_status smelt_cuda_graph_decode(smelt_cuda_ctx* ctx, int n_steps, int32_t* 
     ctx->graph_next_pos += (uint32_t)n_steps;
     if (out_tokens) cudaMemsetAsync(ctx->gen_count, 0, 4, ctx->stream);
     if (out_tokens && (uint32_t)n_steps > ctx->gen_capacity) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "graph decode: too many steps for one readback");
-    for (int i = 0; i < n_steps; ++i) {
-        smelt_status s = check_cuda(ctx, cudaGraphLaunch(ctx->graph_exec, ctx->stream), "cudaGraphLaunch");
+    for (int i = 0; i < n_steps;) {
+        const bool burst = ctx->graph_burst_exec && n_steps - i >= kGraphBurst;
+        smelt_status s = check_cuda(ctx, cudaGraphLaunch(burst ? ctx->graph_burst_exec : ctx->graph_exec, ctx->stream), "cudaGraphLaunch");
         if (s) return s;
+        i += burst ? kGraphBurst : 1;
     }
     if (!out_tokens) return SMELT_OK;
     smelt_status s = check_cuda(ctx, cudaMemcpyAsync(out_tokens, ctx->gen_ring, (size_t)n_steps * B * 4, cudaMemcpyDeviceToHost, ctx->stream), "graph readback");

@@ -516,7 +516,10 @@ cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x
         const int nb = batch - b0 < 8 ? batch - b0 : 8;
         const size_t smem = (size_t)nb * cols * 2;
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
-        int grid = sm_count * 4;
+        // As many CTAs as can be resident at once (eight of 256 threads per SM), no fewer: a smaller
+        // grid launched programmatically behind a kernel that still holds most SMs piles up to
+        // eight CTAs on each of the few SMs that are free and leaves the others without work.
+        int grid = sm_count * 8;
         if (grid > (rows + 7) / 8) grid = (rows + 7) / 8;
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];

@@ -44,6 +44,15 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
         if (_e != cudaSuccess) return check_cuda(ctx, _e, "cudaSetDevice"); \
     }
 
+void smelt::destroy_decode_graphs(smelt_cuda_ctx* ctx) {
+    if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
+    if (ctx->graph) cudaGraphDestroy(ctx->graph);
+    if (ctx->graph_burst_exec) cudaGraphExecDestroy(ctx->graph_burst_exec);
+    if (ctx->graph_burst) cudaGraphDestroy(ctx->graph_burst);
+    ctx->graph_exec = ctx->graph_burst_exec = nullptr;
+    ctx->graph = ctx->graph_burst = nullptr;
+}
+
 extern "C" {
 
 smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
@@ -98,10 +107,7 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     ctx->user_graph_exec = nullptr;
     // Graphs first: a communicator waits for every graph that captured one of its collectives
     // to be released before ncclCommDestroy returns.
-    if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
-    if (ctx->graph) cudaGraphDestroy(ctx->graph);
-    ctx->graph_exec = nullptr;
-    ctx->graph = nullptr;
+    destroy_decode_graphs(ctx);
     tp_destroy(ctx);
     package_destroy(ctx);
     for (auto& s : ctx->slots)
@@ -243,8 +249,7 @@ static smelt_status drop_graphs_for_slot_change(smelt_cuda_ctx* ctx, const char*
     if (!ctx->graph_exec && !ctx->graph && !ctx->user_graph_exec) return SMELT_OK;
     smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), what);
     if (ctx->user_graph_exec) { cudaGraphExecDestroy(ctx->user_graph_exec); ctx->user_graph_exec = nullptr; }
-    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; }
-    if (ctx->graph) { cudaGraphDestroy(ctx->graph); ctx->graph = nullptr; }
+    destroy_decode_graphs(ctx);
     return s;
 }
 

@@ -96,6 +96,8 @@ struct smelt_cuda_ctx {
     // graph replay
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
+    cudaGraph_t graph_burst = nullptr;            // kGraphBurst tokens per launch
+    cudaGraphExec_t graph_burst_exec = nullptr;
     cudaGraphExec_t user_graph_exec = nullptr;  // smelt_cuda_capture_begin / _end / _replay
     int32_t* gen_ring = nullptr;   // device: generated ids, step-major
     uint32_t* gen_count = nullptr; // device: steps written
@@ -114,6 +116,8 @@ struct smelt_cuda_ctx {
 };
 
 namespace smelt {
+constexpr int kGraphBurst = 8;  // tokens per launch of the multi-token decode graph
+void destroy_decode_graphs(smelt_cuda_ctx* ctx);  // the single-token and the multi-token graph
 smelt_status fail(smelt_cuda_ctx* ctx, smelt_status code, const std::string& msg);
 smelt_status check_cuda(smelt_cuda_ctx* ctx, cudaError_t e, const char* what);
 smelt_status tp_all_reduce_f16(smelt_cuda_ctx* ctx, void* data, size_t count, cudaStream_t stream);
