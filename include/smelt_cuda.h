@@ -468,6 +468,46 @@ SMELT_CUDA_API smelt_status smelt_cuda_affine_embedding_gather(smelt_cuda_ctx* c
 SMELT_CUDA_API smelt_status smelt_cuda_argmax_f16(smelt_cuda_ctx* ctx, const void* logits_dev, void* out_dev, int vocab,
                                                   int batch);
 
+/* ── prompt-state snapshots ──────────────────────────────────────────────────
+ * SmeltRuntime.captureDevicePromptSnapshot / restoreDevicePromptSnapshot
+ * (Sources/SmeltRuntime/SmeltRuntime.swift:1385-1553) and the host form with a partial restore,
+ * capturePromptSnapshot / restorePromptSnapshot(_:length:) (:1254-1383).  A KV-cache slot is laid
+ * out [rows, capacity, head_dim] fp16 (rows = KV heads x sequences): the snapshot keeps the first
+ * captured_length positions of every row compactly in a private device buffer; state slots
+ * (recurrent / convolutional state) are copied whole.  Restore writes the first
+ * min(length, captured, destination capacity) positions of every row at the destination's own
+ * stride, derived from the slot's current size as the reference derives it, so the cache may have
+ * been grown in between (grow it first, smelt_cuda_resize_kv_slot, when the whole prefix is
+ * wanted).  length < captured_length is refused (SMELT_ERR_UNSUPPORTED) when the snapshot holds
+ * state slots, which have no positions to rewind to (:1338-1345); length > captured_length is
+ * SMELT_ERR_OUT_OF_RANGE (:1333-1337).  Slots that do not exist are skipped on both sides.  The
+ * caller seeds position and token afterwards (smelt_cuda_graph_seed / decode_step) from
+ * prompt_length / next_token, which the snapshot only carries. */
+typedef struct smelt_cuda_snapshot smelt_cuda_snapshot;
+typedef struct {
+    int32_t slot;
+    int32_t rows;      /* KV heads x sequences */
+    int32_t head_dim;  /* a multiple of 8 */
+} smelt_cuda_kv_slot;
+typedef struct {
+    uint32_t captured_length, prompt_length;
+    int32_t next_token;
+    uint32_t n_slots;
+    uint64_t byte_count;  /* payload bytes held (SmeltPromptSnapshot.byteCount) */
+    uint64_t blob_bytes;  /* size smelt_cuda_snapshot_export needs */
+} smelt_cuda_snapshot_info_t;
+SMELT_CUDA_API smelt_status smelt_cuda_snapshot_capture(smelt_cuda_ctx* ctx, const smelt_cuda_kv_slot* kv_slots, int n_kv,
+                                                        const int32_t* state_slots, int n_state, uint32_t captured_length,
+                                                        uint32_t prompt_length, int32_t next_token,
+                                                        smelt_cuda_snapshot** out);
+SMELT_CUDA_API smelt_status smelt_cuda_snapshot_restore(smelt_cuda_ctx* ctx, const smelt_cuda_snapshot* snap, uint32_t length);
+SMELT_CUDA_API smelt_status smelt_cuda_snapshot_info(const smelt_cuda_snapshot* snap, smelt_cuda_snapshot_info_t* out);
+/* Host form (the serialisable SmeltPromptSnapshot): a self-describing blob of this library's own
+ * layout (header, one record per slot, then the payloads), importable on any context. */
+SMELT_CUDA_API smelt_status smelt_cuda_snapshot_export(smelt_cuda_ctx* ctx, const smelt_cuda_snapshot* snap, void* dst, size_t dst_bytes);
+SMELT_CUDA_API smelt_status smelt_cuda_snapshot_import(smelt_cuda_ctx* ctx, const void* src, size_t src_bytes, smelt_cuda_snapshot** out);
+SMELT_CUDA_API void smelt_cuda_snapshot_destroy(smelt_cuda_snapshot* snap);
+
 #ifdef __cplusplus
 }
 #endif

@@ -94,6 +94,15 @@ class PackageInfo(C.Structure):
                 ("argmax_slot", C.c_int32), ("logits_slot", C.c_int32), ("weights_bytes", C.c_uint64)]
 
 
+class KvSlot(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("rows", C.c_int32), ("head_dim", C.c_int32)]
+
+
+class SnapshotInfo(C.Structure):
+    _fields_ = [("captured_length", C.c_uint32), ("prompt_length", C.c_uint32), ("next_token", C.c_int32), ("n_slots", C.c_uint32),
+                ("byte_count", C.c_uint64), ("blob_bytes", C.c_uint64)]
+
+
 def _declarations() -> dict[str, list[str]]:
     """name -> parameter type strings, parsed from ``smelt_cuda.h``."""
     with open(HEADER_PATH) as f:

@@ -131,6 +131,8 @@ class Bench:
     # ── binary / ternary ──
     def signed(self, config, fmt, rows, cols, batch=1):
         ctx = self.ctx
+        if self.only and self.only not in f"signed fmt{fmt} {rows}x{cols} b{batch}":
+            return
         maker, bpw, name = (synth.binary1, 1 / 8, "signed_binary_matvec_g128") if fmt == 1 else (synth.ternary2, 2 / 8, "signed_ternary_matvec_g128")
         alg = rows * cols * (bpw + 2 / 128) + batch * cols * 2 + batch * rows * 2
         n = copies_for(alg)
@@ -188,7 +190,7 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--markdown", action="store_true", help="print a markdown table after the JSON lines")
     ap.add_argument("--quick", action="store_true", help="fewer attention cases")
-    ap.add_argument("--only", default="", help='only the affine cases whose "<mode> <rows>x<cols> b<batch>" and the attention cases whose "attention <n_q>x<n_kv>x<d> ctx<len> b<batch>" contain this (small runs for profiler captures)')
+    ap.add_argument("--only", default="", help='only the affine cases whose "<mode> <rows>x<cols> b<batch>" the attention cases whose "attention <n_q>x<n_kv>x<d> ctx<len> b<batch>" and the low-bit cases whose "signed fmt<1|2> <rows>x<cols> b<batch>" contain this (small runs for profiler captures)')
     args = ap.parse_args()
     want = {c.strip() for c in args.configs.split(",")}
     b = Bench(args.reps, args.only)

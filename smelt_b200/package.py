@@ -209,6 +209,26 @@ class Decoder:
         for l in range(2 * self.desc.layers):
             self.ctx.call("zero_slot", KV_BASE_SLOT + l)
 
+    # ── prompt-state snapshots (SmeltRuntime.captureDevicePromptSnapshot / restore…, SmeltRuntime.swift:1385-1553) ──
+    def kv_slots(self):
+        """The K and V cache slots of every layer as ``smelt_cuda_kv_slot`` records."""
+        rows = (self.desc.n_kv // max(1, self.desc.tp_world)) * self.batch
+        n = 2 * self.desc.layers
+        arr = (capi.KvSlot * n)()
+        for l in range(n):
+            arr[l] = capi.KvSlot(KV_BASE_SLOT + l, rows, self.desc.head_dim)
+        return arr
+
+    def capture_snapshot(self, captured_length: int, prompt_length: int = 0, next_token: int = 0) -> "Snapshot":
+        kv = self.kv_slots()
+        h = C.c_void_p()
+        self.ctx._check(self.ctx.lib.smelt_cuda_snapshot_capture(self.ctx.h, kv, len(kv), None, 0, int(captured_length), int(prompt_length),
+                                                                 int(next_token), C.byref(h)))
+        return Snapshot(self.ctx, h)
+
+    def restore_snapshot(self, snap: "Snapshot", length: int | None = None):
+        self.ctx._check(self.ctx.lib.smelt_cuda_snapshot_restore(self.ctx.h, snap.h, snap.info().captured_length if length is None else int(length)))
+
     def teacher_forced(self, prompt, teacher, use_graph: bool = True) -> np.ndarray:
         """Scores a given continuation: feeds the prompt, then ``teacher[i - 1]`` at decode step i
         whatever the model itself chose, and returns the argmax of every step, shape
@@ -263,6 +283,35 @@ class Decoder:
             if i + 1 < n_decode:
                 cur = self.decode_step(cur, n_prompt + i)
         return out
+
+
+class Snapshot:
+    """Owner of one ``smelt_cuda_snapshot``."""
+
+    def __init__(self, ctx: capi.Context, handle):
+        self.ctx, self.h = ctx, handle
+
+    def info(self) -> capi.SnapshotInfo:
+        out = capi.SnapshotInfo()
+        self.ctx._check(self.ctx.lib.smelt_cuda_snapshot_info(self.h, C.byref(out)))
+        return out
+
+    def export(self) -> np.ndarray:
+        blob = np.zeros(self.info().blob_bytes, np.uint8)
+        self.ctx._check(self.ctx.lib.smelt_cuda_snapshot_export(self.ctx.h, self.h, blob.ctypes.data_as(C.c_void_p), C.c_size_t(blob.nbytes)))
+        return blob
+
+    @classmethod
+    def from_blob(cls, ctx: capi.Context, blob: np.ndarray) -> "Snapshot":
+        blob = np.ascontiguousarray(blob, dtype=np.uint8)
+        h = C.c_void_p()
+        ctx._check(ctx.lib.smelt_cuda_snapshot_import(ctx.h, blob.ctypes.data_as(C.c_void_p), C.c_size_t(blob.nbytes), C.byref(h)))
+        return cls(ctx, h)
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.smelt_cuda_snapshot_destroy(self.h)
+            self.h = None
 
 
 def write_package(path: str, cfg: DecoderConfig, image: np.ndarray, desc: capi.DecoderDesc, layers, capacity: int,
