@@ -300,8 +300,9 @@ SMELT_CUDA_API smelt_status smelt_cuda_tp_all_reduce_f16(smelt_cuda_ctx* ctx, vo
  * per rank: partials are pushed into the peers' buffers over NVLink in 8-byte stores that carry
  * their sequence number (no fence, no separate flag),
  * each rank adds the partials in rank order in fp32, rounds once to fp16 and adds the residual.
- * Waits are bounded; a peer that never arrives sets bit 8 of the device error word
- * (smelt_cuda_device_error).  Without open exchange buffers the record falls back to
+ * Waits are bounded (about a second); a peer that never arrives sets bit 8 of the device error
+ * word (smelt_cuda_device_error), so the ranks must be aligned (a barrier on the host) between
+ * their set-up and the first exchange.  Without open exchange buffers the record falls back to
  * ncclAllReduce followed by elementwise_add. */
 #define SMELT_TP_HANDLE_BYTES 64
 SMELT_CUDA_API smelt_status smelt_cuda_tp_exchange_handle(smelt_cuda_ctx* ctx, uint8_t handle[SMELT_TP_HANDLE_BYTES]);
