@@ -469,6 +469,37 @@ SMELT_CUDA_API smelt_status smelt_cuda_affine_embedding_gather(smelt_cuda_ctx* c
 SMELT_CUDA_API smelt_status smelt_cuda_argmax_f16(smelt_cuda_ctx* ctx, const void* logits_dev, void* out_dev, int vocab,
                                                   int batch);
 
+/* ── prefill ─────────────────────────────────────────────────────────────────
+ * A chunk of prompt positions at once.  rope_kv_prefill = rope_and_kv_cache_prefill
+ * (Resources/Shaders/prefill_rope_kv.metal:64-187): RoPE in place on q [n_pos, q_heads, head_dim]
+ * and k [n_pos, kv_heads, head_dim] at positions start_pos + t (tables [maxSeq, rope_dim] when
+ * math_mode == 0, analytic from base_log2 when 1; layout 0 adjacent pairs, 1 split-half,
+ * 2 proportional split-half), then the rotated keys and v written to cache rows start_pos + t of
+ * [kv_heads, capacity, head_dim].  attention_prefill = attention_prefill
+ * (Resources/Shaders/prefill_attention.metal:14-413): position t attends causally to keys
+ * [seqStart, start_pos + t] (seqStart from sliding_window, 0 = full), out [n_pos, n_q, head_dim]. */
+SMELT_CUDA_API smelt_status smelt_cuda_rope_kv_prefill(smelt_cuda_ctx* ctx, void* q_dev, void* k_dev, const void* v_dev,
+                                                       const void* cos_dev, const void* sin_dev, void* k_cache_dev,
+                                                       void* v_cache_dev, int head_dim, int rope_dim, int q_heads, int kv_heads,
+                                                       uint32_t n_pos, uint32_t start_pos, uint32_t capacity, int layout,
+                                                       float base_log2, int math_mode);
+SMELT_CUDA_API smelt_status smelt_cuda_attention_prefill(smelt_cuda_ctx* ctx, const void* q_dev, const void* k_cache_dev,
+                                                         const void* v_cache_dev, void* out_dev, int n_q, int n_kv, int head_dim,
+                                                         uint32_t n_pos, uint32_t start_pos, uint32_t capacity, float scale,
+                                                         uint32_t sliding_window);
+/* Prompt tokens [start_pos, start_pos + n_tokens) of one sequence through the decoder that
+ * smelt_cuda_build_decoder was given (same descriptor and layer references, batch 1, one GPU),
+ * `chunk` positions at a time (0 = 512): batched projections (tensor-memory QMM from 17 rows),
+ * rope_kv_prefill, attention_prefill; LM head and argmax for the last position only.  Leaves
+ * the KV caches filled, the last logits in the logits slot and *out_token (optional) = the
+ * argmax after the last prompt token, so decoding continues with smelt_cuda_graph_seed /
+ * smelt_cuda_decode_step at position start_pos + n_tokens.  The reference decodes a prompt
+ * token by token when a package has no prefill table (Sources/SmeltRuntime/SmeltModel.swift
+ * :619-631); this is the batched alternative, same arithmetic per position. */
+SMELT_CUDA_API smelt_status smelt_cuda_prefill(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc, const smelt_layer_ref* layers,
+                                               const int32_t* tokens, int n_tokens, int32_t start_pos, int chunk,
+                                               int32_t* out_token);
+
 /* ── prompt-state snapshots ──────────────────────────────────────────────────
  * SmeltRuntime.captureDevicePromptSnapshot / restoreDevicePromptSnapshot
  * (Sources/SmeltRuntime/SmeltRuntime.swift:1385-1553) and the host form with a partial restore,

@@ -75,6 +75,90 @@ __device__ __forceinline__ void key_range(const AttnDev& p, uint32_t& seq_start,
 
 // One (split, KV head, sequence) work item by one CTA of kAttnThreads threads.  Sync is called
 // once by every thread before the first read of q or the caches (see affine_imma.cuh).
+// One 16-key tile, first half: S^T = K . Q^T from the K unit's pieces (ku: piece p of lane l at
+// p * 512 + l * 16, already offset to this lane), then the online softmax of the tile's columns.
+// valid_a / valid_b: this thread's keys g and g + 8 of the tile take part.  Leaves P^T as fp16
+// high and low parts in B-operand layout (pb0, pb1, pl0, pl1) and rescales m_run, l_run, o.
+template <int D, int NH>
+__device__ __forceinline__ void tile_scores_softmax(const unsigned char* ku, const uint32_t (&qf)[NH][D / 8], bool valid_a, bool valid_b,
+                                                    float scale2, float (&m_run)[NH][2], float (&l_run)[NH][2], float (&o)[NH][D / 16][4],
+                                                    uint32_t (&pb0)[NH], uint32_t (&pb1)[NH], uint32_t (&pl0)[NH], uint32_t (&pl1)[NH]) {
+    constexpr int MT = D / 16, KJ = D / 32;
+    // ── S^T = K · Q^T ──
+    float s[NH][4];
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
+#pragma unroll
+    for (int j = 0; j < KJ; ++j) {
+        const uint4 ka = *reinterpret_cast<const uint4*>(ku + (2 * j) * 512), kb = *reinterpret_cast<const uint4*>(ku + (2 * j + 1) * 512);
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+            mma16816(s[nh], ka.x, kb.x, ka.y, kb.y, qf[nh][4 * j + 0], qf[nh][4 * j + 1]);
+            mma16816(s[nh], ka.z, kb.z, ka.w, kb.w, qf[nh][4 * j + 2], qf[nh][4 * j + 3]);
+        }
+    }
+
+    // ── online softmax per query head (columns 2t, 2t+1 of the tile) ──
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+        float v0 = valid_a ? s[nh][0] * scale2 : kNegBig, v1 = valid_a ? s[nh][1] * scale2 : kNegBig;
+        float v2 = valid_b ? s[nh][2] * scale2 : kNegBig, v3 = valid_b ? s[nh][3] * scale2 : kNegBig;
+        float mx0 = fmaxf(v0, v2), mx1 = fmaxf(v1, v3);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float mn0 = fmaxf(m_run[nh][0], mx0), mn1 = fmaxf(m_run[nh][1], mx1);
+        const float c0 = exp2f(m_run[nh][0] - mn0), c1 = exp2f(m_run[nh][1] - mn1);
+        m_run[nh][0] = mn0; m_run[nh][1] = mn1;
+        // p = hi + lo with both halves fp16: the tensor pipe sees 22 significant bits of p
+        const float p0 = valid_a ? exp2f(v0 - mn0) : 0.f, p1 = valid_a ? exp2f(v1 - mn1) : 0.f;
+        const float p2 = valid_b ? exp2f(v2 - mn0) : 0.f, p3 = valid_b ? exp2f(v3 - mn1) : 0.f;
+        const __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
+        const float2 paf = __half22float2(pa), pbf = __half22float2(pb);
+        const __half2 pa_lo = __floats2half2_rn(p0 - paf.x, p1 - paf.y), pb_lo = __floats2half2_rn(p2 - pbf.x, p3 - pbf.y);
+        l_run[nh][0] = l_run[nh][0] * c0 + (p0 + p2);
+        l_run[nh][1] = l_run[nh][1] * c1 + (p1 + p3);
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            o[nh][i][0] *= c0; o[nh][i][2] *= c0;
+            o[nh][i][1] *= c1; o[nh][i][3] *= c1;
+        }
+        pb0[nh] = movmatrix_trans(h2_as_u32(pa));  // {P[key 2t][head g], P[key 2t+1][head g]}
+        pb1[nh] = movmatrix_trans(h2_as_u32(pb));  // keys 2t+8, 2t+9
+        pl0[nh] = movmatrix_trans(h2_as_u32(pa_lo));
+        pl1[nh] = movmatrix_trans(h2_as_u32(pb_lo));
+    }
+
+}
+
+// Second half: O^T += V^T . P^T from the V unit's pieces (vu, same addressing).
+template <int D, int NH>
+__device__ __forceinline__ void tile_weighted_sum(const unsigned char* vu, float (&o)[NH][D / 16][4], const uint32_t (&pb0)[NH],
+                                                  const uint32_t (&pb1)[NH], const uint32_t (&pl0)[NH], const uint32_t (&pl1)[NH]) {
+    constexpr int VC = D / 64;
+#pragma unroll
+    for (int c = 0; c < VC; ++c) {
+        const uint4 v0 = *reinterpret_cast<const uint4*>(vu + (4 * c + 0) * 512), v1 = *reinterpret_cast<const uint4*>(vu + (4 * c + 1) * 512);
+        const uint4 v2 = *reinterpret_cast<const uint4*>(vu + (4 * c + 2) * 512), v3 = *reinterpret_cast<const uint4*>(vu + (4 * c + 3) * 512);
+        const uint32_t r0[4] = {v0.x, v0.y, v0.z, v0.w};
+        const uint32_t r1[4] = {v1.x, v1.y, v1.z, v1.w};
+        const uint32_t r2[4] = {v2.x, v2.y, v2.z, v2.w};
+        const uint32_t r3[4] = {v3.x, v3.y, v3.z, v3.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t a0 = __byte_perm(r0[e], r1[e], 0x5410), a1 = __byte_perm(r0[e], r1[e], 0x7632);
+            const uint32_t a2 = __byte_perm(r2[e], r3[e], 0x5410), a3 = __byte_perm(r2[e], r3[e], 0x7632);
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) {
+                mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pb0[nh], pb1[nh]);
+                mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pl0[nh], pl1[nh]);
+            }
+        }
+    }
+}
+
 template <int D, int NU>
 __host__ __device__ constexpr size_t attn_ring_bytes() {
     return (size_t)kAttnWarps * NU * (D / 16) * 512;
@@ -283,77 +367,14 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
         cp_async_wait<NU - 1>();  // this thread's pieces of the K unit have landed
         const unsigned char* ku = ring + (size_t)(unit % NU) * CH * 512;
 
-        // ── S^T = K · Q^T ──
-        float s[NH][4];
-#pragma unroll
-        for (int nh = 0; nh < NH; ++nh) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
-#pragma unroll
-        for (int j = 0; j < KJ; ++j) {
-            const uint4 ka = *reinterpret_cast<const uint4*>(ku + (2 * j) * 512), kb = *reinterpret_cast<const uint4*>(ku + (2 * j + 1) * 512);
-#pragma unroll
-            for (int nh = 0; nh < NH; ++nh) {
-                mma16816(s[nh], ka.x, kb.x, ka.y, kb.y, qf[nh][4 * j + 0], qf[nh][4 * j + 1]);
-                mma16816(s[nh], ka.z, kb.z, ka.w, kb.w, qf[nh][4 * j + 2], qf[nh][4 * j + 3]);
-            }
-        }
-
-        // ── online softmax per query head (columns 2t, 2t+1 of the tile) ──
         uint32_t pb0[NH], pb1[NH], pl0[NH], pl1[NH];
-#pragma unroll
-        for (int nh = 0; nh < NH; ++nh) {
-            float v0 = valid_a ? s[nh][0] * scale2 : kNegBig, v1 = valid_a ? s[nh][1] * scale2 : kNegBig;
-            float v2 = valid_b ? s[nh][2] * scale2 : kNegBig, v3 = valid_b ? s[nh][3] * scale2 : kNegBig;
-            float mx0 = fmaxf(v0, v2), mx1 = fmaxf(v1, v3);
-#pragma unroll
-            for (int off = 4; off < 32; off <<= 1) {
-                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-            }
-            const float mn0 = fmaxf(m_run[nh][0], mx0), mn1 = fmaxf(m_run[nh][1], mx1);
-            const float c0 = exp2f(m_run[nh][0] - mn0), c1 = exp2f(m_run[nh][1] - mn1);
-            m_run[nh][0] = mn0; m_run[nh][1] = mn1;
-            // p = hi + lo with both halves fp16: the tensor pipe sees 22 significant bits of p
-            const float p0 = valid_a ? exp2f(v0 - mn0) : 0.f, p1 = valid_a ? exp2f(v1 - mn1) : 0.f;
-            const float p2 = valid_b ? exp2f(v2 - mn0) : 0.f, p3 = valid_b ? exp2f(v3 - mn1) : 0.f;
-            const __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
-            const float2 paf = __half22float2(pa), pbf = __half22float2(pb);
-            const __half2 pa_lo = __floats2half2_rn(p0 - paf.x, p1 - paf.y), pb_lo = __floats2half2_rn(p2 - pbf.x, p3 - pbf.y);
-            l_run[nh][0] = l_run[nh][0] * c0 + (p0 + p2);
-            l_run[nh][1] = l_run[nh][1] * c1 + (p1 + p3);
-#pragma unroll
-            for (int i = 0; i < MT; ++i) {
-                o[nh][i][0] *= c0; o[nh][i][2] *= c0;
-                o[nh][i][1] *= c1; o[nh][i][3] *= c1;
-            }
-            pb0[nh] = movmatrix_trans(h2_as_u32(pa));  // {P[key 2t][head g], P[key 2t+1][head g]}
-            pb1[nh] = movmatrix_trans(h2_as_u32(pb));  // keys 2t+8, 2t+9
-            pl0[nh] = movmatrix_trans(h2_as_u32(pa_lo));
-            pl1[nh] = movmatrix_trans(h2_as_u32(pb_lo));
-        }
+        tile_scores_softmax<D, NH>(ku, qf, valid_a, valid_b, scale2, m_run, l_run, o, pb0, pb1, pl0, pl1);
 
         // ── O^T += V^T · P^T ──
         issue_unit(unit + NU);
         cp_async_wait<NU - 1>();  // the V unit has landed
         const unsigned char* vu = ring + (size_t)((unit + 1) % NU) * CH * 512;
-#pragma unroll
-        for (int c = 0; c < VC; ++c) {
-            const uint4 v0 = *reinterpret_cast<const uint4*>(vu + (4 * c + 0) * 512), v1 = *reinterpret_cast<const uint4*>(vu + (4 * c + 1) * 512);
-            const uint4 v2 = *reinterpret_cast<const uint4*>(vu + (4 * c + 2) * 512), v3 = *reinterpret_cast<const uint4*>(vu + (4 * c + 3) * 512);
-            const uint32_t r0[4] = {v0.x, v0.y, v0.z, v0.w};
-            const uint32_t r1[4] = {v1.x, v1.y, v1.z, v1.w};
-            const uint32_t r2[4] = {v2.x, v2.y, v2.z, v2.w};
-            const uint32_t r3[4] = {v3.x, v3.y, v3.z, v3.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t a0 = __byte_perm(r0[e], r1[e], 0x5410), a1 = __byte_perm(r0[e], r1[e], 0x7632);
-                const uint32_t a2 = __byte_perm(r2[e], r3[e], 0x5410), a3 = __byte_perm(r2[e], r3[e], 0x7632);
-#pragma unroll
-                for (int nh = 0; nh < NH; ++nh) {
-                    mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pb0[nh], pb1[nh]);
-                    mma16816(o[nh][4 * c + e], a0, a1, a2, a3, pl0[nh], pl1[nh]);
-                }
-            }
-        }
+        tile_weighted_sum<D, NH>(vu, o, pb0, pb1, pl0, pl1);
     }
 
     // per-thread partial denominators cover keys g, g+8 only: finish the sum over g

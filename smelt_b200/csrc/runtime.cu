@@ -117,6 +117,7 @@ void smelt_cuda_destroy(smelt_cuda_ctx* ctx) {
     cudaFree(ctx->attn_scratch);
     cudaFree(ctx->attn_counters);
     cudaFree(ctx->qmm_scratch);
+    if (ctx->prefill_scratch) cudaFree(ctx->prefill_scratch);
     cudaFree(ctx->qmm_counters);
     cudaFree(ctx->rope_table);
     cudaFree(ctx->argmax_scratch);

@@ -85,6 +85,8 @@ struct smelt_cuda_ctx {
     float* rope_table = nullptr;   // cos | sin of the current position (256 floats), written once per interpretation
     float* qmm_scratch = nullptr;  // tensor-memory QMM: fp32 sums of CTAs that split a row tile's K (affine_qmm.cu)
     size_t qmm_scratch_bytes = 0;
+    void* prefill_scratch = nullptr;  // activations of one prompt chunk (prefill.cu), grown on demand
+    size_t prefill_scratch_bytes = 0;
     int* qmm_counters = nullptr;   // ... and their arrival counters (4096), zero between launches
     int* attn_counters = nullptr;  // one zeroed int per (sequence, KV head): in-kernel merge of attention splits
     uint64_t* argmax_scratch = nullptr;

@@ -205,6 +205,15 @@ class Decoder:
         self.ctx._check(self.ctx.lib.smelt_cuda_graph_decode(self.ctx.h, n_steps, out.ctypes.data_as(C.c_void_p) if read else None))
         return out
 
+    def prefill(self, tokens, start_pos: int = 0, chunk: int = 0) -> int:
+        """Prompt tokens through ``smelt_cuda_prefill`` (batch 1): fills the KV caches for positions
+        ``start_pos ...`` and returns the argmax after the last token."""
+        tokens = np.ascontiguousarray(np.asarray(tokens).reshape(-1), dtype=np.int32)
+        out = C.c_int32(0)
+        self.ctx._check(self.ctx.lib.smelt_cuda_prefill(self.ctx.h, C.byref(self.desc), self.layers, tokens.ctypes.data_as(C.c_void_p), len(tokens),
+                                                        int(start_pos), int(chunk), C.byref(out)))
+        return int(out.value)
+
     def reset_cache(self):
         for l in range(2 * self.desc.layers):
             self.ctx.call("zero_slot", KV_BASE_SLOT + l)

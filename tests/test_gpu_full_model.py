@@ -70,3 +70,30 @@ def test_full_model_batch8_greedy_tokens_match_the_oracle():
     for b, v in enumerate(verdicts):
         print("full model, batch 8, sequence %d: %d of %d steps identical, %d tie breaks" % (b, v["identical"], v["checked"], v["tie_breaks"]))
         assert v["checked"] == gold["n_decode"] and not v["wrong"], (b, v)
+
+
+def test_full_model_prefill_then_greedy_tokens_match_the_oracle():
+    """The 512-token prompt through smelt_cuda_prefill (chunks of 128 positions: tensor-memory QMM,
+    batched RoPE / KV write, chunked causal attention), then the 64 teacher-forced steps."""
+    gold = load("full_model_tokens.json")
+    cfg = package.FULL_MODEL
+    n_prompt, n_dec = gold["prompt_len"], gold["n_decode"]
+    tokens = np.array(gold["tokens"], np.int32)
+    ctx = capi.Context(0)
+    try:
+        pkg = package.SyntheticPackage(cfg, gold["seed"])
+        image, desc, layers = package.build_image(pkg)
+        dec = package.Decoder(ctx, image, desc, layers, n_prompt + n_dec + 8, 1, fuse_residual=3)
+        del image
+        first = dec.prefill(prompts_of(gold, 1)[0], 0, 128)
+        dec.build_graph()
+        got = [first]
+        for i in range(n_dec - 1):
+            dec.graph_seed(tokens[i:i + 1], n_prompt + i)
+            got.append(int(dec.graph_decode(1, read=True)[0, 0]))
+        assert ctx.device_error() == 0
+    finally:
+        ctx.close()
+    v = package.compare_greedy(np.array(got), tokens, np.array(gold["runner_up"]), np.array(gold["top2_margin"]))
+    print("full model, prefill + decode: %d of %d steps identical, %d tie breaks, first mismatch %s" % (v["identical"], v["checked"], v["tie_breaks"], v["first_mismatch"]))
+    assert v["checked"] == 64 and not v["wrong"], v
