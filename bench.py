@@ -172,6 +172,33 @@ def qmv_block(args) -> list:
     return [{k: r[k] for k in keep} for r in b.rows]
 
 
+def prefill_block(ctx, dec, prompt, args):
+    """tok/s of the prompt through ``smelt_cuda_prefill`` (host token ids in, argmax out; wall
+    clock around the synchronous call, best of three) in chunks of 512 and 128 positions, and
+    whether the token after the prompt is the fixture's."""
+    out = {"prompt_len": int(len(prompt)), "unit": "tok/s", "timing": "wall clock around the synchronous call, best of 3"}
+    first = None
+    for chunk in (512, 128):
+        best = None
+        for _ in range(3):
+            ctx.synchronize()
+            t0 = time.perf_counter()
+            first = dec.prefill(prompt, 0, chunk)
+            dt = time.perf_counter() - t0
+            best = dt if best is None or dt < best else best
+        out["chunk_%d" % chunk] = {"ms": round(best * 1e3, 3), "tok_s": round(len(prompt) / best, 1),
+                                   "launches": int(ctx.lib.smelt_cuda_last_launch_count(ctx.h))}
+    gold_path = os.path.join(ROOT, "tests", "golden", "full_model_tokens.json")
+    if os.path.exists(gold_path) and args.prompt_len == 512:
+        with open(gold_path) as f:
+            gold = json.load(f)
+        if gold["seed"] == SEED and gold["prompt_len"] == len(prompt):
+            ok = first == gold["tokens"][0] or (gold["top2_margin"][0] < 0.02 and first == gold["runner_up"][0])
+            out["first_token_matches_fixture"] = bool(ok)
+    dec.reset_cache()
+    return out
+
+
 def run_ours(args):
     from smelt_b200 import capi, package
 
@@ -213,6 +240,12 @@ def run_ours(args):
         # about a second, so every rank waits here until all are ready to decode.
         ctx.synchronize()
         dist.barrier()
+    # ── prefill (one GPU, batch 1): the same prompt through smelt_cuda_prefill, timed for the
+    # `prefill` block; the token-by-token pass below then overwrites the caches with what the
+    # headline measures ──
+    prefill = None
+    if world == 1 and B == 1 and not args.no_prefill:
+        prefill = prefill_block(ctx, dec, prompts[0], args)
     for i in range(args.prompt_len):  # the reference's no-prefill path: one decode step per prompt token
         dec.graph_seed(prompts[:, i], i)
         if i + 1 < args.prompt_len:
@@ -312,6 +345,8 @@ def run_ours(args):
                                "frac_of_8tbs": tb["total"] / (dev_ms / args.steps / 1e3) / 1e9 / 8000.0},
             "setup_s": gen_s,
         }
+        if prefill is not None:
+            result["prefill"] = prefill
         if world == 1 and not args.no_qmv:
             result["qmv"] = qmv_block(args)
         if keep:
@@ -458,6 +493,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-qmv", action="store_true", help="skip the per-shape matvec bandwidth block (N = 1)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill timing block (N = 1, batch 1)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens decoded before the timed region (512 = the headline configuration; smaller for profiler captures)")
     ap.add_argument("--table", default="fused", choices=["fused", "reference"],
                     help="fused: the builder's fused record table; reference: the reference emitter's record sequence")

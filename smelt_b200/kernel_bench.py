@@ -173,6 +173,32 @@ class Bench:
             kc.free(); vc.free()
         q.free(); out.free()
 
+    def attention_prefill(self, config, n_q, n_kv, d, n_pos, start):
+        """Chunked causal attention of a prompt chunk: n_pos query positions from `start`."""
+        ctx = self.ctx
+        if self.only and self.only not in f"prefill attention {n_q}x{n_kv}x{d} n{n_pos} s{start}":
+            return
+        cap = start + n_pos
+        # K and V of the keys any position of the chunk sees cross HBM once per group of eight positions at worst;
+        # the algorithmic figure is one pass over them plus q and out
+        alg = 2 * n_kv * d * 2 * cap + 2 * n_pos * n_q * d * 2
+        k = synth.kv_cache(5, "pk", 1, n_kv, cap, d)[0]
+        n = copies_for(alg, cap=32)
+        caches = [(ctx.to_device(k), ctx.to_device(k)) for _ in range(n)]
+        q = ctx.to_device(synth.activations(5, "pq", n_pos, n_q, d))
+        out = ctx.alloc(n_pos * n_q * d * 2)
+        scale = C.c_float(1 / np.sqrt(d))
+        def enqueue():
+            for kc, vc in caches:
+                ctx.call("attention_prefill", q, kc, vc, out, n_q, n_kv, d, n_pos, start, cap, scale, 0)
+        # multiply-adds x 2 of QK^T and PV over the causal triangle
+        keys = sum(start + t + 1 for t in range(n_pos))
+        self.run(config, "attention_prefill (chunked causal)", f"{n_q}q x {n_kv}kv x d{d}, {n_pos} positions from {start}", 1, alg, n, enqueue,
+                 flops=4.0 * n_q * d * keys)
+        for kc, vc in caches:
+            kc.free(); vc.free()
+        q.free(); out.free()
+
     def lm_head(self, config, vocab, hidden):
         ctx = self.ctx
         w = ctx.to_device(synth.normal_f16(4, "head", (vocab, hidden), 0.02))
@@ -220,6 +246,8 @@ def main():
             b.affine("config4", 12288, 4096, batch, "gate_up")
             b.affine("config4", 4096, 12288, batch, "add")
             b.affine("config4", 4096, 4096, batch, "matvec")
+        b.attention_prefill("config4", 32, 8, 128, 512, 0)
+        b.attention_prefill("config4", 32, 8, 128, 128, 384)
         if not args.only:
             b.lm_head("config4", 151936, 4096)
     if args.markdown:
