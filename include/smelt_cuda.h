@@ -500,6 +500,31 @@ SMELT_CUDA_API smelt_status smelt_cuda_prefill(smelt_cuda_ctx* ctx, const smelt_
                                                const int32_t* tokens, int n_tokens, int32_t start_pos, int chunk,
                                                int32_t* out_token);
 
+/* ── DeltaNet decode step (hybrid linear-attention layers) ───────────────────
+ * The four kernels between a DeltaNet layer's input projections and its output projection
+ * (Sources/SmeltCompiler/DeltaNetPlugin.swift:196-318), also accepted as records under the
+ * reference's pipeline names with its bindings.
+ * conv1d_update_silu (Resources/Shaders/conv1d.metal:271-331): state [C, K] shifts left by one,
+ *   takes new_val [C]; out [C] = staged-fp16 SiLU of the K-tap dot product with weight [C, K].
+ * rms_scale_qk (Resources/Shaders/norms.metal:1380-1431): in place on the qk_heads Q heads and
+ *   qk_heads K heads at the front of each qkv row: RMS normalisation times 1/head_dim (Q) or
+ *   rsqrt(head_dim) (K).
+ * deltanet_recurrence_decode (Resources/Shaders/recurrence.metal:511-588 and the d128
+ *   specialisations :590-836): per value head, state [Dv, Dk] fp16 decays, takes the rank-one
+ *   update k x (v - state.k) * beta and is read out with q; state in place, out [Hv, D].
+ * rms_norm_gated (Resources/Shaders/norms.metal:1093-1143): per head RMS norm times weight [D]
+ *   times silu(gate). */
+SMELT_CUDA_API smelt_status smelt_cuda_conv1d_update_silu(smelt_cuda_ctx* ctx, void* state_dev, const void* new_val_dev,
+                                                          const void* weight_dev, void* out_dev, int channels, int kernel_size);
+SMELT_CUDA_API smelt_status smelt_cuda_rms_scale_qk(smelt_cuda_ctx* ctx, void* qkv_dev, int head_dim, float eps, int qkv_dim,
+                                                    int qk_heads, int batch);
+SMELT_CUDA_API smelt_status smelt_cuda_deltanet_recurrence_decode(smelt_cuda_ctx* ctx, void* state_dev, const void* qkv_dev,
+                                                                  const void* b_proj_dev, const void* a_proj_dev,
+                                                                  const void* a_log_dev, const void* dt_bias_dev, void* out_dev,
+                                                                  int head_dim, int value_heads, int qk_heads);
+SMELT_CUDA_API smelt_status smelt_cuda_rms_norm_gated(smelt_cuda_ctx* ctx, const void* input_dev, const void* gate_dev,
+                                                      const void* weight_dev, void* out_dev, int head_dim, float eps, int heads);
+
 /* ── prompt-state snapshots ──────────────────────────────────────────────────
  * SmeltRuntime.captureDevicePromptSnapshot / restoreDevicePromptSnapshot
  * (Sources/SmeltRuntime/SmeltRuntime.swift:1385-1553) and the host form with a partial restore,

@@ -386,3 +386,33 @@ def top2(logits) -> tuple[int, int, float]:
     w[best] = -np.inf
     second = int(np.argmax(w))
     return best, second, float(v[best] - v[second])
+
+
+# ── DeltaNet decode step (conv1d.metal, norms.metal, recurrence.metal) ──
+def conv1d_update_silu(state, new_val, weight, channels: int, kernel_size: int):
+    """Returns (state after the shift, activated output)."""
+    st = _h(state).copy()
+    out = np.zeros(channels, np.float16)
+    _check(lib().so_conv1d_update_silu(_p(st), _p(_h(new_val)), _p(_h(weight)), _p(out), channels, kernel_size), "conv1d_update_silu")
+    return st, out
+
+
+def rms_scale_qk(qkv, head_dim: int, eps: float, qkv_dim: int, qk_heads: int, batch: int = 1) -> np.ndarray:
+    out = _h(qkv).copy()
+    _check(lib().so_rms_scale_qk(_p(out), head_dim, C.c_float(eps), qkv_dim, qk_heads, batch), "rms_scale_qk")
+    return out
+
+
+def deltanet_recurrence_decode(state, qkv, b_proj, a_proj, a_log, dt_bias, head_dim: int, value_heads: int, qk_heads: int):
+    """Returns (state after the step, output [value_heads, head_dim])."""
+    st = _h(state).copy()
+    out = np.zeros((value_heads, head_dim), np.float16)
+    _check(lib().so_deltanet_recurrence_decode(_p(st), _p(_h(qkv)), _p(_h(b_proj)), _p(_h(a_proj)), _p(_h(a_log)), _p(_h(dt_bias)), _p(out),
+                                               head_dim, value_heads, qk_heads), "deltanet_recurrence_decode")
+    return st, out
+
+
+def rms_norm_gated(x, gate, weight, head_dim: int, eps: float, heads: int) -> np.ndarray:
+    out = np.zeros((heads, head_dim), np.float16)
+    _check(lib().so_rms_norm_gated(_p(_h(x)), _p(_h(gate)), _p(_h(weight)), _p(out), head_dim, C.c_float(eps), heads), "rms_norm_gated")
+    return out

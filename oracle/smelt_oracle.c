@@ -892,3 +892,146 @@ SO_API int so_model_generate(so_model_t *m, const int32_t *prompt, int n_prompt,
     free(logits);
     return rc;
 }
+
+/* ───────────────────── DeltaNet decode step (hybrid linear-attention layers) ─────────────────────
+ * No scalar Swift oracle exists for these kernels beyond the float references inside the
+ * reference's tests (PrefillKernelTests.swift:583-609, :4400-4441); the functions below restate
+ * the Metal kernels' own arithmetic, including their staged fp16 roundings. */
+
+/* smelt_silu_staged_half (Resources/Shaders/conv1d.metal:4-15): every intermediate an fp16
+ * value; a result of either zero is +0. */
+static inline uint16_t silu_staged_half(uint16_t xh) {
+    float x = h2f(xh);
+    float e = round_h(expf(fabsf(x)));
+    float tail = round_h(1.0f / round_h(1.0f + e));
+    float sig = x < 0.0f ? tail : round_h(1.0f - tail);
+    uint16_t r = f2h(x * sig);
+    return (r & 0x7fffu) == 0u ? (uint16_t)0 : r;
+}
+
+/* conv1d_update_silu (conv1d.metal:271-331): per channel, state [C, K] shifts left by one and
+ * takes the new value; out = silu_staged(half(sum_k state[k] * weight[k])), taps added one at a
+ * time from a float zero (conv1d.metal:20-27).  state is updated in place. */
+SO_API int so_conv1d_update_silu(uint16_t *state, const uint16_t *new_val, const uint16_t *weight, uint16_t *out,
+                                 int channels, int kernel_size) {
+    if (channels <= 0 || kernel_size <= 0 || kernel_size > 8) return SO_ERR_GEOMETRY;
+    for (int ch = 0; ch < channels; ++ch) {
+        uint16_t *st = state + (size_t)ch * kernel_size;
+        const uint16_t *w = weight + (size_t)ch * kernel_size;
+        for (int k = 0; k + 1 < kernel_size; ++k) st[k] = st[k + 1];
+        st[kernel_size - 1] = new_val[ch];
+        float acc = 0.0f;
+        for (int k = 0; k < kernel_size; ++k) acc += h2f(st[k]) * h2f(w[k]);
+        out[ch] = silu_staged_half(f2h(acc));
+    }
+    return SO_OK;
+}
+
+/* rms_scale_qk (Resources/Shaders/norms.metal:1380-1431): for each of the qk_heads Q heads and
+ * qk_heads K heads at the front of qkv [batch, qkv_dim]: x <- half(half(x * rsqrt(mean(x^2) +
+ * eps)) * edge), edge = half(1 / head_dim) for Q, half(rsqrt(head_dim)) for K.  In place. */
+SO_API int so_rms_scale_qk(uint16_t *qkv, int head_dim, float eps, int qkv_dim, int qk_heads, int batch) {
+    if (head_dim <= 0 || head_dim > 512 || qk_heads <= 0 || 2 * qk_heads * head_dim > qkv_dim || batch <= 0) return SO_ERR_GEOMETRY;
+    for (int b = 0; b < batch; ++b)
+        for (int g = 0; g < 2 * qk_heads; ++g) {
+            const int is_k = g >= qk_heads;
+            uint16_t *x = qkv + (size_t)b * qkv_dim + (size_t)g * head_dim; /* K region follows the Q region */
+            float sum = 0.0f;
+            for (int i = 0; i < head_dim; ++i) sum += h2f(x[i]) * h2f(x[i]);
+            const float scale = 1.0f / sqrtf(sum / (float)head_dim + eps);
+            const float edge = is_k ? round_h(1.0f / sqrtf((float)head_dim)) : round_h(1.0f / (float)head_dim);
+            for (int i = 0; i < head_dim; ++i) x[i] = f2h(round_h(h2f(x[i]) * scale) * edge);
+        }
+    return SO_OK;
+}
+
+/* smelt_decode_sigmoid_staged_half / smelt_decode_softplus_staged_half
+ * (Resources/Shaders/recurrence.metal:4-21). */
+static inline float sigmoid_staged_half(uint16_t xh) {
+    float x = h2f(xh);
+    float tail = round_h(1.0f / round_h(1.0f + round_h(expf(fabsf(x)))));
+    return x < 0.0f ? tail : round_h(1.0f - tail);
+}
+static inline float decode_log1p(float x) {
+    const float xp1 = 1.0f + x;
+    if (xp1 == 1.0f) return x;
+    return x * (logf(xp1) / (xp1 - 1.0f));
+}
+static inline float softplus_staged_half(uint16_t xh) {
+    float x = h2f(xh);
+    float mx = x > 0.0f ? x : 0.0f, mn = x < 0.0f ? x : 0.0f;
+    return round_h(mx + decode_log1p(round_h(expf(round_h(mn - mx)))));
+}
+
+/* deltanet_recurrence_mlx_decode (recurrence.metal:511-588): per value head h and output row dv,
+ * state row [Dk] *= decay; kv = state . k; delta = (v[dv] - kv) * beta; state += k * delta;
+ * out = state . q; state written back as fp16.  beta = sigmoid_staged(b[h]); decay =
+ * half(exp(-exp(a_log[h]) * softplus_staged(half(a[h] + dt_bias[h])))).  q / k heads are shared
+ * by value_heads / qk_heads value heads; qkv = [q (Hqk, D) | k (Hqk, D) | v (Hv, D)].  The lane
+ * partition of the Metal kernel (lane l holds dk = l * D/32 ...) fixes the summation order:
+ * per-lane partial sums in dk order, then the 32 lane sums added pairwise as simd_sum does
+ * (butterfly over lane distance 16, 8, 4, 2, 1). */
+static inline float simd_sum32(float *lane) {
+    for (int off = 16; off > 0; off >>= 1)
+        for (int l = 0; l < off; ++l) lane[l] += lane[l + off];
+    return lane[0];
+}
+SO_API int so_deltanet_recurrence_decode(uint16_t *state, const uint16_t *qkv, const uint16_t *b_proj, const uint16_t *a_proj,
+                                         const uint16_t *a_log, const uint16_t *dt_bias, uint16_t *out, int head_dim,
+                                         int value_heads, int qk_heads) {
+    if (head_dim <= 0 || head_dim % 32 || head_dim > 256 || qk_heads <= 0 || value_heads <= 0 || value_heads % qk_heads) return SO_ERR_GEOMETRY;
+    const int D = head_dim, epl = D / 32, rep = value_heads / qk_heads;
+    for (int h = 0; h < value_heads; ++h) {
+        const int qh = h / rep;
+        const uint16_t *q = qkv + (size_t)qh * D, *k = qkv + (size_t)(qk_heads + qh) * D, *v = qkv + (size_t)2 * qk_heads * D + (size_t)h * D;
+        const float beta = sigmoid_staged_half(b_proj[h]);
+        const uint16_t xh = f2h(h2f(a_proj[h]) + h2f(dt_bias[h]));
+        const float decay = round_h(expf(-expf(h2f(a_log[h])) * softplus_staged_half(xh)));
+        for (int dv = 0; dv < D; ++dv) {
+            uint16_t *row = state + ((size_t)h * D + dv) * D;
+            float st[256], lane[32];
+            for (int l = 0; l < 32; ++l) {
+                float p = 0.0f;
+                for (int i = 0; i < epl; ++i) {
+                    const int dk = l * epl + i;
+                    st[dk] = h2f(row[dk]) * decay;
+                    p += st[dk] * h2f(k[dk]);
+                }
+                lane[l] = p;
+            }
+            const float kv = simd_sum32(lane);
+            const float delta = (h2f(v[dv]) - kv) * beta;
+            for (int l = 0; l < 32; ++l) {
+                float p = 0.0f;
+                for (int i = 0; i < epl; ++i) {
+                    const int dk = l * epl + i;
+                    st[dk] += h2f(k[dk]) * delta;
+                    p += st[dk] * h2f(q[dk]);
+                }
+                lane[l] = p;
+            }
+            out[(size_t)h * D + dv] = f2h(simd_sum32(lane));
+            for (int dk = 0; dk < D; ++dk) row[dk] = f2h(st[dk]);
+        }
+    }
+    return SO_OK;
+}
+
+/* rms_norm_gated (norms.metal:1093-1143): per head, out = half(w * (x * rsqrt(mean(x^2) + eps)) *
+ * silu(g)), silu(g) = g / (1 + exp(-g)) in fp32; weight [D] shared by the heads. */
+SO_API int so_rms_norm_gated(const uint16_t *input, const uint16_t *gate, const uint16_t *weight, uint16_t *out, int head_dim,
+                             float eps, int heads) {
+    if (head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < heads; ++h) {
+        const uint16_t *x = input + (size_t)h * head_dim, *g = gate + (size_t)h * head_dim;
+        float sum = 0.0f;
+        for (int i = 0; i < head_dim; ++i) sum += h2f(x[i]) * h2f(x[i]);
+        const float rs = 1.0f / sqrtf(sum / (float)head_dim + eps);
+        for (int i = 0; i < head_dim; ++i) {
+            const float gv = h2f(g[i]);
+            const float silu = gv / (1.0f + expf(-gv));
+            out[(size_t)h * head_dim + i] = f2h(h2f(weight[i]) * (h2f(x[i]) * rs) * silu);
+        }
+    }
+    return SO_OK;
+}

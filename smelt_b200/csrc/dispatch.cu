@@ -119,7 +119,28 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"smelt_tp_argmax", PK_TP_ARGMAX, 0, false},
         {"smelt_rope_qkv_append", PK_ROPE_QKV_APPEND, 0, false},
         {"smelt_rope_attention_decode", PK_ATTN_ROPE, 0, false},
+        {"conv1d_update_silu", PK_CONV1D_SILU, 0, false},
+        {"rms_scale_qk", PK_RMS_SCALE_QK, 0, false},
+        {"deltanet_recurrence_mlx_decode", PK_DELTANET_DECODE, 0, false},
+        {"rms_norm_gated", PK_RMS_NORM_GATED, 0, false},
     };
+    // Shape-specialised DeltaNet names carry their constants in the name
+    // (Resources/Shaders/recurrence.metal:590-836, norms_gated_precise.metal:20-52).
+    {
+        struct Fixed { const char* name; PipeKind kind; int d, hv, hqk; };
+        static const Fixed fixed[] = {
+            {"deltanet_recurrence_mlx_decode_d128_h16", PK_DELTANET_DECODE, 128, 16, 16},
+            {"deltanet_recurrence_mlx_decode_d128_h32_qk16", PK_DELTANET_DECODE, 128, 32, 16},
+            {"deltanet_recurrence_mlx_decode_d128_h48_qk16", PK_DELTANET_DECODE, 128, 48, 16},
+            {"rms_norm_gated_d128", PK_RMS_NORM_GATED, 128, 0, 0},
+        };
+        for (const Fixed& f : fixed)
+            if (name == f.name) {
+                p.kind = f.kind; p.head_dim = f.d; p.n_q = f.hv; p.n_kv = f.hqk; p.fixed_shape = true;
+                *out = p;
+                return true;
+            }
+    }
     for (const Simple& s : table)
         if (name == s.name) {
             p.kind = s.kind; p.bits = s.bits; p.batched = s.batched;
@@ -586,6 +607,56 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             NEED_BYTES(0, (size_t)heads * d * 2); NEED_BYTES(2, (size_t)heads * d * 2);
             in.launches += 1;
             return check_cuda(ctx, launch_per_head_rms_norm(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, heads, (int)d, as_f32(eps_bits)), "per_head_rms_norm");
+        }
+        case PK_CONV1D_SILU: {
+            // conv1d.metal:271-278: 0 state [C, K] (in place), 1 new value [C], 2 weight [C, K], 3 out [C], 4 channels, 5 kernel size.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(4, channels); NEED_U32(5, ksize);
+            if (channels == 0 || ksize == 0 || ksize > 8) return fail(ctx, SMELT_ERR_UNSUPPORTED, "conv1d_update_silu: kernel size in 1..8");
+            NEED_BYTES(0, (size_t)channels * ksize * 2); NEED_BYTES(1, (size_t)channels * 2); NEED_BYTES(2, (size_t)channels * ksize * 2); NEED_BYTES(3, (size_t)channels * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_conv1d_update_silu(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)channels, (int)ksize), "conv1d_update_silu");
+        }
+        case PK_RMS_SCALE_QK: {
+            // norms.metal:1380-1386: 0 qkv (in place), 1 headDim, 2 eps, 3 qkvDim, 4 qkHeads; grid.y = rows of qkv.
+            NEED_BUF(0); NEED_U32(1, d); NEED_U32(2, eps_bits); NEED_U32(3, qkv_dim); NEED_U32(4, qk_heads);
+            const int rows = batch_of(rec);
+            if (d == 0 || qk_heads == 0 || (uint64_t)2 * qk_heads * d > qkv_dim) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "rms_scale_qk: bad shape");
+            NEED_BYTES(0, (size_t)rows * qkv_dim * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_rms_scale_qk(l, (__half*)r.buf[0].ptr, (int)d, as_f32(eps_bits), (int)qkv_dim, (int)qk_heads, rows), "rms_scale_qk");
+        }
+        case PK_DELTANET_DECODE: {
+            // recurrence.metal:511-522: 0 state [Hv, D, D] (in place), 1 qkv, 2 b, 3 a, 4 A_log, 5 dt_bias, 6 out [Hv, D],
+            // 7 headDim, 8 headScale (unused by the kernel: q arrives scaled), 9 valueHeads, 10 qkHeads; the
+            // specialised names fix 7, 9 and 10.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_BUF(5); NEED_BUF(6);
+            uint32_t d = (uint32_t)p.head_dim, hv = (uint32_t)p.n_q, hqk = (uint32_t)p.n_kv;
+            if (!p.fixed_shape) {
+                NEED_U32(7, d_); NEED_U32(9, hv_); NEED_U32(10, hqk_);
+                d = d_; hv = hv_; hqk = hqk_;
+            }
+            if (d == 0 || d % 32 || d > 256 || hv == 0 || hqk == 0 || hv % hqk) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": head_dim a multiple of 32 up to 256, value heads a multiple of q/k heads");
+            NEED_BYTES(0, (size_t)hv * d * d * 2); NEED_BYTES(1, ((size_t)2 * hqk + hv) * d * 2); NEED_BYTES(2, (size_t)hv * 2); NEED_BYTES(3, (size_t)hv * 2);
+            NEED_BYTES(4, (size_t)hv * 2); NEED_BYTES(5, (size_t)hv * 2); NEED_BYTES(6, (size_t)hv * d * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_deltanet_recurrence_decode(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const __half*)r.buf[3].ptr,
+                                                                     (const __half*)r.buf[4].ptr, (const __half*)r.buf[5].ptr, (__half*)r.buf[6].ptr, (int)d, (int)hv, (int)hqk), p.name.c_str());
+        }
+        case PK_RMS_NORM_GATED: {
+            // norms.metal:1093-1099: 0 in [H, D], 1 gate [H, D], 2 weight [D], 3 out, 4 headDim, 5 eps; one threadgroup per
+            // head; rms_norm_gated_d128 fixes headDim 128 and eps 1e-6 (norms_gated_precise.metal:20-52).
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3);
+            uint32_t d = (uint32_t)p.head_dim;
+            float eps = 1e-6f;
+            if (!p.fixed_shape) {
+                NEED_U32(4, d_); NEED_U32(5, eps_bits);
+                d = d_; eps = as_f32(eps_bits);
+            }
+            const int heads = (int)rec.grid[0];
+            if (heads <= 0 || d == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad shape");
+            NEED_BYTES(0, (size_t)heads * d * 2); NEED_BYTES(1, (size_t)heads * d * 2); NEED_BYTES(2, (size_t)d * 2); NEED_BYTES(3, (size_t)heads * d * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_rms_norm_gated(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)d, eps, heads), p.name.c_str());
         }
         case PK_ADD: {
             // activations.metal:56-61: 0 a, 1 b, 2 out, 3 count.

@@ -17,6 +17,11 @@ cudaError_t launch_kv_cache_update(const Launch& l, __half* cache, const __half*
 cudaError_t launch_rope_qkv_append(const Launch& l, __half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache, uint32_t capacity, int head_dim, int n_q, int n_kv, int layout, float base_log2, int batch, size_t seq_stride);
 cudaError_t launch_argmax_partials(const Launch& l, const __half* logits, uint64_t* partials, int vocab, int chunk, int batch);
 cudaError_t launch_argmax_reduce(const Launch& l, const uint64_t* partials, int32_t* out, int n, int batch, int out_stride);
+// DeltaNet decode step (deltanet.cu)
+cudaError_t launch_conv1d_update_silu(const Launch& l, __half* state, const __half* new_val, const __half* weight, __half* out, int channels, int kernel_size);
+cudaError_t launch_rms_scale_qk(const Launch& l, __half* qkv, int head_dim, float eps, int qkv_dim, int qk_heads, int batch);
+cudaError_t launch_deltanet_recurrence_decode(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, int head_dim, int value_heads, int qk_heads);
+cudaError_t launch_rms_norm_gated(const Launch& l, const __half* input, const __half* gate, const __half* weight, __half* out, int head_dim, float eps, int heads);
 cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x, __half* y, int rows, int cols, int batch, int sm_count);
 
 // attention.cu — split-K flash-decode.  scratch holds fp32 partials; see attention_scratch_bytes.

@@ -48,6 +48,10 @@ enum PipeKind : int {
     PK_ATTN_ROPE,
     PK_TP_REDUCE_ADD,
     PK_TP_ARGMAX,
+    PK_CONV1D_SILU,
+    PK_RMS_SCALE_QK,
+    PK_DELTANET_DECODE,
+    PK_RMS_NORM_GATED,
 };
 
 struct Pipeline {

@@ -1,0 +1,240 @@
+"""DeltaNet decode step: the oracle's restatement of the Metal kernels pinned on the closed-form
+fixtures and float references the reference's own tests use (PrefillKernelTests.swift:583-609,
+:1493-1577, :4352-4552), then the CUDA kernels against the oracle, typed and as records."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from smelt_b200 import capi
+from helpers import ulp_diff_f16
+
+F = np.float32
+
+
+def recurrence_fixture(head_dim=128, heads=16):
+    """The inputs of testDeltaNetRecurrenceMlxDecode_GenericAndSpecializedMatchReference
+    (PrefillKernelTests.swift:4400-4421): closed-form sin / cos ramps, Q and K L2-normalised
+    (Q also times 1/sqrt(D)) in fp32 and rounded to fp16."""
+    hidden = head_dim * heads
+    i = np.arange(heads * head_dim * head_dim, dtype=F)
+    state = (np.sin(i * F(0.0007)) * F(0.03)).astype(np.float16)
+    c = np.arange(3 * hidden, dtype=F)
+    qkv = (np.sin(c * F(0.0019)) * F(0.4)).astype(np.float16)
+    h = np.arange(heads, dtype=F)
+    b = (np.cos(h * F(0.017)) * F(0.9)).astype(np.float16)
+    a = (np.sin(h * F(0.013)) * F(0.7)).astype(np.float16)
+    a_log = (F(-1.2) + h * F(0.03)).astype(np.float16)
+    dt_bias = (F(-0.2) + h * F(0.02)).astype(np.float16)
+    q = qkv[:hidden].astype(F).reshape(heads, head_dim)
+    k = qkv[hidden:2 * hidden].astype(F).reshape(heads, head_dim)
+    q = q * (F(1 / np.sqrt(F(head_dim))) / np.maximum(np.sqrt((q * q).sum(1, keepdims=True)), F(1e-6)))
+    k = k * (F(1) / np.maximum(np.sqrt((k * k).sum(1, keepdims=True)), F(1e-6)))
+    qkv = np.concatenate([q.astype(np.float16).reshape(-1), k.astype(np.float16).reshape(-1), qkv[2 * hidden:]])
+    return state, qkv, b, a, a_log, dt_bias
+
+
+def recurrence_float_reference(state, qkv, b, a, a_log, dt_bias, head_dim, heads):
+    """The test's own float reference (PrefillKernelTests.swift:4423-4441): no fp16 staging."""
+    hidden = head_dim * heads
+    st = state.astype(np.float64).reshape(heads, head_dim, head_dim).copy()
+    x = qkv.astype(np.float64)
+    out = np.zeros((heads, head_dim))
+    for h in range(heads):
+        q, k, v = x[h * head_dim:(h + 1) * head_dim], x[hidden + h * head_dim:hidden + (h + 1) * head_dim], x[2 * hidden + h * head_dim:2 * hidden + (h + 1) * head_dim]
+        beta = 1 / (1 + np.exp(-float(b[h])))
+        sp_in = float(a[h]) + float(dt_bias[h])
+        sp = sp_in if sp_in > 20 else np.log1p(np.exp(sp_in))
+        decay = np.exp(-np.exp(float(a_log[h])) * sp)
+        st[h] *= decay
+        delta = (v - st[h] @ k) * beta
+        st[h] += np.outer(delta, k)
+        out[h] = st[h] @ q
+    return st, out
+
+
+def test_oracle_recurrence_is_within_the_references_own_bound(oracle):
+    """The reference asserts max |kernel - float reference| < 0.06 over output and state
+    (PrefillKernelTests.swift:4551); the oracle's staged-fp16 restatement must sit well inside."""
+    fx = recurrence_fixture()
+    st, out = oracle.deltanet_recurrence_decode(*fx, 128, 16, 16)
+    ref_st, ref_out = recurrence_float_reference(*fx, 128, 16)
+    assert np.max(np.abs(out.astype(np.float64) - ref_out)) < 2e-3
+    assert np.max(np.abs(st.astype(np.float64).reshape(ref_st.shape) - ref_st)) < 2e-3
+
+
+def test_oracle_gated_norm_matches_the_references_cpu_reference(oracle):
+    """testRmsNormGatedBatched_Qwen0808Shape_MatchesCPUReference: bound 1e-3 (PrefillKernelTests.swift:1577)."""
+    d, heads = 128, 16 * 18
+    i = np.arange(heads * d, dtype=F)
+    x = (np.sin(i * F(0.0131)) * F(0.2)).astype(np.float16)
+    g = (np.cos(i * F(0.0097)) * F(2.0)).astype(np.float16)
+    w = (F(0.9) + F(0.2) * np.sin(np.arange(d, dtype=F) * F(0.021))).astype(np.float16)
+    got = oracle.rms_norm_gated(x, g, w, d, 1e-6, heads).astype(F)
+    xf, gf = x.astype(F).reshape(heads, d), g.astype(F).reshape(heads, d)
+    rs = F(1) / np.sqrt((xf * xf).sum(1, keepdims=True) / F(d) + F(1e-6))
+    ref = (w.astype(F) * (xf * rs) * (gf / (F(1) + np.exp(-gf)))).astype(np.float16).astype(F)
+    assert np.max(np.abs(got - ref)) < 1e-3
+
+
+def test_oracle_conv1d_shifts_and_activates(oracle):
+    c, k = 96, 4
+    rng = np.random.default_rng(3)
+    state = rng.standard_normal((c, k)).astype(np.float16)
+    new = rng.standard_normal(c).astype(np.float16)
+    w = (rng.standard_normal((c, k)) * 0.5).astype(np.float16)
+    st, out = oracle.conv1d_update_silu(state, new, w, c, k)
+    st = st.reshape(c, k)
+    assert np.array_equal(st[:, :3], state[:, 1:]) and np.array_equal(st[:, 3], new)
+    acc = (st.astype(F) * w.astype(F)).sum(1).astype(np.float16).astype(F)
+    ref = (acc / (1 + np.exp(-acc))).astype(np.float16)
+    assert np.max(ulp_diff_f16(out, ref)) <= 2  # the staged fp16 sigmoid against the float one
+    # an underflowed product is +0, never -0 (conv1d.metal:9-14)
+    zs, zo = oracle.conv1d_update_silu(np.zeros((1, 4), np.float16), np.array([0x8001], np.uint16).view(np.float16), np.ones((1, 4), np.float16), 1, 4)
+    assert zo.view(np.uint16)[0] == 0
+
+
+# ── CUDA against the oracle ──
+@pytest.fixture(scope="module")
+def ctx():
+    c = capi.Context(0)
+    yield c
+    c.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("channels,ksize", [(6144, 4), (1000, 4), (512, 3), (64, 8)])
+def test_conv1d_update_silu(ctx, oracle, channels, ksize):
+    rng = np.random.default_rng(channels + ksize)
+    state = rng.standard_normal((channels, ksize)).astype(np.float16)
+    new = rng.standard_normal(channels).astype(np.float16)
+    w = (rng.standard_normal((channels, ksize)) * 0.5).astype(np.float16)
+    ds, dn, dw = (ctx.to_device(a) for a in (state, new, w))
+    out = ctx.alloc(channels * 2)
+    ctx.call("conv1d_update_silu", ds, dn, dw, out, channels, ksize)
+    want_state, want = oracle.conv1d_update_silu(state, new, w, channels, ksize)
+    assert np.array_equal(ds.download(np.uint16, (channels * ksize,)), want_state.view(np.uint16).reshape(-1)), "the shifted state is exact"
+    assert np.max(ulp_diff_f16(out.download(np.float16, (channels,)), want)) <= 1  # expf of the two libraries
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim,qk_heads,v_heads,batch", [(128, 16, 16, 1), (128, 16, 32, 3), (64, 4, 4, 2), (256, 2, 2, 1)])
+def test_rms_scale_qk(ctx, oracle, head_dim, qk_heads, v_heads, batch):
+    qkv_dim = (2 * qk_heads + v_heads) * head_dim
+    x = np.random.default_rng(head_dim).standard_normal((batch, qkv_dim)).astype(np.float16)
+    dx = ctx.to_device(x)
+    ctx.call("rms_scale_qk", dx, head_dim, C.c_float(1e-6), qkv_dim, qk_heads, batch)
+    got = dx.download(np.float16, (batch, qkv_dim))
+    want = oracle.rms_scale_qk(x, head_dim, 1e-6, qkv_dim, qk_heads, batch).reshape(batch, qkv_dim)
+    assert np.array_equal(got[:, 2 * qk_heads * head_dim:], x[:, 2 * qk_heads * head_dim:]), "V is not touched"
+    # another fp32 order of the sum of squares can flip the first fp16 rounding by an ulp, and the
+    # second rounding (times the edge scale) can carry that to two
+    assert np.max(ulp_diff_f16(got, want)) <= 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim,v_heads,qk_heads", [(128, 16, 16), (128, 32, 16), (128, 48, 16), (64, 8, 4), (256, 4, 2)])
+def test_deltanet_recurrence_decode(ctx, oracle, head_dim, v_heads, qk_heads):
+    rng = np.random.default_rng(head_dim + v_heads)
+    state = (rng.standard_normal((v_heads, head_dim, head_dim)) * 0.05).astype(np.float16)
+    qkv = rng.standard_normal((2 * qk_heads + v_heads) * head_dim).astype(F)
+    for g in range(2 * qk_heads):  # unit-norm q and k, as rms_scale_qk leaves them up to the edge scales
+        seg = qkv[g * head_dim:(g + 1) * head_dim]
+        seg /= np.linalg.norm(seg)
+    qkv = qkv.astype(np.float16)
+    b, a = rng.standard_normal(v_heads).astype(np.float16), rng.standard_normal(v_heads).astype(np.float16)
+    a_log = rng.uniform(-2, 0.5, v_heads).astype(np.float16)
+    dt = rng.uniform(-0.5, 0.5, v_heads).astype(np.float16)
+    dev = [ctx.to_device(t) for t in (state, qkv, b, a, a_log, dt)]
+    out = ctx.alloc(v_heads * head_dim * 2)
+    want_state, want = oracle.deltanet_recurrence_decode(state, qkv, b, a, a_log, dt, head_dim, v_heads, qk_heads)
+    for step in range(2):  # two steps: the second reads the state the first wrote
+        ctx.call("deltanet_recurrence_decode", *dev, out, head_dim, v_heads, qk_heads)
+        got = out.download(np.float16, (v_heads, head_dim))
+        got_state = dev[0].download(np.float16, (v_heads, head_dim, head_dim))
+        assert np.max(np.abs(got.astype(F) - want.astype(F))) <= 2e-3 * max(1.0, float(np.max(np.abs(want.astype(F))))), f"step {step}"
+        assert np.max(ulp_diff_f16(got_state, want_state.reshape(got_state.shape))) <= 1 + step, f"state, step {step}"
+        want_state, want = oracle.deltanet_recurrence_decode(want_state, qkv, b, a, a_log, dt, head_dim, v_heads, qk_heads)
+
+
+@pytest.mark.gpu
+def test_deltanet_reference_fixture(ctx):
+    """The reference test's fixture through the CUDA kernel, against the reference test's float
+    reference and bound (0.06, PrefillKernelTests.swift:4551)."""
+    fx = recurrence_fixture()
+    dev = [ctx.to_device(t) for t in fx]
+    out = ctx.alloc(16 * 128 * 2)
+    ctx.call("deltanet_recurrence_decode", *dev, out, 128, 16, 16)
+    ref_st, ref_out = recurrence_float_reference(*fx, 128, 16)
+    assert np.max(np.abs(out.download(np.float16, (16, 128)).astype(np.float64) - ref_out)) < 0.06
+    assert np.max(np.abs(dev[0].download(np.float16, (16, 128, 128)).astype(np.float64) - ref_st)) < 0.06
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim,heads", [(128, 16), (128, 288), (64, 5), (256, 3)])
+def test_rms_norm_gated(ctx, oracle, head_dim, heads):
+    rng = np.random.default_rng(heads)
+    x = (rng.standard_normal((heads, head_dim)) * 0.3).astype(np.float16)
+    g = (rng.standard_normal((heads, head_dim)) * 2).astype(np.float16)
+    w = (0.9 + 0.2 * rng.standard_normal(head_dim)).astype(np.float16)
+    dx, dg, dw = (ctx.to_device(t) for t in (x, g, w))
+    ctx.call("rms_norm_gated", dx, dg, dw, dx, head_dim, C.c_float(1e-6), heads)  # in place, as the emitter binds it
+    got = dx.download(np.float16, (heads, head_dim))
+    want = oracle.rms_norm_gated(x, g, w, head_dim, 1e-6, heads)
+    assert np.max(ulp_diff_f16(got, want)) <= 1
+
+
+@pytest.mark.gpu
+def test_deltanet_records_run_the_layer_core(ctx, oracle):
+    """The four records the reference's emitter writes for a DeltaNet layer's core
+    (DeltaNetPlugin.swift:196-318), with its pipeline names and bindings, eagerly."""
+    d, hqk, hv, k = 128, 16, 32, 4
+    qkv_dim = (2 * hqk + hv) * d
+    rng = np.random.default_rng(9)
+    conv_state = rng.standard_normal((qkv_dim, k)).astype(np.float16)
+    qkv_in = rng.standard_normal(qkv_dim).astype(np.float16)
+    conv_w = (rng.standard_normal((qkv_dim, k)) * 0.5).astype(np.float16)
+    rec_state = (rng.standard_normal((hv, d, d)) * 0.05).astype(np.float16)
+    b, a = rng.standard_normal(hv).astype(np.float16), rng.standard_normal(hv).astype(np.float16)
+    a_log, dt = rng.uniform(-2, 0.5, hv).astype(np.float16), rng.uniform(-0.5, 0.5, hv).astype(np.float16)
+    z = (rng.standard_normal(hv * d) * 2).astype(np.float16)
+    norm_w = (0.9 + 0.2 * rng.standard_normal(d)).astype(np.float16)
+    tensors = {2: conv_state, 3: qkv_in, 4: conv_w, 5: rec_state, 6: b, 7: a, 9: a_log, 10: dt, 11: np.zeros(hv * d, np.float16), 12: z, 13: norm_w}
+    for slot, t in tensors.items():
+        ctx.call("alloc_slot", slot, C.c_size_t(t.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), t.ctypes.data_as(C.c_void_p), C.c_size_t(t.nbytes)))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    names = ["conv1d_update_silu", "rms_scale_qk", "deltanet_recurrence_mlx_decode_d128_h32_qk16", "rms_norm_gated_d128"]
+    for i, n in enumerate(names):
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, i, n.encode()))
+    f32 = lambda v: int(np.array([v], F).view(np.uint32)[0])
+
+    def rec(pipe, grid, bufs, cons):
+        r = capi.DispatchRecord()
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, pipe, len(bufs), len(cons)
+        r.grid[0], r.grid[1], r.grid[2] = grid[0], grid[1], 1
+        for j, (binding, slot) in enumerate(bufs):
+            r.buf[j].slot, r.buf[j].binding_index, r.buf[j].offset_kind, r.buf[j].offset = slot, binding, 0, 0
+        for j, (binding, kind, value) in enumerate(cons):
+            r.con[j].kind, r.con[j].binding_index, r.con[j].value = kind, binding, value
+        return r
+
+    table = (capi.DispatchRecord * 4)(
+        rec(0, (qkv_dim, 1), [(0, 2), (1, 3), (2, 4), (3, 3)], [(4, 0, qkv_dim), (5, 0, k)]),
+        rec(1, (2 * hqk, 1), [(0, 3)], [(1, 0, d), (2, 1, f32(1e-6)), (3, 0, qkv_dim), (4, 0, hqk)]),
+        rec(2, (32, d), [(0, 5), (1, 3), (2, 6), (3, 7), (4, 9), (5, 10), (6, 11)], []),
+        rec(3, (hv, 1), [(0, 11), (1, 12), (2, 13), (3, 11)], []))
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, table, 4, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+    got = np.zeros(hv * d, np.float16)
+    ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, 11, C.c_size_t(0), got.ctypes.data_as(C.c_void_p), C.c_size_t(got.nbytes)))
+    st, act = oracle.conv1d_update_silu(conv_state, qkv_in, conv_w, qkv_dim, k)
+    scaled = oracle.rms_scale_qk(act, d, 1e-6, qkv_dim, hqk)
+    rst, core = oracle.deltanet_recurrence_decode(rec_state, scaled, b, a, a_log, dt, d, hv, hqk)
+    want = oracle.rms_norm_gated(core, z, norm_w, d, 1e-6, hv).reshape(-1)
+    err = float(np.max(np.abs(got.astype(F) - want.astype(F))) / np.sqrt(np.mean(want.astype(F) ** 2)))
+    assert err < 5e-3, err
