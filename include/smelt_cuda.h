@@ -500,6 +500,24 @@ SMELT_CUDA_API smelt_status smelt_cuda_prefill(smelt_cuda_ctx* ctx, const smelt_
                                                const int32_t* tokens, int n_tokens, int32_t start_pos, int chunk,
                                                int32_t* out_token);
 
+/* ── signed activation bit-planes (the Bonsai low-bit path) ──────────────────
+ * Producers (Resources/Shaders/signed_quant.metal:751-932): per group of 128 activations one fp16
+ * scale and a symmetric integer of n_planes bits as magnitude planes + a sign plane:
+ * planes uint32 [batch, cols/128, n_planes, 4], scales fp16 [batch, cols/128].  up_or_null != null
+ * (n_planes 5 only) is swiglu_signed_activation_bitplanes_i5_g128: x is the gate, the view is taken
+ * of the staged fp16 SwiGLU.  Consumers (:1300-1712, :1732-1822, :2054-2101): packed binary
+ * (format 1) or ternary (format 2) weights times the planes by popcount, exact integer dot per
+ * group scaled by activation scale and weight scale; mode 0 y = half(acc), 1 y = half(half(acc)
+ * + residual), 2 y = staged SwiGLU of the gate (codes) and up (codes2) results. */
+SMELT_CUDA_API smelt_status smelt_cuda_signed_activation_bitplanes(smelt_cuda_ctx* ctx, const void* x_dev, const void* up_or_null_dev,
+                                                                   void* planes_dev, void* scales_dev, int cols, int n_planes,
+                                                                   int batch);
+SMELT_CUDA_API smelt_status smelt_cuda_signed_bitplane_matvec(smelt_cuda_ctx* ctx, int format, int mode, const void* codes_dev,
+                                                              const void* weight_scales_dev, const void* codes2_dev,
+                                                              const void* weight_scales2_dev, const void* planes_dev,
+                                                              const void* act_scales_dev, const void* residual_dev, void* out_dev,
+                                                              int rows, int cols, int n_planes, int batch);
+
 /* ── DeltaNet decode step (hybrid linear-attention layers) ───────────────────
  * The four kernels between a DeltaNet layer's input projections and its output projection
  * (Sources/SmeltCompiler/DeltaNetPlugin.swift:196-318), also accepted as records under the

@@ -416,3 +416,37 @@ def rms_norm_gated(x, gate, weight, head_dim: int, eps: float, heads: int) -> np
     out = np.zeros((heads, head_dim), np.float16)
     _check(lib().so_rms_norm_gated(_p(_h(x)), _p(_h(gate)), _p(_h(weight)), _p(out), head_dim, C.c_float(eps), heads), "rms_norm_gated")
     return out
+
+
+# ── signed activation bit-planes (signed_quant.metal:751-2101) ──
+def signed_activation_bitplanes(x, cols: int, planes: int):
+    """Returns (planes uint32 [groups, planes, 4], scales fp16 [groups])."""
+    groups = cols // 128
+    out = np.zeros((groups, planes, 4), np.uint32)
+    sc = np.zeros(groups, np.float16)
+    _check(lib().so_signed_activation_bitplanes(_p(_h(x)), cols, planes, _p(out), _p(sc)), "signed_activation_bitplanes")
+    return out, sc
+
+
+def swiglu_signed_activation_bitplanes_i5(gate, up, cols: int):
+    groups = cols // 128
+    out = np.zeros((groups, 5, 4), np.uint32)
+    sc = np.zeros(groups, np.float16)
+    _check(lib().so_swiglu_signed_activation_bitplanes_i5(_p(_h(gate)), _p(_h(up)), cols, _p(out), _p(sc)), "swiglu_signed_activation_bitplanes_i5")
+    return out, sc
+
+
+def signed_bitplane_matvec(fmt: int, codes, weight_scales, planes_arr, act_scales, rows: int, cols: int, planes: int, residual=None) -> np.ndarray:
+    out = np.zeros(rows, np.float16)
+    pl = np.ascontiguousarray(planes_arr, dtype=np.uint32)
+    _check(lib().so_signed_bitplane_matvec(fmt, _p(_u8(codes)), _p(_h(weight_scales)), _p(pl), _p(_h(act_scales)),
+                                           _p(_h(residual)) if residual is not None else None, rows, cols, planes, _p(out)), "signed_bitplane_matvec")
+    return out
+
+
+def signed_bitplane_gate_up_swiglu(fmt: int, gc, gs, uc, us, planes_arr, act_scales, rows: int, cols: int, planes: int) -> np.ndarray:
+    out = np.zeros(rows, np.float16)
+    pl = np.ascontiguousarray(planes_arr, dtype=np.uint32)
+    _check(lib().so_signed_bitplane_gate_up_swiglu(fmt, _p(_u8(gc)), _p(_h(gs)), _p(_u8(uc)), _p(_h(us)), _p(pl), _p(_h(act_scales)), rows, cols, planes,
+                                                   _p(out)), "signed_bitplane_gate_up_swiglu")
+    return out

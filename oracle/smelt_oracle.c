@@ -1035,3 +1035,137 @@ SO_API int so_rms_norm_gated(const uint16_t *input, const uint16_t *gate, const 
     }
     return SO_OK;
 }
+
+/* ───────────────────── signed activation bit-planes (the Bonsai low-bit path) ─────────────────────
+ * Producers turn 128 activations into a sign plane and PLANES-1 magnitude planes of a symmetric
+ * integer quantisation plus one fp16 scale; consumers multiply the packed 1-bit / 2-bit weights
+ * with the planes by popcount.  Restated from Resources/Shaders/signed_quant.metal:751-932
+ * (producers) and :1300-1712, :1732-1822, :2054-2101 (consumers): the integer part is exact,
+ * the fp32 accumulation follows the kernels' lane partition (lane l owns groups l, l + 32, ...)
+ * and simd_sum's butterfly. */
+static inline int bitplane_max_q(int planes) { return (1 << (planes - 1)) - 1; } /* i2 1, i3 3, i4 7, i5 15, i6 31 */
+
+static int bitplane_group(const uint16_t *values, int planes, uint32_t *out_planes, uint16_t *out_scale) {
+    /* signed_quant.metal:757-795 (i4), :797-834 (i2, i3 quantise with the unrounded scale; i5, i6 and i4
+     * with the stored fp16 scale) */
+    const int max_q = bitplane_max_q(planes);
+    const int match_stored = planes >= 4;
+    float max_abs = 0.0f;
+    for (int i = 0; i < 128; ++i) max_abs = fmaxf(max_abs, fabsf(h2f(values[i])));
+    const float producer_scale = max_abs > 0.0f ? max_abs / (float)max_q : 1.0f;
+    const uint16_t stored = f2h(producer_scale);
+    const float scale = match_stored ? h2f(stored) : producer_scale;
+    *out_scale = stored;
+    for (int p = 0; p < planes * 4; ++p) out_planes[p] = 0u;
+    for (int w = 0; w < 4; ++w)
+        for (int lane = 0; lane < 32; ++lane) {
+            float v = h2f(values[w * 32 + lane]) / scale;
+            v = v < -(float)max_q ? -(float)max_q : (v > (float)max_q ? (float)max_q : v);
+            const int q = (int)roundf(v); /* round half away from zero, as Metal's round */
+            const unsigned mag = (unsigned)abs(q);
+            for (int p = 0; p < planes; ++p) {
+                const unsigned bit = p == planes - 1 ? (q < 0 ? 1u : 0u) : ((mag >> p) & 1u);
+                out_planes[p * 4 + w] |= bit << lane;
+            }
+        }
+    return SO_OK;
+}
+
+/* signed_activation_bitplanes_i{2..6}_g128: planes [groups, PLANES, 4] words, scales [groups]. */
+SO_API int so_signed_activation_bitplanes(const uint16_t *input, int cols, int planes, uint32_t *out_planes, uint16_t *out_scales) {
+    if (cols <= 0 || cols % 128 || planes < 2 || planes > 6) return SO_ERR_GEOMETRY;
+    for (int g = 0; g < cols / 128; ++g) bitplane_group(input + (size_t)g * 128, planes, out_planes + (size_t)g * planes * 4, out_scales + g);
+    return SO_OK;
+}
+
+/* swiglu_signed_activation_bitplanes_i5_g128 (signed_quant.metal:876-916): the staged fp16 SwiGLU
+ * of gate and up, then the i5 view. */
+SO_API int so_swiglu_signed_activation_bitplanes_i5(const uint16_t *gate, const uint16_t *up, int cols, uint32_t *out_planes,
+                                                    uint16_t *out_scales) {
+    if (cols <= 0 || cols % 128) return SO_ERR_GEOMETRY;
+    uint16_t v[128];
+    for (int g = 0; g < cols / 128; ++g) {
+        for (int i = 0; i < 128; ++i) v[i] = swiglu_staged_half(gate[(size_t)g * 128 + i], up[(size_t)g * 128 + i]);
+        bitplane_group(v, 5, out_planes + (size_t)g * 20, out_scales + g);
+    }
+    return SO_OK;
+}
+
+static inline int popc32(uint32_t v) { return __builtin_popcount(v); }
+
+/* Integer dot of one weight group with the planes: sum_bit 2^bit * (2 * agreements - active). */
+static inline int bitplane_group_dot(int format, const uint8_t *codes, const uint32_t *planes_g, int planes) {
+    uint32_t pos[4], neg[4];
+    if (format == 1) { /* binary: bit 1 = +1, bit 0 = -1; LSB first, 16 bytes per group */
+        memcpy(pos, codes, 16);
+        for (int w = 0; w < 4; ++w) neg[w] = ~pos[w];
+    } else { /* ternary: 2-bit codes 0 / 1 / 2 = -1 / 0 / +1, 32 bytes per group (signed_quant.metal:50-79) */
+        for (int w = 0; w < 4; ++w) {
+            pos[w] = neg[w] = 0u;
+            for (int i = 0; i < 32; ++i) {
+                const int idx = w * 32 + i;
+                const unsigned code = (codes[idx >> 2] >> ((idx & 3) * 2)) & 3u;
+                if (code == 2u) pos[w] |= 1u << i;
+                if (code == 0u) neg[w] |= 1u << i;
+            }
+        }
+    }
+    const uint32_t *sign = planes_g + (size_t)(planes - 1) * 4;
+    int dot = 0;
+    for (int bit = 0; bit + 1 < planes; ++bit) {
+        const uint32_t *mag = planes_g + (size_t)bit * 4;
+        int agree = 0, active = 0;
+        for (int w = 0; w < 4; ++w) {
+            agree += popc32(((pos[w] & ~sign[w]) | (neg[w] & sign[w])) & mag[w]);
+            active += popc32((pos[w] | neg[w]) & mag[w]);
+        }
+        dot += (1 << bit) * (2 * agree - active);
+    }
+    return dot;
+}
+
+static float bitplane_row_acc(int format, const uint8_t *row_codes, const uint16_t *row_scales, const uint32_t *planes_all,
+                              const uint16_t *act_scales, int groups, int planes) {
+    const int group_bytes = format == 1 ? 16 : 32;
+    float lane[32];
+    for (int l = 0; l < 32; ++l) {
+        float acc = 0.0f;
+        for (int g = l; g < groups; g += 32) {
+            const int dot = bitplane_group_dot(format, row_codes + (size_t)g * group_bytes, planes_all + (size_t)g * planes * 4, planes);
+            acc += (float)dot * h2f(act_scales[g]) * h2f(row_scales[g]);
+        }
+        lane[l] = acc;
+    }
+    return simd_sum32(lane);
+}
+
+/* signed_{binary,ternary}_bitplane_i{P}_matvec[_add]_g128_rows8: y[r] = half(acc), with a residual
+ * half(float(half(acc)) + residual[r]) (signed_quant.metal:1697-1710). */
+SO_API int so_signed_bitplane_matvec(int format, const uint8_t *codes, const uint16_t *weight_scales, const uint32_t *planes_all,
+                                     const uint16_t *act_scales, const uint16_t *residual, int rows, int cols, int planes, uint16_t *out) {
+    if ((format != 1 && format != 2) || rows <= 0 || cols <= 0 || cols % 128 || planes < 2 || planes > 6) return SO_ERR_GEOMETRY;
+    const int groups = cols / 128;
+    const size_t row_bytes = format == 1 ? (size_t)cols / 8 : (size_t)cols / 4;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const float acc = bitplane_row_acc(format, codes + (size_t)r * row_bytes, weight_scales + (size_t)r * groups, planes_all, act_scales, groups, planes);
+        out[r] = residual ? f2h(round_h(acc) + h2f(residual[r])) : f2h(acc);
+    }
+    return SO_OK;
+}
+
+/* signed_binary_bitplane_i{P}_gate_up_swiglu_g128_rows8 (signed_quant.metal:1732-1822). */
+SO_API int so_signed_bitplane_gate_up_swiglu(int format, const uint8_t *gate_codes, const uint16_t *gate_scales, const uint8_t *up_codes,
+                                             const uint16_t *up_scales, const uint32_t *planes_all, const uint16_t *act_scales, int rows,
+                                             int cols, int planes, uint16_t *out) {
+    if ((format != 1 && format != 2) || rows <= 0 || cols <= 0 || cols % 128 || planes < 2 || planes > 6) return SO_ERR_GEOMETRY;
+    const int groups = cols / 128;
+    const size_t row_bytes = format == 1 ? (size_t)cols / 8 : (size_t)cols / 4;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const float g = bitplane_row_acc(format, gate_codes + (size_t)r * row_bytes, gate_scales + (size_t)r * groups, planes_all, act_scales, groups, planes);
+        const float u = bitplane_row_acc(format, up_codes + (size_t)r * row_bytes, up_scales + (size_t)r * groups, planes_all, act_scales, groups, planes);
+        out[r] = swiglu_staged_half(f2h(g), f2h(u));
+    }
+    return SO_OK;
+}

@@ -124,6 +124,38 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"deltanet_recurrence_mlx_decode", PK_DELTANET_DECODE, 0, false},
         {"rms_norm_gated", PK_RMS_NORM_GATED, 0, false},
     };
+    // Activation bit-plane producers and consumers (Resources/Shaders/signed_quant.metal:751-2245):
+    // the plane count is part of the name.
+    {
+        int planes = 0, n = 0;
+        if (sscanf(name.c_str(), "signed_activation_bitplanes_i%d_g128%n", &planes, &n) == 1 && planes >= 2 && planes <= 6) {
+            const std::string rest = name.substr(n);
+            if (rest.empty() || rest == "_batched") {
+                p.kind = PK_BITPLANE_PRODUCER; p.planes = planes; p.batched = !rest.empty();
+                *out = p;
+                return true;
+            }
+        }
+        if (name == "swiglu_signed_activation_bitplanes_i5_g128") {
+            p.kind = PK_BITPLANE_SWIGLU_PRODUCER; p.planes = 5;
+            *out = p;
+            return true;
+        }
+        char kind[16] = {0};
+        if (sscanf(name.c_str(), "signed_%15[a-z]_bitplane_i%d_%n", kind, &planes, &n) == 2 && planes >= 2 && planes <= 6) {
+            const std::string fam = kind, rest = name.substr(n);
+            const int bits = fam == "binary" ? 1 : (fam == "ternary" ? 2 : 0);
+            PipeKind k = PK_NONE;
+            if (rest == "matvec_g128_rows8") k = PK_BITPLANE_MATVEC;
+            else if (rest == "matvec_add_g128_rows8" && bits == 1) k = PK_BITPLANE_ADD;
+            else if (rest == "gate_up_swiglu_g128_rows8") k = PK_BITPLANE_GATEUP;
+            if (bits && k != PK_NONE) {
+                p.kind = k; p.bits = bits; p.planes = planes;
+                *out = p;
+                return true;
+            }
+        }
+    }
     // Shape-specialised DeltaNet names carry their constants in the name
     // (Resources/Shaders/recurrence.metal:590-836, norms_gated_precise.metal:20-52).
     {
@@ -607,6 +639,60 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             NEED_BYTES(0, (size_t)heads * d * 2); NEED_BYTES(2, (size_t)heads * d * 2);
             in.launches += 1;
             return check_cuda(ctx, launch_per_head_rms_norm(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, heads, (int)d, as_f32(eps_bits)), "per_head_rms_norm");
+        }
+        case PK_BITPLANE_PRODUCER: {
+            // signed_quant.metal:757-762: 0 input [B, cols], 1 planes, 2 activation scales, 3 cols; one threadgroup per
+            // group, grid.y = rows of the batched form.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, cols);
+            const int rows = p.batched ? batch_of(rec) : 1;
+            if (cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a multiple of 128");
+            NEED_BYTES(0, (size_t)rows * cols * 2); NEED_BYTES(1, (size_t)rows * (cols / 128) * p.planes * 16); NEED_BYTES(2, (size_t)rows * (cols / 128) * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_bitplane_producer(l, (const __half*)r.buf[0].ptr, nullptr, (uint32_t*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)cols, p.planes, rows), p.name.c_str());
+        }
+        case PK_BITPLANE_SWIGLU_PRODUCER: {
+            // signed_quant.metal:876-883: 0 gate, 1 up, 2 planes, 3 activation scales, 4 cols.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(4, cols);
+            if (cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a multiple of 128");
+            NEED_BYTES(0, (size_t)cols * 2); NEED_BYTES(1, (size_t)cols * 2); NEED_BYTES(2, (size_t)(cols / 128) * 5 * 16); NEED_BYTES(3, (size_t)(cols / 128) * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_bitplane_producer(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (uint32_t*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)cols, 5, 1), p.name.c_str());
+        }
+        case PK_BITPLANE_MATVEC: case PK_BITPLANE_ADD: case PK_BITPLANE_GATEUP: {
+            // signed_quant.metal:1564-1572 (matvec: 0 codes, 1 weight scales, 2 planes, 3 activation scales, 4 out, 5 rows,
+            // 6 cols), :2246-2255 (add: 5 residual, 6 rows, 7 cols), :1823-1833 (gate/up: 0 gate codes, 1 gate scales,
+            // 2 up codes, 3 up scales, 4 planes, 5 activation scales, 6 out, 7 rows, 8 cols).
+            BitplaneArgs a = {};
+            a.format = p.bits; a.n_planes = p.planes; a.batch = 1;
+            int irows;
+            if (p.kind == PK_BITPLANE_GATEUP) {
+                for (int i = 0; i <= 6; ++i) if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": buffer bindings 0..6 are required");
+                a.mode = 2; a.codes = (const uint8_t*)r.buf[0].ptr; a.wscales = (const __half*)r.buf[1].ptr; a.codes2 = (const uint8_t*)r.buf[2].ptr; a.wscales2 = (const __half*)r.buf[3].ptr;
+                a.planes = (const uint32_t*)r.buf[4].ptr; a.ascales = (const __half*)r.buf[5].ptr; a.out = (__half*)r.buf[6].ptr;
+                irows = 7;
+            } else {
+                const int nb = p.kind == PK_BITPLANE_ADD ? 5 : 4;
+                for (int i = 0; i <= nb; ++i) if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a buffer binding is missing");
+                a.mode = p.kind == PK_BITPLANE_ADD ? 1 : 0;
+                a.codes = (const uint8_t*)r.buf[0].ptr; a.wscales = (const __half*)r.buf[1].ptr; a.planes = (const uint32_t*)r.buf[2].ptr; a.ascales = (const __half*)r.buf[3].ptr;
+                a.out = (__half*)r.buf[4].ptr;
+                if (a.mode == 1) a.residual = (const __half*)r.buf[5].ptr;
+                irows = nb + 1;
+            }
+            uint32_t rows = 0, cols = 0;
+            if (!host_u32(in, r, irows, &rows) || !host_u32(in, r, irows + 1, &cols)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": rows / cols constants are missing");
+            if (rows == 0 || cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a multiple of 128");
+            a.rows = (int)rows; a.cols = (int)cols;
+            const size_t wbytes = (size_t)rows * cols / (p.bits == 1 ? 8 : 4), sbytes = (size_t)rows * (cols / 128) * 2;
+            const int iplanes = a.mode == 2 ? 4 : 2;
+            if (r.buf[0].avail < wbytes || r.buf[1].avail < sbytes || (a.mode == 2 && (r.buf[2].avail < wbytes || r.buf[3].avail < sbytes)) ||
+                r.buf[iplanes].avail < (size_t)(cols / 128) * p.planes * 16 || r.buf[iplanes + 1].avail < (size_t)(cols / 128) * 2 || r.buf[iplanes + 2].avail < (size_t)rows * 2 ||
+                (a.mode == 1 && r.buf[5].avail < (size_t)rows * 2))
+                return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": a binding is smaller than the shape needs");
+            if ((reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.codes2) | reinterpret_cast<uintptr_t>(a.planes)) & 15u)
+                return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": codes and planes must be 16-byte aligned");
+            in.launches += 1;
+            return check_cuda(ctx, launch_bitplane_matvec(l, a), p.name.c_str());
         }
         case PK_CONV1D_SILU: {
             // conv1d.metal:271-278: 0 state [C, K] (in place), 1 new value [C], 2 weight [C, K], 3 out [C], 4 channels, 5 kernel size.

@@ -17,6 +17,22 @@ cudaError_t launch_kv_cache_update(const Launch& l, __half* cache, const __half*
 cudaError_t launch_rope_qkv_append(const Launch& l, __half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache, uint32_t capacity, int head_dim, int n_q, int n_kv, int layout, float base_log2, int batch, size_t seq_stride);
 cudaError_t launch_argmax_partials(const Launch& l, const __half* logits, uint64_t* partials, int vocab, int chunk, int batch);
 cudaError_t launch_argmax_reduce(const Launch& l, const uint64_t* partials, int32_t* out, int n, int batch, int out_stride);
+// Signed activation bit-planes (bitplane.cu)
+struct BitplaneArgs {
+    int format;              // 1 binary, 2 ternary
+    int mode;                // 0 plain, 1 + residual, 2 gate/up + SwiGLU
+    const uint8_t* codes;    // [rows, cols/8] or [rows, cols/4]
+    const __half* wscales;   // [rows, cols/128]
+    const uint8_t* codes2;   // mode 2: the up matrix
+    const __half* wscales2;
+    const uint32_t* planes;  // [batch, cols/128, n_planes, 4]
+    const __half* ascales;   // [batch, cols/128]
+    const __half* residual;  // mode 1: [batch, rows]
+    __half* out;             // [batch, rows]
+    int rows, cols, n_planes, batch;
+};
+cudaError_t launch_bitplane_producer(const Launch& l, const __half* x, const __half* up, uint32_t* planes, __half* scales, int cols, int n_planes, int batch);
+cudaError_t launch_bitplane_matvec(const Launch& l, const BitplaneArgs& a);
 // DeltaNet decode step (deltanet.cu)
 cudaError_t launch_conv1d_update_silu(const Launch& l, __half* state, const __half* new_val, const __half* weight, __half* out, int channels, int kernel_size);
 cudaError_t launch_rms_scale_qk(const Launch& l, __half* qkv, int head_dim, float eps, int qkv_dim, int qk_heads, int batch);

@@ -52,6 +52,11 @@ enum PipeKind : int {
     PK_RMS_SCALE_QK,
     PK_DELTANET_DECODE,
     PK_RMS_NORM_GATED,
+    PK_BITPLANE_PRODUCER,
+    PK_BITPLANE_SWIGLU_PRODUCER,
+    PK_BITPLANE_MATVEC,
+    PK_BITPLANE_ADD,
+    PK_BITPLANE_GATEUP,
 };
 
 struct Pipeline {
@@ -61,6 +66,7 @@ struct Pipeline {
     bool fixed_shape = false;            // rows come from the name, no numRows constant
     bool batched = false;                // x is [B, C], an actualBatch constant is bound
     int bits = 0;                        // signed kernels: 1 or 2
+    int planes = 0;                      // activation bit-plane kernels: planes of the view (2..6)
     int n_q = 0, n_kv = 0, head_dim = 0; // shape-specialised attention names
 };
 
