@@ -100,7 +100,7 @@ __device__ __forceinline__ float simd_sum(float v) {  // simd_sum's butterfly: l
 }
 
 // MODE 0 plain, 1 + residual, 2 gate/up + SwiGLU.  ROWS weight rows per warp.
-template <int PLANES, bool TERNARY, int MODE, int ROWS>
+template <int PLANES, bool TERNARY, int MODE, int ROWS, int U>
 __global__ void __launch_bounds__(256) bitplane_matvec_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ wscales,
                                                               const uint8_t* __restrict__ codes2, const __half* __restrict__ wscales2,
                                                               const uint32_t* __restrict__ planes, const __half* __restrict__ ascales,
@@ -122,44 +122,66 @@ __global__ void __launch_bounds__(256) bitplane_matvec_kernel(const uint8_t* __r
     for (int m = 0; m < NM; ++m)
 #pragma unroll
         for (int t = 0; t < ROWS; ++t) acc[m][t] = 0.0f;
-    for (int g = lane; g < groups; g += 32) {
-        uint4 pl[PLANES];
+    // U of the lane's groups per round: every load of the round is requested before any is used;
+    // the sums still take the groups in ascending order.
+    for (int g0 = lane; g0 < groups; g0 += 32 * U) {
+        uint4 pl[U][PLANES], wa[U][NM][ROWS], wb[U][NM][ROWS];
+        float as[U], ws[U][NM][ROWS];
 #pragma unroll
-        for (int p = 0; p < PLANES; ++p) pl[p] = *reinterpret_cast<const uint4*>(planes + ((size_t)g * PLANES + p) * 4);
-        const uint4 sign = pl[PLANES - 1];
-        const float as = __half2float(ascales[g]);
+        for (int u = 0; u < U; ++u) {
+            const int g = g0 + 32 * u;
+            if (g >= groups) continue;
 #pragma unroll
-        for (int m = 0; m < NM; ++m) {
-            const uint8_t* cm = m == 0 ? codes : codes2;
-            const __half* sm = m == 0 ? wscales : wscales2;
+            for (int p = 0; p < PLANES; ++p) pl[u][p] = *reinterpret_cast<const uint4*>(planes + ((size_t)g * PLANES + p) * 4);
+            as[u] = __half2float(ascales[g]);
 #pragma unroll
-            for (int t = 0; t < ROWS; ++t) {
-                const int row = row0 + t;
-                if (row >= rows) continue;
-                uint4 pos, neg;
-                if (TERNARY) {
-                    const uint4 a = *reinterpret_cast<const uint4*>(cm + row * row_bytes + (size_t)g * 32);
-                    const uint4 c = *reinterpret_cast<const uint4*>(cm + row * row_bytes + (size_t)g * 32 + 16);
-                    ternary_masks32(a.x, a.y, pos.x, neg.x); ternary_masks32(a.z, a.w, pos.y, neg.y);
-                    ternary_masks32(c.x, c.y, pos.z, neg.z); ternary_masks32(c.z, c.w, pos.w, neg.w);
-                } else {
-                    pos = *reinterpret_cast<const uint4*>(cm + row * row_bytes + (size_t)g * 16);
-                    neg = make_uint4(~pos.x, ~pos.y, ~pos.z, ~pos.w);
+            for (int m = 0; m < NM; ++m) {
+                const uint8_t* cm = m == 0 ? codes : codes2;
+                const __half* sm = m == 0 ? wscales : wscales2;
+#pragma unroll
+                for (int t = 0; t < ROWS; ++t) {
+                    const int row = row0 + t;
+                    if (row >= rows) continue;
+                    const uint8_t* src = cm + row * row_bytes + (size_t)g * (TERNARY ? 32 : 16);
+                    wa[u][m][t] = *reinterpret_cast<const uint4*>(src);
+                    if (TERNARY) wb[u][m][t] = *reinterpret_cast<const uint4*>(src + 16);
+                    ws[u][m][t] = __half2float(sm[(size_t)row * groups + g]);
                 }
-                const uint4 agree = make_uint4((pos.x & ~sign.x) | (neg.x & sign.x), (pos.y & ~sign.y) | (neg.y & sign.y),
-                                               (pos.z & ~sign.z) | (neg.z & sign.z), (pos.w & ~sign.w) | (neg.w & sign.w));
-                int dot = 0;
-#pragma unroll
-                for (int bit = 0; bit < PLANES - 1; ++bit) {
-                    const uint4 mag = pl[bit];
-                    const int ag = __popc(agree.x & mag.x) + __popc(agree.y & mag.y) + __popc(agree.z & mag.z) + __popc(agree.w & mag.w);
-                    int active;
-                    if (TERNARY) active = __popc((pos.x | neg.x) & mag.x) + __popc((pos.y | neg.y) & mag.y) + __popc((pos.z | neg.z) & mag.z) + __popc((pos.w | neg.w) & mag.w);
-                    else active = __popc(mag.x) + __popc(mag.y) + __popc(mag.z) + __popc(mag.w);
-                    dot += (2 * ag - active) << bit;
-                }
-                acc[m][t] = __fadd_rn(acc[m][t], __fmul_rn(__fmul_rn((float)dot, as), __half2float(sm[(size_t)row * groups + g])));
             }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int g = g0 + 32 * u;
+            if (g >= groups) continue;
+            const uint4 sign = pl[u][PLANES - 1];
+#pragma unroll
+            for (int m = 0; m < NM; ++m)
+#pragma unroll
+                for (int t = 0; t < ROWS; ++t) {
+                    if (row0 + t >= rows) continue;
+                    uint4 pos, neg;
+                    if (TERNARY) {
+                        const uint4 a = wa[u][m][t], c = wb[u][m][t];
+                        ternary_masks32(a.x, a.y, pos.x, neg.x); ternary_masks32(a.z, a.w, pos.y, neg.y);
+                        ternary_masks32(c.x, c.y, pos.z, neg.z); ternary_masks32(c.z, c.w, pos.w, neg.w);
+                    } else {
+                        pos = wa[u][m][t];
+                        neg = make_uint4(~pos.x, ~pos.y, ~pos.z, ~pos.w);
+                    }
+                    const uint4 agree = make_uint4((pos.x & ~sign.x) | (neg.x & sign.x), (pos.y & ~sign.y) | (neg.y & sign.y),
+                                                   (pos.z & ~sign.z) | (neg.z & sign.z), (pos.w & ~sign.w) | (neg.w & sign.w));
+                    int dot = 0;
+#pragma unroll
+                    for (int bit = 0; bit < PLANES - 1; ++bit) {
+                        const uint4 mag = pl[u][bit];
+                        const int ag = __popc(agree.x & mag.x) + __popc(agree.y & mag.y) + __popc(agree.z & mag.z) + __popc(agree.w & mag.w);
+                        int active;
+                        if (TERNARY) active = __popc((pos.x | neg.x) & mag.x) + __popc((pos.y | neg.y) & mag.y) + __popc((pos.z | neg.z) & mag.z) + __popc((pos.w | neg.w) & mag.w);
+                        else active = __popc(mag.x) + __popc(mag.y) + __popc(mag.z) + __popc(mag.w);
+                        dot += (2 * ag - active) << bit;
+                    }
+                    acc[m][t] = __fadd_rn(acc[m][t], __fmul_rn(__fmul_rn((float)dot, as[u]), ws[u][m][t]));
+                }
         }
     }
 #pragma unroll
@@ -201,16 +223,26 @@ cudaError_t launch_producer_t(const Launch& l, const __half* x, const __half* up
     return cudaLaunchKernelEx(&cfg, k, x, up, planes, scales, cols, dev_dyn(l));
 }
 
-template <int PLANES, bool TERNARY, int MODE>
-cudaError_t launch_consumer_t(const Launch& l, const BitplaneArgs& a) {
-    constexpr int ROWS = TERNARY ? 1 : 4;  // the reference's rows per simdgroup: the lane partition is part of the arithmetic
+template <int PLANES, bool TERNARY, int MODE, int ROWS, int U>
+cudaError_t launch_consumer_r(const Launch& l, const BitplaneArgs& a) {
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     const int warps = (a.rows + ROWS - 1) / ROWS;
     cfg_launch(l, cfg, attr, dim3((warps + 7) / 8, a.batch), dim3(256));
-    auto k = bitplane_matvec_kernel<PLANES, TERNARY, MODE, ROWS>;
+    auto k = bitplane_matvec_kernel<PLANES, TERNARY, MODE, ROWS, U>;
     prefer_max_shared(k);
     return cudaLaunchKernelEx(&cfg, k, a.codes, a.wscales, a.codes2, a.wscales2, a.planes, a.ascales, a.residual, a.out, a.rows, a.cols, dev_dyn(l));
+}
+
+// A row's arithmetic does not depend on how many rows share a warp (lane l owns the row's groups
+// l, l + 32, ... either way).  Short rows (up to 64 groups) of binary weights: four rows per warp
+// share the plane loads, which outweigh the 16 bytes of weights per group; long rows: one row per
+// warp and two groups in flight per lane (measured 13.2 against 22.0 us at 5120 x 17408).
+template <int PLANES, bool TERNARY, int MODE>
+cudaError_t launch_consumer_t(const Launch& l, const BitplaneArgs& a) {
+    if (TERNARY) return launch_consumer_r<PLANES, true, MODE, 1, 1>(l, a);
+    if (a.cols / 128 <= 64) return launch_consumer_r<PLANES, false, MODE, 4, 1>(l, a);
+    return launch_consumer_r<PLANES, false, MODE, 1, 2>(l, a);
 }
 
 template <bool TERNARY, int MODE>
