@@ -42,29 +42,6 @@ __host__ __device__ inline ImmaLayout imma_layout(int nw, int depth, int warps, 
     return L;
 }
 
-// D = A (u8, 16 x 32) * B (s8, 32 x 8) + C; C may name one register four times.
-__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1, int c0, int c1, int c2, int c3) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
-}
-
-__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-
-// Largest |v| of the eight fp16 values in a 16-byte word, as a float.
-__device__ __forceinline__ float amax8(const uint4& v) {
-    const __half2 m = __hmax2(__hmax2(__habs2(u32_as_h2(v.x)), __habs2(u32_as_h2(v.y))),
-                              __hmax2(__habs2(u32_as_h2(v.z)), __habs2(u32_as_h2(v.w))));
-    const float2 f = __half22float2(m);
-    return fmaxf(f.x, f.y);
-}
-
 // X (|X| < 2^27) as four base-128 digits packed one per byte, least significant first: the low
 // three are the 7-bit fields of the two's-complement value (0..127), the top one is X >> 21
 // (signed).  Every byte is a valid s8 and X = sum digit_k * 128^k.

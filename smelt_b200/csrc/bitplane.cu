@@ -25,14 +25,6 @@ namespace smelt {
 
 namespace {
 
-__device__ __forceinline__ __half swiglu_staged_half(__half gate, __half up) {  // signed_quant.metal:15-20
-    const float g = __half2float(gate);
-    const __half e = __float2half_rn(expf(fabsf(g)));
-    const __half tail = __float2half_rn(1.0f / __half2float(__float2half_rn(1.0f + __half2float(e))));
-    const __half sig = g < 0.0f ? tail : __float2half_rn(1.0f - __half2float(tail));
-    const __half act = __float2half_rn(g * __half2float(sig));
-    return __hmul(act, up);
-}
 
 // One warp per (group, batch row).  SWIGLU: the values are swiglu_staged(gate, up) instead of x.
 template <int PLANES, bool SWIGLU>
@@ -52,7 +44,7 @@ __global__ void __launch_bounds__(128) bitplane_producer_kernel(const __half* x,
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
         __half h = x[base + w * 32 + lane];
-        if (SWIGLU) h = swiglu_staged_half(h, up[base + w * 32 + lane]);
+        if (SWIGLU) h = swiglu_staged(h, up[base + w * 32 + lane]);
         v[w] = __half2float(h);
         max_abs = fmaxf(max_abs, fabsf(v[w]));
     }
@@ -93,11 +85,6 @@ __device__ __forceinline__ void ternary_masks32(uint32_t w0, uint32_t w1, uint32
     neg = compact_even_bits(~(h0 | l0)) | (compact_even_bits(~(h1 | l1)) << 16);
 }
 
-__device__ __forceinline__ float simd_sum(float v) {  // simd_sum's butterfly: lane distance 16, 8, 4, 2, 1
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-    return v;
-}
 
 // MODE 0 plain, 1 + residual, 2 gate/up + SwiGLU.  ROWS weight rows per warp.
 template <int PLANES, bool TERNARY, int MODE, int ROWS, int U>
@@ -187,7 +174,7 @@ __global__ void __launch_bounds__(256) bitplane_matvec_kernel(const uint8_t* __r
 #pragma unroll
     for (int m = 0; m < NM; ++m)
 #pragma unroll
-        for (int t = 0; t < ROWS; ++t) acc[m][t] = simd_sum(acc[m][t]);
+        for (int t = 0; t < ROWS; ++t) acc[m][t] = simd_sum_lane0(acc[m][t]);
     if (lane == 0) {
 #pragma unroll
         for (int t = 0; t < ROWS; ++t) {
@@ -196,7 +183,7 @@ __global__ void __launch_bounds__(256) bitplane_matvec_kernel(const uint8_t* __r
             const size_t o = b * rows + row;
             if (MODE == 0) out[o] = __float2half_rn(acc[0][t]);
             else if (MODE == 1) out[o] = __float2half_rn(__half2float(__float2half_rn(acc[0][t])) + __half2float(residual[o]));
-            else out[o] = swiglu_staged_half(__float2half_rn(acc[0][t]), __float2half_rn(acc[NM - 1][t]));
+            else out[o] = swiglu_staged(__float2half_rn(acc[0][t]), __float2half_rn(acc[NM - 1][t]));
         }
     }
 }

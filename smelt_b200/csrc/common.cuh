@@ -204,6 +204,49 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// 4- and 8-byte asynchronous global -> shared copies (scales and biases beside streamed weights).
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+// D = A (u8, 16 x 32) * B (s8, 32 x 8) + C; C may name one register four times.
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1, int c0, int c1, int c2, int c3) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+
+// Largest |v| of the eight fp16 values in a 16-byte word, as a float.
+__device__ __forceinline__ float amax8(const uint4& v) {
+    const __half2 m = __hmax2(__hmax2(__habs2(u32_as_h2(v.x)), __habs2(u32_as_h2(v.y))),
+                              __hmax2(__habs2(u32_as_h2(v.z)), __habs2(u32_as_h2(v.w))));
+    const float2 f = __half22float2(m);
+    return fmaxf(f.x, f.y);
+}
+
+// The staged fp16 SwiGLU of the reference (Resources/Shaders/activations_precise.metal:9-22,
+// signed_quant.metal:15-20): tail = 1 / (1 + exp(|g|)), sigmoid = g < 0 ? tail : 1 - tail,
+// out = (g * sigmoid) * up, every intermediate an fp16 value; the fp16 exp is half(expf(float)).
+__device__ __forceinline__ __half swiglu_staged(__half gate, __half up) {
+    const float gf = __half2float(gate);
+    const __half e = __float2half_rn(expf(fabsf(gf)));
+    const __half denom = __hadd(__float2half_rn(1.0f), e);
+    const __half tail = __hdiv(__float2half_rn(1.0f), denom);
+    const __half sig = gf < 0.f ? tail : __hsub(__float2half_rn(1.0f), tail);
+    return __hmul(__hmul(gate, sig), up);
+}
+
+// Metal's simd_sum as a butterfly over lane distance 16, 8, 4, 2, 1; the total is in lane 0.
+__device__ __forceinline__ float simd_sum_lane0(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+    return v;
+}
+
 // Error word shared by all kernels of a context: 0 = ok; kernels OR in a code when a bounded
 // wait gives up so the host can report it instead of hanging.
 enum : uint32_t { KERR_BARRIER_TIMEOUT = 1u, KERR_FLAG_TIMEOUT = 2u };

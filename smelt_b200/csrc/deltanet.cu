@@ -92,12 +92,6 @@ __device__ __forceinline__ float softplus_staged_half(__half x) {
     const __half d = __float2half_rn(mn - mx);
     return __half2float(__float2half_rn(mx + decode_log1p(__half2float(exp_half(d)))));
 }
-// simd_sum's butterfly: lane distance 16, 8, 4, 2, 1
-__device__ __forceinline__ float simd_sum(float v) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-    return __shfl_sync(0xffffffffu, v, 0);
-}
 
 template <int EPL>
 __global__ void __launch_bounds__(256) deltanet_recurrence_decode_kernel(__half* state, const __half* qkv, const __half* b_proj,
@@ -126,7 +120,7 @@ __global__ void __launch_bounds__(256) deltanet_recurrence_decode_kernel(__half*
         st[i] = __fmul_rn(st[i], decay);
         kv = __fadd_rn(kv, __fmul_rn(st[i], kr[i]));
     }
-    kv = simd_sum(kv);
+    kv = __shfl_sync(0xffffffffu, simd_sum_lane0(kv), 0);
     const float delta = __fmul_rn(__fsub_rn(__half2float(qkv[(size_t)2 * qk_heads * D + (size_t)head * D + dv]), kv), beta);
     float o = 0.0f;
 #pragma unroll
@@ -134,7 +128,7 @@ __global__ void __launch_bounds__(256) deltanet_recurrence_decode_kernel(__half*
         st[i] = __fadd_rn(st[i], __fmul_rn(kr[i], delta));
         o = __fadd_rn(o, __fmul_rn(st[i], qr[i]));
     }
-    o = simd_sum(o);
+    o = simd_sum_lane0(o);
     if (lane == 0) out[(size_t)head * D + dv] = __float2half_rn(o);
 #pragma unroll
     for (int i = 0; i < EPL; ++i) row[i] = __float2half_rn(st[i]);

@@ -99,17 +99,6 @@ __global__ void elementwise_add_kernel(const __half* a, const __half* b, __half*
     if (i < n) y[i] = __hadd(a[i], b[i]);
 }
 
-// swiglu_fused (Resources/Shaders/activations_precise.metal:9-22): every intermediate is an
-// fp16 value.  The fp16 exp is evaluated as half(expf(float)).
-__device__ __forceinline__ __half swiglu_staged(__half gate, __half up) {
-    const float gf = __half2float(gate);
-    const __half e = __float2half_rn(expf(fabsf(gf)));
-    const __half denom = __hadd(__float2half_rn(1.0f), e);
-    const __half tail = __hdiv(__float2half_rn(1.0f), denom);
-    const __half sig = gf < 0.f ? tail : __hsub(__float2half_rn(1.0f), tail);
-    const __half act = __hmul(gate, sig);
-    return __hmul(act, up);
-}
 
 __global__ void swiglu_fused_kernel(const __half* gate, const __half* up, __half* y, int64_t n, DevDyn dyn) {
     pdl_trigger();

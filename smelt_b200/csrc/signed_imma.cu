@@ -67,24 +67,6 @@ __host__ __device__ inline SignedLayout signed_layout(int nw, int set_bytes, int
     return L;
 }
 
-__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1, int c0, int c1, int c2, int c3) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
-}
-
-__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-
-__device__ __forceinline__ float amax8(const uint4& v) {
-    const __half2 m = __hmax2(__hmax2(__habs2(u32_as_h2(v.x)), __habs2(u32_as_h2(v.y))),
-                              __hmax2(__habs2(u32_as_h2(v.z)), __habs2(u32_as_h2(v.w))));
-    const float2 f = __half22float2(m);
-    return fmaxf(f.x, f.y);
-}
-
 // Four signed base-128 digits of X (|X| < 2^27), least significant first.
 __device__ __forceinline__ void digits128(int X, int (&d)[4]) {
 #pragma unroll
@@ -95,15 +77,6 @@ __device__ __forceinline__ void digits128(int X, int (&d)[4]) {
     d[3] = X;
 }
 
-__device__ __forceinline__ __half swiglu_staged(__half gate, __half up) {
-    // Resources/Shaders/signed_quant.metal:15-20 — every intermediate is an fp16 value.
-    const float gf = __half2float(gate);
-    const __half e = __float2half_rn(expf(fabsf(gf)));
-    const __half denom = __hadd(__float2half_rn(1.0f), e);
-    const __half tail = __hdiv(__float2half_rn(1.0f), denom);
-    const __half sig = gf < 0.f ? tail : __hsub(__float2half_rn(1.0f), tail);
-    return __hmul(__hmul(gate, sig), up);
-}
 
 template <int BITS, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) signed_imma_kernel(const SignedArgs a, int tiles_total, DevDyn dyn) {

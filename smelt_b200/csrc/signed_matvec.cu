@@ -21,15 +21,6 @@ namespace {
 
 constexpr int kGroup = 128;
 
-__device__ __forceinline__ __half swiglu_staged_h(__half gate, __half up) {
-    // Resources/Shaders/signed_quant.metal:15-20 — every intermediate is an fp16 value.
-    const float gf = __half2float(gate);
-    const __half e = __float2half_rn(expf(fabsf(gf)));
-    const __half denom = __hadd(__float2half_rn(1.0f), e);
-    const __half tail = __hdiv(__float2half_rn(1.0f), denom);
-    const __half sig = gf < 0.f ? tail : __hsub(__float2half_rn(1.0f), tail);
-    return __hmul(__hmul(gate, sig), up);
-}
 
 template <int BITS>
 __device__ __forceinline__ float word_dot(uint32_t w, const float* __restrict__ xs) {
@@ -93,7 +84,7 @@ __global__ void __launch_bounds__(256) signed_matvec_kernel(SignedArgs a, DevDyn
         if (MODE == kSignedPlain) a.y[o] = __float2half_rn(v0);
         else if (MODE == kSignedAdd)  // signed_quant.metal:271-278: half(float(half(acc)) + float(residual))
             a.y[o] = __float2half_rn(__half2float(__float2half_rn(v0)) + __half2float(a.residual[o]));
-        else a.y[o] = swiglu_staged_h(__float2half_rn(v0), __float2half_rn(v1));
+        else a.y[o] = swiglu_staged(__float2half_rn(v0), __float2half_rn(v1));
     }
 }
 
