@@ -449,6 +449,11 @@ cudaError_t launch_group(const Launch& l, const AffineArgs& a, int group) {
 
 cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int group) {
     if (args.rows <= 0 || args.cols <= 0 || args.batch <= 0 || args.cols % group != 0) return cudaErrorInvalidValue;
+    if (args.batch > 64) {  // tcgen05 QMM, wide form: the weights are expanded once per 512 batch rows
+        bool handled = false;
+        cudaError_t e = launch_affine_qmm_wide(l, mode, args, group, &handled);
+        if (handled || e != cudaSuccess) return e;
+    }
     if (args.batch >= 17) {  // tcgen05 QMM: the weights cross HBM once per 64 batch rows
         bool handled = false;
         cudaError_t e = launch_affine_qmm(l, mode, args, group, &handled);

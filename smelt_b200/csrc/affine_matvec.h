@@ -52,6 +52,8 @@ cudaError_t launch_affine(const Launch& l, int mode, const AffineArgs& args, int
 cudaError_t launch_affine_stream(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
 // Tensor-memory QMM for batches of seventeen rows and more (affine_qmm.cu).
 cudaError_t launch_affine_qmm(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
+// Wide-batch form (more than 64 rows of x): accumulates all of K in tensor memory (affine_qmm_wide.cu).
+cudaError_t launch_affine_qmm_wide(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
 cudaError_t launch_affine_imma(const Launch& l, int mode, const AffineArgs& args, int group, bool* handled);
 
 }  // namespace smelt

@@ -30,6 +30,7 @@
 // Every wait is bounded: a barrier that does not complete sets bit 10 of the error word and
 // the CTA drains its copies, frees its tensor memory and leaves.
 #include "affine_matvec.h"
+#include "tcgen05.cuh"
 
 namespace smelt {
 
@@ -64,55 +65,6 @@ __host__ __device__ inline QmmLayout qmm_layout(int nw, int nb) {
     return L;
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait on an mbarrier phase: polls without suspending (test_wait), gives up after about
-// half a second and reports failure instead of spinning forever.
-__device__ __forceinline__ bool mbar_poll_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 23); ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if (i > 64) __nanosleep(32);
-    }
-    return false;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// K-major operand tile, rows of 64 fp16 = 128 bytes, 128-byte swizzle: eight rows form a
-// 1024-byte atom, atoms follow one another along the rows (stride 1024 bytes).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// D[128 x N] (+)= A[128 x 16] . B[N x 16]^T, fp16 operands from shared memory, fp32 in tensor memory.
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-
 // Eight nibbles of a packed word (columns c .. c+7, low nibble first) as four half2 of exact
 // integers in column order {c, c+1}, {c+2, c+3}, {c+4, c+5}, {c+6, c+7}.
 __device__ __forceinline__ void nibbles_to_half(uint32_t w, uint32_t (&p)[4]) {
@@ -144,6 +96,7 @@ __global__ void __launch_bounds__(kThreads, 1) affine_qmm_kernel(const AffineArg
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L.bars);      // [2]: producers -> issuer (tiles of a block are written)
     uint64_t* done_bar = full_bar + kTileStages;                          // [2]: tensor core -> producers (the block's MMAs are complete)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + kTileStages);
+    uint32_t* s_dead = tmem_slot + 2;
     float* xsum = reinterpret_cast<float*>(smem + L.xsum);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row0 = (int)blockIdx.x * kRowsPerCta;
@@ -156,6 +109,7 @@ __global__ void __launch_bounds__(kThreads, 1) affine_qmm_kernel(const AffineArg
 
     if (tid == 0) {
         for (int i = 0; i < kTileStages; ++i) { mbar_init(&full_bar[i], kProducers / 32); mbar_init(&done_bar[i], 1); }
+        *s_dead = 0u;
         mbar_fence_init();
     }
     if (warp == kProducers / 32) {  // the issuing warp owns the tensor-memory allocation
@@ -310,6 +264,10 @@ __global__ void __launch_bounds__(kThreads, 1) affine_qmm_kernel(const AffineArg
         if (!dead && nblocks >= 2) { wait_done(nblocks - 2); if (!dead) drain(nblocks - 2, sc_hist[1], bi_hist[1]); }
         if (!dead) { wait_done(nblocks - 1); if (!dead) drain(nblocks - 1, sc_hist[0], bi_hist[0]); }
         cp_async_wait<0>();
+        // a wait that gave up in one thread stops the whole CTA: the barriers below need every producer
+        if (dead) atomicOr(s_dead, 1u);
+        asm volatile("bar.sync 1, %0;" ::"r"(kProducers) : "memory");
+        dead = *reinterpret_cast<volatile uint32_t*>(s_dead) != 0u;
         // ── epilogue: this thread holds row r, batch rows h * CPT ... ──
         const int row = row0 + r;
         bool finish = !dead;

@@ -82,7 +82,7 @@ smelt_status smelt_cuda_create(int device_ordinal, smelt_cuda_ctx** out_ctx) {
     ctx->attn_scratch_bytes = attention_scratch_bytes(64, 256, 8, attention_max_splits());
     ok = ok && cudaMalloc(&ctx->attn_scratch, ctx->attn_scratch_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->rope_table, 256 * sizeof(float)) == cudaSuccess;
-    ctx->qmm_scratch_bytes = (size_t)24 << 20;  // 148 CTAs x two matrices x 64 batch rows x 128 rows of fp32, with room to spare
+    ctx->qmm_scratch_bytes = (size_t)40 << 20;  // 148 CTAs x 512 batch rows x 128 rows of fp32 (the wide QMM's split-K partials), with room to spare
     ok = ok && cudaMalloc(&ctx->qmm_scratch, ctx->qmm_scratch_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->qmm_counters, 4096 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(ctx->qmm_counters, 0, 4096 * sizeof(int)) == cudaSuccess;

@@ -139,12 +139,14 @@ def test_config1_layer_set(ctx, oracle, batch):
             b.free()
 
 
-# batches of seventeen rows and more run on the tcgen05 QMM (weights on the MMA's M, batch on its N)
-@pytest.mark.parametrize("batch", [17, 32, 33, 64, 128, 200, 512])
-@pytest.mark.parametrize("rows,cols", [(2048, 2048), (200, 512), (2048, 6144)])
+# batches of seventeen rows and more run on the tcgen05 QMMs (weights on the MMA's M, batch on its N): up to 64 rows
+# with one accumulator slot per group drained in fp32, beyond that with every K step accumulated in tensor memory
+@pytest.mark.parametrize("batch", [17, 32, 33, 64, 65, 100, 128, 200, 300, 512, 600])
+@pytest.mark.parametrize("rows,cols", [(2048, 2048), (200, 512), (192, 512), (2048, 6144)])
 def test_affine_qmm_modes(ctx, oracle, rows, cols, batch):
     """agent_affine_qmm_fixed_batched_full and the fused gate/up QMM (agent_affine_qmm.h:107-316, :360-742)
-    at M = 17 ... 512: every epilogue, a row tail (200 rows), a long K, passes of 128 batch rows."""
+    at M = 17 ... 600: every epilogue, row tails (200 and 192 rows: the paired wide form needs a multiple of 64),
+    a long K, two chunks of 256 batch rows, a second pass beyond 512."""
     if batch > 128 and cols == 6144:
         pytest.skip("the long-K case is covered up to 128 rows")
     a = synth.affine_u4(33, "qa", rows, cols, 64)
