@@ -27,6 +27,11 @@
 // Matrices with few row tiles split K over gridDim.y CTAs (fp32 partials, ticket, ordered sum).
 // Every wait is bounded: on expiry the CTA sets bit 10 of the error word, drains its copies,
 // frees its tensor memory and returns.
+//
+// What bounds it (ncu at M = 512, gate/up 12288 x 4096: tensor pipe 38 % busy, 59 % while a wave
+// runs): shared-memory bandwidth.  Per 64-column block the MMAs read A_hi + A_lo once per chunk and
+// the B tile once for hi and once for lo, 192 KB, and the producers store 96 KB: about 137 bytes
+// per clock against the SM's 128.  A two-CTA MMA (cta_group::2) would halve the B traffic per SM.
 #include "affine_matvec.h"
 #include "tcgen05.cuh"
 
@@ -37,7 +42,7 @@ namespace {
 constexpr int kRows = 128;
 constexpr int kBlockCols = 64;
 constexpr int kStageCols = 256;
-constexpr int kProducers = 256;
+constexpr int kProducers = 256;                          // eight warps (sixteen measured 364 / 217 / 90 us against 334 / 262 / 78 at M = 512: no clear gain)
 constexpr int kThreads = kProducers + 32;
 constexpr int kRawSliceBytes = 64 + 8 + 8;               // per producer thread and stage: 64 packed bytes + 4 scales + 4 biases
 constexpr int kRawStageBytes = kProducers * kRawSliceBytes;
