@@ -189,10 +189,11 @@ __global__ void __launch_bounds__(kThreads, 1) affine_qmm_wide_kernel(const Affi
                 const int u = kb * nchunks + ch, slot = u % kBSlots, use = u / kBSlots;
                 if (use >= 1 && !mbar_poll_bounded(&done_b[slot], (uint32_t)((use - 1) & 1))) { dead = true; break; }
                 uint8_t* b_tile = smem + L.b_tiles + (size_t)slot * kBTileBytes;
+                const int n_cols = min(kChunk, m_pad - ch * kChunk);  // rows of the tile the MMA reads
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int q = tid + kProducers * i, n = q >> 3, c = q & 7;
-                    *reinterpret_cast<uint4*>(b_tile + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4)) = xreg[i];
+                    if (n < n_cols) *reinterpret_cast<uint4*>(b_tile + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4)) = xreg[i];
                 }
                 load_x(u + 1, xreg);
                 fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
