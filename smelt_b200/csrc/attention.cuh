@@ -164,6 +164,24 @@ __host__ __device__ constexpr size_t attn_ring_bytes() {
     return (size_t)kAttnWarps * NU * (D / 16) * 512;
 }
 
+// Shared memory of a CTA: the rings plus the RoPE prologue's scratch (up to 16 rotated query heads)
+// during the key loop and the warps' merge area [8][heads][D + 2] afterwards, in the same bytes;
+// behind both, where no phase of this CTA ever writes, the area the other ranks of a cluster push
+// their merged states into: [8 ranks][slice] values (16 D + 8 floats cover every split count),
+// then [8 ranks][16 heads][2].
+template <int D, int NH, int NU>
+__host__ __device__ constexpr size_t attn_recv_offset() {
+    const size_t loop = attn_ring_bytes<D, NU>() + (size_t)16 * D * sizeof(__half);
+    const size_t merge = (size_t)kAttnWarps * NH * 8 * (D + 2) * sizeof(float);
+    return ((loop > merge ? loop : merge) + 15) & ~(size_t)15;
+}
+__host__ __device__ constexpr int kRecvMlOffset(int D) { return 16 * D + 8; }
+template <int D, int NH, int NU>
+__host__ __device__ constexpr size_t attn_smem_bytes() {
+    return attn_recv_offset<D, NH, NU>() + ((size_t)16 * D + 8 + 8 * 16 * 2) * sizeof(float);
+}
+
+
 template <int D, int NH, int NU, class Sync>
 __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f, int split, int kvh, int b, Sync sync) {
     constexpr int MT = D / 16;  // m-tiles of O^T
@@ -437,9 +455,20 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
         } else if (p.nsplits == 1) {
             a.out[qh * D + d] = __float2half_rn(acc / lsum);
         } else if (p.cluster) {
-            float* c_o = smem_f + kAttnWarps * HN * (D + 2);  // [16][D] then [16][2]
-            c_o[idx] = acc;
-            if (d == 0) { c_o[16 * D + 2 * h] = mstar; c_o[16 * D + 2 * h + 1] = lsum; }
+            // Pushed, not pulled: this CTA's merged value goes straight into the shared memory of the
+            // rank that finishes the item ([source rank][item of the owner's slice]), its (max, sum)
+            // pairs to every rank; a remote store needs no reply, a remote load is a round trip.
+            cg::cluster_group cluster = cg::this_cluster();
+            float* recv = smem_f + attn_recv_offset<D, NH, NU>() / sizeof(float);  // [8 ranks][slice] values, then [8 ranks][16 heads][2]
+            const int items = ratio * D, per_rank = (items + p.nsplits - 1) / p.nsplits;
+            const int owner = idx / per_rank;
+            cluster.map_shared_rank(recv, owner)[split * per_rank + (idx - owner * per_rank)] = acc;
+            if (d == 0) {
+                for (int s2 = 0; s2 < p.nsplits; ++s2) {
+                    float* ml = cluster.map_shared_rank(recv, s2) + kRecvMlOffset(D) + (split * 16 + h) * 2;
+                    ml[0] = mstar; ml[1] = lsum;
+                }
+            }
         } else {
             p.part_o[(qh * p.nsplits + split) * D + d] = acc;
             if (d == 0) {
@@ -461,40 +490,26 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
         return;
     }
     if (p.nsplits > 1 && p.cluster) {
-        // ── merge across the cluster: rank r finishes a slice of the (head, dim) outputs from
-        // every rank's partials, in rank order (the arithmetic of attn_merge_kernel) ──
+        // ── merge across the cluster: rank r finishes a slice of the (head, dim) outputs from the
+        // values every rank pushed into its shared memory, in rank order (the arithmetic of
+        // attn_merge_kernel).  One cluster barrier: after it nobody touches another CTA's memory. ──
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();
-        float* c_o = smem_f + kAttnWarps * HN * (D + 2);
+        const float* recv = smem_f + attn_recv_offset<D, NH, NU>() / sizeof(float);
         const int items = ratio * D, per_rank = (items + p.nsplits - 1) / p.nsplits;
         const int hi = min(items, (split + 1) * per_rank);
         for (int idx = split * per_rank + tid; idx < hi; idx += kAttnThreads) {
-            const int h = idx / D, d = idx % D;
-            // every rank's (max, sum, O) is requested before any is used: one trip through the
-            // cluster's shared memory, not one per rank
-            float rm[8], rl[8], ro[8];
-#pragma unroll
-            for (int s2 = 0; s2 < 8; ++s2) {
-                rm[s2] = kNegBig; rl[s2] = 0.f; ro[s2] = 0.f;
-                if (s2 < p.nsplits) {
-                    const float* rc = cluster.map_shared_rank(c_o, s2);
-                    rm[s2] = rc[16 * D + 2 * h]; rl[s2] = rc[16 * D + 2 * h + 1]; ro[s2] = rc[idx];
-                }
-            }
+            const int h = idx / D, d = idx % D, local = idx - split * per_rank;
             float mstar = kNegBig;
-#pragma unroll
-            for (int s2 = 0; s2 < 8; ++s2) mstar = fmaxf(mstar, rm[s2]);
+            for (int s2 = 0; s2 < p.nsplits; ++s2) mstar = fmaxf(mstar, recv[kRecvMlOffset(D) + (s2 * 16 + h) * 2]);
             float acc = 0.f, lsum = 0.f;
-#pragma unroll
-            for (int s2 = 0; s2 < 8; ++s2)
-                if (s2 < p.nsplits) {
-                    const float f = exp2f(rm[s2] - mstar);
-                    acc += ro[s2] * f;
-                    lsum += rl[s2] * f;
-                }
+            for (int s2 = 0; s2 < p.nsplits; ++s2) {
+                const float f = exp2f(recv[kRecvMlOffset(D) + (s2 * 16 + h) * 2] - mstar);
+                acc += recv[s2 * per_rank + local] * f;
+                lsum += recv[kRecvMlOffset(D) + (s2 * 16 + h) * 2 + 1] * f;
+            }
             a.out[((size_t)b * a.n_q + (size_t)kvh * ratio + h) * D + d] = __float2half_rn(acc / lsum);
         }
-        cluster.sync();  // nobody leaves while a peer still reads its shared memory
         return;
     }
     if (p.nsplits == 1 || !a.counters) return;
@@ -511,15 +526,6 @@ __device__ __forceinline__ void attn_decode_body(const AttnDev& p, float* smem_f
     if (tid == 0) *counter = 0;
     __threadfence();
     merge_partials<D>(p, smem_f + 4, (size_t)b * a.n_q + (size_t)kvh * ratio, ratio, tid, kAttnThreads);  // + 4: clear of the ticket word
-}
-
-// The rings plus the RoPE prologue's scratch (up to 16 rotated query heads) during
-// the key loop; the warps' and the cluster's merge areas afterwards, in the same bytes.
-template <int D, int NH, int NU>
-__host__ __device__ constexpr size_t attn_smem_bytes() {
-    const size_t loop = attn_ring_bytes<D, NU>() + (size_t)16 * D * sizeof(__half);
-    const size_t merge = ((size_t)kAttnWarps * NH * 8 + 16) * (D + 2) * sizeof(float);
-    return loop > merge ? loop : merge;
 }
 
 }  // namespace attn
