@@ -446,7 +446,7 @@ def open_tp_exchange(ctx: capi.Context, dist, world: int) -> None:
 
 
 def compare_greedy(got, tokens, runner_up, margins, tie: float = 0.02) -> dict:
-    """Verdict of a teacher-forced replay against known-good greedy tokens of one sequence.
+    """Outcome of a teacher-forced replay against known-good greedy tokens of one sequence.
 
     A step counts as identical when the ids are equal.  A differing id is a tie break, not an
     error, only when the known-good top-2 logit margin of that step is below ``tie`` (two fp16

@@ -66,8 +66,8 @@ def test_full_model_batch8_greedy_tokens_match_the_oracle():
     keeps the oracle's generation of the fixture within half an hour)."""
     gold = load("full_model_tokens_batch8.json")
     assert gold["batch"] == 8
-    verdicts = run(gold, 8, 3)
-    for b, v in enumerate(verdicts):
+    outcomes = run(gold, 8, 3)
+    for b, v in enumerate(outcomes):
         print("full model, batch 8, sequence %d: %d of %d steps identical, %d tie breaks" % (b, v["identical"], v["checked"], v["tie_breaks"]))
         assert v["checked"] == gold["n_decode"] and not v["wrong"], (b, v)
 
