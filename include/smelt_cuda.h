@@ -542,6 +542,28 @@ SMELT_CUDA_API smelt_status smelt_cuda_deltanet_recurrence_decode(smelt_cuda_ctx
                                                                   int head_dim, int value_heads, int qk_heads);
 SMELT_CUDA_API smelt_status smelt_cuda_rms_norm_gated(smelt_cuda_ctx* ctx, const void* input_dev, const void* gate_dev,
                                                       const void* weight_dev, void* out_dev, int head_dim, float eps, int heads);
+/* Prompt-chunk forms (the DeltaNet layers of a prefill table).
+ * conv1d_update_silu_prefill (Resources/Shaders/conv1d.metal:129-268: conv1d_update_silu_prefill,
+ *   conv1d_update_silu_c6144_k4_prefill, conv1d_update_silu_prefill_checkpoint): qkv [seq_len,
+ *   channels] is convolved and activated in place, position after position; state [channels,
+ *   kernel_size] is written once at the end.  history_dev (may be NULL) [seq_len + 1, channels,
+ *   kernel_size] receives the entry state and the state after every position.
+ * deltanet_recurrence_prefill (Resources/Shaders/prefill_recurrence.metal:290-673:
+ *   deltanet_recurrence_mlx_prefill and its d128 specialisations): qkv [seq_len, (2 qk_heads +
+ *   value_heads) head_dim], b_proj / a_proj [seq_len, value_heads], out [seq_len, value_heads,
+ *   head_dim]; the recurrent rows stay in fp32 across the chunk and are rounded to fp16 once, at
+ *   the end, as the reference's kernels do.  With history_dev != NULL it is
+ *   deltanet_recurrence_mlx_prefill_checkpoint (:675-775): history [seq_len + 1, value_heads,
+ *   head_dim, head_dim] receives the entry state and the fp16 state after every position, and the
+ *   rows continue from those rounded values, which makes the chunk equal to seq_len decode steps. */
+SMELT_CUDA_API smelt_status smelt_cuda_conv1d_update_silu_prefill(smelt_cuda_ctx* ctx, void* state_dev, void* qkv_dev,
+                                                                  const void* weight_dev, int seq_len, int channels,
+                                                                  int kernel_size, void* history_dev);
+SMELT_CUDA_API smelt_status smelt_cuda_deltanet_recurrence_prefill(smelt_cuda_ctx* ctx, void* state_dev, const void* qkv_dev,
+                                                                   const void* b_proj_dev, const void* a_proj_dev,
+                                                                   const void* a_log_dev, const void* dt_bias_dev, void* out_dev,
+                                                                   int head_dim, int value_heads, int qk_heads, int seq_len,
+                                                                   void* history_dev);
 
 /* ── prompt-state snapshots ──────────────────────────────────────────────────
  * SmeltRuntime.captureDevicePromptSnapshot / restoreDevicePromptSnapshot

@@ -412,6 +412,29 @@ def deltanet_recurrence_decode(state, qkv, b_proj, a_proj, a_log, dt_bias, head_
     return st, out
 
 
+def conv1d_update_silu_prefill(state, qkv, weight, seq_len: int, channels: int, kernel_size: int, history: bool = False):
+    """Returns (state after the chunk, activated qkv [seq_len, channels], history [seq_len + 1, channels, kernel_size] or None)."""
+    st = _h(state).copy()
+    x = _h(qkv).copy()
+    hist = np.zeros((seq_len + 1, channels, kernel_size), np.float16) if history else None
+    _check(lib().so_conv1d_update_silu_prefill(_p(st), _p(x), _p(_h(weight)), seq_len, channels, kernel_size, _p(hist) if history else None),
+           "conv1d_update_silu_prefill")
+    return st, x.reshape(seq_len, channels), hist
+
+
+def deltanet_recurrence_prefill(state, qkv, b_proj, a_proj, a_log, dt_bias, head_dim: int, value_heads: int, qk_heads: int, seq_len: int,
+                                history: bool = False):
+    """Returns (state after the chunk, output [seq_len, value_heads, head_dim], history
+    [seq_len + 1, value_heads, head_dim, head_dim] or None)."""
+    st = _h(state).copy()
+    out = np.zeros((seq_len, value_heads, head_dim), np.float16)
+    hist = np.zeros((seq_len + 1, value_heads, head_dim, head_dim), np.float16) if history else None
+    _check(lib().so_deltanet_recurrence_prefill(_p(st), _p(_h(qkv)), _p(_h(b_proj)), _p(_h(a_proj)), _p(_h(a_log)), _p(_h(dt_bias)), _p(out),
+                                                head_dim, value_heads, qk_heads, seq_len, _p(hist) if history else None),
+           "deltanet_recurrence_prefill")
+    return st, out, hist
+
+
 def rms_norm_gated(x, gate, weight, head_dim: int, eps: float, heads: int) -> np.ndarray:
     out = np.zeros((heads, head_dim), np.float16)
     _check(lib().so_rms_norm_gated(_p(_h(x)), _p(_h(gate)), _p(_h(weight)), _p(out), head_dim, C.c_float(eps), heads), "rms_norm_gated")

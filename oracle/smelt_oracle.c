@@ -1017,6 +1017,98 @@ SO_API int so_deltanet_recurrence_decode(uint16_t *state, const uint16_t *qkv, c
     return SO_OK;
 }
 
+/* conv1d_update_silu_prefill, conv1d_update_silu_c6144_k4_prefill and
+ * conv1d_update_silu_prefill_checkpoint (conv1d.metal:129-268): one channel walks the prompt
+ * chunk qkv [T, C] in place, keeping its taps in registers; state [C, K] is written once at the
+ * end.  The taps are fp16 values throughout, their products with the fp16 weights are exact in
+ * fp32, so the fused multiply-adds of the specialisation and the roundings of the checkpoint
+ * variant change nothing: every variant equals T calls of so_conv1d_update_silu.  history (may
+ * be NULL) [T + 1, C, K] receives the entry state and the state after every token. */
+SO_API int so_conv1d_update_silu_prefill(uint16_t *state, uint16_t *qkv, const uint16_t *weight, int seq_len, int channels,
+                                         int kernel_size, uint16_t *history) {
+    if (channels <= 0 || kernel_size <= 0 || kernel_size > 8 || seq_len < 0) return SO_ERR_GEOMETRY;
+    const size_t hs = (size_t)channels * kernel_size;
+    for (int ch = 0; ch < channels; ++ch) {
+        uint16_t *st = state + (size_t)ch * kernel_size;
+        const uint16_t *w = weight + (size_t)ch * kernel_size;
+        if (history) for (int k = 0; k < kernel_size; ++k) history[(size_t)ch * kernel_size + k] = st[k];
+        for (int pos = 0; pos < seq_len; ++pos) {
+            uint16_t *x = qkv + (size_t)pos * channels + ch;
+            for (int k = 0; k + 1 < kernel_size; ++k) st[k] = st[k + 1];
+            st[kernel_size - 1] = *x;
+            float acc = 0.0f;
+            for (int k = 0; k < kernel_size; ++k) acc += h2f(st[k]) * h2f(w[k]);
+            *x = silu_staged_half(f2h(acc));
+            if (history) for (int k = 0; k < kernel_size; ++k) history[(size_t)(pos + 1) * hs + (size_t)ch * kernel_size + k] = st[k];
+        }
+    }
+    return SO_OK;
+}
+
+/* deltanet_recurrence_mlx_prefill and its _d128_h16 / _d128_h32_qk16 / _d128_h48_qk16
+ * specialisations (Resources/Shaders/prefill_recurrence.metal:290-673): the decode step's
+ * arithmetic over the T positions of qkv [T, (2 Hqk + Hv) D], b_proj / a_proj [T, Hv], with the
+ * recurrent row held in fp32 across the whole chunk and rounded to fp16 only when it is
+ * written back at the end ("keeps the recurrent state in FP32 registers across the entire
+ * chunk", :318-321).  out [T, Hv, D].  With history != NULL it is
+ * deltanet_recurrence_mlx_prefill_checkpoint (:675-775): history [T + 1, Hv, D, D] receives the
+ * entry state and the fp16 state after every token, and the live row continues from that
+ * rounded value, which makes the chunk equal to T decode steps. */
+SO_API int so_deltanet_recurrence_prefill(uint16_t *state, const uint16_t *qkv, const uint16_t *b_proj, const uint16_t *a_proj,
+                                          const uint16_t *a_log, const uint16_t *dt_bias, uint16_t *out, int head_dim,
+                                          int value_heads, int qk_heads, int seq_len, uint16_t *history) {
+    if (head_dim <= 0 || head_dim % 32 || head_dim > 256 || qk_heads <= 0 || value_heads <= 0 || value_heads % qk_heads || seq_len < 0)
+        return SO_ERR_GEOMETRY;
+    const int D = head_dim, epl = D / 32, rep = value_heads / qk_heads;
+    const size_t stride = (size_t)(2 * qk_heads + value_heads) * D, hs = (size_t)value_heads * D * D;
+    for (int h = 0; h < value_heads; ++h) {
+        const int qh = h / rep;
+        for (int dv = 0; dv < D; ++dv) {
+            uint16_t *row = state + ((size_t)h * D + dv) * D;
+            const size_t row_off = ((size_t)h * D + dv) * D;
+            float st[256], lane[32];
+            for (int dk = 0; dk < D; ++dk) st[dk] = h2f(row[dk]);
+            if (history) for (int dk = 0; dk < D; ++dk) history[row_off + dk] = row[dk];
+            for (int pos = 0; pos < seq_len; ++pos) {
+                const uint16_t *x = qkv + (size_t)pos * stride;
+                const uint16_t *q = x + (size_t)qh * D, *k = x + (size_t)(qk_heads + qh) * D, *v = x + (size_t)2 * qk_heads * D + (size_t)h * D;
+                const float beta = sigmoid_staged_half(b_proj[(size_t)pos * value_heads + h]);
+                const uint16_t xh = f2h(h2f(a_proj[(size_t)pos * value_heads + h]) + h2f(dt_bias[h]));
+                const float decay = round_h(expf(-expf(h2f(a_log[h])) * softplus_staged_half(xh)));
+                for (int l = 0; l < 32; ++l) {
+                    float p = 0.0f;
+                    for (int i = 0; i < epl; ++i) {
+                        const int dk = l * epl + i;
+                        st[dk] = st[dk] * decay;
+                        p += st[dk] * h2f(k[dk]);
+                    }
+                    lane[l] = p;
+                }
+                const float kv = simd_sum32(lane);
+                const float delta = (h2f(v[dv]) - kv) * beta;
+                for (int l = 0; l < 32; ++l) {
+                    float p = 0.0f;
+                    for (int i = 0; i < epl; ++i) {
+                        const int dk = l * epl + i;
+                        st[dk] += h2f(k[dk]) * delta;
+                        p += st[dk] * h2f(q[dk]);
+                    }
+                    lane[l] = p;
+                }
+                out[((size_t)pos * value_heads + h) * D + dv] = f2h(simd_sum32(lane));
+                if (history)
+                    for (int dk = 0; dk < D; ++dk) {
+                        const uint16_t r = f2h(st[dk]);
+                        history[(size_t)(pos + 1) * hs + row_off + dk] = r;
+                        st[dk] = h2f(r);
+                    }
+            }
+            for (int dk = 0; dk < D; ++dk) row[dk] = f2h(st[dk]);
+        }
+    }
+    return SO_OK;
+}
+
 /* rms_norm_gated (norms.metal:1093-1143): per head, out = half(w * (x * rsqrt(mean(x^2) + eps)) *
  * silu(g)), silu(g) = g / (1 + exp(-g)) in fp32; weight [D] shared by the heads. */
 SO_API int so_rms_norm_gated(const uint16_t *input, const uint16_t *gate, const uint16_t *weight, uint16_t *out, int head_dim,

@@ -123,6 +123,10 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"rms_scale_qk", PK_RMS_SCALE_QK, 0, false},
         {"deltanet_recurrence_mlx_decode", PK_DELTANET_DECODE, 0, false},
         {"rms_norm_gated", PK_RMS_NORM_GATED, 0, false},
+        {"conv1d_update_silu_prefill", PK_CONV1D_SILU_PREFILL, 0, false},
+        {"conv1d_update_silu_prefill_checkpoint", PK_CONV1D_SILU_PREFILL, 1, false},
+        {"deltanet_recurrence_mlx_prefill", PK_DELTANET_PREFILL, 0, false},
+        {"deltanet_recurrence_mlx_prefill_checkpoint", PK_DELTANET_PREFILL, 1, false},
     };
     // Activation bit-plane producers and consumers (Resources/Shaders/signed_quant.metal:751-2245):
     // the plane count is part of the name.
@@ -165,6 +169,11 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             {"deltanet_recurrence_mlx_decode_d128_h32_qk16", PK_DELTANET_DECODE, 128, 32, 16},
             {"deltanet_recurrence_mlx_decode_d128_h48_qk16", PK_DELTANET_DECODE, 128, 48, 16},
             {"rms_norm_gated_d128", PK_RMS_NORM_GATED, 128, 0, 0},
+            // prompt-chunk forms (Resources/Shaders/prefill_recurrence.metal:290-578, conv1d.metal:129-171): d = channels, hv = taps for the conv
+            {"deltanet_recurrence_mlx_prefill_d128_h16", PK_DELTANET_PREFILL, 128, 16, 16},
+            {"deltanet_recurrence_mlx_prefill_d128_h32_qk16", PK_DELTANET_PREFILL, 128, 32, 16},
+            {"deltanet_recurrence_mlx_prefill_d128_h48_qk16", PK_DELTANET_PREFILL, 128, 48, 16},
+            {"conv1d_update_silu_c6144_k4_prefill", PK_CONV1D_SILU_PREFILL, 6144, 4, 0},
         };
         for (const Fixed& f : fixed)
             if (name == f.name) {
@@ -727,6 +736,50 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             in.launches += 1;
             return check_cuda(ctx, launch_deltanet_recurrence_decode(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const __half*)r.buf[3].ptr,
                                                                      (const __half*)r.buf[4].ptr, (const __half*)r.buf[5].ptr, (__half*)r.buf[6].ptr, (int)d, (int)hv, (int)hqk), p.name.c_str());
+        }
+        case PK_CONV1D_SILU_PREFILL: {
+            // conv1d.metal:129-225: 0 state [C, K] (in place), 1 qkv [T, C] (in place), 2 weight [C, K], 3 seqLen, 4 channels,
+            // 5 kernel size (the c6144_k4 name fixes 4 and 5), 6 history [T + 1, C, K] (the checkpoint name only).
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, seq_len);
+            uint32_t channels = (uint32_t)p.head_dim, ksize = (uint32_t)p.n_q;
+            if (!p.fixed_shape) {
+                NEED_U32(4, c_); NEED_U32(5, k_);
+                channels = c_; ksize = k_;
+            }
+            if (channels == 0 || ksize == 0 || ksize > 8) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": kernel size in 1..8");
+            NEED_BYTES(0, (size_t)channels * ksize * 2); NEED_BYTES(1, (size_t)seq_len * channels * 2); NEED_BYTES(2, (size_t)channels * ksize * 2);
+            __half* history = nullptr;
+            if (p.bits == 1) {
+                NEED_BUF(6); NEED_BYTES(6, ((size_t)seq_len + 1) * channels * ksize * 2);
+                history = (__half*)r.buf[6].ptr;
+            }
+            in.launches += 1;
+            return check_cuda(ctx, launch_conv1d_update_silu_prefill(l, (__half*)r.buf[0].ptr, (__half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (int)seq_len, (int)channels, (int)ksize, history), p.name.c_str());
+        }
+        case PK_DELTANET_PREFILL: {
+            // prefill_recurrence.metal:580-592: 0 state [Hv, D, D] (in place), 1 qkv [T, (2 Hqk + Hv) D], 2 b [T, Hv], 3 a [T, Hv],
+            // 4 A_log, 5 dt_bias, 6 out [T, Hv, D], 7 headDim, 8 valueHeads, 9 qkHeads, 10 seqLen, 11 history [T + 1, Hv, D, D]
+            // (the checkpoint name only); the specialised names fix the shape and bind seqLen at 7 (:290-299).
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_BUF(5); NEED_BUF(6);
+            uint32_t d = (uint32_t)p.head_dim, hv = (uint32_t)p.n_q, hqk = (uint32_t)p.n_kv, seq_len = 0;
+            if (p.fixed_shape) {
+                NEED_U32(7, t_);
+                seq_len = t_;
+            } else {
+                NEED_U32(7, d_); NEED_U32(8, hv_); NEED_U32(9, hqk_); NEED_U32(10, t_);
+                d = d_; hv = hv_; hqk = hqk_; seq_len = t_;
+            }
+            if (d == 0 || d % 32 || d > 256 || hv == 0 || hqk == 0 || hv % hqk) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": head_dim a multiple of 32 up to 256, value heads a multiple of q/k heads");
+            NEED_BYTES(0, (size_t)hv * d * d * 2); NEED_BYTES(1, (size_t)seq_len * ((size_t)2 * hqk + hv) * d * 2); NEED_BYTES(2, (size_t)seq_len * hv * 2); NEED_BYTES(3, (size_t)seq_len * hv * 2);
+            NEED_BYTES(4, (size_t)hv * 2); NEED_BYTES(5, (size_t)hv * 2); NEED_BYTES(6, (size_t)seq_len * hv * d * 2);
+            __half* history = nullptr;
+            if (p.bits == 1) {
+                NEED_BUF(11); NEED_BYTES(11, ((size_t)seq_len + 1) * hv * d * d * 2);
+                history = (__half*)r.buf[11].ptr;
+            }
+            in.launches += 1;
+            return check_cuda(ctx, launch_deltanet_recurrence_prefill(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const __half*)r.buf[3].ptr,
+                                                                      (const __half*)r.buf[4].ptr, (const __half*)r.buf[5].ptr, (__half*)r.buf[6].ptr, (int)d, (int)hv, (int)hqk, (int)seq_len, history), p.name.c_str());
         }
         case PK_RMS_NORM_GATED: {
             // norms.metal:1093-1099: 0 in [H, D], 1 gate [H, D], 2 weight [D], 3 out, 4 headDim, 5 eps; one threadgroup per

@@ -36,6 +36,8 @@ cudaError_t launch_bitplane_matvec(const Launch& l, const BitplaneArgs& a);
 // DeltaNet decode step (deltanet.cu)
 cudaError_t launch_conv1d_update_silu(const Launch& l, __half* state, const __half* new_val, const __half* weight, __half* out, int channels, int kernel_size);
 cudaError_t launch_rms_scale_qk(const Launch& l, __half* qkv, int head_dim, float eps, int qkv_dim, int qk_heads, int batch);
+cudaError_t launch_conv1d_update_silu_prefill(const Launch& l, __half* state, __half* qkv, const __half* weight, int seq_len, int channels, int kernel_size, __half* history);
+cudaError_t launch_deltanet_recurrence_prefill(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, int head_dim, int value_heads, int qk_heads, int seq_len, __half* history);
 cudaError_t launch_deltanet_recurrence_decode(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, int head_dim, int value_heads, int qk_heads);
 cudaError_t launch_rms_norm_gated(const Launch& l, const __half* input, const __half* gate, const __half* weight, __half* out, int head_dim, float eps, int heads);
 cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x, __half* y, int rows, int cols, int batch, int sm_count);

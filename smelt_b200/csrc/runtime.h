@@ -52,6 +52,8 @@ enum PipeKind : int {
     PK_RMS_SCALE_QK,
     PK_DELTANET_DECODE,
     PK_RMS_NORM_GATED,
+    PK_CONV1D_SILU_PREFILL,
+    PK_DELTANET_PREFILL,
     PK_BITPLANE_PRODUCER,
     PK_BITPLANE_SWIGLU_PRODUCER,
     PK_BITPLANE_MATVEC,

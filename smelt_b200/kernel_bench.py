@@ -223,6 +223,33 @@ class Bench:
             kc.free(); vc.free()
         q.free(); out.free()
 
+    def deltanet(self, config, d, hv, hqk, seq_len):
+        """The recurrence of a DeltaNet layer: one decode step (seq_len 1) or a prompt chunk."""
+        ctx = self.ctx
+        if self.only and self.only not in f"deltanet d{d} h{hv} qk{hqk} t{seq_len}":
+            return
+        rng = np.random.default_rng(seq_len)
+        width = (2 * hqk + hv) * d
+        alg = 2 * hv * d * d * 2 + seq_len * (width + hv * d + 2 * hv) * 2
+        n = copies_for(alg, cap=32)
+        states = [ctx.to_device((rng.standard_normal((hv, d, d)) * 0.05).astype(np.float16)) for _ in range(n)]
+        qkv = rng.standard_normal((seq_len, 2 * hqk + hv, d)).astype(np.float32)
+        qkv[:, :2 * hqk] /= np.linalg.norm(qkv[:, :2 * hqk], axis=2, keepdims=True)
+        dq = ctx.to_device(qkv.astype(np.float16))
+        b, a = (ctx.to_device(rng.standard_normal(seq_len * hv).astype(np.float16)) for _ in range(2))
+        a_log, dt = ctx.to_device(rng.uniform(-2, 0.5, hv).astype(np.float16)), ctx.to_device(rng.uniform(-0.5, 0.5, hv).astype(np.float16))
+        out = ctx.alloc(seq_len * hv * d * 2)
+        def enqueue():
+            for st in states:
+                if seq_len == 1:
+                    ctx.call("deltanet_recurrence_decode", st, dq, b, a, a_log, dt, out, d, hv, hqk)
+                else:
+                    ctx.call("deltanet_recurrence_prefill", st, dq, b, a, a_log, dt, out, d, hv, hqk, seq_len, None)
+        name = "deltanet_recurrence_mlx_decode" if seq_len == 1 else "deltanet_recurrence_mlx_prefill"
+        self.run(config, name, f"d{d} h{hv} qk{hqk}, {seq_len} positions", 1, alg, n, enqueue)
+        for t in states + [dq, b, a, a_log, dt, out]:
+            t.free()
+
     def lm_head(self, config, vocab, hidden):
         ctx = self.ctx
         w = ctx.to_device(synth.normal_f16(4, "head", (vocab, hidden), 0.02))
@@ -278,6 +305,9 @@ def main():
         b.attention_prefill("config4", 32, 8, 128, 128, 384)
         if not args.only:
             b.lm_head("config4", 151936, 4096)
+    if "deltanet" in want:  # not one of the headline configurations: the recurrence of a hybrid model's linear-attention layers
+        for t in (1, 64, 512):
+            b.deltanet("deltanet", 128, 32, 16, t)
     if args.markdown:
         print("\n| config | kernel | shape | batch | MB / launch | us / launch | GB/s | of %s peak %.0f GB/s |" % (b.peak_kind, b.peak))
         print("|---|---|---|---|---|---|---|---|")

@@ -238,3 +238,212 @@ def test_deltanet_records_run_the_layer_core(ctx, oracle):
     want = oracle.rms_norm_gated(core, z, norm_w, d, 1e-6, hv).reshape(-1)
     err = float(np.max(np.abs(got.astype(F) - want.astype(F))) / np.sqrt(np.mean(want.astype(F) ** 2)))
     assert err < 5e-3, err
+
+
+# ── prompt-chunk forms (conv1d.metal:129-268, prefill_recurrence.metal:290-775) ──
+def prefill_fixture(seq_len, head_dim=128, heads=16):
+    """The inputs of testDeltaNetRecurrenceMlxPrefill_LargeBatchBoundaries
+    (PrefillKernelTests.swift:4253-4264): the decode fixture's ramps over seq_len rows."""
+    hidden = head_dim * heads
+    i = np.arange(heads * head_dim * head_dim, dtype=F)
+    state = (np.sin(i * F(0.0007)) * F(0.03)).astype(np.float16)
+    c = np.arange(seq_len * 3 * hidden, dtype=F)
+    qkv = (np.sin(c * F(0.0019)) * F(0.4)).astype(np.float16).reshape(seq_len, 3 * hidden)
+    j = np.arange(seq_len * heads, dtype=F)
+    b = (np.cos(j * F(0.017)) * F(0.9)).astype(np.float16)
+    a = (np.sin(j * F(0.013)) * F(0.7)).astype(np.float16)
+    h = np.arange(heads, dtype=F)
+    a_log = (F(-1.2) + h * F(0.03)).astype(np.float16)
+    dt_bias = (F(-0.2) + h * F(0.02)).astype(np.float16)
+    q = qkv[:, :hidden].astype(F).reshape(seq_len, heads, head_dim)
+    k = qkv[:, hidden:2 * hidden].astype(F).reshape(seq_len, heads, head_dim)
+    q = q * (F(1 / np.sqrt(F(head_dim))) / np.maximum(np.sqrt((q * q).sum(2, keepdims=True)), F(1e-6)))
+    k = k * (F(1) / np.maximum(np.sqrt((k * k).sum(2, keepdims=True)), F(1e-6)))
+    qkv = np.concatenate([q.astype(np.float16).reshape(seq_len, hidden), k.astype(np.float16).reshape(seq_len, hidden), qkv[:, 2 * hidden:]], axis=1)
+    return state, np.ascontiguousarray(qkv), b, a, a_log, dt_bias
+
+
+def prefill_float_reference(state, qkv, b, a, a_log, dt_bias, head_dim, heads, seq_len):
+    """The test's own float reference (PrefillKernelTests.swift:4275-4304)."""
+    st = state.reshape(heads, head_dim, head_dim)
+    out = np.zeros((seq_len, heads, head_dim))
+    bb, aa = b.reshape(seq_len, heads), a.reshape(seq_len, heads)
+    for pos in range(seq_len):
+        row = (qkv[pos], bb[pos], aa[pos], a_log, dt_bias)
+        st, out[pos] = recurrence_float_reference(st, *row, head_dim, heads)
+    return st, out
+
+
+def random_chunk(rng, seq_len, head_dim, v_heads, qk_heads):
+    state = (rng.standard_normal((v_heads, head_dim, head_dim)) * 0.05).astype(np.float16)
+    qkv = rng.standard_normal((seq_len, 2 * qk_heads + v_heads, head_dim)).astype(F)
+    qkv[:, :2 * qk_heads] /= np.linalg.norm(qkv[:, :2 * qk_heads], axis=2, keepdims=True)
+    qkv = qkv.astype(np.float16).reshape(seq_len, -1)
+    b, a = rng.standard_normal(seq_len * v_heads).astype(np.float16), rng.standard_normal(seq_len * v_heads).astype(np.float16)
+    a_log = rng.uniform(-2, 0.5, v_heads).astype(np.float16)
+    dt = rng.uniform(-0.5, 0.5, v_heads).astype(np.float16)
+    return state, qkv, b, a, a_log, dt
+
+
+@pytest.mark.parametrize("seq_len", [64, 65])
+def test_oracle_prefill_recurrence_is_within_the_references_own_bound(oracle, seq_len):
+    """The reference asserts max |kernel - float reference| < 0.03 over outputs and final state
+    at 64 and 65 positions (PrefillKernelTests.swift:4349)."""
+    fx = prefill_fixture(seq_len)
+    st, out, _ = oracle.deltanet_recurrence_prefill(*fx, 128, 16, 16, seq_len)
+    ref_st, ref_out = prefill_float_reference(*fx, 128, 16, seq_len)
+    assert np.max(np.abs(out.astype(np.float64) - ref_out)) < 3e-3
+    assert np.max(np.abs(st.astype(np.float64).reshape(ref_st.shape) - ref_st)) < 3e-3
+
+
+def test_oracle_prefill_of_one_position_is_the_decode_step(oracle):
+    """testDeltaNetGenericRecurrenceSingleTokenPrefillIsBitExactWithDecode (PrefillKernelTests.swift:4977):
+    same bits; and the checkpoint form over T positions is T decode steps, history included."""
+    rng = np.random.default_rng(5)
+    d, hv, hqk, t = 64, 8, 4, 5
+    fx = random_chunk(rng, t, d, hv, hqk)
+    state, qkv, b, a, a_log, dt = fx
+    st1, out1, _ = oracle.deltanet_recurrence_prefill(state, qkv[:1], b[:hv], a[:hv], a_log, dt, d, hv, hqk, 1)
+    st_d, out_d = oracle.deltanet_recurrence_decode(state, qkv[0], b[:hv], a[:hv], a_log, dt, d, hv, hqk)
+    assert np.array_equal(st1.view(np.uint16), st_d.view(np.uint16)) and np.array_equal(out1.reshape(-1).view(np.uint16), out_d.reshape(-1).view(np.uint16))
+    st_c, out_c, hist = oracle.deltanet_recurrence_prefill(*fx, d, hv, hqk, t, history=True)
+    st_i = state
+    assert np.array_equal(hist[0].view(np.uint16), state.view(np.uint16))
+    for pos in range(t):
+        st_i, o = oracle.deltanet_recurrence_decode(st_i, qkv[pos], b[pos * hv:(pos + 1) * hv], a[pos * hv:(pos + 1) * hv], a_log, dt, d, hv, hqk)
+        assert np.array_equal(o.view(np.uint16), out_c[pos].view(np.uint16)), pos
+        assert np.array_equal(st_i.reshape(hv, d, d).view(np.uint16), hist[pos + 1].view(np.uint16)), pos
+    assert np.array_equal(st_c.view(np.uint16), st_i.view(np.uint16))
+    # the fp32-resident form is a different trajectory: close, not equal
+    st_f, out_f, _ = oracle.deltanet_recurrence_prefill(*fx, d, hv, hqk, t)
+    assert np.max(np.abs(out_f.astype(F) - out_c.astype(F))) < 2e-2
+
+
+def test_oracle_conv1d_prefill_is_the_iterated_update(oracle):
+    rng = np.random.default_rng(6)
+    c, k, t = 96, 4, 7
+    state = rng.standard_normal((c, k)).astype(np.float16)
+    x = rng.standard_normal((t, c)).astype(np.float16)
+    w = (rng.standard_normal((c, k)) * 0.5).astype(np.float16)
+    st, y, hist = oracle.conv1d_update_silu_prefill(state, x, w, t, c, k, history=True)
+    cur = state
+    assert np.array_equal(hist[0].view(np.uint16), state.view(np.uint16))
+    for pos in range(t):
+        cur, o = oracle.conv1d_update_silu(cur, x[pos], w, c, k)
+        assert np.array_equal(o.view(np.uint16), y[pos].view(np.uint16))
+        assert np.array_equal(cur.reshape(c, k).view(np.uint16), hist[pos + 1].view(np.uint16))
+    assert np.array_equal(st.view(np.uint16), cur.view(np.uint16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("channels,ksize,seq_len,history", [(6144, 4, 65, False), (6144, 4, 3, True), (1000, 4, 64, False), (512, 3, 17, True), (64, 8, 1, False), (64, 8, 0, False)])
+def test_conv1d_update_silu_prefill(ctx, oracle, channels, ksize, seq_len, history):
+    rng = np.random.default_rng(channels + ksize + seq_len)
+    state = rng.standard_normal((channels, ksize)).astype(np.float16)
+    x = rng.standard_normal((max(seq_len, 1), channels)).astype(np.float16)
+    w = (rng.standard_normal((channels, ksize)) * 0.5).astype(np.float16)
+    ds, dx, dw = (ctx.to_device(t) for t in (state, x, w))
+    hist = ctx.alloc((seq_len + 1) * channels * ksize * 2).fill(0) if history else None
+    ctx.call("conv1d_update_silu_prefill", ds, dx, dw, seq_len, channels, ksize, hist)
+    want_state, want, want_hist = oracle.conv1d_update_silu_prefill(state, x[:seq_len], w, seq_len, channels, ksize, history=history)
+    assert np.array_equal(ds.download(np.uint16, (channels * ksize,)), want_state.view(np.uint16).reshape(-1)), "the taps are exact"
+    got = dx.download(np.float16, x.shape)
+    if seq_len:
+        assert np.max(ulp_diff_f16(got[:seq_len], want)) <= 1  # expf of the two libraries
+    else:
+        assert np.array_equal(got.view(np.uint16), x.view(np.uint16))
+    if history:
+        assert np.array_equal(hist.download(np.uint16, want_hist.shape), want_hist.view(np.uint16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim,v_heads,qk_heads,seq_len,history",
+                         [(128, 16, 16, 65, False), (128, 32, 16, 64, False), (128, 48, 16, 130, False), (64, 8, 4, 255, False), (256, 4, 2, 33, False),
+                          (128, 16, 16, 1, False), (128, 16, 16, 9, True), (64, 8, 4, 130, True)])
+def test_deltanet_recurrence_prefill(ctx, oracle, head_dim, v_heads, qk_heads, seq_len, history):
+    rng = np.random.default_rng(head_dim + v_heads + seq_len)
+    fx = random_chunk(rng, seq_len, head_dim, v_heads, qk_heads)
+    dev = [ctx.to_device(t) for t in fx]
+    out = ctx.alloc(seq_len * v_heads * head_dim * 2)
+    hist = ctx.alloc((seq_len + 1) * v_heads * head_dim * head_dim * 2).fill(0) if history else None
+    ctx.call("deltanet_recurrence_prefill", *dev, out, head_dim, v_heads, qk_heads, seq_len, hist)
+    want_state, want, want_hist = oracle.deltanet_recurrence_prefill(*fx, head_dim, v_heads, qk_heads, seq_len, history=history)
+    got = out.download(np.float16, want.shape).astype(F)
+    got_state = dev[0].download(np.float16, (v_heads, head_dim, head_dim))
+    # the same fp32 operations in the same order; a gate whose expf differs by an ulp between the two
+    # libraries can move one fp16 rounding, which the following positions carry along
+    scale = max(1.0, float(np.max(np.abs(want.astype(F)))))
+    assert np.max(np.abs(got - want.astype(F))) <= 2e-3 * scale
+    assert np.max(np.abs(got_state.astype(F) - want_state.reshape(got_state.shape).astype(F))) <= 2e-3
+    assert np.mean(got.view(np.uint32) == want.astype(F).view(np.uint32)) > 0.98, "all but a few values carry the same bits"
+    if history:
+        gh = hist.download(np.float16, want_hist.shape).astype(F)
+        assert np.array_equal(gh[0], fx[0].astype(F))
+        assert np.max(np.abs(gh - want_hist.astype(F))) <= 2e-3
+
+
+@pytest.mark.gpu
+def test_deltanet_prefill_reference_fixture(ctx):
+    """The reference test's fixture at 65 positions through the CUDA kernel, against the test's
+    float reference and bound (0.03, PrefillKernelTests.swift:4349)."""
+    fx = prefill_fixture(65)
+    dev = [ctx.to_device(t) for t in fx]
+    out = ctx.alloc(65 * 16 * 128 * 2)
+    ctx.call("deltanet_recurrence_prefill", *dev, out, 128, 16, 16, 65, None)
+    ref_st, ref_out = prefill_float_reference(*fx, 128, 16, 65)
+    assert np.max(np.abs(out.download(np.float16, (65, 16, 128)).astype(np.float64) - ref_out)) < 0.03
+    assert np.max(np.abs(dev[0].download(np.float16, (16, 128, 128)).astype(np.float64) - ref_st)) < 0.03
+
+
+@pytest.mark.gpu
+def test_deltanet_prefill_records(ctx, oracle):
+    """The prompt-chunk records with the reference's pipeline names and bindings, eagerly:
+    conv1d_update_silu_c6144_k4_prefill -> rms_scale_qk (grid.y = positions) ->
+    deltanet_recurrence_mlx_prefill_d128_h16."""
+    d, h, k, t = 128, 16, 4, 12
+    qkv_dim = 3 * h * d
+    rng = np.random.default_rng(11)
+    conv_state = rng.standard_normal((qkv_dim, k)).astype(np.float16)
+    x = rng.standard_normal((t, qkv_dim)).astype(np.float16)
+    conv_w = (rng.standard_normal((qkv_dim, k)) * 0.5).astype(np.float16)
+    rec_state = (rng.standard_normal((h, d, d)) * 0.05).astype(np.float16)
+    b, a = rng.standard_normal(t * h).astype(np.float16), rng.standard_normal(t * h).astype(np.float16)
+    a_log, dt = rng.uniform(-2, 0.5, h).astype(np.float16), rng.uniform(-0.5, 0.5, h).astype(np.float16)
+    tensors = {2: conv_state, 3: x, 4: conv_w, 5: rec_state, 6: b, 7: a, 9: a_log, 10: dt, 11: np.zeros(t * h * d, np.float16)}
+    for slot, tens in tensors.items():
+        ctx.call("alloc_slot", slot, C.c_size_t(tens.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), tens.ctypes.data_as(C.c_void_p), C.c_size_t(tens.nbytes)))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    names = ["conv1d_update_silu_c6144_k4_prefill", "rms_scale_qk", "deltanet_recurrence_mlx_prefill_d128_h16"]
+    for i, n in enumerate(names):
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 8 + i, n.encode()))
+    f32 = lambda v: int(np.array([v], F).view(np.uint32)[0])
+
+    def rec(pipe, grid, bufs, cons):
+        r = capi.DispatchRecord()
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, pipe, len(bufs), len(cons)
+        r.grid[0], r.grid[1], r.grid[2] = grid[0], grid[1], 1
+        for j, (binding, slot) in enumerate(bufs):
+            r.buf[j].slot, r.buf[j].binding_index, r.buf[j].offset_kind, r.buf[j].offset = slot, binding, 0, 0
+        for j, (binding, kind, value) in enumerate(cons):
+            r.con[j].kind, r.con[j].binding_index, r.con[j].value = kind, binding, value
+        return r
+
+    table = (capi.DispatchRecord * 3)(
+        rec(8, (qkv_dim, 1), [(0, 2), (1, 3), (2, 4)], [(3, 0, t)]),
+        rec(9, (2 * h, t), [(0, 3)], [(1, 0, d), (2, 1, f32(1e-6)), (3, 0, qkv_dim), (4, 0, h)]),
+        rec(10, (32, d), [(0, 5), (1, 3), (2, 6), (3, 7), (4, 9), (5, 10), (6, 11)], [(7, 0, t)]))
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, table, 3, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+    got = np.zeros(t * h * d, np.float16)
+    ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, 11, C.c_size_t(0), got.ctypes.data_as(C.c_void_p), C.c_size_t(got.nbytes)))
+    st, act, _ = oracle.conv1d_update_silu_prefill(conv_state, x, conv_w, t, qkv_dim, k)
+    scaled = oracle.rms_scale_qk(act, d, 1e-6, qkv_dim, h, t).reshape(t, qkv_dim)
+    rst, core, _ = oracle.deltanet_recurrence_prefill(rec_state, scaled, b, a, a_log, dt, d, h, h, t)
+    want = core.reshape(-1).astype(F)
+    err = float(np.max(np.abs(got.astype(F) - want)) / np.sqrt(np.mean(want ** 2)))
+    assert err < 5e-3, err
