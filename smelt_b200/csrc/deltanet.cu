@@ -188,21 +188,23 @@ __global__ void __launch_bounds__(128) conv1d_update_silu_prefill_kernel(__half*
 }
 
 // Prompt chunk of the recurrence (prefill_recurrence.metal:290-775).  The loop over positions
-// is a dependent chain (row decays, warp sum, rank-one update, warp sum) and the kernel is bound
-// by instruction issue along it, not by bytes, so it is built to spend few instructions per
-// row and position and to keep several warps per scheduler:
-//  * a warp carries two rows of one head instead of the reference's one row per simdgroup; the
-//    two rows sit in the halves of packed fp32x2 registers, so every multiply and add of the
-//    reference's scalar code is one packed instruction for both rows, rounding each half as the
-//    scalar instruction would (mul.rn.f32x2 / add.rn.f32x2; no contraction into fused
-//    multiply-adds); the position's k and q are read and converted once for both rows;
+// is a dependent chain per row (decay, warp sum, rank-one update, warp sum) and the kernel is
+// bound by instruction issue along it, not by bytes.  Measured at 512 positions of 32 heads x
+// 128 x 128: 435 us with one row per warp, operands loaded and converted by every warp and two
+// warp sums per position; 230 us in this form (one row per warp with operands shared as floats
+// ran 275 us, four rows per warp 395 us):
+//  * a warp carries two rows of one head; the two rows sit in the halves of packed fp32x2
+//    registers, so every multiply and add of the reference's scalar code is one packed
+//    instruction for both rows, each half rounded as the scalar instruction would
+//    (mul.rn.f32x2 / add.rn.f32x2; nothing is contracted into a fused multiply-add); the
+//    position's k and q are read and converted once for both rows;
 //  * the warp sums share their shuffles: at lane distance 16 and 8 the lanes swap halves of the
 //    value set instead of adding every value everywhere, which leaves one value per lane for the
 //    last three steps.  The additions pair the same lanes in the same order as a butterfly per
 //    value, so the bits are those of simd_sum;
 //  * the read-out sums of position t (state . q) do not feed the state, so they ride along with
-//    the state . k sums of position t + 1 in one four-value reduction: one chain of five shuffle
-//    steps per position instead of two;
+//    the state . k sums of position t + 1 in that one four-value reduction (one chain of five
+//    shuffle steps per position instead of two) and leave in one store per stage;
 //  * the CTA's eight warps share a head: k, q and the CTA's slice of v for blocks of
 //    kDnPosPerStage positions come through a ring of cp.async stages in shared memory, requested
 //    two stages ahead; the gates of up to kDnGateBlock positions are computed once per CTA.
@@ -216,7 +218,7 @@ constexpr int kDnPosPerStage = 8;
 constexpr int kDnStages = 3;
 
 __host__ __device__ constexpr int dn_pos_halves(int d) { return 2 * d + kDnWarps * kDnRows; }  // k | q | the CTA's v values
-__host__ __device__ constexpr int dn_smem_bytes(int d) { return kDnStages * kDnPosPerStage * dn_pos_halves(d) * 2 + 2 * kDnGateBlock * 4; }
+__host__ __device__ constexpr int dn_smem_bytes(int d) { return kDnStages * kDnPosPerStage * dn_pos_halves(d) * 2 + kDnGateBlock * 8; }
 
 // Sum of each of four per-lane values over the warp in simd_sum's order; the total of value j
 // ends up in the eight lanes 8 j .. 8 j + 7.
@@ -263,11 +265,10 @@ __global__ void __launch_bounds__(kDnWarps * 32) deltanet_recurrence_prefill_ker
                                                                                     int qk_heads, int seq_len, __half* history, int vec, DevDyn dyn) {
     constexpr int D = EPL * 32, R = kDnRows, PB = kDnPosPerStage, NS = kDnStages, PH = dn_pos_halves(D);
     constexpr int CH = D / 4 + kDnWarps * R / 8;  // 16-byte pieces per position: k, q, v slice
-    static_assert(R == 2, "the two rows of a warp are the halves of a packed register");
+    static_assert(R == 2 && PB == 8, "two rows per packed register; a stage's sums leave through sixteen lanes");
     extern __shared__ __align__(16) uint8_t dn_smem[];
     __half* ring = reinterpret_cast<__half*>(dn_smem);  // [NS][PB][PH]
-    float* s_beta = reinterpret_cast<float*>(dn_smem + NS * PB * PH * 2);
-    float* s_decay = s_beta + kDnGateBlock;
+    float2* s_gate = reinterpret_cast<float2*>(dn_smem + NS * PB * PH * 2);  // [kDnGateBlock] {decay, beta}
     pdl_trigger();
     pdl_wait();
     if (dyn_skip(dyn)) return;
@@ -330,16 +331,19 @@ __global__ void __launch_bounds__(kDnWarps * 32) deltanet_recurrence_prefill_ker
             const int nb = min(kDnGateBlock, seq_len - p0);
             for (int t = tid; t < nb; t += kDnWarps * 32) {
                 const size_t pi = (size_t)(p0 + t) * value_heads + head;
-                s_beta[t] = sigmoid_staged_half(b_proj[pi]);
                 const __half xh = __hadd(a_proj[pi], dtb);
-                s_decay[t] = __half2float(__float2half_rn(expf(-ea * softplus_staged_half(xh))));
+                s_gate[t] = make_float2(__half2float(__float2half_rn(expf(-ea * softplus_staged_half(xh)))), sigmoid_staged_half(b_proj[pi]));
             }
             __syncthreads();
         }
         const __half* stage = ring + (size_t)(g % NS) * PB * PH;
+        const float2* gates = s_gate + p0 % kDnGateBlock;
         const int np = min(PB, seq_len - p0);
-        for (int pp = 0; pp < np; ++pp) {
-            const int pos = p0 + pp;
+        // One position.  After the reduction lanes 16-23 hold the first row's read-out sum of the position before it
+        // and lanes 24-31 the second row's; lane 16 + pp and lane 24 + pp keep them, and the stage's sums leave in one
+        // store after the loop.
+        float keep = 0.0f;
+        auto step = [&](int pp) {
             const __half* row = stage + pp * PH;
             __half kh[EPL], qh16[EPL], vh[R];
             load_halves<EPL>(row + lane * EPL, kh, true);
@@ -352,8 +356,8 @@ __global__ void __launch_bounds__(kDnWarps * 32) deltanet_recurrence_prefill_ker
                 kk[i] = make_float2(kf, kf);
                 qq[i] = make_float2(qf, qf);
             }
-            const float decay = s_decay[pos % kDnGateBlock], beta = s_beta[pos % kDnGateBlock];
-            const float2 dd = make_float2(decay, decay);
+            const float2 gate = gates[pp];
+            const float2 dd = make_float2(gate.x, gate.x);
             float2 kv = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int i = 0; i < EPL; ++i) {
@@ -361,9 +365,9 @@ __global__ void __launch_bounds__(kDnWarps * 32) deltanet_recurrence_prefill_ker
                 kv = __fadd2_rn(kv, __fmul2_rn(st[i], kk[i]));
             }
             const float red = simd_sum4_grouped(kv.x, kv.y, o_prev.x, o_prev.y, lane);
-            if (pos > 0 && lane >= 16 && (lane & 7) == 0) out[((size_t)(pos - 1) * value_heads + head) * D + dv0 + ((lane - 16) >> 3)] = __float2half_rn(red);
+            keep = (lane & 7) == pp ? red : keep;
             const float2 neg_kv = make_float2(-__shfl_sync(0xffffffffu, red, 0), -__shfl_sync(0xffffffffu, red, 8));
-            const float2 delta = __fmul2_rn(__fadd2_rn(make_float2(__half2float(vh[0]), __half2float(vh[1])), neg_kv), make_float2(beta, beta));
+            const float2 delta = __fmul2_rn(__fadd2_rn(make_float2(__half2float(vh[0]), __half2float(vh[1])), neg_kv), make_float2(gate.y, gate.y));
             float2 o = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int i = 0; i < EPL; ++i) {
@@ -375,11 +379,21 @@ __global__ void __launch_bounds__(kDnWarps * 32) deltanet_recurrence_prefill_ker
 #pragma unroll
                 for (int i = 0; i < EPL; ++i) {
                     const __half h0 = __float2half_rn(st[i].x), h1 = __float2half_rn(st[i].y);
-                    history[(size_t)(pos + 1) * hs + row_off + i] = h0;
-                    history[(size_t)(pos + 1) * hs + row_off + D + i] = h1;
+                    history[(size_t)(p0 + pp + 1) * hs + row_off + i] = h0;
+                    history[(size_t)(p0 + pp + 1) * hs + row_off + D + i] = h1;
                     st[i] = make_float2(__half2float(h0), __half2float(h1));
                 }
             }
+        };
+        if (np == PB) {
+#pragma unroll
+            for (int pp = 0; pp < PB; ++pp) step(pp);
+        } else {
+            for (int pp = 0; pp < np; ++pp) step(pp);
+        }
+        {
+            const int prev = p0 + (lane & 7) - 1;  // the position whose sums lanes 16 + pp and 24 + pp kept
+            if (lane >= 16 && (lane & 7) < np && prev >= 0) out[((size_t)prev * value_heads + head) * D + dv0 + ((lane >> 3) & 1)] = __float2half_rn(keep);
         }
     }
     cp_async_wait<0>();  // nothing of this CTA's may still be in flight when its shared memory retires
