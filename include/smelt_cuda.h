@@ -512,6 +512,25 @@ SMELT_CUDA_API smelt_status smelt_cuda_prefill(smelt_cuda_ctx* ctx, const smelt_
 SMELT_CUDA_API smelt_status smelt_cuda_signed_activation_bitplanes(smelt_cuda_ctx* ctx, const void* x_dev, const void* up_or_null_dev,
                                                                    void* planes_dev, void* scales_dev, int cols, int n_planes,
                                                                    int batch);
+/* Producers with another kernel's arithmetic in front (Resources/Shaders/signed_quant.metal:985-1298):
+ * the fp16 values the staged kernel would have written, then the same view.
+ *   SMELT_BITPLANE_FRONT_SIGMOID_MUL      sigmoid_mul_signed_activation_bitplanes_i6_g128: a * sigmoid(b); n_planes 6
+ *   SMELT_BITPLANE_FRONT_NORM_SCALE       norm_scale_signed_activation_bitplanes_i{2..6}_g128: a = x, c = norm weight,
+ *                                         norm_scale_dev = one float, the row's rsqrt(mean(x^2) + eps) from an earlier dispatch
+ *   SMELT_BITPLANE_FRONT_GATED_NORM_D128  rms_norm_gated_d128_signed_activation_bitplanes_i6_g128: a = x, b = gate [cols],
+ *                                         c = weight [128]; cols = heads * 128; a threadgroup width of 32 selects
+ *                                         rms_norm_gated_d128's arithmetic, any other width rms_norm_gated's */
+enum { SMELT_BITPLANE_FRONT_SIGMOID_MUL = 2, SMELT_BITPLANE_FRONT_NORM_SCALE = 3, SMELT_BITPLANE_FRONT_GATED_NORM_D128 = 4 };
+SMELT_CUDA_API smelt_status smelt_cuda_fused_activation_bitplanes(smelt_cuda_ctx* ctx, int front, const void* a_dev, const void* b_dev,
+                                                                  const void* c_dev, const void* norm_scale_dev, void* planes_dev,
+                                                                  void* scales_dev, int cols, int n_planes, float eps,
+                                                                  int threadgroup_width);
+/* signed_binary_embedding_gather_g128 / signed_ternary_embedding_gather_g128
+ * (Resources/Shaders/signed_quant.metal:690-745): out [batch, hidden] = sem(code) * scale of rows token_ids[b];
+ * format 1 binary, 2 ternary. */
+SMELT_CUDA_API smelt_status smelt_cuda_signed_embedding_gather(smelt_cuda_ctx* ctx, int format, const void* codes_dev,
+                                                               const void* scales_dev, const void* token_ids_dev, void* out_dev,
+                                                               int hidden, int batch);
 SMELT_CUDA_API smelt_status smelt_cuda_signed_bitplane_matvec(smelt_cuda_ctx* ctx, int format, int mode, const void* codes_dev,
                                                               const void* weight_scales_dev, const void* codes2_dev,
                                                               const void* weight_scales2_dev, const void* planes_dev,
@@ -542,6 +561,12 @@ SMELT_CUDA_API smelt_status smelt_cuda_deltanet_recurrence_decode(smelt_cuda_ctx
                                                                   int head_dim, int value_heads, int qk_heads);
 SMELT_CUDA_API smelt_status smelt_cuda_rms_norm_gated(smelt_cuda_ctx* ctx, const void* input_dev, const void* gate_dev,
                                                       const void* weight_dev, void* out_dev, int head_dim, float eps, int heads);
+/* rms_norm_gated as a threadgroup of threadgroup_width threads sums it (the width of the record that dispatches it:
+ * 32 or 128 in the reference's tables), or, with precise_d128 != 0, rms_norm_gated_d128 / rms_norm_gated_d128_batched
+ * (Resources/Shaders/norms_gated_precise.metal:7-87): the norm materialised in fp16 before the fp32 gate. */
+SMELT_CUDA_API smelt_status smelt_cuda_rms_norm_gated_ex(smelt_cuda_ctx* ctx, const void* input_dev, const void* gate_dev,
+                                                         const void* weight_dev, void* out_dev, int head_dim, float eps, int heads,
+                                                         int threadgroup_width, int precise_d128);
 /* Prompt-chunk forms (the DeltaNet layers of a prefill table).
  * conv1d_update_silu_prefill (Resources/Shaders/conv1d.metal:129-268: conv1d_update_silu_prefill,
  *   conv1d_update_silu_c6144_k4_prefill, conv1d_update_silu_prefill_checkpoint): qkv [seq_len,

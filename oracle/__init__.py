@@ -441,6 +441,26 @@ def rms_norm_gated(x, gate, weight, head_dim: int, eps: float, heads: int) -> np
     return out
 
 
+def rms_norm_gated_tg(x, gate, weight, head_dim: int, eps: float, heads: int, tgs: int) -> np.ndarray:
+    """rms_norm_gated as a threadgroup of `tgs` threads sums it."""
+    out = np.zeros((heads, head_dim), np.float16)
+    _check(lib().so_rms_norm_gated_tg(_p(_h(x)), _p(_h(gate)), _p(_h(weight)), _p(out), head_dim, C.c_float(eps), heads, tgs), "rms_norm_gated_tg")
+    return out
+
+
+def rms_norm_gated_d128(x, gate, weight, heads: int) -> np.ndarray:
+    out = np.zeros((heads, 128), np.float16)
+    _check(lib().so_rms_norm_gated_d128(_p(_h(x)), _p(_h(gate)), _p(_h(weight)), _p(out), heads), "rms_norm_gated_d128")
+    return out
+
+
+def signed_embedding_gather(fmt: int, codes, scales, token_ids, hidden: int) -> np.ndarray:
+    ids = np.ascontiguousarray(token_ids, np.int32)
+    out = np.zeros((len(ids), hidden), np.float16)
+    _check(lib().so_signed_embedding_gather(fmt, _p(_u8(codes)), _p(_h(scales)), _p(ids), _p(out), hidden, len(ids)), "signed_embedding_gather")
+    return out
+
+
 # ── signed activation bit-planes (signed_quant.metal:751-2101) ──
 def signed_activation_bitplanes(x, cols: int, planes: int):
     """Returns (planes uint32 [groups, planes, 4], scales fp16 [groups])."""
@@ -456,6 +476,29 @@ def swiglu_signed_activation_bitplanes_i5(gate, up, cols: int):
     out = np.zeros((groups, 5, 4), np.uint32)
     sc = np.zeros(groups, np.float16)
     _check(lib().so_swiglu_signed_activation_bitplanes_i5(_p(_h(gate)), _p(_h(up)), cols, _p(out), _p(sc)), "swiglu_signed_activation_bitplanes_i5")
+    return out, sc
+
+
+def sigmoid_mul_signed_activation_bitplanes_i6(a, b, cols: int):
+    groups = cols // 128
+    out, sc = np.zeros((groups, 6, 4), np.uint32), np.zeros(groups, np.float16)
+    _check(lib().so_sigmoid_mul_signed_activation_bitplanes_i6(_p(_h(a)), _p(_h(b)), cols, _p(out), _p(sc)), "sigmoid_mul_signed_activation_bitplanes_i6")
+    return out, sc
+
+
+def norm_scale_signed_activation_bitplanes(norm_scale: float, x, norm_weight, cols: int, planes: int):
+    groups = cols // 128
+    out, sc = np.zeros((groups, planes, 4), np.uint32), np.zeros(groups, np.float16)
+    rs = np.array([norm_scale], np.float32)
+    _check(lib().so_norm_scale_signed_activation_bitplanes(_p(rs), _p(_h(x)), _p(_h(norm_weight)), cols, planes, _p(out), _p(sc)),
+           "norm_scale_signed_activation_bitplanes")
+    return out, sc
+
+
+def rms_norm_gated_d128_signed_activation_bitplanes_i6(x, gate, weight, heads: int, eps: float, tgs: int):
+    out, sc = np.zeros((heads, 6, 4), np.uint32), np.zeros(heads, np.float16)
+    _check(lib().so_rms_norm_gated_d128_signed_activation_bitplanes_i6(_p(_h(x)), _p(_h(gate)), _p(_h(weight)), heads, C.c_float(eps), tgs, _p(out), _p(sc)),
+           "rms_norm_gated_d128_signed_activation_bitplanes_i6")
     return out, sc
 
 

@@ -1128,6 +1128,91 @@ SO_API int so_rms_norm_gated(const uint16_t *input, const uint16_t *gate, const 
     return SO_OK;
 }
 
+/* rms_norm_gated with the threadgroup width the record dispatches it with (norms.metal:1093-1143):
+ * thread t adds x[t]^2, x[t + tgs]^2, ... in that order, every simdgroup of 32 threads sums its
+ * lanes (simd_sum), the simdgroups' partial sums are added one after the other.  tgs = 32 or 128
+ * in the reference's tables. */
+static float gated_norm_rs(const uint16_t *x, int head_dim, float eps, int tgs) {
+    float total = 0.0f;
+    for (int s = 0; s < tgs / 32; ++s) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            float p = 0.0f;
+            for (int i = s * 32 + l; i < head_dim; i += tgs) p += h2f(x[i]) * h2f(x[i]);
+            lane[l] = p;
+        }
+        total += simd_sum32(lane);
+    }
+    return 1.0f / sqrtf(total / (float)head_dim + eps);
+}
+static inline uint16_t gated_norm_value(uint16_t x, uint16_t g, uint16_t w, float rs) {
+    const float gv = h2f(g);
+    const float silu = gv / (1.0f + expf(-gv));
+    return f2h(h2f(w) * (h2f(x) * rs) * silu);
+}
+SO_API int so_rms_norm_gated_tg(const uint16_t *input, const uint16_t *gate, const uint16_t *weight, uint16_t *out, int head_dim,
+                                float eps, int heads, int tgs) {
+    if (head_dim <= 0 || heads <= 0 || tgs < 32 || tgs % 32 || tgs > 1024) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < heads; ++h) {
+        const uint16_t *x = input + (size_t)h * head_dim, *g = gate + (size_t)h * head_dim;
+        const float rs = gated_norm_rs(x, head_dim, eps, tgs);
+        for (int i = 0; i < head_dim; ++i) out[(size_t)h * head_dim + i] = gated_norm_value(x[i], g[i], weight[i], rs);
+    }
+    return SO_OK;
+}
+
+/* rms_norm_gated_d128 and rms_norm_gated_d128_batched (Resources/Shaders/norms_gated_precise.metal:
+ * 7-87): one simdgroup per head of 128, lane l adds the squares of its four adjacent values
+ * 4 l .. 4 l + 3, simd_sum; value = half(float(w * half(x * rs)) * (g * sigmoid(g))) with the
+ * norm materialised in fp16 (the half product w * half(..) included), the sigmoid in its stable
+ * spelling (tail = 1 / (1 + exp(|g|))) and eps = 1e-6. */
+static float gated_norm_d128_rs(const uint16_t *x) {
+    float lane[32];
+    for (int l = 0; l < 32; ++l) {
+        float p = 0.0f;
+        for (int i = 0; i < 4; ++i) p += h2f(x[4 * l + i]) * h2f(x[4 * l + i]);
+        lane[l] = p;
+    }
+    return 1.0f / sqrtf(simd_sum32(lane) / 128.0f + 1e-6f);
+}
+static inline uint16_t gated_norm_d128_value(uint16_t x, uint16_t g, uint16_t w, float rs) {
+    const float normalized = round_h(h2f(w) * round_h(h2f(x) * rs));
+    const float gv = h2f(g);
+    const float tail = 1.0f / (1.0f + expf(fabsf(gv)));
+    const float sig = gv < 0.0f ? tail : 1.0f - tail;
+    return f2h(normalized * (gv * sig));
+}
+SO_API int so_rms_norm_gated_d128(const uint16_t *input, const uint16_t *gate, const uint16_t *weight, uint16_t *out, int heads) {
+    if (heads <= 0) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < heads; ++h) {
+        const uint16_t *x = input + (size_t)h * 128, *g = gate + (size_t)h * 128;
+        const float rs = gated_norm_d128_rs(x);
+        for (int i = 0; i < 128; ++i) out[(size_t)h * 128 + i] = gated_norm_d128_value(x[i], g[i], weight[i], rs);
+    }
+    return SO_OK;
+}
+
+/* signed_binary_embedding_gather_g128 / signed_ternary_embedding_gather_g128
+ * (Resources/Shaders/signed_quant.metal:690-745): out[b, c] = half(sem(code[row, c]) *
+ * scale[row, c / 128]), row = token_ids[b]; binary bit 0 / 1 = -1 / +1 (LSB first), ternary
+ * 2-bit code - 1. */
+SO_API int so_signed_embedding_gather(int format, const uint8_t *codes, const uint16_t *scales, const int32_t *token_ids, uint16_t *out,
+                                      int hidden, int batch) {
+    if ((format != 1 && format != 2) || hidden <= 0 || hidden % 128 || batch <= 0) return SO_ERR_GEOMETRY;
+    const size_t row_bytes = format == 2 ? (size_t)hidden / 4 : (size_t)hidden / 8;
+    const int groups = hidden / 128;
+    for (int b = 0; b < batch; ++b) {
+        const size_t row = (size_t)token_ids[b];
+        for (int c = 0; c < hidden; ++c) {
+            float v;
+            if (format == 2) v = (float)((int)((codes[row * row_bytes + c / 4] >> (2 * (c & 3))) & 3u) - 1);
+            else v = ((codes[row * row_bytes + c / 8] >> (c & 7)) & 1u) ? 1.0f : -1.0f;
+            out[(size_t)b * hidden + c] = f2h(v * h2f(scales[row * groups + c / 128]));
+        }
+    }
+    return SO_OK;
+}
+
 /* ───────────────────── signed activation bit-planes (the Bonsai low-bit path) ─────────────────────
  * Producers turn 128 activations into a sign plane and PLANES-1 magnitude planes of a symmetric
  * integer quantisation plus one fp16 scale; consumers multiply the packed 1-bit / 2-bit weights
@@ -1179,6 +1264,71 @@ SO_API int so_swiglu_signed_activation_bitplanes_i5(const uint16_t *gate, const 
     for (int g = 0; g < cols / 128; ++g) {
         for (int i = 0; i < 128; ++i) v[i] = swiglu_staged_half(gate[(size_t)g * 128 + i], up[(size_t)g * 128 + i]);
         bitplane_group(v, 5, out_planes + (size_t)g * 20, out_scales + g);
+    }
+    return SO_OK;
+}
+
+/* sigmoid_mul_signed_activation_bitplanes_i6_g128 (signed_quant.metal:985-1031): the staged fp16
+ * a * sigmoid(b) (tail = 1 / (1 + exp(|b|)) in half arithmetic), then the i6 view. */
+SO_API int so_sigmoid_mul_signed_activation_bitplanes_i6(const uint16_t *a, const uint16_t *b, int cols, uint32_t *out_planes,
+                                                         uint16_t *out_scales) {
+    if (cols <= 0 || cols % 128) return SO_ERR_GEOMETRY;
+    uint16_t v[128];
+    for (int g = 0; g < cols / 128; ++g) {
+        for (int i = 0; i < 128; ++i) {
+            const float bv = h2f(b[(size_t)g * 128 + i]);
+            const float tail = round_h(1.0f / round_h(1.0f + round_h(expf(fabsf(bv)))));
+            const float sig = bv < 0.0f ? tail : round_h(1.0f - tail);
+            v[i] = f2h(h2f(a[(size_t)g * 128 + i]) * sig);
+        }
+        bitplane_group(v, 6, out_planes + (size_t)g * 24, out_scales + g);
+    }
+    return SO_OK;
+}
+
+/* norm_scale_signed_activation_bitplanes_i{2..6}_g128 (signed_quant.metal:1175-1298): the value
+ * rms_norm_1pw would write, half(half(x * rs) * half(1 + w)) with rs = norm_scale[0] computed
+ * by an earlier dispatch, then the view. */
+SO_API int so_norm_scale_signed_activation_bitplanes(const float *norm_scale, const uint16_t *input, const uint16_t *norm_weight, int cols,
+                                                     int planes, uint32_t *out_planes, uint16_t *out_scales) {
+    if (cols <= 0 || cols % 128 || planes < 2 || planes > 6) return SO_ERR_GEOMETRY;
+    const float rs = norm_scale[0];
+    uint16_t v[128];
+    for (int g = 0; g < cols / 128; ++g) {
+        for (int i = 0; i < 128; ++i) {
+            const size_t c = (size_t)g * 128 + i;
+            v[i] = f2h(round_h(h2f(input[c]) * rs) * round_h(1.0f + h2f(norm_weight[c])));
+        }
+        bitplane_group(v, planes, out_planes + (size_t)g * planes * 4, out_scales + g);
+    }
+    return SO_OK;
+}
+
+/* rms_norm_gated_d128_signed_activation_bitplanes_i6_g128 (signed_quant.metal:1040-1173): the
+ * gated norm of a head of 128 and its i6 view in one dispatch.  A threadgroup of 32 threads takes
+ * rms_norm_gated_d128's arithmetic, any other width rms_norm_gated's (the fused record keeps the
+ * norm's dispatch, Sources/SmeltCompiler/SmeltFusionPlanner.swift:1239-1280). */
+SO_API int so_rms_norm_gated_d128_signed_activation_bitplanes_i6(const uint16_t *input, const uint16_t *gate, const uint16_t *weight,
+                                                                 int heads, float eps, int tgs, uint32_t *out_planes, uint16_t *out_scales) {
+    if (heads <= 0 || tgs < 32 || tgs % 32 || tgs > 1024) return SO_ERR_GEOMETRY;
+    uint16_t v[128];
+    for (int h = 0; h < heads; ++h) {
+        const uint16_t *x = input + (size_t)h * 128, *g = gate + (size_t)h * 128;
+        if (tgs == 32) {
+            /* the fused kernel passes eps to the precise arithmetic (signed_quant.metal:1083-1085) */
+            float lane[32];
+            for (int l = 0; l < 32; ++l) {
+                float p = 0.0f;
+                for (int i = 0; i < 4; ++i) p += h2f(x[4 * l + i]) * h2f(x[4 * l + i]);
+                lane[l] = p;
+            }
+            const float rs = 1.0f / sqrtf(simd_sum32(lane) / 128.0f + eps);
+            for (int i = 0; i < 128; ++i) v[i] = gated_norm_d128_value(x[i], g[i], weight[i], rs);
+        } else {
+            const float rs = gated_norm_rs(x, 128, eps, tgs);
+            for (int i = 0; i < 128; ++i) v[i] = gated_norm_value(x[i], g[i], weight[i], rs);
+        }
+        bitplane_group(v, 6, out_planes + (size_t)h * 24, out_scales + h);
     }
     return SO_OK;
 }

@@ -26,35 +26,18 @@ namespace smelt {
 namespace {
 
 
-// One warp per (group, batch row).  SWIGLU: the values are swiglu_staged(gate, up) instead of x.
-template <int PLANES, bool SWIGLU>
-__global__ void __launch_bounds__(128) bitplane_producer_kernel(const __half* x, const __half* up, uint32_t* planes, __half* scales, int cols,
-                                                                DevDyn dyn) {
-    pdl_trigger();
-    pdl_wait();
-    if (dyn_skip(dyn)) return;
+// The view of one group held by one warp: v[w] is the fp16 value of column 32 w + lane.
+template <int PLANES>
+__device__ __forceinline__ void pack_group(const float (&v)[4], uint32_t* out, __half* scale_out, int lane) {
     constexpr int kMaxQ = (1 << (PLANES - 1)) - 1;
     constexpr bool kMatchStored = PLANES >= 4;
-    const int groups = cols / 128, lane = threadIdx.x & 31;
-    const int group = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (group >= groups) return;
-    const size_t row = blockIdx.y;
-    const size_t base = row * cols + (size_t)group * 128;
-    float v[4], max_abs = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        __half h = x[base + w * 32 + lane];
-        if (SWIGLU) h = swiglu_staged(h, up[base + w * 32 + lane]);
-        v[w] = __half2float(h);
-        max_abs = fmaxf(max_abs, fabsf(v[w]));
-    }
+    float max_abs = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) max_abs = fmaxf(max_abs, __shfl_xor_sync(0xffffffffu, max_abs, off));
     const float producer_scale = max_abs > 0.0f ? __fdiv_rn(max_abs, (float)kMaxQ) : 1.0f;
     const __half stored = __float2half_rn(producer_scale);
     const float scale = kMatchStored ? __half2float(stored) : producer_scale;
-    if (lane == 0) scales[row * groups + group] = stored;
-    uint32_t* out = planes + (row * groups + group) * (PLANES * 4);
+    if (lane == 0) *scale_out = stored;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
         const float c = fminf(fmaxf(__fdiv_rn(v[w], scale), -(float)kMaxQ), (float)kMaxQ);
@@ -66,6 +49,98 @@ __global__ void __launch_bounds__(128) bitplane_producer_kernel(const __half* x,
             const uint32_t word = __ballot_sync(0xffffffffu, bit);
             if (lane == 0) out[p * 4 + w] = word;
         }
+    }
+}
+
+// One warp per (group, batch row).  SWIGLU: the values are swiglu_staged(gate, up) instead of x.
+template <int PLANES, bool SWIGLU>
+__global__ void __launch_bounds__(128) bitplane_producer_kernel(const __half* x, const __half* up, uint32_t* planes, __half* scales, int cols,
+                                                                DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const int groups = cols / 128, lane = threadIdx.x & 31;
+    const int group = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (group >= groups) return;
+    const size_t row = blockIdx.y;
+    const size_t base = row * cols + (size_t)group * 128;
+    float v[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        __half h = x[base + w * 32 + lane];
+        if (SWIGLU) h = swiglu_staged(h, up[base + w * 32 + lane]);
+        v[w] = __half2float(h);
+    }
+    pack_group<PLANES>(v, planes + (row * groups + group) * (PLANES * 4), scales + row * groups + group, lane);
+}
+
+// Producers with another kernel's arithmetic in front (signed_quant.metal:985-1298): every lane
+// makes the fp16 values the staged kernel would have written, then the view is the same.
+//   FRONT 2  a * sigmoid(b) in half arithmetic (sigmoid_mul), i6
+//   FRONT 3  half(half(x * rs) * half(1 + w)), rs = norm_scale[0] from an earlier dispatch (rms_norm_1pw), i2..i6
+//   FRONT 4  the gated RMS norm of a head of 128 = one group: a threadgroup of 32 threads takes
+//            rms_norm_gated_d128's arithmetic, any other width rms_norm_gated's, i6
+template <int PLANES, int FRONT>
+__global__ void __launch_bounds__(128) bitplane_fused_producer_kernel(const __half* a, const __half* b, const __half* c, const float* norm_scale,
+                                                                      uint32_t* planes, __half* scales, int cols, float eps, int tgs, DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const int groups = cols / 128, lane = threadIdx.x & 31;
+    const int group = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (group >= groups) return;
+    const size_t base = (size_t)group * 128;
+    float v[4];
+    if (FRONT == 2) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const size_t col = base + w * 32 + lane;
+            const __half bv = b[col];
+            const __half tail = __hdiv(__float2half_rn(1.0f), __hadd(__float2half_rn(1.0f), __float2half_rn(expf(fabsf(__half2float(bv))))));
+            const __half sig = __half2float(bv) < 0.0f ? tail : __hsub(__float2half_rn(1.0f), tail);
+            v[w] = __half2float(__hmul(a[col], sig));
+        }
+    } else if (FRONT == 3) {
+        const float rs = norm_scale[0];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const size_t col = base + w * 32 + lane;
+            const __half normalized = __float2half_rn(__fmul_rn(__half2float(a[col]), rs));
+            const __half direct = __float2half_rn(__fadd_rn(1.0f, __half2float(c[col])));
+            v[w] = __half2float(__hmul(normalized, direct));
+        }
+    } else {
+        const bool precise = tgs == 32;
+        const float rs = precise ? gated_norm_d128_rs(a + base, eps, lane) : gated_norm_rs(a + base, 128, eps, tgs, lane);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int i = w * 32 + lane;
+            v[w] = __half2float(precise ? gated_norm_d128_value(a[base + i], b[base + i], c[i], rs) : gated_norm_value(a[base + i], b[base + i], c[i], rs));
+        }
+    }
+    pack_group<PLANES>(v, planes + (size_t)group * (PLANES * 4), scales + group, lane);
+}
+
+// signed_binary_embedding_gather_g128 / signed_ternary_embedding_gather_g128 (signed_quant.metal:690-745):
+// out[b, c] = half(sem(code[row, c]) * scale[row, c / 128]), row = token_ids[b].  One thread per eight columns.
+template <bool TERNARY>
+__global__ void __launch_bounds__(128) signed_embedding_gather_kernel(const uint8_t* codes, const __half* scales, const int32_t* token_ids, __half* out,
+                                                                      int hidden, DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c8 * 8 >= hidden) return;
+    const size_t row = (size_t)token_ids[blockIdx.y];
+    const size_t row_bytes = TERNARY ? (size_t)hidden / 4 : (size_t)hidden / 8;
+    const float scale = __half2float(scales[row * (hidden / 128) + c8 / 16]);
+    const uint8_t* src = codes + row * row_bytes + (TERNARY ? c8 * 2 : c8);
+    const uint32_t bits = TERNARY ? (uint32_t)src[0] | ((uint32_t)src[1] << 8) : (uint32_t)src[0];
+    __half* dst = out + (size_t)blockIdx.y * hidden + (size_t)c8 * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float v = TERNARY ? (float)((int)((bits >> (2 * i)) & 3u) - 1) : (((bits >> i) & 1u) ? 1.0f : -1.0f);
+        dst[i] = __float2half_rn(__fmul_rn(v, scale));
     }
 }
 
@@ -260,6 +335,50 @@ cudaError_t launch_bitplane_producer(const Launch& l, const __half* x, const __h
     }
 }
 
+template <int PLANES, int FRONT>
+cudaError_t launch_fused_producer_t(const Launch& l, const __half* a, const __half* b, const __half* c, const float* norm_scale, uint32_t* planes,
+                                    __half* scales, int cols, float eps, int tgs) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cfg_launch(l, cfg, attr, dim3((cols / 128 + 3) / 4, 1), dim3(128));
+    auto k = bitplane_fused_producer_kernel<PLANES, FRONT>;
+    prefer_max_shared(k);
+    return cudaLaunchKernelEx(&cfg, k, a, b, c, norm_scale, planes, scales, cols, eps, tgs, dev_dyn(l));
+}
+
+cudaError_t launch_bitplane_fused_producer(const Launch& l, int front, const __half* a, const __half* b, const __half* c, const float* norm_scale,
+                                           uint32_t* planes, __half* scales, int cols, int n_planes, float eps, int tgs) {
+    if (cols <= 0 || cols % 128) return cudaErrorInvalidValue;
+    if (front == 2) return n_planes == 6 && a && b ? launch_fused_producer_t<6, 2>(l, a, b, nullptr, nullptr, planes, scales, cols, eps, 32) : cudaErrorInvalidValue;
+    if (front == 4) {
+        if (n_planes != 6 || !a || !b || !c || tgs < 32 || tgs % 32 || tgs > 1024) return cudaErrorInvalidValue;
+        return launch_fused_producer_t<6, 4>(l, a, b, c, nullptr, planes, scales, cols, eps, tgs);
+    }
+    if (front != 3 || !a || !c || !norm_scale) return cudaErrorInvalidValue;
+    switch (n_planes) {
+        case 2: return launch_fused_producer_t<2, 3>(l, a, nullptr, c, norm_scale, planes, scales, cols, eps, 32);
+        case 3: return launch_fused_producer_t<3, 3>(l, a, nullptr, c, norm_scale, planes, scales, cols, eps, 32);
+        case 4: return launch_fused_producer_t<4, 3>(l, a, nullptr, c, norm_scale, planes, scales, cols, eps, 32);
+        case 5: return launch_fused_producer_t<5, 3>(l, a, nullptr, c, norm_scale, planes, scales, cols, eps, 32);
+        case 6: return launch_fused_producer_t<6, 3>(l, a, nullptr, c, norm_scale, planes, scales, cols, eps, 32);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_signed_embedding_gather(const Launch& l, int format, const uint8_t* codes, const __half* scales, const int32_t* token_ids, __half* out,
+                                           int hidden, int batch) {
+    if ((format != 1 && format != 2) || hidden <= 0 || hidden % 128 || batch <= 0) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cfg_launch(l, cfg, attr, dim3((hidden / 8 + 127) / 128, batch), dim3(128));
+    if (format == 2) {
+        prefer_max_shared(signed_embedding_gather_kernel<true>);
+        return cudaLaunchKernelEx(&cfg, signed_embedding_gather_kernel<true>, codes, scales, token_ids, out, hidden, dev_dyn(l));
+    }
+    prefer_max_shared(signed_embedding_gather_kernel<false>);
+    return cudaLaunchKernelEx(&cfg, signed_embedding_gather_kernel<false>, codes, scales, token_ids, out, hidden, dev_dyn(l));
+}
+
 cudaError_t launch_bitplane_matvec(const Launch& l, const BitplaneArgs& a) {
     if (a.rows <= 0 || a.cols <= 0 || a.cols % 128 || a.batch <= 0 || (a.format != 1 && a.format != 2)) return cudaErrorInvalidValue;
     if (a.mode == 2 && (!a.codes2 || !a.wscales2)) return cudaErrorInvalidValue;
@@ -295,6 +414,31 @@ smelt_status smelt_cuda_signed_activation_bitplanes(smelt_cuda_ctx* ctx, const v
     if (!x || !planes || !scales || cols <= 0 || cols % 128 || batch <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "activation bit-planes: cols a multiple of 128");
     if (n_planes < 2 || n_planes > 6 || (up_or_null && n_planes != 5)) return fail(ctx, SMELT_ERR_UNSUPPORTED, "activation bit-planes: 2..6 planes (the SwiGLU producer: 5)");
     return check_cuda(ctx, launch_bitplane_producer(typed(ctx), (const __half*)x, (const __half*)up_or_null, (uint32_t*)planes, (__half*)scales, cols, n_planes, batch), "activation bit-planes");
+}
+
+smelt_status smelt_cuda_fused_activation_bitplanes(smelt_cuda_ctx* ctx, int front, const void* a, const void* b, const void* c, const void* norm_scale,
+                                                   void* planes, void* scales, int cols, int n_planes, float eps, int threadgroup_width) {
+    if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!planes || !scales || cols <= 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "fused activation bit-planes: cols a multiple of 128");
+    const bool ok = (front == SMELT_BITPLANE_FRONT_SIGMOID_MUL && a && b && n_planes == 6) ||
+                    (front == SMELT_BITPLANE_FRONT_NORM_SCALE && a && c && norm_scale && n_planes >= 2 && n_planes <= 6) ||
+                    (front == SMELT_BITPLANE_FRONT_GATED_NORM_D128 && a && b && c && n_planes == 6 && threadgroup_width >= 32 && threadgroup_width % 32 == 0 &&
+                     threadgroup_width <= 1024);
+    if (!ok) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "fused activation bit-planes: operands or plane count do not fit the front end");
+    return check_cuda(ctx, launch_bitplane_fused_producer(typed(ctx), front, (const __half*)a, (const __half*)b, (const __half*)c, (const float*)norm_scale,
+                                                          (uint32_t*)planes, (__half*)scales, cols, n_planes, eps, threadgroup_width),
+                      "fused activation bit-planes");
+}
+
+smelt_status smelt_cuda_signed_embedding_gather(smelt_cuda_ctx* ctx, int format, const void* codes, const void* scales, const void* token_ids, void* out,
+                                                int hidden, int batch) {
+    if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!codes || !scales || !token_ids || !out || hidden <= 0 || hidden % 128 || batch <= 0 || (format != 1 && format != 2))
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "signed embedding gather: bad arguments");
+    return check_cuda(ctx, launch_signed_embedding_gather(typed(ctx), format, (const uint8_t*)codes, (const __half*)scales, (const int32_t*)token_ids, (__half*)out, hidden, batch),
+                      "signed embedding gather");
 }
 
 smelt_status smelt_cuda_signed_bitplane_matvec(smelt_cuda_ctx* ctx, int format, int mode, const void* codes, const void* weight_scales,

@@ -247,6 +247,48 @@ __device__ __forceinline__ float simd_sum_lane0(float v) {
     return v;
 }
 
+// Gated RMS norm of one head by one warp (Resources/Shaders/norms.metal:1093-1143,
+// norms_gated_precise.metal:7-52).  rs as a threadgroup of tgs threads sums it: thread t adds
+// x[t]^2, x[t + tgs]^2, ..., each simdgroup sums its lanes, the simdgroups' sums are added in
+// order; the d128 kernel's lanes add four adjacent squares each.  The total is the same in
+// every lane.
+__device__ __forceinline__ float gated_norm_rs(const __half* x, int head_dim, float eps, int tgs, int lane) {
+    float total = 0.0f;
+    for (int s = 0; s < tgs / 32; ++s) {
+        float p = 0.0f;
+        for (int i = s * 32 + lane; i < head_dim; i += tgs) {
+            const float v = __half2float(x[i]);
+            p = __fadd_rn(p, __fmul_rn(v, v));
+        }
+        total = __fadd_rn(total, __shfl_sync(0xffffffffu, simd_sum_lane0(p), 0));
+    }
+    return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)head_dim), eps)));
+}
+__device__ __forceinline__ float gated_norm_d128_rs(const __half* x, float eps, int lane) {
+    float p = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float v = __half2float(x[4 * lane + i]);
+        p = __fadd_rn(p, __fmul_rn(v, v));
+    }
+    const float total = __shfl_sync(0xffffffffu, simd_sum_lane0(p), 0);
+    return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(total, 128.0f), eps)));
+}
+// half(w * (x * rs) * silu(g)), silu in fp32
+__device__ __forceinline__ __half gated_norm_value(__half x, __half g, __half w, float rs) {
+    const float gf = __half2float(g);
+    const float silu = __fdiv_rn(gf, __fadd_rn(1.0f, expf(-gf)));
+    return __float2half_rn(__fmul_rn(__fmul_rn(__half2float(w), __fmul_rn(__half2float(x), rs)), silu));
+}
+// half(float(w * half(x * rs)) * (g * sigmoid(g))): the norm materialised in fp16, the stable sigmoid in fp32
+__device__ __forceinline__ __half gated_norm_d128_value(__half x, __half g, __half w, float rs) {
+    const __half normalized = __hmul(w, __float2half_rn(__fmul_rn(__half2float(x), rs)));
+    const float gf = __half2float(g);
+    const float tail = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(fabsf(gf))));
+    const float sig = gf < 0.0f ? tail : __fsub_rn(1.0f, tail);
+    return __float2half_rn(__fmul_rn(__half2float(normalized), __fmul_rn(gf, sig)));
+}
+
 // Error word shared by all kernels of a context: 0 = ok; kernels OR in a code when a bounded
 // wait gives up so the host can report it instead of hanging.
 enum : uint32_t { KERR_BARRIER_TIMEOUT = 1u, KERR_FLAG_TIMEOUT = 2u };

@@ -408,26 +408,19 @@ __global__ void __launch_bounds__(kDnWarps * 32) deltanet_recurrence_prefill_ker
     }
 }
 
-// One warp per head: out = half(w * (x * rsqrt(mean(x^2) + eps)) * silu(g)); may run in place.
+// One warp per head; may run in place.  tgs: the threadgroup width whose summation order the sum of
+// squares follows (rms_norm_gated); precise: rms_norm_gated_d128's arithmetic (head_dim 128).
 __global__ void rms_norm_gated_kernel(const __half* input, const __half* gate, const __half* weight, __half* out, int head_dim, float eps,
-                                      DevDyn dyn) {
+                                      int tgs, int precise, DevDyn dyn) {
     pdl_trigger();
     pdl_wait();
     if (dyn_skip(dyn)) return;
     const int lane = threadIdx.x;
     const size_t off = (size_t)blockIdx.x * head_dim;
-    float sum = 0.0f;
-    for (int i = lane; i < head_dim; i += 32) {
-        const float v = __half2float(input[off + i]);
-        sum += v * v;
-    }
-    sum = warp_sum(sum);
-    const float rs = __frcp_rn(__fsqrt_rn(sum / (float)head_dim + eps));
-    for (int i = lane; i < head_dim; i += 32) {
-        const float x = __half2float(input[off + i]), g = __half2float(gate[off + i]);
-        const float silu = g / (1.0f + expf(-g));
-        out[off + i] = __float2half_rn(__half2float(weight[i]) * (x * rs) * silu);
-    }
+    const float rs = precise ? gated_norm_d128_rs(input + off, eps, lane) : gated_norm_rs(input + off, head_dim, eps, tgs, lane);
+    for (int i = lane; i < head_dim; i += 32)
+        out[off + i] = precise ? gated_norm_d128_value(input[off + i], gate[off + i], weight[i], rs)
+                               : gated_norm_value(input[off + i], gate[off + i], weight[i], rs);
 }
 
 cudaError_t cfg_launch(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block) {
@@ -525,13 +518,13 @@ cudaError_t launch_deltanet_recurrence_prefill(const Launch& l, __half* state, c
 }
 
 cudaError_t launch_rms_norm_gated(const Launch& l, const __half* input, const __half* gate, const __half* weight, __half* out, int head_dim,
-                                  float eps, int heads) {
-    if (head_dim <= 0 || heads <= 0) return cudaErrorInvalidValue;
+                                  float eps, int heads, int tgs, bool precise_d128) {
+    if (head_dim <= 0 || heads <= 0 || tgs < 32 || tgs % 32 || tgs > 1024 || (precise_d128 && head_dim != 128)) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cfg_launch(l, cfg, attr, dim3(heads), dim3(32));
     prefer_max_shared(rms_norm_gated_kernel);
-    return cudaLaunchKernelEx(&cfg, rms_norm_gated_kernel, input, gate, weight, out, head_dim, eps, dev_dyn(l));
+    return cudaLaunchKernelEx(&cfg, rms_norm_gated_kernel, input, gate, weight, out, head_dim, eps, tgs, precise_d128 ? 1 : 0, dev_dyn(l));
 }
 
 }  // namespace smelt
@@ -607,7 +600,18 @@ smelt_status smelt_cuda_rms_norm_gated(smelt_cuda_ctx* ctx, const void* input, c
     if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
     if (!input || !gate || !weight || !out || head_dim <= 0 || heads <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "gated rms norm: bad arguments");
-    return check_cuda(ctx, launch_rms_norm_gated(typed(ctx), (const __half*)input, (const __half*)gate, (const __half*)weight, (__half*)out, head_dim, eps, heads), "gated rms norm");
+    return check_cuda(ctx, launch_rms_norm_gated(typed(ctx), (const __half*)input, (const __half*)gate, (const __half*)weight, (__half*)out, head_dim, eps, heads, 32, false), "gated rms norm");
+}
+
+smelt_status smelt_cuda_rms_norm_gated_ex(smelt_cuda_ctx* ctx, const void* input, const void* gate, const void* weight, void* out, int head_dim,
+                                          float eps, int heads, int threadgroup_width, int precise_d128) {
+    if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!input || !gate || !weight || !out || head_dim <= 0 || heads <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "gated rms norm: bad arguments");
+    if (threadgroup_width < 32 || threadgroup_width % 32 || threadgroup_width > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "gated rms norm: threadgroup width a multiple of 32 up to 1024");
+    if (precise_d128 && head_dim != 128) return fail(ctx, SMELT_ERR_UNSUPPORTED, "gated rms norm: the precise form is for heads of 128");
+    return check_cuda(ctx, launch_rms_norm_gated(typed(ctx), (const __half*)input, (const __half*)gate, (const __half*)weight, (__half*)out, head_dim, eps, heads,
+                                                 threadgroup_width, precise_d128 != 0), "gated rms norm");
 }
 
 }  // extern "C"

@@ -106,6 +106,8 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"signed_binary_gate_up_swiglu_g128_rows8", PK_SIGNED_GATEUP, 1, false},
         {"signed_binary_gate_up_swiglu_g128_rows8_batched_b4", PK_SIGNED_GATEUP, 1, true},
         {"signed_ternary_affine_matvec_g128_rows8", PK_SIGNED_TERNARY_AFFINE, 2, false},
+        {"signed_binary_embedding_gather_g128", PK_SIGNED_EMBEDDING_GATHER, 1, false},
+        {"signed_ternary_embedding_gather_g128", PK_SIGNED_EMBEDDING_GATHER, 2, false},
         {"kv_cache_update", PK_KV_UPDATE, 0, false},
         {"apply_rope", PK_APPLY_ROPE, 0, false},
         {"rope_kv_cache_update", PK_ROPE_KV_UPDATE, 0, false},
@@ -145,6 +147,22 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             *out = p;
             return true;
         }
+        // producers with another kernel's arithmetic in front (signed_quant.metal:985-1298)
+        if (name == "sigmoid_mul_signed_activation_bitplanes_i6_g128") {
+            p.kind = PK_BITPLANE_SIGMOID_MUL_PRODUCER; p.planes = 6;
+            *out = p;
+            return true;
+        }
+        if (name == "rms_norm_gated_d128_signed_activation_bitplanes_i6_g128") {
+            p.kind = PK_BITPLANE_GATED_NORM_PRODUCER; p.planes = 6;
+            *out = p;
+            return true;
+        }
+        if (sscanf(name.c_str(), "norm_scale_signed_activation_bitplanes_i%d_g128%n", &planes, &n) == 1 && planes >= 2 && planes <= 6 && name.substr(n).empty()) {
+            p.kind = PK_BITPLANE_NORM_SCALE_PRODUCER; p.planes = planes;
+            *out = p;
+            return true;
+        }
         char kind[16] = {0};
         if (sscanf(name.c_str(), "signed_%15[a-z]_bitplane_i%d_%n", kind, &planes, &n) == 2 && planes >= 2 && planes <= 6) {
             const std::string fam = kind, rest = name.substr(n);
@@ -169,6 +187,7 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             {"deltanet_recurrence_mlx_decode_d128_h32_qk16", PK_DELTANET_DECODE, 128, 32, 16},
             {"deltanet_recurrence_mlx_decode_d128_h48_qk16", PK_DELTANET_DECODE, 128, 48, 16},
             {"rms_norm_gated_d128", PK_RMS_NORM_GATED, 128, 0, 0},
+            {"rms_norm_gated_d128_batched", PK_RMS_NORM_GATED, 128, 0, 1},  // hqk field: 1 = the batched form (grid.y rows of numHeads heads)
             // prompt-chunk forms (Resources/Shaders/prefill_recurrence.metal:290-578, conv1d.metal:129-171): d = channels, hv = taps for the conv
             {"deltanet_recurrence_mlx_prefill_d128_h16", PK_DELTANET_PREFILL, 128, 16, 16},
             {"deltanet_recurrence_mlx_prefill_d128_h32_qk16", PK_DELTANET_PREFILL, 128, 32, 16},
@@ -667,6 +686,47 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             in.launches += 1;
             return check_cuda(ctx, launch_bitplane_producer(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (uint32_t*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)cols, 5, 1), p.name.c_str());
         }
+        case PK_BITPLANE_SIGMOID_MUL_PRODUCER: {
+            // signed_quant.metal:985-992: 0 a, 1 b, 2 planes, 3 activation scales, 4 cols.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(4, cols);
+            if (cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a multiple of 128");
+            NEED_BYTES(0, (size_t)cols * 2); NEED_BYTES(1, (size_t)cols * 2); NEED_BYTES(2, (size_t)(cols / 128) * 6 * 16); NEED_BYTES(3, (size_t)(cols / 128) * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_bitplane_fused_producer(l, SMELT_BITPLANE_FRONT_SIGMOID_MUL, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, nullptr, nullptr,
+                                                                  (uint32_t*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)cols, 6, 0.0f, 32), p.name.c_str());
+        }
+        case PK_BITPLANE_NORM_SCALE_PRODUCER: {
+            // signed_quant.metal:1225-1234: 0 norm scale (one float), 1 input, 2 norm weight, 3 planes, 4 activation scales, 5 cols.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_U32(5, cols);
+            if (cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a multiple of 128");
+            NEED_BYTES(0, 4); NEED_BYTES(1, (size_t)cols * 2); NEED_BYTES(2, (size_t)cols * 2); NEED_BYTES(3, (size_t)(cols / 128) * p.planes * 16); NEED_BYTES(4, (size_t)(cols / 128) * 2);
+            if (reinterpret_cast<uintptr_t>(r.buf[0].ptr) & 3u) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the norm scale must be 4-byte aligned");
+            in.launches += 1;
+            return check_cuda(ctx, launch_bitplane_fused_producer(l, SMELT_BITPLANE_FRONT_NORM_SCALE, (const __half*)r.buf[1].ptr, nullptr, (const __half*)r.buf[2].ptr, (const float*)r.buf[0].ptr,
+                                                                  (uint32_t*)r.buf[3].ptr, (__half*)r.buf[4].ptr, (int)cols, p.planes, 0.0f, 32), p.name.c_str());
+        }
+        case PK_BITPLANE_GATED_NORM_PRODUCER: {
+            // signed_quant.metal:1149-1162: 0 input [H, 128], 1 gate, 2 weight [128], 3 planes, 4 activation scales, 5 headDim, 6 eps;
+            // one threadgroup per head, whose width (32 or 128: the norm's own dispatch) selects the arithmetic.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_U32(5, d); NEED_U32(6, eps_bits);
+            if (d != 128) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": heads of 128");
+            const int heads = (int)rec.grid[0];
+            const int tgs = rec.threadgroup[0] ? (int)rec.threadgroup[0] : 32;
+            if (heads <= 0 || tgs % 32 || tgs > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad grid or threadgroup width");
+            NEED_BYTES(0, (size_t)heads * 256); NEED_BYTES(1, (size_t)heads * 256); NEED_BYTES(2, 256); NEED_BYTES(3, (size_t)heads * 6 * 16); NEED_BYTES(4, (size_t)heads * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_bitplane_fused_producer(l, SMELT_BITPLANE_FRONT_GATED_NORM_D128, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, nullptr,
+                                                                  (uint32_t*)r.buf[3].ptr, (__half*)r.buf[4].ptr, heads * 128, 6, as_f32(eps_bits), tgs), p.name.c_str());
+        }
+        case PK_SIGNED_EMBEDDING_GATHER: {
+            // signed_quant.metal:722-745: 0 codes, 1 scales, 2 token ids, 3 out, 4 hidden; grid.y = tokens.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(4, hidden);
+            const int batch = batch_of(rec);
+            if (hidden == 0 || hidden % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": hidden must be a multiple of 128");
+            NEED_BYTES(2, (size_t)batch * 4); NEED_BYTES(3, (size_t)batch * hidden * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_signed_embedding_gather(l, p.bits, (const uint8_t*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const int32_t*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)hidden, batch), p.name.c_str());
+        }
         case PK_BITPLANE_MATVEC: case PK_BITPLANE_ADD: case PK_BITPLANE_GATEUP: {
             // signed_quant.metal:1564-1572 (matvec: 0 codes, 1 weight scales, 2 planes, 3 activation scales, 4 out, 5 rows,
             // 6 cols), :2246-2255 (add: 5 residual, 6 rows, 7 cols), :1823-1833 (gate/up: 0 gate codes, 1 gate scales,
@@ -783,19 +843,26 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
         }
         case PK_RMS_NORM_GATED: {
             // norms.metal:1093-1099: 0 in [H, D], 1 gate [H, D], 2 weight [D], 3 out, 4 headDim, 5 eps; one threadgroup per
-            // head; rms_norm_gated_d128 fixes headDim 128 and eps 1e-6 (norms_gated_precise.metal:20-52).
+            // head, whose width fixes the order of the sum of squares.  rms_norm_gated_d128 (norms_gated_precise.metal:20-52)
+            // fixes headDim 128 and eps 1e-6 and materialises the norm in fp16; its _batched form binds numHeads at 4 and
+            // takes grid.y rows of heads (:54-87).
             NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3);
             uint32_t d = (uint32_t)p.head_dim;
             float eps = 1e-6f;
+            int heads = (int)rec.grid[0];
             if (!p.fixed_shape) {
                 NEED_U32(4, d_); NEED_U32(5, eps_bits);
                 d = d_; eps = as_f32(eps_bits);
+            } else if (p.n_kv == 1) {
+                NEED_U32(4, num_heads);
+                if (num_heads != rec.grid[0]) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": numHeads must equal grid.x");
+                heads = (int)num_heads * batch_of(rec);
             }
-            const int heads = (int)rec.grid[0];
-            if (heads <= 0 || d == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad shape");
+            const int tgs = !p.fixed_shape && rec.threadgroup[0] ? (int)rec.threadgroup[0] : 32;
+            if (heads <= 0 || d == 0 || tgs % 32 || tgs > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad shape");
             NEED_BYTES(0, (size_t)heads * d * 2); NEED_BYTES(1, (size_t)heads * d * 2); NEED_BYTES(2, (size_t)d * 2); NEED_BYTES(3, (size_t)heads * d * 2);
             in.launches += 1;
-            return check_cuda(ctx, launch_rms_norm_gated(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)d, eps, heads), p.name.c_str());
+            return check_cuda(ctx, launch_rms_norm_gated(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)d, eps, heads, tgs, p.fixed_shape), p.name.c_str());
         }
         case PK_ADD: {
             // activations.metal:56-61: 0 a, 1 b, 2 out, 3 count.

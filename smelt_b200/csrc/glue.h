@@ -32,6 +32,9 @@ struct BitplaneArgs {
     int rows, cols, n_planes, batch;
 };
 cudaError_t launch_bitplane_producer(const Launch& l, const __half* x, const __half* up, uint32_t* planes, __half* scales, int cols, int n_planes, int batch);
+// front 2: a * sigmoid(b) (i6); 3: rms_norm_1pw value from norm_scale[0], a = x, c = norm weight (i2..i6); 4: gated norm of heads of 128, a = x, b = gate, c = weight (i6)
+cudaError_t launch_bitplane_fused_producer(const Launch& l, int front, const __half* a, const __half* b, const __half* c, const float* norm_scale, uint32_t* planes, __half* scales, int cols, int n_planes, float eps, int tgs);
+cudaError_t launch_signed_embedding_gather(const Launch& l, int format, const uint8_t* codes, const __half* scales, const int32_t* token_ids, __half* out, int hidden, int batch);
 cudaError_t launch_bitplane_matvec(const Launch& l, const BitplaneArgs& a);
 // DeltaNet decode step (deltanet.cu)
 cudaError_t launch_conv1d_update_silu(const Launch& l, __half* state, const __half* new_val, const __half* weight, __half* out, int channels, int kernel_size);
@@ -39,7 +42,7 @@ cudaError_t launch_rms_scale_qk(const Launch& l, __half* qkv, int head_dim, floa
 cudaError_t launch_conv1d_update_silu_prefill(const Launch& l, __half* state, __half* qkv, const __half* weight, int seq_len, int channels, int kernel_size, __half* history);
 cudaError_t launch_deltanet_recurrence_prefill(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, int head_dim, int value_heads, int qk_heads, int seq_len, __half* history);
 cudaError_t launch_deltanet_recurrence_decode(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, int head_dim, int value_heads, int qk_heads);
-cudaError_t launch_rms_norm_gated(const Launch& l, const __half* input, const __half* gate, const __half* weight, __half* out, int head_dim, float eps, int heads);
+cudaError_t launch_rms_norm_gated(const Launch& l, const __half* input, const __half* gate, const __half* weight, __half* out, int head_dim, float eps, int heads, int tgs, bool precise_d128);
 cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x, __half* y, int rows, int cols, int batch, int sm_count);
 
 // attention.cu — split-K flash-decode.  scratch holds fp32 partials; see attention_scratch_bytes.

@@ -56,6 +56,10 @@ enum PipeKind : int {
     PK_DELTANET_PREFILL,
     PK_BITPLANE_PRODUCER,
     PK_BITPLANE_SWIGLU_PRODUCER,
+    PK_BITPLANE_SIGMOID_MUL_PRODUCER,
+    PK_BITPLANE_NORM_SCALE_PRODUCER,
+    PK_BITPLANE_GATED_NORM_PRODUCER,
+    PK_SIGNED_EMBEDDING_GATHER,
     PK_BITPLANE_MATVEC,
     PK_BITPLANE_ADD,
     PK_BITPLANE_GATEUP,

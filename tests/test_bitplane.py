@@ -201,3 +201,202 @@ def test_bitplane_records_producer_then_consumer(ctx, oracle):
     pl, sc = oracle.signed_activation_bitplanes(x, cols, planes)
     want = oracle.signed_bitplane_matvec(1, codes, scales, pl, sc, rows, cols, planes)
     assert np.array_equal(got, want.view(np.uint16))
+
+
+# ── producers with another kernel's arithmetic in front; signed embedding gathers ──
+def fused_fixture(cols=5120):
+    """input / weight of testRMSNormActivationViewsAreBitExactWithStagedGraph (SignedQuantKernelTests.swift:2080-2087)."""
+    i = np.arange(cols)
+    x = (np.sin((i * 17 + 3).astype(F)) * (F(0.125) + ((i // 128) % 13).astype(F) * F(0.375))).astype(np.float16)
+    w = (np.cos((i * 7 + 5).astype(F)) * F(0.25)).astype(np.float16)
+    return x, w
+
+
+@pytest.mark.parametrize("planes", [2, 3, 4, 5, 6])
+def test_oracle_norm_scale_view_equals_the_staged_graph(oracle, planes):
+    """The reference asserts fused == rms_norm_1pw then the plain builder, bit for bit
+    (SignedQuantKernelTests.swift:2077-2200): here with the norm's value written in numpy halves."""
+    cols = 5120
+    x, w = fused_fixture(cols)
+    rs = F(1) / np.sqrt(np.mean(x.astype(F) ** 2, dtype=F) + F(1e-6))
+    staged = (x.astype(F) * rs).astype(np.float16) * (F(1) + w.astype(F)).astype(np.float16)  # half * half, rounded once
+    assert staged.dtype == np.float16
+    want_pl, want_sc = oracle.signed_activation_bitplanes(staged, cols, planes)
+    pl, sc = oracle.norm_scale_signed_activation_bitplanes(float(rs), x, w, cols, planes)
+    assert np.array_equal(pl, want_pl) and np.array_equal(sc.view(np.uint16), want_sc.view(np.uint16))
+
+
+def gated_fixture(heads=48):
+    """input / gate / weight of the fused gated-norm test (SignedQuantKernelTests.swift:2302-2313)."""
+    d = 128
+    i = np.arange(heads * d)
+    x = (np.sin((i * 17 + 3).astype(F)) * (F(0.125) + ((i // d) % 12).astype(F) * F(0.625))).astype(np.float16)
+    g = (np.cos((i * 11 + 5).astype(F)) * (F(0.25) + ((i // d) % 9).astype(F) * F(0.5))).astype(np.float16)
+    w = (F(0.5) + ((np.arange(d) * 7) % 31).astype(F) / F(32)).astype(np.float16)
+    return x, g, w
+
+
+@pytest.mark.parametrize("tgs", [32, 128])
+def test_oracle_gated_norm_view_equals_the_staged_graph(oracle, tgs):
+    heads = 48
+    x, g, w = gated_fixture(heads)
+    staged = oracle.rms_norm_gated_d128(x, g, w, heads) if tgs == 32 else oracle.rms_norm_gated_tg(x, g, w, 128, 1e-6, heads, 128)
+    want_pl, want_sc = oracle.signed_activation_bitplanes(staged.reshape(-1), heads * 128, 6)
+    pl, sc = oracle.rms_norm_gated_d128_signed_activation_bitplanes_i6(x, g, w, heads, 1e-6, tgs)
+    assert np.array_equal(pl, want_pl) and np.array_equal(sc.view(np.uint16), want_sc.view(np.uint16))
+    # the precise form is the gated norm up to its extra fp16 boundary
+    plain = oracle.rms_norm_gated(x, g, w, 128, 1e-6, heads)
+    assert np.max(np.abs(staged.astype(F) - plain.astype(F))) <= 2e-3 * max(1.0, float(np.max(np.abs(plain.astype(F)))))
+
+
+def test_oracle_sigmoid_mul_view_equals_the_staged_graph(oracle):
+    cols = 2048
+    rng = np.random.default_rng(8)
+    a, b = rng.standard_normal(cols).astype(np.float16), (rng.standard_normal(cols) * 3).astype(np.float16)
+    one = np.float16(1)
+    tail = one / (one + np.exp(np.abs(b)).astype(np.float16))
+    staged = a * np.where(b < 0, tail, one - tail).astype(np.float16)
+    want_pl, want_sc = oracle.signed_activation_bitplanes(staged, cols, 6)
+    pl, sc = oracle.sigmoid_mul_signed_activation_bitplanes_i6(a, b, cols)
+    agree = sc.view(np.uint16) == want_sc.view(np.uint16)
+    assert agree.mean() > 0.9  # numpy's half exp may round another way than expf + one rounding
+    assert np.array_equal(pl[agree], want_pl[agree]) or np.mean(pl[agree] == want_pl[agree]) > 0.99
+
+
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_oracle_signed_embedding_gather(oracle, fmt):
+    rows, hidden = 40, 384
+    codes, scales = weights(fmt, rows, hidden, 3)
+    ids = np.array([7, 0, 39, 7], np.int32)
+    got = oracle.signed_embedding_gather(fmt, codes, scales, ids, hidden).astype(F)
+    if fmt == 1:
+        sem = np.unpackbits(codes.reshape(rows, -1), axis=1, bitorder="little")[:, :hidden].astype(F) * 2 - 1
+    else:
+        b = codes.reshape(rows, -1)
+        sem = np.stack([(b >> (2 * i)) & 3 for i in range(4)], axis=2).reshape(rows, -1)[:, :hidden].astype(F) - 1
+    want = (sem * scales.reshape(rows, hidden // 128).astype(F)[:, np.arange(hidden) // 128]).astype(np.float16).astype(F)
+    assert np.array_equal(got, want[ids])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("planes", [2, 3, 4, 5, 6])
+def test_norm_scale_producer_is_bit_exact(ctx, oracle, planes):
+    cols = 5120
+    x, w = fused_fixture(cols)
+    rs = np.array([1 / np.sqrt(np.mean(x.astype(F) ** 2, dtype=F) + F(1e-6))], F)
+    dx, dw, drs = ctx.to_device(x), ctx.to_device(w), ctx.to_device(rs)
+    dpl, dsc = ctx.alloc(cols // 128 * planes * 16), ctx.alloc(cols // 128 * 2)
+    ctx.call("fused_activation_bitplanes", 3, dx, None, dw, drs, dpl, dsc, cols, planes, C.c_float(0), 32)
+    pl, sc = oracle.norm_scale_signed_activation_bitplanes(float(rs[0]), x, w, cols, planes)
+    assert np.array_equal(dsc.download(np.uint16, (cols // 128,)), sc.view(np.uint16))
+    assert np.array_equal(dpl.download(np.uint32, pl.shape), pl)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tgs", [32, 128])
+def test_gated_norm_producer_equals_the_staged_kernels(ctx, oracle, tgs):
+    """Fused == gated norm kernel then the plain builder, bit for bit, on the device (the reference's own
+    assertion, SignedQuantKernelTests.swift:2296-2400), and within the expf difference of the oracle."""
+    heads = 48
+    x, g, w = gated_fixture(heads)
+    dx, dg, dw = ctx.to_device(x), ctx.to_device(g), ctx.to_device(w)
+    staged = ctx.alloc(heads * 256)
+    ctx.call("rms_norm_gated_ex", dx, dg, dw, staged, 128, C.c_float(1e-6), heads, tgs, 1 if tgs == 32 else 0)
+    spl, ssc = ctx.alloc(heads * 6 * 16), ctx.alloc(heads * 2)
+    ctx.call("signed_activation_bitplanes", staged, None, spl, ssc, heads * 128, 6, 1)
+    fpl, fsc = ctx.alloc(heads * 6 * 16), ctx.alloc(heads * 2)
+    ctx.call("fused_activation_bitplanes", 4, dx, dg, dw, None, fpl, fsc, heads * 128, 6, C.c_float(1e-6), tgs)
+    assert np.array_equal(fsc.download(np.uint16, (heads,)), ssc.download(np.uint16, (heads,)))
+    assert np.array_equal(fpl.download(np.uint32, (heads, 6, 4)), spl.download(np.uint32, (heads, 6, 4)))
+    want = oracle.rms_norm_gated_d128(x, g, w, heads) if tgs == 32 else oracle.rms_norm_gated_tg(x, g, w, 128, 1e-6, heads, 128)
+    got = staged.download(np.float16, (heads, 128))
+    ulp = np.abs(got.view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
+    assert ulp.max() <= 1 and (ulp == 0).mean() > 0.99
+
+
+@pytest.mark.gpu
+def test_sigmoid_mul_producer(ctx, oracle):
+    cols = 17408
+    a, b = synth.activations(47, "sma", cols), synth.activations(47, "smb", cols)
+    da, db = ctx.to_device(a), ctx.to_device(b)
+    dpl, dsc = ctx.alloc(cols // 128 * 6 * 16), ctx.alloc(cols // 128 * 2)
+    ctx.call("fused_activation_bitplanes", 2, da, db, None, None, dpl, dsc, cols, 6, C.c_float(0), 32)
+    pl, sc = oracle.sigmoid_mul_signed_activation_bitplanes_i6(a, b, cols)
+    got_sc = dsc.download(np.uint16, (cols // 128,))
+    same = got_sc == sc.view(np.uint16)  # expf of the two libraries inside the staged sigmoid
+    assert same.mean() > 0.95
+    got_pl = dpl.download(np.uint32, (cols // 128, 6, 4))
+    flips = sum(bin(int(p) ^ int(q)).count("1") for p, q in zip(got_pl[same].reshape(-1), pl[same].reshape(-1)))
+    assert flips <= cols // 1000, flips
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_signed_embedding_gather(ctx, oracle, fmt):
+    rows, hidden = 300, 5120
+    codes, scales = weights(fmt, rows, hidden, 4)
+    ids = np.array([7, 0, 299, 7, 150], np.int32)
+    dc, ds, di = ctx.to_device(codes), ctx.to_device(scales), ctx.to_device(ids)
+    out = ctx.alloc(len(ids) * hidden * 2)
+    ctx.call("signed_embedding_gather", fmt, dc, ds, di, out, hidden, len(ids))
+    want = oracle.signed_embedding_gather(fmt, codes, scales, ids, hidden)
+    assert np.array_equal(out.download(np.uint16, want.shape), want.view(np.uint16))
+
+
+@pytest.mark.gpu
+def test_fused_producer_and_gather_records(ctx, oracle):
+    """The fused producers and the signed gather as records with the reference's names and bindings."""
+    heads, hidden, rows = 16, 2048, 64
+    x, g, w = gated_fixture(heads)
+    codes, scales = weights(2, rows, hidden, 5)
+    ids = np.array([5], np.int32)
+    nx, nw = fused_fixture(hidden)
+    rs = np.array([0.75], F)
+    tensors = {2: x, 3: g, 4: w, 5: np.zeros(heads * 24, np.uint32), 6: np.zeros(heads, np.float16), 7: codes, 8: scales, 9: ids,
+               10: np.zeros(hidden, np.float16), 11: nx, 12: nw, 13: rs, 14: np.zeros(hidden // 128 * 16, np.uint32), 15: np.zeros(hidden // 128, np.float16)}
+    for slot, t in tensors.items():
+        t = np.ascontiguousarray(t)
+        ctx.call("alloc_slot", slot, C.c_size_t(t.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), t.ctypes.data_as(C.c_void_p), C.c_size_t(t.nbytes)))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    names = ["rms_norm_gated_d128_signed_activation_bitplanes_i6_g128", "signed_ternary_embedding_gather_g128", "norm_scale_signed_activation_bitplanes_i4_g128"]
+    for i, n in enumerate(names):
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 20 + i, n.encode()))
+    f32 = lambda v: int(np.array([v], F).view(np.uint32)[0])
+
+    def rec(pipe, grid, tg, bufs, cons):
+        r = capi.DispatchRecord()
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, pipe, len(bufs), len(cons)
+        r.grid[0], r.grid[1], r.grid[2] = grid[0], grid[1], 1
+        r.threadgroup[0], r.threadgroup[1], r.threadgroup[2] = tg, 1, 1
+        for j, (binding, slot) in enumerate(bufs):
+            r.buf[j].slot, r.buf[j].binding_index, r.buf[j].offset_kind, r.buf[j].offset = slot, binding, 0, 0
+        for j, (binding, kind, value) in enumerate(cons):
+            r.con[j].kind, r.con[j].binding_index, r.con[j].value = kind, binding, value
+        return r
+
+    table = (capi.DispatchRecord * 3)(
+        rec(20, (heads, 1), 128, [(0, 2), (1, 3), (2, 4), (3, 5), (4, 6)], [(5, 0, 128), (6, 1, f32(1e-6))]),
+        rec(21, (hidden, 1), 32, [(0, 7), (1, 8), (2, 9), (3, 10)], [(4, 0, hidden)]),
+        rec(22, (hidden // 128, 1), 32, [(0, 13), (1, 11), (2, 12), (3, 14), (4, 15)], [(5, 0, hidden)]))
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, table, 3, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+
+    def read(slot, dtype, n):
+        out = np.zeros(n, dtype)
+        ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, slot, C.c_size_t(0), out.ctypes.data_as(C.c_void_p), C.c_size_t(out.nbytes)))
+        return out
+
+    pl, sc = oracle.rms_norm_gated_d128_signed_activation_bitplanes_i6(x, g, w, heads, 1e-6, 128)
+    got_sc = read(6, np.uint16, heads)
+    same = got_sc == sc.view(np.uint16)
+    assert same.mean() >= 0.9
+    assert np.mean(read(5, np.uint32, heads * 24).reshape(heads, 6, 4)[same] == pl[same]) > 0.99
+    assert np.array_equal(read(10, np.uint16, hidden), oracle.signed_embedding_gather(2, codes, scales, ids, hidden).view(np.uint16).reshape(-1))
+    npl, nsc = oracle.norm_scale_signed_activation_bitplanes(0.75, nx, nw, hidden, 4)
+    assert np.array_equal(read(15, np.uint16, hidden // 128), nsc.view(np.uint16))
+    assert np.array_equal(read(14, np.uint32, hidden // 128 * 16).reshape(npl.shape), npl)

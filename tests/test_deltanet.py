@@ -77,6 +77,24 @@ def test_oracle_gated_norm_matches_the_references_cpu_reference(oracle):
     assert np.max(np.abs(got - ref)) < 1e-3
 
 
+def test_oracle_precise_gated_norm_matches_the_references_cpu_reference(oracle):
+    """testRmsNormGatedD128Batched_Qwen0808Shape_MatchesCPUReference: 65 rows of 16 heads, bound 0.0021
+    (PrefillKernelTests.swift:1585-1668); and the threadgroup-width form against the plain one."""
+    d, heads = 128, 16 * 65
+    i = np.arange(heads * d, dtype=F)
+    x = (np.sin(i * F(0.0131)) * F(0.2)).astype(np.float16)
+    g = (np.cos(i * F(0.0097)) * F(2.0)).astype(np.float16)
+    w = (F(0.9) + F(0.2) * np.sin(np.arange(d, dtype=F) * F(0.021))).astype(np.float16)
+    xf, gf = x.astype(F).reshape(heads, d), g.astype(F).reshape(heads, d)
+    rs = F(1) / np.sqrt((xf * xf).sum(1, keepdims=True) / F(d) + F(1e-6))
+    ref = (w.astype(F) * (xf * rs) * (gf / (F(1) + np.exp(-gf)))).astype(np.float16).astype(F)  # the test's reference rounds to fp16
+    got = oracle.rms_norm_gated_d128(x, g, w, heads).astype(F)
+    assert np.max(np.abs(got - ref)) < 0.0021
+    for tgs in (32, 128):
+        tg = oracle.rms_norm_gated_tg(x, g, w, d, 1e-6, heads, tgs)
+        assert np.max(ulp_diff_f16(tg, oracle.rms_norm_gated(x, g, w, d, 1e-6, heads))) <= 1
+
+
 def test_oracle_conv1d_shifts_and_activates(oracle):
     c, k = 96, 4
     rng = np.random.default_rng(3)
@@ -185,6 +203,22 @@ def test_rms_norm_gated(ctx, oracle, head_dim, heads):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("tgs,precise", [(32, 1), (32, 0), (128, 0), (64, 0)])
+def test_rms_norm_gated_threadgroup_forms(ctx, oracle, tgs, precise):
+    heads, d = 97, 128
+    rng = np.random.default_rng(tgs + precise)
+    x = (rng.standard_normal((heads, d)) * 0.3).astype(np.float16)
+    g = (rng.standard_normal((heads, d)) * 2).astype(np.float16)
+    w = (0.9 + 0.2 * rng.standard_normal(d)).astype(np.float16)
+    dx, dg, dw = (ctx.to_device(t) for t in (x, g, w))
+    out = ctx.alloc(heads * d * 2)
+    ctx.call("rms_norm_gated_ex", dx, dg, dw, out, d, C.c_float(1e-6), heads, tgs, precise)
+    want = oracle.rms_norm_gated_d128(x, g, w, heads) if precise else oracle.rms_norm_gated_tg(x, g, w, d, 1e-6, heads, tgs)
+    ulp = ulp_diff_f16(out.download(np.float16, (heads, d)), want)
+    assert np.max(ulp) <= 1 and np.mean(ulp == 0) > 0.99  # expf of the two libraries
+
+
+@pytest.mark.gpu
 def test_deltanet_records_run_the_layer_core(ctx, oracle):
     """The four records the reference's emitter writes for a DeltaNet layer's core
     (DeltaNetPlugin.swift:196-318), with its pipeline names and bindings, eagerly."""
@@ -235,7 +269,7 @@ def test_deltanet_records_run_the_layer_core(ctx, oracle):
     st, act = oracle.conv1d_update_silu(conv_state, qkv_in, conv_w, qkv_dim, k)
     scaled = oracle.rms_scale_qk(act, d, 1e-6, qkv_dim, hqk)
     rst, core = oracle.deltanet_recurrence_decode(rec_state, scaled, b, a, a_log, dt, d, hv, hqk)
-    want = oracle.rms_norm_gated(core, z, norm_w, d, 1e-6, hv).reshape(-1)
+    want = oracle.rms_norm_gated_d128(core, z, norm_w, hv).reshape(-1)  # the record names the precise d128 form
     err = float(np.max(np.abs(got.astype(F) - want.astype(F))) / np.sqrt(np.mean(want.astype(F) ** 2)))
     assert err < 5e-3, err
 
