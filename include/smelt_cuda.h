@@ -449,6 +449,26 @@ SMELT_CUDA_API smelt_status smelt_cuda_apply_rope(smelt_cuda_ctx* ctx, void* qk_
 /* rms_norm_1pw (Resources/Shaders/norms.metal:9-67); weight stored as a delta from one. */
 SMELT_CUDA_API smelt_status smelt_cuda_rms_norm_1pw(smelt_cuda_ctx* ctx, const void* x_dev, const void* w_dev, void* y_dev,
                                                     int dim, float eps, int batch);
+/* The element-wise kernels of Resources/Shaders/activations.metal:4-210 and activations_precise.metal:22-35.
+ * a / y [batch, count] fp16; b: [batch, count] (MUL, SIGMOID_MUL), rows of b_stride values (GEGLU: geglu_fused and
+ * geglu_fused_strided_batched), [count] (BIAS_ADD: projection_bias_add_batched), one fp16 value on the device
+ * (SCALAR_MUL_WEIGHT: scalar_mul_weight); scalar: SCALAR_MUL's factor, LOGIT_CAP's cap. */
+enum {
+    SMELT_EW_SILU = 0, SMELT_EW_SIGMOID = 1, SMELT_EW_SOFTPLUS = 2, SMELT_EW_COPY = 3, SMELT_EW_SCALAR_MUL = 4, SMELT_EW_LOGIT_CAP = 5,
+    SMELT_EW_MUL = 6, SMELT_EW_SIGMOID_MUL = 7, SMELT_EW_GEGLU = 8, SMELT_EW_BIAS_ADD = 9, SMELT_EW_SCALAR_MUL_WEIGHT = 10
+};
+SMELT_CUDA_API smelt_status smelt_cuda_elementwise(smelt_cuda_ctx* ctx, int op, const void* a_dev, const void* b_dev, void* y_dev, int count,
+                                                   int batch, int b_stride, float scalar);
+/* gate_split (Resources/Shaders/attention_fused.metal:11-27): [heads, 2 head_dim] rows of query | gate. */
+SMELT_CUDA_API smelt_status smelt_cuda_gate_split(smelt_cuda_ctx* ctx, const void* input_dev, void* query_dev, void* gate_dev, int heads,
+                                                  int head_dim);
+/* The per-head norms of Resources/Shaders/attention_fused.metal:38-330 with their reduction topologies: DIRECT
+ * per_head_rms_norm(_batched) (four adjacent values per thread, y = w * half(x * rs)), ONE_PLUS_W per_head_rms_norm_1pw(_batched)
+ * and NOSCALE per_head_rms_norm_noscale(_batched) (thread t of a threadgroup of threadgroup_width adds x[t]^2,
+ * x[t + width]^2, ...; the batched forms use min(head_dim, 256)).  heads counts every head of every row; may run in place. */
+enum { SMELT_HEAD_NORM_DIRECT = 0, SMELT_HEAD_NORM_ONE_PLUS_W = 1, SMELT_HEAD_NORM_NOSCALE = 2 };
+SMELT_CUDA_API smelt_status smelt_cuda_head_norm(smelt_cuda_ctx* ctx, int mode, const void* x_dev, const void* w_dev, void* y_dev, int heads,
+                                                 int head_dim, float eps, int threadgroup_width);
 /* per_head_rms_norm (Resources/Shaders/attention_fused.metal:93-145); direct weight. */
 SMELT_CUDA_API smelt_status smelt_cuda_per_head_rms_norm(smelt_cuda_ctx* ctx, const void* x_dev, const void* w_dev,
                                                          void* y_dev, int heads, int head_dim, float eps);

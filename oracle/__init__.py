@@ -212,6 +212,34 @@ def rms_norm_1pw(x, w, eps: float, two_stage: bool = True) -> np.ndarray:
     return y
 
 
+HEAD_NORM_DIRECT, HEAD_NORM_1PW, HEAD_NORM_NOSCALE = 0, 1, 2
+EW_SILU, EW_SIGMOID, EW_SOFTPLUS, EW_COPY, EW_SCALAR_MUL, EW_LOGIT_CAP, EW_MUL, EW_SIGMOID_MUL, EW_GEGLU, EW_BIAS_ADD = range(10)
+
+
+def head_norm(mode: int, x, w, heads: int, head_dim: int, eps: float, tgs: int = 32) -> np.ndarray:
+    """The per-head norms of attention_fused.metal with their reduction topologies (w unused for HEAD_NORM_NOSCALE)."""
+    y = np.zeros((heads, head_dim), np.float16)
+    wv = _h(w) if w is not None else np.zeros(head_dim, np.float16)
+    _check(lib().so_head_norm(mode, _p(_h(x)), _p(wv), heads, head_dim, C.c_float(eps), tgs, _p(y)), "head_norm")
+    return y
+
+
+def gate_split(x, heads: int, head_dim: int):
+    q, g = np.zeros((heads, head_dim), np.float16), np.zeros((heads, head_dim), np.float16)
+    lib().so_gate_split(_p(_h(x)), heads, head_dim, _p(q), _p(g))
+    return q, g
+
+
+def elementwise(op: int, a, b=None, scalar: float = 0.0, b_stride: int = 0) -> np.ndarray:
+    """a [batch, count] (or [count]); b per op (see so_elementwise)."""
+    a = _h(a)
+    a2 = a.reshape(1, -1) if a.ndim == 1 else a
+    y = np.zeros_like(a2)
+    _check(lib().so_elementwise(op, _p(a2), _p(_h(b)) if b is not None else None, _p(y), a2.shape[1], a2.shape[0], b_stride or a2.shape[1], C.c_float(scalar)),
+           "elementwise")
+    return y.reshape(a.shape)
+
+
 def per_head_rms_norm(x, w, heads, head_dim, eps) -> np.ndarray:
     x, w = _h(x), _h(w)
     y = np.zeros(x.shape, np.float16)

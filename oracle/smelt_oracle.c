@@ -522,6 +522,119 @@ SO_API int so_per_head_rms_norm(const uint16_t *x, const uint16_t *w, int heads,
     return SO_OK;
 }
 
+/* Metal's simd_sum over 32 lane values: a butterfly over lane distance 16, 8, 4, 2, 1 (the total as lane 0 sees it). */
+static inline float simd_sum32(float *lane) {
+    for (int off = 16; off > 0; off >>= 1)
+        for (int l = 0; l < off; ++l) lane[l] += lane[l + off];
+    return lane[0];
+}
+
+/* The per-head norms of Resources/Shaders/attention_fused.metal:38-330 with their reduction
+ * topologies.  mode 0 per_head_rms_norm(_batched) (:93-145, :247-296): thread t squares its four
+ * adjacent values 4 t .. 4 t + 3, every simdgroup sums its lanes, the simdgroups' sums are
+ * themselves summed with simd_sum; y = w * half(x * rs) as an fp16 product.  mode 1
+ * per_head_rms_norm_1pw(_batched) (:38-91, :188-245): thread t adds x[t]^2, x[t + tgs]^2, ...,
+ * simdgroup sums, then added one after the other; y = half(x * rs * (1 + w)).  mode 2
+ * per_head_rms_norm_noscale(_batched) (:147-186, :298-330): mode 1's reduction, y = half(x * rs).
+ * The batched forms use tgs = min(head_dim, 256). */
+SO_API int so_head_norm(int mode, const uint16_t *x, const uint16_t *w, int heads, int head_dim, float eps, int tgs, uint16_t *y) {
+    if (heads <= 0 || head_dim <= 0 || head_dim > 1024 || mode < 0 || mode > 2 || tgs < 32 || tgs % 32 || tgs > 1024) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < heads; ++h) {
+        const uint16_t *xh = x + (size_t)h * head_dim;
+        float total;
+        if (mode == 0) {
+            float partial[32] = {0};
+            for (int s = 0; s * 128 < head_dim; ++s) {
+                float lane[32];
+                for (int l = 0; l < 32; ++l) {
+                    float p = 0.0f;
+                    for (int i = 0; i < 4; ++i) {
+                        const int e = s * 128 + 4 * l + i;
+                        const float v = e < head_dim ? h2f(xh[e]) : 0.0f;
+                        p += v * v;
+                    }
+                    lane[l] = p;
+                }
+                partial[s] = simd_sum32(lane);
+            }
+            total = simd_sum32(partial);
+        } else {
+            total = 0.0f;
+            for (int s = 0; s < tgs / 32; ++s) {
+                float lane[32];
+                for (int l = 0; l < 32; ++l) {
+                    float p = 0.0f;
+                    for (int i = s * 32 + l; i < head_dim; i += tgs) p += h2f(xh[i]) * h2f(xh[i]);
+                    lane[l] = p;
+                }
+                total += simd_sum32(lane);
+            }
+        }
+        const float rs = 1.0f / sqrtf(total / (float)head_dim + eps);
+        for (int i = 0; i < head_dim; ++i) {
+            const float v = h2f(xh[i]);
+            uint16_t o;
+            if (mode == 0) o = f2h(h2f(w[i]) * round_h(v * rs));
+            else if (mode == 1) o = f2h(v * rs * (1.0f + h2f(w[i])));
+            else o = f2h(v * rs);
+            y[(size_t)h * head_dim + i] = o;
+        }
+    }
+    return SO_OK;
+}
+
+/* gate_split (attention_fused.metal:11-27): [heads, 2 D] rows of query | gate -> query [heads, D], gate [heads, D]. */
+SO_API void so_gate_split(const uint16_t *input, int heads, int head_dim, uint16_t *query, uint16_t *gate) {
+    for (int h = 0; h < heads; ++h)
+        for (int d = 0; d < head_dim; ++d) {
+            query[(size_t)h * head_dim + d] = input[(size_t)h * head_dim * 2 + d];
+            gate[(size_t)h * head_dim + d] = input[(size_t)h * head_dim * 2 + head_dim + d];
+        }
+}
+
+/* The element-wise kernels of Resources/Shaders/activations.metal:4-210 and activations_precise.metal:22-35.
+ * op 0 silu x / (1 + exp(-x)); 1 sigmoid 1 / (1 + exp(-x)); 2 softplus (x > 20 ? x : log(1 + exp(x)));
+ * 3 buffer_copy; 4 scalar_mul half(x * scalar); 5 logit_cap half(cap * tanh(x / cap)); 6 elementwise_mul (fp16
+ * product); 7 sigmoid_mul a * sigmoid(b) in half arithmetic; 8 geglu_fused half(clamp(gelu_tanh(a) * b)), b read
+ * with its own row stride; 9 projection_bias_add_batched a[batch, rows] + b[rows].  a / y [batch, count]. */
+SO_API int so_elementwise(int op, const uint16_t *a, const uint16_t *b, uint16_t *y, int count, int batch, int b_stride, float scalar) {
+    if (count <= 0 || batch <= 0 || op < 0 || op > 9) return SO_ERR_GEOMETRY;
+    for (int r = 0; r < batch; ++r)
+        for (int i = 0; i < count; ++i) {
+            const size_t idx = (size_t)r * count + i;
+            const float x = h2f(a[idx]);
+            uint16_t o;
+            switch (op) {
+                case 0: o = f2h(x / (1.0f + expf(-x))); break;
+                case 1: o = f2h(1.0f / (1.0f + expf(-x))); break;
+                case 2: o = f2h(x > 20.0f ? x : logf(1.0f + expf(x))); break;
+                case 3: o = a[idx]; break;
+                case 4: o = f2h(x * scalar); break;
+                case 5: o = f2h(scalar * tanhf(x / scalar)); break;
+                case 6: o = f2h(x * h2f(b[idx])); break;
+                case 7: {
+                    const float g = h2f(b[idx]);
+                    const float tail = round_h(1.0f / round_h(1.0f + round_h(expf(fabsf(g)))));
+                    const float sig = g < 0.0f ? tail : round_h(1.0f - tail);
+                    o = f2h(x * sig);
+                    break;
+                }
+                case 8: {
+                    const float u = h2f(b[(size_t)r * b_stride + i]);
+                    float inner = 0.7978845608f * (x + 0.044715f * (x * x * x));
+                    inner = inner < -20.0f ? -20.0f : (inner > 20.0f ? 20.0f : inner);
+                    float v = 0.5f * x * (1.0f + tanhf(inner)) * u;
+                    v = v < -65504.0f ? -65504.0f : (v > 65504.0f ? 65504.0f : v);
+                    o = f2h(v);
+                    break;
+                }
+                default: o = f2h(x + h2f(b[i])); break;
+            }
+            y[idx] = o;
+        }
+    return SO_OK;
+}
+
 /* elementwise_add (Resources/Shaders/activations.metal:56-66): fp16 a + b. */
 SO_API void so_elementwise_add(const uint16_t *a, const uint16_t *b, int64_t n, uint16_t *y) {
     for (int64_t i = 0; i < n; ++i) y[i] = f2h(h2f(a[i]) + h2f(b[i]));
@@ -971,11 +1084,6 @@ static inline float softplus_staged_half(uint16_t xh) {
  * partition of the Metal kernel (lane l holds dk = l * D/32 ...) fixes the summation order:
  * per-lane partial sums in dk order, then the 32 lane sums added pairwise as simd_sum does
  * (butterfly over lane distance 16, 8, 4, 2, 1). */
-static inline float simd_sum32(float *lane) {
-    for (int off = 16; off > 0; off >>= 1)
-        for (int l = 0; l < off; ++l) lane[l] += lane[l + off];
-    return lane[0];
-}
 SO_API int so_deltanet_recurrence_decode(uint16_t *state, const uint16_t *qkv, const uint16_t *b_proj, const uint16_t *a_proj,
                                          const uint16_t *a_log, const uint16_t *dt_bias, uint16_t *out, int head_dim,
                                          int value_heads, int qk_heads) {

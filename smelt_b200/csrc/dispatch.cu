@@ -106,8 +106,36 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"signed_binary_gate_up_swiglu_g128_rows8", PK_SIGNED_GATEUP, 1, false},
         {"signed_binary_gate_up_swiglu_g128_rows8_batched_b4", PK_SIGNED_GATEUP, 1, true},
         {"signed_ternary_affine_matvec_g128_rows8", PK_SIGNED_TERNARY_AFFINE, 2, false},
+        // projection banks: the standalone matvec over a larger row space, outputs handed to their consumers
+        // (signed_quant.metal:2634-2960); bits = layout: 0 two weight tensors, 1 one slab and two outputs, 2 one slab and four
+        {"signed_binary_dual_matvec_g128_rows8", PK_SIGNED_BANK, 0, false},
+        {"signed_binary_virtual_bank_matvec_g128_rows8", PK_SIGNED_BANK, 0, false},
+        {"signed_binary_packed_bank_matvec_g128_rows8", PK_SIGNED_BANK, 1, false},
+        {"signed_binary_packed_bank4_matvec_g128_rows8", PK_SIGNED_BANK, 2, false},
         {"signed_binary_embedding_gather_g128", PK_SIGNED_EMBEDDING_GATHER, 1, false},
         {"signed_ternary_embedding_gather_g128", PK_SIGNED_EMBEDDING_GATHER, 2, false},
+        // element-wise kernels (activations.metal:4-210, activations_precise.metal:22-35): bits = the operation
+        {"silu", PK_ELEMENTWISE, kEwSilu, false},
+        {"sigmoid_kernel", PK_ELEMENTWISE, kEwSigmoid, false},
+        {"softplus", PK_ELEMENTWISE, kEwSoftplus, false},
+        {"buffer_copy", PK_ELEMENTWISE, kEwCopy, false},
+        {"scalar_mul", PK_ELEMENTWISE, kEwScalarMul, false},
+        {"scalar_mul_weight", PK_ELEMENTWISE, kEwScalarMul, true},
+        {"logit_cap", PK_ELEMENTWISE, kEwLogitCap, false},
+        {"elementwise_mul", PK_ELEMENTWISE, kEwMul, false},
+        {"sigmoid_mul", PK_ELEMENTWISE, kEwSigmoidMul, false},
+        {"geglu_fused", PK_ELEMENTWISE, kEwGeglu, false},
+        {"geglu_fused_strided_batched", PK_ELEMENTWISE, kEwGeglu, true},
+        {"projection_bias_add_batched", PK_ELEMENTWISE, kEwBiasAdd, true},
+        {"gate_split", PK_GATE_SPLIT, 0, false},
+        // per-head norms (attention_fused.metal:38-330): bits = the form
+        {"per_head_rms_norm_1pw", PK_HEAD_NORM, kHeadNorm1pw, false},
+        {"per_head_rms_norm_noscale", PK_HEAD_NORM, kHeadNormNoScale, false},
+        {"per_head_rms_norm_batched", PK_HEAD_NORM, kHeadNormDirect, true},
+        {"per_head_rms_norm_1pw_batched", PK_HEAD_NORM, kHeadNorm1pw, true},
+        {"per_head_rms_norm_noscale_batched", PK_HEAD_NORM, kHeadNormNoScale, true},
+        {"embedding_gather_batched", PK_EMBEDDING_GATHER_BATCHED, 0, true},
+        {"affine_embedding_gather_batched", PK_AFFINE_EMBEDDING_GATHER_BATCHED, 0, true},
         {"kv_cache_update", PK_KV_UPDATE, 0, false},
         {"apply_rope", PK_APPLY_ROPE, 0, false},
         {"rope_kv_cache_update", PK_ROPE_KV_UPDATE, 0, false},
@@ -168,11 +196,16 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             const std::string fam = kind, rest = name.substr(n);
             const int bits = fam == "binary" ? 1 : (fam == "ternary" ? 2 : 0);
             PipeKind k = PK_NONE;
-            if (rest == "matvec_g128_rows8") k = PK_BITPLANE_MATVEC;
+            bool batched = false;
+            if (rest == "matvec_g128_rows8" || (bits == 2 && rest == "matvec_g128_rows2_wide")) k = PK_BITPLANE_MATVEC;
+            else if (bits == 1 && (rest == "matvec_g128_rows8_batched_b4" || rest == "matvec_g128_rows8_batched_b8" || rest == "matvec_g128_rows8_batched_b16")) {
+                k = PK_BITPLANE_MATVEC; batched = true;  // the prompt-row tiles compute every (row, batch row) as the matvec does (signed_quant.metal:1346-1436)
+            }
+            else if (rest == "bank4_matvec_g128_rows8") k = PK_BITPLANE_BANK4;
             else if (rest == "matvec_add_g128_rows8" && bits == 1) k = PK_BITPLANE_ADD;
             else if (rest == "gate_up_swiglu_g128_rows8") k = PK_BITPLANE_GATEUP;
             if (bits && k != PK_NONE) {
-                p.kind = k; p.bits = bits; p.planes = planes;
+                p.kind = k; p.bits = bits; p.planes = planes; p.batched = batched;
                 *out = p;
                 return true;
             }
@@ -193,6 +226,7 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             {"deltanet_recurrence_mlx_prefill_d128_h32_qk16", PK_DELTANET_PREFILL, 128, 32, 16},
             {"deltanet_recurrence_mlx_prefill_d128_h48_qk16", PK_DELTANET_PREFILL, 128, 48, 16},
             {"conv1d_update_silu_c6144_k4_prefill", PK_CONV1D_SILU_PREFILL, 6144, 4, 0},
+            {"conv1d_update_silu_c6144_k4", PK_CONV1D_SILU, 6144, 4, 0},  // conv1d.metal:34-67: the taps' products are exact in fp32, so its fused multiply-adds equal the generic kernel
         };
         for (const Fixed& f : fixed)
             if (name == f.name) {
@@ -668,6 +702,91 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             in.launches += 1;
             return check_cuda(ctx, launch_per_head_rms_norm(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, heads, (int)d, as_f32(eps_bits)), "per_head_rms_norm");
         }
+        case PK_ELEMENTWISE: {
+            // activations.metal: unary kernels bind 0 in, 1 out, 2 count (scalar_mul: 2 scalar, 3 count; logit_cap: 3 cap);
+            // binary kernels 0 a, 1 b, 2 out, 3 count (scalar_mul_weight: 1 = one fp16 value; geglu_fused_strided_batched:
+            // 4 upStride, grid.y rows; projection_bias_add_batched: 1 bias [rows], 3 rows, grid.y rows).
+            const int op = p.bits;
+            const bool binary = op == kEwMul || op == kEwSigmoidMul || op == kEwGeglu || op == kEwBiasAdd || (op == kEwScalarMul && p.batched);
+            const int iout = binary ? 2 : 1;
+            NEED_BUF(0); NEED_BUF(iout);
+            uint32_t count = 0, scalar_bits = 0, b_stride = 0;
+            int batch = 1;
+            if (binary) {
+                NEED_BUF(1);
+                if (!host_u32(in, r, 3, &count)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the count constant is missing");
+                if ((op == kEwGeglu || op == kEwBiasAdd) && p.batched) batch = batch_of(rec);
+                b_stride = count;
+                if (op == kEwGeglu && p.batched && !host_u32(in, r, 4, &b_stride)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the up stride constant is missing");
+            } else if (op == kEwScalarMul) {
+                if (!host_u32(in, r, 2, &scalar_bits) || !host_u32(in, r, 3, &count)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": scalar / count constants are missing");
+            } else {
+                if (!host_u32(in, r, 2, &count)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the count constant is missing");
+                if (op == kEwLogitCap && !host_u32(in, r, 3, &scalar_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the cap constant is missing");
+            }
+            if (count == 0 || b_stride > 0x7fffffffu) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": count must be positive");
+            const size_t n = (size_t)batch * count * 2;
+            NEED_BYTES(0, n); NEED_BYTES(iout, n);
+            const __half* b = nullptr;
+            const __half* scalar_dev = nullptr;
+            if (binary) {
+                const size_t need = op == kEwBiasAdd ? (size_t)count * 2 : (op == kEwScalarMul ? 2 : (op == kEwGeglu ? ((size_t)(batch - 1) * b_stride + count) * 2 : n));
+                NEED_BYTES(1, need);
+                if (op == kEwScalarMul) scalar_dev = (const __half*)r.buf[1].ptr; else b = (const __half*)r.buf[1].ptr;
+            }
+            in.launches += 1;
+            return check_cuda(ctx, launch_elementwise(l, op, (const __half*)r.buf[0].ptr, b, (__half*)r.buf[iout].ptr, (int)count, batch, (int)b_stride, as_f32(scalar_bits), scalar_dev), p.name.c_str());
+        }
+        case PK_GATE_SPLIT: {
+            // attention_fused.metal:11-18: 0 input [H, 2 D], 1 query, 2 gate, 3 nHeads, 4 headDim.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, heads); NEED_U32(4, d);
+            if (heads == 0 || d == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "gate_split: bad shape");
+            NEED_BYTES(0, (size_t)heads * d * 4); NEED_BYTES(1, (size_t)heads * d * 2); NEED_BYTES(2, (size_t)heads * d * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_gate_split(l, (const __half*)r.buf[0].ptr, (__half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)heads, (int)d), "gate_split");
+        }
+        case PK_HEAD_NORM: {
+            // attention_fused.metal:38-48 (1pw: 0 in, 1 weight, 2 out, 3 headDim, 4 eps), :147-151 (noscale: 0 data, 1 headDim,
+            // 2 eps), :188-196 and :247-255 (batched: 3 nHeads, 4 headDim, 5 eps; grid (nHeads, rows)), :298-303 (noscale
+            // batched: 1 nHeads, 2 headDim, 3 eps).  The threadgroup width of the record fixes the order of the sum of
+            // squares; the batched kernels fix it at min(headDim, 256).
+            const int mode = p.bits;
+            const bool noscale = mode == kHeadNormNoScale;
+            const int iout = noscale ? 0 : 2, ic = noscale ? 1 : 3;
+            NEED_BUF(0); NEED_BUF(iout);
+            if (!noscale) { NEED_BUF(1); }
+            uint32_t d = 0, eps_bits = 0, nheads = rec.grid[0];
+            if (p.batched) {
+                if (!host_u32(in, r, ic, &nheads) || !host_u32(in, r, ic + 1, &d) || !host_u32(in, r, ic + 2, &eps_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": nHeads / headDim / eps constants are missing");
+            } else {
+                if (!host_u32(in, r, ic, &d) || !host_u32(in, r, ic + 1, &eps_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": headDim / eps constants are missing");
+            }
+            const int heads = (int)nheads * (p.batched ? batch_of(rec) : 1);
+            if (heads <= 0 || d == 0 || d > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad shape");
+            int tgs = p.batched ? (int)(d < 256 ? d : 256) : (rec.threadgroup[0] ? (int)rec.threadgroup[0] : 32);
+            tgs = (tgs + 31) / 32 * 32;
+            if (tgs > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad threadgroup width");
+            NEED_BYTES(0, (size_t)heads * d * 2); NEED_BYTES(iout, (size_t)heads * d * 2);
+            if (!noscale) { NEED_BYTES(1, (size_t)d * 2); }
+            in.launches += 1;
+            return check_cuda(ctx, launch_head_norm(l, mode, (const __half*)r.buf[0].ptr, noscale ? nullptr : (const __half*)r.buf[1].ptr, (__half*)r.buf[iout].ptr, heads, (int)d, as_f32(eps_bits), tgs), p.name.c_str());
+        }
+        case PK_EMBEDDING_GATHER_BATCHED: {
+            // lut_matvec.metal:1121-1134: 0 table, 1 token ids [B], 2 out [B, hidden], 3 hidden, 4 batchSize.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, hidden); NEED_U32(4, batch);
+            if (hidden == 0 || batch == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad shape");
+            NEED_BYTES(1, (size_t)batch * 4); NEED_BYTES(2, (size_t)batch * hidden * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_embedding_gather(l, (const __half*)r.buf[0].ptr, (const int32_t*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)hidden, (int)batch, 1), p.name.c_str());
+        }
+        case PK_AFFINE_EMBEDDING_GATHER_BATCHED: {
+            // lut_matvec.metal:1081-1116: 0 W, 1 scales, 2 biases, 3 token ids [B], 4 out [B, cols], 5 cols, 6 batchSize, 7 groupSize.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_U32(5, cols); NEED_U32(6, batch); NEED_U32(7, group);
+            if (cols == 0 || group == 0 || cols % group || cols % 2 || batch == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad cols / group / batch");
+            NEED_BYTES(3, (size_t)batch * 4); NEED_BYTES(4, (size_t)batch * cols * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_affine_embedding_gather(l, (const uint8_t*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const int32_t*)r.buf[3].ptr, (__half*)r.buf[4].ptr, (int)cols, (int)group, (int)batch), p.name.c_str());
+        }
         case PK_BITPLANE_PRODUCER: {
             // signed_quant.metal:757-762: 0 input [B, cols], 1 planes, 2 activation scales, 3 cols; one threadgroup per
             // group, grid.y = rows of the batched form.
@@ -752,10 +871,16 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             if (!host_u32(in, r, irows, &rows) || !host_u32(in, r, irows + 1, &cols)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": rows / cols constants are missing");
             if (rows == 0 || cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a multiple of 128");
             a.rows = (int)rows; a.cols = (int)cols;
+            if (p.batched) {  // the prompt-row tiles bind the number of rows in use after cols (signed_quant.metal:1438-1452)
+                uint32_t nb = 0;
+                if (!host_u32(in, r, irows + 2, &nb) || nb == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the batch constant is missing");
+                a.batch = (int)nb;
+            }
+            const size_t nbat = (size_t)a.batch;
             const size_t wbytes = (size_t)rows * cols / (p.bits == 1 ? 8 : 4), sbytes = (size_t)rows * (cols / 128) * 2;
             const int iplanes = a.mode == 2 ? 4 : 2;
             if (r.buf[0].avail < wbytes || r.buf[1].avail < sbytes || (a.mode == 2 && (r.buf[2].avail < wbytes || r.buf[3].avail < sbytes)) ||
-                r.buf[iplanes].avail < (size_t)(cols / 128) * p.planes * 16 || r.buf[iplanes + 1].avail < (size_t)(cols / 128) * 2 || r.buf[iplanes + 2].avail < (size_t)rows * 2 ||
+                r.buf[iplanes].avail < nbat * (cols / 128) * p.planes * 16 || r.buf[iplanes + 1].avail < nbat * (cols / 128) * 2 || r.buf[iplanes + 2].avail < nbat * rows * 2 ||
                 (a.mode == 1 && r.buf[5].avail < (size_t)rows * 2))
                 return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": a binding is smaller than the shape needs");
             if ((reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.codes2) | reinterpret_cast<uintptr_t>(a.planes)) & 15u)
@@ -763,9 +888,76 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             in.launches += 1;
             return check_cuda(ctx, launch_bitplane_matvec(l, a), p.name.c_str());
         }
+        case PK_BITPLANE_BANK4: {
+            // signed_quant.metal:2475-2497, :2602-2632: 0 codes and 1 weight scales of the members stacked by rows, 2 planes,
+            // 3 activation scales, 4..7 the members' outputs, 8..11 their row counts (trailing members may be empty), 12 cols.
+            // Every row is the standalone matvec's arithmetic, so the members run as that kernel over their row ranges.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(12, cols);
+            if (cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a multiple of 128");
+            const size_t row_bytes = (size_t)cols / (p.bits == 1 ? 8 : 4), groups = cols / 128;
+            NEED_BYTES(2, groups * p.planes * 16); NEED_BYTES(3, groups * 2);
+            if ((reinterpret_cast<uintptr_t>(r.buf[0].ptr) | reinterpret_cast<uintptr_t>(r.buf[2].ptr)) & 15u) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": codes and planes must be 16-byte aligned");
+            size_t first = 0;
+            for (int m = 0; m < 4; ++m) {
+                uint32_t rows = 0;
+                if (!host_u32(in, r, 8 + m, &rows)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a row count is missing");
+                if (rows == 0) continue;
+                if (!r.buf[4 + m].present || r.buf[4 + m].pos_strided || r.buf[4 + m].avail < (size_t)rows * 2) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a member's output binding is missing or too small");
+                if (r.buf[0].avail < (first + rows) * row_bytes || r.buf[1].avail < (first + rows) * groups * 2) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": the stacked weights are smaller than the members need");
+                BitplaneArgs a = {};
+                a.format = p.bits; a.n_planes = p.planes; a.batch = 1; a.mode = 0;
+                a.codes = (const uint8_t*)r.buf[0].ptr + first * row_bytes; a.wscales = (const __half*)r.buf[1].ptr + first * groups;
+                a.planes = (const uint32_t*)r.buf[2].ptr; a.ascales = (const __half*)r.buf[3].ptr; a.out = (__half*)r.buf[4 + m].ptr;
+                a.rows = (int)rows; a.cols = (int)cols;
+                in.launches += 1;
+                const smelt_status st = check_cuda(ctx, launch_bitplane_matvec(l, a), p.name.c_str());
+                if (st) return st;
+                first += rows;
+            }
+            return SMELT_OK;
+        }
+        case PK_SIGNED_BANK: {
+            // signed_quant.metal:2638-2650 (dual, virtual bank: 0 / 1 first codes and scales, 2 / 3 second, 4 input, 5 / 6 outputs,
+            // 7 / 8 row counts, 9 cols), :2802-2813 (packed bank: 0 codes, 1 scales, 2 input, 3 / 4 outputs, 5 / 6 row counts,
+            // 7 cols), :2867-2882 (packed bank of four: 3..6 outputs, 7..10 row counts, 11 cols).  Exact lowerings of the
+            // standalone binary matvec: the members run as that kernel.
+            const int layout = p.bits;
+            const int n_members = layout == 2 ? 4 : 2;
+            const int ix = layout == 0 ? 4 : 2, iout = ix + 1, irows = iout + n_members, icols = irows + n_members;
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(ix);
+            uint32_t cols = 0;
+            if (!host_u32(in, r, icols, &cols) || cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a positive multiple of 128");
+            const size_t row_bytes = (size_t)cols / 8, groups = cols / 128;
+            NEED_BYTES(ix, (size_t)cols * 2);
+            size_t first = 0;
+            for (int m = 0; m < n_members; ++m) {
+                uint32_t rows = 0;
+                if (!host_u32(in, r, irows + m, &rows)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a row count is missing");
+                if (rows == 0) continue;
+                const int ic = layout == 0 ? 2 * m : 0, is = ic + 1;
+                if (!r.buf[ic].present || !r.buf[is].present || r.buf[ic].pos_strided || r.buf[is].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a member's weights are missing");
+                const size_t off = layout == 0 ? 0 : first;
+                if (r.buf[ic].avail < (off + rows) * row_bytes || r.buf[is].avail < (off + rows) * groups * 2) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": the weights are smaller than the members need");
+                if (!r.buf[iout + m].present || r.buf[iout + m].pos_strided || r.buf[iout + m].avail < (size_t)rows * 2) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a member's output binding is missing or too small");
+                SignedArgs a = {};
+                a.codes[0] = (const uint8_t*)r.buf[ic].ptr + off * row_bytes; a.scales[0] = (const __half*)r.buf[is].ptr + off * groups;
+                a.x = (const __half*)r.buf[ix].ptr; a.y = (__half*)r.buf[iout + m].ptr;
+                a.rows = (int)rows; a.cols = (int)cols; a.batch = 1; a.bits = 1;
+                in.launches += 1;
+                const smelt_status st = check_cuda(ctx, launch_signed(l, kSignedPlain, a), p.name.c_str());
+                if (st) return st;
+                first += rows;
+            }
+            return SMELT_OK;
+        }
         case PK_CONV1D_SILU: {
             // conv1d.metal:271-278: 0 state [C, K] (in place), 1 new value [C], 2 weight [C, K], 3 out [C], 4 channels, 5 kernel size.
-            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(4, channels); NEED_U32(5, ksize);
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3);
+            uint32_t channels = (uint32_t)p.head_dim, ksize = (uint32_t)p.n_q;
+            if (!p.fixed_shape) {
+                NEED_U32(4, c_); NEED_U32(5, k_);
+                channels = c_; ksize = k_;
+            }
             if (channels == 0 || ksize == 0 || ksize > 8) return fail(ctx, SMELT_ERR_UNSUPPORTED, "conv1d_update_silu: kernel size in 1..8");
             NEED_BYTES(0, (size_t)channels * ksize * 2); NEED_BYTES(1, (size_t)channels * 2); NEED_BYTES(2, (size_t)channels * ksize * 2); NEED_BYTES(3, (size_t)channels * 2);
             in.launches += 1;

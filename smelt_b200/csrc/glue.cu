@@ -66,30 +66,6 @@ __global__ void __launch_bounds__(256) rms_norm_1pw_vec_kernel(const __half* __r
     }
 }
 
-// per_head_rms_norm (Resources/Shaders/attention_fused.metal:93-145): direct weight,
-// y = w * half(x * rs) as an fp16 product; one CTA per (batch row, head).
-__global__ void per_head_rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
-                                         __half* __restrict__ y, int head_dim, float eps, DevDyn dyn) {
-    __shared__ float scratch[32];
-    pdl_trigger();
-    pdl_wait();
-    if (dyn_skip(dyn)) return;
-    const __half* xr = x + (size_t)blockIdx.x * head_dim;
-    __half* yr = y + (size_t)blockIdx.x * head_dim;
-    float v[8];
-    int n = 0;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < head_dim && n < 8; i += blockDim.x, ++n) {
-        v[n] = __half2float(xr[i]);
-        ss += v[n] * v[n];
-    }
-    const float tot = block_sum(ss, scratch);
-    const float rs = __frcp_rn(__fsqrt_rn(tot / (float)head_dim + eps));
-    n = 0;
-    for (int i = threadIdx.x; i < head_dim && n < 8; i += blockDim.x, ++n)
-        yr[i] = __hmul(w[i], __float2half_rn(v[n] * rs));
-}
-
 // elementwise_add (Resources/Shaders/activations.metal:56-66): fp16 add.
 __global__ void elementwise_add_kernel(const __half* a, const __half* b, __half* y, int64_t n, DevDyn dyn) {
     pdl_trigger();
@@ -130,7 +106,8 @@ __global__ void affine_embedding_gather_kernel(const uint8_t* __restrict__ w, co
     if (dyn_skip(dyn)) return;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= cols / 2) return;
-    const int64_t row = token[0];
+    const int64_t row = token[blockIdx.y];  // grid.y: the rows of affine_embedding_gather_batched (lut_matvec.metal:1081-1116)
+    y += (size_t)blockIdx.y * cols;
     const int groups = cols / group;
     const uint8_t p = w[row * (cols / 2) + i];
     const int c0 = 2 * i, c1 = c0 + 1;
@@ -424,8 +401,7 @@ cudaError_t launch_rms_norm_1pw(const Launch& l, const __half* x, const __half* 
 
 cudaError_t launch_per_head_rms_norm(const Launch& l, const __half* x, const __half* w, __half* y, int heads,
                                      int head_dim, float eps) {
-    if (head_dim > 8 * 128) return cudaErrorInvalidValue;
-    SMELT_LAUNCH(per_head_rms_norm_kernel, dim3(heads), dim3(128), 0, x, w, y, head_dim, eps, dev_dyn(l));
+    return launch_head_norm(l, kHeadNormDirect, x, w, y, heads, head_dim, eps, 32);  // elementwise.cu: the kernel's own reduction topology
 }
 
 cudaError_t launch_elementwise_add(const Launch& l, const __half* a, const __half* b, __half* y, int64_t n) {
@@ -443,8 +419,8 @@ cudaError_t launch_embedding_gather(const Launch& l, const __half* table, const 
 }
 
 cudaError_t launch_affine_embedding_gather(const Launch& l, const uint8_t* w, const __half* s, const __half* b,
-                                           const int32_t* token, __half* y, int cols, int group) {
-    SMELT_LAUNCH(affine_embedding_gather_kernel, dim3((cols / 2 + 255) / 256), dim3(256), 0, w, s, b, token, y, cols,
+                                           const int32_t* token, __half* y, int cols, int group, int batch) {
+    SMELT_LAUNCH(affine_embedding_gather_kernel, dim3((cols / 2 + 255) / 256, batch), dim3(256), 0, w, s, b, token, y, cols,
                  group, dev_dyn(l));
 }
 

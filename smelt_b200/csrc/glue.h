@@ -9,7 +9,7 @@ cudaError_t launch_per_head_rms_norm(const Launch& l, const __half* x, const __h
 cudaError_t launch_elementwise_add(const Launch& l, const __half* a, const __half* b, __half* y, int64_t n);
 cudaError_t launch_swiglu_fused(const Launch& l, const __half* gate, const __half* up, __half* y, int64_t n);
 cudaError_t launch_embedding_gather(const Launch& l, const __half* table, const int32_t* token, __half* y, int hidden, int batch, int token_stride);
-cudaError_t launch_affine_embedding_gather(const Launch& l, const uint8_t* w, const __half* s, const __half* b, const int32_t* token, __half* y, int cols, int group);
+cudaError_t launch_affine_embedding_gather(const Launch& l, const uint8_t* w, const __half* s, const __half* b, const int32_t* token, __half* y, int cols, int group, int batch = 1);
 cudaError_t launch_affine_dequant(const Launch& l, const uint8_t* w, const __half* s, const __half* b, float* out32, __half* out16, int rows, int cols, int group);
 cudaError_t launch_signed_dequant(const Launch& l, const uint8_t* codes, const __half* s, float* out, int rows, int cols, int bits, int group, int* bad);
 cudaError_t launch_apply_rope(const Launch& l, __half* qk, const __half* cos_t, const __half* sin_t, int head_dim, int rope_dim, int heads, int layout, float base_log2, int math_mode, size_t table_stride, int batch);
@@ -34,6 +34,11 @@ struct BitplaneArgs {
 cudaError_t launch_bitplane_producer(const Launch& l, const __half* x, const __half* up, uint32_t* planes, __half* scales, int cols, int n_planes, int batch);
 // front 2: a * sigmoid(b) (i6); 3: rms_norm_1pw value from norm_scale[0], a = x, c = norm weight (i2..i6); 4: gated norm of heads of 128, a = x, b = gate, c = weight (i6)
 cudaError_t launch_bitplane_fused_producer(const Launch& l, int front, const __half* a, const __half* b, const __half* c, const float* norm_scale, uint32_t* planes, __half* scales, int cols, int n_planes, float eps, int tgs);
+enum { kEwSilu = 0, kEwSigmoid, kEwSoftplus, kEwCopy, kEwScalarMul, kEwLogitCap, kEwMul, kEwSigmoidMul, kEwGeglu, kEwBiasAdd };
+enum { kHeadNormDirect = 0, kHeadNorm1pw = 1, kHeadNormNoScale = 2 };
+cudaError_t launch_elementwise(const Launch& l, int op, const __half* a, const __half* b, __half* y, int count, int batch, int b_stride, float scalar, const __half* scalar_dev);
+cudaError_t launch_gate_split(const Launch& l, const __half* in, __half* query, __half* gate, int heads, int head_dim);
+cudaError_t launch_head_norm(const Launch& l, int mode, const __half* x, const __half* w, __half* y, int heads, int head_dim, float eps, int tgs);
 cudaError_t launch_signed_embedding_gather(const Launch& l, int format, const uint8_t* codes, const __half* scales, const int32_t* token_ids, __half* out, int hidden, int batch);
 cudaError_t launch_bitplane_matvec(const Launch& l, const BitplaneArgs& a);
 // DeltaNet decode step (deltanet.cu)

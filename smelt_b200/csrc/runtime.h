@@ -60,6 +60,13 @@ enum PipeKind : int {
     PK_BITPLANE_NORM_SCALE_PRODUCER,
     PK_BITPLANE_GATED_NORM_PRODUCER,
     PK_SIGNED_EMBEDDING_GATHER,
+    PK_SIGNED_BANK,
+    PK_ELEMENTWISE,
+    PK_GATE_SPLIT,
+    PK_HEAD_NORM,
+    PK_EMBEDDING_GATHER_BATCHED,
+    PK_AFFINE_EMBEDDING_GATHER_BATCHED,
+    PK_BITPLANE_BANK4,
     PK_BITPLANE_MATVEC,
     PK_BITPLANE_ADD,
     PK_BITPLANE_GATEUP,

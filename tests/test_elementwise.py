@@ -1,0 +1,182 @@
+"""The small kernels between a layer's projections: element-wise activations and products
+(Resources/Shaders/activations.metal:4-210, activations_precise.metal:22-35), the per-head RMS
+norms with their reduction topologies and the gate split (attention_fused.metal:11-330), the
+batched embedding gathers (lut_matvec.metal:1081-1134).  The oracle against plain float formulas,
+then the CUDA kernels against the oracle, typed and as records under the reference's names."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from smelt_b200 import capi
+from helpers import ulp_diff_f16
+
+F = np.float32
+
+
+def halves(rng, *shape, scale=1.0):
+    return (rng.standard_normal(shape) * scale).astype(np.float16)
+
+
+def test_oracle_elementwise_against_float_formulas(oracle):
+    rng = np.random.default_rng(1)
+    x, b = halves(rng, 3, 500, scale=3), halves(rng, 3, 500)
+    xf, bf = x.astype(F), b.astype(F)
+    cases = [
+        (oracle.EW_SILU, None, 0.0, xf / (1 + np.exp(-xf))),
+        (oracle.EW_SIGMOID, None, 0.0, 1 / (1 + np.exp(-xf))),
+        (oracle.EW_SOFTPLUS, None, 0.0, np.where(xf > 20, xf, np.log1p(np.exp(xf)))),
+        (oracle.EW_SCALAR_MUL, None, 0.37, xf * F(0.37)),
+        (oracle.EW_LOGIT_CAP, None, 30.0, F(30) * np.tanh(xf / F(30))),
+        (oracle.EW_MUL, b, 0.0, xf * bf),
+        (oracle.EW_SIGMOID_MUL, b, 0.0, xf / (1 + np.exp(-bf))),
+        (oracle.EW_GEGLU, b, 0.0, 0.5 * xf * (1 + np.tanh(np.clip(F(0.7978845608) * (xf + F(0.044715) * xf ** 3), -20, 20))) * bf),
+    ]
+    for op, second, scalar, ref in cases:
+        got = oracle.elementwise(op, x, second, scalar)
+        close = (ulp_diff_f16(got, ref.astype(np.float16)) <= 2) | (np.abs(got.astype(F) - ref) < 1e-6)  # 1 + tanh cancels near -1: tiny values
+        assert np.all(close), op  # staged fp16 roundings against the float formula
+    assert np.array_equal(oracle.elementwise(oracle.EW_COPY, x).view(np.uint16), x.view(np.uint16))
+    bias = halves(rng, 500)
+    assert np.array_equal(oracle.elementwise(oracle.EW_BIAS_ADD, x, bias), x + bias[None, :])
+    # the strided form reads row r of `up` at r * stride
+    up = halves(rng, 3, 700)
+    got = oracle.elementwise(oracle.EW_GEGLU, x, up, b_stride=700)
+    assert np.array_equal(got, oracle.elementwise(oracle.EW_GEGLU, x, np.ascontiguousarray(up[:, :500])))
+
+
+@pytest.mark.parametrize("head_dim,tgs", [(128, 32), (256, 64), (256, 256), (512, 128), (96, 32)])
+def test_oracle_head_norms_against_float_formulas(oracle, head_dim, tgs):
+    rng = np.random.default_rng(head_dim)
+    heads = 11
+    x, w = halves(rng, heads, head_dim), halves(rng, head_dim, scale=0.2)
+    xf = x.astype(F)
+    rs = 1 / np.sqrt((xf * xf).mean(1, keepdims=True) + F(1e-6))
+    direct = oracle.head_norm(oracle.HEAD_NORM_DIRECT, x, w, heads, head_dim, 1e-6, tgs)
+    one_pw = oracle.head_norm(oracle.HEAD_NORM_1PW, x, w, heads, head_dim, 1e-6, tgs)
+    plain = oracle.head_norm(oracle.HEAD_NORM_NOSCALE, x, None, heads, head_dim, 1e-6, tgs)
+    assert np.max(ulp_diff_f16(direct, (w.astype(F) * (xf * rs).astype(np.float16).astype(F)).astype(np.float16))) <= 1
+    assert np.max(ulp_diff_f16(one_pw, (xf * rs * (1 + w.astype(F))).astype(np.float16))) <= 1
+    assert np.max(ulp_diff_f16(plain, (xf * rs).astype(np.float16))) <= 1
+    # the sequential restatement the earlier tests use agrees to an ulp
+    assert np.max(ulp_diff_f16(direct, oracle.per_head_rms_norm(x.reshape(-1), w, heads, head_dim, 1e-6).reshape(heads, head_dim))) <= 1
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = capi.Context(0)
+    yield c
+    c.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("op,exact", [(0, False), (1, False), (2, False), (3, True), (4, True), (5, False), (6, True), (7, False), (8, False), (9, True)])
+def test_elementwise_kernels(ctx, oracle, op, exact):
+    rng = np.random.default_rng(op)
+    batch, count = (3, 5000) if op in (8, 9) else (1, 12288)
+    x, b = halves(rng, batch, count, scale=3), halves(rng, batch, count)
+    stride = count
+    if op == 8:
+        b, stride = halves(rng, batch, count + 300), count + 300
+    if op == 9:
+        b = halves(rng, count)
+    scalar = {4: 0.37, 5: 30.0}.get(op, 0.0)
+    dx, db, dy = ctx.to_device(x), ctx.to_device(b), ctx.alloc(x.nbytes)
+    ctx.call("elementwise", op, dx, db if op >= 6 else None, dy, count, batch, stride, C.c_float(scalar))
+    got = dy.download(np.float16, x.shape)
+    want = oracle.elementwise(op, x, b if op >= 6 else None, scalar, stride)
+    if exact:
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    else:
+        ulp = ulp_diff_f16(got, want)  # expf / tanhf / logf of the two libraries
+        tiny = np.abs(got.astype(F) - want.astype(F)) < 1e-6  # 1 + tanh cancels near -1
+        assert np.all((ulp <= 1) | tiny) and np.mean(ulp == 0) > 0.98
+    if op == 4:  # scalar_mul_weight: the factor comes from the device
+        dw = ctx.to_device(np.array([0.37], np.float16))
+        ctx.call("elementwise", 10, dx, dw, dy, count, batch, count, C.c_float(0))
+        assert np.array_equal(dy.download(np.float16, x.shape), oracle.elementwise(4, x, None, float(np.float16(0.37))))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("head_dim,tgs", [(128, 32), (256, 64), (256, 256), (512, 128), (96, 32)])
+def test_head_norm_kernels_are_bit_exact(ctx, oracle, mode, head_dim, tgs):
+    rng = np.random.default_rng(head_dim + mode)
+    heads = 37
+    x, w = halves(rng, heads, head_dim), halves(rng, head_dim, scale=0.2)
+    dx, dw = ctx.to_device(x), ctx.to_device(w)
+    ctx.call("head_norm", mode, dx, None if mode == 2 else dw, dx, heads, head_dim, C.c_float(1e-6), tgs)  # in place
+    want = oracle.head_norm(mode, x, None if mode == 2 else w, heads, head_dim, 1e-6, tgs)
+    assert np.array_equal(dx.download(np.uint16, (heads, head_dim)), want.view(np.uint16))  # IEEE operations only: same bits
+
+
+@pytest.mark.gpu
+def test_gate_split_and_batched_gathers(ctx, oracle):
+    rng = np.random.default_rng(3)
+    heads, d = 12, 256
+    x = halves(rng, heads, 2 * d)
+    dq, dg = ctx.alloc(heads * d * 2), ctx.alloc(heads * d * 2)
+    ctx.call("gate_split", ctx.to_device(x), dq, dg, heads, d)
+    q, g = oracle.gate_split(x, heads, d)
+    assert np.array_equal(dq.download(np.float16, (heads, d)), q) and np.array_equal(dg.download(np.float16, (heads, d)), g)
+
+
+@pytest.mark.gpu
+def test_glue_records(ctx, oracle):
+    """gate_split -> per_head_rms_norm_1pw (threadgroup of 64) -> sigmoid_mul -> geglu_fused_strided_batched,
+    embedding_gather_batched, with the reference's names and bindings."""
+    rng = np.random.default_rng(4)
+    heads, d, vocab, hidden, batch = 8, 256, 50, 512, 3
+    x = halves(rng, heads, 2 * d)
+    w = halves(rng, d, scale=0.2)
+    att = halves(rng, heads * d)
+    gate_rows, up_rows = halves(rng, batch, 400, scale=2), halves(rng, batch, 640)
+    table = halves(rng, vocab, hidden)
+    ids = np.array([7, 0, 49], np.int32)
+    tensors = {2: x, 3: np.zeros(heads * d, np.float16), 4: np.zeros(heads * d, np.float16), 5: w, 6: att, 7: np.zeros(heads * d, np.float16),
+               8: gate_rows, 9: up_rows, 10: np.zeros((batch, 400), np.float16), 11: table, 12: ids, 13: np.zeros((batch, hidden), np.float16)}
+    for slot, t in tensors.items():
+        t = np.ascontiguousarray(t)
+        ctx.call("alloc_slot", slot, C.c_size_t(t.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), t.ctypes.data_as(C.c_void_p), C.c_size_t(t.nbytes)))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    names = ["gate_split", "per_head_rms_norm_1pw", "sigmoid_mul", "geglu_fused_strided_batched", "embedding_gather_batched"]
+    for i, n in enumerate(names):
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 30 + i, n.encode()))
+    f32 = lambda v: int(np.array([v], F).view(np.uint32)[0])
+
+    def rec(pipe, grid, tg, bufs, cons):
+        r = capi.DispatchRecord()
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, pipe, len(bufs), len(cons)
+        r.grid[0], r.grid[1], r.grid[2] = grid[0], grid[1], 1
+        r.threadgroup[0], r.threadgroup[1], r.threadgroup[2] = tg, 1, 1
+        for j, (binding, slot) in enumerate(bufs):
+            r.buf[j].slot, r.buf[j].binding_index, r.buf[j].offset_kind, r.buf[j].offset = slot, binding, 0, 0
+        for j, (binding, kind, value) in enumerate(cons):
+            r.con[j].kind, r.con[j].binding_index, r.con[j].value = kind, binding, value
+        return r
+
+    tbl = (capi.DispatchRecord * 5)(
+        rec(30, (d, heads), 32, [(0, 2), (1, 3), (2, 4)], [(3, 0, heads), (4, 0, d)]),
+        rec(31, (heads, 1), 64, [(0, 3), (1, 5), (2, 3)], [(3, 0, d), (4, 1, f32(1e-6))]),
+        rec(32, (heads * d, 1), 32, [(0, 6), (1, 4), (2, 7)], [(3, 0, heads * d)]),
+        rec(33, (400, batch), 32, [(0, 8), (1, 9), (2, 10)], [(3, 0, 400), (4, 0, 640)]),
+        rec(34, (hidden, batch), 32, [(0, 11), (1, 12), (2, 13)], [(3, 0, hidden), (4, 0, batch)]))
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, tbl, 5, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+
+    def read(slot, shape):
+        out = np.zeros(shape, np.float16)
+        ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, slot, C.c_size_t(0), out.ctypes.data_as(C.c_void_p), C.c_size_t(out.nbytes)))
+        return out
+
+    q, g = oracle.gate_split(x, heads, d)
+    assert np.array_equal(read(3, (heads, d)), oracle.head_norm(oracle.HEAD_NORM_1PW, q, w, heads, d, 1e-6, 64))
+    assert np.max(ulp_diff_f16(read(7, (heads * d,)), oracle.elementwise(oracle.EW_SIGMOID_MUL, att, g.reshape(-1)))) <= 1
+    gg, gw = read(10, (batch, 400)), oracle.elementwise(oracle.EW_GEGLU, gate_rows, up_rows, b_stride=640)
+    assert np.all((ulp_diff_f16(gg, gw) <= 1) | (np.abs(gg.astype(F) - gw.astype(F)) < 1e-6))
+    assert np.array_equal(read(13, (batch, hidden)), table[ids])
