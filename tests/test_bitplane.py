@@ -400,3 +400,65 @@ def test_fused_producer_and_gather_records(ctx, oracle):
     npl, nsc = oracle.norm_scale_signed_activation_bitplanes(0.75, nx, nw, hidden, 4)
     assert np.array_equal(read(15, np.uint16, hidden // 128), nsc.view(np.uint16))
     assert np.array_equal(read(14, np.uint32, hidden // 128 * 16).reshape(npl.shape), npl)
+
+
+@pytest.mark.gpu
+def test_bank_and_prompt_row_records(ctx, oracle):
+    """Projection banks and the prompt-row tiles as records with the reference's names and bindings
+    (signed_quant.metal:2475-2497 bank of four over one view, :1438-1452 batched tiles, :2867-2882 packed
+    bank of four over the fp16 input): every member row must be the standalone kernel's value."""
+    cols, planes, members = 384, 3, (40, 24, 0, 16)
+    total = sum(members)
+    codes, scales = weights(1, total, cols, 80)
+    groups = cols // 128
+    xs = synth.activations(81, "bank", 5, cols)
+    pls, scs = zip(*(oracle.signed_activation_bitplanes(xs[b], cols, planes) for b in range(5)))
+    pl5, sc5 = np.stack(pls), np.stack(scs)
+    pl4 = np.stack([oracle.signed_activation_bitplanes(xs[b], cols, 4)[0] for b in range(5)])
+    sc4 = np.stack([oracle.signed_activation_bitplanes(xs[b], cols, 4)[1] for b in range(5)])
+    tensors = {2: codes, 3: scales, 4: pl5[0], 5: sc5[0], 6: np.zeros(40, np.float16), 7: np.zeros(24, np.float16), 8: np.zeros(8, np.float16),
+               9: np.zeros(16, np.float16), 10: pl4, 11: sc4, 12: np.zeros((5, total), np.float16), 13: xs[0],
+               14: np.zeros(40, np.float16), 15: np.zeros(24, np.float16), 16: np.zeros(16, np.float16)}
+    for slot, t in tensors.items():
+        t = np.ascontiguousarray(t)
+        ctx.call("alloc_slot", slot, C.c_size_t(t.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), t.ctypes.data_as(C.c_void_p), C.c_size_t(t.nbytes)))
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    names = ["signed_binary_bitplane_i3_bank4_matvec_g128_rows8", "signed_binary_bitplane_i4_matvec_g128_rows8_batched_b8", "signed_binary_packed_bank4_matvec_g128_rows8"]
+    for i, n in enumerate(names):
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 40 + i, n.encode()))
+
+    def rec(pipe, grid, bufs, cons):
+        r = capi.DispatchRecord()
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, pipe, len(bufs), len(cons)
+        r.grid[0], r.grid[1], r.grid[2] = grid[0], grid[1], 1
+        for j, (binding, slot) in enumerate(bufs):
+            r.buf[j].slot, r.buf[j].binding_index, r.buf[j].offset_kind, r.buf[j].offset = slot, binding, 0, 0
+        for j, (binding, value) in enumerate(cons):
+            r.con[j].kind, r.con[j].binding_index, r.con[j].value = 0, binding, value
+        return r
+
+    table = (capi.DispatchRecord * 3)(
+        rec(40, ((total + 7) // 8, 1), [(0, 2), (1, 3), (2, 4), (3, 5), (4, 6), (5, 7), (6, 8), (7, 9)], [(8, 40), (9, 24), (10, 0), (11, 16), (12, cols)]),
+        rec(41, ((total + 3) // 4, 1), [(0, 2), (1, 3), (2, 10), (3, 11), (4, 12)], [(5, total), (6, cols), (7, 5)]),
+        rec(42, ((total + 7) // 8, 1), [(0, 2), (1, 3), (2, 13), (3, 14), (4, 15), (5, 8), (6, 16)], [(7, 40), (8, 24), (9, 0), (10, 16), (11, cols)]))
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, table, 3, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+
+    def read(slot, shape):
+        out = np.zeros(shape, np.float16)
+        ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, slot, C.c_size_t(0), out.ctypes.data_as(C.c_void_p), C.c_size_t(out.nbytes)))
+        return out
+
+    whole = oracle.signed_bitplane_matvec(1, codes, scales, pl5[0], sc5[0], total, cols, planes)
+    assert np.array_equal(read(6, 40), whole[:40]) and np.array_equal(read(7, 24), whole[40:64]) and np.array_equal(read(9, 16), whole[64:])
+    got = read(12, (5, total))
+    for b in range(5):
+        assert np.array_equal(got[b], oracle.signed_bitplane_matvec(1, codes, scales, pl4[b], sc4[b], total, cols, 4)), b
+    direct = oracle.signed_matvec(1, codes, scales, xs[0], total, cols).astype(F)
+    packed = np.concatenate([read(14, 40), read(15, 24), read(16, 16)]).astype(F)
+    assert np.max(np.abs(packed - direct)) <= 2e-3 * max(1.0, float(np.max(np.abs(direct))))
