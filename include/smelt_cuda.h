@@ -459,6 +459,22 @@ enum {
 };
 SMELT_CUDA_API smelt_status smelt_cuda_elementwise(smelt_cuda_ctx* ctx, int op, const void* a_dev, const void* b_dev, void* y_dev, int count,
                                                    int batch, int b_stride, float scalar);
+/* The row norms of Resources/Shaders/norms.metal beyond rms_norm_1pw, each with the reduction topology and the
+ * roundings of its kernel; x / y [rows, dim] fp16 (y may be x), scale_out (may be NULL) [rows] fp32.
+ * topology SMELT_ROW_NORM_TILES4: rms_norm_1pw_batched (:1488-1550): four adjacent values per thread and tile of
+ *   4 x threadgroup_width; SMELT_ROW_NORM_QUADS2: the d1024 / d1536 / d2048 / d2560 kernels (:72-176, :262-990): dim / 8
+ *   threads, two quads each; SMELT_ROW_NORM_STRIDED: rms_norm_scale_only(_precise), the d256 kernels, l2_normalize
+ *   (:177-260, :991-1090, :1155-1190, :1436-1486): thread t adds x[t], x[t + width], ...
+ * value 0: the scale only; 1: half(1 + w) * half(x * rs); 2: half(x * (rs * (1 + w))) (the dXXXX kernels);
+ *   3: half(x * rs * (1 + w)) (d256); 4: half(x * rs) (l2_normalize).
+ * scale 0: rsqrt(mean(x^2) + eps); 1: 1 / max(sqrt(sum x^2), eps).
+ * pre_dev (may be NULL): the row is half(x + pre) and, with value 0, is written to y
+ *   (residual_add_rms_norm_scale_only_precise, :1059-1090); residual_dev / scalar_dev (may be NULL): the _add kernels'
+ *   half(norm + residual) and rms_norm_1pw_d256_add_scalar_weight's final product. */
+enum { SMELT_ROW_NORM_TILES4 = 0, SMELT_ROW_NORM_QUADS2 = 1, SMELT_ROW_NORM_STRIDED = 2 };
+SMELT_CUDA_API smelt_status smelt_cuda_row_norm(smelt_cuda_ctx* ctx, const void* x_dev, const void* pre_dev, const void* w_dev,
+                                                const void* residual_dev, const void* scalar_dev, void* y_dev, void* scale_out_dev,
+                                                int rows, int dim, float eps, int topology, int threadgroup_width, int value, int scale);
 /* gate_split (Resources/Shaders/attention_fused.metal:11-27): [heads, 2 head_dim] rows of query | gate. */
 SMELT_CUDA_API smelt_status smelt_cuda_gate_split(smelt_cuda_ctx* ctx, const void* input_dev, void* query_dev, void* gate_dev, int heads,
                                                   int head_dim);

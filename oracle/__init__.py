@@ -224,6 +224,19 @@ def head_norm(mode: int, x, w, heads: int, head_dim: int, eps: float, tgs: int =
     return y
 
 
+def row_norm(x, w=None, *, topology: int, value: int, tgs: int = 256, eps: float = 1e-6, scale: int = 0, pre=None, residual=None, scalar=None):
+    """The row norms of norms.metal with their reduction topologies (see so_row_norm).  Returns (y or None, scales [rows])."""
+    x = _h(x)
+    x2 = x.reshape(1, -1) if x.ndim == 1 else x
+    rows, dim = x2.shape
+    y = np.zeros_like(x2) if (value or pre is not None) else None
+    sc = np.zeros(rows, np.float32)
+    opt = lambda a: _p(_h(a)) if a is not None else None
+    _check(lib().so_row_norm(_p(x2), opt(pre), opt(w), opt(residual), opt(scalar), _p(y) if y is not None else None, _p(sc), rows, dim, C.c_float(eps),
+                             topology, tgs, value, scale), "row_norm")
+    return (y.reshape(x.shape) if y is not None else None), sc
+
+
 def gate_split(x, heads: int, head_dim: int):
     q, g = np.zeros((heads, head_dim), np.float16), np.zeros((heads, head_dim), np.float16)
     lib().so_gate_split(_p(_h(x)), heads, head_dim, _p(q), _p(g))

@@ -583,6 +583,100 @@ SO_API int so_head_norm(int mode, const uint16_t *x, const uint16_t *w, int head
     return SO_OK;
 }
 
+/* The row norms of Resources/Shaders/norms.metal beyond rms_norm_1pw, with their reduction
+ * topologies and roundings.  One row of `dim` values per threadgroup.
+ * topology 0 (rms_norm_1pw_batched, :1488-1550): thread t of tgs adds the squares of its four
+ *   adjacent values in every tile of 4 tgs values; simdgroup sums; the sums summed by simd_sum.
+ * topology 1 (the d1024 / d1536 / d2048 / d2560 kernels, :72-176, :262-575, :579-652, :727-990):
+ *   dim / 8 threads, thread t takes values 4 t .. 4 t + 3 and 4 (t + dim / 8) ..: dot(x0, x0) +
+ *   dot(x1, x1); simdgroup sums added one after the other.
+ * topology 2 (rms_norm_scale_only(_precise), the d256 kernels, l2_normalize, :177-260, :991-1090,
+ *   :1155-1190, :1436-1486): thread t adds x[t]^2, x[t + tgs]^2, ...; simdgroup sums added one
+ *   after the other.
+ * scale 0: rsqrt(total / dim + eps); 1 (l2_normalize): 1 / max(sqrt(total), eps).
+ * value 0: none (the scale alone, to scale_out[row]); 1: half(1 + w) * half(x * rs) as an fp16
+ *   product; 2: half(x * (rs * (1 + w))); 3: half(x * rs * (1 + w)); 4: half(x * rs).
+ * pre (may be NULL): the row is half(x + pre), which is also written to y
+ *   (residual_add_rms_norm_scale_only_precise, :1059-1090).  residual (may be NULL): y =
+ *   half(y + residual) after the norm is rounded; scalar (may be NULL): y = half(float(y) *
+ *   float(scalar[0])) after that (rms_norm_1pw_d256_add_scalar_weight). */
+SO_API int so_row_norm(const uint16_t *x, const uint16_t *pre, const uint16_t *w, const uint16_t *residual, const uint16_t *scalar,
+                       uint16_t *y, float *scale_out, int rows, int dim, float eps, int topology, int tgs, int value, int scale) {
+    if (rows <= 0 || dim <= 0 || dim > 16384 || topology < 0 || topology > 2 || value < 0 || value > 4 || scale < 0 || scale > 1) return SO_ERR_GEOMETRY;
+    if (topology == 1) { if (dim % 256) return SO_ERR_GEOMETRY; tgs = dim / 8; }
+    if (tgs < 32 || tgs % 32 || tgs > 1024) return SO_ERR_GEOMETRY;
+    float *v = (float *)malloc((size_t)dim * sizeof(float));
+    if (!v) return SO_ERR_GEOMETRY;
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t *xr = x + (size_t)r * dim;
+        for (int i = 0; i < dim; ++i) {
+            if (pre) {
+                const uint16_t sum = f2h(h2f(xr[i]) + h2f(pre[(size_t)r * dim + i]));
+                v[i] = h2f(sum);
+                if (value == 0 && y) y[(size_t)r * dim + i] = sum;
+            } else {
+                v[i] = h2f(xr[i]);
+            }
+        }
+        float total;
+        if (topology == 0) {
+            float partial[32] = {0};
+            for (int s = 0; s < tgs / 32; ++s) {
+                float lane[32];
+                for (int l = 0; l < 32; ++l) {
+                    const int t = 32 * s + l;
+                    float p = 0.0f;
+                    for (int tile = 0; tile < dim; tile += 4 * tgs)
+                        for (int k = 0; k < 4; ++k) {
+                            const int i = tile + 4 * t + k;
+                            if (i < dim) p += v[i] * v[i];
+                        }
+                    lane[l] = p;
+                }
+                partial[s] = simd_sum32(lane);
+            }
+            total = simd_sum32(partial);
+        } else {
+            total = 0.0f;
+            for (int s = 0; s < tgs / 32; ++s) {
+                float lane[32];
+                for (int l = 0; l < 32; ++l) {
+                    const int t = 32 * s + l;
+                    float p;
+                    if (topology == 1) {
+                        const float *a = v + 4 * t, *b = v + 4 * (t + tgs);
+                        const float d0 = ((a[0] * a[0] + a[1] * a[1]) + a[2] * a[2]) + a[3] * a[3];
+                        const float d1 = ((b[0] * b[0] + b[1] * b[1]) + b[2] * b[2]) + b[3] * b[3];
+                        p = d0 + d1;
+                    } else {
+                        p = 0.0f;
+                        for (int i = t; i < dim; i += tgs) p += v[i] * v[i];
+                    }
+                    lane[l] = p;
+                }
+                total += simd_sum32(lane);
+            }
+        }
+        const float sqrt_total = sqrtf(total);
+        const float rs = scale == 0 ? 1.0f / sqrtf(total / (float)dim + eps) : 1.0f / (sqrt_total > eps ? sqrt_total : eps);
+        if (scale_out) scale_out[r] = rs;
+        if (value == 0) continue;
+        for (int i = 0; i < dim; ++i) {
+            float o;
+            const float wv = w ? h2f(w[i]) : 0.0f;
+            if (value == 1) o = round_h(round_h(1.0f + wv) * round_h(v[i] * rs));
+            else if (value == 2) o = round_h(v[i] * (rs * (1.0f + wv)));
+            else if (value == 3) o = round_h(v[i] * rs * (1.0f + wv));
+            else o = round_h(v[i] * rs);
+            if (residual) o = round_h(o + h2f(residual[(size_t)r * dim + i]));
+            if (scalar) o = round_h(o * h2f(scalar[0]));
+            y[(size_t)r * dim + i] = f2h(o);
+        }
+    }
+    free(v);
+    return SO_OK;
+}
+
 /* gate_split (attention_fused.metal:11-27): [heads, 2 D] rows of query | gate -> query [heads, D], gate [heads, D]. */
 SO_API void so_gate_split(const uint16_t *input, int heads, int head_dim, uint16_t *query, uint16_t *gate) {
     for (int h = 0; h < heads; ++h)

@@ -43,6 +43,44 @@ bool parse_shape(std::string& rest, Pipeline* p) {
     return false;
 }
 
+// The row norms of norms.metal beyond rms_norm_1pw.  form = the binding layout:
+//   0: 0 in, 1 weight, 2 out, 3 dim, 4 eps (rows = grid.x)          1: 0 in, 1 weight, 2 out
+//   2: 0 in, 1 weight, 2 residual, 3 out                            3: 0 in, 1 weight, 2 residual, 3 scalar, 4 out
+//   4: 0 in, 1 scale out, 2 dim, 3 eps                              5: 0 in, 1 scale out
+//   6: 0 a, 1 b, 2 out (a + b), 3 scale out, 4 dim, 5 eps           7: 0 data (in place), 1 headDim, 2 eps (rows = grid.x)
+//   8: 0 data (in place)
+struct RowNormName { const char* name; int dim, topology, value, scale, form; float eps; bool batched; };
+constexpr int kT4 = SMELT_ROW_NORM_TILES4, kQ2 = SMELT_ROW_NORM_QUADS2, kST = SMELT_ROW_NORM_STRIDED;
+const RowNormName kRowNorms[] = {
+    {"rms_norm_1pw_batched", 0, kT4, 1, 0, 0, 0.0f, true},
+    {"rms_norm_1pw_d2048", 2048, kQ2, 2, 0, 1, 1e-6f, false},
+    {"rms_norm_1pw_d1024", 1024, kQ2, 2, 0, 1, 1e-6f, false},
+    {"rms_norm_1pw_d1024_batched", 1024, kQ2, 2, 0, 1, 1e-6f, true},
+    {"rms_norm_1pw_d1536", 1536, kQ2, 2, 0, 1, 1e-6f, false},
+    {"rms_norm_1pw_d1536_add", 1536, kQ2, 2, 0, 2, 1e-6f, false},
+    {"rms_norm_1pw_d1536_batched", 1536, kQ2, 2, 0, 1, 1e-6f, true},
+    {"rms_norm_1pw_d1536_add_batched", 1536, kQ2, 2, 0, 2, 1e-6f, true},
+    {"rms_norm_1pw_d2560", 2560, kQ2, 2, 0, 1, 1e-6f, false},
+    {"rms_norm_1pw_d2560_add", 2560, kQ2, 2, 0, 2, 1e-6f, false},
+    {"rms_norm_1pw_d2560_batched", 2560, kQ2, 2, 0, 1, 1e-6f, true},
+    {"rms_norm_1pw_d2560_add_batched", 2560, kQ2, 2, 0, 2, 1e-6f, true},
+    {"rms_norm_1pw_d256_add", 256, kST, 3, 0, 2, 1e-6f, false},
+    {"rms_norm_1pw_d256_add_scalar_weight", 256, kST, 3, 0, 3, 1e-6f, false},
+    {"rms_norm_scale_only", 0, kST, 0, 0, 4, 0.0f, false},
+    {"rms_norm_scale_only_precise", 0, kST, 0, 0, 4, 0.0f, false},
+    {"rms_norm_scale_only_d1536", 1536, kQ2, 0, 0, 5, 1e-6f, false},
+    {"rms_norm_scale_only_d2560", 2560, kQ2, 0, 0, 5, 1e-6f, false},
+    {"rms_norm_scale_only_d1024_batched", 1024, kQ2, 0, 0, 5, 1e-6f, true},
+    {"rms_norm_scale_only_d2048_batched", 2048, kST, 0, 0, 5, 1e-6f, true},
+    {"rms_norm_scale_only_d2048_eps1e5_batched", 2048, kST, 0, 0, 5, 1e-5f, true},
+    {"rms_norm_scale_only_d2560_batched", 2560, kST, 0, 0, 5, 1e-6f, true},
+    {"rms_norm_scale_only_d3072_eps1e5_batched", 3072, kST, 0, 0, 5, 1e-5f, true},
+    {"residual_add_rms_norm_scale_only_precise", 0, kST, 0, 0, 6, 0.0f, false},
+    {"l2_normalize", 0, kST, 4, 1, 7, 0.0f, true},
+    {"l2_normalize_d128", 128, kST, 4, 1, 8, 1e-6f, true},
+};
+constexpr int kRowNormCount = (int)(sizeof(kRowNorms) / sizeof(kRowNorms[0]));
+
 bool parse_affine(const std::string& name, const char* base, PipeKind kind, Pipeline* p) {
     if (!starts_with(name, base)) return false;
     std::string rest = name.substr(strlen(base));
@@ -211,6 +249,13 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             }
         }
     }
+    // The row norms of norms.metal beyond rms_norm_1pw: each name fixes a reduction topology, a value formula and its bindings.
+    for (int i = 0; i < kRowNormCount; ++i)
+        if (name == kRowNorms[i].name) {
+            p.kind = PK_ROW_NORM; p.planes = i;
+            *out = p;
+            return true;
+        }
     // Shape-specialised DeltaNet names carry their constants in the name
     // (Resources/Shaders/recurrence.metal:590-836, norms_gated_precise.metal:20-52).
     {
@@ -770,6 +815,44 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             if (!noscale) { NEED_BYTES(1, (size_t)d * 2); }
             in.launches += 1;
             return check_cuda(ctx, launch_head_norm(l, mode, (const __half*)r.buf[0].ptr, noscale ? nullptr : (const __half*)r.buf[1].ptr, (__half*)r.buf[iout].ptr, heads, (int)d, as_f32(eps_bits), tgs), p.name.c_str());
+        }
+        case PK_ROW_NORM: {
+            const RowNormName& n = kRowNorms[p.planes];
+            uint32_t dim = (uint32_t)n.dim, eps_bits = 0;
+            float eps = n.eps;
+            int ix = 0, ipre = -1, iw = -1, ires = -1, iscalar = -1, iy = -1, iscale = -1;
+            switch (n.form) {
+                case 0: iw = 1; iy = 2; if (!host_u32(in, r, 3, &dim) || !host_u32(in, r, 4, &eps_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": dim / eps constants are missing"); eps = as_f32(eps_bits); break;
+                case 1: iw = 1; iy = 2; break;
+                case 2: iw = 1; ires = 2; iy = 3; break;
+                case 3: iw = 1; ires = 2; iscalar = 3; iy = 4; break;
+                case 4: iscale = 1; if (!host_u32(in, r, 2, &dim) || !host_u32(in, r, 3, &eps_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": dim / eps constants are missing"); eps = as_f32(eps_bits); break;
+                case 5: iscale = 1; break;
+                case 6: ipre = 1; iy = 2; iscale = 3; if (!host_u32(in, r, 4, &dim) || !host_u32(in, r, 5, &eps_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": dim / eps constants are missing"); eps = as_f32(eps_bits); break;
+                case 7: iy = 0; if (!host_u32(in, r, 1, &dim) || !host_u32(in, r, 2, &eps_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": headDim / eps constants are missing"); eps = as_f32(eps_bits); break;
+                default: iy = 0; break;
+            }
+            const int rows = n.batched ? (int)rec.grid[0] : 1;
+            int tgs = n.form == 8 ? 128 : (n.dim == 256 ? 256 : (rec.threadgroup[0] ? (int)rec.threadgroup[0] : 256));
+            if (n.topology == kQ2) tgs = (int)dim / 8;
+            if (rows <= 0 || dim == 0 || dim > 16384 || tgs < 32 || tgs % 32 || tgs > 1024 || (n.topology == kQ2 && dim % 256)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows, dim or threadgroup width");
+            const size_t row_bytes = (size_t)rows * dim * 2;
+            const int bufs[] = {ix, ipre, ires, iy};
+            for (int b : bufs)
+                if (b >= 0) {
+                    if (!r.buf[b].present || r.buf[b].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a buffer binding is missing");
+                    if (r.buf[b].avail < row_bytes) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, p.name + ": a binding is smaller than the rows need");
+                }
+            if (iw >= 0) { NEED_BUF(iw); NEED_BYTES(iw, (size_t)dim * 2); }
+            if (iscalar >= 0) { NEED_BUF(iscalar); NEED_BYTES(iscalar, 2); }
+            if (iscale >= 0) {
+                NEED_BUF(iscale); NEED_BYTES(iscale, (size_t)rows * 4);
+                if (reinterpret_cast<uintptr_t>(r.buf[iscale].ptr) & 3u) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the scale output must be 4-byte aligned");
+            }
+            auto hp = [&](int i) { return i >= 0 ? (const __half*)r.buf[i].ptr : (const __half*)nullptr; };
+            in.launches += 1;
+            return check_cuda(ctx, launch_row_norm(l, hp(ix), hp(ipre), hp(iw), hp(ires), hp(iscalar), iy >= 0 ? (__half*)r.buf[iy].ptr : nullptr,
+                                                   iscale >= 0 ? (float*)r.buf[iscale].ptr : nullptr, rows, (int)dim, eps, n.topology, tgs, n.value, n.scale), p.name.c_str());
         }
         case PK_EMBEDDING_GATHER_BATCHED: {
             // lut_matvec.metal:1121-1134: 0 table, 1 token ids [B], 2 out [B, hidden], 3 hidden, 4 batchSize.

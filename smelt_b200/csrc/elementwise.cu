@@ -7,6 +7,8 @@
 //                                                     scalar_mul_weight, geglu_fused(_strided_batched), logit_cap
 //   Resources/Shaders/activations_precise.metal:22-35 sigmoid_mul (half arithmetic)
 //   Resources/Shaders/attention_fused.metal:11-330    gate_split, per_head_rms_norm[_1pw | _noscale][_batched]
+//   Resources/Shaders/norms.metal:72-1090, :1155-1550 the shape-specialised and batched rms_norm_1pw forms, the
+//                                                     scale-only norms, l2_normalize
 #include <string>
 
 #include "common.cuh"
@@ -122,6 +124,82 @@ __global__ void __launch_bounds__(32) head_norm_kernel(const __half* x, const __
     }
 }
 
+// The row norms of norms.metal beyond rms_norm_1pw (norms.metal:72-1090, :1155-1190, :1436-1550): one warp per
+// row plays the threadgroup, simdgroup after simdgroup, so that the sum of squares is added in the kernel's own
+// order.  topology 0: thread t of tgs adds its four adjacent values of every tile of 4 tgs; the simdgroups' sums
+// are summed by simd_sum.  1: dim / 8 threads, thread t takes dot(x0, x0) + dot(x1, x1) of the quads t and
+// t + dim / 8; simdgroup sums added in order.  2: thread t adds x[t]^2, x[t + tgs]^2, ...; sums added in order.
+// scale 0: rsqrt(total / dim + eps); 1: 1 / max(sqrt(total), eps).  value 0: the scale only; 1: half(1 + w) *
+// half(x * rs); 2: half(x * (rs * (1 + w))); 3: half(x * rs * (1 + w)); 4: half(x * rs).  pre: the row is
+// half(x + pre), also written to y when value is 0.  residual / scalar: applied to the rounded norm.
+struct RowNormArgs {
+    const __half* x; const __half* pre; const __half* w; const __half* residual; const __half* scalar;
+    __half* y; float* scale_out;
+    int dim, tgs, topology, value, scale;
+    float eps;
+};
+
+__global__ void __launch_bounds__(32) row_norm_kernel(const RowNormArgs a, DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const int lane = threadIdx.x;
+    const size_t off = (size_t)blockIdx.x * a.dim;
+    const __half* x = a.x + off;
+    auto val = [&](int i) -> float {
+        if (a.pre) return __half2float(__hadd(x[i], a.pre[off + i]));
+        return __half2float(x[i]);
+    };
+    float total = 0.0f, mine = 0.0f;
+    for (int s = 0; s < a.tgs / 32; ++s) {
+        const int t = 32 * s + lane;
+        float p = 0.0f;
+        if (a.topology == 0) {
+            for (int tile = 0; tile < a.dim; tile += 4 * a.tgs)
+                for (int k = 0; k < 4; ++k) {
+                    const int i = tile + 4 * t + k;
+                    if (i < a.dim) { const float v = val(i); p = __fadd_rn(p, __fmul_rn(v, v)); }
+                }
+        } else if (a.topology == 1) {
+            float d[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int b = 4 * (t + h * a.tgs);
+                const float v0 = val(b), v1 = val(b + 1), v2 = val(b + 2), v3 = val(b + 3);
+                d[h] = __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(v0, v0), __fmul_rn(v1, v1)), __fmul_rn(v2, v2)), __fmul_rn(v3, v3));
+            }
+            p = __fadd_rn(d[0], d[1]);
+        } else {
+            for (int i = t; i < a.dim; i += a.tgs) { const float v = val(i); p = __fadd_rn(p, __fmul_rn(v, v)); }
+        }
+        const float part = __shfl_sync(0xffffffffu, simd_sum_lane0(p), 0);
+        if (a.topology == 0) { if (lane == s) mine = part; }
+        else total = __fadd_rn(total, part);
+    }
+    if (a.topology == 0) total = __shfl_sync(0xffffffffu, simd_sum_lane0(mine), 0);
+    const float rs = a.scale == 0 ? __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)a.dim), a.eps))) : __frcp_rn(fmaxf(__fsqrt_rn(total), a.eps));
+    if (lane == 0 && a.scale_out) a.scale_out[blockIdx.x] = rs;
+    if (a.value == 0) {
+        if (a.pre && a.y)
+            for (int i = lane; i < a.dim; i += 32) a.y[off + i] = __hadd(x[i], a.pre[off + i]);
+        return;
+    }
+    // in place is allowed: position i is read and written by the same lane, after the whole row was summed
+    __syncwarp();
+    for (int i = lane; i < a.dim; i += 32) {
+        const float v = val(i);
+        const float wv = a.w ? __half2float(a.w[i]) : 0.0f;
+        __half o;
+        if (a.value == 1) o = __hmul(__float2half_rn(__fadd_rn(1.0f, wv)), __float2half_rn(__fmul_rn(v, rs)));
+        else if (a.value == 2) o = __float2half_rn(__fmul_rn(v, __fmul_rn(rs, __fadd_rn(1.0f, wv))));
+        else if (a.value == 3) o = __float2half_rn(__fmul_rn(__fmul_rn(v, rs), __fadd_rn(1.0f, wv)));
+        else o = __float2half_rn(__fmul_rn(v, rs));
+        if (a.residual) o = __hadd(o, a.residual[off + i]);
+        if (a.scalar) o = __float2half_rn(__fmul_rn(__half2float(o), __half2float(a.scalar[0])));
+        a.y[off + i] = o;
+    }
+}
+
 cudaError_t cfg_launch(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block) {
     cfg = {};
     cfg.gridDim = grid;
@@ -187,6 +265,23 @@ cudaError_t launch_head_norm(const Launch& l, int mode, const __half* x, const _
     }
 }
 
+cudaError_t launch_row_norm(const Launch& l, const __half* x, const __half* pre, const __half* w, const __half* residual, const __half* scalar, __half* y,
+                            float* scale_out, int rows, int dim, float eps, int topology, int tgs, int value, int scale) {
+    if (rows <= 0 || dim <= 0 || !x || topology < 0 || topology > 2 || value < 0 || value > 4 || scale < 0 || scale > 1) return cudaErrorInvalidValue;
+    if (topology == 1) {
+        if (dim % 256) return cudaErrorInvalidValue;
+        tgs = dim / 8;
+    }
+    if (tgs < 32 || tgs % 32 || tgs > 1024 || (value && !y) || (!value && !scale_out && !pre)) return cudaErrorInvalidValue;
+    if ((value == 1 || value == 2 || value == 3) && !w) return cudaErrorInvalidValue;
+    RowNormArgs a = {x, pre, w, residual, scalar, y, scale_out, dim, tgs, topology, value, scale, eps};
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cfg_launch(l, cfg, attr, dim3(rows), dim3(32));
+    prefer_max_shared(row_norm_kernel);
+    return cudaLaunchKernelEx(&cfg, row_norm_kernel, a, dev_dyn(l));
+}
+
 }  // namespace smelt
 
 using namespace smelt;
@@ -228,6 +323,20 @@ smelt_status smelt_cuda_head_norm(smelt_cuda_ctx* ctx, int mode, const void* x, 
     if (head_dim > 1024) return fail(ctx, SMELT_ERR_UNSUPPORTED, "head norm: heads of up to 1024 values");
     if (threadgroup_width < 32 || threadgroup_width % 32 || threadgroup_width > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "head norm: threadgroup width a multiple of 32 up to 1024");
     return check_cuda(ctx, launch_head_norm(typed(ctx), mode, (const __half*)x, (const __half*)w, (__half*)y, heads, head_dim, eps, threadgroup_width), "head norm");
+}
+
+smelt_status smelt_cuda_row_norm(smelt_cuda_ctx* ctx, const void* x, const void* pre, const void* w, const void* residual, const void* scalar, void* y,
+                                 void* scale_out, int rows, int dim, float eps, int topology, int threadgroup_width, int value, int scale) {
+    if (!ctx) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!x || rows <= 0 || dim <= 0 || topology < 0 || topology > 2 || value < 0 || value > 4 || scale < 0 || scale > 1 || (value && !y) ||
+        ((value == 1 || value == 2 || value == 3) && !w) || (!value && !scale_out && !pre))
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "row norm: bad arguments");
+    if (topology == 1 && dim % 256) return fail(ctx, SMELT_ERR_UNSUPPORTED, "row norm: the two-quads-per-thread form needs a multiple of 256 values");
+    if (topology != 1 && (threadgroup_width < 32 || threadgroup_width % 32 || threadgroup_width > 1024)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "row norm: threadgroup width a multiple of 32 up to 1024");
+    if (scale_out && (reinterpret_cast<uintptr_t>(scale_out) & 3u)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "row norm: the scale output must be 4-byte aligned");
+    return check_cuda(ctx, launch_row_norm(typed(ctx), (const __half*)x, (const __half*)pre, (const __half*)w, (const __half*)residual, (const __half*)scalar, (__half*)y,
+                                           (float*)scale_out, rows, dim, eps, topology, threadgroup_width, value, scale), "row norm");
 }
 
 }  // extern "C"

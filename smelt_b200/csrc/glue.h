@@ -37,6 +37,7 @@ cudaError_t launch_bitplane_fused_producer(const Launch& l, int front, const __h
 enum { kEwSilu = 0, kEwSigmoid, kEwSoftplus, kEwCopy, kEwScalarMul, kEwLogitCap, kEwMul, kEwSigmoidMul, kEwGeglu, kEwBiasAdd };
 enum { kHeadNormDirect = 0, kHeadNorm1pw = 1, kHeadNormNoScale = 2 };
 cudaError_t launch_elementwise(const Launch& l, int op, const __half* a, const __half* b, __half* y, int count, int batch, int b_stride, float scalar, const __half* scalar_dev);
+cudaError_t launch_row_norm(const Launch& l, const __half* x, const __half* pre, const __half* w, const __half* residual, const __half* scalar, __half* y, float* scale_out, int rows, int dim, float eps, int topology, int tgs, int value, int scale);
 cudaError_t launch_gate_split(const Launch& l, const __half* in, __half* query, __half* gate, int heads, int head_dim);
 cudaError_t launch_head_norm(const Launch& l, int mode, const __half* x, const __half* w, __half* y, int heads, int head_dim, float eps, int tgs);
 cudaError_t launch_signed_embedding_gather(const Launch& l, int format, const uint8_t* codes, const __half* scales, const int32_t* token_ids, __half* out, int hidden, int batch);

@@ -64,6 +64,7 @@ enum PipeKind : int {
     PK_ELEMENTWISE,
     PK_GATE_SPLIT,
     PK_HEAD_NORM,
+    PK_ROW_NORM,
     PK_EMBEDDING_GATHER_BATCHED,
     PK_AFFINE_EMBEDDING_GATHER_BATCHED,
     PK_BITPLANE_BANK4,

@@ -180,3 +180,120 @@ def test_glue_records(ctx, oracle):
     gg, gw = read(10, (batch, 400)), oracle.elementwise(oracle.EW_GEGLU, gate_rows, up_rows, b_stride=640)
     assert np.all((ulp_diff_f16(gg, gw) <= 1) | (np.abs(gg.astype(F) - gw.astype(F)) < 1e-6))
     assert np.array_equal(read(13, (batch, hidden)), table[ids])
+
+
+# ── the row norms of norms.metal beyond rms_norm_1pw ──
+ROW_NORM_CASES = [  # (dim, topology, value, scale, tgs, residual, scalar, pre)
+    (2048, 1, 2, 0, 0, False, False, False),    # rms_norm_1pw_d2048
+    (1536, 1, 2, 0, 0, True, False, False),     # rms_norm_1pw_d1536_add(_batched)
+    (2560, 1, 2, 0, 0, False, False, False),    # rms_norm_1pw_d2560
+    (256, 2, 3, 0, 256, True, True, False),     # rms_norm_1pw_d256_add_scalar_weight
+    (4096, 0, 1, 0, 256, False, False, False),  # rms_norm_1pw_batched
+    (1000, 0, 1, 0, 128, False, False, False),  # ... with a ragged last tile
+    (5120, 2, 0, 0, 512, False, False, True),   # residual_add_rms_norm_scale_only_precise
+    (128, 2, 4, 1, 128, False, False, False),   # l2_normalize_d128
+]
+
+
+@pytest.mark.parametrize("dim,topology,value,scale,tgs,residual,scalar,pre", ROW_NORM_CASES)
+def test_oracle_row_norms_against_float_formulas(oracle, dim, topology, value, scale, tgs, residual, scalar, pre):
+    rng = np.random.default_rng(dim)
+    rows = 3
+    x, w = halves(rng, rows, dim), halves(rng, dim, scale=0.2)
+    res = halves(rng, rows, dim) if residual else None
+    pr = halves(rng, rows, dim) if pre else None
+    sc = np.array([0.75], np.float16) if scalar else None
+    y, scales = oracle.row_norm(x, w, topology=topology, value=value, tgs=tgs or 256, scale=scale, pre=pr, residual=res, scalar=sc)
+    v = (x + pr).astype(F) if pre else x.astype(F)
+    total = (v.astype(np.float64) ** 2).sum(1)
+    ref_scale = 1 / np.sqrt(total / dim + 1e-6) if scale == 0 else 1 / np.maximum(np.sqrt(total), 1e-6)
+    assert np.allclose(scales, ref_scale, rtol=2e-6)
+    if value == 0:
+        assert np.array_equal(y, x + pr)
+        return
+    rs = scales[:, None]
+    ref = {1: (1 + w.astype(F)).astype(np.float16).astype(F) * (v * rs).astype(np.float16).astype(F), 2: v * (rs * (1 + w.astype(F))),
+           3: v * rs * (1 + w.astype(F)), 4: v * rs}[value].astype(np.float16)
+    if residual:
+        ref = ref + res
+    if scalar:
+        ref = (ref.astype(F) * F(np.float16(0.75))).astype(np.float16)
+    assert np.max(ulp_diff_f16(y, ref)) <= 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,topology,value,scale,tgs,residual,scalar,pre", ROW_NORM_CASES)
+def test_row_norm_kernels_are_bit_exact(ctx, oracle, dim, topology, value, scale, tgs, residual, scalar, pre):
+    rng = np.random.default_rng(dim + 1)
+    rows = 5
+    x, w = halves(rng, rows, dim), halves(rng, dim, scale=0.2)
+    res = halves(rng, rows, dim) if residual else None
+    pr = halves(rng, rows, dim) if pre else None
+    sc = np.array([0.75], np.float16) if scalar else None
+    dev = lambda a: ctx.to_device(a) if a is not None else None
+    dx, dy, dscale = ctx.to_device(x), ctx.alloc(x.nbytes), ctx.alloc(rows * 4)
+    ctx.call("row_norm", dx, dev(pr), ctx.to_device(w), dev(res), dev(sc), dy, dscale, rows, dim, C.c_float(1e-6), topology, tgs or 256, value, scale)
+    want_y, want_scale = oracle.row_norm(x, w, topology=topology, value=value, tgs=tgs or 256, scale=scale, pre=pr, residual=res, scalar=sc)
+    assert np.array_equal(dscale.download(np.uint32, (rows,)), want_scale.view(np.uint32))  # IEEE operations only: same bits
+    assert np.array_equal(dy.download(np.uint16, x.shape), want_y.view(np.uint16))
+
+
+@pytest.mark.gpu
+def test_row_norm_records_feed_the_norm_scale_view(ctx, oracle):
+    """residual_add_rms_norm_scale_only_precise -> norm_scale_signed_activation_bitplanes_i4_g128 (the Bonsai
+    layer entry), rms_norm_1pw_d2048, rms_norm_1pw_d1536_add_batched and l2_normalize_d128 as records."""
+    rng = np.random.default_rng(9)
+    hidden = 5120
+    a, b, nw = halves(rng, hidden), halves(rng, hidden), halves(rng, hidden, scale=0.2)
+    x2048, w2048 = halves(rng, 2048), halves(rng, 2048, scale=0.2)
+    x1536, w1536, r1536 = halves(rng, 3, 1536), halves(rng, 1536, scale=0.2), halves(rng, 3, 1536)
+    qk = halves(rng, 6, 128)
+    groups = hidden // 128
+    tensors = {2: a, 3: b, 4: np.zeros(hidden, np.float16), 5: np.zeros(1, F), 6: nw, 7: np.zeros(groups * 16, np.uint32), 8: np.zeros(groups, np.float16),
+               9: x2048, 10: w2048, 11: np.zeros(2048, np.float16), 12: x1536, 13: w1536, 14: r1536, 15: np.zeros((3, 1536), np.float16), 16: qk}
+    for slot, t in tensors.items():
+        t = np.ascontiguousarray(t)
+        ctx.call("alloc_slot", slot, C.c_size_t(t.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), t.ctypes.data_as(C.c_void_p), C.c_size_t(t.nbytes)))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    names = ["residual_add_rms_norm_scale_only_precise", "norm_scale_signed_activation_bitplanes_i4_g128", "rms_norm_1pw_d2048", "rms_norm_1pw_d1536_add_batched", "l2_normalize_d128"]
+    for i, n in enumerate(names):
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 50 + i, n.encode()))
+    f32 = lambda v: int(np.array([v], F).view(np.uint32)[0])
+
+    def rec(pipe, grid, tg, bufs, cons):
+        r = capi.DispatchRecord()
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, pipe, len(bufs), len(cons)
+        r.grid[0], r.grid[1], r.grid[2] = grid, 1, 1
+        r.threadgroup[0], r.threadgroup[1], r.threadgroup[2] = tg, 1, 1
+        for j, (binding, slot) in enumerate(bufs):
+            r.buf[j].slot, r.buf[j].binding_index, r.buf[j].offset_kind, r.buf[j].offset = slot, binding, 0, 0
+        for j, (binding, kind, value) in enumerate(cons):
+            r.con[j].kind, r.con[j].binding_index, r.con[j].value = kind, binding, value
+        return r
+
+    tbl = (capi.DispatchRecord * 5)(
+        rec(50, 1, 512, [(0, 2), (1, 3), (2, 4), (3, 5)], [(4, 0, hidden), (5, 1, f32(1e-6))]),
+        rec(51, groups, 32, [(0, 5), (1, 4), (2, 6), (3, 7), (4, 8)], [(5, 0, hidden)]),
+        rec(52, 1, 256, [(0, 9), (1, 10), (2, 11)], []),
+        rec(53, 3, 192, [(0, 12), (1, 13), (2, 14), (3, 15)], []),
+        rec(54, 6, 128, [(0, 16)], []))
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, tbl, 5, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+
+    def read(slot, shape, dtype=np.float16):
+        out = np.zeros(shape, dtype)
+        ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, slot, C.c_size_t(0), out.ctypes.data_as(C.c_void_p), C.c_size_t(out.nbytes)))
+        return out
+
+    summed, scale = oracle.row_norm(a, None, topology=2, value=0, tgs=512, pre=b)
+    assert np.array_equal(read(4, hidden), summed) and np.array_equal(read(5, 1, F).view(np.uint32), scale.view(np.uint32))
+    pl, sc = oracle.norm_scale_signed_activation_bitplanes(float(scale[0]), summed, nw, hidden, 4)
+    assert np.array_equal(read(8, groups).view(np.uint16), sc.view(np.uint16)) and np.array_equal(read(7, groups * 16, np.uint32).reshape(pl.shape), pl)
+    assert np.array_equal(read(11, 2048), oracle.row_norm(x2048, w2048, topology=1, value=2)[0])
+    assert np.array_equal(read(15, (3, 1536)), oracle.row_norm(x1536, w1536, topology=1, value=2, residual=r1536)[0])
+    assert np.array_equal(read(16, (6, 128)), oracle.row_norm(qk, None, topology=2, value=4, tgs=128, scale=1)[0])
