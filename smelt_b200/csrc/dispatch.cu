@@ -89,7 +89,8 @@ bool parse_affine(const std::string& name, const char* base, PipeKind kind, Pipe
     q.kind = kind;
     if (!rest.empty()) {
         if (!parse_shape(rest, &q)) return false;
-        if (starts_with(rest, "_rows4")) rest = rest.substr(6);
+        if (starts_with(rest, "_rows4_sg1")) rest = rest.substr(10);  // row-tile forms of the same kernel (lut_matvec.metal:7727-7742, :8701-8738)
+        else if (starts_with(rest, "_rows4") || starts_with(rest, "_rows8")) rest = rest.substr(6);
         if (starts_with(rest, "_batched")) { q.batched = true; rest.clear(); }  // _batched, _batched_full, _batched_tile3, _batched_sg4_bt5, _batched_ext_b5 ...
         if (!rest.empty()) return false;
     }

@@ -1,0 +1,54 @@
+"""Which of the reference's Metal kernels the library binds by name.  tests/golden/kernel_names.txt lists every
+`kernel void` of the reference's shaders (written by tests/golden/make_kernel_names.py); the library's own
+name table is asked, without a GPU, through smelt_cuda_pipeline_supported.  The shader files of the decode
+path must be covered completely or up to the exceptions spelled out here, so that a change that drops a name
+fails, and a package that names a kernel outside this list fails when it is opened, not in the middle of a token."""
+import collections
+import ctypes as C
+import os
+
+from smelt_b200 import capi
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# file -> the names NOT bound (everything else in the file must be)
+EXPECTED_GAPS = {
+    "signed_quant.metal": set(),
+    "activations.metal": set(),
+    "activations_precise.metal": set(),
+    "attention_fused.metal": set(),
+    "norms_gated_precise.metal": set(),
+    "norms.metal": {"l2_normalize_q_prefill", "l2_normalize_k_prefill", "l2_normalize_q_d128_c6144_h16_prefill", "l2_normalize_k_d128_c6144_h16_prefill"},
+    "conv1d.metal": {"conv1d_update_silu_l2_qk_c6144_k4_d128_h16"},
+    "prefill_recurrence.metal": {"deltanet_recurrence_prefill"},
+    "signed_quant_precise.metal": {"signed_ternary_affine_bank4_matvec_g128_rows8", "signed_ternary_affine_gate_up_swiglu_g128_rows8",
+                                   "signed_ternary_affine_matvec_add_g128_rows8", "signed_ternary_affine_qmm_g128_bm32_bn32_bk32"},
+}
+
+
+def supported_by_file():
+    lib = C.CDLL(capi.LIB_PATH)
+    lib.smelt_cuda_pipeline_supported.argtypes = [C.c_char_p]
+    lib.smelt_cuda_pipeline_supported.restype = C.c_int
+    by = collections.defaultdict(dict)
+    for line in open(os.path.join(HERE, "golden", "kernel_names.txt")):
+        f, name = line.split()
+        by[f][name] = bool(lib.smelt_cuda_pipeline_supported(name.encode()))
+    return by
+
+
+def test_decode_path_shaders_are_bound_by_name():
+    by = supported_by_file()
+    for f, gaps in EXPECTED_GAPS.items():
+        missing = {n for n, ok in by[f].items() if not ok}
+        assert missing == gaps, (f, sorted(missing ^ gaps))
+
+
+def test_affine_and_attention_families_do_not_shrink():
+    by = supported_by_file()
+    families = ("affine_matvec", "fused_affine_matvec_add", "fused_affine_gate_up_swiglu", "fused_dual_affine_matvec", "affine_embedding_gather")
+    affine = [n for n in by["lut_matvec.metal"] if n.startswith(families) and "argmax" not in n and not n.endswith("_reference")]
+    bound = [n for n in affine if by["lut_matvec.metal"][n]]
+    assert len(bound) == len(affine), sorted(set(affine) - set(bound))
+    assert sum(by["attention.metal"].values()) >= 16
+    assert sum(sum(d.values()) for d in by.values()) >= 351
