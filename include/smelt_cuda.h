@@ -85,9 +85,18 @@ enum {
     SMELT_CONST_LITERAL_F32 = 1,
     SMELT_CONST_POSITION = 2,
     SMELT_CONST_POSITION_PLUS1 = 3,
+    /* prompt chunks only (smelt_cuda_enqueue_prefill): seqLen, startPos, startPos + value, seqLen * value, seqLen % value,
+     * the same with the dispatch skipped when it is zero (SmeltDispatchTable.swift:68-79) */
+    SMELT_CONST_SEQ_LEN = 4,
+    SMELT_CONST_START_POS = 5,
+    SMELT_CONST_START_POS_PLUS = 6,
+    SMELT_CONST_SEQ_LEN_MUL = 7,
+    SMELT_CONST_SEQ_LEN_MOD = 8,
+    SMELT_CONST_SEQ_LEN_MOD_SKIP_IF_ZERO = 9,
     SMELT_CONST_SKIP_UNLESS_POS1_LT = 10,
     SMELT_CONST_SKIP_UNLESS_POS1_GE = 11,
-    SMELT_CONST_CACHE_SEQ_CAPACITY = 12
+    SMELT_CONST_CACHE_SEQ_CAPACITY = 12,
+    SMELT_CONST_SKIP_UNLESS_SEQ_LEN_LT = 13 /* prompt chunks only: the dispatch runs only while seqLen < value */
 };
 enum { SMELT_OP_DISPATCH = 0, SMELT_OP_SWAP = 1 };
 enum { SMELT_SLOT_CUR = -1, SMELT_SLOT_ALT = -2 };
@@ -161,6 +170,14 @@ SMELT_CUDA_API int smelt_cuda_pipeline_supported(const char* name);
 /* One decoded token, synchronously: writes token / position into their slots, interprets the
  * table, waits, reads the argmax slot (SmeltRuntime.decodeStep, SmeltRuntime.swift:1573-1641).
  * tokens / out_tokens hold config.batch entries. */
+/* A prompt chunk through a prefill dispatch table (encodeTrunkPrefill, SmeltRuntime.swift:5062-5091): writes seq_len
+ * token ids to the token slot and interprets the records with the prompt-chunk kinds resolved on the host: constants
+ * seqLen / startPos / startPos + v / seqLen * v / seqLen % v (4..9) and the seqLen < v guard (13), position kinds as
+ * startPos, buffer offsets startPos * stride + addend / (seqLen - 1) * stride / floor(seqLen / d) * stride (2..4), grid
+ * dimensions that follow seqLen (style bits 2..7) and the record's minSeqLen guard.  Enqueue only; eager (not captured);
+ * start_pos + seq_len must stay inside min(context_limit, cache_seq_capacity). */
+SMELT_CUDA_API smelt_status smelt_cuda_enqueue_prefill(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records,
+                                                       const int32_t* tokens_host, int32_t seq_len, int32_t start_pos);
 SMELT_CUDA_API smelt_status smelt_cuda_decode_step(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records,
                                                    const int32_t* tokens, int32_t position, int32_t* out_tokens);
 /* Enqueue-only form (encodeTrunkDecode, SmeltRuntime.swift:5029-5091): no wait, no readback.
@@ -244,6 +261,15 @@ typedef struct {
 SMELT_CUDA_API smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc,
                                                      const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
                                                      smelt_dispatch_record* records, size_t* n_records);
+/* The prompt-chunk table of the decoder smelt_cuda_build_decoder built (same descriptor and layer references; one
+ * GPU, batch 1), in the reference's prefill record shapes (Sources/SmeltCompiler/PrefillEmitter.swift): chunk length
+ * and start position are run-time constants, so one table serves every chunk of up to max_chunk positions through
+ * smelt_cuda_enqueue_prefill.  Allocates the chunk's activation slots (2..7, 9, 10), grows the token slot to
+ * max_chunk ids (call it before smelt_cuda_graph_build: growing a slot drops a captured graph) and registers the
+ * table's pipelines after the decode table's.  Null ctx / records: counts only. */
+SMELT_CUDA_API smelt_status smelt_cuda_build_prefill_table(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc,
+                                                           const smelt_layer_ref* layers, uint32_t max_chunk,
+                                                           smelt_dispatch_record* records, size_t* n_records);
 
 /* The manifest.pipelines array matching the table smelt_cuda_build_decoder writes for `desc`
  * and `batch`: names in index order, newline separated.  *needed_bytes receives the size of

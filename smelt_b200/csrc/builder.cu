@@ -30,11 +30,12 @@ struct Emitter {
     size_t cap, n = 0;
     std::map<std::string, int> pipes;
     smelt_status status = SMELT_OK;
+    int base = 0;  // first pipeline index this table may register (a prefill table comes after the decode table's)
 
     int pipe(const std::string& name) {
         auto it = pipes.find(name);
         if (it != pipes.end()) return it->second;
-        const int idx = (int)pipes.size();
+        const int idx = base + (int)pipes.size();
         if (ctx) {
             smelt_status s = smelt_cuda_register_pipeline(ctx, idx, name.c_str());
             if (s && !status) status = s;
@@ -71,6 +72,14 @@ struct Rec {
         return *this;
     }
     Rec& u32(int binding, uint32_t v) { return con(binding, SMELT_CONST_LITERAL_U32, v); }
+    // grid dimension `dim` follows the chunk length: kind 1 seqLen, 2 seqLen * literal, 3 ceil(seqLen / literal) (SmeltDispatchTable.swift:163-222)
+    Rec& grid_kind(int dim, uint8_t kind) { r->style = (uint8_t)(r->style | (kind << (2 + 2 * dim))); return *this; }
+    Rec& buf_kind(int binding, int slot, uint8_t kind, uint64_t offset) {
+        buf(binding, slot, offset);
+        r->buf[r->buffer_count - 1].offset_kind = kind;
+        return *this;
+    }
+    Rec& tg(uint32_t w) { r->threadgroup[0] = w; return *this; }
     Rec& f32(int binding, float v) { return con(binding, SMELT_CONST_LITERAL_F32, f32_bits(v)); }
     Rec& affine(int first, const smelt_affine_ref& w) {
         return buf(first, kWeights, w.packed).buf(first + 1, kWeights, w.scales).buf(first + 2, kWeights, w.biases);
@@ -251,6 +260,79 @@ extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smel
                                                  const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
                                                  smelt_dispatch_record* records, size_t* n_records) {
     return build_decoder_impl(ctx, d, layers, capacity, batch, records, n_records, nullptr);
+}
+
+// The prompt-chunk table of the same decoder, in the reference's prefill record shapes
+// (Sources/SmeltCompiler/PrefillEmitter.swift: batched gathers and norms, *_batched projections with actualBatch =
+// seqLen, rope_and_kv_cache_prefill_analytic, attention_prefill, last-row offset for the LM head): chunk length and
+// start position are run-time constants, so one table serves every chunk up to max_chunk positions.
+enum PrefillSlot : int { kPfX0 = 2, kPfX1 = 3, kPfNorm = 4, kPfQ = 5, kPfK = 6, kPfV = 7, kPfAttn = 9, kPfFfn = 10 };
+
+extern "C" smelt_status smelt_cuda_build_prefill_table(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
+                                                       uint32_t max_chunk, smelt_dispatch_record* records, size_t* n_records) {
+    if (!d || !layers || !n_records) return SMELT_ERR_BAD_ARGUMENT;
+    if (d->layers <= 0 || d->layers > 100 || d->hidden <= 0 || d->inter <= 0 || d->n_q <= 0 || d->n_kv <= 0 || d->n_q % d->n_kv || d->head_dim <= 0 || d->vocab <= 0 ||
+        max_chunk == 0 || d->tp_world > 1)
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: bad model description (one GPU, batch 1)");
+    const int H = d->hidden, I = d->inter, D = d->head_dim, G = d->group, L = d->layers, V = d->vocab;
+    const int qd = d->n_q * D, kvd = d->n_kv * D;
+    const size_t T = max_chunk;
+    Emitter e{ctx, records, records ? *n_records : 0};
+    if (ctx) {
+        if (!records) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: a context needs a record buffer (query the count with a null context)");
+        if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+        if (!ctx->configured || ctx->cfg.batch != 1 || !ctx->slots[kWeights].ptr || !ctx->slots[kKvBase].ptr)
+            return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: build the decoder (batch 1) first");
+        struct { int slot; size_t bytes; } plan[] = {
+            {kPfX0, T * H * 2}, {kPfX1, T * H * 2}, {kPfNorm, T * H * 2}, {kPfQ, T * qd * 2}, {kPfK, T * kvd * 2}, {kPfV, T * kvd * 2},
+            {kPfAttn, T * qd * 2}, {kPfFfn, T * I * 2},
+        };
+        for (auto& p : plan) {
+            smelt_status s = smelt_cuda_alloc_slot(ctx, p.slot, p.bytes);
+            if (s) return s;
+        }
+        if (ctx->slots[kTokenId].bytes < T * 4) {  // a chunk's token ids (dropping any captured graph: rebuild it afterwards)
+            smelt_status s = smelt_cuda_alloc_slot(ctx, kTokenId, T * 4);
+            if (s) return s;
+        }
+        e.base = (int)ctx->pipelines.size();
+    }
+    const float log2_theta = log2f(d->rope_theta), scale = 1.0f / sqrtf((float)D);
+    const uint8_t kSeq = SMELT_CONST_SEQ_LEN, kStart = SMELT_CONST_START_POS;
+    Rec(e, "embedding_gather_batched", (H + 63) / 64, 1).grid_kind(1, 1).buf(0, kWeights, d->embedding).buf(1, kTokenId).buf(2, kPfX0).u32(3, H).con(4, kSeq);
+    for (int l = 0; l < L; ++l) {
+        const smelt_layer_ref& w = layers[l];
+        const int kslot = kKvBase + l, vslot = kKvBase + L + l;
+        Rec(e, "rms_norm_1pw_batched", 1).grid_kind(0, 1).tg(256).buf(0, kPfX0).buf(1, kWeights, w.input_norm).buf(2, kPfNorm).u32(3, H).f32(4, d->eps);
+        { Rec r(e, shaped("affine_matvec", H, qd, G, true) + "_full", (qd + 31) / 32, 1); r.grid_kind(1, 3).r->grid[1] = 8; r.affine(0, w.q).buf(3, kPfNorm).buf(4, kPfQ).con(5, kSeq); }
+        { Rec r(e, shaped("fused_dual_affine_matvec", H, kvd, G, true), (kvd + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.k).affine(3, w.v).buf(6, kPfNorm).buf(7, kPfK).buf(8, kPfV).con(9, kSeq); }
+        Rec(e, "rope_and_kv_cache_prefill_analytic", 1, (uint32_t)(d->n_q > d->n_kv ? d->n_q : d->n_kv)).grid_kind(0, 1).buf(0, kPfQ).buf(1, kPfK).buf(2, kPfV).buf(3, kslot).buf(4, vslot)
+            .u32(5, (uint32_t)D | ((uint32_t)D << 16)).u32(6, (uint32_t)d->n_q | ((uint32_t)d->n_kv << 16)).con(7, kSeq).con(8, kStart)
+            .con(9, SMELT_CONST_CACHE_SEQ_CAPACITY).u32(10, 1).f32(11, log2_theta);
+        {
+            Rec r(e, "attention_prefill", d->n_q, 1);
+            r.grid_kind(1, 1).buf(0, kPfQ).buf(1, kslot).buf(2, vslot).buf(3, kPfAttn).u32(4, D).con(5, kSeq).con(6, kStart).con(7, SMELT_CONST_CACHE_SEQ_CAPACITY);
+            // a record holds eight constants: numKVHeads and scale follow, the sliding window (none) stays unbound
+            r.u32(8, d->n_kv).f32(9, scale);
+        }
+        { Rec r(e, shaped("fused_affine_matvec_add", qd, H, G, true), (H + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.o).buf(3, kPfAttn).buf(4, kPfX1).buf(5, kPfX0).con(6, kSeq); }
+        Rec(e, "rms_norm_1pw_batched", 1).grid_kind(0, 1).tg(256).buf(0, kPfX1).buf(1, kWeights, w.post_norm).buf(2, kPfNorm).u32(3, H).f32(4, d->eps);
+        { Rec r(e, shaped("fused_affine_gate_up_swiglu", H, I, G, true), (I + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.gate).affine(3, w.up).buf(6, kPfNorm).buf(7, kPfFfn).con(8, kSeq); }
+        { Rec r(e, shaped("fused_affine_matvec_add", I, H, G, true), (H + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.down).buf(3, kPfFfn).buf(4, kPfX0).buf(5, kPfX1).con(6, kSeq); }
+    }
+    // the last position only: final norm, LM head, argmax (offset kind 3: (seqLen - 1) * row bytes)
+    Rec(e, "rms_norm_1pw", 1).buf_kind(0, kPfX0, 3, (uint64_t)H * 2).buf(1, kWeights, d->final_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
+    Rec(e, "fp16_matvec", V, 1).buf(0, kWeights, d->lm_head).buf(1, kNormOut).buf(2, kLogits).u32(3, H);
+    const int chunk = 2048, parts = (V + chunk - 1) / chunk;
+    Rec(e, "argmax_fp16_partials", parts, 1).buf(0, kLogits).buf(1, kArgmaxScratch).u32(2, V).u32(3, chunk);
+    Rec(e, "argmax_key_reduce", 1, 1).buf(0, kArgmaxScratch).buf(1, kArgmax).u32(2, parts);
+    const size_t need = e.n;
+    if (records && need > *n_records) {
+        *n_records = need;
+        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: record buffer too small");
+    }
+    *n_records = need;
+    return e.status;
 }
 
 extern "C" smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_desc* d, uint32_t batch, char* out, size_t out_bytes,

@@ -175,6 +175,10 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"per_head_rms_norm_noscale_batched", PK_HEAD_NORM, kHeadNormNoScale, true},
         {"embedding_gather_batched", PK_EMBEDDING_GATHER_BATCHED, 0, true},
         {"affine_embedding_gather_batched", PK_AFFINE_EMBEDDING_GATHER_BATCHED, 0, true},
+        // prompt chunks (prefill_rope_kv.metal:64-187, prefill_rope_kv_precise.metal:8-60, prefill_attention.metal:14-413): bits 1 = analytic RoPE
+        {"rope_and_kv_cache_prefill", PK_ROPE_KV_PREFILL, 0, true},
+        {"rope_and_kv_cache_prefill_analytic", PK_ROPE_KV_PREFILL, 1, true},
+        {"attention_prefill", PK_ATTN_PREFILL, 0, true},
         {"kv_cache_update", PK_KV_UPDATE, 0, false},
         {"apply_rope", PK_APPLY_ROPE, 0, false},
         {"rope_kv_cache_update", PK_ROPE_KV_UPDATE, 0, false},
@@ -345,6 +349,8 @@ struct Interp {
     uint32_t position;  // host copy (valid when !device_pos)
     int cur, alt;
     int launches = 0;
+    bool prefill = false;    // a prompt chunk: seq_len positions from start_pos (position == start_pos; SmeltRuntime.swift:1217-1250)
+    uint32_t seq_len = 0, start_pos = 0;
     int rope_half = 0;       // the position's cos | sin table holds this many pairs ...
     float rope_base = 0.f;   // ... for this log2(theta); 0 pairs = not written in this interpretation
 };
@@ -364,8 +370,15 @@ smelt_status resolve(Interp& in, const smelt_dispatch_record& rec, Resolved* out
         if (b.offset_kind == 1) {
             if (in.device_pos) { r.pos_strided = true; r.stride = b.offset; off = 0; }
             else off = (uint64_t)in.position * b.offset;
+        } else if (b.offset_kind >= 2 && b.offset_kind <= 4) {
+            // the prompt-chunk offsets (resolveDispatchBufferOffset, SmeltRuntime.swift:6160-6185)
+            if (!in.prefill) return fail(ctx, SMELT_ERR_UNSUPPORTED, "record: prefill offset kinds are outside the decode path");
+            const uint64_t lo = b.offset & 0xFFFFFFFFull, hi = b.offset >> 32;
+            if (b.offset_kind == 2) off = (uint64_t)in.start_pos * lo + hi;
+            else if (b.offset_kind == 3) off = (uint64_t)(in.seq_len - 1) * b.offset;
+            else off = ((uint64_t)in.seq_len / (hi ? hi : 1)) * lo;
         } else if (b.offset_kind != 0) {
-            return fail(ctx, SMELT_ERR_UNSUPPORTED, "record: prefill offset kinds are outside the decode path");
+            return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record: unknown offset kind " + std::to_string(b.offset_kind));
         }
         if (off > ctx->slots[slot].bytes)
             return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "record: offset " + std::to_string(off) + " is outside slot " + std::to_string(slot));
@@ -386,13 +399,38 @@ smelt_status resolve(Interp& in, const smelt_dispatch_record& rec, Resolved* out
             case SMELT_CONST_LITERAL_U32: case SMELT_CONST_LITERAL_F32: case SMELT_CONST_POSITION:
             case SMELT_CONST_POSITION_PLUS1: case SMELT_CONST_CACHE_SEQ_CAPACITY:
                 break;
+            case SMELT_CONST_SEQ_LEN: case SMELT_CONST_START_POS: case SMELT_CONST_START_POS_PLUS: case SMELT_CONST_SEQ_LEN_MUL:
+            case SMELT_CONST_SEQ_LEN_MOD: case SMELT_CONST_SEQ_LEN_MOD_SKIP_IF_ZERO: case SMELT_CONST_SKIP_UNLESS_SEQ_LEN_LT:
+                if (!in.prefill) return fail(ctx, SMELT_ERR_UNSUPPORTED, "record: constant kind " + std::to_string(c.kind) + " is outside the decode path");
+                break;
             default:
-                return fail(ctx, SMELT_ERR_UNSUPPORTED, "record: constant kind " + std::to_string(c.kind) + " is outside the decode path");
+                return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record: unknown constant kind " + std::to_string(c.kind));
+        }
+        uint8_t kind = c.kind;
+        uint32_t value = c.value;
+        if (in.prefill) {
+            // resolvePrefillConstant (SmeltRuntime.swift:1217-1250): every run-time kind becomes a plain value here
+            switch (c.kind) {
+                case SMELT_CONST_SEQ_LEN: value = in.seq_len; kind = SMELT_CONST_LITERAL_U32; break;
+                case SMELT_CONST_START_POS: value = in.start_pos; kind = SMELT_CONST_LITERAL_U32; break;
+                case SMELT_CONST_START_POS_PLUS: value = in.start_pos + c.value; kind = SMELT_CONST_LITERAL_U32; break;
+                case SMELT_CONST_SEQ_LEN_MUL: value = in.seq_len * c.value; kind = SMELT_CONST_LITERAL_U32; break;
+                case SMELT_CONST_SEQ_LEN_MOD: value = c.value ? in.seq_len % c.value : 0u; kind = SMELT_CONST_LITERAL_U32; break;
+                case SMELT_CONST_SEQ_LEN_MOD_SKIP_IF_ZERO:
+                    value = c.value ? in.seq_len % c.value : 0u; kind = SMELT_CONST_LITERAL_U32;
+                    if (value == 0) out->skip = true;
+                    break;
+                case SMELT_CONST_SKIP_UNLESS_SEQ_LEN_LT:
+                    value = in.seq_len < c.value ? 1u : 0u; kind = SMELT_CONST_LITERAL_U32;
+                    if (value == 0) out->skip = true;
+                    break;
+                default: break;
+            }
         }
         if (c.binding_index != 255) {
             if (c.binding_index >= 32) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record: constant binding index out of range");
             RConst& r = out->con[c.binding_index];
-            r.present = true; r.kind = c.kind; r.value = c.value;
+            r.present = true; r.kind = kind; r.value = value;
         }
     }
     return SMELT_OK;
@@ -599,8 +637,25 @@ smelt_status run_attention(Interp& in, const Pipeline& p, const smelt_dispatch_r
     return check_cuda(ctx, launch_attention_decode(make_launch(in, r), a), p.name.c_str());
 }
 
-smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
+smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
     smelt_cuda_ctx* ctx = in.ctx;
+    smelt_dispatch_record rec = rec_in;
+    if (in.prefill) {
+        // minSeqLen guard and the grid dimensions that follow the chunk length (SmeltDispatchTable.swift:163-222,
+        // resolvePrefillGrid, SmeltRuntime.swift:6187-6207): handlers read the resolved grid
+        if (rec.min_seq_len && in.seq_len < rec.min_seq_len) return SMELT_OK;
+        for (int d = 0; d < 3; ++d) {
+            const uint32_t kind = (rec.style >> (2 + 2 * d)) & 3u, lit = rec.grid[d];
+            if (kind == 1) rec.grid[d] = in.seq_len;
+            else if (kind == 2) rec.grid[d] = in.seq_len * lit;
+            else if (kind == 3) {
+                const uint32_t div = (lit & 0x7FFFFFFFu) ? (lit & 0x7FFFFFFFu) : 1u;
+                rec.grid[d] = (lit & 0x80000000u) ? in.seq_len / div : (in.seq_len + div - 1) / div;
+            }
+        }
+    } else if (rec.style >> 2) {
+        return fail(ctx, SMELT_ERR_UNSUPPORTED, "record: prefill grid kinds are outside the decode path");
+    }
     if (rec.pipeline >= ctx->pipelines.size() || ctx->pipelines[rec.pipeline].kind == PK_NONE)
         return fail(ctx, SMELT_ERR_UNKNOWN_PIPELINE, "record names pipeline index " + std::to_string(rec.pipeline) + " which is not registered");
     const Pipeline& p = ctx->pipelines[rec.pipeline];
@@ -854,6 +909,50 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec) {
             in.launches += 1;
             return check_cuda(ctx, launch_row_norm(l, hp(ix), hp(ipre), hp(iw), hp(ires), hp(iscalar), iy >= 0 ? (__half*)r.buf[iy].ptr : nullptr,
                                                    iscale >= 0 ? (float*)r.buf[iscale].ptr : nullptr, rows, (int)dim, eps, n.topology, tgs, n.value, n.scale), p.name.c_str());
+        }
+        case PK_ROPE_KV_PREFILL: {
+            // prefill_rope_kv.metal:64-79: 0 q [T, Hq, D] and 1 k [T, Hkv, D] (rotated in place), 2 v, 3 cos and 4 sin tables
+            // [maxSeq, ropeDim], 5 K cache, 6 V cache, 7 headDim, 8 ropeDim, 9 qHeads, 10 kvHeads, 11 seqLen, 12 startPos,
+            // 13 cacheSeqCapacity, 14 ropeLayout.  prefill_rope_kv_precise.metal:8-21 (analytic): 3 K cache, 4 V cache,
+            // 5 headDim | ropeDim << 16, 6 qHeads | kvHeads << 16, 7 seqLen, 8 startPos, 9 cacheSeqCapacity, 10 ropeLayout, 11 log2(theta).
+            const bool analytic = p.bits == 1;
+            const int ikc = analytic ? 3 : 5, ic = analytic ? 5 : 7;
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(ikc); NEED_BUF(ikc + 1);
+            uint32_t d = 0, rope = 0, hq = 0, hkv = 0, t = 0, start = 0, cap = 0, layout = 0, base_bits = 0;
+            if (analytic) {
+                uint32_t dims = 0, heads = 0;
+                if (!host_u32(in, r, 5, &dims) || !host_u32(in, r, 6, &heads) || !host_u32(in, r, 7, &t) || !host_u32(in, r, 8, &start) || !host_u32(in, r, 9, &cap) ||
+                    !host_u32(in, r, 10, &layout) || !host_u32(in, r, 11, &base_bits))
+                    return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a constant binding is missing");
+                d = dims & 0xffffu; rope = dims >> 16; hq = heads & 0xffffu; hkv = heads >> 16;
+            } else {
+                NEED_BUF(3); NEED_BUF(4);
+                if (!host_u32(in, r, ic, &d) || !host_u32(in, r, ic + 1, &rope) || !host_u32(in, r, ic + 2, &hq) || !host_u32(in, r, ic + 3, &hkv) || !host_u32(in, r, ic + 4, &t) ||
+                    !host_u32(in, r, ic + 5, &start) || !host_u32(in, r, ic + 6, &cap) || !host_u32(in, r, ic + 7, &layout))
+                    return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a constant binding is missing");
+            }
+            if (d == 0 || d % 2 || rope == 0 || rope > d || rope % 2 || layout > 2 || (uint64_t)start + t > cap) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad shape, layout or positions past the cache capacity");
+            NEED_BYTES(0, (size_t)t * hq * d * 2); NEED_BYTES(1, (size_t)t * hkv * d * 2); NEED_BYTES(2, (size_t)t * hkv * d * 2);
+            NEED_BYTES(ikc, (size_t)hkv * cap * d * 2); NEED_BYTES(ikc + 1, (size_t)hkv * cap * d * 2);
+            if (!analytic) { NEED_BYTES(3, ((size_t)start + t) * rope * 2); NEED_BYTES(4, ((size_t)start + t) * rope * 2); }
+            in.launches += 1;
+            return check_cuda(ctx, launch_rope_kv_prefill(l, (__half*)r.buf[0].ptr, (__half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, analytic ? nullptr : (const __half*)r.buf[3].ptr,
+                                                          analytic ? nullptr : (const __half*)r.buf[4].ptr, (__half*)r.buf[ikc].ptr, (__half*)r.buf[ikc + 1].ptr, (int)d, (int)rope, (int)hq, (int)hkv,
+                                                          t, start, cap, (int)layout, analytic ? as_f32(base_bits) : 0.0f, analytic ? 1 : 0, (size_t)rope), p.name.c_str());
+        }
+        case PK_ATTN_PREFILL: {
+            // prefill_attention.metal:14-25: 0 q [T, Hq, D], 1 K cache, 2 V cache, 3 out, 4 headDim, 5 seqLen, 6 startPos,
+            // 7 cacheSeqCapacity, 8 numKVHeads, 9 scale, 10 slidingWindow; grid (numQHeads, seqLen).
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(4, d); NEED_U32(5, t); NEED_U32(6, start); NEED_U32(7, cap); NEED_U32(8, hkv); NEED_U32(9, scale_bits);
+            uint32_t window = 0;
+            (void)host_u32(in, r, 10, &window);
+            const int hq = (int)rec.grid[0];
+            if (hq <= 0 || hkv == 0 || hq % (int)hkv || hq / (int)hkv > 16 || (d != 64 && d != 128 && d != 256) || (uint64_t)start + t > cap)
+                return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": head_dim 64 / 128 / 256, up to 16 query heads per KV head, positions inside the cache");
+            NEED_BYTES(0, (size_t)t * hq * d * 2); NEED_BYTES(3, (size_t)t * hq * d * 2); NEED_BYTES(1, (size_t)hkv * cap * d * 2); NEED_BYTES(2, (size_t)hkv * cap * d * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_attention_prefill(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, hq, (int)hkv, (int)d,
+                                                            t, start, cap, as_f32(scale_bits), window), p.name.c_str());
         }
         case PK_EMBEDDING_GATHER_BATCHED: {
             // lut_matvec.metal:1121-1134: 0 table, 1 token ids [B], 2 out [B, hidden], 3 hidden, 4 batchSize.
@@ -1371,6 +1470,44 @@ smelt_status smelt_cuda_enqueue_decode(smelt_cuda_ctx* ctx, const smelt_dispatch
     s = write_dynamic(ctx, tokens, position);
     if (s) return s;
     return interpret(ctx, table, n_records, false, (uint32_t)position);
+}
+
+// A prompt chunk through a prefill table: seq_len token ids into the token slot, then every record with seqLen /
+// startPos resolved on the host (resolvePrefillConstant, resolveDispatchBufferOffset, resolvePrefillGrid;
+// SmeltRuntime.swift:1217-1250, :6160-6207).  Eager only: a prefill table's shapes change with the chunk.
+smelt_status smelt_cuda_enqueue_prefill(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records, const int32_t* tokens,
+                                        int32_t seq_len, int32_t start_pos) {
+    if (!ctx || !table || !tokens) return SMELT_ERR_BAD_ARGUMENT;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
+    if (!ctx->configured) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "context is not configured");
+    if (ctx->capturing) return fail(ctx, SMELT_ERR_UNSUPPORTED, "prefill tables are interpreted eagerly, not captured");
+    const uint64_t limit = ctx->cfg.context_limit < ctx->cfg.cache_seq_capacity ? ctx->cfg.context_limit : ctx->cfg.cache_seq_capacity;
+    if (seq_len <= 0 || start_pos < 0 || (uint64_t)start_pos + (uint64_t)seq_len > limit)
+        return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "prefill: positions [" + std::to_string(start_pos) + ", " + std::to_string((int64_t)start_pos + seq_len) + ") are outside [0, " + std::to_string(limit) + ")");
+    if ((size_t)seq_len > ctx->h_pinned_count - 256) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "prefill: at most " + std::to_string(ctx->h_pinned_count - 256) + " positions per chunk");
+    for (int32_t i = 0; i < seq_len; ++i)
+        if (tokens[i] < 0 || (uint32_t)tokens[i] >= ctx->cfg.vocab_size) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "tokenId out of range [0, " + std::to_string(ctx->cfg.vocab_size) + ")");
+    Slot& ts = ctx->slots[ctx->cfg.token_id_slot];
+    if (!ts.ptr || ts.bytes < (size_t)seq_len * 4) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "prefill: the token slot holds fewer than seq_len ids");
+    // the staging area may still feed an earlier chunk's copy
+    smelt_status s = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "prefill: chunk boundary");
+    if (s) return s;
+    for (int32_t i = 0; i < seq_len; ++i) ctx->h_pinned[256 + i] = tokens[i];
+    s = check_cuda(ctx, cudaMemcpyAsync(ts.ptr, ctx->h_pinned + 256, (size_t)seq_len * 4, cudaMemcpyHostToDevice, ctx->stream), "prefill: token ids");
+    if (s) return s;
+    Interp in;
+    in.ctx = ctx; in.device_pos = false; in.position = (uint32_t)start_pos;
+    in.prefill = true; in.seq_len = (uint32_t)seq_len; in.start_pos = (uint32_t)start_pos;
+    in.cur = ctx->cfg.cur_slot; in.alt = ctx->cfg.alt_slot;
+    for (size_t i = 0; i < n_records; ++i) {
+        const smelt_dispatch_record& rec = table[i];
+        if (rec.op_kind == SMELT_OP_SWAP) { int t = in.cur; in.cur = in.alt; in.alt = t; continue; }
+        if (rec.op_kind != SMELT_OP_DISPATCH) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "record " + std::to_string(i) + ": unknown op kind");
+        s = run_record(in, rec);
+        if (s) { ctx->err = "record " + std::to_string(i) + ": " + ctx->err; return s; }
+    }
+    ctx->launch_count = in.launches;
+    return SMELT_OK;
 }
 
 smelt_status smelt_cuda_decode_step(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records,

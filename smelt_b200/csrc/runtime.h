@@ -65,6 +65,8 @@ enum PipeKind : int {
     PK_GATE_SPLIT,
     PK_HEAD_NORM,
     PK_ROW_NORM,
+    PK_ROPE_KV_PREFILL,
+    PK_ATTN_PREFILL,
     PK_EMBEDDING_GATHER_BATCHED,
     PK_AFFINE_EMBEDDING_GATHER_BATCHED,
     PK_BITPLANE_BANK4,

@@ -214,6 +214,30 @@ class Decoder:
                                                         int(start_pos), int(chunk), C.byref(out)))
         return int(out.value)
 
+    def build_prefill_table(self, max_chunk: int = 512):
+        """The prompt-chunk dispatch table of this decoder in the reference's prefill record shapes
+        (``smelt_cuda_build_prefill_table``); call it before ``build_graph``."""
+        n = C.c_size_t(0)
+        self.ctx._check(self.ctx.lib.smelt_cuda_build_prefill_table(None, C.byref(self.desc), self.layers, int(max_chunk), None, C.byref(n)))
+        self.prefill_records = (capi.DispatchRecord * n.value)()
+        self.ctx._check(self.ctx.lib.smelt_cuda_build_prefill_table(self.ctx.h, C.byref(self.desc), self.layers, int(max_chunk), self.prefill_records, C.byref(n)))
+        self.prefill_chunk = int(max_chunk)
+        return self.prefill_records
+
+    def prefill_by_table(self, tokens, start_pos: int = 0) -> int:
+        """Prompt tokens through the prefill table, a chunk at a time (``smelt_cuda_enqueue_prefill``): the
+        record-interpreted twin of ``prefill``.  Returns the argmax after the last token."""
+        tokens = np.ascontiguousarray(np.asarray(tokens).reshape(-1), dtype=np.int32)
+        if not hasattr(self, "prefill_records"):
+            self.build_prefill_table()
+        for t0 in range(0, len(tokens), self.prefill_chunk):
+            part = np.ascontiguousarray(tokens[t0:t0 + self.prefill_chunk])
+            self.ctx._check(self.ctx.lib.smelt_cuda_enqueue_prefill(self.ctx.h, self.prefill_records, len(self.prefill_records), part.ctypes.data_as(C.c_void_p),
+                                                                    len(part), int(start_pos) + t0))
+        out = np.zeros(1, np.int32)
+        self.ctx._check(self.ctx.lib.smelt_cuda_read_slot(self.ctx.h, ARGMAX_SLOT, 0, out.ctypes.data_as(C.c_void_p), 4))
+        return int(out[0])
+
     def reset_cache(self):
         for l in range(2 * self.desc.layers):
             self.ctx.call("zero_slot", KV_BASE_SLOT + l)

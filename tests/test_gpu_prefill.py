@@ -150,3 +150,50 @@ def test_prefill_in_two_calls_continues_the_cache(ctx, oracle):
     # past the capacity: refused before anything runs
     st = ctx.lib.smelt_cuda_prefill(ctx.h, C.byref(dec.desc), dec.layers, prompt.ctypes.data_as(C.c_void_p), 33, 40, 0, None)
     assert st == capi.OUT_OF_RANGE and "pass the limit" in ctx.last_error()
+
+
+@pytest.mark.parametrize("cfg,n_prompt,chunk", [(SMALL, 45, 16), (MID, 70, 64), (MID, 20, 512)])
+def test_prefill_table_equals_the_typed_driver(ctx, oracle, cfg, n_prompt, chunk):
+    """The prompt through the prefill dispatch table in the reference's record shapes (seqLen / startPos constants,
+    grid kinds, last-row offset) against the typed driver: same caches and logits within kernel tolerance, same next
+    token; then the oracle's continuation from the table-filled cache."""
+    cap, n_dec = n_prompt + 40, 16
+    pkg, dec = make(ctx, cfg, 23, cap)
+    prompt = synth.rng_for(23, "prefill prompt").integers(0, cfg.vocab, size=n_prompt).astype(np.int32)
+    ref = oracle.model_from_package(pkg, cap)
+    want, runner, margins = ref.greedy_top2(prompt, n_dec)
+    tok_typed = dec.prefill(prompt, 0, chunk)
+    logits_typed = dec.logits()[0].astype(np.float32)
+    kv_typed = kv_of(dec, cfg, cap)
+    dec.reset_cache()
+    dec.build_prefill_table(chunk)
+    tok_table = dec.prefill_by_table(prompt)
+    logits_table = dec.logits()[0].astype(np.float32)
+    kv_table = kv_of(dec, cfg, cap)
+    for l, (a, b) in enumerate(zip(kv_table, kv_typed)):
+        assert not a[:, n_prompt:].any(), "nothing is written beyond the prompt"
+        assert rms_err(a[:, :n_prompt], b[:, :n_prompt]) < 1e-2, f"cache slot {l}"
+    err = float(np.max(np.abs(logits_table - logits_typed)) / np.sqrt(np.mean(logits_typed * logits_typed)))
+    assert err < 1e-2, err
+    v0 = package.compare_greedy(np.array([tok_table]), want[:1], runner[:1], margins[:1])
+    assert not v0["wrong"], (tok_table, tok_typed, v0)
+    got = [tok_table]
+    for i in range(n_dec - 1):
+        got.append(int(dec.decode_step([want[i]], n_prompt + i)[0]))
+    v = package.compare_greedy(np.array(got), want, runner, margins)
+    assert v["checked"] == n_dec and not v["wrong"], v
+
+
+def test_prefill_table_refuses_what_it_cannot_run(ctx):
+    pkg, dec = make(ctx, SMALL, 29, 64)
+    dec.build_prefill_table(16)
+    toks = np.arange(20, dtype=np.int32)
+    lib, h = ctx.lib, ctx.h
+    n = len(dec.prefill_records)
+    assert lib.smelt_cuda_enqueue_prefill(h, dec.prefill_records, n, toks.ctypes.data_as(C.c_void_p), 10, 60) == capi.OUT_OF_RANGE  # past the cache
+    assert lib.smelt_cuda_enqueue_prefill(h, dec.prefill_records, n, toks.ctypes.data_as(C.c_void_p), 20, 0) == capi.OUT_OF_RANGE  # token slot holds 16 ids
+    bad = toks.copy(); bad[3] = SMALL.vocab
+    assert lib.smelt_cuda_enqueue_prefill(h, dec.prefill_records, n, bad.ctypes.data_as(C.c_void_p), 8, 0) == capi.OUT_OF_RANGE
+    # a decode step refuses the prompt-chunk record kinds
+    tok = np.zeros(1, np.int32)
+    assert lib.smelt_cuda_enqueue_decode(h, dec.prefill_records, n, tok.ctypes.data_as(C.c_void_p), 0) == capi.UNSUPPORTED
