@@ -145,6 +145,12 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"signed_binary_gate_up_swiglu_g128_rows8", PK_SIGNED_GATEUP, 1, false},
         {"signed_binary_gate_up_swiglu_g128_rows8_batched_b4", PK_SIGNED_GATEUP, 1, true},
         {"signed_ternary_affine_matvec_g128_rows8", PK_SIGNED_TERNARY_AFFINE, 2, false},
+        // the other MLX-affine ternary forms (signed_quant_precise.metal:113-420): the bias scales repeat the scales, so they
+        // are the ternary kernels with one more binding
+        {"signed_ternary_affine_matvec_add_g128_rows8", PK_SIGNED_TERNARY_AFFINE_ADD, 2, false},
+        {"signed_ternary_affine_gate_up_swiglu_g128_rows8", PK_SIGNED_TERNARY_AFFINE_GATEUP, 2, false},
+        {"signed_ternary_affine_qmm_g128_bm32_bn32_bk32", PK_SIGNED_TERNARY_AFFINE, 2, true},
+        {"signed_ternary_affine_bank4_matvec_g128_rows8", PK_SIGNED_BANK, 3, false},
         // projection banks: the standalone matvec over a larger row space, outputs handed to their consumers
         // (signed_quant.metal:2634-2960); bits = layout: 0 two weight tensors, 1 one slab and two outputs, 2 one slab and four
         {"signed_binary_dual_matvec_g128_rows8", PK_SIGNED_BANK, 0, false},
@@ -532,9 +538,12 @@ smelt_status run_signed(Interp& in, const Pipeline& p, const smelt_dispatch_reco
     // signed_quant.metal:574-583 (matvec), :662-672 (add), :625-636 (gate/up); signed_quant_precise.metal:41-50
     SignedArgs a = {};
     int ix, iy, irows, ires = -1, mode = kSignedPlain;
+    int icodes2 = 2;  // gate / up: where the second matrix's codes are bound
     if (p.kind == PK_SIGNED_MATVEC) { ix = 2; iy = 3; irows = 4; }
     else if (p.kind == PK_SIGNED_ADD) { ix = 2; iy = 3; ires = 4; irows = 5; mode = kSignedAdd; }
     else if (p.kind == PK_SIGNED_GATEUP) { ix = 4; iy = 5; irows = 6; mode = kSignedGateUp; }
+    else if (p.kind == PK_SIGNED_TERNARY_AFFINE_ADD) { ix = 3; iy = 4; ires = 5; irows = 6; mode = kSignedAdd; }  // signed_quant_precise.metal:113-121
+    else if (p.kind == PK_SIGNED_TERNARY_AFFINE_GATEUP) { ix = 6; iy = 7; irows = 8; icodes2 = 3; mode = kSignedGateUp; }  // :268-278
     else { ix = 3; iy = 4; irows = 5; }  // ternary affine: binding 2 repeats the scales as the bias source
     NEED_U32(irows, rows); NEED_U32(irows + 1, cols);
     int batch = batch_of(rec);
@@ -544,8 +553,8 @@ smelt_status run_signed(Interp& in, const Pipeline& p, const smelt_dispatch_reco
     NEED_BUF(0); NEED_BUF(1); NEED_BYTES(0, code_bytes); NEED_BYTES(1, scale_bytes);
     a.codes[0] = r.buf[0].ptr; a.scales[0] = (const __half*)r.buf[1].ptr;
     if (mode == kSignedGateUp) {
-        NEED_BUF(2); NEED_BUF(3); NEED_BYTES(2, code_bytes); NEED_BYTES(3, scale_bytes);
-        a.codes[1] = r.buf[2].ptr; a.scales[1] = (const __half*)r.buf[3].ptr;
+        NEED_BUF(icodes2); NEED_BUF(icodes2 + 1); NEED_BYTES(icodes2, code_bytes); NEED_BYTES(icodes2 + 1, scale_bytes);
+        a.codes[1] = r.buf[icodes2].ptr; a.scales[1] = (const __half*)r.buf[icodes2 + 1].ptr;
     }
     NEED_BUF(ix); NEED_BUF(iy);
     NEED_BYTES(ix, (size_t)batch * cols * 2); NEED_BYTES(iy, (size_t)batch * rows * 2);
@@ -668,6 +677,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
         case PK_AFFINE_MATVEC: case PK_AFFINE_ADD: case PK_AFFINE_GATEUP: case PK_AFFINE_DUAL:
             return run_affine(in, p, rec, r);
         case PK_SIGNED_MATVEC: case PK_SIGNED_ADD: case PK_SIGNED_GATEUP: case PK_SIGNED_TERNARY_AFFINE:
+        case PK_SIGNED_TERNARY_AFFINE_ADD: case PK_SIGNED_TERNARY_AFFINE_GATEUP:
             return run_signed(in, p, rec, r);
         case PK_ATTN_GENERIC: case PK_ATTN_INPLACE: case PK_ATTN_ROPE: case PK_ATTN_MLX_2PASS_1:
             return run_attention(in, p, rec, r);
@@ -1104,13 +1114,16 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             // 7 / 8 row counts, 9 cols), :2802-2813 (packed bank: 0 codes, 1 scales, 2 input, 3 / 4 outputs, 5 / 6 row counts,
             // 7 cols), :2867-2882 (packed bank of four: 3..6 outputs, 7..10 row counts, 11 cols).  Exact lowerings of the
             // standalone binary matvec: the members run as that kernel.
+            // signed_quant_precise.metal:186-199 (ternary-affine bank of four: 0 codes, 1 scales, 2 bias scales, 3 input, 4..7 outputs,
+            // 8..11 row counts, 12 cols) is layout 3.
             const int layout = p.bits;
-            const int n_members = layout == 2 ? 4 : 2;
-            const int ix = layout == 0 ? 4 : 2, iout = ix + 1, irows = iout + n_members, icols = irows + n_members;
+            const int n_members = layout >= 2 ? 4 : 2;
+            const int ix = layout == 0 ? 4 : (layout == 3 ? 3 : 2), iout = ix + 1, irows = iout + n_members, icols = irows + n_members;
+            const int wbits = layout == 3 ? 2 : 1;
             NEED_BUF(0); NEED_BUF(1); NEED_BUF(ix);
             uint32_t cols = 0;
             if (!host_u32(in, r, icols, &cols) || cols == 0 || cols % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": cols must be a positive multiple of 128");
-            const size_t row_bytes = (size_t)cols / 8, groups = cols / 128;
+            const size_t row_bytes = (size_t)cols * wbits / 8, groups = cols / 128;
             NEED_BYTES(ix, (size_t)cols * 2);
             size_t first = 0;
             for (int m = 0; m < n_members; ++m) {
@@ -1125,7 +1138,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
                 SignedArgs a = {};
                 a.codes[0] = (const uint8_t*)r.buf[ic].ptr + off * row_bytes; a.scales[0] = (const __half*)r.buf[is].ptr + off * groups;
                 a.x = (const __half*)r.buf[ix].ptr; a.y = (__half*)r.buf[iout + m].ptr;
-                a.rows = (int)rows; a.cols = (int)cols; a.batch = 1; a.bits = 1;
+                a.rows = (int)rows; a.cols = (int)cols; a.batch = 1; a.bits = wbits;
                 in.launches += 1;
                 const smelt_status st = check_cuda(ctx, launch_signed(l, kSignedPlain, a), p.name.c_str());
                 if (st) return st;

@@ -61,6 +61,8 @@ enum PipeKind : int {
     PK_BITPLANE_GATED_NORM_PRODUCER,
     PK_SIGNED_EMBEDDING_GATHER,
     PK_SIGNED_BANK,
+    PK_SIGNED_TERNARY_AFFINE_ADD,
+    PK_SIGNED_TERNARY_AFFINE_GATEUP,
     PK_ELEMENTWISE,
     PK_GATE_SPLIT,
     PK_HEAD_NORM,

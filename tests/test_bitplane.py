@@ -462,3 +462,65 @@ def test_bank_and_prompt_row_records(ctx, oracle):
     direct = oracle.signed_matvec(1, codes, scales, xs[0], total, cols).astype(F)
     packed = np.concatenate([read(14, 40), read(15, 24), read(16, 16)]).astype(F)
     assert np.max(np.abs(packed - direct)) <= 2e-3 * max(1.0, float(np.max(np.abs(direct))))
+
+
+@pytest.mark.gpu
+def test_ternary_affine_records(ctx, oracle):
+    """The MLX-affine ternary forms as records (signed_quant_precise.metal:41-420: matvec, + residual, gate / up +
+    SwiGLU, bank of four, prompt-row QMM), whose bias scales repeat the scales: the ternary kernels' values."""
+    rows, cols, batch = 96, 512, 3
+    members = (40, 0, 24, 32)
+    codes, scales = weights(2, rows, cols, 90)
+    codes2, scales2 = weights(2, rows, cols, 91)
+    xs = synth.activations(92, "ta", batch, cols)
+    res = synth.activations(93, "tr", rows)
+    tensors = {2: codes, 3: scales, 4: codes2, 5: scales2, 6: xs, 7: res, 8: np.zeros(rows, np.float16), 9: np.zeros(rows, np.float16), 10: np.zeros(40, np.float16),
+               11: np.zeros(8, np.float16), 12: np.zeros(24, np.float16), 13: np.zeros(32, np.float16), 14: np.zeros((batch, rows), np.float16)}
+    for slot, t in tensors.items():
+        t = np.ascontiguousarray(t)
+        ctx.call("alloc_slot", slot, C.c_size_t(t.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), t.ctypes.data_as(C.c_void_p), C.c_size_t(t.nbytes)))
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    names = ["signed_ternary_affine_matvec_add_g128_rows8", "signed_ternary_affine_gate_up_swiglu_g128_rows8", "signed_ternary_affine_bank4_matvec_g128_rows8",
+             "signed_ternary_affine_qmm_g128_bm32_bn32_bk32"]
+    for i, n in enumerate(names):
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 60 + i, n.encode()))
+
+    def rec(pipe, bufs, cons):
+        r = capi.DispatchRecord()
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, pipe, len(bufs), len(cons)
+        r.grid[0], r.grid[1], r.grid[2] = 1, 1, 1
+        for j, (binding, slot) in enumerate(bufs):
+            r.buf[j].slot, r.buf[j].binding_index, r.buf[j].offset_kind, r.buf[j].offset = slot, binding, 0, 0
+        for j, (binding, value) in enumerate(cons):
+            r.con[j].kind, r.con[j].binding_index, r.con[j].value = 0, binding, value
+        return r
+
+    table = (capi.DispatchRecord * 4)(
+        rec(60, [(0, 2), (1, 3), (2, 3), (3, 6), (4, 8), (5, 7)], [(6, rows), (7, cols)]),
+        rec(61, [(0, 2), (1, 3), (2, 3), (3, 4), (4, 5), (5, 5), (6, 6), (7, 9)], [(8, rows), (9, cols)]),
+        rec(62, [(0, 2), (1, 3), (2, 3), (3, 6), (4, 10), (5, 11), (6, 12), (7, 13)], [(8, 40), (9, 0), (10, 24), (11, 32), (12, cols)]),
+        rec(63, [(0, 2), (1, 3), (2, 3), (3, 6), (4, 14)], [(5, rows), (6, cols), (7, batch)]))
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, table, 4, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+
+    def read(slot, shape):
+        out = np.zeros(shape, np.float16)
+        ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, slot, C.c_size_t(0), out.ctypes.data_as(C.c_void_p), C.c_size_t(out.nbytes)))
+        return out.astype(F)
+
+    def close(got, want):
+        want = want.astype(F)
+        return np.max(np.abs(got - want)) <= 2e-3 * max(1.0, float(np.max(np.abs(want))))
+
+    assert close(read(8, rows), oracle.signed_matvec_add(2, codes, scales, xs[0], res, rows, cols))
+    assert close(read(9, rows), oracle.signed_gate_up_swiglu(2, codes, scales, codes2, scales2, xs[0], rows, cols))
+    whole = oracle.signed_matvec(2, codes, scales, xs[0], rows, cols)
+    assert close(np.concatenate([read(10, 40), read(12, 24), read(13, 32)]), whole)
+    got = read(14, (batch, rows))
+    for b in range(batch):
+        assert close(got[b], oracle.signed_matvec(2, codes, scales, xs[b], rows, cols)), b
