@@ -271,6 +271,10 @@ SMELT_CUDA_API smelt_status smelt_cuda_build_prefill_table(smelt_cuda_ctx* ctx, 
                                                            const smelt_layer_ref* layers, uint32_t max_chunk,
                                                            smelt_dispatch_record* records, size_t* n_records);
 
+/* The pipeline names of the table smelt_cuda_build_prefill_table writes, in the order of the indices a table built
+ * without a context carries (0, 1, ...): newline separated, as smelt_cuda_decoder_pipelines reports the decode table's. */
+SMELT_CUDA_API smelt_status smelt_cuda_prefill_pipelines(const smelt_decoder_desc* desc, char* out, size_t out_bytes, size_t* needed_bytes);
+
 /* The manifest.pipelines array matching the table smelt_cuda_build_decoder writes for `desc`
  * and `batch`: names in index order, newline separated.  *needed_bytes receives the size of
  * the text including its terminator; out may be NULL to query it. */
@@ -281,8 +285,9 @@ SMELT_CUDA_API smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_des
  * The part of SmeltRuntime.init between a .smeltpkg directory and the first decoded token
  * (Sources/SmeltRuntime/SmeltRuntime.swift:668-998): manifest.json (pipelines, buffers.slots,
  * slotLayout, config.vocabSize, weights.entries: Sources/SmeltSchema/SmeltManifest.swift:26-98,
- * :806-817, :1649-1768), weights.bin, dispatches.bin.  Prefill tables, model.metallib, checksums
- * and prepared-prefix snapshots are not read. */
+ * :806-817, :1649-1768), weights.bin, dispatches.bin and, when present, prefill_dispatches.bin
+ * (SmeltRuntime.swift:842-853).  model.metallib, checksums, the verify tables and prepared-prefix
+ * snapshots are not read. */
 typedef struct {
     uint32_t context_capacity; /* positions every KV cache slot holds; 0 = the capacity the slots were compiled for */
     uint32_t context_limit;    /* 0 = context_capacity */
@@ -292,6 +297,8 @@ typedef struct {
     uint32_t vocab_size, hidden_size, num_layers, cache_seq_capacity;
     int32_t token_id_slot, position_slot, weights_slot, argmax_slot, logits_slot;
     uint64_t weights_bytes;
+    uint32_t n_prefill_records; /* records of prefill_dispatches.bin when the package has one and every kernel it names is bound; else 0 */
+    uint32_t _pad;
 } smelt_package_info;
 /* Host only (no device needed): parses and validates a package the way the loader does and
  * reports the first problem in err: manifest fields missing, a weight entry outside weights.bin
@@ -310,6 +317,10 @@ SMELT_CUDA_API smelt_status smelt_cuda_open_package(smelt_cuda_ctx* ctx, const c
 /* The decode table of the open package (owned by the context; valid until the next open or destroy):
  * pass it to smelt_cuda_decode_step / smelt_cuda_enqueue_decode / smelt_cuda_graph_build. */
 SMELT_CUDA_API smelt_status smelt_cuda_package_table(smelt_cuda_ctx* ctx, const smelt_dispatch_record** out_table, size_t* out_n);
+/* The prompt-chunk table of the open package for smelt_cuda_enqueue_prefill.  A package without
+ * prefill_dispatches.bin, or whose prefill table names a kernel that is not bound, still opens and decodes; this call
+ * then fails with the reason (SMELT_ERR_UNSUPPORTED / SMELT_ERR_UNKNOWN_PIPELINE) and the prompt goes through decode steps. */
+SMELT_CUDA_API smelt_status smelt_cuda_package_prefill_table(smelt_cuda_ctx* ctx, const smelt_dispatch_record** out_table, size_t* out_n);
 
 /* ── tensor parallelism (no counterpart in the reference, which is single-device) ──
  * One process per GPU.  Rank 0 creates an id, the caller ships it to the other ranks, every

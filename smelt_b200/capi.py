@@ -91,7 +91,8 @@ class PackageInfo(C.Structure):
     _fields_ = [("n_records", C.c_uint32), ("n_pipelines", C.c_uint32), ("n_pipelines_used", C.c_uint32), ("n_slots", C.c_uint32),
                 ("n_weight_entries", C.c_uint32), ("vocab_size", C.c_uint32), ("hidden_size", C.c_uint32), ("num_layers", C.c_uint32),
                 ("cache_seq_capacity", C.c_uint32), ("token_id_slot", C.c_int32), ("position_slot", C.c_int32), ("weights_slot", C.c_int32),
-                ("argmax_slot", C.c_int32), ("logits_slot", C.c_int32), ("weights_bytes", C.c_uint64)]
+                ("argmax_slot", C.c_int32), ("logits_slot", C.c_int32), ("weights_bytes", C.c_uint64),
+                ("n_prefill_records", C.c_uint32), ("_pad", C.c_uint32)]
 
 
 class KvSlot(C.Structure):

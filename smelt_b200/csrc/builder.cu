@@ -268,8 +268,8 @@ extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smel
 // start position are run-time constants, so one table serves every chunk up to max_chunk positions.
 enum PrefillSlot : int { kPfX0 = 2, kPfX1 = 3, kPfNorm = 4, kPfQ = 5, kPfK = 6, kPfV = 7, kPfAttn = 9, kPfFfn = 10 };
 
-extern "C" smelt_status smelt_cuda_build_prefill_table(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
-                                                       uint32_t max_chunk, smelt_dispatch_record* records, size_t* n_records) {
+static smelt_status build_prefill_impl(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers, uint32_t max_chunk,
+                                       smelt_dispatch_record* records, size_t* n_records, std::vector<std::string>* names) {
     if (!d || !layers || !n_records) return SMELT_ERR_BAD_ARGUMENT;
     if (d->layers <= 0 || d->layers > 100 || d->hidden <= 0 || d->inter <= 0 || d->n_q <= 0 || d->n_kv <= 0 || d->n_q % d->n_kv || d->head_dim <= 0 || d->vocab <= 0 ||
         max_chunk == 0 || d->tp_world > 1)
@@ -332,7 +332,30 @@ extern "C" smelt_status smelt_cuda_build_prefill_table(smelt_cuda_ctx* ctx, cons
         return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: record buffer too small");
     }
     *n_records = need;
+    if (names) {
+        names->assign(e.pipes.size(), std::string());
+        for (auto& kv : e.pipes) (*names)[kv.second - e.base] = kv.first;
+    }
     return e.status;
+}
+
+extern "C" smelt_status smelt_cuda_build_prefill_table(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
+                                                       uint32_t max_chunk, smelt_dispatch_record* records, size_t* n_records) {
+    return build_prefill_impl(ctx, d, layers, max_chunk, records, n_records, nullptr);
+}
+
+extern "C" smelt_status smelt_cuda_prefill_pipelines(const smelt_decoder_desc* d, char* out, size_t out_bytes, size_t* needed_bytes) {
+    if (!d || !needed_bytes) return SMELT_ERR_BAD_ARGUMENT;
+    std::vector<smelt_layer_ref> layers(d->layers > 0 && d->layers <= 100 ? d->layers : 1);
+    std::vector<std::string> names;
+    size_t n = 0;
+    smelt_status s = build_prefill_impl(nullptr, d, layers.data(), 1, nullptr, &n, &names);
+    if (s) return s;
+    std::string joined;
+    for (size_t i = 0; i < names.size(); ++i) joined += names[i] + "\n";
+    *needed_bytes = joined.size() + 1;
+    if (out && out_bytes >= joined.size() + 1) memcpy(out, joined.c_str(), joined.size() + 1);
+    return SMELT_OK;
 }
 
 extern "C" smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_desc* d, uint32_t batch, char* out, size_t out_bytes,

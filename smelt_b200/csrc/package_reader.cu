@@ -163,6 +163,10 @@ struct SlotSpec {
 };
 
 struct Package {
+    std::vector<smelt_dispatch_record> prefill_table;   // prefill_dispatches.bin, when present and runnable
+    std::vector<int> prefill_pipelines;                 // manifest indices its records name
+    std::string prefill_problem;                        // why the prompt-chunk table is not available (empty = it is)
+    smelt_status prefill_status = SMELT_ERR_UNSUPPORTED;
     std::vector<std::string> pipelines;
     std::vector<SlotSpec> slots;
     int token_id_slot = -1, position_slot = -1, weights_slot = -1, key_base = -1, val_base = -1;
@@ -292,6 +296,44 @@ smelt_status load_package(const std::string& dir, Package& pk, std::string& err)
             }
             pk.used_pipelines.push_back((int)i);
         }
+    // prefill_dispatches.bin is optional (SmeltRuntime.swift:842-853); a table this library cannot run does not
+    // stop the package from decoding
+    std::vector<uint8_t> praw;
+    if (!read_file(dir + "/prefill_dispatches.bin", praw)) {
+        pk.prefill_problem = "the package has no prefill_dispatches.bin";
+        return SMELT_OK;
+    }
+    if (praw.empty() || praw.size() % sizeof(smelt_dispatch_record) != 0) {
+        pk.prefill_problem = "prefill_dispatches.bin size " + std::to_string(praw.size()) + " is not a positive multiple of dispatch stride " + std::to_string(sizeof(smelt_dispatch_record));
+        pk.prefill_status = SMELT_ERR_BAD_ARGUMENT;
+        return SMELT_OK;
+    }
+    std::vector<smelt_dispatch_record> pt(praw.size() / sizeof(smelt_dispatch_record));
+    memcpy(pt.data(), praw.data(), praw.size());
+    std::vector<bool> pused(pk.pipelines.size(), false);
+    for (size_t i = 0; i < pt.size(); ++i) {
+        const smelt_dispatch_record& r = pt[i];
+        if (r.op_kind == SMELT_OP_SWAP) continue;
+        if (r.op_kind != SMELT_OP_DISPATCH || r.pipeline >= pk.pipelines.size()) {
+            pk.prefill_problem = "prefill_dispatches.bin record " + std::to_string(i) + ": unknown op kind or pipeline index";
+            pk.prefill_status = SMELT_ERR_BAD_ARGUMENT;
+            return SMELT_OK;
+        }
+        pused[r.pipeline] = true;
+    }
+    for (size_t i = 0; i < pused.size(); ++i)
+        if (pused[i]) {
+            Pipeline p;
+            if (!parse_pipeline(pk.pipelines[i].c_str(), &p)) {
+                pk.prefill_problem = "pipeline " + std::to_string(i) + " '" + pk.pipelines[i] + "' is used by prefill_dispatches.bin and is not an implemented kernel";
+                pk.prefill_status = SMELT_ERR_UNKNOWN_PIPELINE;
+                pk.prefill_pipelines.clear();
+                return SMELT_OK;
+            }
+            pk.prefill_pipelines.push_back((int)i);
+        }
+    pk.prefill_table.swap(pt);
+    pk.prefill_status = SMELT_OK;
     return SMELT_OK;
 }
 
@@ -308,6 +350,7 @@ void fill_info(const Package& pk, uint32_t capacity, smelt_package_info* info) {
     info->token_id_slot = pk.token_id_slot; info->position_slot = pk.position_slot; info->weights_slot = pk.weights_slot;
     info->argmax_slot = 17; info->logits_slot = 16;
     info->weights_bytes = pk.weights_file;
+    info->n_prefill_records = (uint32_t)pk.prefill_table.size();
 }
 
 void copy_err(const std::string& e, char* out, size_t n) {
@@ -321,6 +364,9 @@ void copy_err(const std::string& e, char* out, size_t n) {
 
 struct smelt_package_state {
     std::vector<smelt_dispatch_record> table;
+    std::vector<smelt_dispatch_record> prefill_table;
+    std::string prefill_problem;
+    smelt_status prefill_status = SMELT_ERR_UNSUPPORTED;
 };
 
 extern "C" {
@@ -371,6 +417,10 @@ smelt_status smelt_cuda_open_package(smelt_cuda_ctx* ctx, const char* package_di
         s = smelt_cuda_register_pipeline(ctx, idx, pk.pipelines[idx].c_str());
         if (s) return s;
     }
+    for (int idx : pk.prefill_pipelines) {
+        s = smelt_cuda_register_pipeline(ctx, idx, pk.pipelines[idx].c_str());
+        if (s) return s;
+    }
     smelt_cuda_runtime_config cfg = {};
     cfg.token_id_slot = pk.token_id_slot; cfg.position_slot = pk.position_slot; cfg.weights_slot = pk.weights_slot;
     cfg.argmax_slot = 17; cfg.cur_slot = 0; cfg.alt_slot = 1;
@@ -383,6 +433,9 @@ smelt_status smelt_cuda_open_package(smelt_cuda_ctx* ctx, const char* package_di
     if (!ctx->package) return fail(ctx, SMELT_ERR_ALLOC, "open_package: out of host memory");
     ctx->package->table.swap(pk.table);
     fill_info(pk, capacity, out_info);
+    ctx->package->prefill_table.swap(pk.prefill_table);
+    ctx->package->prefill_problem = pk.prefill_problem;
+    ctx->package->prefill_status = pk.prefill_status;
     if (out_info) out_info->n_records = (uint32_t)ctx->package->table.size();
     return SMELT_OK;
 }
@@ -392,6 +445,15 @@ smelt_status smelt_cuda_package_table(smelt_cuda_ctx* ctx, const smelt_dispatch_
     if (!ctx->package) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "no package is open");
     *out_table = ctx->package->table.data();
     *out_n = ctx->package->table.size();
+    return SMELT_OK;
+}
+
+smelt_status smelt_cuda_package_prefill_table(smelt_cuda_ctx* ctx, const smelt_dispatch_record** out_table, size_t* out_n) {
+    if (!ctx || !out_table || !out_n) return SMELT_ERR_BAD_ARGUMENT;
+    if (!ctx->package) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "no package is open");
+    if (ctx->package->prefill_status != SMELT_OK) return fail(ctx, ctx->package->prefill_status, ctx->package->prefill_problem);
+    *out_table = ctx->package->prefill_table.data();
+    *out_n = ctx->package->prefill_table.size();
     return SMELT_OK;
 }
 

@@ -348,12 +348,15 @@ class Snapshot:
 
 
 def write_package(path: str, cfg: DecoderConfig, image: np.ndarray, desc: capi.DecoderDesc, layers, capacity: int,
-                  fuse_residual: int = 0) -> None:
+                  fuse_residual: int = 0, prefill_chunk: int = 0) -> None:
     """Writes a ``.smeltpkg`` directory for a synthetic decoder in the reference's wire formats:
     ``manifest.json`` (top-level and slotLayout keys camelCase, weight entries and buffer slots
     snake_case, Sources/SmeltSchema/SmeltManifest.swift:26-98, :806-817, :1710-1768),
     ``weights.bin`` (the image) and ``dispatches.bin`` (the decode table as raw 360-byte records,
-    Sources/SmeltRuntime/SmeltRuntime.swift:6322-6350).  Stands in for the build-time compiler."""
+    Sources/SmeltRuntime/SmeltRuntime.swift:6322-6350) and, with ``prefill_chunk`` > 0,
+    ``prefill_dispatches.bin`` (the prompt-chunk table for chunks of up to that many positions, its
+    pipelines appended to the manifest's and its activation slots to the buffer plan).  Stands in
+    for the build-time compiler."""
     lib = capi.load()
     os.makedirs(path, exist_ok=True)
     desc.fuse_residual = int(fuse_residual)
@@ -400,6 +403,28 @@ def write_package(path: str, cfg: DecoderConfig, image: np.ndarray, desc: capi.D
     entries += [{"name": "embedding", "offset": int(desc.embedding), "size_bytes": cfg.vocab * H * 2, "shape": [cfg.vocab, H], "dtype": "fp16"},
                 {"name": "lm_head", "offset": int(desc.lm_head), "size_bytes": rows_head * H * 2, "shape": [rows_head, H], "dtype": "fp16"},
                 {"name": "final_norm", "offset": int(desc.final_norm), "size_bytes": H * 2, "shape": [H], "dtype": "fp16"}]
+    prefill_table = None
+    if prefill_chunk > 0:
+        T = int(prefill_chunk)
+        pn = C.c_size_t(0)
+        if lib.smelt_cuda_build_prefill_table(None, C.byref(desc), layers, T, None, C.byref(pn)) != 0:
+            raise capi.SmeltError(1, "build_prefill_table (count) failed")
+        prefill_table = (capi.DispatchRecord * pn.value)()
+        if lib.smelt_cuda_build_prefill_table(None, C.byref(desc), layers, T, prefill_table, C.byref(pn)) != 0:
+            raise capi.SmeltError(1, "build_prefill_table (dry run) failed")
+        lib.smelt_cuda_prefill_pipelines(C.byref(desc), None, C.c_size_t(0), C.byref(need))
+        pbuf = C.create_string_buffer(need.value)
+        lib.smelt_cuda_prefill_pipelines(C.byref(desc), pbuf, C.c_size_t(need.value), C.byref(need))
+        base = len(pipelines)
+        pipelines = pipelines + [p for p in pbuf.value.decode().split("\n") if p]
+        for r in prefill_table:  # the dry run numbers its pipelines from 0: they follow the decode table's in the manifest
+            if r.op_kind == 0:
+                r.pipeline += base
+        slots = [s_ if s_[0] != 33 else (33, "tokenId", T * 4, "int32", [T], "dynamic") for s_ in slots]
+        slots += [(2, "prefillHiddenA", T * H * 2, "fp16", [T, H], "activation"), (3, "prefillHiddenB", T * H * 2, "fp16", [T, H], "activation"),
+                  (4, "prefillNormOut", T * H * 2, "fp16", [T, H], "activation"), (5, "prefillQ", T * qd * 2, "fp16", [T, qd], "activation"),
+                  (6, "prefillK", T * kvd * 2, "fp16", [T, kvd], "activation"), (7, "prefillV", T * kvd * 2, "fp16", [T, kvd], "activation"),
+                  (9, "prefillAttnOut", T * qd * 2, "fp16", [T, qd], "activation"), (10, "prefillFfn", T * I * 2, "fp16", [T, I], "activation")]
     manifest = {
         "version": 1, "kind": "text-generation", "architecture": "text-generation", "modelName": "synthetic-affine-u4-decoder",
         "config": {"hiddenSize": H, "numLayers": cfg.layers, "vocabSize": cfg.vocab, "staticSeqCapacity": capacity, "ropeDim": D,
@@ -416,6 +441,9 @@ def write_package(path: str, cfg: DecoderConfig, image: np.ndarray, desc: capi.D
     np.asarray(image, np.uint8).tofile(os.path.join(path, "weights.bin"))
     with open(os.path.join(path, "dispatches.bin"), "wb") as f:
         f.write(bytes(table))
+    if prefill_table is not None:
+        with open(os.path.join(path, "prefill_dispatches.bin"), "wb") as f:
+            f.write(bytes(prefill_table))
 
 
 class PackageSession:
@@ -439,6 +467,21 @@ class PackageSession:
 
     def build_graph(self):
         self.ctx._check(self.ctx.lib.smelt_cuda_graph_build(self.ctx.h, self.table, self.n_records))
+
+    def prefill(self, tokens, start_pos: int = 0, chunk: int = 0) -> int:
+        """The prompt through the package's own prefill table (``smelt_cuda_package_prefill_table`` +
+        ``smelt_cuda_enqueue_prefill``), ``chunk`` positions at a time (0 = all at once); returns the argmax after
+        the last token.  Raises when the package has no runnable prefill table."""
+        table, n = C.c_void_p(), C.c_size_t(0)
+        self.ctx._check(self.ctx.lib.smelt_cuda_package_prefill_table(self.ctx.h, C.byref(table), C.byref(n)))
+        tokens = np.ascontiguousarray(np.asarray(tokens).reshape(-1), dtype=np.int32)
+        step = int(chunk) if chunk else len(tokens)
+        for t0 in range(0, len(tokens), step):
+            part = np.ascontiguousarray(tokens[t0:t0 + step])
+            self.ctx._check(self.ctx.lib.smelt_cuda_enqueue_prefill(self.ctx.h, table, n.value, part.ctypes.data_as(C.c_void_p), len(part), int(start_pos) + t0))
+        out = np.zeros(1, np.int32)
+        self.ctx._check(self.ctx.lib.smelt_cuda_read_slot(self.ctx.h, self.info.argmax_slot, 0, out.ctypes.data_as(C.c_void_p), 4))
+        return int(out[0])
 
     def graph_step(self, token: int, position: int) -> int:
         tok, out = np.array([token], np.int32), np.zeros(1, np.int32)

@@ -7,7 +7,7 @@ import os
 import numpy as np
 import pytest
 
-from smelt_b200 import capi, package
+from smelt_b200 import capi, package, synth
 
 CFG = package.DecoderConfig(layers=2, hidden=1024, inter=3072, n_q=8, n_kv=2, head_dim=128, vocab=2048)
 
@@ -139,5 +139,46 @@ def test_package_from_disk_decodes_the_oracle_tokens(tmp_path, oracle, fuse):
         assert ctx.device_error() == 0
         st = ctx.lib.smelt_cuda_decode_step(ctx.h, ses.table, ses.n_records, np.array([1], np.int32).ctypes.data_as(capi.C.c_void_p), 80, None)
         assert st == capi.OUT_OF_RANGE  # past the context the package was opened for
+    finally:
+        ctx.close()
+
+
+def test_inspect_counts_the_prefill_table(tmp_path):
+    d = str(tmp_path / "p.smeltpkg")
+    pkg = package.SyntheticPackage(CFG, 6)
+    image, desc, layers = package.build_image(pkg)
+    package.write_package(d, CFG, image, desc, layers, 48, prefill_chunk=16)
+    st, info, err = package.inspect_package(d)
+    assert st == 0, err
+    assert info.n_prefill_records == 5 + 9 * CFG.layers  # gather + nine records per layer + final norm, LM head, two argmax
+    # a prefill table that names a kernel this library does not bind leaves the package openable for decoding
+    m = json.load(open(os.path.join(d, "manifest.json")))
+    m["pipelines"][-1] = "fused_lut_matmul"
+    json.dump(m, open(os.path.join(d, "manifest.json"), "w"))
+    st, info, err = package.inspect_package(d)
+    assert st == 0 and info.n_prefill_records == 0 and info.n_records > 0
+
+
+@pytest.mark.gpu
+def test_package_prefill_table_then_decode(tmp_path, oracle):
+    """A package with prefill_dispatches.bin: the prompt in chunks through its own prompt-chunk table, then the
+    oracle's tokens from its decode table."""
+    d = str(tmp_path / "p.smeltpkg")
+    pkg = package.SyntheticPackage(CFG, 7)
+    image, desc, layers = package.build_image(pkg, keep_for_oracle=True)
+    package.write_package(d, CFG, image, desc, layers, 64, fuse_residual=3, prefill_chunk=16)
+    ref = oracle.model_from_package(pkg, 64)
+    prompt = synth.rng_for(7, "package prompt").integers(0, CFG.vocab, size=37).astype(np.int32)
+    want, runner, margins = ref.greedy_top2(prompt, 20)
+    ctx = capi.Context(0)
+    try:
+        ses = package.PackageSession(ctx, d)
+        assert ses.info.n_prefill_records > 0
+        got = [ses.prefill(prompt, 0, 16)]
+        for i in range(19):
+            got.append(ses.decode_step(int(want[i]), len(prompt) + i))
+        v = package.compare_greedy(np.array(got), want, runner, margins)
+        assert v["checked"] == 20 and not v["wrong"], v
+        assert ctx.device_error() == 0
     finally:
         ctx.close()
