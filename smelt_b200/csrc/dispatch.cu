@@ -703,6 +703,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, hidden);
             const int batch = batch_of(rec);
             NEED_BYTES(1, (size_t)batch * 4); NEED_BYTES(2, (size_t)batch * hidden * 2);
+            NEED_BYTES(0, (size_t)ctx->cfg.vocab_size * hidden * 2);  // token ids are checked against vocab_size when they are written
             in.launches += 1;
             return check_cuda(ctx, launch_embedding_gather(l, (const __half*)r.buf[0].ptr, (const int32_t*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)hidden, batch, 1), "embedding_gather");
         }
@@ -711,6 +712,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_U32(5, cols); NEED_U32(6, group);
             if (cols == 0 || group == 0 || cols % group || cols % 2) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "affine_embedding_gather: bad cols/group");
             NEED_BYTES(4, (size_t)cols * 2);
+            NEED_BYTES(0, (size_t)ctx->cfg.vocab_size * cols / 2); NEED_BYTES(1, (size_t)ctx->cfg.vocab_size * (cols / group) * 2); NEED_BYTES(2, (size_t)ctx->cfg.vocab_size * (cols / group) * 2);
             in.launches += 1;
             return check_cuda(ctx, launch_affine_embedding_gather(l, r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const int32_t*)r.buf[3].ptr, (__half*)r.buf[4].ptr, (int)cols, (int)group), "affine_embedding_gather");
         }
@@ -969,6 +971,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_U32(3, hidden); NEED_U32(4, batch);
             if (hidden == 0 || batch == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad shape");
             NEED_BYTES(1, (size_t)batch * 4); NEED_BYTES(2, (size_t)batch * hidden * 2);
+            NEED_BYTES(0, (size_t)ctx->cfg.vocab_size * hidden * 2);
             in.launches += 1;
             return check_cuda(ctx, launch_embedding_gather(l, (const __half*)r.buf[0].ptr, (const int32_t*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (int)hidden, (int)batch, 1), p.name.c_str());
         }
@@ -977,6 +980,7 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_U32(5, cols); NEED_U32(6, batch); NEED_U32(7, group);
             if (cols == 0 || group == 0 || cols % group || cols % 2 || batch == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad cols / group / batch");
             NEED_BYTES(3, (size_t)batch * 4); NEED_BYTES(4, (size_t)batch * cols * 2);
+            NEED_BYTES(0, (size_t)ctx->cfg.vocab_size * cols / 2); NEED_BYTES(1, (size_t)ctx->cfg.vocab_size * (cols / group) * 2); NEED_BYTES(2, (size_t)ctx->cfg.vocab_size * (cols / group) * 2);
             in.launches += 1;
             return check_cuda(ctx, launch_affine_embedding_gather(l, (const uint8_t*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const int32_t*)r.buf[3].ptr, (__half*)r.buf[4].ptr, (int)cols, (int)group, (int)batch), p.name.c_str());
         }
@@ -1036,6 +1040,8 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             const int batch = batch_of(rec);
             if (hidden == 0 || hidden % 128) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": hidden must be a multiple of 128");
             NEED_BYTES(2, (size_t)batch * 4); NEED_BYTES(3, (size_t)batch * hidden * 2);
+            // token ids are checked against vocab_size when they are written: the table must hold that many rows
+            NEED_BYTES(0, (size_t)ctx->cfg.vocab_size * hidden * p.bits / 8); NEED_BYTES(1, (size_t)ctx->cfg.vocab_size * (hidden / 128) * 2);
             in.launches += 1;
             return check_cuda(ctx, launch_signed_embedding_gather(l, p.bits, (const uint8_t*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const int32_t*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)hidden, batch), p.name.c_str());
         }
