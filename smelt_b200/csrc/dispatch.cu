@@ -49,6 +49,8 @@ bool parse_shape(std::string& rest, Pipeline* p) {
 //   4: 0 in, 1 scale out, 2 dim, 3 eps                              5: 0 in, 1 scale out
 //   6: 0 a, 1 b, 2 out (a + b), 3 scale out, 4 dim, 5 eps           7: 0 data (in place), 1 headDim, 2 eps (rows = grid.x)
 //   8: 0 data (in place)
+//   9: 0 qkv (in place), 1 headDim, 2 eps, 3 qkvDim, 4 qkHeads; grid (qkHeads, positions); dim < 0: the K heads, which follow the Q heads
+//  10: 0 qkv (in place) with headDim 128, qkvDim 6144, 16 heads fixed; grid (16, positions)
 struct RowNormName { const char* name; int dim, topology, value, scale, form; float eps; bool batched; };
 constexpr int kT4 = SMELT_ROW_NORM_TILES4, kQ2 = SMELT_ROW_NORM_QUADS2, kST = SMELT_ROW_NORM_STRIDED;
 const RowNormName kRowNorms[] = {
@@ -78,6 +80,11 @@ const RowNormName kRowNorms[] = {
     {"residual_add_rms_norm_scale_only_precise", 0, kST, 0, 0, 6, 0.0f, false},
     {"l2_normalize", 0, kST, 4, 1, 7, 0.0f, true},
     {"l2_normalize_d128", 128, kST, 4, 1, 8, 1e-6f, true},
+    // the Q / K heads of a prompt chunk's qkv rows (norms.metal:1192-1378)
+    {"l2_normalize_q_prefill", 0, kST, 4, 1, 9, 0.0f, true},
+    {"l2_normalize_k_prefill", -1, kST, 4, 1, 9, 0.0f, true},
+    {"l2_normalize_q_d128_c6144_h16_prefill", 128, kST, 4, 1, 10, 1e-6f, true},
+    {"l2_normalize_k_d128_c6144_h16_prefill", -128, kST, 4, 1, 10, 1e-6f, true},
 };
 constexpr int kRowNormCount = (int)(sizeof(kRowNorms) / sizeof(kRowNorms[0]));
 
@@ -900,10 +907,35 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
                 case 7: iy = 0; if (!host_u32(in, r, 1, &dim) || !host_u32(in, r, 2, &eps_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": headDim / eps constants are missing"); eps = as_f32(eps_bits); break;
                 default: iy = 0; break;
             }
-            const int rows = n.batched ? (int)rec.grid[0] : 1;
-            int tgs = n.form == 8 ? 128 : (n.dim == 256 ? 256 : (rec.threadgroup[0] ? (int)rec.threadgroup[0] : 256));
+            int rows = n.batched ? (int)rec.grid[0] : 1;
+            int group_rows = 0, group_stride = 0;
+            size_t base = 0;  // first value of the first row inside binding 0
+            if (n.form == 9 || n.form == 10) {
+                uint32_t qkv_dim = 6144, heads = 16;
+                iy = 0;
+                if (n.form == 9) {
+                    if (!host_u32(in, r, 1, &dim) || !host_u32(in, r, 2, &eps_bits) || !host_u32(in, r, 3, &qkv_dim) || !host_u32(in, r, 4, &heads))
+                        return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": headDim / eps / qkvDim / qkHeads constants are missing");
+                    eps = as_f32(eps_bits);
+                } else {
+                    dim = 128;
+                }
+                const bool k_heads = n.dim < 0;
+                const int positions = batch_of(rec);
+                if (heads == 0 || dim == 0 || (uint64_t)2 * heads * dim > qkv_dim || positions <= 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad head layout");
+                group_rows = (int)heads; group_stride = (int)qkv_dim; rows = (int)heads * positions;
+                base = k_heads ? (size_t)heads * dim : 0;
+            }
+            int tgs = (n.form == 8 || n.form == 10) ? 128 : (n.dim == 256 ? 256 : (rec.threadgroup[0] ? (int)rec.threadgroup[0] : 256));
             if (n.topology == kQ2) tgs = (int)dim / 8;
             if (rows <= 0 || dim == 0 || dim > 16384 || tgs < 32 || tgs % 32 || tgs > 1024 || (n.topology == kQ2 && dim % 256)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": bad rows, dim or threadgroup width");
+            if (group_rows) {
+                NEED_BUF(0);
+                NEED_BYTES(0, ((size_t)(rows / group_rows - 1) * group_stride + base + (size_t)group_rows * dim) * 2);
+                __half* data = (__half*)r.buf[0].ptr + base;
+                in.launches += 1;
+                return check_cuda(ctx, launch_row_norm(l, data, nullptr, nullptr, nullptr, nullptr, data, nullptr, rows, (int)dim, eps, n.topology, tgs, n.value, n.scale, group_rows, group_stride), p.name.c_str());
+            }
             const size_t row_bytes = (size_t)rows * dim * 2;
             const int bufs[] = {ix, ipre, ires, iy};
             for (int b : bufs)

@@ -137,6 +137,7 @@ struct RowNormArgs {
     __half* y; float* scale_out;
     int dim, tgs, topology, value, scale;
     float eps;
+    int group_rows, group_stride;  // rows come in groups of group_rows adjacent rows, group_stride values apart (0: all rows adjacent)
 };
 
 __global__ void __launch_bounds__(32) row_norm_kernel(const RowNormArgs a, DevDyn dyn) {
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(32) row_norm_kernel(const RowNormArgs a, DevDy
     pdl_wait();
     if (dyn_skip(dyn)) return;
     const int lane = threadIdx.x;
-    const size_t off = (size_t)blockIdx.x * a.dim;
+    const size_t off = a.group_rows ? (size_t)(blockIdx.x / a.group_rows) * a.group_stride + (size_t)(blockIdx.x % a.group_rows) * a.dim : (size_t)blockIdx.x * a.dim;
     const __half* x = a.x + off;
     auto val = [&](int i) -> float {
         if (a.pre) return __half2float(__hadd(x[i], a.pre[off + i]));
@@ -266,7 +267,7 @@ cudaError_t launch_head_norm(const Launch& l, int mode, const __half* x, const _
 }
 
 cudaError_t launch_row_norm(const Launch& l, const __half* x, const __half* pre, const __half* w, const __half* residual, const __half* scalar, __half* y,
-                            float* scale_out, int rows, int dim, float eps, int topology, int tgs, int value, int scale) {
+                            float* scale_out, int rows, int dim, float eps, int topology, int tgs, int value, int scale, int group_rows, int group_stride) {
     if (rows <= 0 || dim <= 0 || !x || topology < 0 || topology > 2 || value < 0 || value > 4 || scale < 0 || scale > 1) return cudaErrorInvalidValue;
     if (topology == 1) {
         if (dim % 256) return cudaErrorInvalidValue;
@@ -274,7 +275,8 @@ cudaError_t launch_row_norm(const Launch& l, const __half* x, const __half* pre,
     }
     if (tgs < 32 || tgs % 32 || tgs > 1024 || (value && !y) || (!value && !scale_out && !pre)) return cudaErrorInvalidValue;
     if ((value == 1 || value == 2 || value == 3) && !w) return cudaErrorInvalidValue;
-    RowNormArgs a = {x, pre, w, residual, scalar, y, scale_out, dim, tgs, topology, value, scale, eps};
+    if (group_rows < 0 || (group_rows > 0 && (group_stride < group_rows * dim || rows % group_rows))) return cudaErrorInvalidValue;
+    RowNormArgs a = {x, pre, w, residual, scalar, y, scale_out, dim, tgs, topology, value, scale, eps, group_rows, group_stride};
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cfg_launch(l, cfg, attr, dim3(rows), dim3(32));
@@ -336,7 +338,7 @@ smelt_status smelt_cuda_row_norm(smelt_cuda_ctx* ctx, const void* x, const void*
     if (topology != 1 && (threadgroup_width < 32 || threadgroup_width % 32 || threadgroup_width > 1024)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "row norm: threadgroup width a multiple of 32 up to 1024");
     if (scale_out && (reinterpret_cast<uintptr_t>(scale_out) & 3u)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "row norm: the scale output must be 4-byte aligned");
     return check_cuda(ctx, launch_row_norm(typed(ctx), (const __half*)x, (const __half*)pre, (const __half*)w, (const __half*)residual, (const __half*)scalar, (__half*)y,
-                                           (float*)scale_out, rows, dim, eps, topology, threadgroup_width, value, scale), "row norm");
+                                           (float*)scale_out, rows, dim, eps, topology, threadgroup_width, value, scale, 0, 0), "row norm");
 }
 
 }  // extern "C"

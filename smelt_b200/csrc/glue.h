@@ -37,7 +37,7 @@ cudaError_t launch_bitplane_fused_producer(const Launch& l, int front, const __h
 enum { kEwSilu = 0, kEwSigmoid, kEwSoftplus, kEwCopy, kEwScalarMul, kEwLogitCap, kEwMul, kEwSigmoidMul, kEwGeglu, kEwBiasAdd };
 enum { kHeadNormDirect = 0, kHeadNorm1pw = 1, kHeadNormNoScale = 2 };
 cudaError_t launch_elementwise(const Launch& l, int op, const __half* a, const __half* b, __half* y, int count, int batch, int b_stride, float scalar, const __half* scalar_dev);
-cudaError_t launch_row_norm(const Launch& l, const __half* x, const __half* pre, const __half* w, const __half* residual, const __half* scalar, __half* y, float* scale_out, int rows, int dim, float eps, int topology, int tgs, int value, int scale);
+cudaError_t launch_row_norm(const Launch& l, const __half* x, const __half* pre, const __half* w, const __half* residual, const __half* scalar, __half* y, float* scale_out, int rows, int dim, float eps, int topology, int tgs, int value, int scale, int group_rows = 0, int group_stride = 0);
 // prompt-chunk RoPE + KV write and causal attention (prefill.cu)
 cudaError_t launch_rope_kv_prefill(const Launch& l, __half* q, __half* k, const __half* v, const __half* cos_t, const __half* sin_t, __half* k_cache, __half* v_cache, int head_dim, int rope_dim, int q_heads, int kv_heads, uint32_t n_pos, uint32_t start_pos, uint32_t capacity, int layout, float base_log2, int math_mode, size_t table_stride);
 cudaError_t launch_attention_prefill(const Launch& l, const __half* q, const __half* k_cache, const __half* v_cache, __half* out, int n_q, int n_kv, int head_dim, uint32_t n_pos, uint32_t start_pos, uint32_t capacity, float scale, uint32_t window);

@@ -297,3 +297,41 @@ def test_row_norm_records_feed_the_norm_scale_view(ctx, oracle):
     assert np.array_equal(read(11, 2048), oracle.row_norm(x2048, w2048, topology=1, value=2)[0])
     assert np.array_equal(read(15, (3, 1536)), oracle.row_norm(x1536, w1536, topology=1, value=2, residual=r1536)[0])
     assert np.array_equal(read(16, (6, 128)), oracle.row_norm(qk, None, topology=2, value=4, tgs=128, scale=1)[0])
+
+
+@pytest.mark.gpu
+def test_l2_normalize_prefill_records(ctx, oracle):
+    """The Q and K heads of a prompt chunk's qkv rows normalised in place (norms.metal:1192-1378): the generic
+    forms with their constants and the d128 / c6144 / h16 specialisations."""
+    rng = np.random.default_rng(12)
+    cases = [("l2_normalize_q_prefill", 64, 4, 6, 64 * 14, False), ("l2_normalize_k_prefill", 64, 4, 6, 64 * 14, True),
+             ("l2_normalize_q_d128_c6144_h16_prefill", 128, 16, 3, 6144, False), ("l2_normalize_k_d128_c6144_h16_prefill", 128, 16, 3, 6144, True)]
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    f32 = lambda v: int(np.array([v], F).view(np.uint32)[0])
+    for i, (name, d, heads, positions, qkv_dim, k_heads) in enumerate(cases):
+        x = halves(rng, positions, qkv_dim)
+        ctx.call("alloc_slot", 2, C.c_size_t(x.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, 2, C.c_size_t(0), x.ctypes.data_as(C.c_void_p), C.c_size_t(x.nbytes)))
+        ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 70 + i, name.encode()))
+        r = capi.DispatchRecord()
+        generic = "d128" not in name
+        r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, 70 + i, 1, 4 if generic else 0
+        r.grid[0], r.grid[1], r.grid[2] = heads, positions, 1
+        r.threadgroup[0], r.threadgroup[1], r.threadgroup[2] = 64 if generic else 128, 1, 1
+        r.buf[0].slot, r.buf[0].binding_index = 2, 0
+        if generic:
+            for j, (binding, kind, value) in enumerate([(1, 0, d), (2, 1, f32(1e-6)), (3, 0, qkv_dim), (4, 0, heads)]):
+                r.con[j].kind, r.con[j].binding_index, r.con[j].value = kind, binding, value
+        tok = np.zeros(1, np.int32)
+        ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, (capi.DispatchRecord * 1)(r), 1, tok.ctypes.data_as(C.c_void_p), 0))
+        ctx.synchronize()
+        got = np.zeros_like(x)
+        ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, 2, C.c_size_t(0), got.ctypes.data_as(C.c_void_p), C.c_size_t(got.nbytes)))
+        want = x.copy()
+        first = heads * d if k_heads else 0
+        region = np.ascontiguousarray(x[:, first:first + heads * d]).reshape(positions * heads, d)
+        want[:, first:first + heads * d] = oracle.row_norm(region, None, topology=2, value=4, tgs=64 if generic else 128, scale=1)[0].reshape(positions, heads * d)
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), name
