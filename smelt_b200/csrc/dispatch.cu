@@ -289,7 +289,9 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
             {"deltanet_recurrence_mlx_prefill_d128_h32_qk16", PK_DELTANET_PREFILL, 128, 32, 16},
             {"deltanet_recurrence_mlx_prefill_d128_h48_qk16", PK_DELTANET_PREFILL, 128, 48, 16},
             {"conv1d_update_silu_c6144_k4_prefill", PK_CONV1D_SILU_PREFILL, 6144, 4, 0},
-            {"conv1d_update_silu_c6144_k4", PK_CONV1D_SILU, 6144, 4, 0},  // conv1d.metal:34-67: the taps' products are exact in fp32, so its fused multiply-adds equal the generic kernel
+            {"conv1d_update_silu_c6144_k4", PK_CONV1D_SILU, 6144, 4, 0},
+            // + l2_normalize_d128 on the 32 Q / K heads of the output (conv1d.metal:69-127; the reference asserts equality with the staged pair)
+            {"conv1d_update_silu_l2_qk_c6144_k4_d128_h16", PK_CONV1D_SILU, 6144, 4, 32},  // conv1d.metal:34-67: the taps' products are exact in fp32, so its fused multiply-adds equal the generic kernel
         };
         for (const Fixed& f : fixed)
             if (name == f.name) {
@@ -1195,7 +1197,12 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             if (channels == 0 || ksize == 0 || ksize > 8) return fail(ctx, SMELT_ERR_UNSUPPORTED, "conv1d_update_silu: kernel size in 1..8");
             NEED_BYTES(0, (size_t)channels * ksize * 2); NEED_BYTES(1, (size_t)channels * 2); NEED_BYTES(2, (size_t)channels * ksize * 2); NEED_BYTES(3, (size_t)channels * 2);
             in.launches += 1;
-            return check_cuda(ctx, launch_conv1d_update_silu(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)channels, (int)ksize), "conv1d_update_silu");
+            {
+                const smelt_status st = check_cuda(ctx, launch_conv1d_update_silu(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (__half*)r.buf[3].ptr, (int)channels, (int)ksize), p.name.c_str());
+                if (st || !(p.fixed_shape && p.n_kv > 0)) return st;
+            }
+            in.launches += 1;  // the fused name: its Q / K heads of 128, L2-normalised in place in the output
+            return check_cuda(ctx, launch_row_norm(l, (const __half*)r.buf[3].ptr, nullptr, nullptr, nullptr, nullptr, (__half*)r.buf[3].ptr, nullptr, p.n_kv, 128, 1e-6f, SMELT_ROW_NORM_STRIDED, 128, 4, 1), p.name.c_str());
         }
         case PK_RMS_SCALE_QK: {
             // norms.metal:1380-1386: 0 qkv (in place), 1 headDim, 2 eps, 3 qkvDim, 4 qkHeads; grid.y = rows of qkv.

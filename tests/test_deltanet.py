@@ -481,3 +481,41 @@ def test_deltanet_prefill_records(ctx, oracle):
     want = core.reshape(-1).astype(F)
     err = float(np.max(np.abs(got.astype(F) - want)) / np.sqrt(np.mean(want ** 2)))
     assert err < 5e-3, err
+
+
+@pytest.mark.gpu
+def test_fused_conv_l2_record_equals_the_staged_pair(ctx, oracle):
+    """conv1d_update_silu_l2_qk_c6144_k4_d128_h16 against conv1d_update_silu_c6144_k4 then l2_normalize_d128 on the 32
+    Q / K heads (the reference's own assertion, PrefillKernelTests.swift:5294-5364), in place as the emitter binds it."""
+    rng = np.random.default_rng(21)
+    c, k = 6144, 4
+    state = rng.standard_normal((c, k)).astype(np.float16)
+    new = rng.standard_normal(c).astype(np.float16)
+    w = (rng.standard_normal((c, k)) * 0.5).astype(np.float16)
+    for slot, t in {2: state, 3: new, 4: w}.items():
+        ctx.call("alloc_slot", slot, C.c_size_t(t.nbytes))
+        ctx._check(ctx.lib.smelt_cuda_write_slot(ctx.h, slot, C.c_size_t(0), t.ctypes.data_as(C.c_void_p), C.c_size_t(t.nbytes)))
+    cfg = capi.RuntimeConfig(0, 1, 2, 2, 0, 1, 64, 64, 16, 1)
+    for slot in (0, 1):
+        ctx.call("alloc_slot", slot, C.c_size_t(64))
+    ctx._check(ctx.lib.smelt_cuda_configure(ctx.h, C.byref(cfg)))
+    ctx._check(ctx.lib.smelt_cuda_register_pipeline(ctx.h, 80, b"conv1d_update_silu_l2_qk_c6144_k4_d128_h16"))
+    r = capi.DispatchRecord()
+    r.op_kind, r.pipeline, r.buffer_count, r.constant_count = 0, 80, 4, 0
+    r.grid[0], r.grid[1], r.grid[2] = 48, 1, 1
+    r.threadgroup[0] = 128
+    for j, (binding, slot) in enumerate([(0, 2), (1, 3), (2, 4), (3, 3)]):
+        r.buf[j].slot, r.buf[j].binding_index = slot, binding
+    tok = np.zeros(1, np.int32)
+    ctx._check(ctx.lib.smelt_cuda_enqueue_decode(ctx.h, (capi.DispatchRecord * 1)(r), 1, tok.ctypes.data_as(C.c_void_p), 0))
+    ctx.synchronize()
+    got = np.zeros(c, np.float16)
+    ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, 3, C.c_size_t(0), got.ctypes.data_as(C.c_void_p), C.c_size_t(got.nbytes)))
+    got_state = np.zeros((c, k), np.float16)
+    ctx._check(ctx.lib.smelt_cuda_read_slot(ctx.h, 2, C.c_size_t(0), got_state.ctypes.data_as(C.c_void_p), C.c_size_t(got_state.nbytes)))
+    want_state, act = oracle.conv1d_update_silu(state, new, w, c, k)
+    want = act.copy()
+    want[:32 * 128] = oracle.row_norm(act[:32 * 128].reshape(32, 128), None, topology=2, value=4, tgs=128, scale=1)[0].reshape(-1)
+    assert np.array_equal(got_state.view(np.uint16), want_state.reshape(c, k).view(np.uint16))
+    assert np.max(ulp_diff_f16(got, want)) <= 2  # expf of the two libraries inside the staged SiLU, carried through the norm
+    assert np.array_equal(got[32 * 128:].view(np.uint16) == act[32 * 128:].view(np.uint16), np.ones(c - 32 * 128, bool)) or np.max(ulp_diff_f16(got[32 * 128:], act[32 * 128:])) <= 1

@@ -19,7 +19,7 @@ EXPECTED_GAPS = {
     "attention_fused.metal": set(),
     "norms_gated_precise.metal": set(),
     "norms.metal": set(),
-    "conv1d.metal": {"conv1d_update_silu_l2_qk_c6144_k4_d128_h16"},
+    "conv1d.metal": set(),
     "prefill_recurrence.metal": {"deltanet_recurrence_prefill"},
     "signed_quant_precise.metal": set(),
 }
@@ -50,4 +50,4 @@ def test_affine_and_attention_families_do_not_shrink():
     bound = [n for n in affine if by["lut_matvec.metal"][n]]
     assert len(bound) == len(affine), sorted(set(affine) - set(bound))
     assert sum(by["attention.metal"].values()) >= 16
-    assert sum(sum(d.values()) for d in by.values()) >= 364
+    assert sum(sum(d.values()) for d in by.values()) >= 365
