@@ -263,6 +263,77 @@ __global__ void __launch_bounds__(256) bitplane_matvec_kernel(const uint8_t* __r
     }
 }
 
+// Prompt rows (signed_quant.metal:1346-1436, the batched_b4 / b8 / b16 tiles): a warp takes ROWS weight rows and BT
+// activation rows, reads each weight group once and walks the BT rows' planes against it.  Every (weight row,
+// activation row) pair adds the same terms in the same order as the matvec above, so the tile is bit-identical to
+// independent rows, which is what the reference asserts of its own tiles.  Binary weights, plain output.
+template <int PLANES, int ROWS, int BT>
+__global__ void __launch_bounds__(256) bitplane_matvec_tile_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ wscales,
+                                                                   const uint32_t* __restrict__ planes, const __half* __restrict__ ascales,
+                                                                   __half* out, int rows, int cols, int batch, DevDyn dyn) {
+    pdl_trigger();
+    pdl_wait();
+    if (dyn_skip(dyn)) return;
+    const int lane = threadIdx.x & 31;
+    const int row0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROWS;
+    if (row0 >= rows) return;
+    const int groups = cols / 128;
+    const size_t row_bytes = (size_t)cols / 8;
+    const int b0 = blockIdx.y * BT;
+    float acc[ROWS][BT];
+#pragma unroll
+    for (int t = 0; t < ROWS; ++t)
+#pragma unroll
+        for (int b = 0; b < BT; ++b) acc[t][b] = 0.0f;
+    for (int g = lane; g < groups; g += 32) {
+        uint4 w[ROWS];
+        float ws[ROWS];
+#pragma unroll
+        for (int t = 0; t < ROWS; ++t) {
+            const int row = row0 + t < rows ? row0 + t : rows - 1;  // a ragged last tile repeats its last row; the copy is not stored
+            w[t] = *reinterpret_cast<const uint4*>(codes + row * row_bytes + (size_t)g * 16);
+            ws[t] = __half2float(wscales[(size_t)row * groups + g]);
+        }
+#pragma unroll
+        for (int b = 0; b < BT; ++b) {
+            if (b0 + b >= batch) break;
+            const uint32_t* pb = planes + ((size_t)(b0 + b) * groups + g) * (PLANES * 4);
+            uint4 pl[PLANES];
+#pragma unroll
+            for (int p = 0; p < PLANES; ++p) pl[p] = *reinterpret_cast<const uint4*>(pb + p * 4);
+            const float as = __half2float(ascales[(size_t)(b0 + b) * groups + g]);
+            const uint4 sign = pl[PLANES - 1];
+            int active[PLANES - 1];
+#pragma unroll
+            for (int bit = 0; bit < PLANES - 1; ++bit) active[bit] = __popc(pl[bit].x) + __popc(pl[bit].y) + __popc(pl[bit].z) + __popc(pl[bit].w);
+#pragma unroll
+            for (int t = 0; t < ROWS; ++t) {
+                // agree = weight bit where the activation is positive, its complement where it is negative
+                const uint4 agree = make_uint4(w[t].x ^ sign.x, w[t].y ^ sign.y, w[t].z ^ sign.z, w[t].w ^ sign.w);
+                int dot = 0;
+#pragma unroll
+                for (int bit = 0; bit < PLANES - 1; ++bit) {
+                    const uint4 mag = pl[bit];
+                    const int ag = __popc(agree.x & mag.x) + __popc(agree.y & mag.y) + __popc(agree.z & mag.z) + __popc(agree.w & mag.w);
+                    dot += (2 * ag - active[bit]) << bit;
+                }
+                acc[t][b] = __fadd_rn(acc[t][b], __fmul_rn(__fmul_rn((float)dot, as), ws[t]));
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < ROWS; ++t)
+#pragma unroll
+        for (int b = 0; b < BT; ++b) acc[t][b] = simd_sum_lane0(acc[t][b]);
+    if (lane == 0) {
+#pragma unroll
+        for (int t = 0; t < ROWS; ++t)
+#pragma unroll
+            for (int b = 0; b < BT; ++b)
+                if (row0 + t < rows && b0 + b < batch) out[(size_t)(b0 + b) * rows + row0 + t] = __float2half_rn(acc[t][b]);
+    }
+}
+
 cudaError_t cfg_launch(const Launch& l, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block) {
     cfg = {};
     cfg.gridDim = grid;
@@ -300,8 +371,21 @@ cudaError_t launch_consumer_r(const Launch& l, const BitplaneArgs& a) {
 // l, l + 32, ... either way).  Short rows (up to 64 groups) of binary weights: four rows per warp
 // share the plane loads, which outweigh the 16 bytes of weights per group; long rows: one row per
 // warp and two groups in flight per lane (measured 13.2 against 22.0 us at 5120 x 17408).
+template <int PLANES>
+cudaError_t launch_consumer_tile(const Launch& l, const BitplaneArgs& a) {
+    constexpr int ROWS = 4, BT = 4;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    const int warps = (a.rows + ROWS - 1) / ROWS;
+    cfg_launch(l, cfg, attr, dim3((warps + 7) / 8, (a.batch + BT - 1) / BT), dim3(256));
+    auto k = bitplane_matvec_tile_kernel<PLANES, ROWS, BT>;
+    prefer_max_shared(k);
+    return cudaLaunchKernelEx(&cfg, k, a.codes, a.wscales, a.planes, a.ascales, a.out, a.rows, a.cols, a.batch, dev_dyn(l));
+}
+
 template <int PLANES, bool TERNARY, int MODE>
 cudaError_t launch_consumer_t(const Launch& l, const BitplaneArgs& a) {
+    if (!TERNARY && MODE == 0 && a.batch >= 2) return launch_consumer_tile<PLANES>(l, a);  // prompt rows: weights read once per four rows
     if (TERNARY) return launch_consumer_r<PLANES, true, MODE, 1, 1>(l, a);
     if (a.cols / 128 <= 64) return launch_consumer_r<PLANES, false, MODE, 4, 1>(l, a);
     return launch_consumer_r<PLANES, false, MODE, 1, 2>(l, a);

@@ -148,24 +148,25 @@ class Bench:
                 b.free()
         x.free(); y.free()
 
-    def bitplane(self, config, fmt, planes, rows, cols):
-        """The low-bit activation path: bit-plane view of x (producer) + popcount matvec (consumer), two launches."""
+    def bitplane(self, config, fmt, planes, rows, cols, batch=1):
+        """The low-bit activation path: bit-plane view of x (producer) + popcount matvec (consumer), two launches;
+        batch > 1: prompt rows through the batched view and the weight-sharing tile."""
         ctx = self.ctx
-        if self.only and self.only not in f"bitplane fmt{fmt} i{planes} {rows}x{cols}":
+        if self.only and self.only not in f"bitplane fmt{fmt} i{planes} {rows}x{cols} b{batch}":
             return
         maker, bpw = (synth.binary1, 1 / 8) if fmt == 1 else (synth.ternary2, 2 / 8)
         groups = cols // 128
-        alg = rows * cols * (bpw + 2 / 128) + cols * 2 + rows * 2 + 2 * (groups * planes * 16 + groups * 2)  # planes written once, read once
+        alg = rows * cols * (bpw + 2 / 128) + batch * (cols * 2 + rows * 2 + 2 * (groups * planes * 16 + groups * 2))  # planes written once, read once
         n = copies_for(alg)
         sets = self.dev_copies(maker(2, f"bp{fmt}{rows}", rows, cols), n)
-        x = ctx.to_device(synth.activations(2, "bpx", 1, cols))
-        pl, sc, y = ctx.alloc(groups * planes * 16), ctx.alloc(groups * 2), ctx.alloc(rows * 2)
+        x = ctx.to_device(synth.activations(2, "bpx", batch, cols))
+        pl, sc, y = ctx.alloc(batch * groups * planes * 16), ctx.alloc(batch * groups * 2), ctx.alloc(batch * rows * 2)
         def enqueue():
             for s in sets:
-                ctx.call("signed_activation_bitplanes", x, None, pl, sc, cols, planes, 1)
-                ctx.call("signed_bitplane_matvec", fmt, 0, *s, None, None, pl, sc, None, y, rows, cols, planes, 1)
+                ctx.call("signed_activation_bitplanes", x, None, pl, sc, cols, planes, batch)
+                ctx.call("signed_bitplane_matvec", fmt, 0, *s, None, None, pl, sc, None, y, rows, cols, planes, batch)
         name = ("signed_binary" if fmt == 1 else "signed_ternary") + f"_bitplane_i{planes}_matvec_g128 (+ view producer)"
-        self.run(config, name, f"{rows}x{cols}", 1, alg, n, enqueue)
+        self.run(config, name, f"{rows}x{cols}", batch, alg, n, enqueue)
         for s in sets:
             for b in s:
                 b.free()
@@ -284,6 +285,8 @@ def main():
         b.bitplane("config2", 1, 4, 5120, 17408)
         b.bitplane("config2", 2, 5, 17408, 5120)
         b.bitplane("config2", 2, 5, 5120, 17408)
+        b.bitplane("config2", 1, 4, 17408, 5120, batch=8)   # prompt rows: the weight-sharing tile
+        b.bitplane("config2", 1, 4, 5120, 17408, batch=8)
     if "3" in want:
         for (nq, nkv, d) in ((16, 4, 128), (8, 2, 256)):
             for ctx_len in ((1024, 32768) if args.quick else (1024, 4096, 16384, 32768)):
