@@ -261,6 +261,26 @@ typedef struct {
 SMELT_CUDA_API smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc,
                                                      const smelt_layer_ref* layers, uint32_t capacity, uint32_t batch,
                                                      smelt_dispatch_record* records, size_t* n_records);
+/* A hybrid decoder: layers whose token mixer is a DeltaNet (gated linear-attention) block instead of attention, as the
+ * reference's DeltaNetPlugin emits them (Sources/SmeltCompiler/DeltaNetPlugin.swift:60-420): input norm, the QKV / Z / A / B
+ * projections of the normed hidden state, conv1d_update_silu on the QKV row, rms_scale_qk, deltanet_recurrence_mlx_decode,
+ * rms_norm_gated with Z, the output projection + residual; then the same feed-forward half as an attention layer.
+ * kinds[l] = 0 attention (layers[l] complete), 1 DeltaNet (layers[l] supplies the norms and the feed-forward tensors,
+ * delta[l] the mixer's).  Per DeltaNet layer two state slots are allocated after the KV slots: the convolution taps
+ * [qkv_dim, conv_kernel] at 40 + 2 L + l and the recurrent matrix [value_heads, head_dim, head_dim] at 40 + 3 L + l
+ * (fp16, zero at start).  One GPU, batch 1; the norm + projection fusions apply to the feed-forward half only. */
+typedef struct {
+    int32_t value_heads, qk_heads, head_dim, conv_kernel;
+} smelt_delta_desc;
+typedef struct {
+    smelt_affine_ref qkv, z, a, b, out;                   /* [(2 qk_heads + value_heads) D, H], [value_heads D, H], [value_heads, H] x 2, [H, value_heads D] */
+    uint64_t conv_weight, a_log, dt_bias, norm_weight;    /* fp16 [qkv_dim, conv_kernel], [value_heads], [value_heads], [D] */
+} smelt_delta_ref;
+SMELT_CUDA_API smelt_status smelt_cuda_build_hybrid_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc,
+                                                            const smelt_layer_ref* layers, const smelt_delta_desc* delta_desc,
+                                                            const smelt_delta_ref* delta, const uint8_t* kinds, uint32_t capacity,
+                                                            smelt_dispatch_record* records, size_t* n_records);
+
 /* The prompt-chunk table of the decoder smelt_cuda_build_decoder built (same descriptor and layer references; one
  * GPU, batch 1), in the reference's prefill record shapes (Sources/SmeltCompiler/PrefillEmitter.swift): chunk length
  * and start position are run-time constants, so one table serves every chunk of up to max_chunk positions through

@@ -357,6 +357,22 @@ class Model:
         self._keep += arrs
         _check(lib().so_model_set_norms(self._m, layer, *[_p(a) for a in arrs]), "model_set_norms")
 
+    DELTA_WHICH = {"dqkv": 0, "dz": 1, "da": 2, "db": 3, "dout": 4}
+
+    def set_delta_geometry(self, value_heads: int, qk_heads: int, head_dim: int, conv_kernel: int):
+        _check(lib().so_model_set_delta_geometry(self._m, value_heads, qk_heads, head_dim, conv_kernel), "model_set_delta_geometry")
+
+    def set_delta_layer(self, layer: int, tensors: dict, conv_w, a_log, dt_bias, norm_w):
+        """Turns `layer` into a DeltaNet layer: its five projections (dqkv, dz, da, db, dout) and four small tensors."""
+        for name, idx in self.DELTA_WHICH.items():
+            w, s, b = tensors[name]
+            arrs = [_u8(w), _h(s), _h(b)]
+            self._keep += arrs
+            _check(lib().so_model_set_delta_affine(self._m, layer, idx, *[_p(a) for a in arrs]), "model_set_delta_affine")
+        arrs = [_h(conv_w), _h(a_log), _h(dt_bias), _h(norm_w)]
+        self._keep += arrs
+        _check(lib().so_model_set_delta_params(self._m, layer, *[_p(a) for a in arrs]), "model_set_delta_params")
+
     def reset(self):
         lib().so_model_reset_cache(self._m)
 
@@ -411,10 +427,17 @@ def model_from_package(pkg, capacity: int) -> Model:
     m = Model(c.as_dict(), capacity)
     emb, head, fin = pkg.tensors.get("globals") or (pkg.embedding(), pkg.lm_head(), pkg.norm_delta("final_norm"))
     m.set_globals(emb, head, fin)
+    delta_layers = tuple(getattr(c, "delta_layers", ()) or ())
+    if delta_layers:
+        m.set_delta_geometry(c.delta_value_heads, c.delta_qk_heads, c.delta_head_dim, c.conv_kernel)
     for l in range(c.layers):
         t = {name: pkg.tensors.get((l, name)) or pkg.layer_tensor(l, name) for name in Model.WHICH}
         norms = pkg.tensors.get((l, "norms")) or (pkg.norm_delta(f"layer{l}.input_norm"), pkg.norm_delta(f"layer{l}.post_norm"))
         m.set_layer(l, t, *norms)
+        if l in delta_layers:
+            dt = {name: pkg.tensors.get((l, name)) or pkg.delta_tensor(l, name) for name in Model.DELTA_WHICH}
+            small = pkg.tensors.get((l, "delta_small")) or pkg.delta_small(l)
+            m.set_delta_layer(l, dt, *small)
     return m
 
 

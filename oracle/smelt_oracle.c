@@ -937,6 +937,14 @@ SO_API int so_attention_decode_mlx_2pass(const uint16_t *q, const uint16_t *k_ca
     return SO_OK;
 }
 
+/* the DeltaNet kernels are restated further down */
+SO_API int so_conv1d_update_silu(uint16_t *state, const uint16_t *new_val, const uint16_t *weight, uint16_t *out, int channels, int kernel_size);
+SO_API int so_rms_scale_qk(uint16_t *qkv, int head_dim, float eps, int qkv_dim, int qk_heads, int batch);
+SO_API int so_deltanet_recurrence_decode(uint16_t *state, const uint16_t *qkv, const uint16_t *b_proj, const uint16_t *a_proj, const uint16_t *a_log,
+                                         const uint16_t *dt_bias, uint16_t *out, int head_dim, int value_heads, int qk_heads);
+SO_API int so_rms_norm_gated_tg(const uint16_t *input, const uint16_t *gate, const uint16_t *weight, uint16_t *out, int head_dim, float eps, int heads, int tgs);
+SO_API int so_rms_norm_gated_d128(const uint16_t *input, const uint16_t *gate, const uint16_t *weight, uint16_t *out, int heads);
+
 /* ───────────────────────── whole decoder ─────────────────────────
  * Structure: Sources/SmeltRuntime/Qwen3TTSTalker.swift:229-292 (forwardStep: norm → q/k/v →
  * RoPE → cache append → GQA attention → o → residual → norm → gate/up SwiGLU → down →
@@ -954,6 +962,11 @@ typedef struct {
 typedef struct {
     const uint16_t *input_norm, *post_norm; /* stored as weight-1 */
     so_affine_t q, k, v, o, gate, up, down;
+    /* a DeltaNet layer (kind 1) replaces q / k / v / o by these (Sources/SmeltCompiler/DeltaNetPlugin.swift:60-420) */
+    int kind;
+    so_affine_t dqkv, dz, da, db, dout;
+    const uint16_t *conv_w, *a_log, *dt_bias, *gnorm_w;
+    uint16_t *conv_state, *rec_state;
 } so_layer_t;
 
 typedef struct {
@@ -964,6 +977,7 @@ typedef struct {
     const uint16_t *final_norm; /* weight-1 */
     so_layer_t *layer;
     uint16_t **k_cache, **v_cache; /* per layer [n_kv, capacity, head_dim] */
+    int d_value_heads, d_qk_heads, d_head_dim, d_conv_kernel; /* linear-attention geometry of the DeltaNet layers */
 } so_model_t;
 
 SO_API so_model_t *so_model_create(int layers, int hidden, int inter, int n_q, int n_kv, int head_dim,
@@ -986,7 +1000,7 @@ SO_API so_model_t *so_model_create(int layers, int hidden, int inter, int n_q, i
 
 SO_API void so_model_destroy(so_model_t *m) {
     if (!m) return;
-    for (int l = 0; l < m->layers; ++l) { free(m->k_cache[l]); free(m->v_cache[l]); }
+    for (int l = 0; l < m->layers; ++l) { free(m->k_cache[l]); free(m->v_cache[l]); free(m->layer[l].conv_state); free(m->layer[l].rec_state); }
     free(m->k_cache); free(m->v_cache); free(m->layer); free(m);
 }
 
@@ -1010,9 +1024,41 @@ SO_API int so_model_set_norms(so_model_t *m, int layer, const uint16_t *input_no
     return SO_OK;
 }
 
+/* Hybrid models: the geometry of the DeltaNet layers, then per DeltaNet layer its five projections (which: 0 qkv,
+ * 1 z, 2 a, 3 b, 4 out) and its four small tensors.  Marking a layer allocates its zeroed states. */
+SO_API int so_model_set_delta_geometry(so_model_t *m, int value_heads, int qk_heads, int head_dim, int conv_kernel) {
+    if (value_heads <= 0 || qk_heads <= 0 || value_heads % qk_heads || head_dim <= 0 || head_dim % 32 || head_dim > 256 || conv_kernel <= 0 || conv_kernel > 8)
+        return SO_ERR_GEOMETRY;
+    m->d_value_heads = value_heads; m->d_qk_heads = qk_heads; m->d_head_dim = head_dim; m->d_conv_kernel = conv_kernel;
+    return SO_OK;
+}
+SO_API int so_model_set_delta_affine(so_model_t *m, int layer, int which, const uint8_t *w, const uint16_t *s, const uint16_t *b) {
+    if (layer < 0 || layer >= m->layers || which < 0 || which > 4 || !m->d_value_heads) return SO_ERR_GEOMETRY;
+    so_affine_t *t = &m->layer[layer].dqkv + which;
+    t->w = w; t->s = s; t->b = b;
+    return SO_OK;
+}
+SO_API int so_model_set_delta_params(so_model_t *m, int layer, const uint16_t *conv_w, const uint16_t *a_log, const uint16_t *dt_bias,
+                                     const uint16_t *norm_w) {
+    if (layer < 0 || layer >= m->layers || !m->d_value_heads) return SO_ERR_GEOMETRY;
+    so_layer_t *L = &m->layer[layer];
+    L->kind = 1; L->conv_w = conv_w; L->a_log = a_log; L->dt_bias = dt_bias; L->gnorm_w = norm_w;
+    const size_t dq = (size_t)(2 * m->d_qk_heads + m->d_value_heads) * m->d_head_dim;
+    free(L->conv_state); free(L->rec_state);
+    L->conv_state = (uint16_t *)calloc(dq * m->d_conv_kernel, 2);
+    L->rec_state = (uint16_t *)calloc((size_t)m->d_value_heads * m->d_head_dim * m->d_head_dim, 2);
+    return L->conv_state && L->rec_state ? SO_OK : SO_ERR_ALLOC;
+}
+
 SO_API void so_model_reset_cache(so_model_t *m) {
     size_t kv = (size_t)m->n_kv * m->capacity * m->head_dim;
-    for (int l = 0; l < m->layers; ++l) { memset(m->k_cache[l], 0, kv * 2); memset(m->v_cache[l], 0, kv * 2); }
+    for (int l = 0; l < m->layers; ++l) {
+        memset(m->k_cache[l], 0, kv * 2); memset(m->v_cache[l], 0, kv * 2);
+        if (m->layer[l].kind == 1) {
+            memset(m->layer[l].conv_state, 0, (size_t)(2 * m->d_qk_heads + m->d_value_heads) * m->d_head_dim * m->d_conv_kernel * 2);
+            memset(m->layer[l].rec_state, 0, (size_t)m->d_value_heads * m->d_head_dim * m->d_head_dim * 2);
+        }
+    }
 }
 
 /* Benchmark support: loads rows [0, n_positions) of one layer's K and V caches from
@@ -1034,12 +1080,15 @@ SO_API int so_model_decode_step(so_model_t *m, int32_t token, int position, uint
                                 int32_t *out_token) {
     if (token < 0 || token >= m->vocab || position < 0 || position >= m->capacity) return SO_ERR_GEOMETRY;
     int H = m->hidden, I = m->inter, D = m->head_dim, qd = m->n_q * D, kvd = m->n_kv * D, G = m->group;
-    size_t scratch = (size_t)H * 3 + qd * 2 + kvd * 2 + I;
+    const int DD = m->d_head_dim, Hv = m->d_value_heads, Hqk = m->d_qk_heads;
+    const int dq = (2 * Hqk + Hv) * DD, dv = Hv * DD;
+    size_t scratch = (size_t)H * 3 + qd * 2 + kvd * 2 + I + (size_t)dq + 2 * (size_t)dv + 2 * (size_t)Hv;
     uint16_t *buf = (uint16_t *)malloc(scratch * 2);
     uint16_t *logits = logits_out ? logits_out : (uint16_t *)malloc((size_t)m->vocab * 2);
     if (!buf || !logits) { free(buf); if (!logits_out) free(logits); return SO_ERR_ALLOC; }
     uint16_t *h = buf, *normed = h + H, *tmp = normed + H, *q = tmp + H, *attn = q + qd, *k = attn + qd,
              *v = k + kvd, *act = v + kvd;
+    uint16_t *dqkv = act + I, *dz = dqkv + dq, *dout = dz + dv, *da = dout + dv, *db = da + Hv;
     int rc = SO_OK;
     float base_log2 = log2f(m->rope_theta);
     float scale = 1.0f / sqrtf((float)D);
@@ -1047,6 +1096,27 @@ SO_API int so_model_decode_step(so_model_t *m, int32_t token, int position, uint
     for (int l = 0; l < m->layers && rc == SO_OK; ++l) {
         so_layer_t *L = &m->layer[l];
         rc = so_rms_norm_1pw(h, L->input_norm, H, m->eps, 1, normed);
+        if (!rc && L->kind == 1) {
+            /* DeltaNetPlugin.swift:60-420: QKV / Z / A / B projections, conv + SiLU in place, Q / K scaling, recurrence,
+             * gated norm with Z (the d128 form when the head is 128 wide and eps is 1e-6, else a threadgroup of
+             * min(head_dim, 256)), output projection + residual */
+            rc = so_affine_matvec(L->dqkv.w, L->dqkv.s, L->dqkv.b, normed, dq, H, G, 1, dqkv);
+            if (!rc) rc = so_affine_matvec(L->dz.w, L->dz.s, L->dz.b, normed, dv, H, G, 1, dz);
+            if (!rc) rc = so_affine_matvec(L->da.w, L->da.s, L->da.b, normed, Hv, H, G, 1, da);
+            if (!rc) rc = so_affine_matvec(L->db.w, L->db.s, L->db.b, normed, Hv, H, G, 1, db);
+            if (!rc) rc = so_conv1d_update_silu(L->conv_state, dqkv, L->conv_w, dqkv, dq, m->d_conv_kernel);
+            if (!rc) rc = so_rms_scale_qk(dqkv, DD, 1e-6f, dq, Hqk, 1);
+            if (!rc) rc = so_deltanet_recurrence_decode(L->rec_state, dqkv, db, da, L->a_log, L->dt_bias, dout, DD, Hv, Hqk);
+            if (!rc) rc = (DD == 128 && m->eps == 1e-6f) ? so_rms_norm_gated_d128(dout, dz, L->gnorm_w, dout, Hv)
+                                                         : so_rms_norm_gated_tg(dout, dz, L->gnorm_w, dout, DD, m->eps, Hv, DD < 256 ? DD : 256);
+            if (!rc) rc = so_affine_matvec(L->dout.w, L->dout.s, L->dout.b, dout, H, dv, G, 1, tmp);
+            if (!rc) so_elementwise_add(h, tmp, H, h);
+            if (!rc) rc = so_rms_norm_1pw(h, L->post_norm, H, m->eps, 1, normed);
+            if (!rc) rc = so_affine_gate_up_swiglu(L->gate.w, L->gate.s, L->gate.b, L->up.w, L->up.s, L->up.b, normed, I, H, G, 1, 0, act);
+            if (!rc) rc = so_affine_matvec(L->down.w, L->down.s, L->down.b, act, H, I, G, 1, tmp);
+            if (!rc) so_elementwise_add(h, tmp, H, h);
+            continue;
+        }
         if (!rc) rc = so_affine_matvec(L->q.w, L->q.s, L->q.b, normed, qd, H, G, 1, q);
         if (!rc) rc = so_affine_matvec(L->k.w, L->k.s, L->k.b, normed, kvd, H, G, 1, k);
         if (!rc) rc = so_affine_matvec(L->v.w, L->v.s, L->v.b, normed, kvd, H, G, 1, v);

@@ -83,6 +83,17 @@ class DecoderDesc(C.Structure):
                 ("fuse_residual", C.c_int32)]
 
 
+class DeltaDesc(C.Structure):
+    """``smelt_delta_desc``: the linear-attention geometry of a hybrid decoder's DeltaNet layers."""
+    _fields_ = [("value_heads", C.c_int32), ("qk_heads", C.c_int32), ("head_dim", C.c_int32), ("conv_kernel", C.c_int32)]
+
+
+class DeltaRef(C.Structure):
+    """``smelt_delta_ref``: one DeltaNet layer's mixer tensors inside the weights image."""
+    _fields_ = [("qkv", AffineRef), ("z", AffineRef), ("a", AffineRef), ("b", AffineRef), ("out", AffineRef),
+                ("conv_weight", C.c_uint64), ("a_log", C.c_uint64), ("dt_bias", C.c_uint64), ("norm_weight", C.c_uint64)]
+
+
 class PackageOptions(C.Structure):
     _fields_ = [("context_capacity", C.c_uint32), ("context_limit", C.c_uint32)]
 

@@ -92,10 +92,23 @@ std::string shaped(const char* base, int cols, int rows, int group, bool batched
 
 }  // namespace
 
+struct Hybrid {
+    const smelt_delta_desc* dd;
+    const smelt_delta_ref* refs;
+    const uint8_t* kinds;
+};
+enum DeltaSlot : int { kDeltaQkv = 24, kDeltaZ = 25, kDeltaA = 26, kDeltaB = 27, kDeltaOut = 28 };
+
 static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
                                        uint32_t capacity, uint32_t batch, smelt_dispatch_record* records,
-                                       size_t* n_records, std::vector<std::string>* names) {
+                                       size_t* n_records, std::vector<std::string>* names, const Hybrid* hy = nullptr) {
     if (!d || !layers || !n_records) return SMELT_ERR_BAD_ARGUMENT;
+    if (hy) {
+        const smelt_delta_desc* dd = hy->dd;
+        if (!dd || !hy->refs || !hy->kinds || dd->value_heads <= 0 || dd->qk_heads <= 0 || dd->value_heads % dd->qk_heads || dd->head_dim <= 0 || dd->head_dim % 32 ||
+            dd->head_dim > 256 || dd->conv_kernel <= 0 || dd->conv_kernel > 8 || batch != 1 || d->tp_world > 1)
+            return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_hybrid_decoder: bad linear-attention geometry (one GPU, batch 1)");
+    }
     if (d->layers <= 0 || d->hidden <= 0 || d->inter <= 0 || d->n_q <= 0 || d->n_kv <= 0 || d->n_q % d->n_kv || d->head_dim <= 0 ||
         d->vocab <= 0 || batch == 0 || batch > 64 || capacity == 0 || d->layers > 100)
         return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_decoder: bad model description");
@@ -131,8 +144,26 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
         }
         const size_t kv_bytes = (size_t)B * d->n_kv * capacity * D * 2;  // heads * capacity * headDim * 2 per sequence
         for (int l = 0; l < 2 * L; ++l) {
+            if (hy && hy->kinds[l % L]) continue;  // a DeltaNet layer keeps no KV cache
             smelt_status s = smelt_cuda_alloc_slot(ctx, kKvBase + l, kv_bytes);
             if (s) return s;
+        }
+        if (hy) {
+            const smelt_delta_desc* dd = hy->dd;
+            const size_t dq = (size_t)(2 * dd->qk_heads + dd->value_heads) * dd->head_dim, dv = (size_t)dd->value_heads * dd->head_dim;
+            if (kKvBase + 4 * L > (int)ctx->slots.size()) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_hybrid_decoder: too many layers for the slot table");
+            struct { int slot; size_t bytes; } dplan[] = {{kDeltaQkv, dq * 2}, {kDeltaZ, dv * 2}, {kDeltaA, (size_t)dd->value_heads * 2 < 16 ? 16 : (size_t)dd->value_heads * 2},
+                                                          {kDeltaB, (size_t)dd->value_heads * 2 < 16 ? 16 : (size_t)dd->value_heads * 2}, {kDeltaOut, dv * 2}};
+            for (auto& p : dplan) {
+                smelt_status s = smelt_cuda_alloc_slot(ctx, p.slot, p.bytes);
+                if (s) return s;
+            }
+            for (int l = 0; l < L; ++l)
+                if (hy->kinds[l]) {
+                    smelt_status s = smelt_cuda_alloc_slot(ctx, kKvBase + 2 * L + l, dq * dd->conv_kernel * 2);
+                    if (!s) s = smelt_cuda_alloc_slot(ctx, kKvBase + 3 * L + l, (size_t)dd->value_heads * dd->head_dim * dd->head_dim * 2);
+                    if (s) return s;
+                }
         }
         smelt_cuda_runtime_config cfg = {};
         cfg.token_id_slot = kTokenId; cfg.position_slot = kPosition; cfg.weights_slot = kWeights; cfg.argmax_slot = kArgmax;
@@ -157,6 +188,38 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
     for (int l = 0; l < L; ++l) {
         const smelt_layer_ref& w = layers[l];
         const int kslot = kKvBase + l, vslot = kKvBase + L + l;
+        const bool is_delta = hy && hy->kinds[l];
+        if (is_delta) {
+            // DeltaNetPlugin.swift:60-420: projections of the normed hidden state, convolution, Q / K scaling, recurrence, gated norm
+            const smelt_delta_desc* dd = hy->dd;
+            const smelt_delta_ref& x = hy->refs[l];
+            const int DD = dd->head_dim, Hv = dd->value_heads, Hqk = dd->qk_heads;
+            const int dq = (2 * Hqk + Hv) * DD, dv = Hv * DD;
+            const int conv_slot = kKvBase + 2 * L + l, rec_slot = kKvBase + 3 * L + l;
+            Rec(e, "rms_norm_1pw", 1).buf(0, SMELT_SLOT_CUR).buf(1, kWeights, w.input_norm).buf(2, kNormOut).u32(3, H).f32(4, d->eps);
+            { Rec r(e, matvec_name(H, dq), (dq + 7) / 8); r.affine(0, x.qkv).buf(3, kNormOut).buf(4, kDeltaQkv); count_const(r, 5, dq); }
+            { Rec r(e, matvec_name(H, dv), (dv + 7) / 8); r.affine(0, x.z).buf(3, kNormOut).buf(4, kDeltaZ); count_const(r, 5, dv); }
+            { Rec r(e, matvec_name(H, Hv), (Hv + 7) / 8); r.affine(0, x.a).buf(3, kNormOut).buf(4, kDeltaA); count_const(r, 5, Hv); }
+            { Rec r(e, matvec_name(H, Hv), (Hv + 7) / 8); r.affine(0, x.b).buf(3, kNormOut).buf(4, kDeltaB); count_const(r, 5, Hv); }
+            Rec(e, "conv1d_update_silu", (dq + 255) / 256).tg(256).buf(0, conv_slot).buf(1, kDeltaQkv).buf(2, kWeights, x.conv_weight).buf(3, kDeltaQkv)
+                .u32(4, dq).u32(5, dd->conv_kernel);
+            Rec(e, "rms_scale_qk", 2 * Hqk).tg(32u * (uint32_t)((DD + 127) / 128)).buf(0, kDeltaQkv).u32(1, DD).f32(2, 1e-6f).u32(3, dq).u32(4, Hqk);
+            Rec(e, "deltanet_recurrence_mlx_decode", 32, DD).tg(32).buf(0, rec_slot).buf(1, kDeltaQkv).buf(2, kDeltaB).buf(3, kDeltaA).buf(4, kWeights, x.a_log)
+                .buf(5, kWeights, x.dt_bias).buf(6, kDeltaOut).u32(7, DD).f32(8, 1.0f / sqrtf((float)DD)).u32(9, Hv).u32(10, Hqk);
+            if (DD == 128 && d->eps == 1e-6f)
+                Rec(e, "rms_norm_gated_d128", Hv).tg(32).buf(0, kDeltaOut).buf(1, kDeltaZ).buf(2, kWeights, x.norm_weight).buf(3, kDeltaOut);
+            else
+                Rec(e, "rms_norm_gated", Hv).tg((uint32_t)(DD < 256 ? DD : 256)).buf(0, kDeltaOut).buf(1, kDeltaZ).buf(2, kWeights, x.norm_weight).buf(3, kDeltaOut)
+                    .u32(4, DD).f32(5, d->eps);
+            if (fuse) {
+                Rec r(e, "fused_affine_matvec_add:" + std::to_string(dv) + ":" + std::to_string(G), (H + 7) / 8);
+                r.affine(0, x.out).buf(3, kDeltaOut).buf(4, SMELT_SLOT_ALT).buf(5, SMELT_SLOT_CUR);
+                count_const(r, 6, H);
+            } else {
+                { Rec r(e, matvec_name(dv, H), (H + 7) / 8); r.affine(0, x.out).buf(3, kDeltaOut).buf(4, kNormOut); count_const(r, 5, H); }
+                Rec(e, "elementwise_add", (H + 63) / 64).buf(0, SMELT_SLOT_CUR).buf(1, kNormOut).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)H);
+            }
+        } else {
         if (fuse2) {
             Rec r(e, "smelt_rmsnorm_affine_qkv:" + std::to_string(H) + ":64", ((qd + 2 * kvd) + 15) / 16);
             r.affine(0, w.q).affine(3, w.k).affine(6, w.v).buf(9, SMELT_SLOT_CUR).buf(10, kWeights, w.input_norm)
@@ -204,6 +267,7 @@ static smelt_status build_decoder_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
             Rec(e, "elementwise_add", (B * H + 63) / 64).buf(0, SMELT_SLOT_CUR).buf(1, kNormOut).buf(2, SMELT_SLOT_ALT).u32(3, (uint32_t)(B * H));
             }
         }
+        }  // attention mixer
         e.swap();
         // post-attention norm + FFN (TopLevelEmitter.swift:1021-1322 emitSwiGLU)
         if (fuse2) {
@@ -356,6 +420,13 @@ extern "C" smelt_status smelt_cuda_prefill_pipelines(const smelt_decoder_desc* d
     *needed_bytes = joined.size() + 1;
     if (out && out_bytes >= joined.size() + 1) memcpy(out, joined.c_str(), joined.size() + 1);
     return SMELT_OK;
+}
+
+extern "C" smelt_status smelt_cuda_build_hybrid_decoder(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
+                                                        const smelt_delta_desc* delta_desc, const smelt_delta_ref* delta, const uint8_t* kinds,
+                                                        uint32_t capacity, smelt_dispatch_record* records, size_t* n_records) {
+    const Hybrid hy{delta_desc, delta, kinds};
+    return build_decoder_impl(ctx, d, layers, capacity, 1, records, n_records, nullptr, &hy);
 }
 
 extern "C" smelt_status smelt_cuda_decoder_pipelines(const smelt_decoder_desc* d, uint32_t batch, char* out, size_t out_bytes,

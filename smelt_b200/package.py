@@ -66,6 +66,12 @@ class DecoderConfig:
     group: int = 64
     eps: float = 1e-6
     rope_theta: float = 1e6
+    # hybrid decoders: the layers whose token mixer is a DeltaNet block, and that block's geometry
+    delta_layers: tuple = ()
+    delta_value_heads: int = 0
+    delta_qk_heads: int = 0
+    delta_head_dim: int = 0
+    conv_kernel: int = 4
 
     def as_dict(self):
         return dict(self.__dict__)
@@ -89,6 +95,26 @@ class SyntheticPackage:
                   "down": (c.hidden, c.inter)}
         rows, cols = shapes[name]
         return synth.affine_u4_model(self.seed, f"layer{layer}.{name}", rows, cols, c.group)
+
+    def delta_tensor(self, layer: int, name: str):
+        """(packed, scales, biases) of one DeltaNet projection: dqkv, dz, da, db, dout."""
+        c = self.cfg
+        dq, dv = (2 * c.delta_qk_heads + c.delta_value_heads) * c.delta_head_dim, c.delta_value_heads * c.delta_head_dim
+        shapes = {"dqkv": (dq, c.hidden), "dz": (dv, c.hidden), "da": (c.delta_value_heads, c.hidden), "db": (c.delta_value_heads, c.hidden),
+                  "dout": (c.hidden, dv)}
+        rows, cols = shapes[name]
+        return synth.affine_u4_model(self.seed, f"layer{layer}.{name}", rows, cols, c.group)
+
+    def delta_small(self, layer: int):
+        """(conv weight [qkv_dim, K], A_log [Hv], dt_bias [Hv], gated-norm weight [D]) of a DeltaNet layer."""
+        c = self.cfg
+        g = synth.rng_for(self.seed, f"layer{layer}.delta_small")
+        dq = (2 * c.delta_qk_heads + c.delta_value_heads) * c.delta_head_dim
+        conv_w = (g.standard_normal((dq, c.conv_kernel)) * 0.5).astype(np.float16)
+        a_log = g.uniform(-2.0, 0.5, c.delta_value_heads).astype(np.float16)
+        dt_bias = g.uniform(-0.5, 0.5, c.delta_value_heads).astype(np.float16)
+        norm_w = (1.0 + 0.1 * g.standard_normal(c.delta_head_dim)).astype(np.float16)
+        return conv_w, a_log, dt_bias, norm_w
 
     def norm_delta(self, name: str) -> np.ndarray:
         """Stored norm weight (w - 1): weight == 1 plus small seeded noise, so the stored tensor is near zero."""
@@ -162,21 +188,79 @@ def build_image(pkg: SyntheticPackage, tp_rank: int = 0, tp_world: int = 1, keep
     return img.tobytes(), desc, layers
 
 
+@dataclass
+class HybridRefs:
+    """What ``smelt_cuda_build_hybrid_decoder`` needs beside the plain decoder's description."""
+    desc: "capi.DeltaDesc"
+    refs: object     # (capi.DeltaRef * layers)
+    kinds: object    # (c_uint8 * layers): 1 = DeltaNet layer
+
+
+def build_hybrid_image(pkg: SyntheticPackage, keep_for_oracle: bool = False):
+    """``build_image`` for a hybrid decoder: every layer's norms and feed-forward tensors, attention tensors for the
+    attention layers, the DeltaNet mixer's tensors for ``cfg.delta_layers``.  Returns (image, desc, layers, HybridRefs)."""
+    c = pkg.cfg
+    img = WeightsImage()
+    layers = (capi.LayerRef * c.layers)()
+    refs = (capi.DeltaRef * c.layers)()
+    kinds = (C.c_uint8 * c.layers)()
+    keep = pkg.tensors if keep_for_oracle else None
+    for l in range(c.layers):
+        ref = layers[l]
+        is_delta = l in c.delta_layers
+        for name in ("q", "k", "v", "o", "gate", "up", "down"):
+            t = pkg.layer_tensor(l, name)
+            if keep is not None:
+                keep[(l, name)] = t
+            if is_delta and name in ("q", "k", "v", "o"):
+                continue  # the mixer of this layer is the DeltaNet block
+            setattr(ref, name, img.add_affine(*t))
+        n_in, n_post = pkg.norm_delta(f"layer{l}.input_norm"), pkg.norm_delta(f"layer{l}.post_norm")
+        if keep is not None:
+            keep[(l, "norms")] = (n_in, n_post)
+        ref.input_norm, ref.post_norm = img.add(n_in), img.add(n_post)
+        if is_delta:
+            kinds[l] = 1
+            for name, field_ in (("dqkv", "qkv"), ("dz", "z"), ("da", "a"), ("db", "b"), ("dout", "out")):
+                t = pkg.delta_tensor(l, name)
+                if keep is not None:
+                    keep[(l, name)] = t
+                setattr(refs[l], field_, img.add_affine(*t))
+            small = pkg.delta_small(l)
+            if keep is not None:
+                keep[(l, "delta_small")] = small
+            refs[l].conv_weight, refs[l].a_log, refs[l].dt_bias, refs[l].norm_weight = (img.add(a) for a in small)
+    emb, head, fin = pkg.embedding(), pkg.lm_head(), pkg.norm_delta("final_norm")
+    if keep is not None:
+        keep["globals"] = (emb, head, fin)
+    desc = capi.DecoderDesc(layers=c.layers, hidden=c.hidden, inter=c.inter, n_q=c.n_q, n_kv=c.n_kv, head_dim=c.head_dim, vocab=c.vocab,
+                            group=c.group, eps=c.eps, rope_theta=c.rope_theta, embedding=img.add(emb), lm_head=img.add(head),
+                            final_norm=img.add(fin), tp_world=1, tp_rank=0, fuse_residual=0)
+    ddesc = capi.DeltaDesc(c.delta_value_heads, c.delta_qk_heads, c.delta_head_dim, c.conv_kernel)
+    return img.tobytes(), desc, layers, HybridRefs(ddesc, refs, kinds)
+
+
 class Decoder:
     """Drives the C ABI the way ``SmeltRuntime`` does: upload weights, build the record table,
     then ``decode_step`` per token or replay a captured graph."""
 
     def __init__(self, ctx: capi.Context, image: np.ndarray, desc: capi.DecoderDesc, layers, capacity: int, batch: int = 1,
-                 fuse_residual: int = 0):
+                 fuse_residual: int = 0, hybrid: "HybridRefs | None" = None):
         self.ctx, self.desc, self.layers, self.capacity, self.batch = ctx, desc, layers, capacity, batch
+        self.hybrid = hybrid
         desc.fuse_residual = int(fuse_residual)
         ctx.call("upload_weights", WEIGHTS_SLOT, image, C.c_size_t(image.nbytes))
         n = C.c_size_t(0)
-        st = ctx.lib.smelt_cuda_build_decoder(None, C.byref(desc), layers, capacity, batch, None, C.byref(n))
+        if hybrid is not None:
+            build = lambda h, table: ctx.lib.smelt_cuda_build_hybrid_decoder(h, C.byref(desc), layers, C.byref(hybrid.desc), hybrid.refs, hybrid.kinds,
+                                                                             capacity, table, C.byref(n))
+        else:
+            build = lambda h, table: ctx.lib.smelt_cuda_build_decoder(h, C.byref(desc), layers, capacity, batch, table, C.byref(n))
+        st = build(None, None)
         if st != 0:
             raise capi.SmeltError(st, "build_decoder (count) failed")
         self.table = (capi.DispatchRecord * n.value)()
-        ctx._check(ctx.lib.smelt_cuda_build_decoder(ctx.h, C.byref(desc), layers, capacity, batch, self.table, C.byref(n)))
+        ctx._check(build(ctx.h, self.table))
         self.n_records = n.value
         self.graph_ready = False
 
@@ -239,24 +323,40 @@ class Decoder:
         return int(out[0])
 
     def reset_cache(self):
-        for l in range(2 * self.desc.layers):
-            self.ctx.call("zero_slot", KV_BASE_SLOT + l)
+        L = self.desc.layers
+        for l in range(2 * L):
+            if self.hybrid is None or not self.hybrid.kinds[l % L]:
+                self.ctx.call("zero_slot", KV_BASE_SLOT + l)
+        if self.hybrid is not None:  # the DeltaNet layers' convolution taps and recurrent matrices
+            for l in range(L):
+                if self.hybrid.kinds[l]:
+                    self.ctx.call("zero_slot", KV_BASE_SLOT + 2 * L + l)
+                    self.ctx.call("zero_slot", KV_BASE_SLOT + 3 * L + l)
 
     # ── prompt-state snapshots (SmeltRuntime.captureDevicePromptSnapshot / restore…, SmeltRuntime.swift:1385-1553) ──
     def kv_slots(self):
         """The K and V cache slots of every layer as ``smelt_cuda_kv_slot`` records."""
         rows = (self.desc.n_kv // max(1, self.desc.tp_world)) * self.batch
-        n = 2 * self.desc.layers
-        arr = (capi.KvSlot * n)()
-        for l in range(n):
-            arr[l] = capi.KvSlot(KV_BASE_SLOT + l, rows, self.desc.head_dim)
+        L = self.desc.layers
+        which = [l for l in range(2 * L) if self.hybrid is None or not self.hybrid.kinds[l % L]]
+        arr = (capi.KvSlot * len(which))()
+        for i, l in enumerate(which):
+            arr[i] = capi.KvSlot(KV_BASE_SLOT + l, rows, self.desc.head_dim)
         return arr
+
+    def state_slots(self):
+        """The convolution-tap and recurrent-matrix slots of a hybrid decoder's DeltaNet layers (copied whole by a snapshot)."""
+        if self.hybrid is None:
+            return []
+        L = self.desc.layers
+        return [KV_BASE_SLOT + 2 * L + l for l in range(L) if self.hybrid.kinds[l]] + [KV_BASE_SLOT + 3 * L + l for l in range(L) if self.hybrid.kinds[l]]
 
     def capture_snapshot(self, captured_length: int, prompt_length: int = 0, next_token: int = 0) -> "Snapshot":
         kv = self.kv_slots()
+        st = np.array(self.state_slots(), np.int32)
         h = C.c_void_p()
-        self.ctx._check(self.ctx.lib.smelt_cuda_snapshot_capture(self.ctx.h, kv, len(kv), None, 0, int(captured_length), int(prompt_length),
-                                                                 int(next_token), C.byref(h)))
+        self.ctx._check(self.ctx.lib.smelt_cuda_snapshot_capture(self.ctx.h, kv, len(kv), st.ctypes.data_as(C.c_void_p) if len(st) else None, len(st),
+                                                                 int(captured_length), int(prompt_length), int(next_token), C.byref(h)))
         return Snapshot(self.ctx, h)
 
     def restore_snapshot(self, snap: "Snapshot", length: int | None = None):

@@ -519,3 +519,22 @@ def test_fused_conv_l2_record_equals_the_staged_pair(ctx, oracle):
     assert np.array_equal(got_state.view(np.uint16), want_state.reshape(c, k).view(np.uint16))
     assert np.max(ulp_diff_f16(got, want)) <= 2  # expf of the two libraries inside the staged SiLU, carried through the norm
     assert np.array_equal(got[32 * 128:].view(np.uint16) == act[32 * 128:].view(np.uint16), np.ones(c - 32 * 128, bool)) or np.max(ulp_diff_f16(got[32 * 128:], act[32 * 128:])) <= 1
+
+
+def test_hybrid_table_follows_the_plugins_record_order():
+    """smelt_cuda_build_hybrid_decoder without a context: a DeltaNet layer is norm, four projections, conv, Q / K
+    scaling, recurrence, gated norm, output projection + residual (DeltaNetPlugin.swift:60-420), then the feed-forward half."""
+    from smelt_b200 import package
+    cfg = package.DecoderConfig(layers=2, hidden=512, inter=1024, n_q=4, n_kv=2, head_dim=64, vocab=512, delta_layers=(0,),
+                                delta_value_heads=8, delta_qk_heads=4, delta_head_dim=64)
+    image, desc, layers, hy = package.build_hybrid_image(package.SyntheticPackage(cfg, 1))
+    lib = capi.load()
+    n = C.c_size_t(0)
+    assert lib.smelt_cuda_build_hybrid_decoder(None, C.byref(desc), layers, C.byref(hy.desc), hy.refs, hy.kinds, 32, None, C.byref(n)) == 0
+    table = (capi.DispatchRecord * n.value)()
+    assert lib.smelt_cuda_build_hybrid_decoder(None, C.byref(desc), layers, C.byref(hy.desc), hy.refs, hy.kinds, 32, table, C.byref(n)) == 0
+    dispatches = [r for r in table if r.op_kind == 0]
+    # embedding + delta layer (11 mixer records incl. the residual add, 4 feed-forward) + attention layer (9 + 4) + 4 final
+    assert len(dispatches) == 1 + (11 + 4) + (9 + 4) + 4
+    bad = capi.DeltaDesc(8, 3, 64, 4)  # value heads not a multiple of the q / k heads
+    assert lib.smelt_cuda_build_hybrid_decoder(None, C.byref(desc), layers, C.byref(bad), hy.refs, hy.kinds, 32, None, C.byref(n)) == capi.BAD_ARGUMENT
