@@ -280,6 +280,14 @@ SMELT_CUDA_API smelt_status smelt_cuda_build_hybrid_decoder(smelt_cuda_ctx* ctx,
                                                             const smelt_layer_ref* layers, const smelt_delta_desc* delta_desc,
                                                             const smelt_delta_ref* delta, const uint8_t* kinds, uint32_t capacity,
                                                             smelt_dispatch_record* records, size_t* n_records);
+/* The same for a hybrid decoder (smelt_cuda_build_hybrid_decoder): a DeltaNet layer runs its batched projections,
+ * conv1d_update_silu_prefill, rms_scale_qk over the chunk's rows, deltanet_recurrence_mlx_prefill and the gated norm per
+ * (position, head).  The recurrent rows stay in fp32 across a chunk and are rounded at its end, as the reference's
+ * prompt-chunk kernel does, so the chunking is part of the result.  Adds the chunk slots 11, 12, 15, 18, 19. */
+SMELT_CUDA_API smelt_status smelt_cuda_build_hybrid_prefill_table(smelt_cuda_ctx* ctx, const smelt_decoder_desc* desc,
+                                                                  const smelt_layer_ref* layers, const smelt_delta_desc* delta_desc,
+                                                                  const smelt_delta_ref* delta, const uint8_t* kinds, uint32_t max_chunk,
+                                                                  smelt_dispatch_record* records, size_t* n_records);
 
 /* The prompt-chunk table of the decoder smelt_cuda_build_decoder built (same descriptor and layer references; one
  * GPU, batch 1), in the reference's prefill record shapes (Sources/SmeltCompiler/PrefillEmitter.swift): chunk length

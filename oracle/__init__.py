@@ -388,6 +388,16 @@ class Model:
                                           C.byref(out)), "model_decode_step")
         return (out.value, logits) if want_logits else out.value
 
+    def prefill(self, tokens, start_pos: int = 0, chunk: int = 512, want_logits: bool = False):
+        """The prompt `chunk` positions at a time, layer by layer over each chunk (so_model_prefill).  Returns the
+        greedy token after the last position (and its logits)."""
+        toks = np.ascontiguousarray(np.asarray(tokens).reshape(-1), np.int32)
+        logits = np.zeros(self.cfg["vocab"], np.float16) if want_logits else None
+        out = C.c_int32(-1)
+        _check(lib().so_model_prefill(self._m, _p(toks), len(toks), int(start_pos), int(chunk), _p(logits) if want_logits else None, C.byref(out)),
+               "model_prefill")
+        return (out.value, logits) if want_logits else out.value
+
     def greedy_top2(self, prompt, n_decode: int):
         """Greedy decode of one sequence from an empty cache; per step the token, the runner-up
         and the logit margin between the two (lists of n_decode entries).  A teacher-forced replay

@@ -1141,6 +1141,78 @@ SO_API int so_model_decode_step(so_model_t *m, int32_t token, int position, uint
     return rc;
 }
 
+/* A prompt through the model `chunk` positions at a time, every layer over the whole chunk before the next layer,
+ * as a prefill table runs it.  For attention layers this equals token-by-token decoding (each position sees the
+ * cache rows before it); a DeltaNet layer takes the prompt-chunk kernels, whose recurrent rows stay in fp32 across
+ * the chunk and are rounded to fp16 at its end (prefill_recurrence.metal:318-321), so the chunking is part of the
+ * result.  Writes the logits of the last position and its greedy token. */
+SO_API int so_conv1d_update_silu_prefill(uint16_t *state, uint16_t *qkv, const uint16_t *weight, int seq_len, int channels, int kernel_size, uint16_t *history);
+SO_API int so_deltanet_recurrence_prefill(uint16_t *state, const uint16_t *qkv, const uint16_t *b_proj, const uint16_t *a_proj, const uint16_t *a_log,
+                                          const uint16_t *dt_bias, uint16_t *out, int head_dim, int value_heads, int qk_heads, int seq_len, uint16_t *history);
+SO_API int so_model_prefill(so_model_t *m, const int32_t *tokens, int n_tokens, int start_pos, int chunk, uint16_t *logits_out, int32_t *out_token) {
+    if (n_tokens <= 0 || start_pos < 0 || start_pos + n_tokens > m->capacity || chunk <= 0) return SO_ERR_GEOMETRY;
+    const int H = m->hidden, I = m->inter, D = m->head_dim, qd = m->n_q * D, kvd = m->n_kv * D, G = m->group;
+    const int DD = m->d_head_dim, Hv = m->d_value_heads, Hqk = m->d_qk_heads;
+    const int dq = (2 * Hqk + Hv) * DD, dv = Hv * DD;
+    const size_t T = (size_t)(chunk < n_tokens ? chunk : n_tokens);
+    const size_t per = (size_t)H * 3 + qd * 2 + kvd * 2 + I + (size_t)dq + 2 * (size_t)dv + 2 * (size_t)Hv;
+    uint16_t *buf = (uint16_t *)malloc(per * T * 2);
+    uint16_t *logits = logits_out ? logits_out : (uint16_t *)malloc((size_t)m->vocab * 2);
+    if (!buf || !logits) { free(buf); if (!logits_out) free(logits); return SO_ERR_ALLOC; }
+    uint16_t *hs = buf, *normed = hs + T * H, *tmp = normed + T * H, *q = tmp + T * H, *attn = q + T * qd, *k = attn + T * qd, *v = k + T * kvd,
+             *act = v + T * kvd, *dqkv = act + T * I, *dz = dqkv + T * dq, *dout = dz + T * dv, *da = dout + T * dv, *db = da + T * Hv;
+    const float base_log2 = log2f(m->rope_theta), scale = 1.0f / sqrtf((float)D);
+    int rc = SO_OK;
+    for (int t0 = 0; t0 < n_tokens && !rc; t0 += chunk) {
+        const int n = n_tokens - t0 < chunk ? n_tokens - t0 : chunk, p0 = start_pos + t0;
+        for (int t = 0; t < n; ++t) {
+            if (tokens[t0 + t] < 0 || tokens[t0 + t] >= m->vocab) { rc = SO_ERR_GEOMETRY; break; }
+            so_embedding_gather(m->embedding, tokens[t0 + t], H, hs + (size_t)t * H);
+        }
+        for (int l = 0; l < m->layers && !rc; ++l) {
+            so_layer_t *L = &m->layer[l];
+            for (int t = 0; t < n && !rc; ++t) rc = so_rms_norm_1pw(hs + (size_t)t * H, L->input_norm, H, m->eps, 1, normed + (size_t)t * H);
+            if (!rc && L->kind == 1) {
+                rc = so_affine_matvec(L->dqkv.w, L->dqkv.s, L->dqkv.b, normed, dq, H, G, n, dqkv);
+                if (!rc) rc = so_affine_matvec(L->dz.w, L->dz.s, L->dz.b, normed, dv, H, G, n, dz);
+                if (!rc) rc = so_affine_matvec(L->da.w, L->da.s, L->da.b, normed, Hv, H, G, n, da);
+                if (!rc) rc = so_affine_matvec(L->db.w, L->db.s, L->db.b, normed, Hv, H, G, n, db);
+                if (!rc) rc = so_conv1d_update_silu_prefill(L->conv_state, dqkv, L->conv_w, n, dq, m->d_conv_kernel, NULL);
+                if (!rc) rc = so_rms_scale_qk(dqkv, DD, 1e-6f, dq, Hqk, n);
+                if (!rc) rc = so_deltanet_recurrence_prefill(L->rec_state, dqkv, db, da, L->a_log, L->dt_bias, dout, DD, Hv, Hqk, n, NULL);
+                if (!rc) rc = (DD == 128 && m->eps == 1e-6f) ? so_rms_norm_gated_d128(dout, dz, L->gnorm_w, dout, n * Hv)
+                                                             : so_rms_norm_gated_tg(dout, dz, L->gnorm_w, dout, DD, m->eps, n * Hv, DD < 256 ? DD : 256);
+                if (!rc) rc = so_affine_matvec(L->dout.w, L->dout.s, L->dout.b, dout, H, dv, G, n, tmp);
+            } else if (!rc) {
+                rc = so_affine_matvec(L->q.w, L->q.s, L->q.b, normed, qd, H, G, n, q);
+                if (!rc) rc = so_affine_matvec(L->k.w, L->k.s, L->k.b, normed, kvd, H, G, n, k);
+                if (!rc) rc = so_affine_matvec(L->v.w, L->v.s, L->v.b, normed, kvd, H, G, n, v);
+                for (int t = 0; t < n && !rc; ++t) {
+                    rc = so_apply_rope(q + (size_t)t * qd, NULL, NULL, D, D, m->n_q, 1, (uint32_t)(p0 + t), base_log2, 1);
+                    if (!rc) rc = so_rope_kv_cache_update(m->k_cache[l], k + (size_t)t * kvd, NULL, NULL, m->capacity, D, p0 + t, m->n_kv, D, 1, base_log2, 1);
+                    if (!rc) rc = so_kv_cache_update(m->v_cache[l], v + (size_t)t * kvd, m->capacity, D, p0 + t, m->n_kv);
+                    if (!rc) rc = so_attention_decode(q + (size_t)t * qd, m->k_cache[l], m->v_cache[l], m->n_q, m->n_kv, D, m->capacity, p0 + t + 1, scale, 0,
+                                                      attn + (size_t)t * qd);
+                }
+                if (!rc) rc = so_affine_matvec(L->o.w, L->o.s, L->o.b, attn, H, qd, G, n, tmp);
+            }
+            if (!rc) so_elementwise_add(hs, tmp, (int64_t)n * H, hs);
+            for (int t = 0; t < n && !rc; ++t) rc = so_rms_norm_1pw(hs + (size_t)t * H, L->post_norm, H, m->eps, 1, normed + (size_t)t * H);
+            if (!rc) rc = so_affine_gate_up_swiglu(L->gate.w, L->gate.s, L->gate.b, L->up.w, L->up.s, L->up.b, normed, I, H, G, n, 0, act);
+            if (!rc) rc = so_affine_matvec(L->down.w, L->down.s, L->down.b, act, H, I, G, n, tmp);
+            if (!rc) so_elementwise_add(hs, tmp, (int64_t)n * H, hs);
+        }
+        if (!rc && t0 + n >= n_tokens) {
+            rc = so_rms_norm_1pw(hs + (size_t)(n - 1) * H, m->final_norm, H, m->eps, 1, normed);
+            if (!rc) rc = so_fp16_matvec(m->lm_head, normed, m->vocab, H, 1, logits);
+            if (!rc && out_token) *out_token = so_argmax_f16(logits, m->vocab);
+        }
+    }
+    free(buf);
+    if (!logits_out) free(logits);
+    return rc;
+}
+
 /* Greedy generation: feed the prompt token by token (the reference does the same when a
  * package has no prefill table, Sources/SmeltRuntime/SmeltModel.swift:619-631), then
  * n_decode greedy steps.  out_tokens receives n_decode ids; margins (optional, n_decode

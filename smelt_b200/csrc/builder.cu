@@ -332,9 +332,17 @@ extern "C" smelt_status smelt_cuda_build_decoder(smelt_cuda_ctx* ctx, const smel
 // start position are run-time constants, so one table serves every chunk up to max_chunk positions.
 enum PrefillSlot : int { kPfX0 = 2, kPfX1 = 3, kPfNorm = 4, kPfQ = 5, kPfK = 6, kPfV = 7, kPfAttn = 9, kPfFfn = 10 };
 
+enum PrefillDeltaSlot : int { kPfDeltaQkv = 11, kPfDeltaZ = 12, kPfDeltaA = 15, kPfDeltaB = 18, kPfDeltaOut = 19 };
+
 static smelt_status build_prefill_impl(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers, uint32_t max_chunk,
-                                       smelt_dispatch_record* records, size_t* n_records, std::vector<std::string>* names) {
+                                       smelt_dispatch_record* records, size_t* n_records, std::vector<std::string>* names, const Hybrid* hy = nullptr) {
     if (!d || !layers || !n_records) return SMELT_ERR_BAD_ARGUMENT;
+    if (hy) {
+        const smelt_delta_desc* dd = hy->dd;
+        if (!dd || !hy->refs || !hy->kinds || dd->value_heads <= 0 || dd->qk_heads <= 0 || dd->value_heads % dd->qk_heads || dd->head_dim <= 0 || dd->head_dim % 32 ||
+            dd->head_dim > 256 || dd->conv_kernel <= 0 || dd->conv_kernel > 8)
+            return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_hybrid_prefill_table: bad linear-attention geometry");
+    }
     if (d->layers <= 0 || d->layers > 100 || d->hidden <= 0 || d->inter <= 0 || d->n_q <= 0 || d->n_kv <= 0 || d->n_q % d->n_kv || d->head_dim <= 0 || d->vocab <= 0 ||
         max_chunk == 0 || d->tp_world > 1)
         return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: bad model description (one GPU, batch 1)");
@@ -345,8 +353,18 @@ static smelt_status build_prefill_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
     if (ctx) {
         if (!records) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: a context needs a record buffer (query the count with a null context)");
         if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, SMELT_ERR_CUDA, "cudaSetDevice");
-        if (!ctx->configured || ctx->cfg.batch != 1 || !ctx->slots[kWeights].ptr || !ctx->slots[kKvBase].ptr)
+        if (!ctx->configured || ctx->cfg.batch != 1 || !ctx->slots[kWeights].ptr)
             return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "build_prefill_table: build the decoder (batch 1) first");
+        if (hy) {
+            const smelt_delta_desc* dd = hy->dd;
+            const size_t dq = (size_t)(2 * dd->qk_heads + dd->value_heads) * dd->head_dim, dv = (size_t)dd->value_heads * dd->head_dim;
+            struct { int slot; size_t bytes; } dplan[] = {{kPfDeltaQkv, T * dq * 2}, {kPfDeltaZ, T * dv * 2}, {kPfDeltaA, T * dd->value_heads * 2 + 16},
+                                                          {kPfDeltaB, T * dd->value_heads * 2 + 16}, {kPfDeltaOut, T * dv * 2}};
+            for (auto& p : dplan) {
+                smelt_status s = smelt_cuda_alloc_slot(ctx, p.slot, p.bytes);
+                if (s) return s;
+            }
+        }
         struct { int slot; size_t bytes; } plan[] = {
             {kPfX0, T * H * 2}, {kPfX1, T * H * 2}, {kPfNorm, T * H * 2}, {kPfQ, T * qd * 2}, {kPfK, T * kvd * 2}, {kPfV, T * kvd * 2},
             {kPfAttn, T * qd * 2}, {kPfFfn, T * I * 2},
@@ -368,6 +386,30 @@ static smelt_status build_prefill_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
         const smelt_layer_ref& w = layers[l];
         const int kslot = kKvBase + l, vslot = kKvBase + L + l;
         Rec(e, "rms_norm_1pw_batched", 1).grid_kind(0, 1).tg(256).buf(0, kPfX0).buf(1, kWeights, w.input_norm).buf(2, kPfNorm).u32(3, H).f32(4, d->eps);
+        if (hy && hy->kinds[l]) {
+            // the DeltaNet mixer over the chunk: batched projections, the prompt-chunk convolution and recurrence, gated norm per (position, head)
+            const smelt_delta_desc* dd = hy->dd;
+            const smelt_delta_ref& x = hy->refs[l];
+            const int DD = dd->head_dim, Hv = dd->value_heads, Hqk = dd->qk_heads;
+            const int dq = (2 * Hqk + Hv) * DD, dv = Hv * DD;
+            const int conv_slot = kKvBase + 2 * L + l, rec_slot = kKvBase + 3 * L + l;
+            auto proj = [&](const smelt_affine_ref& wt, int rows, int out_slot) {
+                Rec r(e, shaped("affine_matvec", H, rows, G, true) + "_full", (rows + 31) / 32, 1);
+                r.grid_kind(1, 3).r->grid[1] = 8;
+                r.affine(0, wt).buf(3, kPfNorm).buf(4, out_slot).con(5, kSeq);
+            };
+            proj(x.qkv, dq, kPfDeltaQkv); proj(x.z, dv, kPfDeltaZ); proj(x.a, Hv, kPfDeltaA); proj(x.b, Hv, kPfDeltaB);
+            Rec(e, "conv1d_update_silu_prefill", (dq + 255) / 256).tg(256).buf(0, conv_slot).buf(1, kPfDeltaQkv).buf(2, kWeights, x.conv_weight).con(3, kSeq).u32(4, dq).u32(5, dd->conv_kernel);
+            Rec(e, "rms_scale_qk", 2 * Hqk, 1).grid_kind(1, 1).tg(32u * (uint32_t)((DD + 127) / 128)).buf(0, kPfDeltaQkv).u32(1, DD).f32(2, 1e-6f).u32(3, dq).u32(4, Hqk);
+            Rec(e, "deltanet_recurrence_mlx_prefill", 32, DD).tg(32).buf(0, rec_slot).buf(1, kPfDeltaQkv).buf(2, kPfDeltaB).buf(3, kPfDeltaA).buf(4, kWeights, x.a_log)
+                .buf(5, kWeights, x.dt_bias).buf(6, kPfDeltaOut).u32(7, DD).u32(8, Hv).u32(9, Hqk).con(10, kSeq);
+            if (DD == 128 && d->eps == 1e-6f)
+                Rec(e, "rms_norm_gated_d128_batched", Hv, 1).grid_kind(1, 1).tg(32).buf(0, kPfDeltaOut).buf(1, kPfDeltaZ).buf(2, kWeights, x.norm_weight).buf(3, kPfDeltaOut).u32(4, Hv);
+            else
+                Rec(e, "rms_norm_gated", Hv).grid_kind(0, 2).tg((uint32_t)(DD < 256 ? DD : 256)).buf(0, kPfDeltaOut).buf(1, kPfDeltaZ).buf(2, kWeights, x.norm_weight).buf(3, kPfDeltaOut)
+                    .u32(4, DD).f32(5, d->eps);
+            { Rec r(e, shaped("fused_affine_matvec_add", dv, H, G, true), (H + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, x.out).buf(3, kPfDeltaOut).buf(4, kPfX1).buf(5, kPfX0).con(6, kSeq); }
+        } else {
         { Rec r(e, shaped("affine_matvec", H, qd, G, true) + "_full", (qd + 31) / 32, 1); r.grid_kind(1, 3).r->grid[1] = 8; r.affine(0, w.q).buf(3, kPfNorm).buf(4, kPfQ).con(5, kSeq); }
         { Rec r(e, shaped("fused_dual_affine_matvec", H, kvd, G, true), (kvd + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.k).affine(3, w.v).buf(6, kPfNorm).buf(7, kPfK).buf(8, kPfV).con(9, kSeq); }
         Rec(e, "rope_and_kv_cache_prefill_analytic", 1, (uint32_t)(d->n_q > d->n_kv ? d->n_q : d->n_kv)).grid_kind(0, 1).buf(0, kPfQ).buf(1, kPfK).buf(2, kPfV).buf(3, kslot).buf(4, vslot)
@@ -380,6 +422,7 @@ static smelt_status build_prefill_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
             r.u32(8, d->n_kv).f32(9, scale);
         }
         { Rec r(e, shaped("fused_affine_matvec_add", qd, H, G, true), (H + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.o).buf(3, kPfAttn).buf(4, kPfX1).buf(5, kPfX0).con(6, kSeq); }
+        }  // attention mixer
         Rec(e, "rms_norm_1pw_batched", 1).grid_kind(0, 1).tg(256).buf(0, kPfX1).buf(1, kWeights, w.post_norm).buf(2, kPfNorm).u32(3, H).f32(4, d->eps);
         { Rec r(e, shaped("fused_affine_gate_up_swiglu", H, I, G, true), (I + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.gate).affine(3, w.up).buf(6, kPfNorm).buf(7, kPfFfn).con(8, kSeq); }
         { Rec r(e, shaped("fused_affine_matvec_add", I, H, G, true), (H + 7) / 8, 1); r.grid_kind(1, 3).r->grid[1] = 4; r.affine(0, w.down).buf(3, kPfFfn).buf(4, kPfX0).buf(5, kPfX1).con(6, kSeq); }
@@ -406,6 +449,13 @@ static smelt_status build_prefill_impl(smelt_cuda_ctx* ctx, const smelt_decoder_
 extern "C" smelt_status smelt_cuda_build_prefill_table(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
                                                        uint32_t max_chunk, smelt_dispatch_record* records, size_t* n_records) {
     return build_prefill_impl(ctx, d, layers, max_chunk, records, n_records, nullptr);
+}
+
+extern "C" smelt_status smelt_cuda_build_hybrid_prefill_table(smelt_cuda_ctx* ctx, const smelt_decoder_desc* d, const smelt_layer_ref* layers,
+                                                              const smelt_delta_desc* delta_desc, const smelt_delta_ref* delta, const uint8_t* kinds,
+                                                              uint32_t max_chunk, smelt_dispatch_record* records, size_t* n_records) {
+    const Hybrid hy{delta_desc, delta, kinds};
+    return build_prefill_impl(ctx, d, layers, max_chunk, records, n_records, nullptr, &hy);
 }
 
 extern "C" smelt_status smelt_cuda_prefill_pipelines(const smelt_decoder_desc* d, char* out, size_t out_bytes, size_t* needed_bytes) {

@@ -302,9 +302,15 @@ class Decoder:
         """The prompt-chunk dispatch table of this decoder in the reference's prefill record shapes
         (``smelt_cuda_build_prefill_table``); call it before ``build_graph``."""
         n = C.c_size_t(0)
-        self.ctx._check(self.ctx.lib.smelt_cuda_build_prefill_table(None, C.byref(self.desc), self.layers, int(max_chunk), None, C.byref(n)))
+        lib, hy = self.ctx.lib, self.hybrid
+        if hy is not None:
+            build = lambda h, table: lib.smelt_cuda_build_hybrid_prefill_table(h, C.byref(self.desc), self.layers, C.byref(hy.desc), hy.refs, hy.kinds,
+                                                                               int(max_chunk), table, C.byref(n))
+        else:
+            build = lambda h, table: lib.smelt_cuda_build_prefill_table(h, C.byref(self.desc), self.layers, int(max_chunk), table, C.byref(n))
+        self.ctx._check(build(None, None))
         self.prefill_records = (capi.DispatchRecord * n.value)()
-        self.ctx._check(self.ctx.lib.smelt_cuda_build_prefill_table(self.ctx.h, C.byref(self.desc), self.layers, int(max_chunk), self.prefill_records, C.byref(n)))
+        self.ctx._check(build(self.ctx.h, self.prefill_records))
         self.prefill_chunk = int(max_chunk)
         return self.prefill_records
 

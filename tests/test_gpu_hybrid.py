@@ -80,3 +80,37 @@ def test_hybrid_snapshot_carries_the_recurrent_state(ctx, oracle):
     with pytest.raises(capi.SmeltError):
         dec.restore_snapshot(snap, len(prompt) - 2)
     snap.close()
+
+
+@pytest.mark.parametrize("cfg,chunk", [(GENERIC, 16), (GENERIC, 24), (D128, 20), (D128, 80)])
+def test_hybrid_prefill_table_matches_the_oracles_chunked_prefill(ctx, oracle, cfg, chunk):
+    """The prompt of a hybrid decoder through its prompt-chunk table (batched projections, conv1d_update_silu_prefill,
+    deltanet_recurrence_mlx_prefill, the gated norm per position and head) against the oracle running the same chunks
+    layer by layer; then the oracle's continuation from the state the table left.  The recurrent rows stay in fp32
+    across a chunk in both, so the two must chunk alike."""
+    n_prompt, n_dec = 90, 16
+    cap = n_prompt + n_dec + 8
+    pkg = package.SyntheticPackage(cfg, 41)
+    image, desc, layers, hy = package.build_hybrid_image(pkg, keep_for_oracle=True)
+    dec = package.Decoder(ctx, image, desc, layers, cap, 1, fuse_residual=3, hybrid=hy)
+    dec.build_prefill_table(chunk)
+    ref = oracle.model_from_package(pkg, cap)
+    prompt = np.random.default_rng(41).integers(0, cfg.vocab, size=n_prompt).astype(np.int32)
+    ref.reset()
+    want0, want_logits = ref.prefill(prompt, 0, chunk, want_logits=True)
+    got0 = dec.prefill_by_table(prompt)
+    got_logits = dec.logits()[0].astype(np.float32)
+    wl = want_logits.astype(np.float32)
+    err = float(np.max(np.abs(got_logits - wl)) / np.sqrt(np.mean(wl * wl)))
+    assert err < 1e-2, err
+    best, second, margin = oracle.top2(want_logits)
+    assert got0 == best or (margin < 0.02 and got0 == second), (got0, best, second, margin)
+    # teacher-forced continuation: the oracle continues from its own prefill state, the library from the table's
+    tok = want0
+    for i in range(n_dec):
+        w, wlog = ref.decode_step(int(tok), n_prompt + i, want_logits=True)
+        g = int(dec.decode_step([int(tok)], n_prompt + i)[0])
+        b, s2, mg = oracle.top2(wlog)
+        assert g == b or (mg < 0.02 and g == s2), (i, g, b, s2, mg)
+        tok = w
+    assert ctx.device_error() == 0
