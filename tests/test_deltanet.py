@@ -538,3 +538,31 @@ def test_hybrid_table_follows_the_plugins_record_order():
     assert len(dispatches) == 1 + (11 + 4) + (9 + 4) + 4
     bad = capi.DeltaDesc(8, 3, 64, 4)  # value heads not a multiple of the q / k heads
     assert lib.smelt_cuda_build_hybrid_decoder(None, C.byref(desc), layers, C.byref(bad), hy.refs, hy.kinds, 32, None, C.byref(n)) == capi.BAD_ARGUMENT
+
+
+def test_oracle_chunked_prefill_against_token_by_token_decoding(oracle):
+    """so_model_prefill: an attention-only model gives the decode steps' logits bit for bit at any chunking; a hybrid
+    model does so at chunks of one position (the prompt-chunk recurrence of one position is the decode step) and
+    stays close at longer chunks, where its rows are kept in fp32 across the chunk."""
+    from smelt_b200 import package
+    prompt = np.array([5, 9, 100, 7, 3, 200, 11, 64, 300], np.int32)
+    plain = package.DecoderConfig(layers=2, hidden=512, inter=1024, n_q=4, n_kv=2, head_dim=64, vocab=512)
+    m = oracle.model_from_package(package.SyntheticPackage(plain, 4), 32)
+    m.reset()
+    seq = [m.decode_step(int(t), i, True) for i, t in enumerate(prompt)][-1]
+    for chunk in (1, 4, 16):
+        m.reset()
+        tok, logits = m.prefill(prompt, 0, chunk, want_logits=True)
+        assert tok == seq[0] and np.array_equal(logits.view(np.uint16), seq[1].view(np.uint16)), chunk
+    hybrid = package.DecoderConfig(layers=3, hidden=512, inter=1024, n_q=4, n_kv=2, head_dim=64, vocab=512, delta_layers=(0, 1),
+                                   delta_value_heads=8, delta_qk_heads=4, delta_head_dim=64)
+    h = oracle.model_from_package(package.SyntheticPackage(hybrid, 5), 32)
+    h.reset()
+    seq = [h.decode_step(int(t), i, True) for i, t in enumerate(prompt)][-1]
+    h.reset()
+    tok, logits = h.prefill(prompt, 0, 1, want_logits=True)
+    assert tok == seq[0] and np.array_equal(logits.view(np.uint16), seq[1].view(np.uint16))
+    h.reset()
+    tok, logits = h.prefill(prompt, 0, 4, want_logits=True)
+    ref = seq[1].astype(F)
+    assert float(np.max(np.abs(logits.astype(F) - ref)) / np.sqrt(np.mean(ref * ref))) < 2e-2
