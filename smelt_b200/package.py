@@ -74,7 +74,13 @@ class DecoderConfig:
     conv_kernel: int = 4
 
     def as_dict(self):
-        return dict(self.__dict__)
+        d = dict(self.__dict__)
+        if not self.delta_layers:  # a plain decoder describes itself as before the hybrid fields existed (committed fixtures compare it)
+            for k in ("delta_layers", "delta_value_heads", "delta_qk_heads", "delta_head_dim", "conv_kernel"):
+                d.pop(k)
+        else:
+            d["delta_layers"] = list(self.delta_layers)
+        return d
 
 
 # BASELINE config 4: the full random-init decoder.

@@ -51,3 +51,15 @@ def test_affine_and_attention_families_do_not_shrink():
     assert len(bound) == len(affine), sorted(set(affine) - set(bound))
     assert sum(by["attention.metal"].values()) >= 16
     assert sum(sum(d.values()) for d in by.values()) >= 365
+
+
+def test_committed_token_fixtures_describe_the_current_full_model():
+    """bench.py and the full-model GPU test replay tests/golden/full_model_tokens*.json only when the fixture's
+    configuration equals the model's own description: a new configuration field must not silently switch that off."""
+    import json
+
+    from smelt_b200 import package
+    for name in ("full_model_tokens.json", "full_model_tokens_batch8.json"):
+        with open(os.path.join(HERE, "golden", name)) as f:
+            gold = json.load(f)
+        assert gold["config"] == package.FULL_MODEL.as_dict(), name
