@@ -172,9 +172,11 @@ cudaError_t launch_attention_decode(const Launch& l, const AttnArgs& a) {
     // Short contexts are latency bound: up to 4096 keys, eight splits of a KV head run as one
     // thread-block cluster and merge through distributed shared memory, with no partials in
     // global memory (measured against one tile per warp and the ticket merge: 11.2 against
-    // 13.9 us at 4096 keys, batch 1).
+    // 13.9 us at 4096 keys, batch 1).  Always eight: the key ranges are cut from the live
+    // length, so with a fixed split count the summation order, and with it every output bit,
+    // is the same whatever capacity the cache was given or has grown to.
     const bool cluster = n_max <= 4096 && by_len >= 2 && !a.mlx_partials;
-    if (cluster) nsplits = by_len < 8 ? by_len : 8;
+    if (cluster) nsplits = 8;
     AttnDev p;
     p.a = a;
     p.nsplits = nsplits;

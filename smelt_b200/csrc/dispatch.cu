@@ -1616,7 +1616,11 @@ static smelt_status capture_tokens(smelt_cuda_ctx* ctx, const smelt_dispatch_rec
     s = check_cuda(ctx, e, "cudaStreamEndCapture");
     if (s) return s;
     *graph = g;
-    return check_cuda(ctx, cudaGraphInstantiate(exec, g, 0), "cudaGraphInstantiate");
+    s = check_cuda(ctx, cudaGraphInstantiate(exec, g, 0), "cudaGraphInstantiate");
+    if (s) return s;
+    // Upload now: otherwise the first launch of the graph pays for it (about a millisecond for
+    // the eight-token graph's two thousand nodes), inside whatever the caller is timing.
+    return check_cuda(ctx, cudaGraphUpload(*exec, ctx->stream), "cudaGraphUpload");
 }
 
 smelt_status smelt_cuda_graph_build(smelt_cuda_ctx* ctx, const smelt_dispatch_record* table, size_t n_records) {
