@@ -509,6 +509,83 @@ def deltanet_recurrence_prefill(state, qkv, b_proj, a_proj, a_log, dt_bias, head
     return st, out, hist
 
 
+def dn_compute_gates(b_proj, a_proj, a_log, dt_bias, heads: int):
+    """compute_gates: (beta [heads], g [heads]) as fp16."""
+    beta, g = np.zeros(heads, np.float16), np.zeros(heads, np.float16)
+    _check(lib().so_dn_compute_gates(_p(_h(b_proj)), _p(_h(a_proj)), _p(_h(a_log)), _p(_h(dt_bias)), _p(beta), _p(g), heads), "dn_compute_gates")
+    return beta, g
+
+
+def dn_state_decay(state, g_val, head_dim: int, heads: int) -> np.ndarray:
+    st = _h(state).copy()
+    _check(lib().so_dn_state_decay(_p(st), _p(_h(g_val)), head_dim, heads), "dn_state_decay")
+    return st
+
+
+def dn_kv_mem_readout(state, key, head_dim: int, heads: int) -> np.ndarray:
+    out = np.zeros((heads, head_dim), np.float32)
+    _check(lib().so_dn_kv_mem_readout(_p(_h(state)), _p(_h(key)), _p(out), head_dim, heads), "dn_kv_mem_readout")
+    return out
+
+
+def dn_compute_delta(value, kv_mem, beta, head_dim: int, heads: int) -> np.ndarray:
+    out = np.zeros((heads, head_dim), np.float32)
+    _check(lib().so_dn_compute_delta(_p(_h(value)), _p(np.ascontiguousarray(kv_mem, np.float32)), _p(_h(beta)), _p(out), head_dim, heads), "dn_compute_delta")
+    return out
+
+
+def dn_outer_product_update(state, key, delta, head_dim: int, heads: int, g_val=None) -> np.ndarray:
+    """outer_product_update, or state_decay_update when g_val is given."""
+    st = _h(state).copy()
+    _check(lib().so_dn_outer_product_update(_p(st), _p(_h(g_val)) if g_val is not None else None, _p(_h(key)),
+                                            _p(np.ascontiguousarray(delta, np.float32)), head_dim, heads), "dn_outer_product_update")
+    return st
+
+
+def dn_kv_readout_delta(state, key, value, g_val, beta, head_dim: int, heads: int) -> np.ndarray:
+    out = np.zeros((heads, head_dim), np.float32)
+    _check(lib().so_dn_kv_readout_delta(_p(_h(state)), _p(_h(key)), _p(_h(value)), _p(_h(g_val)), _p(_h(beta)), None, None, None, None,
+                                        _p(out), None, head_dim, heads), "dn_kv_readout_delta")
+    return out
+
+
+def dn_gates_kv_readout_delta(state, key, value, b_proj, a_proj, a_log, dt_bias, head_dim: int, heads: int):
+    """Returns (delta [heads, head_dim] fp32, g [heads] fp16)."""
+    out, g = np.zeros((heads, head_dim), np.float32), np.zeros(heads, np.float16)
+    _check(lib().so_dn_kv_readout_delta(_p(_h(state)), _p(_h(key)), _p(_h(value)), None, None, _p(_h(b_proj)), _p(_h(a_proj)), _p(_h(a_log)),
+                                        _p(_h(dt_bias)), _p(out), _p(g), head_dim, heads), "dn_gates_kv_readout_delta")
+    return out, g
+
+
+def dn_query_readout(state, query, head_dim: int, scale: float, heads: int) -> np.ndarray:
+    out = np.zeros((heads, head_dim), np.float16)
+    _check(lib().so_dn_query_readout(_p(_h(state)), _p(_h(query)), _p(out), head_dim, C.c_float(scale), heads), "dn_query_readout")
+    return out
+
+
+def deltanet_recurrence_fused(state, qkv, b_proj, a_proj, a_log, dt_bias, conv_state, conv_weight, z_proj, norm_weight, head_dim: int,
+                              head_scale: float, qkv_dim: int, conv_k: int, heads: int, rms_eps: float, tgs: int = 256):
+    """deltanet_recurrence_fused: returns (state, conv state, out [heads, head_dim])."""
+    st, cs = _h(state).copy(), _h(conv_state).copy()
+    out = np.zeros((heads, head_dim), np.float16)
+    _check(lib().so_deltanet_recurrence_fused(_p(st), _p(_h(qkv)), _p(_h(b_proj)), _p(_h(a_proj)), _p(_h(a_log)), _p(_h(dt_bias)), _p(out), _p(cs),
+                                              _p(_h(conv_weight)), _p(_h(z_proj)), _p(_h(norm_weight)), head_dim, C.c_float(head_scale), qkv_dim,
+                                              conv_k, heads, C.c_float(rms_eps), tgs), "deltanet_recurrence_fused")
+    return st, cs, out
+
+
+def deltanet_recurrence_prefill_fused(state, conv_state, qkv, conv_weight, a_log, dt_bias, b_buf, a_buf, head_dim: int, heads: int, seq_len: int,
+                                      qkv_dim: int, conv_k: int, head_scale: float, l2_eps: float, tgs: int = 0):
+    """deltanet_recurrence_prefill (the fused per-head kernel): returns (state, conv state, qkv after conv and
+    norms [seq_len, qkv_dim], out [seq_len, heads, head_dim])."""
+    st, cs, x = _h(state).copy(), _h(conv_state).copy(), _h(qkv).copy()
+    out = np.zeros((seq_len, heads, head_dim), np.float16)
+    _check(lib().so_deltanet_recurrence_prefill_fused(_p(st), _p(cs), _p(x), _p(_h(conv_weight)), _p(_h(a_log)), _p(_h(dt_bias)), _p(_h(b_buf)),
+                                                      _p(_h(a_buf)), _p(out), head_dim, heads, seq_len, qkv_dim, conv_k, C.c_float(head_scale),
+                                                      C.c_float(l2_eps), tgs or max(32, (head_dim + 31) // 32 * 32)), "deltanet_recurrence_prefill_fused")
+    return st, cs, x.reshape(seq_len, qkv_dim), out
+
+
 def rms_norm_gated(x, gate, weight, head_dim: int, eps: float, heads: int) -> np.ndarray:
     out = np.zeros((heads, head_dim), np.float16)
     _check(lib().so_rms_norm_gated(_p(_h(x)), _p(_h(gate)), _p(_h(weight)), _p(out), head_dim, C.c_float(eps), heads), "rms_norm_gated")

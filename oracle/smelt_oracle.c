@@ -1453,6 +1453,277 @@ SO_API int so_deltanet_recurrence_prefill(uint16_t *state, const uint16_t *qkv, 
     return SO_OK;
 }
 
+/* ── The DeltaNet step as separate launches (Resources/Shaders/recurrence.metal:44-302, :836-862) ──
+ * The reference's kernel catalog still lists these pipelines (SmeltKernelCatalog.swift:655-696,
+ * :847-893) although its emitters now dispatch the tiled forms above.  State here is
+ * [H, Dk, Dv]: state[k * D + v].  The gates are plain fp32 (no staged roundings) and the sums
+ * over k run one term at a time in k order.  The reference holds no test or scalar oracle for
+ * them: parity unpinned beyond this restatement of the kernels' arithmetic. */
+static inline void plain_gates(uint16_t b, uint16_t a, uint16_t a_log, uint16_t dt_bias, float *beta, float *g) {
+    *beta = 1.0f / (1.0f + expf(-h2f(b)));
+    const float x = h2f(a) + h2f(dt_bias);
+    const float sp = x > 20.0f ? x : logf(1.0f + expf(x));
+    *g = -expf(h2f(a_log)) * sp;
+}
+
+/* compute_gates (recurrence.metal:839-862): beta = half(sigmoid(b)), g = half(-exp(A_log) softplus(a + dt_bias)). */
+SO_API int so_dn_compute_gates(const uint16_t *b_proj, const uint16_t *a_proj, const uint16_t *a_log, const uint16_t *dt_bias,
+                               uint16_t *beta_out, uint16_t *g_out, int heads) {
+    if (heads <= 0) return SO_ERR_GEOMETRY;
+    for (int h = 0; h < heads; ++h) {
+        float beta, g;
+        plain_gates(b_proj[h], a_proj[h], a_log[h], dt_bias[h], &beta, &g);
+        beta_out[h] = f2h(beta);
+        g_out[h] = f2h(g);
+    }
+    return SO_OK;
+}
+
+/* state_decay (:48-63): state <- half(state * exp(g[h])). */
+SO_API int so_dn_state_decay(uint16_t *state, const uint16_t *g_val, int head_dim, int heads) {
+    if (head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    const size_t n = (size_t)head_dim * head_dim;
+    for (int h = 0; h < heads; ++h) {
+        const float decay = expf(h2f(g_val[h]));
+        for (size_t i = 0; i < n; ++i) state[h * n + i] = f2h(h2f(state[h * n + i]) * decay);
+    }
+    return SO_OK;
+}
+
+/* kv_mem_readout (:70-90): kv_mem[h, v] = sum_k state[h, k, v] * key[h, k], fp32 out. */
+SO_API int so_dn_kv_mem_readout(const uint16_t *state, const uint16_t *key, float *kv_mem, int head_dim, int heads) {
+    if (head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    const int D = head_dim;
+    for (int h = 0; h < heads; ++h)
+        for (int v = 0; v < D; ++v) {
+            float acc = 0.0f;
+            for (int k = 0; k < D; ++k) acc += h2f(state[((size_t)h * D + k) * D + v]) * h2f(key[(size_t)h * D + k]);
+            kv_mem[(size_t)h * D + v] = acc;
+        }
+    return SO_OK;
+}
+
+/* compute_delta (:95-108): delta = (value - kv_mem) * beta[h], fp32 out. */
+SO_API int so_dn_compute_delta(const uint16_t *value, const float *kv_mem, const uint16_t *beta, float *delta, int head_dim, int heads) {
+    if (head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    for (int i = 0; i < heads * head_dim; ++i) delta[i] = (h2f(value[i]) - kv_mem[i]) * h2f(beta[i / head_dim]);
+    return SO_OK;
+}
+
+/* outer_product_update (:113-142) and, with g_val != NULL, state_decay_update (:246-276):
+ * state[h, k, v] <- half(state (* exp(g[h])) + key[h, k] * delta[h, v]). */
+SO_API int so_dn_outer_product_update(uint16_t *state, const uint16_t *g_val, const uint16_t *key, const float *delta, int head_dim, int heads) {
+    if (head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    const int D = head_dim;
+    for (int h = 0; h < heads; ++h) {
+        const float decay = g_val ? expf(h2f(g_val[h])) : 1.0f;
+        for (int k = 0; k < D; ++k)
+            for (int v = 0; v < D; ++v) {
+                uint16_t *s = state + ((size_t)h * D + k) * D + v;
+                const float old = h2f(*s);
+                const float upd = h2f(key[(size_t)h * D + k]) * delta[(size_t)h * D + v];
+                *s = f2h(g_val ? old * decay + upd : old + upd);
+            }
+    }
+    return SO_OK;
+}
+
+/* kv_readout_delta (:150-178) and, with b_proj != NULL, gates_kv_readout_delta (:186-239): the
+ * readout of the un-decayed state times exp(g), then delta = (value - kv_mem) * beta.  The first
+ * takes g and beta as fp16 inputs (g_val, beta); the second computes both in fp32 from b_proj,
+ * a_proj, a_log, dt_bias and writes g_out[h] = half(g). */
+SO_API int so_dn_kv_readout_delta(const uint16_t *state, const uint16_t *key, const uint16_t *value, const uint16_t *g_val,
+                                  const uint16_t *beta_in, const uint16_t *b_proj, const uint16_t *a_proj, const uint16_t *a_log,
+                                  const uint16_t *dt_bias, float *delta, uint16_t *g_out, int head_dim, int heads) {
+    if (head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    const int D = head_dim;
+    for (int h = 0; h < heads; ++h) {
+        float decay, beta;
+        if (b_proj) {
+            float g;
+            plain_gates(b_proj[h], a_proj[h], a_log[h], dt_bias[h], &beta, &g);
+            decay = expf(g);
+            g_out[h] = f2h(g);
+        } else {
+            decay = expf(h2f(g_val[h]));
+            beta = h2f(beta_in[h]);
+        }
+        for (int v = 0; v < D; ++v) {
+            float acc = 0.0f;
+            for (int k = 0; k < D; ++k) acc += h2f(state[((size_t)h * D + k) * D + v]) * h2f(key[(size_t)h * D + k]);
+            const float kv_mem = acc * decay;
+            delta[(size_t)h * D + v] = (h2f(value[(size_t)h * D + v]) - kv_mem) * beta;
+        }
+    }
+    return SO_OK;
+}
+
+/* query_readout (:282-302): out[h, v] = half(sum_k state[h, k, v] * (query[h, k] * scale)). */
+SO_API int so_dn_query_readout(const uint16_t *state, const uint16_t *query, uint16_t *out, int head_dim, float scale, int heads) {
+    if (head_dim <= 0 || heads <= 0) return SO_ERR_GEOMETRY;
+    const int D = head_dim;
+    for (int h = 0; h < heads; ++h)
+        for (int v = 0; v < D; ++v) {
+            float acc = 0.0f;
+            for (int k = 0; k < D; ++k) {
+                const float q = h2f(query[(size_t)h * D + k]) * scale;
+                acc += h2f(state[((size_t)h * D + k) * D + v]) * q;
+            }
+            out[(size_t)h * D + v] = f2h(acc);
+        }
+    return SO_OK;
+}
+
+/* Sum of x[i]^2 over a head as a threadgroup of tgs threads forms it in these kernels: thread t
+ * adds its elements t, t + tgs, ...; every simdgroup sums its 32 lanes (simd_sum); thread 0 adds
+ * the simdgroups' sums one after the other. */
+static float tg_sumsq(const float *x, int n, int tgs) {
+    float total = 0.0f;
+    for (int s = 0; s < tgs / 32; ++s) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            float p = 0.0f;
+            for (int i = s * 32 + l; i < n; i += tgs) p += x[i] * x[i];
+            lane[l] = p;
+        }
+        total += simd_sum32(lane);
+    }
+    return total;
+}
+
+/* deltanet_recurrence_fused (recurrence.metal:310-503): one threadgroup of tgs threads per head
+ * runs conv1d + SiLU (plain fp32, no fp16 staging) on the head's Q, K and V channels, L2-
+ * normalises Q (times head_scale) and K, computes the gates in fp32, runs the recurrence on the
+ * [H, Dv, Dk] state with lane l of a simdgroup holding dk = l, l + 32, ..., and applies the
+ * gated RMS norm.  qkv = [Q (H, D) | K (H, D) | V (H, D)]; conv_state / conv_weight
+ * [qkv_dim, conv_k]; z [H, D]; norm_weight [D]; out [H, D]. */
+SO_API int so_deltanet_recurrence_fused(uint16_t *state, const uint16_t *qkv, const uint16_t *b_proj, const uint16_t *a_proj,
+                                        const uint16_t *a_log, const uint16_t *dt_bias, uint16_t *out, uint16_t *conv_state,
+                                        const uint16_t *conv_weight, const uint16_t *z_proj, const uint16_t *norm_weight, int head_dim,
+                                        float head_scale, int qkv_dim, int conv_k, int heads, float rms_eps, int tgs) {
+    if (head_dim <= 0 || head_dim % 32 || head_dim > 256 || heads <= 0 || conv_k <= 0 || conv_k > 8 || qkv_dim < 3 * heads * head_dim ||
+        tgs <= 0 || tgs % 32 || tgs > 1024)
+        return SO_ERR_GEOMETRY;
+    const int D = head_dim, epl = D / 32;
+    for (int h = 0; h < heads; ++h) {
+        float q[256], k[256], v[256], raw[256];
+        for (int i = 0; i < 3 * D; ++i) {
+            const int part = i / D, local = i % D;
+            const int ch = part * heads * D + h * D + local;
+            uint16_t *st = conv_state + (size_t)ch * conv_k;
+            const uint16_t *w = conv_weight + (size_t)ch * conv_k;
+            for (int t = 0; t + 1 < conv_k; ++t) st[t] = st[t + 1];
+            st[conv_k - 1] = qkv[ch];
+            float acc = 0.0f;
+            for (int t = 0; t < conv_k; ++t) acc += h2f(st[t]) * h2f(w[t]);
+            const float act = acc / (1.0f + expf(-acc));
+            (part == 0 ? q : part == 1 ? k : v)[local] = act;
+        }
+        const float q_scale = 1.0f / fmaxf(sqrtf(tg_sumsq(q, D, tgs)), 1e-6f);
+        const float k_scale = 1.0f / fmaxf(sqrtf(tg_sumsq(k, D, tgs)), 1e-6f);
+        float beta, g;
+        plain_gates(b_proj[h], a_proj[h], a_log[h], dt_bias[h], &beta, &g);
+        const float decay = expf(g);
+        for (int i = 0; i < D; ++i) {
+            q[i] *= q_scale * head_scale;
+            k[i] *= k_scale;
+        }
+        for (int row = 0; row < D; ++row) {
+            uint16_t *srow = state + ((size_t)h * D + row) * D;
+            float st[256], lane[32];
+            for (int l = 0; l < 32; ++l) {
+                float p = 0.0f;
+                for (int i = 0; i < epl; ++i) {
+                    const int dk = i * 32 + l;
+                    st[dk] = h2f(srow[dk]) * decay;
+                    p += st[dk] * k[dk];
+                }
+                lane[l] = p;
+            }
+            const float kv_mem = simd_sum32(lane);
+            const float delta = (v[row] - kv_mem) * beta;
+            for (int l = 0; l < 32; ++l) {
+                float p = 0.0f;
+                for (int i = 0; i < epl; ++i) {
+                    const int dk = i * 32 + l;
+                    st[dk] += k[dk] * delta;
+                    p += st[dk] * q[dk];
+                    srow[dk] = f2h(st[dk]);
+                }
+                lane[l] = p;
+            }
+            raw[row] = simd_sum32(lane);
+        }
+        const float rs = 1.0f / sqrtf(tg_sumsq(raw, D, tgs) / (float)D + rms_eps);
+        for (int i = 0; i < D; ++i) {
+            const float z = h2f(z_proj[(size_t)h * D + i]);
+            const float silu_z = z / (1.0f + expf(-z));
+            out[(size_t)h * D + i] = f2h(raw[i] * rs * h2f(norm_weight[i]) * silu_z);
+        }
+    }
+    return SO_OK;
+}
+
+/* deltanet_recurrence_prefill (Resources/Shaders/prefill_recurrence.metal:42-285): one threadgroup
+ * of tgs threads per head walks the T positions of qkv [T, qkv_dim] = [Q | K | V] (H heads each):
+ * conv1d + SiLU on the head's channels (written back as fp16), L2 norm of Q and of K in place
+ * (scale = 1 / max(norm, l2_eps)), gates in fp32, then on the [H, Dv, Dk] state: decay (rounded
+ * to fp16), kv_mem[v] = sum_k state[v, k] key[k], delta = (value - kv_mem) beta, state <-
+ * half(state + delta[v] key[k]), out[v] = half(sum_k state[v, k] (q[k] head_scale)).  b / a
+ * [T, H]; out [T, H, D]; conv_state [qkv_dim, conv_k] in place. */
+SO_API int so_deltanet_recurrence_prefill_fused(uint16_t *state, uint16_t *conv_state, uint16_t *qkv, const uint16_t *conv_weight,
+                                                const uint16_t *a_log, const uint16_t *dt_bias, const uint16_t *b_buf,
+                                                const uint16_t *a_buf, uint16_t *out, int head_dim, int heads, int seq_len, int qkv_dim,
+                                                int conv_k, float head_scale, float l2_eps, int tgs) {
+    if (head_dim <= 0 || head_dim > 256 || heads <= 0 || conv_k <= 0 || conv_k > 8 || qkv_dim < 3 * heads * head_dim || seq_len < 0 ||
+        tgs <= 0 || tgs % 32 || tgs > 1024)
+        return SO_ERR_GEOMETRY;
+    const int D = head_dim, HD = heads * head_dim;
+    for (int h = 0; h < heads; ++h) {
+        uint16_t *S = state + (size_t)h * D * D;
+        for (int pos = 0; pos < seq_len; ++pos) {
+            uint16_t *x = qkv + (size_t)pos * qkv_dim;
+            for (int i = 0; i < 3 * D; ++i) {
+                const int ch = (i / D) * HD + h * D + i % D;
+                uint16_t *st = conv_state + (size_t)ch * conv_k;
+                const uint16_t *w = conv_weight + (size_t)ch * conv_k;
+                for (int t = 0; t + 1 < conv_k; ++t) st[t] = st[t + 1];
+                st[conv_k - 1] = x[ch];
+                float acc = 0.0f;
+                for (int t = 0; t < conv_k; ++t) acc += h2f(st[t]) * h2f(w[t]);
+                x[ch] = f2h(acc / (1.0f + expf(-acc)));
+            }
+            for (int part = 0; part < 2; ++part) {
+                uint16_t *p = x + part * HD + h * D;
+                float f[256];
+                for (int i = 0; i < D; ++i) f[i] = h2f(p[i]);
+                const float scale = 1.0f / fmaxf(sqrtf(tg_sumsq(f, D, tgs)), l2_eps);
+                for (int i = 0; i < D; ++i) p[i] = f2h(f[i] * scale);
+            }
+            const uint16_t *q = x + h * D, *k = x + HD + h * D, *v = x + 2 * HD + h * D;
+            float beta, g;
+            plain_gates(b_buf[(size_t)pos * heads + h], a_buf[(size_t)pos * heads + h], a_log[h], dt_bias[h], &beta, &g);
+            const float decay = expf(g);
+            for (int vi = 0; vi < D; ++vi) {
+                uint16_t *row = S + (size_t)vi * D;
+                float acc = 0.0f;
+                for (int kk = 0; kk < D; ++kk) {
+                    row[kk] = f2h(h2f(row[kk]) * decay);
+                    acc += h2f(row[kk]) * h2f(k[kk]);
+                }
+                const float delta = (h2f(v[vi]) - acc) * beta;
+                float o = 0.0f;
+                for (int kk = 0; kk < D; ++kk) {
+                    row[kk] = f2h(h2f(row[kk]) + delta * h2f(k[kk]));
+                    o += h2f(row[kk]) * (h2f(q[kk]) * head_scale);
+                }
+                out[((size_t)pos * heads + h) * D + vi] = f2h(o);
+            }
+        }
+    }
+    return SO_OK;
+}
+
 /* rms_norm_gated (norms.metal:1093-1143): per head, out = half(w * (x * rsqrt(mean(x^2) + eps)) *
  * silu(g)), silu(g) = g / (1 + exp(-g)) in fp32; weight [D] shared by the heads. */
 SO_API int so_rms_norm_gated(const uint16_t *input, const uint16_t *gate, const uint16_t *weight, uint16_t *out, int head_dim,

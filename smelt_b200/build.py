@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(OUT_DIR, "libsmelt_cuda.so")
-SOURCES = ["runtime.cu", "dispatch.cu", "builder.cu", "tp.cu", "affine_matvec.cu", "affine_stream.cu", "affine_imma.cu", "affine_qmm.cu", "affine_qmm_wide.cu", "attention.cu", "glue.cu", "signed_matvec.cu", "signed_imma.cu", "no_alloc.cu", "package_reader.cu", "snapshot.cu", "prefill.cu", "deltanet.cu", "bitplane.cu", "elementwise.cu"]
+SOURCES = ["runtime.cu", "dispatch.cu", "builder.cu", "tp.cu", "affine_matvec.cu", "affine_stream.cu", "affine_imma.cu", "affine_qmm.cu", "affine_qmm_wide.cu", "attention.cu", "glue.cu", "signed_matvec.cu", "signed_imma.cu", "no_alloc.cu", "package_reader.cu", "snapshot.cu", "prefill.cu", "deltanet.cu", "recurrence_steps.cu", "bitplane.cu", "elementwise.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-DSMELT_BUILD",

@@ -213,6 +213,19 @@ bool parse_pipeline(const char* entry, Pipeline* out) {
         {"conv1d_update_silu_prefill_checkpoint", PK_CONV1D_SILU_PREFILL, 1, false},
         {"deltanet_recurrence_mlx_prefill", PK_DELTANET_PREFILL, 0, false},
         {"deltanet_recurrence_mlx_prefill_checkpoint", PK_DELTANET_PREFILL, 1, false},
+        // the DeltaNet step as separate launches and the one-CTA-per-head fused forms (recurrence.metal:44-503, :836-862,
+        // prefill_recurrence.metal:42-285); bits = which of a family
+        {"compute_gates", PK_DN_GATES, 0, false},
+        {"state_decay", PK_DN_STATE_UPDATE, 0, false},
+        {"outer_product_update", PK_DN_STATE_UPDATE, 1, false},
+        {"state_decay_update", PK_DN_STATE_UPDATE, 2, false},
+        {"kv_mem_readout", PK_DN_READOUT, 0, false},
+        {"kv_readout_delta", PK_DN_READOUT, 1, false},
+        {"gates_kv_readout_delta", PK_DN_READOUT, 2, false},
+        {"query_readout", PK_DN_READOUT, 3, false},
+        {"compute_delta", PK_DN_DELTA, 0, false},
+        {"deltanet_recurrence_fused", PK_DN_FUSED_DECODE, 0, false},
+        {"deltanet_recurrence_prefill", PK_DN_FUSED_PREFILL, 0, false},
     };
     // Activation bit-plane producers and consumers (Resources/Shaders/signed_quant.metal:751-2245):
     // the plane count is part of the name.
@@ -1273,6 +1286,132 @@ smelt_status run_record(Interp& in, const smelt_dispatch_record& rec_in) {
             in.launches += 1;
             return check_cuda(ctx, launch_deltanet_recurrence_prefill(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const __half*)r.buf[3].ptr,
                                                                       (const __half*)r.buf[4].ptr, (const __half*)r.buf[5].ptr, (__half*)r.buf[6].ptr, (int)d, (int)hv, (int)hqk, (int)seq_len, history), p.name.c_str());
+        }
+        case PK_DN_GATES: {
+            // recurrence.metal:839-847: 0 b, 1 a, 2 A_log, 3 dt_bias, 4 beta out, 5 g out, 6 numHeads.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_BUF(4); NEED_BUF(5); NEED_U32(6, heads);
+            if (heads == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "compute_gates: no heads");
+            for (int i = 0; i < 6; ++i)
+                if (r.buf[i].avail < (size_t)heads * 2) return fail(ctx, SMELT_ERR_OUT_OF_RANGE, "compute_gates: a binding is shorter than numHeads halves");
+            in.launches += 1;
+            return check_cuda(ctx, launch_dn_compute_gates(l, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const __half*)r.buf[3].ptr,
+                                                           (__half*)r.buf[4].ptr, (__half*)r.buf[5].ptr, (int)heads), "compute_gates");
+        }
+        case PK_DN_STATE_UPDATE: {
+            // state_decay (recurrence.metal:48-55): 0 state, 1 g, 2 headDim.  outer_product_update (:113-121): 0 state, 1 key,
+            // 2 delta (fp32), 3 headDim.  state_decay_update (:246-255): 0 state, 1 g, 2 key, 3 delta, 4 headDim.  One
+            // threadgroup per head: grid.x heads (state_decay dispatched by threads: grid.x = heads * D * D).
+            const int form = p.bits, ig = form == 1 ? -1 : 1, ikey = form == 0 ? -1 : (form == 1 ? 1 : 2), idelta = ikey < 0 ? -1 : ikey + 1;
+            const int id = form == 0 ? 2 : (form == 1 ? 3 : 4);
+            NEED_BUF(0);
+            uint32_t d = 0;
+            if (!host_u32(in, r, id, &d) || d == 0 || d > 1024) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": headDim constant is missing or out of range");
+            uint32_t heads = rec.grid[0];
+            if ((rec.style & 3) == 1) {
+                if (heads % (d * d)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a grid of threads must hold heads * headDim^2");
+                heads /= d * d;
+            }
+            if (heads == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": no heads in the grid");
+            NEED_BYTES(0, (size_t)heads * d * d * 2);
+            const __half *g = nullptr, *key = nullptr;
+            const float* delta = nullptr;
+            if (ig >= 0) {
+                if (!r.buf[ig].present || r.buf[ig].avail < (size_t)heads * 2) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the gate binding is missing or short");
+                g = (const __half*)r.buf[ig].ptr;
+            }
+            if (ikey >= 0) {
+                if (!r.buf[ikey].present || r.buf[ikey].avail < (size_t)heads * d * 2 || !r.buf[idelta].present || r.buf[idelta].avail < (size_t)heads * d * 4)
+                    return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the key or delta binding is missing or short");
+                key = (const __half*)r.buf[ikey].ptr;
+                delta = (const float*)r.buf[idelta].ptr;
+            }
+            in.launches += 1;
+            return check_cuda(ctx, launch_dn_state_update(l, (__half*)r.buf[0].ptr, g, key, delta, (int)d, (int)heads), p.name.c_str());
+        }
+        case PK_DN_READOUT: {
+            // kv_mem_readout (recurrence.metal:70-77): 0 state, 1 key, 2 kv_mem (fp32), 3 headDim.  kv_readout_delta (:150-160):
+            // 0 state, 1 key, 2 value, 3 g, 4 beta, 5 delta (fp32), 6 headDim.  gates_kv_readout_delta (:186-199): 0 state, 1 key,
+            // 2 value, 3 b, 4 a, 5 A_log, 6 dt_bias, 7 delta, 8 g out, 9 headDim.  query_readout (:282-290): 0 state, 1 query,
+            // 2 out, 3 headDim, 4 scale.  grid.x = heads.
+            const int mode = p.bits;
+            const int nbuf = mode == 0 ? 3 : (mode == 1 ? 6 : (mode == 2 ? 9 : 3));
+            for (int i = 0; i < nbuf; ++i)
+                if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": a buffer binding is missing");
+            uint32_t d = 0, scale_bits = 0;
+            if (!host_u32(in, r, nbuf, &d) || d == 0 || d > 256) return fail(ctx, SMELT_ERR_UNSUPPORTED, p.name + ": headDim constant missing or above 256");
+            if (mode == 3 && !host_u32(in, r, 4, &scale_bits)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": the scale constant is missing");
+            const uint32_t heads = rec.grid[0];
+            if (heads == 0) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, p.name + ": no heads in the grid");
+            const size_t vec = (size_t)heads * d * 2, hb = (size_t)heads * 2;
+            NEED_BYTES(0, (size_t)heads * d * d * 2); NEED_BYTES(1, vec);
+            const __half *value = nullptr, *g = nullptr, *beta = nullptr, *b = nullptr, *a = nullptr, *al = nullptr, *dt = nullptr;
+            float* out32 = nullptr;
+            __half *out16 = nullptr, *g_out = nullptr;
+            if (mode == 0) {
+                NEED_BYTES(2, vec * 2);
+                out32 = (float*)r.buf[2].ptr;
+            } else if (mode == 1) {
+                NEED_BYTES(2, vec); NEED_BYTES(3, hb); NEED_BYTES(4, hb); NEED_BYTES(5, vec * 2);
+                value = (const __half*)r.buf[2].ptr; g = (const __half*)r.buf[3].ptr; beta = (const __half*)r.buf[4].ptr; out32 = (float*)r.buf[5].ptr;
+            } else if (mode == 2) {
+                NEED_BYTES(2, vec); NEED_BYTES(3, hb); NEED_BYTES(4, hb); NEED_BYTES(5, hb); NEED_BYTES(6, hb); NEED_BYTES(7, vec * 2); NEED_BYTES(8, hb);
+                value = (const __half*)r.buf[2].ptr; b = (const __half*)r.buf[3].ptr; a = (const __half*)r.buf[4].ptr; al = (const __half*)r.buf[5].ptr;
+                dt = (const __half*)r.buf[6].ptr; out32 = (float*)r.buf[7].ptr; g_out = (__half*)r.buf[8].ptr;
+            } else {
+                NEED_BYTES(2, vec);
+                out16 = (__half*)r.buf[2].ptr;
+            }
+            in.launches += 1;
+            return check_cuda(ctx, launch_dn_readout(l, mode, (const __half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, value, g, beta, b, a, al, dt, out32, out16, g_out,
+                                                     (int)d, as_f32(scale_bits), (int)heads), p.name.c_str());
+        }
+        case PK_DN_DELTA: {
+            // recurrence.metal:95-102: 0 value, 1 kv_mem (fp32), 2 beta, 3 delta (fp32), 4 headDim; one thread per element.
+            NEED_BUF(0); NEED_BUF(1); NEED_BUF(2); NEED_BUF(3); NEED_U32(4, d);
+            const uint64_t total = (rec.style & 3) == 1 ? rec.grid[0] : (uint64_t)rec.grid[0] * (rec.threadgroup[0] ? rec.threadgroup[0] : 1);
+            if (d == 0 || total == 0 || total % d || total > (1u << 30)) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "compute_delta: the grid must hold heads * headDim threads");
+            const uint32_t heads = (uint32_t)(total / d);
+            NEED_BYTES(0, total * 2); NEED_BYTES(1, total * 4); NEED_BYTES(2, (size_t)heads * 2); NEED_BYTES(3, total * 4);
+            in.launches += 1;
+            return check_cuda(ctx, launch_dn_compute_delta(l, (const __half*)r.buf[0].ptr, (const float*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (float*)r.buf[3].ptr, (int)d, (int)heads), "compute_delta");
+        }
+        case PK_DN_FUSED_DECODE: {
+            // recurrence.metal:310-333: 0 state [H, Dv, Dk], 1 qkv, 2 b, 3 a, 4 A_log, 5 dt_bias, 6 out, 7 conv state, 8 conv weight,
+            // 9 z, 10 norm weight, 11 headDim, 12 headScale, 13 qkvDim, 14 convK, 15 numHeads, 16 rmsEps; one threadgroup per head,
+            // whose width fixes the order of the three sums of squares.
+            for (int i = 0; i <= 10; ++i)
+                if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "deltanet_recurrence_fused: a buffer binding is missing");
+            NEED_U32(11, d); NEED_U32(12, scale_bits); NEED_U32(13, qkv_dim); NEED_U32(14, conv_k); NEED_U32(15, heads); NEED_U32(16, eps_bits);
+            const int tgs = rec.threadgroup[0] ? (int)rec.threadgroup[0] : 256;
+            if (d == 0 || d % 32 || d > 256 || heads == 0 || conv_k == 0 || conv_k > 8 || (uint64_t)3 * heads * d > qkv_dim || tgs % 32 || tgs > 1024)
+                return fail(ctx, SMELT_ERR_UNSUPPORTED, "deltanet_recurrence_fused: head_dim a multiple of 32 up to 256, conv kernel up to 8, threadgroup a multiple of 32");
+            const size_t hb = (size_t)heads * 2, hd = (size_t)heads * d * 2, cs = (size_t)qkv_dim * conv_k * 2;
+            NEED_BYTES(0, hd * d); NEED_BYTES(1, (size_t)qkv_dim * 2); NEED_BYTES(2, hb); NEED_BYTES(3, hb); NEED_BYTES(4, hb); NEED_BYTES(5, hb); NEED_BYTES(6, hd);
+            NEED_BYTES(7, cs); NEED_BYTES(8, cs); NEED_BYTES(9, hd); NEED_BYTES(10, (size_t)d * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_dn_fused_decode(l, (__half*)r.buf[0].ptr, (const __half*)r.buf[1].ptr, (const __half*)r.buf[2].ptr, (const __half*)r.buf[3].ptr,
+                                                          (const __half*)r.buf[4].ptr, (const __half*)r.buf[5].ptr, (__half*)r.buf[6].ptr, (__half*)r.buf[7].ptr,
+                                                          (const __half*)r.buf[8].ptr, (const __half*)r.buf[9].ptr, (const __half*)r.buf[10].ptr, (int)d, as_f32(scale_bits),
+                                                          (int)qkv_dim, (int)conv_k, (int)heads, as_f32(eps_bits), tgs), "deltanet_recurrence_fused");
+        }
+        case PK_DN_FUSED_PREFILL: {
+            // prefill_recurrence.metal:42-62: 0 state [H, Dv, Dk], 1 conv state, 2 qkv [T, C] (in place), 3 conv weight, 4 A_log,
+            // 5 dt_bias, 6 b [T, H], 7 a [T, H], 8 out [T, H, D], 9 headDim, 10 numHeads, 11 seqLen, 12 qkvDim, 13 convKernel,
+            // 14 headScale, 15 l2Eps; one threadgroup of headDim threads per head.
+            for (int i = 0; i <= 8; ++i)
+                if (!r.buf[i].present || r.buf[i].pos_strided) return fail(ctx, SMELT_ERR_BAD_ARGUMENT, "deltanet_recurrence_prefill: a buffer binding is missing");
+            NEED_U32(9, d); NEED_U32(10, heads); NEED_U32(11, seq_len); NEED_U32(12, qkv_dim); NEED_U32(13, conv_k); NEED_U32(14, scale_bits); NEED_U32(15, eps_bits);
+            const int tgs = rec.threadgroup[0] ? (int)rec.threadgroup[0] : (int)((d + 31) / 32 * 32);
+            if (d == 0 || d > 256 || heads == 0 || conv_k == 0 || conv_k > 8 || (uint64_t)3 * heads * d > qkv_dim || tgs % 32 || tgs > 1024)
+                return fail(ctx, SMELT_ERR_UNSUPPORTED, "deltanet_recurrence_prefill: head_dim up to 256, conv kernel up to 8, threadgroup a multiple of 32");
+            const size_t hb = (size_t)heads * 2, cs = (size_t)qkv_dim * conv_k * 2;
+            NEED_BYTES(0, (size_t)heads * d * d * 2); NEED_BYTES(1, cs); NEED_BYTES(2, (size_t)seq_len * qkv_dim * 2); NEED_BYTES(3, cs); NEED_BYTES(4, hb); NEED_BYTES(5, hb);
+            NEED_BYTES(6, (size_t)seq_len * hb); NEED_BYTES(7, (size_t)seq_len * hb); NEED_BYTES(8, (size_t)seq_len * heads * d * 2);
+            in.launches += 1;
+            return check_cuda(ctx, launch_dn_fused_prefill(l, (__half*)r.buf[0].ptr, (__half*)r.buf[1].ptr, (__half*)r.buf[2].ptr, (const __half*)r.buf[3].ptr,
+                                                           (const __half*)r.buf[4].ptr, (const __half*)r.buf[5].ptr, (const __half*)r.buf[6].ptr, (const __half*)r.buf[7].ptr,
+                                                           (__half*)r.buf[8].ptr, (int)d, (int)heads, (int)seq_len, (int)qkv_dim, (int)conv_k, as_f32(scale_bits), as_f32(eps_bits), tgs),
+                              "deltanet_recurrence_prefill");
         }
         case PK_RMS_NORM_GATED: {
             // norms.metal:1093-1099: 0 in [H, D], 1 gate [H, D], 2 weight [D], 3 out, 4 headDim, 5 eps; one threadgroup per

@@ -52,6 +52,15 @@ cudaError_t launch_conv1d_update_silu_prefill(const Launch& l, __half* state, __
 cudaError_t launch_deltanet_recurrence_prefill(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, int head_dim, int value_heads, int qk_heads, int seq_len, __half* history);
 cudaError_t launch_deltanet_recurrence_decode(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, int head_dim, int value_heads, int qk_heads);
 cudaError_t launch_rms_norm_gated(const Launch& l, const __half* input, const __half* gate, const __half* weight, __half* out, int head_dim, float eps, int heads, int tgs, bool precise_d128);
+// The DeltaNet step as separate launches and its two one-CTA-per-head fused forms (recurrence_steps.cu).
+// launch_dn_state_update: state_decay (key null), outer_product_update (g_val null), state_decay_update (both).
+// launch_dn_readout mode: 0 kv_mem_readout, 1 kv_readout_delta, 2 gates_kv_readout_delta, 3 query_readout.
+cudaError_t launch_dn_compute_gates(const Launch& l, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* beta_out, __half* g_out, int heads);
+cudaError_t launch_dn_state_update(const Launch& l, __half* state, const __half* g_val, const __half* key, const float* delta, int head_dim, int heads);
+cudaError_t launch_dn_readout(const Launch& l, int mode, const __half* state, const __half* vec, const __half* value, const __half* g_val, const __half* beta, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, float* out_f32, __half* out_f16, __half* g_out, int head_dim, float scale, int heads);
+cudaError_t launch_dn_compute_delta(const Launch& l, const __half* value, const float* kv_mem, const __half* beta, float* delta, int head_dim, int heads);
+cudaError_t launch_dn_fused_decode(const Launch& l, __half* state, const __half* qkv, const __half* b_proj, const __half* a_proj, const __half* a_log, const __half* dt_bias, __half* out, __half* conv_state, const __half* conv_weight, const __half* z_proj, const __half* norm_weight, int head_dim, float head_scale, int qkv_dim, int conv_k, int heads, float rms_eps, int tgs);
+cudaError_t launch_dn_fused_prefill(const Launch& l, __half* state, __half* conv_state, __half* qkv, const __half* conv_weight, const __half* a_log, const __half* dt_bias, const __half* b_buf, const __half* a_buf, __half* out, int head_dim, int heads, int seq_len, int qkv_dim, int conv_k, float head_scale, float l2_eps, int tgs);
 cudaError_t launch_fp16_matvec(const Launch& l, const __half* w, const __half* x, __half* y, int rows, int cols, int batch, int sm_count);
 
 // attention.cu — split-K flash-decode.  scratch holds fp32 partials; see attention_scratch_bytes.

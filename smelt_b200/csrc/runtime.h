@@ -75,6 +75,12 @@ enum PipeKind : int {
     PK_BITPLANE_MATVEC,
     PK_BITPLANE_ADD,
     PK_BITPLANE_GATEUP,
+    PK_DN_GATES,
+    PK_DN_STATE_UPDATE,
+    PK_DN_READOUT,
+    PK_DN_DELTA,
+    PK_DN_FUSED_DECODE,
+    PK_DN_FUSED_PREFILL,
 };
 
 struct Pipeline {
